@@ -1,0 +1,214 @@
+/*
+ * pm_b200 — C ABI of the B200 (sm_100a) Mamba2 SSD block backend.
+ *
+ * Every entry point takes plain pointers and sizes.  Pointers named d_* are device
+ * pointers on the current CUDA device; h_* are host pointers.  `stream` is a
+ * cudaStream_t passed as void* (NULL = the legacy default stream).  All tensors are
+ * row-major (last axis fastest) unless a leading dimension is given.  Every function
+ * returns a pmb_status; pmb_last_error() returns the text of the last failure on the
+ * calling thread.  Nothing here falls back to the CPU: an unsupported request is an
+ * error.  The library is not re-entrant per model handle (one host thread per GPU
+ * rank, like the reference's single-threaded step loop, crates/pm-cli/src/train_cmd.rs:220).
+ *
+ * Symbols and the reference interface each one stands behind (paths relative to the
+ * reference checkout):
+ *   pmb_gemm_f32              Ops::matmul                 crates/pm-core/src/ops.rs (matmul), block.rs:143-144,224-225
+ *   pmb_conv_silu_dt_fwd/bwd  Ops::conv1d+silu+softplus   crates/pm-core/src/mamba2/block.rs:150-163,184-188
+ *   pmb_ssd_scan_fwd/bwd      Ops::ssd_scan               crates/pm-core/src/ops.rs:345-352, mamba2/ssd_ops.rs:61-284
+ *   pmb_gated_rmsnorm_fwd/bwd silu/mul/Ops::rmsnorm       crates/pm-core/src/mamba2/block.rs:216-222, ops.rs:91-96
+ *   pmb_mamba2_block_fwd/bwd  Mamba2Block::forward + its autograd backward   mamba2/block.rs:118-226
+ *   pmb_mamba2_step           Mamba2Block::step           crates/pm-core/src/mamba2/block.rs:278-417
+ *   pmb_stack_fwd_ckpt/bwd    ContextEncoder::forward_checkpointed + checkpoint_backward
+ *                                                         photon/encoder.rs:73-87, checkpoint.rs:68-135
+ *   pmb_lm_*                  FlatMamba::forward_checkpointed_hidden + fused CE + backward
+ *                                                         flat.rs:122-161, pm-train/src/loss.rs:39-69,121-138
+ */
+#ifndef PM_B200_H
+#define PM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum pmb_status {
+  PMB_OK = 0,
+  PMB_ERR_SHAPE = 1,        /* dimension / divisibility / alignment violation */
+  PMB_ERR_UNSUPPORTED = 2,  /* dtype or feature this build does not implement */
+  PMB_ERR_CUDA = 3,         /* a CUDA runtime or driver call failed */
+  PMB_ERR_WORKSPACE = 4,    /* caller-provided workspace too small */
+  PMB_ERR_DEVICE_STATUS = 5,/* a kernel gave up on a bounded wait and raised its status word */
+  PMB_ERR_ARG = 6           /* NULL pointer or invalid enum */
+} pmb_status;
+
+/* Mirror of Mamba2Config (crates/pm-core/src/mamba2/block.rs:48-57). */
+typedef struct pmb_mamba2_config {
+  int32_t d_model;
+  int32_t d_state;     /* N */
+  int32_t d_head;      /* P */
+  int32_t n_heads;     /* H */
+  int32_t n_groups;    /* 1 or n_heads */
+  int32_t d_conv;      /* K, 2..8 */
+  int32_t block_len;   /* SSD chunk length Q */
+  float   rmsnorm_eps;
+} pmb_mamba2_config;
+
+/* Parameter order of Mamba2Block::append_params (block.rs:440-450). All fp32. */
+typedef struct pmb_block_params {
+  const float* in_proj_weight;   /* (D, J)  used as x @ W */
+  const float* conv1d_weight;    /* (X, 1, K) */
+  const float* conv1d_bias;      /* (X) */
+  const float* a_log;            /* (H) */
+  const float* d_skip;           /* (H) */
+  const float* dt_bias;          /* (H) */
+  const float* norm_weight;      /* (I) */
+  const float* out_proj_weight;  /* (I, D) */
+} pmb_block_params;
+
+typedef struct pmb_block_grads {
+  float* in_proj_weight;
+  float* conv1d_weight;
+  float* conv1d_bias;
+  float* a_log;
+  float* d_skip;
+  float* dt_bias;
+  float* norm_weight;
+  float* out_proj_weight;
+} pmb_block_grads;
+
+const char* pmb_last_error(void);
+/* Library build string ("pm_b200 <ver> sm_100a"). */
+const char* pmb_version(void);
+/* Number of kernels this library has launched since load (all threads). */
+int64_t pmb_launch_count(void);
+/* Reads and clears the device status word (0 = no kernel gave up on a bounded wait). */
+pmb_status pmb_device_status(int32_t* h_word_out);
+
+/* ---- GEMM (Ops::matmul).  C[M,N] = op(A)·op(B) (+ R).  fp32 storage.
+ * trans_a = 0: A is (M,K) row-major with leading dimension lda; 1: A is stored (K,M).
+ * trans_b = 0: B is (K,N) row-major with ldb;                   1: B is stored (N,K).
+ * d_R (may be NULL) is added to the product (same shape/ld as C); d_R may equal d_C.
+ * engine: 0 = auto (tcgen05 3xTF32 when alignment allows, else SIMT), 1 = SIMT fp32, 2 = tcgen05 only. */
+pmb_status pmb_gemm_f32(void* stream, int32_t trans_a, int32_t trans_b, int64_t M, int64_t N, int64_t K,
+                        const float* d_A, int64_t lda, const float* d_B, int64_t ldb,
+                        float* d_C, int64_t ldc, const float* d_R, int32_t engine);
+
+/* ---- conv1d + SiLU + dt softplus (block.rs:150-163,184-188).
+ * d_xzd (B,T,J): columns [0,I) z, [I,I+X) xBC pre-conv, [I+X,J) dt_raw.
+ * d_act (B,T,X) = silu(causal depthwise conv + bias); d_dt (B,T,H) = softplus(dt_raw + dt_bias). */
+pmb_status pmb_conv_silu_dt_fwd(void* stream, const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen,
+                                const float* d_xzd, const float* d_conv_w, const float* d_conv_b,
+                                const float* d_dt_bias, float* d_act, float* d_dt);
+/* Backward of the conv+SiLU part.  d_dact (B,T,X) is the gradient w.r.t. d_act.  Writes the xBC
+ * columns of d_dxzd (B,T,J) and d_dconv_w (X,K), d_dconv_b (X).  d_ws: workspace of
+ * pmb_conv_bwd_workspace_bytes() bytes. */
+size_t pmb_conv_bwd_workspace_bytes(const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen);
+pmb_status pmb_conv_silu_bwd(void* stream, const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen,
+                             const float* d_xzd, const float* d_conv_w, const float* d_conv_b,
+                             const float* d_dact, float* d_dxzd, float* d_dconv_w, float* d_dconv_b,
+                             void* d_ws, size_t ws_bytes);
+
+/* ---- SSD scan (Ops::ssd_scan, ops.rs:345-352).  y[b,t,h,:] = sum_{s<=t} exp(sum_{k=s+1..t} a_k)(C_t·B_s) x_s.
+ * x (B,T,H,P) with row stride ldx between tokens (ldx >= H*P), a (B,T,H), b/c (B,T,G,N) with token
+ * stride ldbc (G = n_groups in {1,H}: groups are NOT broadcast in memory), y (B,T,H,P) stride ldy.
+ * T must be a multiple of block_len (the reference routes other T to its dense O(T^2) path; pass
+ * block_len = T for that case).  d_init_state / d_final_state (B,H,N,P) may be NULL.
+ * d_ws: workspace of pmb_ssd_workspace_bytes(); after the call it holds the per-chunk cumulative
+ * sums and entering states that pmb_ssd_scan_bwd reads (keep it untouched between the two). */
+size_t pmb_ssd_workspace_bytes(int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
+                               int32_t d_state, int32_t n_groups, int32_t block_len);
+pmb_status pmb_ssd_scan_fwd(void* stream, int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
+                            int32_t d_state, int32_t n_groups, int32_t block_len,
+                            const float* d_x, int64_t ldx, const float* d_a,
+                            const float* d_b, const float* d_c, int64_t ldbc,
+                            const float* d_init_state, float* d_y, int64_t ldy, float* d_final_state,
+                            void* d_ws, size_t ws_bytes);
+/* Backward: given dy, writes dx (stride lddx), da (B,T,H), db, dc (B,T,G,N; stride lddbc). */
+pmb_status pmb_ssd_scan_bwd(void* stream, int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
+                            int32_t d_state, int32_t n_groups, int32_t block_len,
+                            const float* d_x, int64_t ldx, const float* d_a,
+                            const float* d_b, const float* d_c, int64_t ldbc,
+                            const float* d_y, int64_t ldy, const float* d_dy, int64_t lddy,
+                            float* d_dx, int64_t lddx, float* d_da, float* d_db, float* d_dc, int64_t lddbc,
+                            void* d_ws, size_t ws_bytes);
+
+/* ---- gated RMSNorm (block.rs:216-222): out = rmsnorm(y * silu(z), w, eps) over the last axis (I).
+ * z has token stride ldz (it lives inside xzd).  d_rstd (rows) receives 1/sqrt(mean+eps). */
+pmb_status pmb_gated_rmsnorm_fwd(void* stream, int64_t rows, int32_t width, float eps,
+                                 const float* d_y, const float* d_z, int64_t ldz, const float* d_w,
+                                 float* d_out, float* d_rstd);
+size_t pmb_gated_rmsnorm_bwd_workspace_bytes(int64_t rows, int32_t width);
+pmb_status pmb_gated_rmsnorm_bwd(void* stream, int64_t rows, int32_t width,
+                                 const float* d_dout, const float* d_y, const float* d_z, int64_t ldz,
+                                 const float* d_w, const float* d_rstd,
+                                 float* d_dy, float* d_dz, int64_t lddz, float* d_dw,
+                                 void* d_ws, size_t ws_bytes);
+
+/* ---- one Mamba2 block (block.rs:118-226) and its backward with in-call recompute.
+ * fwd: out (B,T,D) = Block(x); if d_residual != NULL, out = residual + Block(x) (the caller's
+ * `h + Block(h)`, photon/encoder.rs:54-59; d_residual may equal d_x).  Nothing is kept for backward.
+ * bwd: recomputes the block from x (the only stored activation), then writes dx (B,T,D) — added to
+ * d_dx_accum when that is non-NULL (dx = dx_accum + dBlock/dx; may alias d_dx) — and all 8 parameter
+ * gradients (overwritten, not accumulated). */
+size_t pmb_mamba2_block_workspace_bytes(const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen);
+pmb_status pmb_mamba2_block_fwd(void* stream, const pmb_mamba2_config* cfg, const pmb_block_params* params,
+                                int32_t batch, int32_t seqlen, const float* d_x, const float* d_residual,
+                                float* d_out, void* d_ws, size_t ws_bytes);
+pmb_status pmb_mamba2_block_bwd(void* stream, const pmb_mamba2_config* cfg, const pmb_block_params* params,
+                                int32_t batch, int32_t seqlen, const float* d_x, const float* d_dout,
+                                const float* d_dx_accum, float* d_dx, const pmb_block_grads* grads,
+                                void* d_ws, size_t ws_bytes);
+
+/* ---- one-token decode (Mamba2Block::step, block.rs:278-417).  x_t (B,1,D) -> y_t (B,1,D);
+ * ssm_state (B,H,N,P) and conv_window (B,X,K-1) are updated in place. */
+size_t pmb_mamba2_step_workspace_bytes(const pmb_mamba2_config* cfg, int32_t batch);
+pmb_status pmb_mamba2_step(void* stream, const pmb_mamba2_config* cfg, const pmb_block_params* params,
+                           int32_t batch, const float* d_x_t, float* d_ssm_state, float* d_conv_window,
+                           float* d_y_t, void* d_ws, size_t ws_bytes);
+
+/* ---- residual stack with the re-planned checkpoint policy (encoder.rs:73-87, checkpoint.rs:68-135).
+ * Stored across the stack: the input of every block, d_saved (n_layers+1, B,T,D) (slot l = input of
+ * block l, slot n_layers = stack output).  Backward walks blocks last to first, recomputing each one.
+ * d_dhidden (B,T,D) is the gradient w.r.t. the stack output and is overwritten with the gradient
+ * w.r.t. the stack input.  `on_layer_done(layer, user)` (may be NULL) is called on the host right
+ * after layer `layer`'s gradient kernels have been enqueued (data-parallel callers enqueue that
+ * layer's gradient all-reduce from it). */
+typedef void (*pmb_layer_callback)(int32_t layer, void* user);
+pmb_status pmb_stack_fwd_ckpt(void* stream, const pmb_mamba2_config* cfg, int32_t n_layers,
+                              const pmb_block_params* layers, int32_t batch, int32_t seqlen,
+                              float* d_saved, void* d_ws, size_t ws_bytes);
+pmb_status pmb_stack_bwd(void* stream, const pmb_mamba2_config* cfg, int32_t n_layers,
+                         const pmb_block_params* layers, const pmb_block_grads* grads,
+                         int32_t batch, int32_t seqlen, const float* d_saved, float* d_dhidden,
+                         void* d_ws, size_t ws_bytes, pmb_layer_callback on_layer_done, void* user);
+
+/* ---- flat Mamba2 LM training step (flat.rs:122-161 + pm-train/src/loss.rs:121-138): tied embedding ->
+ * checkpointed stack -> tied head -> mean cross-entropy, forward + backward (no optimizer).
+ * The model handle owns activations and workspaces (cudaMalloc at create).  Parameters and gradients
+ * live in two caller-visible flat fp32 device buffers with identical layout:
+ *   [embedding (V,D)] then per layer the 8 tensors in append_params order, each 256-byte aligned;
+ * pmb_lm_param_offset() gives element offsets.  Ids/targets are int64 (crates/pm-core/src/dtype.rs I64). */
+typedef struct pmb_lm pmb_lm;
+pmb_status pmb_lm_create(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t vocab,
+                         int32_t batch, int32_t seqlen, pmb_lm** out);
+void       pmb_lm_destroy(pmb_lm* lm);
+int64_t    pmb_lm_param_count(const pmb_lm* lm);                 /* elements in the flat buffer (with padding) */
+int64_t    pmb_lm_param_offset(const pmb_lm* lm, int32_t layer, int32_t which); /* layer=-1: embedding; which 0..7 */
+float*     pmb_lm_params(pmb_lm* lm);                            /* device pointer, pmb_lm_param_count() floats */
+float*     pmb_lm_grads(pmb_lm* lm);                             /* device pointer, same layout */
+int64_t    pmb_lm_activation_bytes(const pmb_lm* lm);            /* stored activations + transient workspace */
+/* One fwd+bwd step with inputs already on the device.  Loss is left in a device scalar (pmb_lm_loss_device). */
+pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t* d_ids, const int64_t* d_targets,
+                              pmb_layer_callback on_layer_done, void* user);
+const float* pmb_lm_loss_device(const pmb_lm* lm);
+/* Same step through host buffers: copies ids/targets (pinned or pageable host memory) to the device,
+ * runs the step, copies the loss back and synchronises the stream.  This is the call a host trainer makes. */
+pmb_status pmb_lm_step_host(pmb_lm* lm, void* stream, const int64_t* h_ids, const int64_t* h_targets,
+                            float* h_loss, pmb_layer_callback on_layer_done, void* user);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PM_B200_H */

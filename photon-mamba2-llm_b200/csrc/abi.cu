@@ -1,0 +1,148 @@
+// C ABI entry points for the individual kernels, library-wide state, and the GEMM engine dispatch.
+#include "common.cuh"
+#include <cstdlib>
+#include "kernels.h"
+
+namespace pmb {
+
+thread_local char g_err[512] = "";
+std::atomic<long long> g_launches{0};
+
+pmb_status gemm(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                const float* B, int64_t ldb, float* C, int64_t ldc, const float* R, int engine) {
+  if (!A || !B || !C) return fail(PMB_ERR_ARG, "gemm: NULL operand");
+  // PMB_GEMM_ENGINE=simt routes engine-0 ("auto") calls to the fp32 FMA kernel: a debugging aid for
+  // telling a tensor-core problem from a problem elsewhere.  Explicit engine requests are honoured as given.
+  static const int forced = [] { const char* e = getenv("PMB_GEMM_ENGINE"); return (e && strcmp(e, "simt") == 0) ? 1 : 0; }();
+  if (engine == 0 && forced) engine = 1;
+  if (engine == 1) return gemm_simt(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
+  bool ok = gemm_tc_supported(ta, tb, M, N, K, A, lda, B, ldb, C, ldc);
+  if (engine == 2 && !ok) return fail(PMB_ERR_UNSUPPORTED, "gemm: tcgen05 engine needs 16-byte aligned operands and leading dimensions");
+  if (ok) return gemm_tc(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
+  return gemm_simt(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
+}
+
+}  // namespace pmb
+
+using namespace pmb;
+
+extern "C" const char* pmb_last_error(void) { return g_err; }
+extern "C" const char* pmb_version(void) { return "pm_b200 0.1 sm_100a"; }
+extern "C" int64_t pmb_launch_count(void) { return (int64_t)g_launches.load(); }
+
+extern "C" pmb_status pmb_device_status(int32_t* h_word_out) {
+  unsigned int w = 0;
+  PMB_TRY(read_clear_device_status(&w));
+  if (h_word_out) *h_word_out = (int32_t)w;
+  return PMB_OK;
+}
+
+extern "C" pmb_status pmb_gemm_f32(void* stream, int32_t trans_a, int32_t trans_b, int64_t M, int64_t N, int64_t K,
+                                   const float* d_A, int64_t lda, const float* d_B, int64_t ldb,
+                                   float* d_C, int64_t ldc, const float* d_R, int32_t engine) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail(PMB_ERR_SHAPE, "gemm: M, N, K must be positive (got %lld, %lld, %lld)", (long long)M, (long long)N, (long long)K);
+  if (lda < (trans_a ? M : K) || ldb < (trans_b ? K : N) || ldc < N) return fail(PMB_ERR_SHAPE, "gemm: leading dimension smaller than the row length");
+  if (engine < 0 || engine > 2) return fail(PMB_ERR_ARG, "gemm: engine must be 0, 1 or 2");
+  return gemm(static_cast<cudaStream_t>(stream), trans_a != 0, trans_b != 0, M, N, K, d_A, lda, d_B, ldb, d_C, ldc, d_R, engine);
+}
+
+extern "C" pmb_status pmb_conv_silu_dt_fwd(void* stream, const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen,
+                                           const float* d_xzd, const float* d_conv_w, const float* d_conv_b,
+                                           const float* d_dt_bias, float* d_act, float* d_dt) {
+  Dims d;
+  PMB_TRY(make_dims(cfg, batch, seqlen, &d));
+  if (!d_xzd || !d_conv_w || !d_act || (d_dt && !d_dt_bias)) return fail(PMB_ERR_ARG, "conv_silu_dt_fwd: NULL argument");
+  return conv_silu_dt_fwd(static_cast<cudaStream_t>(stream), d, d_xzd, d_conv_w, d_conv_b, d_dt_bias, d_act, d_dt);
+}
+
+extern "C" size_t pmb_conv_bwd_workspace_bytes(const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen) {
+  Dims d;
+  if (make_dims(cfg, batch, seqlen, &d) != PMB_OK) return 0;
+  return conv_bwd_ws_bytes(d);
+}
+
+extern "C" pmb_status pmb_conv_silu_bwd(void* stream, const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen,
+                                        const float* d_xzd, const float* d_conv_w, const float* d_conv_b,
+                                        const float* d_dact, float* d_dxzd, float* d_dconv_w, float* d_dconv_b,
+                                        void* d_ws, size_t ws_bytes) {
+  Dims d;
+  PMB_TRY(make_dims(cfg, batch, seqlen, &d));
+  if (!d_xzd || !d_conv_w || !d_dact || !d_dxzd || !d_dconv_w || !d_dconv_b || !d_ws) return fail(PMB_ERR_ARG, "conv_silu_bwd: NULL argument");
+  return conv_silu_bwd(static_cast<cudaStream_t>(stream), d, d_xzd, d_conv_w, d_conv_b, d_dact, d_dxzd, d_dconv_w, d_dconv_b, d_ws, ws_bytes);
+}
+
+static pmb_status ssd_check(int32_t batch, int32_t seqlen, int32_t H, int32_t P, int32_t N, int32_t G, int32_t Q) {
+  if (batch <= 0 || seqlen <= 0 || H <= 0 || P <= 0 || N <= 0) return fail(PMB_ERR_SHAPE, "ssd: non-positive dimension");
+  if (!(G == 1 || G == H)) return fail(PMB_ERR_SHAPE, "ssd: n_groups must be 1 or n_heads");
+  if (Q <= 0 || seqlen % Q != 0) return fail(PMB_ERR_SHAPE, "ssd: seqlen %d is not a multiple of block_len %d", seqlen, Q);
+  return PMB_OK;
+}
+
+extern "C" size_t pmb_ssd_workspace_bytes(int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
+                                          int32_t d_state, int32_t n_groups, int32_t block_len) {
+  if (ssd_check(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len) != PMB_OK) return 0;
+  return ssd_ws_layout(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, nullptr, 0, nullptr);
+}
+
+extern "C" pmb_status pmb_ssd_scan_fwd(void* stream, int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
+                                       int32_t d_state, int32_t n_groups, int32_t block_len,
+                                       const float* d_x, int64_t ldx, const float* d_a,
+                                       const float* d_b, const float* d_c, int64_t ldbc,
+                                       const float* d_init_state, float* d_y, int64_t ldy, float* d_final_state,
+                                       void* d_ws, size_t ws_bytes) {
+  PMB_TRY(ssd_check(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len));
+  if (!d_x || !d_a || !d_b || !d_c || !d_y || !d_ws) return fail(PMB_ERR_ARG, "ssd_scan_fwd: NULL argument");
+  if (ldx < (int64_t)n_heads * d_head || ldy < (int64_t)n_heads * d_head || ldbc < (int64_t)n_groups * d_state)
+    return fail(PMB_ERR_SHAPE, "ssd_scan_fwd: token stride smaller than the row length");
+  SsdWs ws;
+  if (ssd_ws_layout(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, d_ws, ws_bytes, &ws) == 0)
+    return fail(PMB_ERR_WORKSPACE, "ssd workspace too small");
+  SsdIn in{};
+  in.B = batch; in.T = seqlen; in.H = n_heads; in.P = d_head; in.N = d_state; in.G = n_groups; in.Q = block_len;
+  in.x = d_x; in.ldx = ldx; in.a = d_a; in.b = d_b; in.c = d_c; in.ldbc = ldbc;
+  return ssd_fwd(static_cast<cudaStream_t>(stream), in, d_init_state, d_y, ldy, d_final_state, ws);
+}
+
+extern "C" pmb_status pmb_ssd_scan_bwd(void* stream, int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
+                                       int32_t d_state, int32_t n_groups, int32_t block_len,
+                                       const float* d_x, int64_t ldx, const float* d_a,
+                                       const float* d_b, const float* d_c, int64_t ldbc,
+                                       const float* d_y, int64_t ldy, const float* d_dy, int64_t lddy,
+                                       float* d_dx, int64_t lddx, float* d_da, float* d_db, float* d_dc, int64_t lddbc,
+                                       void* d_ws, size_t ws_bytes) {
+  PMB_TRY(ssd_check(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len));
+  if (!d_x || !d_a || !d_b || !d_c || !d_y || !d_dy || !d_dx || !d_da || !d_db || !d_dc || !d_ws)
+    return fail(PMB_ERR_ARG, "ssd_scan_bwd: NULL argument");
+  SsdWs ws;
+  if (ssd_ws_layout(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, d_ws, ws_bytes, &ws) == 0)
+    return fail(PMB_ERR_WORKSPACE, "ssd workspace too small");
+  SsdIn in{};
+  in.B = batch; in.T = seqlen; in.H = n_heads; in.P = d_head; in.N = d_state; in.G = n_groups; in.Q = block_len;
+  in.x = d_x; in.ldx = ldx; in.a = d_a; in.b = d_b; in.c = d_c; in.ldbc = ldbc;
+  SsdGrads g{};
+  g.dx = d_dx; g.lddx = lddx; g.db = d_db; g.dc = d_dc; g.lddbc = lddbc; g.da = d_da;
+  return ssd_bwd(static_cast<cudaStream_t>(stream), in, d_y, ldy, d_dy, lddy, g, ws);
+}
+
+extern "C" pmb_status pmb_gated_rmsnorm_fwd(void* stream, int64_t rows, int32_t width, float eps,
+                                            const float* d_y, const float* d_z, int64_t ldz, const float* d_w,
+                                            float* d_out, float* d_rstd) {
+  if (rows <= 0 || width <= 0 || ldz < width) return fail(PMB_ERR_SHAPE, "gated_rmsnorm_fwd: bad shape");
+  if (!d_y || !d_z || !d_w || !d_out) return fail(PMB_ERR_ARG, "gated_rmsnorm_fwd: NULL argument");
+  return gated_rmsnorm_fwd(static_cast<cudaStream_t>(stream), rows, width, eps, d_y, d_z, ldz, d_w, d_out, d_rstd);
+}
+
+extern "C" size_t pmb_gated_rmsnorm_bwd_workspace_bytes(int64_t rows, int32_t width) {
+  if (rows <= 0 || width <= 0) return 0;
+  return gated_rmsnorm_bwd_ws_bytes(rows, width);
+}
+
+extern "C" pmb_status pmb_gated_rmsnorm_bwd(void* stream, int64_t rows, int32_t width,
+                                            const float* d_dout, const float* d_y, const float* d_z, int64_t ldz,
+                                            const float* d_w, const float* d_rstd,
+                                            float* d_dy, float* d_dz, int64_t lddz, float* d_dw,
+                                            void* d_ws, size_t ws_bytes) {
+  if (rows <= 0 || width <= 0 || ldz < width || lddz < width) return fail(PMB_ERR_SHAPE, "gated_rmsnorm_bwd: bad shape");
+  if (!d_dout || !d_y || !d_z || !d_w || !d_rstd || !d_dy || !d_dz || !d_dw || !d_ws) return fail(PMB_ERR_ARG, "gated_rmsnorm_bwd: NULL argument");
+  return gated_rmsnorm_bwd(static_cast<cudaStream_t>(stream), rows, width, d_dout, d_y, d_z, ldz, d_w, d_rstd, d_dy, d_dz, lddz, d_dw, d_ws, ws_bytes);
+}

@@ -1,0 +1,195 @@
+// Host orchestration of one Mamba2 block (forward, and backward with in-call recompute) and of the
+// residual stack with the re-planned checkpoint policy: across the stack only each block's input is
+// kept; everything else (projection outputs, conv activations, chunk states, gate inputs) lives in one
+// transient workspace that every layer reuses.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace pmb {
+
+__global__ void a_neg_kernel(const float* __restrict__ a_log, float* __restrict__ A, int H) {
+  int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h < H) A[h] = -expf(a_log[h]);
+}
+
+// One block per head: ddt_raw = ddt * sigmoid(dt_raw + bias) written into the dt columns of dxzd;
+// ddt_bias[h] = sum over tokens; da_log[h] = A[h] * dA[h]  (A = -exp(a_log)).
+__global__ void __launch_bounds__(256) dt_bwd_kernel(const float* __restrict__ xzd, float* __restrict__ dxzd, int64_t ld, int col0,
+                                                     const float* __restrict__ dt_bias, const float* __restrict__ ddt,
+                                                     const float* __restrict__ A, const float* __restrict__ dA,
+                                                     float* __restrict__ ddt_bias, float* __restrict__ da_log, int64_t rows, int H) {
+  __shared__ float red[32];
+  int h = blockIdx.x;
+  float bias = dt_bias[h], acc = 0.0f;
+  for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) {
+    float s = sigmoid_acc(xzd[r * ld + col0 + h] + bias);
+    float g = ddt[r * H + h] * s;
+    dxzd[r * ld + col0 + h] = g;
+    acc += g;
+  }
+  float tot = block_sum(acc, red);
+  if (threadIdx.x == 0) {
+    ddt_bias[h] = tot;
+    da_log[h] = A[h] * dA[h];
+  }
+}
+
+struct BlockWs {
+  float *xzd, *act, *dt, *y, *rstd, *normed, *Aneg;
+  SsdWs ssd;
+  float *dnormed, *dxzd, *dact, *ddt, *dA, *scratch;
+  size_t scratch_bytes;
+};
+
+static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* out) {
+  Arena ar(base, bytes);
+  BlockWs w{};
+  w.xzd = ar.take<float>((size_t)d.M * d.J);
+  w.act = ar.take<float>((size_t)d.M * d.X);
+  w.dt = ar.take<float>((size_t)d.M * d.H);
+  w.y = ar.take<float>((size_t)d.M * d.I);
+  w.rstd = ar.take<float>((size_t)d.M);
+  w.normed = ar.take<float>((size_t)d.M * d.I);
+  w.Aneg = ar.take<float>((size_t)d.H);
+  {
+    size_t need = ssd_ws_layout(d.B, d.T, d.H, d.P, d.N, d.G, d.Q, nullptr, 0, nullptr);
+    char* sub = ar.take<char>(need);
+    if (sub) ssd_ws_layout(d.B, d.T, d.H, d.P, d.N, d.G, d.Q, sub, need, &w.ssd);
+  }
+  w.dnormed = ar.take<float>((size_t)d.M * d.I);
+  w.dxzd = ar.take<float>((size_t)d.M * d.J);
+  w.dact = ar.take<float>((size_t)d.M * d.X);
+  w.ddt = ar.take<float>((size_t)d.M * d.H);
+  w.dA = ar.take<float>((size_t)d.H);
+  w.scratch_bytes = conv_bwd_ws_bytes(d);
+  size_t nb = gated_rmsnorm_bwd_ws_bytes(d.M, d.I);
+  if (nb > w.scratch_bytes) w.scratch_bytes = nb;
+  w.scratch = reinterpret_cast<float*>(ar.take<char>(w.scratch_bytes));
+  if (out) *out = w;
+  return ar.ok ? ar.used() : 0;
+}
+
+size_t block_ws_bytes(const Dims& d) { return block_ws_layout(d, nullptr, 0, nullptr); }
+
+static SsdIn ssd_inputs(const Dims& d, const pmb_block_params& p, const BlockWs& w) {
+  SsdIn in{};
+  in.B = d.B; in.T = d.T; in.H = d.H; in.P = d.P; in.N = d.N; in.G = d.G; in.Q = d.Q;
+  in.x = w.act; in.ldx = d.X;
+  in.dt = w.dt; in.A = w.Aneg; in.a = nullptr;
+  in.b = w.act + d.I; in.c = w.act + d.I + d.G * d.N; in.ldbc = d.X;
+  in.D = p.d_skip;
+  return in;
+}
+
+// Steps 1-8 of Mamba2Block::forward (block.rs:143-222): everything up to the normalised gate output.
+static pmb_status block_fwd_core(cudaStream_t st, const Dims& d, const pmb_block_params& p, const float* x, const BlockWs& w) {
+  PMB_TRY(gemm(st, 0, 0, d.M, d.J, d.D, x, d.D, p.in_proj_weight, d.J, w.xzd, d.J, nullptr, 0));
+  PMB_TRY(conv_silu_dt_fwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, p.dt_bias, w.act, w.dt));
+  a_neg_kernel<<<(unsigned)cdiv(d.H, 128), 128, 0, st>>>(p.a_log, w.Aneg, d.H);
+  PMB_LAUNCHED();
+  PMB_TRY(ssd_fwd(st, ssd_inputs(d, p, w), nullptr, w.y, d.I, nullptr, w.ssd));
+  PMB_TRY(gated_rmsnorm_fwd(st, d.M, d.I, d.eps, w.y, w.xzd, d.J, p.norm_weight, w.normed, w.rstd));
+  return PMB_OK;
+}
+
+pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const float* x, const float* residual,
+                     float* out, void* ws, size_t ws_bytes) {
+  BlockWs w;
+  if (block_ws_layout(d, ws, ws_bytes, &w) == 0 || !ws) return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_bytes(d));
+  PMB_TRY(block_fwd_core(st, d, p, x, w));
+  PMB_TRY(gemm(st, 0, 0, d.M, d.D, d.I, w.normed, d.I, p.out_proj_weight, d.D, out, d.D, residual, 0));
+  return PMB_OK;
+}
+
+pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const float* x, const float* dout,
+                     const float* dx_accum, float* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes) {
+  BlockWs w;
+  if (block_ws_layout(d, ws, ws_bytes, &w) == 0 || !ws) return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_bytes(d));
+  // recompute (the out_proj product itself is not needed for gradients)
+  PMB_TRY(block_fwd_core(st, d, p, x, w));
+  // out_proj: dW_out = normed^T dout;  dnormed = dout W_out^T
+  PMB_TRY(gemm(st, 1, 0, d.I, d.D, d.M, w.normed, d.I, dout, d.D, g.out_proj_weight, d.D, nullptr, 0));
+  PMB_TRY(gemm(st, 0, 1, d.M, d.I, d.D, dout, d.D, p.out_proj_weight, d.D, w.dnormed, d.I, nullptr, 0));
+  // gate + norm: dy (in place over dnormed), dz -> z columns of dxzd
+  PMB_TRY(gated_rmsnorm_bwd(st, d.M, d.I, w.dnormed, w.y, w.xzd, d.J, p.norm_weight, w.rstd, w.dnormed, w.dxzd, d.J,
+                            g.norm_weight, w.scratch, w.scratch_bytes));
+  // scan
+  SsdGrads sg{};
+  sg.dx = w.dact; sg.lddx = d.X;
+  sg.db = w.dact + d.I; sg.dc = w.dact + d.I + d.G * d.N; sg.lddbc = d.X;
+  sg.da = nullptr; sg.ddt = w.ddt; sg.dA = w.dA; sg.dD = g.d_skip;
+  PMB_TRY(ssd_bwd(st, ssd_inputs(d, p, w), w.y, d.I, w.dnormed, d.I, sg, w.ssd));
+  dt_bwd_kernel<<<(unsigned)d.H, 256, 0, st>>>(w.xzd, w.dxzd, d.J, d.I + d.X, p.dt_bias, w.ddt, w.Aneg, w.dA, g.dt_bias, g.a_log, d.M, d.H);
+  PMB_LAUNCHED();
+  // conv + SiLU
+  PMB_TRY(conv_silu_bwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, w.dact, w.dxzd, g.conv1d_weight, g.conv1d_bias,
+                        w.scratch, w.scratch_bytes));
+  // in_proj: dW_in = x^T dxzd;  dx = dxzd W_in^T (+ accumulated residual gradient)
+  PMB_TRY(gemm(st, 1, 0, d.D, d.J, d.M, x, d.D, w.dxzd, d.J, g.in_proj_weight, d.J, nullptr, 0));
+  PMB_TRY(gemm(st, 0, 1, d.M, d.D, d.J, w.dxzd, d.J, p.in_proj_weight, d.J, dx, d.D, dx_accum, 0));
+  return PMB_OK;
+}
+
+}  // namespace pmb
+
+// -----------------------------------------------------------------------------------------------
+// C ABI
+// -----------------------------------------------------------------------------------------------
+using namespace pmb;
+
+extern "C" size_t pmb_mamba2_block_workspace_bytes(const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen) {
+  Dims d;
+  if (make_dims(cfg, batch, seqlen, &d) != PMB_OK) return 0;
+  return block_ws_bytes(d);
+}
+
+extern "C" pmb_status pmb_mamba2_block_fwd(void* stream, const pmb_mamba2_config* cfg, const pmb_block_params* params,
+                                           int32_t batch, int32_t seqlen, const float* d_x, const float* d_residual,
+                                           float* d_out, void* d_ws, size_t ws_bytes) {
+  Dims d;
+  PMB_TRY(make_dims(cfg, batch, seqlen, &d));
+  if (!params || !d_x || !d_out) return fail(PMB_ERR_ARG, "block_fwd: NULL argument");
+  return block_fwd(static_cast<cudaStream_t>(stream), d, *params, d_x, d_residual, d_out, d_ws, ws_bytes);
+}
+
+extern "C" pmb_status pmb_mamba2_block_bwd(void* stream, const pmb_mamba2_config* cfg, const pmb_block_params* params,
+                                           int32_t batch, int32_t seqlen, const float* d_x, const float* d_dout,
+                                           const float* d_dx_accum, float* d_dx, const pmb_block_grads* grads,
+                                           void* d_ws, size_t ws_bytes) {
+  Dims d;
+  PMB_TRY(make_dims(cfg, batch, seqlen, &d));
+  if (!params || !grads || !d_x || !d_dout || !d_dx) return fail(PMB_ERR_ARG, "block_bwd: NULL argument");
+  return block_bwd(static_cast<cudaStream_t>(stream), d, *params, d_x, d_dout, d_dx_accum, d_dx, *grads, d_ws, ws_bytes);
+}
+
+extern "C" pmb_status pmb_stack_fwd_ckpt(void* stream, const pmb_mamba2_config* cfg, int32_t n_layers,
+                                         const pmb_block_params* layers, int32_t batch, int32_t seqlen,
+                                         float* d_saved, void* d_ws, size_t ws_bytes) {
+  Dims d;
+  PMB_TRY(make_dims(cfg, batch, seqlen, &d));
+  if (!layers || !d_saved || n_layers <= 0) return fail(PMB_ERR_ARG, "stack_fwd: bad argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  size_t slot = (size_t)d.M * d.D;
+  for (int l = 0; l < n_layers; ++l) {
+    const float* h = d_saved + (size_t)l * slot;
+    PMB_TRY(block_fwd(st, d, layers[l], h, h, d_saved + (size_t)(l + 1) * slot, d_ws, ws_bytes));
+  }
+  return PMB_OK;
+}
+
+extern "C" pmb_status pmb_stack_bwd(void* stream, const pmb_mamba2_config* cfg, int32_t n_layers,
+                                    const pmb_block_params* layers, const pmb_block_grads* grads,
+                                    int32_t batch, int32_t seqlen, const float* d_saved, float* d_dhidden,
+                                    void* d_ws, size_t ws_bytes, pmb_layer_callback on_layer_done, void* user) {
+  Dims d;
+  PMB_TRY(make_dims(cfg, batch, seqlen, &d));
+  if (!layers || !grads || !d_saved || !d_dhidden || n_layers <= 0) return fail(PMB_ERR_ARG, "stack_bwd: bad argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  size_t slot = (size_t)d.M * d.D;
+  // dh_{l-1} = dh_l + dBlock_l/dx  (checkpoint.rs:110-135 reproduces this sum through the residual adds)
+  for (int l = n_layers - 1; l >= 0; --l) {
+    PMB_TRY(block_bwd(st, d, layers[l], d_saved + (size_t)l * slot, d_dhidden, d_dhidden, d_dhidden, grads[l], d_ws, ws_bytes));
+    if (on_layer_done) on_layer_done(l, user);
+  }
+  return PMB_OK;
+}

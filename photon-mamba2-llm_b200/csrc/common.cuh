@@ -1,0 +1,124 @@
+// Shared host/device helpers for the pm_b200 library.
+#pragma once
+#include <cuda_runtime.h>
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include "../../include/pm_b200.h"
+
+namespace pmb {
+
+extern thread_local char g_err[512];
+extern std::atomic<long long> g_launches;
+
+inline pmb_status fail(pmb_status st, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return st;
+}
+
+#define PMB_CUDA(expr)                                                                         \
+  do {                                                                                         \
+    cudaError_t e__ = (expr);                                                                  \
+    if (e__ != cudaSuccess)                                                                    \
+      return pmb::fail(PMB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__),  \
+                       __FILE__, __LINE__);                                                    \
+  } while (0)
+
+#define PMB_TRY(expr)                   \
+  do {                                  \
+    pmb_status s__ = (expr);            \
+    if (s__ != PMB_OK) return s__;      \
+  } while (0)
+
+// Call after every kernel launch: counts it and surfaces launch-configuration errors.
+#define PMB_LAUNCHED()                                                                          \
+  do {                                                                                          \
+    pmb::g_launches.fetch_add(1, std::memory_order_relaxed);                                    \
+    cudaError_t e__ = cudaGetLastError();                                                       \
+    if (e__ != cudaSuccess)                                                                     \
+      return pmb::fail(PMB_ERR_CUDA, "kernel launch failed: %s (%s:%d)", cudaGetErrorString(e__), \
+                       __FILE__, __LINE__);                                                     \
+  } while (0)
+
+inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Bump allocator over a caller-provided workspace.
+struct Arena {
+  char* base;
+  size_t size;
+  size_t off = 0;
+  bool ok = true;
+  Arena(void* p, size_t n) : base(static_cast<char*>(p)), size(n) {}
+  template <class T>
+  T* take(size_t count) {
+    off = align_up(off, 256);
+    size_t bytes = count * sizeof(T);
+    if (base != nullptr && off + bytes > size) ok = false;
+    T* r = base ? reinterpret_cast<T*>(base + off) : nullptr;
+    off += bytes;
+    return r;
+  }
+  size_t used() const { return align_up(off, 256); }
+};
+
+struct Dims {
+  int B, T, D, N, P, H, G, K, Q, I, X, J, nc;
+  int64_t M;  // tokens
+  float eps;
+};
+
+inline pmb_status make_dims(const pmb_mamba2_config* c, int batch, int seqlen, Dims* d) {
+  if (!c) return fail(PMB_ERR_ARG, "config is NULL");
+  if (c->d_model <= 0 || c->d_state <= 0 || c->d_head <= 0 || c->n_heads <= 0 || batch <= 0 || seqlen <= 0)
+    return fail(PMB_ERR_SHAPE, "non-positive dimension in config/batch/seqlen");
+  if (!(c->n_groups == 1 || c->n_groups == c->n_heads))
+    return fail(PMB_ERR_SHAPE, "n_groups must be 1 or n_heads (got %d, H=%d)", c->n_groups, c->n_heads);
+  if (c->d_conv < 2 || c->d_conv > 8) return fail(PMB_ERR_SHAPE, "d_conv must be in 2..8 (got %d)", c->d_conv);
+  d->B = batch; d->T = seqlen; d->D = c->d_model; d->N = c->d_state; d->P = c->d_head; d->H = c->n_heads;
+  d->G = c->n_groups; d->K = c->d_conv;
+  // The reference routes block_len == 0, >= T or not dividing T to its dense path (ssd_ops.rs:70-78):
+  // one chunk spanning the whole sequence computes the same quantity.
+  int q = c->block_len;
+  if (q <= 0 || q >= seqlen || seqlen % q != 0) q = seqlen;
+  d->Q = q;
+  d->nc = seqlen / q;
+  d->I = d->H * d->P;
+  d->X = d->I + 2 * d->G * d->N;
+  d->J = d->I + d->X + d->H;
+  d->M = (int64_t)batch * seqlen;
+  d->eps = c->rmsnorm_eps;
+  return PMB_OK;
+}
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_acc(float x) { return 1.0f / (1.0f + expf(-x)); }
+// softplus in the reference's stable form max(x,0)+log(1+exp(-|x|)) (pm-candle ops_impl.rs:123-133)
+__device__ __forceinline__ float softplus_acc(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Block-wide sum for blockDim.x <= 1024 (multiple of 32); `red` is 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float r = (threadIdx.x < nw) ? red[threadIdx.x] : 0.0f;
+  if (w == 0) r = warp_sum(r);
+  if (threadIdx.x == 0) red[0] = r;
+  __syncthreads();
+  return red[0];
+}
+
+}  // namespace pmb

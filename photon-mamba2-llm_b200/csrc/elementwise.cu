@@ -1,0 +1,345 @@
+// HBM-bound kernels of the Mamba2 block: causal depthwise conv1d + bias + SiLU, dt softplus,
+// gated RMSNorm, their backward passes, and small deterministic reductions.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace pmb {
+
+// ---------------------------------------------------------------------------------------------
+// conv1d (causal, depthwise) + bias + SiLU, forward.   u[t,c] = b[c] + sum_k w[c,k] * xbc[t-(K-1)+k, c]
+// Layout stays (B,T,channels): a thread owns VEC adjacent channels and walks TT consecutive time steps
+// with the K-1 previous inputs in registers, so every global access is a coalesced vector access and
+// each input row is read (TT+K-1)/TT times.
+// ---------------------------------------------------------------------------------------------
+template <int K, int VEC>
+__global__ void __launch_bounds__(128) conv_silu_fwd_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
+                                                            const float* __restrict__ w, const float* __restrict__ bias,
+                                                            float* __restrict__ act, int X, int T, int TT) {
+  int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  if (c >= X) return;
+  int tblocks = (T + TT - 1) / TT;
+  int b = blockIdx.y / tblocks;
+  int t0 = (blockIdx.y % tblocks) * TT;
+  int t1 = min(t0 + TT, T);
+  float wr[VEC][K], br[VEC], win[VEC][K];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) {
+    br[v] = bias ? bias[c + v] : 0.0f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) wr[v][k] = w[(c + v) * K + k];
+  }
+  const float* src = xzd + (int64_t)b * T * ldx + col0 + c;
+#pragma unroll
+  for (int k = 0; k < K - 1; ++k) {
+    int t = t0 - (K - 1) + k;
+    if (VEC == 4) {
+      float4 q = t >= 0 ? *reinterpret_cast<const float4*>(src + (int64_t)t * ldx) : make_float4(0, 0, 0, 0);
+      win[0][k] = q.x; win[1 % VEC][k] = q.y; win[2 % VEC][k] = q.z; win[3 % VEC][k] = q.w;
+    } else {
+      win[0][k] = t >= 0 ? src[(int64_t)t * ldx] : 0.0f;
+    }
+  }
+  float* dst = act + (int64_t)b * T * X + c;
+  for (int t = t0; t < t1; ++t) {
+    if (VEC == 4) {
+      float4 q = *reinterpret_cast<const float4*>(src + (int64_t)t * ldx);
+      win[0][K - 1] = q.x; win[1 % VEC][K - 1] = q.y; win[2 % VEC][K - 1] = q.z; win[3 % VEC][K - 1] = q.w;
+    } else {
+      win[0][K - 1] = src[(int64_t)t * ldx];
+    }
+    float o[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      float u = br[v];
+#pragma unroll
+      for (int k = 0; k < K; ++k) u = fmaf(wr[v][k], win[v][k], u);
+      o[v] = u * sigmoid_acc(u);
+#pragma unroll
+      for (int k = 0; k < K - 1; ++k) win[v][k] = win[v][k + 1];
+    }
+    if (VEC == 4) *reinterpret_cast<float4*>(dst + (int64_t)t * X) = make_float4(o[0], o[1 % VEC], o[2 % VEC], o[3 % VEC]);
+    else dst[(int64_t)t * X] = o[0];
+  }
+}
+
+__global__ void dt_softplus_kernel(const float* __restrict__ xzd, int64_t ldx, int col0, const float* __restrict__ dt_bias,
+                                   float* __restrict__ dt, int64_t rows, int H) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * H) return;
+  int64_t r = i / H;
+  int h = (int)(i % H);
+  dt[i] = softplus_acc(xzd[r * ldx + col0 + h] + dt_bias[h]);
+}
+
+template <int K>
+static pmb_status launch_conv_fwd_k(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b, float* act) {
+  const int TT = 32;
+  bool vec = (d.X % 4 == 0) && (d.J % 4 == 0) && (d.I % 4 == 0) && ((reinterpret_cast<uintptr_t>(xzd) | reinterpret_cast<uintptr_t>(act)) % 16 == 0);
+  int tblocks = (d.T + TT - 1) / TT;
+  if (vec) {
+    dim3 grid((unsigned)cdiv(d.X / 4, 128), (unsigned)(d.B * tblocks));
+    conv_silu_fwd_kernel<K, 4><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T, TT);
+  } else {
+    dim3 grid((unsigned)cdiv(d.X, 128), (unsigned)(d.B * tblocks));
+    conv_silu_fwd_kernel<K, 1><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T, TT);
+  }
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
+pmb_status conv_silu_dt_fwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
+                            const float* dt_bias, float* act, float* dt) {
+  switch (d.K) {
+    case 2: PMB_TRY(launch_conv_fwd_k<2>(st, d, xzd, w, b, act)); break;
+    case 3: PMB_TRY(launch_conv_fwd_k<3>(st, d, xzd, w, b, act)); break;
+    case 4: PMB_TRY(launch_conv_fwd_k<4>(st, d, xzd, w, b, act)); break;
+    case 5: PMB_TRY(launch_conv_fwd_k<5>(st, d, xzd, w, b, act)); break;
+    case 6: PMB_TRY(launch_conv_fwd_k<6>(st, d, xzd, w, b, act)); break;
+    case 7: PMB_TRY(launch_conv_fwd_k<7>(st, d, xzd, w, b, act)); break;
+    case 8: PMB_TRY(launch_conv_fwd_k<8>(st, d, xzd, w, b, act)); break;
+    default: return fail(PMB_ERR_SHAPE, "d_conv %d unsupported", d.K);
+  }
+  if (dt) {
+    int64_t n = d.M * d.H;
+    dt_softplus_kernel<<<(unsigned)cdiv(n, 256), 256, 0, st>>>(xzd, d.J, d.I + d.X, dt_bias, dt, d.M, d.H);
+    PMB_LAUNCHED();
+  }
+  return PMB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// conv backward.  du = dact * silu'(u) with u recomputed from the pre-conv window;
+// dxbc[t',c] = sum_k w[c,k] du[t'+(K-1)-k, c];  dw[c,k] = sum_{b,t} du[t,c] xbc[t-(K-1)+k,c];  db = sum du.
+// A thread owns one channel and TT time steps; per-(block-row) partial dw/db go to `partial`
+// (rows = gridDim.y, K+1 values per channel) and are summed by column_sum_kernel (fixed order).
+// ---------------------------------------------------------------------------------------------
+template <int K>
+__global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
+                                                            const float* __restrict__ w, const float* __restrict__ bias,
+                                                            const float* __restrict__ dact, float* __restrict__ dxzd,
+                                                            float* __restrict__ partial, int X, int T, int TT) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= X) return;
+  int tblocks = (T + TT - 1) / TT;
+  int b = blockIdx.y / tblocks;
+  int t0 = (blockIdx.y % tblocks) * TT;
+  int t1 = min(t0 + TT, T);
+  float wr[K], br = bias ? bias[c] : 0.0f;
+#pragma unroll
+  for (int k = 0; k < K; ++k) wr[k] = w[c * K + k];
+  const float* src = xzd + (int64_t)b * T * ldx + col0 + c;
+  const float* dsrc = dact + (int64_t)b * T * X + c;
+  float* ddst = dxzd + (int64_t)b * T * ldx + col0 + c;
+  // xin holds xbc[t-(K-1) .. t]; dus holds du[t-(K-1) .. t] for the current t.
+  float xin[K], dus[K], dwacc[K], dbacc = 0.0f;
+#pragma unroll
+  for (int k = 0; k < K; ++k) { dwacc[k] = 0.0f; dus[k] = 0.0f; xin[k] = 0.0f; }
+#pragma unroll
+  for (int k = 0; k < K - 1; ++k) {
+    int t = t0 - (K - 1) + k;
+    xin[k + 1] = t >= 0 ? src[(int64_t)t * ldx] : 0.0f;
+  }
+  // Walk t from t0 to t1-1+(K-1): du[t] is needed by dxbc[t-(K-1) .. t].
+  int tend = min(t1 + K - 1, T + K - 1);
+  for (int t = t0; t < tend; ++t) {
+#pragma unroll
+    for (int k = 0; k < K - 1; ++k) { xin[k] = xin[k + 1]; dus[k] = dus[k + 1]; }
+    float du = 0.0f;
+    if (t < T) {
+      xin[K - 1] = src[(int64_t)t * ldx];
+      float u = br;
+#pragma unroll
+      for (int k = 0; k < K; ++k) u = fmaf(wr[k], xin[k], u);
+      float s = sigmoid_acc(u);
+      du = dsrc[(int64_t)t * X] * (s + u * s * (1.0f - s));
+      if (t < t1) {  // this block owns the parameter-gradient contribution of t in [t0,t1)
+        dbacc += du;
+#pragma unroll
+        for (int k = 0; k < K; ++k) dwacc[k] = fmaf(du, xin[k], dwacc[k]);
+      }
+    }
+    dus[K - 1] = du;
+    int tp = t - (K - 1);  // dxbc[tp] = sum_k w[k] * du[tp + (K-1) - k] = sum_k w[k] * dus[K-1-k]
+    if (tp >= t0 && tp < t1) {
+      float g = 0.0f;
+#pragma unroll
+      for (int k = 0; k < K; ++k) g = fmaf(wr[k], dus[K - 1 - k], g);
+      ddst[(int64_t)tp * ldx] = g;
+    }
+  }
+  // Outputs tp in [t0,t1) whose future du lies beyond T were covered because du=0 there; but when
+  // tend was clipped to T+K-1 nothing is lost.  Rows t1-(K-1)..t1-1 need du up to t1+K-2 < tend. OK.
+  float* prow = partial + (int64_t)blockIdx.y * X * (K + 1);
+#pragma unroll
+  for (int k = 0; k < K; ++k) prow[(int64_t)c * (K + 1) + k] = dwacc[k];
+  prow[(int64_t)c * (K + 1) + K] = dbacc;
+}
+
+// out[j] = sum_r partial[r*cols + j] in fixed order; optional second destination with a stride split
+// is handled by the caller through `map`: element j of the sum goes to out_a[j / (K+1) * K + j % (K+1)]
+// when j % (K+1) < K, else to out_b[j / (K+1)].
+__global__ void conv_partial_reduce_kernel(const float* __restrict__ partial, int rows, int X, int K,
+                                           float* __restrict__ dw, float* __restrict__ db) {
+  int j = blockIdx.x * blockDim.x + threadIdx.x;
+  int cols = X * (K + 1);
+  if (j >= cols) return;
+  float s = 0.0f;
+  for (int r = 0; r < rows; ++r) s += partial[(int64_t)r * cols + j];
+  int c = j / (K + 1), k = j % (K + 1);
+  if (k < K) dw[c * K + k] = s; else db[c] = s;
+}
+
+static const int CONV_BWD_TT = 128;
+
+size_t conv_bwd_ws_bytes(const Dims& d) {
+  int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;
+  return align_up((size_t)d.B * tblocks * d.X * (d.K + 1) * sizeof(float), 256);
+}
+
+template <int K>
+static pmb_status launch_conv_bwd_k(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
+                                    const float* dact, float* dxzd, float* partial) {
+  int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;
+  dim3 grid((unsigned)cdiv(d.X, 128), (unsigned)(d.B * tblocks));
+  conv_silu_bwd_kernel<K><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, CONV_BWD_TT);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
+pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
+                         const float* dact, float* dxzd, float* dw, float* db, void* ws, size_t ws_bytes) {
+  if (ws_bytes < conv_bwd_ws_bytes(d)) return fail(PMB_ERR_WORKSPACE, "conv bwd workspace too small");
+  float* partial = static_cast<float*>(ws);
+  switch (d.K) {
+    case 2: PMB_TRY(launch_conv_bwd_k<2>(st, d, xzd, w, b, dact, dxzd, partial)); break;
+    case 3: PMB_TRY(launch_conv_bwd_k<3>(st, d, xzd, w, b, dact, dxzd, partial)); break;
+    case 4: PMB_TRY(launch_conv_bwd_k<4>(st, d, xzd, w, b, dact, dxzd, partial)); break;
+    case 5: PMB_TRY(launch_conv_bwd_k<5>(st, d, xzd, w, b, dact, dxzd, partial)); break;
+    case 6: PMB_TRY(launch_conv_bwd_k<6>(st, d, xzd, w, b, dact, dxzd, partial)); break;
+    case 7: PMB_TRY(launch_conv_bwd_k<7>(st, d, xzd, w, b, dact, dxzd, partial)); break;
+    case 8: PMB_TRY(launch_conv_bwd_k<8>(st, d, xzd, w, b, dact, dxzd, partial)); break;
+    default: return fail(PMB_ERR_SHAPE, "d_conv %d unsupported", d.K);
+  }
+  int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;
+  int cols = d.X * (d.K + 1);
+  conv_partial_reduce_kernel<<<(unsigned)cdiv(cols, 256), 256, 0, st>>>(partial, d.B * tblocks, d.X, d.K, dw, db);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// gated RMSNorm.  g = y * z * sigmoid(z); r = rsqrt(mean(g^2)+eps); out = g * r * w.
+// One 256-thread block per row; the row stays in registers between the two passes.
+// ---------------------------------------------------------------------------------------------
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAX_PER_THREAD = 32;  // width <= 8192
+
+__global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_fwd_kernel(const float* __restrict__ y, const float* __restrict__ z,
+                                                                         int64_t ldz, const float* __restrict__ w,
+                                                                         float* __restrict__ out, float* __restrict__ rstd,
+                                                                         int width, float eps) {
+  __shared__ float red[32];
+  int64_t row = blockIdx.x;
+  const float* yr = y + row * width;
+  const float* zr = z + row * ldz;
+  float g[NORM_MAX_PER_THREAD];
+  float ss = 0.0f;
+  int n = 0;
+  for (int i = threadIdx.x; i < width; i += NORM_THREADS, ++n) {
+    float zv = zr[i];
+    float gv = yr[i] * zv * sigmoid_acc(zv);
+    g[n] = gv;
+    ss = fmaf(gv, gv, ss);
+  }
+  float tot = block_sum(ss, red);
+  float r = 1.0f / sqrtf(tot / (float)width + eps);
+  if (threadIdx.x == 0 && rstd) rstd[row] = r;
+  n = 0;
+  for (int i = threadIdx.x; i < width; i += NORM_THREADS, ++n) out[row * width + i] = g[n] * r * w[i];
+}
+
+pmb_status gated_rmsnorm_fwd(cudaStream_t st, int64_t rows, int width, float eps, const float* y, const float* z, int64_t ldz,
+                             const float* w, float* out, float* rstd) {
+  if (width > NORM_THREADS * NORM_MAX_PER_THREAD) return fail(PMB_ERR_SHAPE, "rmsnorm width %d > %d", width, NORM_THREADS * NORM_MAX_PER_THREAD);
+  gated_rmsnorm_fwd_kernel<<<(unsigned)rows, NORM_THREADS, 0, st>>>(y, z, ldz, w, out, rstd, width, eps);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
+// Backward.  dg = w r dout - g r^3 (sum_j dout_j g_j w_j)/I;  dy = dg z sig(z);
+// dz = dg y (sig + z sig (1-sig));  dw_i = sum_rows dout_i g_i r.
+// A block handles NORM_ROWS consecutive rows so the dw partial stays in registers across them.
+constexpr int NORM_ROWS = 16;
+
+__global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_bwd_kernel(const float* __restrict__ dout, const float* __restrict__ y,
+                                                                         const float* __restrict__ z, int64_t ldz,
+                                                                         const float* __restrict__ w, const float* __restrict__ rstd,
+                                                                         float* __restrict__ dy, float* __restrict__ dz, int64_t lddz,
+                                                                         float* __restrict__ dw_partial, int64_t rows, int width) {
+  __shared__ float red[32];
+  float dwacc[NORM_MAX_PER_THREAD];
+#pragma unroll
+  for (int n = 0; n < NORM_MAX_PER_THREAD; ++n) dwacc[n] = 0.0f;
+  int64_t r0 = (int64_t)blockIdx.x * NORM_ROWS;
+  for (int rr = 0; rr < NORM_ROWS; ++rr) {
+    int64_t row = r0 + rr;
+    if (row >= rows) break;  // uniform across the block
+    float r = rstd[row];
+    float dot = 0.0f;
+    for (int i = threadIdx.x; i < width; i += NORM_THREADS) {
+      float zv = z[row * ldz + i];
+      float gv = y[row * width + i] * zv * sigmoid_acc(zv);
+      dot = fmaf(dout[row * width + i] * gv, w[i], dot);
+    }
+    float tot = block_sum(dot, red);
+    float coef = r * r * r * tot / (float)width;
+    int n = 0;
+    for (int i = threadIdx.x; i < width; i += NORM_THREADS, ++n) {
+      float zv = z[row * ldz + i];
+      float yv = y[row * width + i];
+      float s = sigmoid_acc(zv);
+      float gv = yv * zv * s;
+      float dn = dout[row * width + i];
+      float dg = w[i] * r * dn - gv * coef;
+      dwacc[n] = fmaf(dn * gv, r, dwacc[n]);
+      dy[row * width + i] = dg * zv * s;
+      dz[row * lddz + i] = dg * yv * (s + zv * s * (1.0f - s));
+    }
+  }
+  int n = 0;
+  for (int i = threadIdx.x; i < width; i += NORM_THREADS, ++n) dw_partial[(int64_t)blockIdx.x * width + i] = dwacc[n];
+}
+
+// out[j] = scale * sum_r partial[r*cols + j], fixed order (deterministic).
+__global__ void column_sum_kernel(const float* __restrict__ partial, int64_t rows, int cols, float* __restrict__ out) {
+  int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= cols) return;
+  float s = 0.0f;
+  for (int64_t r = 0; r < rows; ++r) s += partial[r * cols + j];
+  out[j] = s;
+}
+
+size_t gated_rmsnorm_bwd_ws_bytes(int64_t rows, int width) {
+  return align_up((size_t)cdiv(rows, NORM_ROWS) * width * sizeof(float), 256);
+}
+
+pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const float* dout, const float* y, const float* z, int64_t ldz,
+                             const float* w, const float* rstd, float* dy, float* dz, int64_t lddz, float* dw, void* ws, size_t ws_bytes) {
+  if (width > NORM_THREADS * NORM_MAX_PER_THREAD) return fail(PMB_ERR_SHAPE, "rmsnorm width %d too large", width);
+  if (ws_bytes < gated_rmsnorm_bwd_ws_bytes(rows, width)) return fail(PMB_ERR_WORKSPACE, "rmsnorm bwd workspace too small");
+  float* partial = static_cast<float*>(ws);
+  int64_t nblk = cdiv(rows, NORM_ROWS);
+  gated_rmsnorm_bwd_kernel<<<(unsigned)nblk, NORM_THREADS, 0, st>>>(dout, y, z, ldz, w, rstd, dy, dz, lddz, partial, rows, width);
+  PMB_LAUNCHED();
+  column_sum_kernel<<<(unsigned)cdiv(width, 256), 256, 0, st>>>(partial, nblk, width, dw);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
+pmb_status column_sum(cudaStream_t st, const float* partial, int64_t rows, int cols, float* out) {
+  column_sum_kernel<<<(unsigned)cdiv(cols, 256), 256, 0, st>>>(partial, rows, cols, out);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
+}  // namespace pmb

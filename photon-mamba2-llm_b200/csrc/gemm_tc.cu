@@ -1,0 +1,356 @@
+// fp32-accurate GEMM on the 5th-generation tensor cores (tcgen05, sm_100a): C = op(A) op(B) (+ R).
+//
+// Operands are fp32 in HBM.  tcgen05 has no fp32-input MMA, so each operand tile is split in shared
+// memory into a TF32-exact high part and a low remainder (a = hi + lo, hi keeps the top 10 mantissa
+// bits) and every k-step issues three kind::tf32 MMAs (hi*hi, lo*hi, hi*lo) into one fp32 TMEM
+// accumulator.  The dropped lo*lo term and the truncation of lo are ~2^-20 relative per product.
+//
+// CTA = one 128x128 output tile, 6 warps:
+//   warp 0      TMA producer (one lane): 128B-swizzled tiles of A and B into a 3-stage ring
+//   warp 1      allocates TMEM, issues tcgen05.mma (one lane), commits to the ring's "empty" barriers
+//   warps 2..5  split each landed stage into hi/lo in place, then drain TMEM -> registers -> HBM
+// Both operand majornesses are handled by the smem matrix descriptors, so x@W, dY@W^T and X^T@dY all
+// run without a transpose pass.  K/M/N tails rely on TMA zero fill and predicated stores.
+// Every mbarrier wait is bounded; on expiry the kernel raises a status word and drains.
+#include <cuda.h>
+#include "common.cuh"
+#include "kernels.h"
+
+namespace pmb {
+
+__device__ unsigned int g_dev_status = 0;
+
+pmb_status read_clear_device_status(unsigned int* word) {
+  unsigned int zero = 0;
+  PMB_CUDA(cudaMemcpyFromSymbol(word, g_dev_status, sizeof(unsigned int)));
+  if (*word) PMB_CUDA(cudaMemcpyToSymbol(g_dev_status, &zero, sizeof(unsigned int)));
+  return PMB_OK;
+}
+
+namespace tc {
+
+constexpr int TBM = 128, TBN = 128, TBK = 32, STAGES = 3;
+constexpr int TILE_BYTES = TBM * TBK * 4;                  // 16 KiB per operand tile
+constexpr int STAGE_BYTES = 4 * TILE_BYTES;                // A_hi, B_hi, A_lo, B_lo
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int NTHREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr int TMEM_COLS = 128;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait: false when the phase did not complete within SPIN_LIMIT polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading/stride byte offsets (16-byte units),
+// descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+struct Params {
+  int M, N, K;
+  int a_mn_major, b_mn_major;  // 1: operand is contiguous along M (resp. N) in memory
+  float* C; int64_t ldc; const float* R;
+};
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;                    // 1024-byte aligned ring
+  uint8_t* tiles_ptr = smem_raw + (tiles - raw);
+  const uint32_t bars = tiles + STAGES * STAGE_BYTES;               // barrier block (8-byte aligned)
+  // barrier slots: full[s], split[s], empty[s], accum
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto split_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto empty_bar = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+  const uint32_t accum_bar = bars + 8u * (3 * STAGES);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tiles_ptr + STAGES * STAGE_BYTES + 8 * (3 * STAGES + 1));
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * TBN;
+  const int num_kt = (p.K + TBK - 1) / TBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(split_bar(s), 4);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int armed = 0;
+      for (int kt = 0; kt < num_kt; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t ph = (kt / STAGES) & 1;
+        if (!mbar_wait(empty_bar(s), ph ^ 1u)) { atomicOr(&g_dev_status, 1u); *abort_flag = 1; break; }
+        if (*abort_flag) break;
+        const uint32_t a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + TILE_BYTES;
+        mbar_expect_tx(full_bar(s), 2 * TILE_BYTES);
+        const int k0 = kt * TBK;
+        if (!p.a_mn_major) {
+          tma_load_2d(a_dst, &mapA, k0, m0, full_bar(s));
+        } else {
+#pragma unroll
+          for (int j = 0; j < TBM / 32; ++j) tma_load_2d(a_dst + j * (TBK * 128), &mapA, m0 + 32 * j, k0, full_bar(s));
+        }
+        if (!p.b_mn_major) {
+          tma_load_2d(b_dst, &mapB, k0, n0, full_bar(s));
+        } else {
+#pragma unroll
+          for (int j = 0; j < TBN / 32; ++j) tma_load_2d(b_dst + j * (TBK * 128), &mapB, n0 + 32 * j, k0, full_bar(s));
+        }
+        armed = kt + 1;
+      }
+      if (*abort_flag) {
+        // Drain: give the copies already in flight a bounded chance to land before the CTA exits.
+        for (int kt = max(0, armed - STAGES); kt < armed; ++kt) mbar_wait(full_bar(kt % STAGES), (kt / STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+                             ((uint32_t)(TBN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
+      const uint32_t a_lbo = p.a_mn_major ? TBK * 128 : 16, b_lbo = p.b_mn_major ? TBK * 128 : 16;
+      const uint32_t a_kstep = p.a_mn_major ? 1024 : 32, b_kstep = p.b_mn_major ? 1024 : 32;
+      bool ok = true;
+      for (int kt = 0; kt < num_kt && ok; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t ph = (kt / STAGES) & 1;
+        if (!mbar_wait(split_bar(s), ph)) { atomicOr(&g_dev_status, 2u); *abort_flag = 1; ok = false; break; }
+        if (*abort_flag) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_hi = tiles + s * STAGE_BYTES, b_hi = a_hi + TILE_BYTES, a_lo = a_hi + 2 * TILE_BYTES, b_lo = a_hi + 3 * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < TBK / 8; ++k) {
+          const uint64_t dah = make_desc(a_hi + k * a_kstep, a_lbo, 1024), dbh = make_desc(b_hi + k * b_kstep, b_lbo, 1024);
+          const uint64_t dal = make_desc(a_lo + k * a_kstep, a_lbo, 1024), dbl = make_desc(b_lo + k * b_kstep, b_lbo, 1024);
+          mma_tf32(tmem_acc, dal, dbh, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          mma_tf32(tmem_acc, dah, dbl, idesc, 1u);
+          mma_tf32(tmem_acc, dah, dbh, idesc, 1u);
+        }
+        umma_commit(empty_bar(s));   // stage reusable once these MMAs have read it
+      }
+      umma_commit(accum_bar);        // accumulator complete (also releases the epilogue after an abort)
+    }
+  } else {
+    // ---------------- split (hi/lo) then epilogue: warps 2..5 ----------------
+    const int st = threadIdx.x - 64;  // 0..127
+    bool ok = true;
+    for (int kt = 0; kt < num_kt; ++kt) {
+      const int s = kt % STAGES;
+      const uint32_t ph = (kt / STAGES) & 1;
+      // the verdict is made warp-uniform so that the warp-synchronous instructions below stay converged
+      const bool landed = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph));
+      if (!landed) { if (lane == 0) { atomicOr(&g_dev_status, 4u); *abort_flag = 1; } ok = false; break; }
+      if (__any_sync(0xffffffffu, *abort_flag != 0)) { ok = false; break; }
+      uint4* hi = reinterpret_cast<uint4*>(tiles_ptr + s * STAGE_BYTES);
+      uint4* lo = reinterpret_cast<uint4*>(tiles_ptr + s * STAGE_BYTES + 2 * TILE_BYTES);
+#pragma unroll 4
+      for (int i = st; i < 2 * TILE_BYTES / 16; i += 128) {
+        uint4 v = hi[i];
+        uint4 h, l;
+        h.x = v.x & 0xFFFFE000u; h.y = v.y & 0xFFFFE000u; h.z = v.z & 0xFFFFE000u; h.w = v.w & 0xFFFFE000u;
+        l.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(h.x));
+        l.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(h.y));
+        l.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(h.z));
+        l.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(h.w));
+        hi[i] = h;
+        lo[i] = l;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive(split_bar(s));
+    }
+    // epilogue
+    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0));
+    if (!acc_ok && lane == 0) { atomicOr(&g_dev_status, 8u); *abort_flag = 1; }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const bool aborted = __any_sync(0xffffffffu, *abort_flag != 0);
+    if (ok && acc_ok && !aborted) {
+      const int lane_base = (warp & 3) * 32;
+      const int m = m0 + lane_base + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TBN; c0 += 32) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_acc + ((uint32_t)lane_base << 16) + (uint32_t)c0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (m < p.M) {
+          const int nb = n0 + c0;
+          float* crow = p.C + (int64_t)m * p.ldc + nb;
+          const float* rrow = p.R ? p.R + (int64_t)m * p.ldc + nb : nullptr;
+          const bool vec = (nb + 32 <= p.N) && ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                           (!p.R || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+          if (vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              if (rrow) {
+                float4 q = *reinterpret_cast<const float4*>(rrow + j);
+                v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+              }
+              *reinterpret_cast<float4*>(crow + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nb + j < p.N) crow[j] = __uint_as_float(r[j]) + (rrow ? rrow[j] : 0.0f);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &ptr, 12000, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D fp32 map: inner extent `inner` (contiguous), outer extent `outer` with row pitch ld floats.
+static pmb_status make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, int64_t ld, int box_inner, int box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail(PMB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(PMB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (inner=%lld outer=%lld ld=%lld)", (int)r,
+                                     (long long)inner, (long long)outer, (long long)ld);
+  return PMB_OK;
+}
+
+}  // namespace tc
+
+bool gemm_tc_supported(int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
+                       int64_t ldb, const float* C, int64_t ldc) {
+  (void)ta; (void)tb; (void)C; (void)ldc;
+  if (M <= 0 || N <= 0 || K <= 0) return false;
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return false;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return false;
+  if ((lda & 3) || (ldb & 3)) return false;
+  if (cdiv(M, tc::TBM) > 65535) return false;
+  return true;
+}
+
+pmb_status gemm_tc(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                   const float* B, int64_t ldb, float* C, int64_t ldc, const float* R) {
+  using namespace tc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    PMB_CUDA(cudaFuncSetAttribute(gemm_3xtf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr_set = true;
+  }
+  CUtensorMap mapA, mapB;
+  // A: ta=0 -> stored (M,K), K contiguous (K-major);  ta=1 -> stored (K,M), M contiguous (MN-major)
+  if (!ta) PMB_TRY(make_map(&mapA, A, K, M, lda, TBK, TBM)); else PMB_TRY(make_map(&mapA, A, M, K, lda, 32, TBK));
+  // B: tb=1 -> stored (N,K), K contiguous (K-major);  tb=0 -> stored (K,N), N contiguous (MN-major)
+  if (tb) PMB_TRY(make_map(&mapB, B, K, N, ldb, TBK, TBN)); else PMB_TRY(make_map(&mapB, B, N, K, ldb, 32, TBK));
+  Params p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.a_mn_major = ta ? 1 : 0; p.b_mn_major = tb ? 0 : 1;
+  p.C = C; p.ldc = ldc; p.R = R;
+  dim3 grid((unsigned)cdiv(N, TBN), (unsigned)cdiv(M, TBM));
+  gemm_3xtf32_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, p);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
+}  // namespace pmb

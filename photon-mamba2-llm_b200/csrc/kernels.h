@@ -1,0 +1,81 @@
+// Internal host-side launch interface shared by the translation units of the library.
+#pragma once
+#include "common.cuh"
+
+namespace pmb {
+
+// ---- elementwise.cu
+pmb_status conv_silu_dt_fwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
+                            const float* dt_bias, float* act, float* dt);
+size_t conv_bwd_ws_bytes(const Dims& d);
+pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
+                         const float* dact, float* dxzd, float* dw, float* db, void* ws, size_t ws_bytes);
+pmb_status gated_rmsnorm_fwd(cudaStream_t st, int64_t rows, int width, float eps, const float* y, const float* z,
+                             int64_t ldz, const float* w, float* out, float* rstd);
+size_t gated_rmsnorm_bwd_ws_bytes(int64_t rows, int width);
+pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const float* dout, const float* y, const float* z,
+                             int64_t ldz, const float* w, const float* rstd, float* dy, float* dz, int64_t lddz,
+                             float* dw, void* ws, size_t ws_bytes);
+pmb_status column_sum(cudaStream_t st, const float* partial, int64_t rows, int cols, float* out);
+
+// ---- ssd.cu
+// Inputs of the scan in "block form": x (B,T,H,P) stride ldx; either (dt, A) with a = A[h]*dt and x~ = x*dt
+// (dt != NULL), or `a` given directly and x~ = x (dt == NULL).  b/c (B,T,G,N) stride ldbc.
+struct SsdIn {
+  int B, T, H, P, N, G, Q;
+  const float* x; int64_t ldx;
+  const float* dt;        // (B,T,H) or NULL
+  const float* A;         // (H) = -exp(a_log), used when dt != NULL
+  const float* a;         // (B,T,H), used when dt == NULL
+  const float* b; const float* c; int64_t ldbc;
+  const float* D;         // (H) skip weights or NULL:  y += D[h] * x
+};
+struct SsdWs {            // persistent between fwd and bwd of one scan
+  float* S;               // (B,H,T) inclusive cumsum of a within each chunk
+  float* hprev;           // (B,nc,H,N,P) state entering each chunk
+  float* hlast;           // (B,H,N,P) state leaving the last chunk
+  float* CB;              // (B,nc,G,Q,Q)
+  // backward scratch
+  float* dh;              // (B,nc,H,N,P)
+  float* dG;              // (B,nc,G,Q,Q)
+  float* dxt;             // (B,T,H,P) gradient w.r.t. x~
+  float* rows;            // 4 x (B,T,H): ddt_x, dS, dDrow, dSend(padded)
+  float* part;            // (B*nc, 3H) partial sums
+};
+size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base, size_t bytes, SsdWs* out);
+pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, float* y, int64_t ldy,
+                   float* final_state, const SsdWs& ws);
+// Backward.  dy (stride lddy) is the gradient w.r.t. y (skip term included when in.D != NULL).
+// Outputs: dx (stride lddx; gradient w.r.t. raw x when dt != NULL), db/dc (stride lddbc),
+// and either `da` (B,T,H) when in.dt == NULL, or ddt (B,T,H), dA (H), dD (H) when in.dt != NULL.
+struct SsdGrads {
+  float* dx; int64_t lddx;
+  float* db; float* dc; int64_t lddbc;
+  float* da;    // dt == NULL mode
+  float* ddt;   // dt != NULL mode: gradient w.r.t. dt (B,T,H)
+  float* dA;    // (H) gradient w.r.t. A
+  float* dD;    // (H) gradient w.r.t. D, or NULL
+};
+pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy, const float* dy, int64_t lddy,
+                   const SsdGrads& g, const SsdWs& ws);
+
+// ---- gemm_simt.cu / gemm_tc.cu
+pmb_status gemm_simt(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                     const float* B, int64_t ldb, float* C, int64_t ldc, const float* R);
+// returns PMB_ERR_UNSUPPORTED (without touching the error text) when alignment rules are not met
+pmb_status gemm_tc(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                   const float* B, int64_t ldb, float* C, int64_t ldc, const float* R);
+bool gemm_tc_supported(int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                       const float* B, int64_t ldb, const float* C, int64_t ldc);
+pmb_status gemm(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                const float* B, int64_t ldb, float* C, int64_t ldc, const float* R, int engine);
+pmb_status read_clear_device_status(unsigned int* word);
+
+// ---- block.cu
+size_t block_ws_bytes(const Dims& d);
+pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const float* x, const float* residual,
+                     float* out, void* ws, size_t ws_bytes);
+pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const float* x, const float* dout,
+                     const float* dx_accum, float* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes);
+
+}  // namespace pmb

@@ -1,0 +1,251 @@
+// Flat Mamba2 language model training step (forward + backward, no optimizer): tied embedding ->
+// checkpointed residual stack -> tied head -> mean cross-entropy.  Mirrors
+// FlatMamba::forward_checkpointed_hidden + fused cross-entropy + checkpoint_backward
+// (crates/pm-core/src/flat.rs:122-161, crates/pm-train/src/loss.rs:121-138, crates/pm-core/src/checkpoint.rs:110-135).
+// The logits are produced in row tiles of at most LM_TILE_ROWS tokens and turned into their gradient in
+// place, so the (tokens, vocab) matrix never exists as a whole (the reference tiles for the same reason,
+// crates/pm-core/src/loss.rs:73-209).
+#include <vector>
+#include "common.cuh"
+#include "kernels.h"
+
+namespace pmb {
+
+constexpr int LM_TILE_ROWS = 4096;
+
+__global__ void embedding_fwd_kernel(const float* __restrict__ table, const int64_t* __restrict__ ids, float* __restrict__ out,
+                                     int64_t rows, int D, int V, unsigned int* __restrict__ bad) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t n = rows * (D / 4);
+  if (i >= n) return;
+  int64_t r = i / (D / 4);
+  int c = (int)(i % (D / 4)) * 4;
+  int64_t id = ids[r];
+  if (id < 0 || id >= V) { if (c == 0) atomicOr(bad, 1u); id = 0; }
+  *reinterpret_cast<float4*>(out + r * D + c) = *reinterpret_cast<const float4*>(table + id * D + c);
+}
+
+__global__ void embedding_bwd_kernel(float* __restrict__ dtable, const int64_t* __restrict__ ids, const float* __restrict__ dh,
+                                     int64_t rows, int D, int V) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * D) return;
+  int64_t r = i / D;
+  int c = (int)(i % D);
+  int64_t id = ids[r];
+  if (id < 0 || id >= V) return;
+  atomicAdd(dtable + id * D + c, dh[i]);
+}
+
+// One block per row.  Pass 1: online max / sum-exp; pass 2: logits <- (softmax - onehot) * inv_rows.
+// row_loss[r] = logsumexp - logit[target].
+__global__ void __launch_bounds__(256) cross_entropy_kernel(float* __restrict__ logits, int64_t ld, int V,
+                                                            const int64_t* __restrict__ targets, float* __restrict__ row_loss,
+                                                            float inv_rows) {
+  __shared__ float red[32];
+  __shared__ float sh_max;
+  int64_t r = blockIdx.x;
+  float* row = logits + r * ld;
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) m = fmaxf(m, row[i]);
+  // block max
+  {
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red[w] = m;
+    __syncthreads();
+    if (w == 0) {
+      float v = lane < (int)(blockDim.x >> 5) ? red[lane] : -INFINITY;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+      if (lane == 0) sh_max = v;
+    }
+    __syncthreads();
+    m = sh_max;
+  }
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) s += expf(row[i] - m);
+  float tot = block_sum(s, red);
+  float lse = m + logf(tot);
+  int64_t tg = targets[r];
+  if (threadIdx.x == 0) row_loss[r] = (tg >= 0 && tg < V) ? lse - row[tg] : 0.0f;
+  __syncthreads();
+  float inv = 1.0f / tot;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float pr = expf(row[i] - m) * inv;
+    row[i] = (pr - (i == tg ? 1.0f : 0.0f)) * inv_rows;
+  }
+}
+
+__global__ void __launch_bounds__(256) mean_kernel(const float* __restrict__ v, int64_t n, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.0f;
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) s += v[i];
+  float tot = block_sum(s, red);
+  if (threadIdx.x == 0) *out = tot / (float)n;
+}
+
+}  // namespace pmb
+
+using namespace pmb;
+
+struct pmb_lm {
+  pmb_mamba2_config cfg;
+  Dims d;
+  int L, V, Vp, tile_rows;
+  int64_t n_params;
+  std::vector<int64_t> off;  // [0] embedding, then 8 per layer
+  float* params = nullptr;
+  float* grads = nullptr;
+  float* saved = nullptr;     // (L+1) x (M, D)
+  float* dhidden = nullptr;   // (M, D)
+  float* logits = nullptr;    // (tile_rows, Vp)
+  float* row_loss = nullptr;  // (M)
+  float* loss = nullptr;      // scalar
+  unsigned int* bad = nullptr;
+  int64_t* ids = nullptr;
+  int64_t* targets = nullptr;
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  int64_t act_bytes = 0;
+  std::vector<pmb_block_params> lp;
+  std::vector<pmb_block_grads> lg;
+};
+
+static int64_t tensor_elems(const Dims& d, int which) {
+  switch (which) {
+    case 0: return (int64_t)d.D * d.J;
+    case 1: return (int64_t)d.X * d.K;
+    case 2: return d.X;
+    case 3: case 4: case 5: return d.H;
+    case 6: return d.I;
+    case 7: return (int64_t)d.I * d.D;
+  }
+  return 0;
+}
+
+extern "C" pmb_status pmb_lm_create(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t vocab, int32_t batch,
+                                    int32_t seqlen, pmb_lm** out) {
+  if (!out) return fail(PMB_ERR_ARG, "lm_create: out is NULL");
+  *out = nullptr;
+  Dims d;
+  PMB_TRY(make_dims(cfg, batch, seqlen, &d));
+  if (n_layers <= 0 || vocab <= 0) return fail(PMB_ERR_SHAPE, "lm_create: n_layers and vocab must be positive");
+  if (d.D % 4 != 0) return fail(PMB_ERR_SHAPE, "lm_create: d_model must be a multiple of 4");
+  pmb_lm* lm = new pmb_lm();
+  lm->cfg = *cfg; lm->d = d; lm->L = n_layers; lm->V = vocab;
+  lm->Vp = (int)align_up((size_t)vocab, 64);
+  lm->tile_rows = (int)(d.M < LM_TILE_ROWS ? d.M : LM_TILE_ROWS);
+  int64_t o = 0;
+  auto place = [&](int64_t n) { int64_t at = o; o += (int64_t)align_up((size_t)n, 64); return at; };
+  lm->off.push_back(place((int64_t)vocab * d.D));
+  for (int l = 0; l < n_layers; ++l)
+    for (int w = 0; w < 8; ++w) lm->off.push_back(place(tensor_elems(d, w)));
+  lm->n_params = o;
+  lm->ws_bytes = block_ws_bytes(d);
+  size_t slot = (size_t)d.M * d.D * sizeof(float);
+  auto alloc = [&](void** p, size_t bytes) -> bool { return cudaMalloc(p, bytes) == cudaSuccess; };
+  bool ok = true;
+  ok = ok && alloc((void**)&lm->params, (size_t)o * 4);
+  ok = ok && alloc((void**)&lm->grads, (size_t)o * 4);
+  ok = ok && alloc((void**)&lm->saved, slot * (n_layers + 1));
+  ok = ok && alloc((void**)&lm->dhidden, slot);
+  ok = ok && alloc((void**)&lm->logits, (size_t)lm->tile_rows * lm->Vp * 4);
+  ok = ok && alloc((void**)&lm->row_loss, (size_t)d.M * 4);
+  ok = ok && alloc((void**)&lm->loss, 256);
+  ok = ok && alloc((void**)&lm->bad, 256);
+  ok = ok && alloc((void**)&lm->ids, (size_t)d.M * 8);
+  ok = ok && alloc((void**)&lm->targets, (size_t)d.M * 8);
+  ok = ok && alloc(&lm->ws, lm->ws_bytes);
+  if (!ok) {
+    pmb_status s = fail(PMB_ERR_CUDA, "lm_create: cudaMalloc failed: %s", cudaGetErrorString(cudaGetLastError()));
+    pmb_lm_destroy(lm);
+    return s;
+  }
+  cudaMemset(lm->params, 0, (size_t)o * 4);
+  cudaMemset(lm->grads, 0, (size_t)o * 4);
+  cudaMemset(lm->bad, 0, 256);
+  lm->act_bytes = (int64_t)(slot * (n_layers + 1) + slot + (size_t)lm->tile_rows * lm->Vp * 4 + (size_t)d.M * 4 + lm->ws_bytes);
+  lm->lp.resize(n_layers); lm->lg.resize(n_layers);
+  for (int l = 0; l < n_layers; ++l) {
+    const int64_t* f = &lm->off[1 + 8 * l];
+    float* P = lm->params; float* G = lm->grads;
+    lm->lp[l] = pmb_block_params{P + f[0], P + f[1], P + f[2], P + f[3], P + f[4], P + f[5], P + f[6], P + f[7]};
+    lm->lg[l] = pmb_block_grads{G + f[0], G + f[1], G + f[2], G + f[3], G + f[4], G + f[5], G + f[6], G + f[7]};
+  }
+  *out = lm;
+  return PMB_OK;
+}
+
+extern "C" void pmb_lm_destroy(pmb_lm* lm) {
+  if (!lm) return;
+  cudaFree(lm->params); cudaFree(lm->grads); cudaFree(lm->saved); cudaFree(lm->dhidden); cudaFree(lm->logits);
+  cudaFree(lm->row_loss); cudaFree(lm->loss); cudaFree(lm->bad); cudaFree(lm->ids); cudaFree(lm->targets); cudaFree(lm->ws);
+  delete lm;
+}
+
+extern "C" int64_t pmb_lm_param_count(const pmb_lm* lm) { return lm ? lm->n_params : 0; }
+extern "C" int64_t pmb_lm_param_offset(const pmb_lm* lm, int32_t layer, int32_t which) {
+  if (!lm) return -1;
+  if (layer < 0) return lm->off[0];
+  if (layer >= lm->L || which < 0 || which > 7) return -1;
+  return lm->off[1 + 8 * layer + which];
+}
+extern "C" float* pmb_lm_params(pmb_lm* lm) { return lm ? lm->params : nullptr; }
+extern "C" float* pmb_lm_grads(pmb_lm* lm) { return lm ? lm->grads : nullptr; }
+extern "C" int64_t pmb_lm_activation_bytes(const pmb_lm* lm) { return lm ? lm->act_bytes : 0; }
+extern "C" const float* pmb_lm_loss_device(const pmb_lm* lm) { return lm ? lm->loss : nullptr; }
+
+extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t* d_ids, const int64_t* d_targets,
+                                         pmb_layer_callback on_layer_done, void* user) {
+  if (!lm || !d_ids || !d_targets) return fail(PMB_ERR_ARG, "lm_step: NULL argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const Dims& d = lm->d;
+  const int64_t M = d.M;
+  const int D = d.D, V = lm->V, Vp = lm->Vp;
+  float* table = lm->params + lm->off[0];
+  float* dtable = lm->grads + lm->off[0];
+  size_t slot = (size_t)M * D;
+  embedding_fwd_kernel<<<(unsigned)cdiv(M * (D / 4), 256), 256, 0, st>>>(table, d_ids, lm->saved, M, D, V, lm->bad);
+  PMB_LAUNCHED();
+  PMB_TRY(pmb_stack_fwd_ckpt(stream, &lm->cfg, lm->L, lm->lp.data(), d.B, d.T, lm->saved, lm->ws, lm->ws_bytes));
+  const float* hidden = lm->saved + (size_t)lm->L * slot;
+  for (int64_t r0 = 0; r0 < M; r0 += lm->tile_rows) {
+    int64_t rows = M - r0 < lm->tile_rows ? M - r0 : lm->tile_rows;
+    const float* hrows = hidden + r0 * D;
+    // logits = hidden E^T   (photon/embedding.rs:54-60)
+    PMB_TRY(gemm(st, 0, 1, rows, V, D, hrows, D, table, D, lm->logits, Vp, nullptr, 0));
+    cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>(lm->logits, Vp, V, d_targets + r0, lm->row_loss + r0, 1.0f / (float)M);
+    PMB_LAUNCHED();
+    // dhidden = dlogits E ;  dE (+)= dlogits^T hidden
+    PMB_TRY(gemm(st, 0, 0, rows, D, V, lm->logits, Vp, table, D, lm->dhidden + r0 * D, D, nullptr, 0));
+    PMB_TRY(gemm(st, 1, 0, V, D, rows, lm->logits, Vp, hrows, D, dtable, D, r0 == 0 ? nullptr : dtable, 0));
+  }
+  mean_kernel<<<1, 256, 0, st>>>(lm->row_loss, M, lm->loss);
+  PMB_LAUNCHED();
+  PMB_TRY(pmb_stack_bwd(stream, &lm->cfg, lm->L, lm->lp.data(), lm->lg.data(), d.B, d.T, lm->saved, lm->dhidden, lm->ws,
+                        lm->ws_bytes, on_layer_done, user));
+  embedding_bwd_kernel<<<(unsigned)cdiv(M * D, 256), 256, 0, st>>>(dtable, d_ids, lm->dhidden, M, D, V);
+  PMB_LAUNCHED();
+  if (on_layer_done) on_layer_done(-1, user);
+  return PMB_OK;
+}
+
+extern "C" pmb_status pmb_lm_step_host(pmb_lm* lm, void* stream, const int64_t* h_ids, const int64_t* h_targets,
+                                       float* h_loss, pmb_layer_callback on_layer_done, void* user) {
+  if (!lm || !h_ids || !h_targets || !h_loss) return fail(PMB_ERR_ARG, "lm_step_host: NULL argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  size_t bytes = (size_t)lm->d.M * sizeof(int64_t);
+  PMB_CUDA(cudaMemcpyAsync(lm->ids, h_ids, bytes, cudaMemcpyHostToDevice, st));
+  PMB_CUDA(cudaMemcpyAsync(lm->targets, h_targets, bytes, cudaMemcpyHostToDevice, st));
+  PMB_TRY(pmb_lm_step_device(lm, stream, lm->ids, lm->targets, on_layer_done, user));
+  PMB_CUDA(cudaMemcpyAsync(h_loss, lm->loss, sizeof(float), cudaMemcpyDeviceToHost, st));
+  PMB_CUDA(cudaStreamSynchronize(st));
+  unsigned int bad = 0;
+  PMB_CUDA(cudaMemcpy(&bad, lm->bad, sizeof(bad), cudaMemcpyDeviceToHost));
+  if (bad) {
+    cudaMemset(lm->bad, 0, sizeof(bad));
+    return fail(PMB_ERR_ARG, "lm_step_host: a token id was outside [0, vocab)");
+  }
+  return PMB_OK;
+}

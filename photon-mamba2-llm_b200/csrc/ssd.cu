@@ -1,0 +1,517 @@
+// Chunked SSD scan (forward and fused-recompute backward) as a set of batched tile contractions.
+//
+// Per (batch b, chunk c, head h), with S = inclusive cumsum of a inside the chunk, L[t,s] = exp(S_t - S_s) (s <= t),
+// x~ = x * dt:
+//   forward   CB = C B^T                                   (per group)
+//             states = sum_q exp(S_end - S_q) B_q (x) x~_q  -> exclusive scan over chunks -> h_prev
+//             Y = (CB o L) x~ + diag(exp S) C h_prev (+ D x)
+//   backward  dh_prev = sum_t exp(S_t) C_t (x) dY_t + exp(S_end) dh   (reverse scan over chunks)
+//             dx~ = (CB o L)^T dY + exp(S_end - S_s) B_s dh
+//             dG = sum_heads L o (dY x~^T);  dC = dG B + sum_h exp(S_t) dY_t h_prev^T;
+//             dB = dG^T C + sum_h exp(S_end - S_s) x~_s dh^T
+//             dS_t = <dY_t, Y_t> - <x~_t, dx~_t>, dS_{Q-1} += <dh, h_next>;  da = reverse cumsum(dS)
+// The reference computes the same quantities with ~40 primitive ops and autograd
+// (crates/pm-core/src/mamba2/ssd_ops.rs:167-284); nothing of size (Q,Q) per head is stored here.
+//
+// This file holds the SIMT (fp32 FMA) engine: one 64x64-tile kernel template, specialised by small functor
+// structs that say how to read operand elements and where results go.
+#include "common.cuh"
+#include "kernels.h"
+#include "bgemm.cuh"
+
+namespace pmb {
+
+struct SsdP {
+  int B, T, H, P, N, G, Q, nc, hpg;
+  const float* x; int64_t ldx;
+  const float* dt; const float* A; const float* a;
+  const float* b; const float* c; int64_t ldbc;
+  const float* D;
+  float* S; float* hprev; float* hlast; float* CB; float* dh; float* dG; float* dxt;
+  const float* y; int64_t ldy;
+  const float* dy; int64_t lddy;
+  float* yout; int64_t ldyo;
+  float* db; float* dc; int64_t lddbc;
+
+  __device__ __forceinline__ int64_t tok(int bb, int cc, int q) const { return (int64_t)bb * T + (int64_t)cc * Q + q; }
+  __device__ __forceinline__ float Sv(int bb, int h, int cc, int q) const { return S[((int64_t)bb * H + h) * T + (int64_t)cc * Q + q]; }
+  __device__ __forceinline__ float dtv(int64_t tk, int h) const { return dt ? dt[tk * H + h] : 1.0f; }
+};
+
+// ---- F1: CB[t,s] = sum_n C[t,n] B[s,n], per (b,c,g) --------------------------------------------
+struct OpCB {
+  static constexpr bool SEG_SCALE = false;
+  SsdP p; int Mdim, Ndim;
+  int bb, cc, g; const float* cp; const float* bp; float* out;
+  __device__ bool init(int batch, int m0, int n0) {
+    if (n0 > m0 + BM - 1) return false;  // strictly above the diagonal: never read
+    g = batch % p.G; int bc = batch / p.G; cc = bc % p.nc; bb = bc / p.nc;
+    cp = p.c + p.tok(bb, cc, 0) * p.ldbc + g * p.N;
+    bp = p.b + p.tok(bb, cc, 0) * p.ldbc + g * p.N;
+    out = p.CB + (int64_t)batch * p.Q * p.Q;
+    return true;
+  }
+  __device__ int nseg() const { return 1; }
+  __device__ void krange(int, int, int, int& k0, int& k1) const { k0 = 0; k1 = p.N; }
+  __device__ bool a_kcontig(int) const { return true; }
+  __device__ bool b_kcontig(int) const { return true; }
+  __device__ float a(int, int m, int k) const { return cp[(int64_t)m * p.ldbc + k]; }
+  __device__ float b(int, int k, int n) const { return bp[(int64_t)n * p.ldbc + k]; }
+  __device__ float seg_scale(int, int, int) const { return 1.0f; }
+  __device__ void store(int m, int n, float v) const { out[(int64_t)m * p.Q + n] = v; }
+};
+
+// Common context for per-(b,c,h) ops.
+struct HeadCtx {
+  int bb, cc, h, g; int64_t t0;  // first token of the chunk
+  __device__ void set(const SsdP& p, int batch) {
+    h = batch % p.H; int bc = batch / p.H; cc = bc % p.nc; bb = bc / p.nc; g = h / p.hpg;
+    t0 = p.tok(bb, cc, 0);
+  }
+};
+
+// ---- F2: states[n,p] = sum_q B[q,n] exp(S_end - S_q) x~[q,p], per (b,c,h) -----------------------
+struct OpState {
+  static constexpr bool SEG_SCALE = false;
+  SsdP p; int Mdim, Ndim;
+  HeadCtx cx; float send; const float* sp; float* out;
+  __device__ bool init(int batch, int, int) {
+    cx.set(p, batch);
+    sp = p.S + ((int64_t)cx.bb * p.H + cx.h) * p.T + (int64_t)cx.cc * p.Q;
+    send = sp[p.Q - 1];
+    out = p.hprev + (int64_t)batch * p.N * p.P;
+    return true;
+  }
+  __device__ int nseg() const { return 1; }
+  __device__ void krange(int, int, int, int& k0, int& k1) const { k0 = 0; k1 = p.Q; }
+  __device__ bool a_kcontig(int) const { return false; }
+  __device__ bool b_kcontig(int) const { return false; }
+  __device__ float a(int, int m, int k) const {
+    int64_t tk = cx.t0 + k;
+    return p.b[tk * p.ldbc + cx.g * p.N + m] * expf(send - sp[k]) * p.dtv(tk, cx.h);
+  }
+  __device__ float b(int, int k, int n) const { return p.x[(cx.t0 + k) * p.ldx + cx.h * p.P + n]; }
+  __device__ float seg_scale(int, int, int) const { return 1.0f; }
+  __device__ void store(int m, int n, float v) const { out[(int64_t)m * p.P + n] = v; }
+};
+
+// ---- F4: Y[t,p] = sum_{s<=t} CB[t,s] L[t,s] x~[s,p] + exp(S_t) sum_n C[t,n] h_prev[n,p] (+ D x) --
+struct OpScan {
+  static constexpr bool SEG_SCALE = false;
+  SsdP p; int Mdim, Ndim;
+  HeadCtx cx; const float* sp; const float* cb; const float* hp;
+  __device__ bool init(int batch, int, int) {
+    cx.set(p, batch);
+    sp = p.S + ((int64_t)cx.bb * p.H + cx.h) * p.T + (int64_t)cx.cc * p.Q;
+    cb = p.CB + (((int64_t)cx.bb * p.nc + cx.cc) * p.G + cx.g) * p.Q * p.Q;
+    hp = p.hprev + (int64_t)batch * p.N * p.P;
+    return true;
+  }
+  __device__ int nseg() const { return 2; }
+  __device__ void krange(int seg, int m0, int, int& k0, int& k1) const {
+    k0 = 0; k1 = seg == 0 ? min(p.Q, m0 + BM) : p.N;
+  }
+  __device__ bool a_kcontig(int) const { return true; }
+  __device__ bool b_kcontig(int) const { return false; }
+  __device__ float a(int seg, int m, int k) const {
+    if (seg == 0) {
+      if (k > m) return 0.0f;
+      return cb[(int64_t)m * p.Q + k] * expf(sp[m] - sp[k]) * p.dtv(cx.t0 + k, cx.h);
+    }
+    return p.c[(cx.t0 + m) * p.ldbc + cx.g * p.N + k] * expf(sp[m]);
+  }
+  __device__ float b(int seg, int k, int n) const {
+    if (seg == 0) return p.x[(cx.t0 + k) * p.ldx + cx.h * p.P + n];
+    return hp[(int64_t)k * p.P + n];
+  }
+  __device__ float seg_scale(int, int, int) const { return 1.0f; }
+  __device__ void store(int m, int n, float v) const {
+    if (p.D) v = fmaf(p.D[cx.h], p.x[(cx.t0 + m) * p.ldx + cx.h * p.P + n], v);
+    p.yout[(cx.t0 + m) * p.ldyo + cx.h * p.P + n] = v;
+  }
+};
+
+// ---- B1: contrib[n,p] = sum_t C[t,n] exp(S_t) dY[t,p], per (b,c,h) ------------------------------
+struct OpDstate {
+  static constexpr bool SEG_SCALE = false;
+  SsdP p; int Mdim, Ndim;
+  HeadCtx cx; const float* sp; float* out;
+  __device__ bool init(int batch, int, int) {
+    cx.set(p, batch);
+    sp = p.S + ((int64_t)cx.bb * p.H + cx.h) * p.T + (int64_t)cx.cc * p.Q;
+    out = p.dh + (int64_t)batch * p.N * p.P;
+    return true;
+  }
+  __device__ int nseg() const { return 1; }
+  __device__ void krange(int, int, int, int& k0, int& k1) const { k0 = 0; k1 = p.Q; }
+  __device__ bool a_kcontig(int) const { return false; }
+  __device__ bool b_kcontig(int) const { return false; }
+  __device__ float a(int, int m, int k) const { return p.c[(cx.t0 + k) * p.ldbc + cx.g * p.N + m] * expf(sp[k]); }
+  __device__ float b(int, int k, int n) const { return p.dy[(cx.t0 + k) * p.lddy + cx.h * p.P + n]; }
+  __device__ float seg_scale(int, int, int) const { return 1.0f; }
+  __device__ void store(int m, int n, float v) const { out[(int64_t)m * p.P + n] = v; }
+};
+
+// ---- B3: dx~[s,p] = sum_{t>=s} CB[t,s] L[t,s] dY[t,p] + exp(S_end - S_s) sum_n B[s,n] dh[n,p] ----
+struct OpDx {
+  static constexpr bool SEG_SCALE = false;
+  SsdP p; int Mdim, Ndim;
+  HeadCtx cx; const float* sp; const float* cb; const float* dhp; float send;
+  __device__ bool init(int batch, int, int) {
+    cx.set(p, batch);
+    sp = p.S + ((int64_t)cx.bb * p.H + cx.h) * p.T + (int64_t)cx.cc * p.Q;
+    send = sp[p.Q - 1];
+    cb = p.CB + (((int64_t)cx.bb * p.nc + cx.cc) * p.G + cx.g) * p.Q * p.Q;
+    dhp = p.dh + (int64_t)batch * p.N * p.P;
+    return true;
+  }
+  __device__ int nseg() const { return 2; }
+  __device__ void krange(int seg, int m0, int, int& k0, int& k1) const {
+    if (seg == 0) { k0 = m0; k1 = p.Q; } else { k0 = 0; k1 = p.N; }
+  }
+  __device__ bool a_kcontig(int seg) const { return seg != 0; }
+  __device__ bool b_kcontig(int) const { return false; }
+  __device__ float a(int seg, int m, int k) const {
+    if (seg == 0) {
+      if (k < m) return 0.0f;
+      return cb[(int64_t)k * p.Q + m] * expf(sp[k] - sp[m]);
+    }
+    return p.b[(cx.t0 + m) * p.ldbc + cx.g * p.N + k] * expf(send - sp[m]);
+  }
+  __device__ float b(int seg, int k, int n) const {
+    if (seg == 0) return p.dy[(cx.t0 + k) * p.lddy + cx.h * p.P + n];
+    return dhp[(int64_t)k * p.P + n];
+  }
+  __device__ float seg_scale(int, int, int) const { return 1.0f; }
+  __device__ void store(int m, int n, float v) const { p.dxt[(cx.t0 + m) * (int64_t)(p.H * p.P) + cx.h * p.P + n] = v; }
+};
+
+// ---- B5: dG[t,s] = sum_{h in group} L_h[t,s] sum_p dY_h[t,p] x~_h[s,p], per (b,c,g) --------------
+struct OpDG {
+  static constexpr bool SEG_SCALE = true;
+  SsdP p; int Mdim, Ndim;
+  int bb, cc, g; int64_t t0; float* out;
+  __device__ bool init(int batch, int m0, int n0) {
+    if (n0 > m0 + BM - 1) return false;
+    g = batch % p.G; int bc = batch / p.G; cc = bc % p.nc; bb = bc / p.nc;
+    t0 = p.tok(bb, cc, 0);
+    out = p.dG + (int64_t)batch * p.Q * p.Q;
+    return true;
+  }
+  __device__ int nseg() const { return p.hpg; }
+  __device__ void krange(int, int, int, int& k0, int& k1) const { k0 = 0; k1 = p.P; }
+  __device__ bool a_kcontig(int) const { return true; }
+  __device__ bool b_kcontig(int) const { return true; }
+  __device__ float a(int seg, int m, int k) const { return p.dy[(t0 + m) * p.lddy + (g * p.hpg + seg) * p.P + k]; }
+  __device__ float b(int seg, int k, int n) const {
+    int h = g * p.hpg + seg;
+    return p.x[(t0 + n) * p.ldx + h * p.P + k] * p.dtv(t0 + n, h);
+  }
+  __device__ float seg_scale(int seg, int m, int n) const {
+    if (n > m) return 0.0f;
+    int h = g * p.hpg + seg;
+    const float* sp = p.S + ((int64_t)bb * p.H + h) * p.T + (int64_t)cc * p.Q;
+    return expf(sp[m] - sp[n]);
+  }
+  __device__ void store(int m, int n, float v) const { out[(int64_t)m * p.Q + n] = v; }
+};
+
+// ---- B6a: dC[t,n] = sum_{s<=t} dG[t,s] B[s,n] + sum_h exp(S_h,t) sum_p dY_h[t,p] h_prev_h[n,p] ----
+struct OpDC {
+  static constexpr bool SEG_SCALE = false;
+  SsdP p; int Mdim, Ndim;
+  int bb, cc, g; int64_t t0; const float* dg;
+  __device__ bool init(int batch, int, int) {
+    g = batch % p.G; int bc = batch / p.G; cc = bc % p.nc; bb = bc / p.nc;
+    t0 = p.tok(bb, cc, 0);
+    dg = p.dG + (int64_t)batch * p.Q * p.Q;
+    return true;
+  }
+  __device__ int nseg() const { return 1 + p.hpg; }
+  __device__ void krange(int seg, int m0, int, int& k0, int& k1) const {
+    k0 = 0; k1 = seg == 0 ? min(p.Q, m0 + BM) : p.P;
+  }
+  __device__ bool a_kcontig(int) const { return true; }
+  __device__ bool b_kcontig(int seg) const { return seg != 0; }
+  __device__ float a(int seg, int m, int k) const {
+    if (seg == 0) return dg[(int64_t)m * p.Q + k];
+    int h = g * p.hpg + seg - 1;
+    return p.dy[(t0 + m) * p.lddy + h * p.P + k] * expf(p.Sv(bb, h, cc, m));
+  }
+  __device__ float b(int seg, int k, int n) const {
+    if (seg == 0) return p.b[(t0 + k) * p.ldbc + g * p.N + n];
+    int h = g * p.hpg + seg - 1;
+    return p.hprev[((((int64_t)bb * p.nc + cc) * p.H + h) * p.N + n) * p.P + k];
+  }
+  __device__ float seg_scale(int, int, int) const { return 1.0f; }
+  __device__ void store(int m, int n, float v) const { p.dc[(t0 + m) * p.lddbc + g * p.N + n] = v; }
+};
+
+// ---- B6b: dB[s,n] = sum_{t>=s} dG[t,s] C[t,n] + sum_h exp(S_end - S_s) sum_p x~_h[s,p] dh_h[n,p] --
+struct OpDB {
+  static constexpr bool SEG_SCALE = false;
+  SsdP p; int Mdim, Ndim;
+  int bb, cc, g; int64_t t0; const float* dg;
+  __device__ bool init(int batch, int, int) {
+    g = batch % p.G; int bc = batch / p.G; cc = bc % p.nc; bb = bc / p.nc;
+    t0 = p.tok(bb, cc, 0);
+    dg = p.dG + (int64_t)batch * p.Q * p.Q;
+    return true;
+  }
+  __device__ int nseg() const { return 1 + p.hpg; }
+  __device__ void krange(int seg, int m0, int, int& k0, int& k1) const {
+    if (seg == 0) { k0 = m0; k1 = p.Q; } else { k0 = 0; k1 = p.P; }
+  }
+  __device__ bool a_kcontig(int seg) const { return seg != 0; }
+  __device__ bool b_kcontig(int seg) const { return seg != 0; }
+  __device__ float a(int seg, int m, int k) const {
+    if (seg == 0) return dg[(int64_t)k * p.Q + m];
+    int h = g * p.hpg + seg - 1;
+    float send = p.Sv(bb, h, cc, p.Q - 1);
+    return p.x[(t0 + m) * p.ldx + h * p.P + k] * p.dtv(t0 + m, h) * expf(send - p.Sv(bb, h, cc, m));
+  }
+  __device__ float b(int seg, int k, int n) const {
+    if (seg == 0) return p.c[(t0 + k) * p.ldbc + g * p.N + n];
+    int h = g * p.hpg + seg - 1;
+    return p.dh[((((int64_t)bb * p.nc + cc) * p.H + h) * p.N + n) * p.P + k];
+  }
+  __device__ float seg_scale(int, int, int) const { return 1.0f; }
+  __device__ void store(int m, int n, float v) const { p.db[(t0 + m) * p.lddbc + g * p.N + n] = v; }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Small kernels
+// ---------------------------------------------------------------------------------------------
+
+// S[b,h,c*Q+q] = inclusive cumsum over q of a.  One warp per (b,c,h).
+__global__ void chunk_cumsum_kernel(SsdP p) {
+  int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  int total = p.B * p.nc * p.H;
+  if (w >= total) return;
+  int h = w % p.H, bc = w / p.H, cc = bc % p.nc, bb = bc / p.nc;
+  float carry = 0.0f;
+  float* out = p.S + ((int64_t)bb * p.H + h) * p.T + (int64_t)cc * p.Q;
+  for (int q0 = 0; q0 < p.Q; q0 += 32) {
+    int q = q0 + lane;
+    float v = 0.0f;
+    if (q < p.Q) {
+      int64_t tk = p.tok(bb, cc, q);
+      v = p.dt ? p.A[h] * p.dt[tk * p.H + h] : p.a[tk * p.H + h];
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      float u = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += u;
+    }
+    v += carry;
+    if (q < p.Q) out[q] = v;
+    carry = __shfl_sync(0xffffffffu, v, 31);
+  }
+}
+
+// In place: buffer holds states[c] on entry, h_prev[c] (state entering chunk c) on exit; hlast = final state.
+__global__ void state_pass_kernel(SsdP p, const float* __restrict__ init) {
+  int64_t NP = (int64_t)p.N * p.P;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)p.B * p.H * NP) return;
+  int64_t e = i % NP; int64_t bh = i / NP; int h = (int)(bh % p.H); int bb = (int)(bh / p.H);
+  float run = init ? init[i] : 0.0f;
+  for (int cc = 0; cc < p.nc; ++cc) {
+    float* slot = p.hprev + (((int64_t)bb * p.nc + cc) * p.H + h) * NP + e;
+    float tmp = *slot;
+    *slot = run;
+    run = fmaf(expf(p.Sv(bb, h, cc, p.Q - 1)), run, tmp);
+  }
+  p.hlast[i] = run;
+}
+
+// Reverse scan.  On entry dh[c] holds contrib[c]; on exit dh[c] = adjoint of the state leaving chunk c.
+// dsend[b,c,h] = <dh[c], h_next[c]> with h_next[c] = h_prev[c+1] (the last chunk's dh is zero).
+constexpr int SPB_THREADS = 256;
+constexpr int SPB_MAX_PER_THREAD = 64;  // N*P <= 16384
+__global__ void __launch_bounds__(SPB_THREADS) state_pass_bwd_kernel(SsdP p, float* __restrict__ dsend) {
+  __shared__ float red[32];
+  int bh = blockIdx.x, h = bh % p.H, bb = bh / p.H;
+  int NP = p.N * p.P;
+  float run[SPB_MAX_PER_THREAD];
+#pragma unroll
+  for (int k = 0; k < SPB_MAX_PER_THREAD; ++k) run[k] = 0.0f;
+  for (int cc = p.nc - 1; cc >= 0; --cc) {
+    float* slot = p.dh + (((int64_t)bb * p.nc + cc) * p.H + h) * NP;
+    const float* hnext = (cc + 1 < p.nc) ? p.hprev + (((int64_t)bb * p.nc + cc + 1) * p.H + h) * NP : p.hlast + ((int64_t)bb * p.H + h) * NP;
+    float decay = expf(p.Sv(bb, h, cc, p.Q - 1));
+    float dot = 0.0f;
+    int k = 0;
+    for (int e = threadIdx.x; e < NP; e += SPB_THREADS, ++k) {
+      float tmp = slot[e];
+      float r = run[k];
+      slot[e] = r;
+      dot = fmaf(r, hnext[e], dot);
+      run[k] = fmaf(decay, r, tmp);
+    }
+    float tot = block_sum(dot, red);
+    if (threadIdx.x == 0) dsend[((int64_t)bb * p.nc + cc) * p.H + h] = tot;
+  }
+}
+
+// One warp per (b,t,h): row dot products and dx.
+//   ddt_x = <dx~, x>;  dS = <dY, Y - D x> - dt * ddt_x;  dDrow = <dY, x>;  dx = dx~ * dt + D * dY
+__global__ void ssd_rowdots_kernel(SsdP p, float* __restrict__ dx, int64_t lddx, float* __restrict__ ddt_x,
+                                   float* __restrict__ dS, float* __restrict__ dDrow) {
+  int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  int64_t total = (int64_t)p.B * p.T * p.H;
+  if (w >= total) return;
+  int h = (int)(w % p.H); int64_t tk = w / p.H;
+  float dtv = p.dtv(tk, h), Dv = p.D ? p.D[h] : 0.0f;
+  float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+  for (int pp = lane; pp < p.P; pp += 32) {
+    float xv = p.x[tk * p.ldx + h * p.P + pp];
+    float dxt = p.dxt[tk * (int64_t)(p.H * p.P) + h * p.P + pp];
+    float dyv = p.dy[tk * p.lddy + h * p.P + pp];
+    float yv = p.y[tk * p.ldy + h * p.P + pp] - Dv * xv;
+    s1 = fmaf(dxt, xv, s1);
+    s2 = fmaf(dyv, yv, s2);
+    s3 = fmaf(dyv, xv, s3);
+    dx[tk * lddx + h * p.P + pp] = fmaf(dxt, dtv, Dv * dyv);
+  }
+  s1 = warp_sum(s1); s2 = warp_sum(s2); s3 = warp_sum(s3);
+  if (lane == 0) {
+    ddt_x[w] = s1;
+    dS[w] = s2 - dtv * s1;
+    dDrow[w] = s3;
+  }
+}
+
+// One warp per (b,c,h): da = reverse inclusive cumsum of dS (dS[Q-1] += dsend).
+// a-mode (dt == NULL): writes da.  dt-mode: ddt = ddt_x + A da; partial sums of da*dt and dDrow per chunk.
+__global__ void ssd_chunk_finish_kernel(SsdP p, const float* __restrict__ ddt_x, const float* __restrict__ dS,
+                                        const float* __restrict__ dDrow, const float* __restrict__ dsend,
+                                        float* __restrict__ da_out, float* __restrict__ ddt_out, float* __restrict__ part) {
+  int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  int total = p.B * p.nc * p.H;
+  if (w >= total) return;
+  int h = w % p.H, bc = w / p.H, cc = bc % p.nc, bb = bc / p.nc;
+  float carry = 0.0f, pA = 0.0f, pD = 0.0f;
+  float Ah = p.dt ? p.A[h] : 0.0f;
+  int nblk = (p.Q + 31) / 32;
+  for (int blk = nblk - 1; blk >= 0; --blk) {
+    int q = blk * 32 + lane;
+    float v = 0.0f;
+    int64_t idx = 0;
+    if (q < p.Q) {
+      idx = p.tok(bb, cc, q) * p.H + h;
+      v = dS[idx];
+      if (q == p.Q - 1) v += dsend[w];
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      float u = __shfl_down_sync(0xffffffffu, v, o);
+      if (lane + o < 32) v += u;
+    }
+    v += carry;
+    if (q < p.Q) {
+      if (p.dt) {
+        ddt_out[idx] = fmaf(Ah, v, ddt_x[idx]);
+        pA = fmaf(v, p.dt[idx], pA);
+        pD += dDrow[idx];
+      } else {
+        da_out[idx] = v;
+      }
+    }
+    carry = __shfl_sync(0xffffffffu, v, 0);
+  }
+  if (p.dt) {
+    pA = warp_sum(pA); pD = warp_sum(pD);
+    if (lane == 0) {
+      part[(int64_t)bc * p.H + h] = pA;
+      part[(int64_t)p.B * p.nc * p.H + (int64_t)bc * p.H + h] = pD;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base, size_t bytes, SsdWs* out) {
+  Arena ar(base, bytes);
+  int nc = T / Q;
+  SsdWs w;
+  w.S = ar.take<float>((size_t)B * H * T);
+  w.hprev = ar.take<float>((size_t)B * nc * H * N * P);
+  w.hlast = ar.take<float>((size_t)B * H * N * P);
+  w.CB = ar.take<float>((size_t)B * nc * G * Q * Q);
+  w.dh = ar.take<float>((size_t)B * nc * H * N * P);
+  w.dG = ar.take<float>((size_t)B * nc * G * Q * Q);
+  w.dxt = ar.take<float>((size_t)B * T * H * P);
+  w.rows = ar.take<float>((size_t)4 * B * T * H);
+  w.part = ar.take<float>((size_t)B * nc * 2 * H);
+  if (out) *out = w;
+  return ar.ok ? ar.used() : 0;
+}
+
+static pmb_status fill_params(const SsdIn& in, const SsdWs& ws, SsdP* pp) {
+  if (in.Q <= 0 || in.T % in.Q != 0) return fail(PMB_ERR_SHAPE, "ssd: T=%d is not a multiple of block_len=%d", in.T, in.Q);
+  if (!(in.G == 1 || in.G == in.H)) return fail(PMB_ERR_SHAPE, "ssd: n_groups must be 1 or n_heads");
+  if ((int64_t)in.N * in.P > (int64_t)SPB_THREADS * SPB_MAX_PER_THREAD)
+    return fail(PMB_ERR_SHAPE, "ssd: d_state*d_head=%lld exceeds %d", (long long)in.N * in.P, SPB_THREADS * SPB_MAX_PER_THREAD);
+  SsdP p{};
+  p.B = in.B; p.T = in.T; p.H = in.H; p.P = in.P; p.N = in.N; p.G = in.G; p.Q = in.Q; p.nc = in.T / in.Q; p.hpg = in.H / in.G;
+  p.x = in.x; p.ldx = in.ldx; p.dt = in.dt; p.A = in.A; p.a = in.a; p.b = in.b; p.c = in.c; p.ldbc = in.ldbc; p.D = in.D;
+  p.S = ws.S; p.hprev = ws.hprev; p.hlast = ws.hlast; p.CB = ws.CB; p.dh = ws.dh; p.dG = ws.dG; p.dxt = ws.dxt;
+  *pp = p;
+  return PMB_OK;
+}
+
+template <class Op>
+static Op make_op(const SsdP& p, int Mdim, int Ndim) {
+  Op op{};
+  op.p = p; op.Mdim = Mdim; op.Ndim = Ndim;
+  return op;
+}
+
+pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, float* y, int64_t ldy, float* final_state,
+                   const SsdWs& ws) {
+  SsdP p;
+  PMB_TRY(fill_params(in, ws, &p));
+  p.yout = y; p.ldyo = ldy;
+  int nbch = p.B * p.nc * p.H, nbcg = p.B * p.nc * p.G;
+  chunk_cumsum_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p);
+  PMB_LAUNCHED();
+  PMB_TRY(launch_bgemm(st, make_op<OpCB>(p, p.Q, p.Q), nbcg));
+  PMB_TRY(launch_bgemm(st, make_op<OpState>(p, p.N, p.P), nbch));
+  int64_t nel = (int64_t)p.B * p.H * p.N * p.P;
+  state_pass_kernel<<<(unsigned)cdiv(nel, 256), 256, 0, st>>>(p, init_state);
+  PMB_LAUNCHED();
+  PMB_TRY(launch_bgemm(st, make_op<OpScan>(p, p.Q, p.P), nbch));
+  if (final_state) PMB_CUDA(cudaMemcpyAsync(final_state, ws.hlast, (size_t)nel * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  return PMB_OK;
+}
+
+pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy, const float* dy, int64_t lddy,
+                   const SsdGrads& g, const SsdWs& ws) {
+  SsdP p;
+  PMB_TRY(fill_params(in, ws, &p));
+  p.y = y; p.ldy = ldy; p.dy = dy; p.lddy = lddy; p.db = g.db; p.dc = g.dc; p.lddbc = g.lddbc;
+  int nbch = p.B * p.nc * p.H, nbcg = p.B * p.nc * p.G;
+  int64_t rows = (int64_t)p.B * p.T * p.H;
+  float* ddt_x = ws.rows; float* dS = ws.rows + rows; float* dDrow = ws.rows + 2 * rows; float* dsend = ws.rows + 3 * rows;
+  PMB_TRY(launch_bgemm(st, make_op<OpDstate>(p, p.N, p.P), nbch));
+  state_pass_bwd_kernel<<<(unsigned)(p.B * p.H), SPB_THREADS, 0, st>>>(p, dsend);
+  PMB_LAUNCHED();
+  PMB_TRY(launch_bgemm(st, make_op<OpDx>(p, p.Q, p.P), nbch));
+  ssd_rowdots_kernel<<<(unsigned)cdiv(rows * 32, 256), 256, 0, st>>>(p, g.dx, g.lddx, ddt_x, dS, dDrow);
+  PMB_LAUNCHED();
+  ssd_chunk_finish_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p, ddt_x, dS, dDrow, dsend, g.da, g.ddt, ws.part);
+  PMB_LAUNCHED();
+  if (in.dt) {  // part = [dA partials (B*nc,H)] [dD partials (B*nc,H)]
+    PMB_TRY(column_sum(st, ws.part, (int64_t)p.B * p.nc, p.H, g.dA));
+    if (g.dD) PMB_TRY(column_sum(st, ws.part + (int64_t)p.B * p.nc * p.H, (int64_t)p.B * p.nc, p.H, g.dD));
+  }
+  PMB_TRY(launch_bgemm(st, make_op<OpDG>(p, p.Q, p.Q), nbcg));
+  PMB_TRY(launch_bgemm(st, make_op<OpDC>(p, p.Q, p.N), nbcg));
+  PMB_TRY(launch_bgemm(st, make_op<OpDB>(p, p.Q, p.N), nbcg));
+  return PMB_OK;
+}
+
+}  // namespace pmb

@@ -1,0 +1,431 @@
+"""Host-side mirror of the reference's operator interface for the Mamba2 SSD block path,
+bound to libpm_b200.so (hand-written sm_100a CUDA) through its C ABI with ctypes.
+
+Names follow the reference: `Mamba2Config` / `Mamba2Block.forward` / `Mamba2Block.step`
+(crates/pm-core/src/mamba2/block.rs:48-88,118-226,278-417), `ssd_scan` (crates/pm-core/src/ops.rs:345-352),
+`ContextEncoder.forward_checkpointed` + `checkpoint_backward` (photon/encoder.rs:73-87, checkpoint.rs:110-135),
+`FlatMamba` (flat.rs:89-161).  torch is used only to own device memory and streams; every computation is a
+call into the library, and there is no CPU or eager-PyTorch fallback: a missing library raises ImportError.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import pathlib
+from dataclasses import dataclass
+
+import torch
+
+_HERE = pathlib.Path(__file__).resolve().parent
+_LIB_PATH = _HERE / "libpm_b200.so"
+
+PARAM_ORDER = ("in_proj_weight", "conv1d_weight", "conv1d_bias", "a_log", "d_skip", "dt_bias",
+               "norm_weight", "out_proj_weight")
+
+
+class PmbError(RuntimeError):
+    """Raised when a library call returns a non-zero pmb_status (the reference's typed backend error,
+    crates/pm-cuda/src/error.rs:4-23)."""
+
+    def __init__(self, status: int, text: str):
+        super().__init__(f"pm_b200 status {status}: {text}")
+        self.status = status
+
+
+class _Cfg(C.Structure):
+    _fields_ = [("d_model", C.c_int32), ("d_state", C.c_int32), ("d_head", C.c_int32), ("n_heads", C.c_int32),
+                ("n_groups", C.c_int32), ("d_conv", C.c_int32), ("block_len", C.c_int32), ("rmsnorm_eps", C.c_float)]
+
+
+class _Params(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in PARAM_ORDER]
+
+
+LAYER_CALLBACK = C.CFUNCTYPE(None, C.c_int32, C.c_void_p)
+
+
+def _load():
+    if not _LIB_PATH.exists():
+        raise ImportError(f"{_LIB_PATH} is missing: build it with `python photon-mamba2-llm_b200/build.py` "
+                          "(there is no fallback path)")
+    lib = C.CDLL(str(_LIB_PATH))
+    vp, i32, i64, f32, sz = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_size_t
+    cfgp = C.POINTER(_Cfg)
+    sig = {
+        "pmb_last_error": (C.c_char_p, []),
+        "pmb_version": (C.c_char_p, []),
+        "pmb_launch_count": (i64, []),
+        "pmb_device_status": (i32, [C.POINTER(i32)]),
+        "pmb_gemm_f32": (i32, [vp, i32, i32, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp, i32]),
+        "pmb_conv_silu_dt_fwd": (i32, [vp, cfgp, i32, i32, vp, vp, vp, vp, vp, vp]),
+        "pmb_conv_bwd_workspace_bytes": (sz, [cfgp, i32, i32]),
+        "pmb_conv_silu_bwd": (i32, [vp, cfgp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, sz]),
+        "pmb_ssd_workspace_bytes": (sz, [i32] * 7),
+        "pmb_ssd_scan_fwd": (i32, [vp] + [i32] * 7 + [vp, i64, vp, vp, vp, i64, vp, vp, i64, vp, vp, sz]),
+        "pmb_ssd_scan_bwd": (i32, [vp] + [i32] * 7 + [vp, i64, vp, vp, vp, i64, vp, i64, vp, i64, vp, i64, vp, vp, vp, i64, vp, sz]),
+        "pmb_gated_rmsnorm_fwd": (i32, [vp, i64, i32, f32, vp, vp, i64, vp, vp, vp]),
+        "pmb_gated_rmsnorm_bwd_workspace_bytes": (sz, [i64, i32]),
+        "pmb_gated_rmsnorm_bwd": (i32, [vp, i64, i32, vp, vp, vp, i64, vp, vp, vp, vp, i64, vp, vp, sz]),
+        "pmb_mamba2_block_workspace_bytes": (sz, [cfgp, i32, i32]),
+        "pmb_mamba2_block_fwd": (i32, [vp, cfgp, C.POINTER(_Params), i32, i32, vp, vp, vp, vp, sz]),
+        "pmb_mamba2_block_bwd": (i32, [vp, cfgp, C.POINTER(_Params), i32, i32, vp, vp, vp, vp, C.POINTER(_Params), vp, sz]),
+        "pmb_mamba2_step_workspace_bytes": (sz, [cfgp, i32]),
+        "pmb_mamba2_step": (i32, [vp, cfgp, C.POINTER(_Params), i32, vp, vp, vp, vp, vp, sz]),
+        "pmb_stack_fwd_ckpt": (i32, [vp, cfgp, i32, C.POINTER(_Params), i32, i32, vp, vp, sz]),
+        "pmb_stack_bwd": (i32, [vp, cfgp, i32, C.POINTER(_Params), C.POINTER(_Params), i32, i32, vp, vp, vp, sz, LAYER_CALLBACK, vp]),
+        "pmb_lm_create": (i32, [cfgp, i32, i32, i32, i32, C.POINTER(vp)]),
+        "pmb_lm_destroy": (None, [vp]),
+        "pmb_lm_param_count": (i64, [vp]),
+        "pmb_lm_param_offset": (i64, [vp, i32, i32]),
+        "pmb_lm_params": (vp, [vp]),
+        "pmb_lm_grads": (vp, [vp]),
+        "pmb_lm_activation_bytes": (i64, [vp]),
+        "pmb_lm_step_device": (i32, [vp, vp, vp, vp, LAYER_CALLBACK, vp]),
+        "pmb_lm_loss_device": (vp, [vp]),
+        "pmb_lm_step_host": (i32, [vp, vp, vp, vp, C.POINTER(f32), LAYER_CALLBACK, vp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)   # AttributeError here = the library does not export a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    return lib, sorted(sig)
+
+
+lib, EXPORTED = _load()
+
+
+def _check(status: int):
+    if status != 0:
+        raise PmbError(status, lib.pmb_last_error().decode())
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _dev(t: torch.Tensor, name: str) -> torch.Tensor:
+    if not (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()):
+        raise PmbError(2, f"{name}: expected a contiguous float32 CUDA tensor, got {t.dtype} on {t.device}")
+    return t
+
+
+def launch_count() -> int:
+    return int(lib.pmb_launch_count())
+
+
+def device_status() -> int:
+    w = C.c_int32(0)
+    _check(lib.pmb_device_status(C.byref(w)))
+    return w.value
+
+
+@dataclass
+class Mamba2Config:
+    """crates/pm-core/src/mamba2/block.rs:48-72."""
+    d_model: int
+    d_state: int
+    d_head: int
+    n_heads: int
+    n_groups: int = 1
+    d_conv: int = 4
+    block_len: int = 64
+    rmsnorm_eps: float = 1e-5
+
+    @property
+    def d_inner(self): return self.n_heads * self.d_head
+    @property
+    def xbc_dim(self): return self.d_inner + 2 * self.n_groups * self.d_state
+    @property
+    def in_proj_dim(self): return self.d_inner + self.xbc_dim + self.n_heads
+
+    def c(self) -> _Cfg:
+        return _Cfg(self.d_model, self.d_state, self.d_head, self.n_heads, self.n_groups, self.d_conv,
+                    self.block_len, self.rmsnorm_eps)
+
+    def param_shapes(self):
+        return {"in_proj_weight": (self.d_model, self.in_proj_dim), "conv1d_weight": (self.xbc_dim, 1, self.d_conv),
+                "conv1d_bias": (self.xbc_dim,), "a_log": (self.n_heads,), "d_skip": (self.n_heads,),
+                "dt_bias": (self.n_heads,), "norm_weight": (self.d_inner,), "out_proj_weight": (self.d_inner, self.d_model)}
+
+
+def _params_struct(p: dict) -> _Params:
+    s = _Params()
+    for n in PARAM_ORDER:
+        setattr(s, n, _dev(p[n], n).data_ptr())
+    return s
+
+
+# ------------------------------------------------------------------------------------------------
+# primitive ops
+# ------------------------------------------------------------------------------------------------
+
+def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a=False, trans_b=False, residual=None, engine=0, out=None):
+    """Ops::matmul on 2-D operands.  C = op(a) @ op(b) (+ residual)."""
+    _dev(a, "a"); _dev(b, "b")
+    M, K = (a.shape[1], a.shape[0]) if trans_a else a.shape
+    K2, N = (b.shape[1], b.shape[0]) if trans_b else b.shape
+    if K != K2:
+        raise PmbError(1, f"matmul: inner dimensions differ ({K} vs {K2})")
+    if out is None:
+        out = torch.empty(M, N, device=a.device, dtype=torch.float32)
+    _check(lib.pmb_gemm_f32(_stream(), int(trans_a), int(trans_b), M, N, K, a.data_ptr(), a.stride(0), b.data_ptr(),
+                            b.stride(0), out.data_ptr(), out.stride(0), _ptr(residual), engine))
+    return out
+
+
+def conv_silu_dt_fwd(cfg: Mamba2Config, xzd, conv_w, conv_b, dt_bias):
+    B, T, J = xzd.shape
+    act = torch.empty(B, T, cfg.xbc_dim, device=xzd.device, dtype=torch.float32)
+    dt = torch.empty(B, T, cfg.n_heads, device=xzd.device, dtype=torch.float32)
+    _check(lib.pmb_conv_silu_dt_fwd(_stream(), C.byref(cfg.c()), B, T, _dev(xzd, "xzd").data_ptr(), conv_w.data_ptr(),
+                                    _ptr(conv_b), dt_bias.data_ptr(), act.data_ptr(), dt.data_ptr()))
+    return act, dt
+
+
+def conv_silu_bwd(cfg: Mamba2Config, xzd, conv_w, conv_b, dact):
+    B, T, J = xzd.shape
+    dxzd = torch.zeros_like(xzd)
+    dw = torch.empty_like(conv_w)
+    db = torch.empty(cfg.xbc_dim, device=xzd.device, dtype=torch.float32)
+    n = lib.pmb_conv_bwd_workspace_bytes(C.byref(cfg.c()), B, T)
+    ws = torch.empty(n, device=xzd.device, dtype=torch.uint8)
+    _check(lib.pmb_conv_silu_bwd(_stream(), C.byref(cfg.c()), B, T, xzd.data_ptr(), conv_w.data_ptr(), _ptr(conv_b),
+                                 _dev(dact, "dact").data_ptr(), dxzd.data_ptr(), dw.data_ptr(), db.data_ptr(), ws.data_ptr(), n))
+    return dxzd, dw, db
+
+
+class SsdScan:
+    """`Ops::ssd_scan` with its backward.  x (B,T,H,P), a (B,T,H), b/c (B,T,G,N), G in {1,H}."""
+
+    def __init__(self, x, a, b, c, block_len):
+        self.x, self.a, self.b, self.c = (_dev(t, n) for t, n in ((x, "x"), (a, "a"), (b, "b"), (c, "c")))
+        self.B, self.T, self.H, self.P = x.shape
+        self.G, self.N = b.shape[2], b.shape[3]
+        q = block_len
+        if q <= 0 or q >= self.T or self.T % q != 0:   # the reference's dense route (ssd_ops.rs:70-78)
+            q = self.T
+        self.Q = q
+        self.dims = (self.B, self.T, self.H, self.P, self.N, self.G, self.Q)
+        n = lib.pmb_ssd_workspace_bytes(*self.dims)
+        if n == 0:
+            raise PmbError(1, lib.pmb_last_error().decode())
+        self.ws = torch.empty(n, device=x.device, dtype=torch.uint8)
+        self.y = None
+
+    def forward(self, init_state=None, want_final_state=False):
+        x, b = self.x, self.b
+        self.y = torch.empty_like(x)
+        fs = torch.empty(self.B, self.H, self.N, self.P, device=x.device, dtype=torch.float32) if want_final_state else None
+        _check(lib.pmb_ssd_scan_fwd(_stream(), *self.dims, x.data_ptr(), self.H * self.P, self.a.data_ptr(),
+                                    b.data_ptr(), self.c.data_ptr(), self.G * self.N, _ptr(init_state), self.y.data_ptr(),
+                                    self.H * self.P, _ptr(fs), self.ws.data_ptr(), self.ws.numel()))
+        return (self.y, fs) if want_final_state else self.y
+
+    def backward(self, dy):
+        x = self.x
+        dx, da, db, dc = torch.empty_like(x), torch.empty_like(self.a), torch.empty_like(self.b), torch.empty_like(self.c)
+        hp, gn = self.H * self.P, self.G * self.N
+        _check(lib.pmb_ssd_scan_bwd(_stream(), *self.dims, x.data_ptr(), hp, self.a.data_ptr(), self.b.data_ptr(),
+                                    self.c.data_ptr(), gn, self.y.data_ptr(), hp, _dev(dy, "dy").data_ptr(), hp,
+                                    dx.data_ptr(), hp, da.data_ptr(), db.data_ptr(), dc.data_ptr(), gn,
+                                    self.ws.data_ptr(), self.ws.numel()))
+        return dx, da, db, dc
+
+
+def ssd_scan(x, a, b, c, block_len):
+    return SsdScan(x, a, b, c, block_len).forward()
+
+
+def gated_rmsnorm_fwd(y, z, w, eps):
+    rows, width = y.shape
+    out = torch.empty_like(y)
+    rstd = torch.empty(rows, device=y.device, dtype=torch.float32)
+    _check(lib.pmb_gated_rmsnorm_fwd(_stream(), rows, width, eps, _dev(y, "y").data_ptr(), z.data_ptr(), z.stride(0),
+                                     w.data_ptr(), out.data_ptr(), rstd.data_ptr()))
+    return out, rstd
+
+
+def gated_rmsnorm_bwd(dout, y, z, w, rstd):
+    rows, width = y.shape
+    dy, dz, dw = torch.empty_like(y), torch.empty(rows, width, device=y.device, dtype=torch.float32), torch.empty_like(w)
+    n = lib.pmb_gated_rmsnorm_bwd_workspace_bytes(rows, width)
+    ws = torch.empty(n, device=y.device, dtype=torch.uint8)
+    _check(lib.pmb_gated_rmsnorm_bwd(_stream(), rows, width, _dev(dout, "dout").data_ptr(), y.data_ptr(), z.data_ptr(),
+                                     z.stride(0), w.data_ptr(), rstd.data_ptr(), dy.data_ptr(), dz.data_ptr(), width,
+                                     dw.data_ptr(), ws.data_ptr(), n))
+    return dy, dz, dw
+
+
+# ------------------------------------------------------------------------------------------------
+# Mamba2Block
+# ------------------------------------------------------------------------------------------------
+
+class Mamba2Block:
+    """One block: parameters are a dict of fp32 CUDA tensors in `PARAM_ORDER`."""
+
+    def __init__(self, config: Mamba2Config, params: dict):
+        self.config = config
+        self.params = {k: _dev(params[k], k) for k in PARAM_ORDER}
+        for k, shp in config.param_shapes().items():
+            if tuple(self.params[k].shape) != tuple(shp):
+                raise PmbError(1, f"{k}: shape {tuple(self.params[k].shape)} != {shp}")
+        self._ws = None
+
+    def _workspace(self, B, T, device):
+        n = lib.pmb_mamba2_block_workspace_bytes(C.byref(self.config.c()), B, T)
+        if n == 0:
+            raise PmbError(1, lib.pmb_last_error().decode())
+        if self._ws is None or self._ws.numel() < n:
+            self._ws = torch.empty(n, device=device, dtype=torch.uint8)
+        return self._ws
+
+    def forward(self, x, residual=None):
+        B, T, D = x.shape
+        ws = self._workspace(B, T, x.device)
+        out = torch.empty_like(x)
+        ps = _params_struct(self.params)
+        _check(lib.pmb_mamba2_block_fwd(_stream(), C.byref(self.config.c()), C.byref(ps), B, T, _dev(x, "x").data_ptr(),
+                                        _ptr(residual), out.data_ptr(), ws.data_ptr(), ws.numel()))
+        return out
+
+    def backward(self, x, dout, dx_accum=None):
+        """Recomputes the block from `x` and returns (dx, {param gradients})."""
+        B, T, D = x.shape
+        ws = self._workspace(B, T, x.device)
+        dx = torch.empty_like(x)
+        grads = {k: torch.empty_like(v) for k, v in self.params.items()}
+        ps, gs = _params_struct(self.params), _params_struct(grads)
+        _check(lib.pmb_mamba2_block_bwd(_stream(), C.byref(self.config.c()), C.byref(ps), B, T, _dev(x, "x").data_ptr(),
+                                        _dev(dout, "dout").data_ptr(), _ptr(dx_accum), dx.data_ptr(), C.byref(gs),
+                                        ws.data_ptr(), ws.numel()))
+        return dx, grads
+
+    def zero_state(self, batch, device="cuda"):
+        cfg = self.config
+        return {"ssm_state": torch.zeros(batch, cfg.n_heads, cfg.d_state, cfg.d_head, device=device),
+                "conv_window": torch.zeros(batch, cfg.xbc_dim, cfg.d_conv - 1, device=device)}
+
+    def step(self, x_t, state):
+        """`Mamba2Block::step`: x_t (B,1,D); the state dict is updated in place and returned."""
+        B = x_t.shape[0]
+        n = lib.pmb_mamba2_step_workspace_bytes(C.byref(self.config.c()), B)
+        ws = torch.empty(n, device=x_t.device, dtype=torch.uint8)
+        y = torch.empty_like(x_t)
+        ps = _params_struct(self.params)
+        _check(lib.pmb_mamba2_step(_stream(), C.byref(self.config.c()), C.byref(ps), B, _dev(x_t, "x_t").data_ptr(),
+                                   state["ssm_state"].data_ptr(), state["conv_window"].data_ptr(), y.data_ptr(),
+                                   ws.data_ptr(), n))
+        return y, state
+
+
+class ContextEncoder:
+    """Residual stack h_l = h_{l-1} + Block_l(h_{l-1}) with the re-planned checkpoint policy."""
+
+    def __init__(self, config: Mamba2Config, layers: list):
+        self.config = config
+        self.layers = [{k: _dev(p[k], k) for k in PARAM_ORDER} for p in layers]
+        self._ws = None
+
+    def _arrays(self, dicts):
+        arr = (_Params * len(dicts))()
+        for i, p in enumerate(dicts):
+            arr[i] = _params_struct(p)
+        return arr
+
+    def forward_checkpointed(self, x):
+        B, T, D = x.shape
+        L = len(self.layers)
+        n = lib.pmb_mamba2_block_workspace_bytes(C.byref(self.config.c()), B, T)
+        if self._ws is None or self._ws.numel() < n:
+            self._ws = torch.empty(n, device=x.device, dtype=torch.uint8)
+        saved = torch.empty(L + 1, B, T, D, device=x.device, dtype=torch.float32)
+        saved[0].copy_(x)
+        _check(lib.pmb_stack_fwd_ckpt(_stream(), C.byref(self.config.c()), L, self._arrays(self.layers), B, T,
+                                      saved.data_ptr(), self._ws.data_ptr(), self._ws.numel()))
+        return saved[L], saved
+
+    def checkpoint_backward(self, saved, dhidden, on_layer_done=None):
+        L, B, T, D = saved.shape[0] - 1, saved.shape[1], saved.shape[2], saved.shape[3]
+        grads = [{k: torch.empty_like(v) for k, v in p.items()} for p in self.layers]
+        dh = dhidden.clone()
+        cb = LAYER_CALLBACK(on_layer_done) if on_layer_done else C.cast(None, LAYER_CALLBACK)
+        _check(lib.pmb_stack_bwd(_stream(), C.byref(self.config.c()), L, self._arrays(self.layers), self._arrays(grads),
+                                 B, T, saved.data_ptr(), dh.data_ptr(), self._ws.data_ptr(), self._ws.numel(), cb, None))
+        return dh, grads
+
+
+class FlatMamba:
+    """Flat LM (tied embedding -> stack -> tied head -> mean CE).  Owns a library model handle whose flat
+    parameter/gradient buffers are exposed as torch views."""
+
+    def __init__(self, config: Mamba2Config, n_layers: int, vocab: int, batch: int, seqlen: int):
+        self.config, self.n_layers, self.vocab, self.batch, self.seqlen = config, n_layers, vocab, batch, seqlen
+        h = C.c_void_p()
+        _check(lib.pmb_lm_create(C.byref(config.c()), n_layers, vocab, batch, seqlen, C.byref(h)))
+        self._h = h
+        n = lib.pmb_lm_param_count(h)
+        self.flat_params = _as_tensor(lib.pmb_lm_params(h), n)
+        self.flat_grads = _as_tensor(lib.pmb_lm_grads(h), n)
+        self.loss_dev = _as_tensor(lib.pmb_lm_loss_device(h), 1)
+
+    def view(self, flat, layer, which=0):
+        """Tensor view of one parameter (layer=-1: embedding (V,D))."""
+        off = lib.pmb_lm_param_offset(self._h, layer, which)
+        if layer < 0:
+            shp = (self.vocab, self.config.d_model)
+        else:
+            shp = self.config.param_shapes()[PARAM_ORDER[which]]
+        n = 1
+        for s in shp:
+            n *= s
+        return flat[off:off + n].view(*shp)
+
+    def load(self, embed, layers):
+        self.view(self.flat_params, -1).copy_(embed)
+        for l, p in enumerate(layers):
+            for w, name in enumerate(PARAM_ORDER):
+                self.view(self.flat_params, l, w).copy_(p[name])
+
+    def grads(self):
+        g_embed = self.view(self.flat_grads, -1)
+        g_layers = [{name: self.view(self.flat_grads, l, w) for w, name in enumerate(PARAM_ORDER)} for l in range(self.n_layers)]
+        return g_embed, g_layers
+
+    @property
+    def activation_bytes(self):
+        return int(lib.pmb_lm_activation_bytes(self._h))
+
+    def step_device(self, ids, targets, on_layer_done=None):
+        cb = LAYER_CALLBACK(on_layer_done) if on_layer_done else C.cast(None, LAYER_CALLBACK)
+        _check(lib.pmb_lm_step_device(self._h, _stream(), ids.data_ptr(), targets.data_ptr(), cb, None))
+        return self.loss_dev
+
+    def step_host(self, ids_host, targets_host, on_layer_done=None):
+        """ids/targets: int64 CPU tensors (pinned for an asynchronous copy).  Returns the loss as a float."""
+        loss = C.c_float(0)
+        cb = LAYER_CALLBACK(on_layer_done) if on_layer_done else C.cast(None, LAYER_CALLBACK)
+        _check(lib.pmb_lm_step_host(self._h, _stream(), ids_host.data_ptr(), targets_host.data_ptr(), C.byref(loss), cb, None))
+        return loss.value
+
+    def close(self):
+        if self._h:
+            lib.pmb_lm_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _as_tensor(ptr: int, n: int) -> torch.Tensor:
+    """Wraps library-owned device memory (fp32) as a torch tensor without copying."""
+    class _Iface:
+        pass
+    o = _Iface()
+    o.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (int(ptr), False), "version": 2}
+    return torch.as_tensor(o, device="cuda")

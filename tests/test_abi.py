@@ -1,0 +1,59 @@
+"""CPU-side checks of the drop-in boundary: the library loads, exports every symbol the public header
+declares, and its host-only entry points behave (sizes, shape errors).  No kernel is launched here."""
+import ctypes as C
+import pathlib
+import re
+
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def pm():
+    import __graft_entry__ as ge
+    ge.build()
+    import pm_b200
+    return pm_b200
+
+
+def test_every_declared_symbol_is_exported(pm):
+    header = (ROOT / "include" / "pm_b200.h").read_text()
+    body = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(pmb_[a-z0-9_]+)\s*\(", body))
+    declared -= {"pmb_layer_callback"}
+    assert len(declared) >= 30
+    lib = C.CDLL(str(ROOT / "photon-mamba2-llm_b200" / "pm_b200" / "libpm_b200.so"))
+    missing = [s for s in sorted(declared) if not hasattr(lib, s)]
+    assert not missing, f"declared in include/pm_b200.h but not exported: {missing}"
+    assert set(pm.EXPORTED) == declared, sorted(set(pm.EXPORTED) ^ declared)
+
+
+def test_version_and_launch_counter(pm):
+    assert b"sm_100a" in pm.lib.pmb_version()
+    assert pm.launch_count() >= 0
+
+
+def test_workspace_sizes_and_shape_errors(pm):
+    cfg = pm.Mamba2Config(d_model=128, d_state=16, d_head=32, n_heads=8, block_len=64)
+    assert cfg.in_proj_dim == 552 and cfg.xbc_dim == 288
+    n = pm.lib.pmb_mamba2_block_workspace_bytes(C.byref(cfg.c()), 2, 128)
+    assert n > 2 * 128 * 552 * 4 * 2
+    assert pm.lib.pmb_ssd_workspace_bytes(1, 128, 2, 8, 16, 2, 64) > 0
+    # T not a multiple of block_len is rejected by the raw scan entry point
+    assert pm.lib.pmb_ssd_workspace_bytes(1, 100, 2, 8, 16, 2, 64) == 0
+    assert b"multiple" in pm.lib.pmb_last_error()
+    # n_groups must be 1 or n_heads (block.rs:128-131)
+    bad = pm.Mamba2Config(d_model=128, d_state=16, d_head=32, n_heads=8, n_groups=2)
+    assert pm.lib.pmb_mamba2_block_workspace_bytes(C.byref(bad.c()), 2, 128) == 0
+    # block_len that does not divide T falls back to one chunk over the sequence (ssd_ops.rs:70-78)
+    odd = pm.Mamba2Config(d_model=128, d_state=16, d_head=32, n_heads=8, block_len=48)
+    assert pm.lib.pmb_mamba2_block_workspace_bytes(C.byref(odd.c()), 2, 128) > 0
+
+
+def test_null_arguments_are_errors_not_crashes(pm):
+    cfg = pm.Mamba2Config(d_model=128, d_state=16, d_head=32, n_heads=8, block_len=64)
+    st = pm.lib.pmb_mamba2_block_fwd(None, C.byref(cfg.c()), None, 2, 128, None, None, None, None, 0)
+    assert st == 6
+    st = pm.lib.pmb_gemm_f32(None, 0, 0, 0, 4, 4, None, 4, None, 4, None, 4, None, 0)
+    assert st == 1

@@ -1,0 +1,62 @@
+"""Shared helpers for the parity tests."""
+import pathlib
+
+import numpy as np
+import torch
+
+from oracle import mamba2_oracle as orc
+
+GOLD = pathlib.Path(__file__).resolve().parent / "golden"
+
+# Parity bar for fp32 work: max |ours - oracle| <= FP32_TOL * max |oracle| per tensor
+# (the reference compares backends by max-abs error at 1e-4 on O(1) data, SUMMARY.md:44-45).
+FP32_TOL = 1e-4
+
+
+def rel_err(ours, ref) -> float:
+    ours = ours.detach().double().cpu() if torch.is_tensor(ours) else torch.as_tensor(np.asarray(ours)).double()
+    ref = ref.detach().double().cpu() if torch.is_tensor(ref) else torch.as_tensor(np.asarray(ref)).double()
+    assert ours.shape == ref.shape, (ours.shape, ref.shape)
+    scale = float(ref.abs().max())
+    return float((ours - ref).abs().max()) / (scale if scale > 0 else 1.0)
+
+
+def assert_close(ours, ref, tol=FP32_TOL, what=""):
+    e = rel_err(ours, ref)
+    assert e <= tol, f"{what}: rel max err {e:.3e} > {tol:.1e}"
+    return e
+
+
+def randn(shape, seed, scale=1.0):
+    g = torch.Generator(); g.manual_seed(seed)
+    return torch.randn(shape, generator=g) * scale
+
+
+def rand(shape, seed):
+    g = torch.Generator(); g.manual_seed(seed)
+    return torch.rand(shape, generator=g)
+
+
+def oracle_cfg(**kw):
+    return orc.Mamba2Config(**kw)
+
+
+def to_pm_cfg(cfg):
+    import pm_b200
+    return pm_b200.Mamba2Config(d_model=cfg.d_model, d_state=cfg.d_state, d_head=cfg.d_head, n_heads=cfg.n_heads,
+                                n_groups=cfg.n_groups, d_conv=cfg.d_conv, block_len=cfg.block_len,
+                                rmsnorm_eps=cfg.rmsnorm_eps)
+
+
+def block_params(cfg, seed, perturb=True):
+    """Oracle-initialised block parameters; bias/norm weight perturbed so their gradients matter."""
+    p = orc.init_block_params(cfg, seed)
+    if perturb:
+        p["conv1d_bias"] = p["conv1d_bias"] + randn(p["conv1d_bias"].shape, seed * 7 + 1, 0.1)
+        p["norm_weight"] = p["norm_weight"] + randn(p["norm_weight"].shape, seed * 7 + 2, 0.1)
+        p["d_skip"] = p["d_skip"] + randn(p["d_skip"].shape, seed * 7 + 3, 0.1)
+    return p
+
+
+def cuda_params(p):
+    return {k: v.detach().clone().cuda().contiguous() for k, v in p.items()}
