@@ -83,6 +83,12 @@ const char* pmb_last_error(void);
 const char* pmb_version(void);
 /* Number of kernels this library has launched since load (all threads). */
 int64_t pmb_launch_count(void);
+/* Optional per-kernel timing for benchmarks (no reference counterpart; the reference's analogue is its
+ * env-gated op profiler, crates/pm-cuda/src/profiler.rs).  Between start and stop every kernel group is
+ * bracketed by CUDA events on its launching stream; stop synchronises the device and writes a JSON array
+ * [{"name","launches","ms","flops","bytes"}] of per-name totals (algorithmic FLOPs / bytes) into h_json. */
+void pmb_profile_start(void);
+pmb_status pmb_profile_stop(char* h_json, size_t capacity);
 /* Reads and clears the device status word (0 = no kernel gave up on a bounded wait). */
 pmb_status pmb_device_status(int32_t* h_word_out);
 

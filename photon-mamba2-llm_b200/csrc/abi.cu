@@ -7,6 +7,8 @@ namespace pmb {
 
 thread_local char g_err[512] = "";
 std::atomic<long long> g_launches{0};
+bool g_prof_on = false;
+std::vector<ProfRec> g_prof;
 
 pmb_status gemm(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                 const float* B, int64_t ldb, float* C, int64_t ldc, const float* R, int engine) {
@@ -29,6 +31,38 @@ using namespace pmb;
 extern "C" const char* pmb_last_error(void) { return g_err; }
 extern "C" const char* pmb_version(void) { return "pm_b200 0.1 sm_100a"; }
 extern "C" int64_t pmb_launch_count(void) { return (int64_t)g_launches.load(); }
+
+extern "C" void pmb_profile_start(void) {
+  for (auto& r : g_prof) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
+  g_prof.clear();
+  g_prof_on = true;
+}
+
+// Writes a JSON array [{"name":..,"launches":..,"ms":..,"flops":..,"bytes":..},...] (totals per scope name).
+extern "C" pmb_status pmb_profile_stop(char* h_json, size_t capacity) {
+  g_prof_on = false;
+  PMB_CUDA(cudaDeviceSynchronize());
+  struct Agg { const char* name; long n; double ms, flops, bytes; };
+  std::vector<Agg> agg;
+  for (auto& r : g_prof) {
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, r.e0, r.e1);
+    cudaEventDestroy(r.e0); cudaEventDestroy(r.e1);
+    size_t i = 0;
+    for (; i < agg.size(); ++i) if (strcmp(agg[i].name, r.name) == 0) break;
+    if (i == agg.size()) agg.push_back(Agg{r.name, 0, 0, 0, 0});
+    agg[i].n += 1; agg[i].ms += ms; agg[i].flops += r.flops; agg[i].bytes += r.bytes;
+  }
+  g_prof.clear();
+  if (!h_json || capacity < 3) return fail(PMB_ERR_ARG, "profile_stop: buffer too small");
+  size_t off = 0;
+  off += snprintf(h_json + off, capacity - off, "[");
+  for (size_t i = 0; i < agg.size() && off + 256 < capacity; ++i)
+    off += snprintf(h_json + off, capacity - off, "%s{\"name\":\"%s\",\"launches\":%ld,\"ms\":%.6f,\"flops\":%.6e,\"bytes\":%.6e}",
+                    i ? "," : "", agg[i].name, agg[i].n, agg[i].ms, agg[i].flops, agg[i].bytes);
+  snprintf(h_json + off, capacity - off, "]");
+  return PMB_OK;
+}
 
 extern "C" pmb_status pmb_device_status(int32_t* h_word_out) {
   unsigned int w = 0;

@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <vector>
 #include "../../include/pm_b200.h"
 
 namespace pmb {
@@ -44,6 +45,27 @@ inline pmb_status fail(pmb_status st, const char* fmt, ...) {
       return pmb::fail(PMB_ERR_CUDA, "kernel launch failed: %s (%s:%d)", cudaGetErrorString(e__), \
                        __FILE__, __LINE__);                                                     \
   } while (0)
+
+// ---- optional per-kernel timing (off by default; pmb_profile_start/stop) -------------------------
+// A scope records one CUDA event before and one after the launches it brackets, on the launching
+// stream; pmb_profile_stop() synchronises and aggregates elapsed time, algorithmic FLOPs and bytes by name.
+struct ProfRec { const char* name; double flops, bytes; cudaEvent_t e0, e1; };
+extern bool g_prof_on;
+extern std::vector<ProfRec> g_prof;
+struct ProfScope {
+  cudaStream_t st; ProfRec r; bool on;
+  ProfScope(cudaStream_t s, const char* name, double flops, double bytes) : st(s), on(g_prof_on) {
+    if (!on) return;
+    r.name = name; r.flops = flops; r.bytes = bytes;
+    cudaEventCreate(&r.e0); cudaEventCreate(&r.e1);
+    cudaEventRecord(r.e0, st);
+  }
+  ~ProfScope() {
+    if (!on) return;
+    cudaEventRecord(r.e1, st);
+    g_prof.push_back(r);
+  }
+};
 
 inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }

@@ -89,6 +89,7 @@ static pmb_status launch_conv_fwd_k(cudaStream_t st, const Dims& d, const float*
 
 pmb_status conv_silu_dt_fwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
                             const float* dt_bias, float* act, float* dt) {
+  ProfScope prof(st, "conv_silu_dt_fwd", 0.0, 4.0 * d.M * (2.0 * d.X + 2.0 * d.H));
   switch (d.K) {
     case 2: PMB_TRY(launch_conv_fwd_k<2>(st, d, xzd, w, b, act)); break;
     case 3: PMB_TRY(launch_conv_fwd_k<3>(st, d, xzd, w, b, act)); break;
@@ -210,6 +211,7 @@ pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const
                          const float* dact, float* dxzd, float* dw, float* db, void* ws, size_t ws_bytes) {
   if (ws_bytes < conv_bwd_ws_bytes(d)) return fail(PMB_ERR_WORKSPACE, "conv bwd workspace too small");
   float* partial = static_cast<float*>(ws);
+  ProfScope prof(st, "conv_silu_bwd", 0.0, 4.0 * d.M * 3.0 * d.X);
   switch (d.K) {
     case 2: PMB_TRY(launch_conv_bwd_k<2>(st, d, xzd, w, b, dact, dxzd, partial)); break;
     case 3: PMB_TRY(launch_conv_bwd_k<3>(st, d, xzd, w, b, dact, dxzd, partial)); break;
@@ -261,6 +263,7 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_fwd_kernel(const f
 pmb_status gated_rmsnorm_fwd(cudaStream_t st, int64_t rows, int width, float eps, const float* y, const float* z, int64_t ldz,
                              const float* w, float* out, float* rstd) {
   if (width > NORM_THREADS * NORM_MAX_PER_THREAD) return fail(PMB_ERR_SHAPE, "rmsnorm width %d > %d", width, NORM_THREADS * NORM_MAX_PER_THREAD);
+  ProfScope prof(st, "gated_rmsnorm_fwd", 0.0, 4.0 * rows * 3.0 * width);
   gated_rmsnorm_fwd_kernel<<<(unsigned)rows, NORM_THREADS, 0, st>>>(y, z, ldz, w, out, rstd, width, eps);
   PMB_LAUNCHED();
   return PMB_OK;
@@ -329,6 +332,7 @@ pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const flo
   if (ws_bytes < gated_rmsnorm_bwd_ws_bytes(rows, width)) return fail(PMB_ERR_WORKSPACE, "rmsnorm bwd workspace too small");
   float* partial = static_cast<float*>(ws);
   int64_t nblk = cdiv(rows, NORM_ROWS);
+  ProfScope prof(st, "gated_rmsnorm_bwd", 0.0, 4.0 * rows * 5.0 * width);
   gated_rmsnorm_bwd_kernel<<<(unsigned)nblk, NORM_THREADS, 0, st>>>(dout, y, z, ldz, w, rstd, dy, dz, lddz, partial, rows, width);
   PMB_LAUNCHED();
   column_sum_kernel<<<(unsigned)cdiv(width, 256), 256, 0, st>>>(partial, nblk, width, dw);

@@ -31,6 +31,7 @@ pmb_status gemm_simt(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
   OpGemm op{};
   op.Mdim = (int)M; op.Ndim = (int)N; op.K = (int)K; op.ta = ta; op.tb = tb;
   op.A = A; op.lda = lda; op.B = B; op.ldb = ldb; op.C = C; op.ldc = ldc; op.R = R;
+  ProfScope prof(st, "gemm_simt", 2.0 * M * N * K, 4.0 * ((double)M * K + (double)K * N + (double)M * N * (R ? 2 : 1)));
   return launch_bgemm(st, op, 1);
 }
 

@@ -72,14 +72,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 }
 
 // Shared-memory matrix descriptor (tcgen05): start address, leading/stride byte offsets (16-byte units),
-// descriptor version 1, 128-byte swizzle.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// descriptor version 1, layout type (2 = 128-byte swizzle of 16-byte units, used for K-major tiles;
+// 1 = 128-byte swizzle of 32-byte units, the only layout the tensor core accepts for MN-major tf32).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)layout_type << 61;
   return d;
 }
 
@@ -179,6 +180,10 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                              ((uint32_t)(TBN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
       const uint32_t a_lbo = p.a_mn_major ? TBK * 128 : 16, b_lbo = p.b_mn_major ? TBK * 128 : 16;
       const uint32_t a_kstep = p.a_mn_major ? 1024 : 32, b_kstep = p.b_mn_major ? 1024 : 32;
+      // K-major: 8-row groups of 128-byte rows are 1024 B apart.  MN-major: the swizzle atom is 4 k-rows
+      // (512 B), MN blocks of 32 floats are TBK*128 B apart.
+      const uint32_t a_sbo = p.a_mn_major ? 512 : 1024, b_sbo = p.b_mn_major ? 512 : 1024;
+      const uint32_t a_lt = p.a_mn_major ? 1 : 2, b_lt = p.b_mn_major ? 1 : 2;
       bool ok = true;
       for (int kt = 0; kt < num_kt && ok; ++kt) {
         const int s = kt % STAGES;
@@ -189,8 +194,8 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
         const uint32_t a_hi = tiles + s * STAGE_BYTES, b_hi = a_hi + TILE_BYTES, a_lo = a_hi + 2 * TILE_BYTES, b_lo = a_hi + 3 * TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < TBK / 8; ++k) {
-          const uint64_t dah = make_desc(a_hi + k * a_kstep, a_lbo, 1024), dbh = make_desc(b_hi + k * b_kstep, b_lbo, 1024);
-          const uint64_t dal = make_desc(a_lo + k * a_kstep, a_lbo, 1024), dbl = make_desc(b_lo + k * b_kstep, b_lbo, 1024);
+          const uint64_t dah = make_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lt), dbh = make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lt);
+          const uint64_t dal = make_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lt), dbl = make_desc(b_lo + k * b_kstep, b_lbo, b_sbo, b_lt);
           mma_tf32(tmem_acc, dal, dbh, idesc, (kt > 0 || k > 0) ? 1u : 0u);
           mma_tf32(tmem_acc, dah, dbl, idesc, 1u);
           mma_tf32(tmem_acc, dah, dbh, idesc, 1u);
@@ -302,7 +307,8 @@ static EncodeTiledFn get_encode() {
 }
 
 // 2-D fp32 map: inner extent `inner` (contiguous), outer extent `outer` with row pitch ld floats.
-static pmb_status make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, int64_t ld, int box_inner, int box_outer) {
+static pmb_status make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, int64_t ld, int box_inner, int box_outer,
+                           CUtensorMapSwizzle swz) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return fail(PMB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
@@ -310,7 +316,7 @@ static pmb_status make_map(CUtensorMap* map, const float* base, int64_t inner, i
   cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(PMB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (inner=%lld outer=%lld ld=%lld)", (int)r,
                                      (long long)inner, (long long)outer, (long long)ld);
@@ -340,14 +346,16 @@ pmb_status gemm_tc(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_
   }
   CUtensorMap mapA, mapB;
   // A: ta=0 -> stored (M,K), K contiguous (K-major);  ta=1 -> stored (K,M), M contiguous (MN-major)
-  if (!ta) PMB_TRY(make_map(&mapA, A, K, M, lda, TBK, TBM)); else PMB_TRY(make_map(&mapA, A, M, K, lda, 32, TBK));
+  const CUtensorMapSwizzle kmaj = CU_TENSOR_MAP_SWIZZLE_128B, mnmaj = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+  if (!ta) PMB_TRY(make_map(&mapA, A, K, M, lda, TBK, TBM, kmaj)); else PMB_TRY(make_map(&mapA, A, M, K, lda, 32, TBK, mnmaj));
   // B: tb=1 -> stored (N,K), K contiguous (K-major);  tb=0 -> stored (K,N), N contiguous (MN-major)
-  if (tb) PMB_TRY(make_map(&mapB, B, K, N, ldb, TBK, TBN)); else PMB_TRY(make_map(&mapB, B, N, K, ldb, 32, TBK));
+  if (tb) PMB_TRY(make_map(&mapB, B, K, N, ldb, TBK, TBN, kmaj)); else PMB_TRY(make_map(&mapB, B, N, K, ldb, 32, TBK, mnmaj));
   Params p{};
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.a_mn_major = ta ? 1 : 0; p.b_mn_major = tb ? 0 : 1;
   p.C = C; p.ldc = ldc; p.R = R;
   dim3 grid((unsigned)cdiv(N, TBN), (unsigned)cdiv(M, TBM));
+  ProfScope prof(st, "gemm_3xtf32", 2.0 * M * N * K, 4.0 * ((double)M * K + (double)K * N + (double)M * N * (R ? 2 : 1)));
   gemm_3xtf32_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, p);
   PMB_LAUNCHED();
   return PMB_OK;

@@ -215,8 +215,9 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
     const float* hrows = hidden + r0 * D;
     // logits = hidden E^T   (photon/embedding.rs:54-60)
     PMB_TRY(gemm(st, 0, 1, rows, V, D, hrows, D, table, D, lm->logits, Vp, nullptr, 0));
+    { ProfScope prof(st, "cross_entropy", 0.0, 4.0 * rows * 3.0 * V);
     cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>(lm->logits, Vp, V, d_targets + r0, lm->row_loss + r0, 1.0f / (float)M);
-    PMB_LAUNCHED();
+    PMB_LAUNCHED(); }
     // dhidden = dlogits E ;  dE (+)= dlogits^T hidden
     PMB_TRY(gemm(st, 0, 0, rows, D, V, lm->logits, Vp, table, D, lm->dhidden + r0 * D, D, nullptr, 0));
     PMB_TRY(gemm(st, 1, 0, V, D, rows, lm->logits, Vp, hrows, D, dtable, D, r0 == 0 ? nullptr : dtable, 0));

@@ -464,6 +464,12 @@ static pmb_status fill_params(const SsdIn& in, const SsdWs& ws, SsdP* pp) {
 }
 
 template <class Op>
+static pmb_status run_op(cudaStream_t st, const char* name, const Op& op, int batches, double flops) {
+  ProfScope prof(st, name, flops, 0.0);
+  return launch_bgemm(st, op, batches);
+}
+
+template <class Op>
 static Op make_op(const SsdP& p, int Mdim, int Ndim) {
   Op op{};
   op.p = p; op.Mdim = Mdim; op.Ndim = Ndim;
@@ -476,14 +482,21 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
   PMB_TRY(fill_params(in, ws, &p));
   p.yout = y; p.ldyo = ldy;
   int nbch = p.B * p.nc * p.H, nbcg = p.B * p.nc * p.G;
-  chunk_cumsum_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p);
-  PMB_LAUNCHED();
-  PMB_TRY(launch_bgemm(st, make_op<OpCB>(p, p.Q, p.Q), nbcg));
-  PMB_TRY(launch_bgemm(st, make_op<OpState>(p, p.N, p.P), nbch));
+  const double tok = (double)p.B * p.T;
+  {
+    ProfScope prof(st, "ssd_chunk_cumsum", 0.0, 8.0 * tok * p.H);
+    chunk_cumsum_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p);
+    PMB_LAUNCHED();
+  }
+  PMB_TRY(run_op(st, "ssd_cb", make_op<OpCB>(p, p.Q, p.Q), nbcg, 2.0 * tok * p.Q * p.N * p.G));
+  PMB_TRY(run_op(st, "ssd_chunk_state", make_op<OpState>(p, p.N, p.P), nbch, 2.0 * tok * p.H * p.N * p.P));
   int64_t nel = (int64_t)p.B * p.H * p.N * p.P;
-  state_pass_kernel<<<(unsigned)cdiv(nel, 256), 256, 0, st>>>(p, init_state);
-  PMB_LAUNCHED();
-  PMB_TRY(launch_bgemm(st, make_op<OpScan>(p, p.Q, p.P), nbch));
+  {
+    ProfScope prof(st, "ssd_state_pass", 0.0, 8.0 * nel * p.nc);
+    state_pass_kernel<<<(unsigned)cdiv(nel, 256), 256, 0, st>>>(p, init_state);
+    PMB_LAUNCHED();
+  }
+  PMB_TRY(run_op(st, "ssd_chunk_scan", make_op<OpScan>(p, p.Q, p.P), nbch, 2.0 * tok * p.H * p.P * (p.Q + p.N)));
   if (final_state) PMB_CUDA(cudaMemcpyAsync(final_state, ws.hlast, (size_t)nel * sizeof(float), cudaMemcpyDeviceToDevice, st));
   return PMB_OK;
 }
@@ -496,21 +509,28 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   int nbch = p.B * p.nc * p.H, nbcg = p.B * p.nc * p.G;
   int64_t rows = (int64_t)p.B * p.T * p.H;
   float* ddt_x = ws.rows; float* dS = ws.rows + rows; float* dDrow = ws.rows + 2 * rows; float* dsend = ws.rows + 3 * rows;
-  PMB_TRY(launch_bgemm(st, make_op<OpDstate>(p, p.N, p.P), nbch));
-  state_pass_bwd_kernel<<<(unsigned)(p.B * p.H), SPB_THREADS, 0, st>>>(p, dsend);
-  PMB_LAUNCHED();
-  PMB_TRY(launch_bgemm(st, make_op<OpDx>(p, p.Q, p.P), nbch));
-  ssd_rowdots_kernel<<<(unsigned)cdiv(rows * 32, 256), 256, 0, st>>>(p, g.dx, g.lddx, ddt_x, dS, dDrow);
-  PMB_LAUNCHED();
-  ssd_chunk_finish_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p, ddt_x, dS, dDrow, dsend, g.da, g.ddt, ws.part);
-  PMB_LAUNCHED();
+  const double tok = (double)p.B * p.T;
+  PMB_TRY(run_op(st, "ssd_bwd_dstate", make_op<OpDstate>(p, p.N, p.P), nbch, 2.0 * tok * p.H * p.N * p.P));
+  {
+    ProfScope prof(st, "ssd_bwd_state_pass", 0.0, 12.0 * p.B * p.H * p.N * p.P * p.nc);
+    state_pass_bwd_kernel<<<(unsigned)(p.B * p.H), SPB_THREADS, 0, st>>>(p, dsend);
+    PMB_LAUNCHED();
+  }
+  PMB_TRY(run_op(st, "ssd_bwd_dx", make_op<OpDx>(p, p.Q, p.P), nbch, 2.0 * tok * p.H * p.P * (p.Q + p.N)));
+  {
+    ProfScope prof(st, "ssd_bwd_rows", 0.0, 4.0 * tok * p.H * (5.0 * p.P + 8.0));
+    ssd_rowdots_kernel<<<(unsigned)cdiv(rows * 32, 256), 256, 0, st>>>(p, g.dx, g.lddx, ddt_x, dS, dDrow);
+    PMB_LAUNCHED();
+    ssd_chunk_finish_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p, ddt_x, dS, dDrow, dsend, g.da, g.ddt, ws.part);
+    PMB_LAUNCHED();
+  }
   if (in.dt) {  // part = [dA partials (B*nc,H)] [dD partials (B*nc,H)]
     PMB_TRY(column_sum(st, ws.part, (int64_t)p.B * p.nc, p.H, g.dA));
     if (g.dD) PMB_TRY(column_sum(st, ws.part + (int64_t)p.B * p.nc * p.H, (int64_t)p.B * p.nc, p.H, g.dD));
   }
-  PMB_TRY(launch_bgemm(st, make_op<OpDG>(p, p.Q, p.Q), nbcg));
-  PMB_TRY(launch_bgemm(st, make_op<OpDC>(p, p.Q, p.N), nbcg));
-  PMB_TRY(launch_bgemm(st, make_op<OpDB>(p, p.Q, p.N), nbcg));
+  PMB_TRY(run_op(st, "ssd_bwd_dg", make_op<OpDG>(p, p.Q, p.Q), nbcg, 2.0 * tok * p.H * p.Q * p.P));
+  PMB_TRY(run_op(st, "ssd_bwd_dc", make_op<OpDC>(p, p.Q, p.N), nbcg, 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P)));
+  PMB_TRY(run_op(st, "ssd_bwd_db", make_op<OpDB>(p, p.Q, p.N), nbcg, 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P)));
   return PMB_OK;
 }
 

@@ -55,6 +55,8 @@ def _load():
         "pmb_version": (C.c_char_p, []),
         "pmb_launch_count": (i64, []),
         "pmb_device_status": (i32, [C.POINTER(i32)]),
+        "pmb_profile_start": (None, []),
+        "pmb_profile_stop": (i32, [C.c_char_p, sz]),
         "pmb_gemm_f32": (i32, [vp, i32, i32, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp, i32]),
         "pmb_conv_silu_dt_fwd": (i32, [vp, cfgp, i32, i32, vp, vp, vp, vp, vp, vp]),
         "pmb_conv_bwd_workspace_bytes": (sz, [cfgp, i32, i32]),
@@ -120,6 +122,18 @@ def device_status() -> int:
     w = C.c_int32(0)
     _check(lib.pmb_device_status(C.byref(w)))
     return w.value
+
+
+def profile_start():
+    lib.pmb_profile_start()
+
+
+def profile_stop() -> list:
+    """Per-kernel totals since profile_start(): list of dicts (name, launches, ms, flops, bytes)."""
+    import json
+    buf = C.create_string_buffer(1 << 16)
+    _check(lib.pmb_profile_stop(buf, len(buf)))
+    return json.loads(buf.value.decode())
 
 
 @dataclass

@@ -13,6 +13,18 @@ GOLD = pathlib.Path(__file__).resolve().parent / "golden"
 FP32_TOL = 1e-4
 
 
+# The gradients of the per-head scalars a_log and dt_bias are sums over every token of differences of
+# nearly equal O(1) terms (d/dS of the decay mask: row sums minus column sums).  Two correct fp32
+# evaluations with different summation orders differ by a few 1e-5..1e-4 there (the fp32 oracle itself is
+# 2e-5 from its fp64 run at production dims), and the reference's own cross-backend gradient tests hold
+# SSD gradients to 1e-3 (crates/pm-cuda/tests/grad_ssd.rs:62-227).  They are held to 5e-4 here.
+CANCELLATION_TOL = 5e-4
+
+
+def tol_for(name: str) -> float:
+    return CANCELLATION_TOL if name.endswith(("a_log", "dt_bias")) else FP32_TOL
+
+
 def rel_err(ours, ref) -> float:
     ours = ours.detach().double().cpu() if torch.is_tensor(ours) else torch.as_tensor(np.asarray(ours)).double()
     ref = ref.detach().double().cpu() if torch.is_tensor(ref) else torch.as_tensor(np.asarray(ref)).double()
