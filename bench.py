@@ -340,8 +340,81 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------------------
+# single-kernel micro workloads (for ncu captures and per-kernel roofline numbers)
+# --------------------------------------------------------------------------------------------------
+MICRO = {
+    # name: (kind, args)
+    "gemm_in_proj_fwd": ("gemm", dict(M=65536, N=3224, K=768, ta=0, tb=0)),
+    "gemm_in_proj_dgrad": ("gemm", dict(M=65536, N=768, K=3224, ta=0, tb=1)),
+    "gemm_in_proj_wgrad": ("gemm", dict(M=768, N=3224, K=65536, ta=1, tb=0)),
+    "gemm_out_proj_fwd": ("gemm", dict(M=65536, N=768, K=1536, ta=0, tb=0)),
+    "gemm_small_c2_in_proj": ("gemm", dict(M=2048, N=3224, K=768, ta=0, tb=0)),
+    "ssd_scan_fp32": ("ssd", dict(B=4, T=8192, H=32, P=64, N=128, G=1, Q=256)),
+    "decode_step_fp32": ("decode", dict(B=256, D=2048, H=32, P=64, N=128)),
+}
+
+
+def run_micro(args):
+    import __graft_entry__ as ge
+    ge.build()
+    import pm_b200
+    kind, a = MICRO[args.micro]
+    torch.cuda.set_device(0)
+    peaks = load_peaks()
+    g = torch.Generator(device="cuda"); g.manual_seed(1)
+    rnd = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    steps, warm = args.steps, max(args.warmup, 3)
+    if kind == "gemm":
+        M, N, K, ta, tb = a["M"], a["N"], a["K"], a["ta"], a["tb"]
+        A = rnd(K, M) if ta else rnd(M, K)
+        Bm = rnd(N, K) if tb else rnd(K, N)
+        out = torch.empty(M, N, device="cuda")
+        fn = lambda: pm_b200.matmul(A, Bm, trans_a=bool(ta), trans_b=bool(tb), out=out, engine=args.engine)
+        flops, nbytes = 2.0 * M * N * K, 4.0 * (M * K + K * N + M * N)
+    elif kind == "ssd":
+        B, T, H, P, N, G, Q = (a[k] for k in "BTHPNGQ")
+        x, dy = rnd(B, T, H, P), rnd(B, T, H, P)
+        av = -torch.nn.functional.softplus(rnd(B, T, H) * 0.5 - 2.0) * 4.0
+        bm, cm = rnd(B, T, G, N), rnd(B, T, G, N)
+        scan = pm_b200.SsdScan(x, av, bm, cm, Q)
+        fn = lambda: (scan.forward(), scan.backward(dy))
+        fwd = 2.0 * Q * N * G + H * (2.0 * Q * P + 4.0 * N * P)
+        bwd = H * (4.0 * Q * P + 8.0 * N * P) + 6.0 * Q * N * G
+        flops, nbytes = B * T * (fwd + bwd), 4.0 * B * T * (H * P * 5 + 2 * G * N * 2 + 2 * H)
+    else:
+        B, D, H, P, N = (a[k] for k in "BDHPN")
+        from oracle import mamba2_oracle as orc
+        ocfg = orc.Mamba2Config(d_model=D, d_state=N, d_head=P, n_heads=H, n_groups=1, block_len=256)
+        cfg = pm_b200.Mamba2Config(d_model=D, d_state=N, d_head=P, n_heads=H, n_groups=1, block_len=256)
+        blk = pm_b200.Mamba2Block(cfg, {k: v.cuda() for k, v in orc.init_block_params(ocfg, 1).items()})
+        st = blk.zero_state(B)
+        st["ssm_state"].normal_()
+        xt = rnd(B, 1, D)
+        fn = lambda: blk.step(xt, st)
+        flops, nbytes = 0.0, 8.0 * B * H * N * P
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    line = {"micro": args.micro, "args": a, "ms": ms, "steps": steps, "engine": args.engine,
+            "tflops": flops / (ms * 1e-3) / 1e12 if flops else None, "gbs": nbytes / (ms * 1e-3) / 1e9,
+            "frac_of_bf16_burst": (flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"]) if flops else None,
+            "frac_of_hbm": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "peaks": peaks["source"],
+            "device_status": pm_b200.device_status()}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--micro", default=None, choices=sorted(MICRO))
+    ap.add_argument("--engine", type=int, default=0)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -350,7 +423,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.micro:
+        run_micro(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
