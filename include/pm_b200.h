@@ -152,6 +152,21 @@ pmb_status pmb_gated_rmsnorm_bwd(void* stream, int64_t rows, int32_t width,
                                  float* d_dy, float* d_dz, int64_t lddz, float* d_dw,
                                  void* d_ws, size_t ws_bytes);
 
+/* Same backward for callers that cannot allocate device memory (no counterpart in the reference).
+ * Hosts that gave the whole GPU to their own pool at start-up, or that must keep out of the driver's
+ * allocator on a latency-critical path, have no workspace to pass.  This variant takes none: the
+ * weight-gradient partials go to a 4 MiB array built into the library image (held by every GPU that
+ * loads the library until exit), so ceil(rows/16) * width * 4 bytes must not exceed
+ * pmb_gated_rmsnorm_bwd_static_max_bytes(); larger problems get PMB_ERR_SHAPE.  It calls no cudaMalloc /
+ * cudaFree.  The first call on each device resolves the array's device address (make that call outside
+ * stream capture).  All calls share the array: calls that may overlap on the GPU race and must be
+ * ordered by the caller.  Results equal pmb_gated_rmsnorm_bwd's. */
+size_t pmb_gated_rmsnorm_bwd_static_max_bytes(void);
+pmb_status pmb_gated_rmsnorm_bwd_static(void* stream, int64_t rows, int32_t width,
+                                        const float* d_dout, const float* d_y, const float* d_z, int64_t ldz,
+                                        const float* d_w, const float* d_rstd,
+                                        float* d_dy, float* d_dz, int64_t lddz, float* d_dw);
+
 /* ---- one Mamba2 block (block.rs:118-226) and its backward with in-call recompute.
  * fwd: out (B,T,D) = Block(x); if d_residual != NULL, out = residual + Block(x) (the caller's
  * `h + Block(h)`, photon/encoder.rs:54-59; d_residual may equal d_x).  Nothing is kept for backward.

@@ -340,6 +340,52 @@ pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const flo
   return PMB_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Gated RMSNorm backward for callers that cannot allocate device memory.
+//
+// Some hosts may not call cudaMalloc at the point where they need this kernel: a trainer that handed the
+// whole device to its own pool at start-up and has nothing left to carve a workspace from, or a
+// latency-bound serving loop that must stay out of the driver's allocator.  For them the per-row-block
+// weight-gradient partials live in the array below, which is part of the library image: every GPU that
+// loads the library holds these 4 MiB until the process exits.
+//
+// In host code `g_static_scratch` names a host-side shadow of the symbol, not device memory; the device
+// address is looked up once per device with cudaGetSymbolAddress (with that device current) and cached.
+// That lookup happens on the first call on a device, so make that first call outside any stream capture.
+// Nothing has to be zeroed between calls: each call overwrites the rows of the array it later reads.
+// All calls share the one array, so two calls whose kernels may overlap on the GPU (different streams
+// without an ordering between them) race on it; serialise them.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t STATIC_SCRATCH_BYTES = 4u << 20;
+static __device__ __align__(256) float g_static_scratch[STATIC_SCRATCH_BYTES / sizeof(float)];
+constexpr int STATIC_SCRATCH_MAX_DEVICES = 64;
+static float* g_static_scratch_addr[STATIC_SCRATCH_MAX_DEVICES] = {nullptr};
+
+static pmb_status static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  PMB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= STATIC_SCRATCH_MAX_DEVICES) return fail(PMB_ERR_UNSUPPORTED, "device ordinal %d is outside 0..%d", dev, STATIC_SCRATCH_MAX_DEVICES - 1);
+  if (!g_static_scratch_addr[dev]) {
+    void* p = nullptr;
+    PMB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    g_static_scratch_addr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_scratch_addr[dev];
+  return PMB_OK;
+}
+
+pmb_status gated_rmsnorm_bwd_static(cudaStream_t st, int64_t rows, int width, const float* dout, const float* y, const float* z,
+                                    int64_t ldz, const float* w, const float* rstd, float* dy, float* dz, int64_t lddz, float* dw) {
+  size_t need = gated_rmsnorm_bwd_ws_bytes(rows, width);
+  if (need > STATIC_SCRATCH_BYTES)
+    return fail(PMB_ERR_SHAPE, "gated_rmsnorm_bwd_static: rows=%lld x width=%d needs %zu bytes of scratch, the built-in array holds %zu "
+                "(ceil(rows/%d) * width * 4 must not exceed it); use pmb_gated_rmsnorm_bwd with a caller workspace",
+                (long long)rows, width, need, STATIC_SCRATCH_BYTES, NORM_ROWS);
+  float* scratch = nullptr;
+  PMB_TRY(static_scratch_for_current_device(&scratch));
+  return gated_rmsnorm_bwd(st, rows, width, dout, y, z, ldz, w, rstd, dy, dz, lddz, dw, scratch, STATIC_SCRATCH_BYTES);
+}
+
 pmb_status column_sum(cudaStream_t st, const float* partial, int64_t rows, int cols, float* out) {
   column_sum_kernel<<<(unsigned)cdiv(cols, 256), 256, 0, st>>>(partial, rows, cols, out);
   PMB_LAUNCHED();
@@ -347,3 +393,15 @@ pmb_status column_sum(cudaStream_t st, const float* partial, int64_t rows, int c
 }
 
 }  // namespace pmb
+
+extern "C" size_t pmb_gated_rmsnorm_bwd_static_max_bytes(void) { return pmb::STATIC_SCRATCH_BYTES; }
+
+extern "C" pmb_status pmb_gated_rmsnorm_bwd_static(void* stream, int64_t rows, int32_t width,
+                                                   const float* d_dout, const float* d_y, const float* d_z, int64_t ldz,
+                                                   const float* d_w, const float* d_rstd,
+                                                   float* d_dy, float* d_dz, int64_t lddz, float* d_dw) {
+  using namespace pmb;
+  if (rows <= 0 || width <= 0 || ldz < width || lddz < width) return fail(PMB_ERR_SHAPE, "gated_rmsnorm_bwd_static: bad shape");
+  if (!d_dout || !d_y || !d_z || !d_w || !d_rstd || !d_dy || !d_dz || !d_dw) return fail(PMB_ERR_ARG, "gated_rmsnorm_bwd_static: NULL argument");
+  return gated_rmsnorm_bwd_static(static_cast<cudaStream_t>(stream), rows, width, d_dout, d_y, d_z, ldz, d_w, d_rstd, d_dy, d_dz, lddz, d_dw);
+}

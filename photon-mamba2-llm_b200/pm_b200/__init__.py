@@ -67,6 +67,8 @@ def _load():
         "pmb_gated_rmsnorm_fwd": (i32, [vp, i64, i32, f32, vp, vp, i64, vp, vp, vp]),
         "pmb_gated_rmsnorm_bwd_workspace_bytes": (sz, [i64, i32]),
         "pmb_gated_rmsnorm_bwd": (i32, [vp, i64, i32, vp, vp, vp, i64, vp, vp, vp, vp, i64, vp, vp, sz]),
+        "pmb_gated_rmsnorm_bwd_static_max_bytes": (sz, []),
+        "pmb_gated_rmsnorm_bwd_static": (i32, [vp, i64, i32, vp, vp, vp, i64, vp, vp, vp, vp, i64, vp]),
         "pmb_mamba2_block_workspace_bytes": (sz, [cfgp, i32, i32]),
         "pmb_mamba2_block_fwd": (i32, [vp, cfgp, C.POINTER(_Params), i32, i32, vp, vp, vp, vp, sz]),
         "pmb_mamba2_block_bwd": (i32, [vp, cfgp, C.POINTER(_Params), i32, i32, vp, vp, vp, vp, C.POINTER(_Params), vp, sz]),
@@ -270,6 +272,19 @@ def gated_rmsnorm_bwd(dout, y, z, w, rstd):
     _check(lib.pmb_gated_rmsnorm_bwd(_stream(), rows, width, _dev(dout, "dout").data_ptr(), y.data_ptr(), z.data_ptr(),
                                      z.stride(0), w.data_ptr(), rstd.data_ptr(), dy.data_ptr(), dz.data_ptr(), width,
                                      dw.data_ptr(), ws.data_ptr(), n))
+    return dy, dz, dw
+
+
+def gated_rmsnorm_bwd_static(dout, y, z, w, rstd):
+    """Gated RMSNorm backward without any device allocation by the library: for hosts that cannot
+    call cudaMalloc where they need it (all memory already in their own pool, or an allocator-free
+    hot loop).  The scratch is a fixed 4 MiB array inside the library, so ceil(rows/16)*width*4 bytes
+    must fit; calls share it and must not overlap on the GPU.  Output buffers are the caller's."""
+    rows, width = y.shape
+    dy, dz, dw = torch.empty_like(y), torch.empty(rows, width, device=y.device, dtype=torch.float32), torch.empty_like(w)
+    _check(lib.pmb_gated_rmsnorm_bwd_static(_stream(), rows, width, _dev(dout, "dout").data_ptr(), y.data_ptr(), z.data_ptr(),
+                                            z.stride(0), w.data_ptr(), rstd.data_ptr(), dy.data_ptr(), dz.data_ptr(), width,
+                                            dw.data_ptr()))
     return dy, dz, dw
 
 
