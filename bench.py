@@ -200,29 +200,18 @@ def run_ours(args):
     lm.load(embed.cuda(), [{k: v.cuda() for k, v in p.items()} for p in layers])
     del embed, layers
 
-    # data-parallel gradient all-reduce: one bucket per layer, enqueued on a side stream from the library's
-    # per-layer callback so it overlaps the remaining recompute/backward; the embedding bucket goes last.
-    comm = torch.cuda.Stream() if world > 1 else None
-    pending = []
-    bounds = [pm_b200.lib.pmb_lm_param_offset(lm._h, l, 0) for l in range(L)] + [pm_b200.lib.pmb_lm_param_count(lm._h)]
-    emb_n = V * D
-
-    def on_layer_done(layer, _user):
-        if world == 1:
-            return
-        ev = torch.cuda.Event()
-        ev.record(torch.cuda.current_stream())
-        comm.wait_event(ev)
-        bucket = lm.flat_grads[:emb_n] if layer < 0 else lm.flat_grads[bounds[layer]:bounds[layer + 1]]
-        with torch.cuda.stream(comm):
-            pending.append(dist.all_reduce(bucket, op=dist.ReduceOp.AVG, async_op=True))
+    # data-parallel gradient averaging: one bucket per layer, enqueued on a side stream from the library's
+    # per-layer host callback (pm_b200/dp.py) so it overlaps the remaining recompute/backward.
+    reducer = None
+    if world > 1:
+        from pm_b200.dp import GradAllReducer
+        offsets = [pm_b200.lib.pmb_lm_param_offset(lm._h, l, 0) for l in range(L)]
+        reducer = GradAllReducer(lm.flat_grads, offsets)
+    on_layer_done = reducer.on_layer_done if reducer else None
 
     def finish_comm():
-        for h in pending:
-            h.wait()
-        pending.clear()
-        if comm is not None:
-            torch.cuda.current_stream().wait_stream(comm)
+        if reducer:
+            reducer.finish()
 
     n_tok = 8
     host_batches = [make_tokens(w, rank, s, pin=True) for s in range(n_tok)]
@@ -230,12 +219,12 @@ def run_ours(args):
 
     def step_device(s):
         ids, tg = dev_batches[s % n_tok]
-        lm.step_device(ids, tg, on_layer_done if world > 1 else None)
+        lm.step_device(ids, tg, on_layer_done)
         finish_comm()
 
     def step_host(s):
         ids, tg = host_batches[s % n_tok]
-        loss = lm.step_host(ids, tg, on_layer_done if world > 1 else None)
+        loss = lm.step_host(ids, tg, on_layer_done)
         finish_comm()
         return loss
 

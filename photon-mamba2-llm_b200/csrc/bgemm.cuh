@@ -13,6 +13,7 @@ constexpr int BM = 64, BN = 64, BK = 16, NTHR = 256;
 //   bool a_kcontig(int seg), b_kcontig(int seg)   memory contiguity of the operands (for coalescing)
 //   float a(int seg, int m, int k), b(int seg, int k, int n)   (called only in range)
 //   float seg_scale(int seg, int m, int n)   (only when Op::SEG_SCALE)
+//   bool seg_active(int seg)                 (false = segment belongs to another split of the same tile)
 //   void store(int m, int n, float v)
 // ---------------------------------------------------------------------------------------------
 template <class Op>
@@ -29,6 +30,7 @@ __global__ void __launch_bounds__(NTHR) bgemm_kernel(Op op) {
     for (int j = 0; j < 4; ++j) total[i][j] = 0.0f;
   const int nseg = op.nseg();
   for (int seg = 0; seg < nseg; ++seg) {
+    if (!op.seg_active(seg)) continue;  // split-K: this CTA owns a subset of the segments
     float acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)

@@ -18,6 +18,7 @@ struct OpGemm {
   __device__ float a(int, int m, int k) const { return ta ? A[(int64_t)k * lda + m] : A[(int64_t)m * lda + k]; }
   __device__ float b(int, int k, int n) const { return tb ? B[(int64_t)n * ldb + k] : B[(int64_t)k * ldb + n]; }
   __device__ float seg_scale(int, int, int) const { return 1.0f; }
+  __device__ bool seg_active(int) const { return true; }
   __device__ void store(int m, int n, float v) const {
     int64_t i = (int64_t)m * ldc + n;
     C[i] = R ? v + R[i] : v;

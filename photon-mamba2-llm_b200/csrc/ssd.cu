@@ -58,6 +58,7 @@ struct OpCB {
   __device__ float a(int, int m, int k) const { return cp[(int64_t)m * p.ldbc + k]; }
   __device__ float b(int, int k, int n) const { return bp[(int64_t)n * p.ldbc + k]; }
   __device__ float seg_scale(int, int, int) const { return 1.0f; }
+  __device__ bool seg_active(int) const { return true; }
   __device__ void store(int m, int n, float v) const { out[(int64_t)m * p.Q + n] = v; }
 };
 
@@ -92,6 +93,7 @@ struct OpState {
   }
   __device__ float b(int, int k, int n) const { return p.x[(cx.t0 + k) * p.ldx + cx.h * p.P + n]; }
   __device__ float seg_scale(int, int, int) const { return 1.0f; }
+  __device__ bool seg_active(int) const { return true; }
   __device__ void store(int m, int n, float v) const { out[(int64_t)m * p.P + n] = v; }
 };
 
@@ -125,6 +127,7 @@ struct OpScan {
     return hp[(int64_t)k * p.P + n];
   }
   __device__ float seg_scale(int, int, int) const { return 1.0f; }
+  __device__ bool seg_active(int) const { return true; }
   __device__ void store(int m, int n, float v) const {
     if (p.D) v = fmaf(p.D[cx.h], p.x[(cx.t0 + m) * p.ldx + cx.h * p.P + n], v);
     p.yout[(cx.t0 + m) * p.ldyo + cx.h * p.P + n] = v;
@@ -149,6 +152,7 @@ struct OpDstate {
   __device__ float a(int, int m, int k) const { return p.c[(cx.t0 + k) * p.ldbc + cx.g * p.N + m] * expf(sp[k]); }
   __device__ float b(int, int k, int n) const { return p.dy[(cx.t0 + k) * p.lddy + cx.h * p.P + n]; }
   __device__ float seg_scale(int, int, int) const { return 1.0f; }
+  __device__ bool seg_active(int) const { return true; }
   __device__ void store(int m, int n, float v) const { out[(int64_t)m * p.P + n] = v; }
 };
 
@@ -183,6 +187,7 @@ struct OpDx {
     return dhp[(int64_t)k * p.P + n];
   }
   __device__ float seg_scale(int, int, int) const { return 1.0f; }
+  __device__ bool seg_active(int) const { return true; }
   __device__ void store(int m, int n, float v) const { p.dxt[(cx.t0 + m) * (int64_t)(p.H * p.P) + cx.h * p.P + n] = v; }
 };
 
@@ -190,14 +195,17 @@ struct OpDx {
 struct OpDG {
   static constexpr bool SEG_SCALE = true;
   SsdP p; int Mdim, Ndim;
-  int bb, cc, g; int64_t t0; float* out;
+  int nsplit; float* part;      // split-K over heads: partial tiles go to `part`, summed by splitk_reduce_kernel
+  int bb, cc, g, split; int64_t t0; float* out;
   __device__ bool init(int batch, int m0, int n0) {
     if (n0 > m0 + BM - 1) return false;
+    split = batch % nsplit; batch /= nsplit;
     g = batch % p.G; int bc = batch / p.G; cc = bc % p.nc; bb = bc / p.nc;
     t0 = p.tok(bb, cc, 0);
-    out = p.dG + (int64_t)batch * p.Q * p.Q;
+    out = nsplit > 1 ? part + (int64_t)blockIdx.z * p.Q * p.Q : p.dG + (int64_t)batch * p.Q * p.Q;
     return true;
   }
+  __device__ bool seg_active(int seg) const { return seg % nsplit == split; }
   __device__ int nseg() const { return p.hpg; }
   __device__ void krange(int, int, int, int& k0, int& k1) const { k0 = 0; k1 = p.P; }
   __device__ bool a_kcontig(int) const { return true; }
@@ -220,13 +228,17 @@ struct OpDG {
 struct OpDC {
   static constexpr bool SEG_SCALE = false;
   SsdP p; int Mdim, Ndim;
-  int bb, cc, g; int64_t t0; const float* dg;
+  int nsplit; float* part;
+  int bb, cc, g, split; int64_t t0; const float* dg; float* pout;
   __device__ bool init(int batch, int, int) {
+    split = batch % nsplit; batch /= nsplit;
     g = batch % p.G; int bc = batch / p.G; cc = bc % p.nc; bb = bc / p.nc;
     t0 = p.tok(bb, cc, 0);
     dg = p.dG + (int64_t)batch * p.Q * p.Q;
+    pout = part + (int64_t)blockIdx.z * Mdim * Ndim;
     return true;
   }
+  __device__ bool seg_active(int seg) const { return seg == 0 ? split == 0 : (seg - 1) % nsplit == split; }
   __device__ int nseg() const { return 1 + p.hpg; }
   __device__ void krange(int seg, int m0, int, int& k0, int& k1) const {
     k0 = 0; k1 = seg == 0 ? min(p.Q, m0 + BM) : p.P;
@@ -244,20 +256,26 @@ struct OpDC {
     return p.hprev[((((int64_t)bb * p.nc + cc) * p.H + h) * p.N + n) * p.P + k];
   }
   __device__ float seg_scale(int, int, int) const { return 1.0f; }
-  __device__ void store(int m, int n, float v) const { p.dc[(t0 + m) * p.lddbc + g * p.N + n] = v; }
+  __device__ void store(int m, int n, float v) const {
+    if (nsplit > 1) pout[(int64_t)m * Ndim + n] = v; else p.dc[(t0 + m) * p.lddbc + g * p.N + n] = v;
+  }
 };
 
 // ---- B6b: dB[s,n] = sum_{t>=s} dG[t,s] C[t,n] + sum_h exp(S_end - S_s) sum_p x~_h[s,p] dh_h[n,p] --
 struct OpDB {
   static constexpr bool SEG_SCALE = false;
   SsdP p; int Mdim, Ndim;
-  int bb, cc, g; int64_t t0; const float* dg;
+  int nsplit; float* part;
+  int bb, cc, g, split; int64_t t0; const float* dg; float* pout;
   __device__ bool init(int batch, int, int) {
+    split = batch % nsplit; batch /= nsplit;
     g = batch % p.G; int bc = batch / p.G; cc = bc % p.nc; bb = bc / p.nc;
     t0 = p.tok(bb, cc, 0);
     dg = p.dG + (int64_t)batch * p.Q * p.Q;
+    pout = part + (int64_t)blockIdx.z * Mdim * Ndim;
     return true;
   }
+  __device__ bool seg_active(int seg) const { return seg == 0 ? split == 0 : (seg - 1) % nsplit == split; }
   __device__ int nseg() const { return 1 + p.hpg; }
   __device__ void krange(int seg, int m0, int, int& k0, int& k1) const {
     if (seg == 0) { k0 = m0; k1 = p.Q; } else { k0 = 0; k1 = p.P; }
@@ -276,7 +294,9 @@ struct OpDB {
     return p.dh[((((int64_t)bb * p.nc + cc) * p.H + h) * p.N + n) * p.P + k];
   }
   __device__ float seg_scale(int, int, int) const { return 1.0f; }
-  __device__ void store(int m, int n, float v) const { p.db[(t0 + m) * p.lddbc + g * p.N + n] = v; }
+  __device__ void store(int m, int n, float v) const {
+    if (nsplit > 1) pout[(int64_t)m * Ndim + n] = v; else p.db[(t0 + m) * p.lddbc + g * p.N + n] = v;
+  }
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -430,6 +450,31 @@ __global__ void ssd_chunk_finish_kernel(SsdP p, const float* __restrict__ ddt_x,
   }
 }
 
+// Sums the split-K partial tiles in a fixed order.  mode 0: dG (lower-triangular 64x64 tiles only, the
+// others were never produced); mode 1/2: dC/dB rows go to out + token * ld + g * cols.
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, int nsplit, int rows, int cols, int mode, int G, int Q,
+                                     float* __restrict__ out, int64_t ld, int64_t total) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  int64_t mn = (int64_t)rows * cols;
+  int64_t batch = i / mn; int64_t r = i % mn; int m = (int)(r / cols), n = (int)(r % cols);
+  if (mode == 0 && n / BN > m / BM) return;
+  float s = 0.0f;
+  for (int k = 0; k < nsplit; ++k) s += part[(batch * nsplit + k) * mn + r];
+  if (mode == 0) {
+    out[batch * mn + r] = s;
+  } else {
+    int g = (int)(batch % G); int64_t bc = batch / G;
+    out[(bc * Q + m) * ld + g * cols + n] = s;
+  }
+}
+
+static int pick_nsplit(int batches, int tiles, int hpg) {
+  int want = (int)cdiv(2 * 148, (int64_t)batches * tiles);
+  if (want < 1) want = 1;
+  return want > hpg ? hpg : want;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
@@ -446,6 +491,12 @@ size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base
   w.dxt = ar.take<float>((size_t)B * T * H * P);
   w.rows = ar.take<float>((size_t)4 * B * T * H);
   w.part = ar.take<float>((size_t)B * nc * 2 * H);
+  {
+    int nbcg = B * nc * G, hpg = H / G, qt = (int)cdiv(Q, BM);
+    size_t a = (size_t)pick_nsplit(nbcg, qt * (qt + 1) / 2, hpg) * nbcg * Q * Q;
+    size_t b = (size_t)pick_nsplit(nbcg, qt * (int)cdiv(N, BN), hpg) * nbcg * Q * N;
+    w.splitk = ar.take<float>(a > b ? a : b);
+  }
   if (out) *out = w;
   return ar.ok ? ar.used() : 0;
 }
@@ -528,9 +579,37 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
     PMB_TRY(column_sum(st, ws.part, (int64_t)p.B * p.nc, p.H, g.dA));
     if (g.dD) PMB_TRY(column_sum(st, ws.part + (int64_t)p.B * p.nc * p.H, (int64_t)p.B * p.nc, p.H, g.dD));
   }
-  PMB_TRY(run_op(st, "ssd_bwd_dg", make_op<OpDG>(p, p.Q, p.Q), nbcg, 2.0 * tok * p.H * p.Q * p.P));
-  PMB_TRY(run_op(st, "ssd_bwd_dc", make_op<OpDC>(p, p.Q, p.N), nbcg, 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P)));
-  PMB_TRY(run_op(st, "ssd_bwd_db", make_op<OpDB>(p, p.Q, p.N), nbcg, 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P)));
+  // The three per-group contractions sum over the heads of the group; with few (batch, chunk) pairs the
+  // head loop is split across CTAs and the partial tiles are summed in a fixed order afterwards.
+  const int qt = (int)cdiv(p.Q, BM);
+  auto reduce = [&](int nsplit, int cols, int mode, float* out, int64_t ld) -> pmb_status {
+    if (nsplit <= 1) return PMB_OK;
+    int64_t total = (int64_t)nbcg * p.Q * cols;
+    splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(ws.splitk, nsplit, p.Q, cols, mode, p.G, p.Q, out, ld, total);
+    PMB_LAUNCHED();
+    return PMB_OK;
+  };
+  {
+    OpDG op = make_op<OpDG>(p, p.Q, p.Q);
+    op.nsplit = pick_nsplit(nbcg, qt * (qt + 1) / 2, p.hpg); op.part = ws.splitk;
+    ProfScope prof(st, "ssd_bwd_dg", 2.0 * tok * p.H * p.Q * p.P, 0.0);
+    PMB_TRY(launch_bgemm(st, op, nbcg * op.nsplit));
+    PMB_TRY(reduce(op.nsplit, p.Q, 0, ws.dG, 0));
+  }
+  {
+    OpDC op = make_op<OpDC>(p, p.Q, p.N);
+    op.nsplit = pick_nsplit(nbcg, qt * (int)cdiv(p.N, BN), p.hpg); op.part = ws.splitk;
+    ProfScope prof(st, "ssd_bwd_dc", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
+    PMB_TRY(launch_bgemm(st, op, nbcg * op.nsplit));
+    PMB_TRY(reduce(op.nsplit, p.N, 1, g.dc, g.lddbc));
+  }
+  {
+    OpDB op = make_op<OpDB>(p, p.Q, p.N);
+    op.nsplit = pick_nsplit(nbcg, qt * (int)cdiv(p.N, BN), p.hpg); op.part = ws.splitk;
+    ProfScope prof(st, "ssd_bwd_db", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
+    PMB_TRY(launch_bgemm(st, op, nbcg * op.nsplit));
+    PMB_TRY(reduce(op.nsplit, p.N, 2, g.db, g.lddbc));
+  }
   return PMB_OK;
 }
 
