@@ -2,6 +2,7 @@
 #include "common.cuh"
 #include <cstdlib>
 #include "kernels.h"
+#include "ssd_tc.h"
 
 namespace pmb {
 
@@ -65,8 +66,10 @@ extern "C" pmb_status pmb_profile_stop(char* h_json, size_t capacity) {
 }
 
 extern "C" pmb_status pmb_device_status(int32_t* h_word_out) {
-  unsigned int w = 0;
+  unsigned int w = 0, w2 = 0;
   PMB_TRY(read_clear_device_status(&w));
+  PMB_TRY(read_clear_device_status_ssd(&w2));
+  w |= w2 << 8;
   if (h_word_out) *h_word_out = (int32_t)w;
   return PMB_OK;
 }

@@ -42,6 +42,8 @@ struct SsdWs {            // persistent between fwd and bwd of one scan
   float* rows;            // 4 x (B,T,H): ddt_x, dS, dDrow, dSend(padded)
   float* part;            // (B*nc, 2H) partial sums
   float* splitk;          // split-K partial tiles of the per-group backward contractions
+  float* xs;              // (B,T,H,P) x * dt * exp(S_end - S_t)   (tensor-core path only)
+  float* dys;             // (B,T,H,P) dY * exp(S_t)               (tensor-core path only)
 };
 size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base, size_t bytes, SsdWs* out);
 pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, float* y, int64_t ldy,

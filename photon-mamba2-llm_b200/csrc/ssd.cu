@@ -18,6 +18,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "bgemm.cuh"
+#include "ssd_tc.h"
 
 namespace pmb {
 
@@ -453,12 +454,12 @@ __global__ void ssd_chunk_finish_kernel(SsdP p, const float* __restrict__ ddt_x,
 // Sums the split-K partial tiles in a fixed order.  mode 0: dG (lower-triangular 64x64 tiles only, the
 // others were never produced); mode 1/2: dC/dB rows go to out + token * ld + g * cols.
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, int nsplit, int rows, int cols, int mode, int G, int Q,
-                                     float* __restrict__ out, int64_t ld, int64_t total) {
+                                     float* __restrict__ out, int64_t ld, int64_t total, int tile) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   int64_t mn = (int64_t)rows * cols;
   int64_t batch = i / mn; int64_t r = i % mn; int m = (int)(r / cols), n = (int)(r % cols);
-  if (mode == 0 && n / BN > m / BM) return;
+  if (mode == 0 && n / tile > m / tile) return;   // tiles above the diagonal were never produced
   float s = 0.0f;
   for (int k = 0; k < nsplit; ++k) s += part[(batch * nsplit + k) * mn + r];
   if (mode == 0) {
@@ -468,6 +469,9 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, int nsplit,
     out[(bc * Q + m) * ld + g * cols + n] = s;
   }
 }
+
+// above this many floats of per-head partials the per-group contractions stay on the FMA engine
+constexpr size_t TC_DG_PARTIAL_CAP = (size_t)1 << 28;
 
 static int pick_nsplit(int batches, int tiles, int hpg) {
   int want = (int)cdiv(2 * 148, (int64_t)batches * tiles);
@@ -495,7 +499,18 @@ size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base
     int nbcg = B * nc * G, hpg = H / G, qt = (int)cdiv(Q, BM);
     size_t a = (size_t)pick_nsplit(nbcg, qt * (qt + 1) / 2, hpg) * nbcg * Q * Q;
     size_t b = (size_t)pick_nsplit(nbcg, qt * (int)cdiv(N, BN), hpg) * nbcg * Q * N;
-    w.splitk = ar.take<float>(a > b ? a : b);
+    size_t need = a > b ? a : b;
+    // the tensor-core path keeps one masked (Q,Q) product per head before the per-group sum
+    size_t tcp = (size_t)B * nc * H * Q * Q;
+    if (Q % 64 == 0 && N % 32 == 0 && P % 64 == 0 && tcp <= TC_DG_PARTIAL_CAP) {
+      if (tcp > need) need = tcp;
+      size_t dbc = (size_t)hpg * nbcg * Q * N;   // upper bound of the head-split dB / dC partial tiles
+      if (dbc > need) need = dbc;
+    }
+    w.splitk = ar.take<float>(need);
+    bool tcshape = Q % 64 == 0 && N % 32 == 0 && P % 64 == 0;
+    w.xs = ar.take<float>(tcshape ? (size_t)B * T * H * P : 0);
+    w.dys = ar.take<float>(tcshape ? (size_t)B * T * H * P : 0);
   }
   if (out) *out = w;
   return ar.ok ? ar.used() : 0;
@@ -539,15 +554,22 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
     chunk_cumsum_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p);
     PMB_LAUNCHED();
   }
-  PMB_TRY(run_op(st, "ssd_cb", make_op<OpCB>(p, p.Q, p.Q), nbcg, 2.0 * tok * p.Q * p.N * p.G));
-  PMB_TRY(run_op(st, "ssd_chunk_state", make_op<OpState>(p, p.N, p.P), nbch, 2.0 * tok * p.H * p.N * p.P));
+  const bool tc = ssd_tc_supported(in) && (ldy % 4 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0);
+  if (tc) {
+    PMB_TRY(ssd_tc_cb(st, in, ws));
+    PMB_TRY(ssd_tc_state(st, in, ws));
+  } else {
+    PMB_TRY(run_op(st, "ssd_cb", make_op<OpCB>(p, p.Q, p.Q), nbcg, 2.0 * tok * p.Q * p.N * p.G));
+    PMB_TRY(run_op(st, "ssd_chunk_state", make_op<OpState>(p, p.N, p.P), nbch, 2.0 * tok * p.H * p.N * p.P));
+  }
   int64_t nel = (int64_t)p.B * p.H * p.N * p.P;
   {
     ProfScope prof(st, "ssd_state_pass", 0.0, 8.0 * nel * p.nc);
     state_pass_kernel<<<(unsigned)cdiv(nel, 256), 256, 0, st>>>(p, init_state);
     PMB_LAUNCHED();
   }
-  PMB_TRY(run_op(st, "ssd_chunk_scan", make_op<OpScan>(p, p.Q, p.P), nbch, 2.0 * tok * p.H * p.P * (p.Q + p.N)));
+  if (tc) PMB_TRY(ssd_tc_scan(st, in, y, ldy, ws));
+  else PMB_TRY(run_op(st, "ssd_chunk_scan", make_op<OpScan>(p, p.Q, p.P), nbch, 2.0 * tok * p.H * p.P * (p.Q + p.N)));
   if (final_state) PMB_CUDA(cudaMemcpyAsync(final_state, ws.hlast, (size_t)nel * sizeof(float), cudaMemcpyDeviceToDevice, st));
   return PMB_OK;
 }
@@ -561,13 +583,18 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   int64_t rows = (int64_t)p.B * p.T * p.H;
   float* ddt_x = ws.rows; float* dS = ws.rows + rows; float* dDrow = ws.rows + 2 * rows; float* dsend = ws.rows + 3 * rows;
   const double tok = (double)p.B * p.T;
-  PMB_TRY(run_op(st, "ssd_bwd_dstate", make_op<OpDstate>(p, p.N, p.P), nbch, 2.0 * tok * p.H * p.N * p.P));
+  const bool tc = ssd_tc_supported(in) && (lddy % 4 == 0) && (reinterpret_cast<uintptr_t>(dy) % 16 == 0) && (g.lddbc % 4 == 0) &&
+                  ((reinterpret_cast<uintptr_t>(g.db) | reinterpret_cast<uintptr_t>(g.dc)) % 16 == 0);
+  const bool tc_group = tc && ssd_tc_dg_partial_floats(in) <= TC_DG_PARTIAL_CAP;
+  if (tc) PMB_TRY(ssd_tc_dstate(st, in, dy, lddy, ws));
+  else PMB_TRY(run_op(st, "ssd_bwd_dstate", make_op<OpDstate>(p, p.N, p.P), nbch, 2.0 * tok * p.H * p.N * p.P));
   {
     ProfScope prof(st, "ssd_bwd_state_pass", 0.0, 12.0 * p.B * p.H * p.N * p.P * p.nc);
     state_pass_bwd_kernel<<<(unsigned)(p.B * p.H), SPB_THREADS, 0, st>>>(p, dsend);
     PMB_LAUNCHED();
   }
-  PMB_TRY(run_op(st, "ssd_bwd_dx", make_op<OpDx>(p, p.Q, p.P), nbch, 2.0 * tok * p.H * p.P * (p.Q + p.N)));
+  if (tc) PMB_TRY(ssd_tc_dx(st, in, dy, lddy, ws));
+  else PMB_TRY(run_op(st, "ssd_bwd_dx", make_op<OpDx>(p, p.Q, p.P), nbch, 2.0 * tok * p.H * p.P * (p.Q + p.N)));
   {
     ProfScope prof(st, "ssd_bwd_rows", 0.0, 4.0 * tok * p.H * (5.0 * p.P + 8.0));
     ssd_rowdots_kernel<<<(unsigned)cdiv(rows * 32, 256), 256, 0, st>>>(p, g.dx, g.lddx, ddt_x, dS, dDrow);
@@ -582,13 +609,33 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   // The three per-group contractions sum over the heads of the group; with few (batch, chunk) pairs the
   // head loop is split across CTAs and the partial tiles are summed in a fixed order afterwards.
   const int qt = (int)cdiv(p.Q, BM);
-  auto reduce = [&](int nsplit, int cols, int mode, float* out, int64_t ld) -> pmb_status {
+  auto reduce = [&](int nsplit, int cols, int mode, float* out, int64_t ld, int tile = BM) -> pmb_status {
     if (nsplit <= 1) return PMB_OK;
     int64_t total = (int64_t)nbcg * p.Q * cols;
-    splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(ws.splitk, nsplit, p.Q, cols, mode, p.G, p.Q, out, ld, total);
+    splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(ws.splitk, nsplit, p.Q, cols, mode, p.G, p.Q, out, ld, total, tile);
     PMB_LAUNCHED();
     return PMB_OK;
   };
+  if (tc_group) {
+    {
+      ProfScope prof(st, "ssd_bwd_dg_tc", 2.0 * tok * p.H * p.Q * p.P, 0.0);
+      PMB_TRY(ssd_tc_dg_partials(st, in, dy, lddy, ws));
+      PMB_TRY(reduce(p.hpg, p.Q, 0, ws.dG, 0, 128));
+      if (p.hpg == 1) PMB_CUDA(cudaMemcpyAsync(ws.dG, ws.splitk, (size_t)nbcg * p.Q * p.Q * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    }
+    const int ns = ssd_tc_dbc_nsplit(in);
+    {
+      ProfScope prof(st, "ssd_bwd_dc_tc", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
+      PMB_TRY(ssd_tc_dc(st, in, g.dc, g.lddbc, ws, ns));
+      PMB_TRY(reduce(ns, p.N, 1, g.dc, g.lddbc));
+    }
+    {
+      ProfScope prof(st, "ssd_bwd_db_tc", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
+      PMB_TRY(ssd_tc_db(st, in, g.db, g.lddbc, ws, ns));
+      PMB_TRY(reduce(ns, p.N, 2, g.db, g.lddbc));
+    }
+    return PMB_OK;
+  }
   {
     OpDG op = make_op<OpDG>(p, p.Q, p.Q);
     op.nsplit = pick_nsplit(nbcg, qt * (qt + 1) / 2, p.hpg); op.part = ws.splitk;

@@ -139,6 +139,11 @@ SSD_CASES = [  # B, T, H, P, N, G, Q
     (1, 96, 3, 20, 12, 1, 96),      # one chunk, ragged tile sizes
     (1, 512, 4, 64, 64, 1, 256),    # production chunk length
     (2, 80, 2, 16, 8, 2, 40),       # chunk length not a multiple of the tile
+    # shapes the tensor-core scan takes (block_len % 64 == 0, d_state % 32 == 0, d_head % 64 == 0)
+    (2, 256, 4, 64, 32, 4, 64),     # per-head B/C, chunk shorter than the 128-row tile
+    (1, 256, 2, 128, 128, 1, 128),  # wide head, large state
+    (2, 512, 8, 64, 64, 1, 128),
+    (1, 768, 3, 64, 64, 1, 256),    # three chunks of the production length
 ]
 
 
@@ -162,9 +167,10 @@ def test_ssd_fwd_bwd_vs_oracle(pm, B, T, H, P, N, G, Q):
     assert_close(dc, c.grad, what="dc")
 
 
-def test_ssd_strong_decay_underflows_cleanly(pm):
+@pytest.mark.parametrize("P,N", [(16, 16), (64, 32)])   # FMA engine / tensor-core engine
+def test_ssd_strong_decay_underflows_cleanly(pm, P, N):
     # A = -16, dt ~ 0.13, Q = 256: in-chunk sums reach about -530; exp must go to 0 without NaN
-    B, T, H, P, N = 1, 512, 2, 16, 16
+    B, T, H = 1, 512, 2
     x, b, c = randn((B, T, H, P), 1), randn((B, T, 1, N), 2), randn((B, T, 1, N), 3)
     a = torch.full((B, T, H), -16.0 * 0.13)
     y_ref = orc.ssd_scan_chunked(x, a, b.expand(B, T, H, N), c.expand(B, T, H, N), 256)
@@ -192,8 +198,8 @@ def test_ssd_initial_state_and_final_state_chain(pm):
     assert_close(fs2, fs_full, tol=1e-5, what="final state")
 
 
-def test_kernels_are_deterministic(pm):
-    B, T, H, P, N, G, Q = 2, 128, 8, 32, 16, 1, 64
+@pytest.mark.parametrize("B,T,H,P,N,G,Q", [(2, 128, 8, 32, 16, 1, 64), (2, 256, 8, 64, 64, 1, 128)])
+def test_kernels_are_deterministic(pm, B, T, H, P, N, G, Q):
     x, a = randn((B, T, H, P), 1).cuda(), (-rand((B, T, H), 2)).cuda()
     b, c, dy = randn((B, T, G, N), 3).cuda(), randn((B, T, G, N), 4).cuda(), randn((B, T, H, P), 5).cuda()
     outs = []
