@@ -114,66 +114,94 @@ pmb_status conv_silu_dt_fwd(cudaStream_t st, const Dims& d, const float* xzd, co
 // A thread owns one channel and TT time steps; per-(block-row) partial dw/db go to `partial`
 // (rows = gridDim.y, K+1 values per channel) and are summed by column_sum_kernel (fixed order).
 // ---------------------------------------------------------------------------------------------
-template <int K>
+template <int K, int VEC>
 __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
                                                             const float* __restrict__ w, const float* __restrict__ bias,
                                                             const float* __restrict__ dact, float* __restrict__ dxzd,
                                                             float* __restrict__ partial, int X, int T, int TT) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (c >= X) return;
   int tblocks = (T + TT - 1) / TT;
   int b = blockIdx.y / tblocks;
   int t0 = (blockIdx.y % tblocks) * TT;
   int t1 = min(t0 + TT, T);
-  float wr[K], br = bias ? bias[c] : 0.0f;
+  float wr[VEC][K], br[VEC];
 #pragma unroll
-  for (int k = 0; k < K; ++k) wr[k] = w[c * K + k];
+  for (int v = 0; v < VEC; ++v) {
+    br[v] = bias ? bias[c + v] : 0.0f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) wr[v][k] = w[(c + v) * K + k];
+  }
   const float* src = xzd + (int64_t)b * T * ldx + col0 + c;
   const float* dsrc = dact + (int64_t)b * T * X + c;
   float* ddst = dxzd + (int64_t)b * T * ldx + col0 + c;
   // xin holds xbc[t-(K-1) .. t]; dus holds du[t-(K-1) .. t] for the current t.
-  float xin[K], dus[K], dwacc[K], dbacc = 0.0f;
+  float xin[VEC][K], dus[VEC][K], dwacc[VEC][K], dbacc[VEC];
 #pragma unroll
-  for (int k = 0; k < K; ++k) { dwacc[k] = 0.0f; dus[k] = 0.0f; xin[k] = 0.0f; }
+  for (int v = 0; v < VEC; ++v) {
+    dbacc[v] = 0.0f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) { dwacc[v][k] = 0.0f; dus[v][k] = 0.0f; xin[v][k] = 0.0f; }
+  }
+  auto load = [&](const float* p, float (&o)[VEC]) {
+    if (VEC == 4) { float4 q = *reinterpret_cast<const float4*>(p); o[0] = q.x; o[1 % VEC] = q.y; o[2 % VEC] = q.z; o[3 % VEC] = q.w; }
+    else o[0] = *p;
+  };
 #pragma unroll
   for (int k = 0; k < K - 1; ++k) {
     int t = t0 - (K - 1) + k;
-    xin[k + 1] = t >= 0 ? src[(int64_t)t * ldx] : 0.0f;
+    float o[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) o[v] = 0.0f;
+    if (t >= 0) load(src + (int64_t)t * ldx, o);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) xin[v][k + 1] = o[v];
   }
-  // Walk t from t0 to t1-1+(K-1): du[t] is needed by dxbc[t-(K-1) .. t].
+  // Walk t from t0 to t1-1+(K-1): du[t] is needed by dxbc[t-(K-1) .. t]; du beyond the sequence end is 0.
   int tend = min(t1 + K - 1, T + K - 1);
   for (int t = t0; t < tend; ++t) {
+    float xn[VEC], dn[VEC];
 #pragma unroll
-    for (int k = 0; k < K - 1; ++k) { xin[k] = xin[k + 1]; dus[k] = dus[k + 1]; }
-    float du = 0.0f;
-    if (t < T) {
-      xin[K - 1] = src[(int64_t)t * ldx];
-      float u = br;
+    for (int v = 0; v < VEC; ++v) { xn[v] = 0.0f; dn[v] = 0.0f; }
+    if (t < T) { load(src + (int64_t)t * ldx, xn); load(dsrc + (int64_t)t * X, dn); }
+    float g[VEC];
 #pragma unroll
-      for (int k = 0; k < K; ++k) u = fmaf(wr[k], xin[k], u);
-      float s = sigmoid_acc(u);
-      du = dsrc[(int64_t)t * X] * (s + u * s * (1.0f - s));
-      if (t < t1) {  // this block owns the parameter-gradient contribution of t in [t0,t1)
-        dbacc += du;
+    for (int v = 0; v < VEC; ++v) {
 #pragma unroll
-        for (int k = 0; k < K; ++k) dwacc[k] = fmaf(du, xin[k], dwacc[k]);
+      for (int k = 0; k < K - 1; ++k) { xin[v][k] = xin[v][k + 1]; dus[v][k] = dus[v][k + 1]; }
+      float du = 0.0f;
+      if (t < T) {
+        xin[v][K - 1] = xn[v];
+        float u = br[v];
+#pragma unroll
+        for (int k = 0; k < K; ++k) u = fmaf(wr[v][k], xin[v][k], u);
+        float s = sigmoid_acc(u);
+        du = dn[v] * (s + u * s * (1.0f - s));
+        if (t < t1) {  // this block owns the parameter-gradient contribution of t in [t0,t1)
+          dbacc[v] += du;
+#pragma unroll
+          for (int k = 0; k < K; ++k) dwacc[v][k] = fmaf(du, xin[v][k], dwacc[v][k]);
+        }
       }
-    }
-    dus[K - 1] = du;
-    int tp = t - (K - 1);  // dxbc[tp] = sum_k w[k] * du[tp + (K-1) - k] = sum_k w[k] * dus[K-1-k]
-    if (tp >= t0 && tp < t1) {
-      float g = 0.0f;
+      dus[v][K - 1] = du;
+      float acc = 0.0f;   // dxbc[tp] = sum_k w[k] * du[tp + (K-1) - k] = sum_k w[k] * dus[K-1-k]
 #pragma unroll
-      for (int k = 0; k < K; ++k) g = fmaf(wr[k], dus[K - 1 - k], g);
-      ddst[(int64_t)tp * ldx] = g;
+      for (int k = 0; k < K; ++k) acc = fmaf(wr[v][k], dus[v][K - 1 - k], acc);
+      g[v] = acc;
+    }
+    int tp = t - (K - 1);
+    if (tp >= t0 && tp < t1) {
+      if (VEC == 4) *reinterpret_cast<float4*>(ddst + (int64_t)tp * ldx) = make_float4(g[0], g[1 % VEC], g[2 % VEC], g[3 % VEC]);
+      else ddst[(int64_t)tp * ldx] = g[0];
     }
   }
-  // Outputs tp in [t0,t1) whose future du lies beyond T were covered because du=0 there; but when
-  // tend was clipped to T+K-1 nothing is lost.  Rows t1-(K-1)..t1-1 need du up to t1+K-2 < tend. OK.
   float* prow = partial + (int64_t)blockIdx.y * X * (K + 1);
 #pragma unroll
-  for (int k = 0; k < K; ++k) prow[(int64_t)c * (K + 1) + k] = dwacc[k];
-  prow[(int64_t)c * (K + 1) + K] = dbacc;
+  for (int v = 0; v < VEC; ++v) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) prow[(int64_t)(c + v) * (K + 1) + k] = dwacc[v][k];
+    prow[(int64_t)(c + v) * (K + 1) + K] = dbacc[v];
+  }
 }
 
 // out[j] = sum_r partial[r*cols + j] in fixed order; optional second destination with a stride split
@@ -190,7 +218,7 @@ __global__ void conv_partial_reduce_kernel(const float* __restrict__ partial, in
   if (k < K) dw[c * K + k] = s; else db[c] = s;
 }
 
-static const int CONV_BWD_TT = 128;
+static const int CONV_BWD_TT = 32;
 
 size_t conv_bwd_ws_bytes(const Dims& d) {
   int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;
@@ -201,8 +229,15 @@ template <int K>
 static pmb_status launch_conv_bwd_k(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
                                     const float* dact, float* dxzd, float* partial) {
   int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;
-  dim3 grid((unsigned)cdiv(d.X, 128), (unsigned)(d.B * tblocks));
-  conv_silu_bwd_kernel<K><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, CONV_BWD_TT);
+  bool vec = (d.X % 4 == 0) && (d.J % 4 == 0) && (d.I % 4 == 0) &&
+             ((reinterpret_cast<uintptr_t>(xzd) | reinterpret_cast<uintptr_t>(dact) | reinterpret_cast<uintptr_t>(dxzd)) % 16 == 0);
+  if (vec) {
+    dim3 grid((unsigned)cdiv(d.X / 4, 128), (unsigned)(d.B * tblocks));
+    conv_silu_bwd_kernel<K, 4><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, CONV_BWD_TT);
+  } else {
+    dim3 grid((unsigned)cdiv(d.X, 128), (unsigned)(d.B * tblocks));
+    conv_silu_bwd_kernel<K, 1><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, CONV_BWD_TT);
+  }
   PMB_LAUNCHED();
   return PMB_OK;
 }
@@ -234,7 +269,7 @@ pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const
 // One 256-thread block per row; the row stays in registers between the two passes.
 // ---------------------------------------------------------------------------------------------
 constexpr int NORM_THREADS = 256;
-constexpr int NORM_MAX_PER_THREAD = 32;  // width <= 8192
+constexpr int NORM_MAX_PER_THREAD = 8;   // width <= 2048 (registers hold a whole row)
 
 __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_fwd_kernel(const float* __restrict__ y, const float* __restrict__ z,
                                                                          int64_t ldz, const float* __restrict__ w,
@@ -246,18 +281,24 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_fwd_kernel(const f
   const float* zr = z + row * ldz;
   float g[NORM_MAX_PER_THREAD];
   float ss = 0.0f;
-  int n = 0;
-  for (int i = threadIdx.x; i < width; i += NORM_THREADS, ++n) {
-    float zv = zr[i];
-    float gv = yr[i] * zv * sigmoid_acc(zv);
-    g[n] = gv;
-    ss = fmaf(gv, gv, ss);
+#pragma unroll
+  for (int n = 0; n < NORM_MAX_PER_THREAD; ++n) {
+    int i = threadIdx.x + n * NORM_THREADS;
+    if (i < width) {
+      float zv = zr[i];
+      float gv = yr[i] * zv * sigmoid_acc(zv);
+      g[n] = gv;
+      ss = fmaf(gv, gv, ss);
+    }
   }
   float tot = block_sum(ss, red);
   float r = 1.0f / sqrtf(tot / (float)width + eps);
   if (threadIdx.x == 0 && rstd) rstd[row] = r;
-  n = 0;
-  for (int i = threadIdx.x; i < width; i += NORM_THREADS, ++n) out[row * width + i] = g[n] * r * w[i];
+#pragma unroll
+  for (int n = 0; n < NORM_MAX_PER_THREAD; ++n) {
+    int i = threadIdx.x + n * NORM_THREADS;
+    if (i < width) out[row * width + i] = g[n] * r * w[i];
+  }
 }
 
 pmb_status gated_rmsnorm_fwd(cudaStream_t st, int64_t rows, int width, float eps, const float* y, const float* z, int64_t ldz,
@@ -272,7 +313,7 @@ pmb_status gated_rmsnorm_fwd(cudaStream_t st, int64_t rows, int width, float eps
 // Backward.  dg = w r dout - g r^3 (sum_j dout_j g_j w_j)/I;  dy = dg z sig(z);
 // dz = dg y (sig + z sig (1-sig));  dw_i = sum_rows dout_i g_i r.
 // A block handles NORM_ROWS consecutive rows so the dw partial stays in registers across them.
-constexpr int NORM_ROWS = 16;
+constexpr int NORM_ROWS = 4;
 
 __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_bwd_kernel(const float* __restrict__ dout, const float* __restrict__ y,
                                                                          const float* __restrict__ z, int64_t ldz,
@@ -288,38 +329,57 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_bwd_kernel(const f
     int64_t row = r0 + rr;
     if (row >= rows) break;  // uniform across the block
     float r = rstd[row];
+    // pass 1: load the row once, keep it in registers
+    float zv[NORM_MAX_PER_THREAD], yv[NORM_MAX_PER_THREAD], dn[NORM_MAX_PER_THREAD];
     float dot = 0.0f;
-    for (int i = threadIdx.x; i < width; i += NORM_THREADS) {
-      float zv = z[row * ldz + i];
-      float gv = y[row * width + i] * zv * sigmoid_acc(zv);
-      dot = fmaf(dout[row * width + i] * gv, w[i], dot);
+#pragma unroll
+    for (int n = 0; n < NORM_MAX_PER_THREAD; ++n) {
+      int i = threadIdx.x + n * NORM_THREADS;
+      if (i < width) {
+        zv[n] = z[row * ldz + i]; yv[n] = y[row * width + i]; dn[n] = dout[row * width + i];
+        float gv = yv[n] * zv[n] * sigmoid_acc(zv[n]);
+        dot = fmaf(dn[n] * gv, w[i], dot);
+      }
     }
     float tot = block_sum(dot, red);
     float coef = r * r * r * tot / (float)width;
-    int n = 0;
-    for (int i = threadIdx.x; i < width; i += NORM_THREADS, ++n) {
-      float zv = z[row * ldz + i];
-      float yv = y[row * width + i];
-      float s = sigmoid_acc(zv);
-      float gv = yv * zv * s;
-      float dn = dout[row * width + i];
-      float dg = w[i] * r * dn - gv * coef;
-      dwacc[n] = fmaf(dn * gv, r, dwacc[n]);
-      dy[row * width + i] = dg * zv * s;
-      dz[row * lddz + i] = dg * yv * (s + zv * s * (1.0f - s));
+#pragma unroll
+    for (int n = 0; n < NORM_MAX_PER_THREAD; ++n) {
+      int i = threadIdx.x + n * NORM_THREADS;
+      if (i < width) {
+        float s = sigmoid_acc(zv[n]);
+        float gv = yv[n] * zv[n] * s;
+        float dg = w[i] * r * dn[n] - gv * coef;
+        dwacc[n] = fmaf(dn[n] * gv, r, dwacc[n]);
+        dy[row * width + i] = dg * zv[n] * s;
+        dz[row * lddz + i] = dg * yv[n] * (s + zv[n] * s * (1.0f - s));
+      }
     }
   }
-  int n = 0;
-  for (int i = threadIdx.x; i < width; i += NORM_THREADS, ++n) dw_partial[(int64_t)blockIdx.x * width + i] = dwacc[n];
+#pragma unroll
+  for (int n = 0; n < NORM_MAX_PER_THREAD; ++n) {
+    int i = threadIdx.x + n * NORM_THREADS;
+    if (i < width) dw_partial[(int64_t)blockIdx.x * width + i] = dwacc[n];
+  }
 }
 
-// out[j] = scale * sum_r partial[r*cols + j], fixed order (deterministic).
-__global__ void column_sum_kernel(const float* __restrict__ partial, int64_t rows, int cols, float* __restrict__ out) {
-  int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= cols) return;
+// out[j] = sum_r partial[r*cols + j].  Block = 32 columns x 8 row lanes; each lane sums rows ty, ty+8, ...
+// and the 8 lane sums are added in a fixed order (deterministic).
+__global__ void __launch_bounds__(256) column_sum_kernel(const float* __restrict__ partial, int64_t rows, int cols, float* __restrict__ out) {
+  __shared__ float sh[8][33];
+  int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  int j = blockIdx.x * 32 + tx;
   float s = 0.0f;
-  for (int64_t r = 0; r < rows; ++r) s += partial[r * cols + j];
-  out[j] = s;
+  if (j < cols)
+    for (int64_t r = ty; r < rows; r += 8) s += partial[r * cols + j];
+  sh[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && j < cols) {
+    float t = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sh[k][tx];
+    out[j] = t;
+  }
 }
 
 size_t gated_rmsnorm_bwd_ws_bytes(int64_t rows, int width) {
@@ -335,7 +395,7 @@ pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const flo
   ProfScope prof(st, "gated_rmsnorm_bwd", 0.0, 4.0 * rows * 5.0 * width);
   gated_rmsnorm_bwd_kernel<<<(unsigned)nblk, NORM_THREADS, 0, st>>>(dout, y, z, ldz, w, rstd, dy, dz, lddz, partial, rows, width);
   PMB_LAUNCHED();
-  column_sum_kernel<<<(unsigned)cdiv(width, 256), 256, 0, st>>>(partial, nblk, width, dw);
+  column_sum_kernel<<<(unsigned)cdiv(width, 32), 256, 0, st>>>(partial, nblk, width, dw);
   PMB_LAUNCHED();
   return PMB_OK;
 }
@@ -387,7 +447,7 @@ pmb_status gated_rmsnorm_bwd_static(cudaStream_t st, int64_t rows, int width, co
 }
 
 pmb_status column_sum(cudaStream_t st, const float* partial, int64_t rows, int cols, float* out) {
-  column_sum_kernel<<<(unsigned)cdiv(cols, 256), 256, 0, st>>>(partial, rows, cols, out);
+  column_sum_kernel<<<(unsigned)cdiv(cols, 32), 256, 0, st>>>(partial, rows, cols, out);
   PMB_LAUNCHED();
   return PMB_OK;
 }

@@ -211,7 +211,8 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
           h.z = __float_as_uint(f[2]) & 0xFFFFE000u; h.w = __float_as_uint(f[3]) & 0xFFFFE000u;
           l.x = __float_as_uint(f[0] - __uint_as_float(h.x)); l.y = __float_as_uint(f[1] - __uint_as_float(h.y));
           l.z = __float_as_uint(f[2] - __uint_as_float(h.z)); l.w = __float_as_uint(f[3] - __uint_as_float(h.w));
-          hi[i] = h;
+          // kind::tf32 ignores the 13 low mantissa bits, so an unscaled tile serves as its own high part
+          if (Op::A_SCALE) hi[i] = make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
           lo[i] = l;
         }
         // B tile
@@ -238,7 +239,7 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
           h.z = __float_as_uint(f[2]) & 0xFFFFE000u; h.w = __float_as_uint(f[3]) & 0xFFFFE000u;
           l.x = __float_as_uint(f[0] - __uint_as_float(h.x)); l.y = __float_as_uint(f[1] - __uint_as_float(h.y));
           l.z = __float_as_uint(f[2] - __uint_as_float(h.z)); l.w = __float_as_uint(f[3] - __uint_as_float(h.w));
-          bhi[i] = h;
+          if (Op::B_SCALE) bhi[i] = make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
           blo[i] = l;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
