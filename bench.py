@@ -28,7 +28,11 @@ WORKLOADS = {
     # name: (layers, d_model, headdim, heads, d_state, chunk, vocab, batch per GPU, seq)
     "c2_flat100m_fp32_b4_t512": (24, 768, 64, 24, 64, 256, 50257, 4, 512),
     "c1_single_block_dims_lm": (2, 128, 32, 8, 16, 64, 1000, 2, 128),   # tiny, for quick checks only
+    # BASELINE configs[3]: same model, bf16 storage / fp32 accumulation, batch 8, long context
+    "c4_flat100m_bf16_b8_t2048": (24, 768, 64, 24, 64, 256, 50257, 8, 2048),
+    "c4_flat100m_bf16_b8_t8192": (24, 768, 64, 24, 64, 256, 50257, 8, 8192),
 }
+BF16_WORKLOADS = {"c4_flat100m_bf16_b8_t2048", "c4_flat100m_bf16_b8_t8192"}
 DEFAULT_WORKLOAD = "c2_flat100m_fp32_b4_t512"
 
 
@@ -195,7 +199,8 @@ def run_ours(args):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = pm_b200.Mamba2Config(d_model=D, d_state=N, d_head=P, n_heads=H, n_groups=1, d_conv=4, block_len=Q)
-    lm = pm_b200.FlatMamba(cfg, L, V, B, T)
+    bf16 = w in BF16_WORKLOADS
+    lm = pm_b200.FlatMamba(cfg, L, V, B, T, compute_dtype=torch.bfloat16 if bf16 else torch.float32)
     embed, layers = make_weights(w)
     lm.load(embed.cuda(), [{k: v.cuda() for k, v in p.items()} for p in layers])
     del embed, layers
@@ -306,7 +311,7 @@ def run_ours(args):
         line = {
             "metric": "train tokens/sec (fwd+bwd, ckpt)", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage / f32 accumulate" if bf16 else "f32", "data": "synthetic",
             "config": {"workload": w, "layers": L, "d_model": D, "d_state": N, "headdim": P, "chunk": Q, "vocab": V,
                        "per_gpu_batch": B, "seq_len": T, "global_batch": B * world, "parallelism": f"dp{world}",
                        "checkpointing": "per block; stored across the stack: block inputs only",

@@ -101,6 +101,15 @@ pmb_status pmb_gemm_f32(void* stream, int32_t trans_a, int32_t trans_b, int64_t 
                         const float* d_A, int64_t lda, const float* d_B, int64_t ldb,
                         float* d_C, int64_t ldc, const float* d_R, int32_t engine);
 
+/* bf16 GEMM for the bf16-storage configurations (block.rs:24-42): A, B are bf16 bit patterns, accumulation is
+ * fp32 on the tensor cores; d_C and d_R are fp32 (out_bf16 = 0) or bf16 (out_bf16 = 1).  Operand bases must be
+ * 16-byte aligned and lda, ldb multiples of 8 elements. */
+pmb_status pmb_gemm_bf16(void* stream, int32_t trans_a, int32_t trans_b, int64_t M, int64_t N, int64_t K,
+                         const uint16_t* d_A, int64_t lda, const uint16_t* d_B, int64_t ldb,
+                         void* d_C, int64_t ldc, const void* d_R, int32_t out_bf16);
+/* Ops::to_dtype(F32 -> BF16) (ops.rs:54-73), round to nearest even. */
+pmb_status pmb_cast_f32_to_bf16(void* stream, const float* d_src, uint16_t* d_dst, int64_t n);
+
 /* ---- conv1d + SiLU + dt softplus (block.rs:150-163,184-188).
  * d_xzd (B,T,J): columns [0,I) z, [I,I+X) xBC pre-conv, [I+X,J) dt_raw.
  * d_act (B,T,X) = silu(causal depthwise conv + bias); d_dt (B,T,H) = softplus(dt_raw + dt_bias). */
@@ -182,6 +191,22 @@ pmb_status pmb_mamba2_block_bwd(void* stream, const pmb_mamba2_config* cfg, cons
                                 const float* d_dx_accum, float* d_dx, const pmb_block_grads* grads,
                                 void* d_ws, size_t ws_bytes);
 
+/* bf16-storage block ("compute dtype" bf16, block.rs:24-42): x, residual, out, dout, dx are bf16; parameters stay
+ * fp32 and the caller supplies bf16 copies of the two projection weights (pmb_cast_f32_to_bf16, refreshed whenever
+ * the fp32 masters change).  The projections run as bf16 GEMMs with fp32 accumulation; conv, softplus, exp, the
+ * scan and the norm run in fp32 as in the reference.  Parameter gradients are fp32.  Needs d_model, d_inner and
+ * in_proj_dim to be multiples of 8. */
+size_t pmb_mamba2_block_workspace_bytes_bf16(const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen);
+pmb_status pmb_mamba2_block_fwd_bf16(void* stream, const pmb_mamba2_config* cfg, const pmb_block_params* params,
+                                     const uint16_t* d_in_proj_bf16, const uint16_t* d_out_proj_bf16,
+                                     int32_t batch, int32_t seqlen, const uint16_t* d_x, const uint16_t* d_residual,
+                                     uint16_t* d_out, void* d_ws, size_t ws_bytes);
+pmb_status pmb_mamba2_block_bwd_bf16(void* stream, const pmb_mamba2_config* cfg, const pmb_block_params* params,
+                                     const uint16_t* d_in_proj_bf16, const uint16_t* d_out_proj_bf16,
+                                     int32_t batch, int32_t seqlen, const uint16_t* d_x, const uint16_t* d_dout,
+                                     const uint16_t* d_dx_accum, uint16_t* d_dx, const pmb_block_grads* grads,
+                                     void* d_ws, size_t ws_bytes);
+
 /* ---- one-token decode (Mamba2Block::step, block.rs:278-417).  x_t (B,1,D) -> y_t (B,1,D);
  * ssm_state (B,H,N,P) and conv_window (B,X,K-1) are updated in place. */
 size_t pmb_mamba2_step_workspace_bytes(const pmb_mamba2_config* cfg, int32_t batch);
@@ -214,6 +239,11 @@ pmb_status pmb_stack_bwd(void* stream, const pmb_mamba2_config* cfg, int32_t n_l
 typedef struct pmb_lm pmb_lm;
 pmb_status pmb_lm_create(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t vocab,
                          int32_t batch, int32_t seqlen, pmb_lm** out);
+/* Same with the storage dtype chosen: bf16_storage != 0 keeps activations (block inputs, hidden, gradient stream)
+ * and the GEMM operands in bf16 with fp32 accumulation, islands and logits in fp32 (FlatMamba::with_compute_dtype,
+ * flat.rs:74-78); parameters and gradients stay fp32. */
+pmb_status pmb_lm_create_dtype(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t vocab,
+                               int32_t batch, int32_t seqlen, int32_t bf16_storage, pmb_lm** out);
 void       pmb_lm_destroy(pmb_lm* lm);
 int64_t    pmb_lm_param_count(const pmb_lm* lm);                 /* elements in the flat buffer (with padding) */
 int64_t    pmb_lm_param_offset(const pmb_lm* lm, int32_t layer, int32_t which); /* layer=-1: embedding; which 0..7 */

@@ -70,6 +70,8 @@ extern "C" pmb_status pmb_device_status(int32_t* h_word_out) {
   PMB_TRY(read_clear_device_status(&w));
   PMB_TRY(read_clear_device_status_ssd(&w2));
   w |= w2 << 8;
+  PMB_TRY(read_clear_device_status_bf16(&w2));
+  w |= w2 << 16;
   if (h_word_out) *h_word_out = (int32_t)w;
   return PMB_OK;
 }

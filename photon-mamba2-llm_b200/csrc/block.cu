@@ -34,14 +34,42 @@ __global__ void __launch_bounds__(256) dt_bwd_kernel(const float* __restrict__ x
   }
 }
 
+// fp32 -> bf16 (round to nearest even), 4 elements per thread
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ src, uint16_t* __restrict__ dst, int64_t n4, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  auto cvt = [](float f) -> uint32_t {
+    uint32_t u = __float_as_uint(f);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (u >> 16) | 0x40;
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return u >> 16;
+  };
+  if (i < n4) {
+    float4 v = reinterpret_cast<const float4*>(src)[i];
+    uint2 o;
+    o.x = cvt(v.x) | (cvt(v.y) << 16);
+    o.y = cvt(v.z) | (cvt(v.w) << 16);
+    reinterpret_cast<uint2*>(dst)[i] = o;
+  }
+  if (i == 0) for (int64_t j = n4 * 4; j < n; ++j) dst[j] = (uint16_t)cvt(src[j]);
+}
+
+pmb_status cast_f32_bf16(cudaStream_t st, const float* src, uint16_t* dst, int64_t n) {
+  int64_t n4 = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) ? 0 : n / 4;
+  ProfScope prof(st, "cast_f32_bf16", 0.0, 6.0 * n);
+  cast_f32_bf16_kernel<<<(unsigned)cdiv(n4 > 0 ? n4 : 1, 256), 256, 0, st>>>(src, dst, n4, n);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
 struct BlockWs {
   float *xzd, *act, *dt, *y, *rstd, *normed, *Aneg;
   SsdWs ssd;
   float *dnormed, *dxzd, *dact, *ddt, *dA, *scratch;
   size_t scratch_bytes;
+  uint16_t *normed16, *dxzd16;   // bf16 copies of the two GEMM operands (bf16-storage mode only)
 };
 
-static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* out) {
+static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* out, bool bf16 = false) {
   Arena ar(base, bytes);
   BlockWs w{};
   w.xzd = ar.take<float>((size_t)d.M * d.J);
@@ -65,11 +93,13 @@ static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* 
   size_t nb = gated_rmsnorm_bwd_ws_bytes(d.M, d.I);
   if (nb > w.scratch_bytes) w.scratch_bytes = nb;
   w.scratch = reinterpret_cast<float*>(ar.take<char>(w.scratch_bytes));
+  w.normed16 = ar.take<uint16_t>(bf16 ? (size_t)d.M * d.I : 0);
+  w.dxzd16 = ar.take<uint16_t>(bf16 ? (size_t)d.M * d.J : 0);
   if (out) *out = w;
   return ar.ok ? ar.used() : 0;
 }
 
-size_t block_ws_bytes(const Dims& d) { return block_ws_layout(d, nullptr, 0, nullptr); }
+size_t block_ws_bytes(const Dims& d, bool bf16) { return block_ws_layout(d, nullptr, 0, nullptr, bf16); }
 
 static SsdIn ssd_inputs(const Dims& d, const pmb_block_params& p, const BlockWs& w) {
   SsdIn in{};
@@ -82,34 +112,49 @@ static SsdIn ssd_inputs(const Dims& d, const pmb_block_params& p, const BlockWs&
 }
 
 // Steps 1-8 of Mamba2Block::forward (block.rs:143-222): everything up to the normalised gate output.
-static pmb_status block_fwd_core(cudaStream_t st, const Dims& d, const pmb_block_params& p, const float* x, const BlockWs& w) {
-  PMB_TRY(gemm(st, 0, 0, d.M, d.J, d.D, x, d.D, p.in_proj_weight, d.J, w.xzd, d.J, nullptr, 0));
+// In bf16-storage mode (w16 != NULL) x is bf16, the two projections run as bf16 GEMMs with fp32 accumulation
+// against bf16 copies of the weights, and everything between them (the reference's "fp32 islands",
+// block.rs:24-42) stays in fp32.
+static pmb_status block_fwd_core(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const BlockWs& w,
+                                 const Weights16* w16) {
+  if (w16) PMB_TRY(gemm_bf16(st, 0, 0, d.M, d.J, d.D, x, d.D, w16->in_proj, d.J, w.xzd, d.J, nullptr, 0));
+  else PMB_TRY(gemm(st, 0, 0, d.M, d.J, d.D, static_cast<const float*>(x), d.D, p.in_proj_weight, d.J, w.xzd, d.J, nullptr, 0));
   PMB_TRY(conv_silu_dt_fwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, p.dt_bias, w.act, w.dt));
   a_neg_kernel<<<(unsigned)cdiv(d.H, 128), 128, 0, st>>>(p.a_log, w.Aneg, d.H);
   PMB_LAUNCHED();
   PMB_TRY(ssd_fwd(st, ssd_inputs(d, p, w), nullptr, w.y, d.I, nullptr, w.ssd));
   PMB_TRY(gated_rmsnorm_fwd(st, d.M, d.I, d.eps, w.y, w.xzd, d.J, p.norm_weight, w.normed, w.rstd));
+  if (w16) PMB_TRY(cast_f32_bf16(st, w.normed, w.normed16, d.M * d.I));
   return PMB_OK;
 }
 
-pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const float* x, const float* residual,
-                     float* out, void* ws, size_t ws_bytes) {
+pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* residual,
+                     void* out, void* ws, size_t ws_bytes, const Weights16* w16) {
   BlockWs w;
-  if (block_ws_layout(d, ws, ws_bytes, &w) == 0 || !ws) return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_bytes(d));
-  PMB_TRY(block_fwd_core(st, d, p, x, w));
-  PMB_TRY(gemm(st, 0, 0, d.M, d.D, d.I, w.normed, d.I, p.out_proj_weight, d.D, out, d.D, residual, 0));
+  if (block_ws_layout(d, ws, ws_bytes, &w, w16 != nullptr) == 0 || !ws)
+    return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_bytes(d, w16 != nullptr));
+  PMB_TRY(block_fwd_core(st, d, p, x, w, w16));
+  if (w16) PMB_TRY(gemm_bf16(st, 0, 0, d.M, d.D, d.I, w.normed16, d.I, w16->out_proj, d.D, out, d.D, residual, 1));
+  else PMB_TRY(gemm(st, 0, 0, d.M, d.D, d.I, w.normed, d.I, p.out_proj_weight, d.D, static_cast<float*>(out), d.D, static_cast<const float*>(residual), 0));
   return PMB_OK;
 }
 
-pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const float* x, const float* dout,
-                     const float* dx_accum, float* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes) {
+pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* dout,
+                     const void* dx_accum, void* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes, const Weights16* w16) {
   BlockWs w;
-  if (block_ws_layout(d, ws, ws_bytes, &w) == 0 || !ws) return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_bytes(d));
+  if (block_ws_layout(d, ws, ws_bytes, &w, w16 != nullptr) == 0 || !ws)
+    return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_bytes(d, w16 != nullptr));
   // recompute (the out_proj product itself is not needed for gradients)
-  PMB_TRY(block_fwd_core(st, d, p, x, w));
+  PMB_TRY(block_fwd_core(st, d, p, x, w, w16));
   // out_proj: dW_out = normed^T dout;  dnormed = dout W_out^T
-  PMB_TRY(gemm(st, 1, 0, d.I, d.D, d.M, w.normed, d.I, dout, d.D, g.out_proj_weight, d.D, nullptr, 0));
-  PMB_TRY(gemm(st, 0, 1, d.M, d.I, d.D, dout, d.D, p.out_proj_weight, d.D, w.dnormed, d.I, nullptr, 0));
+  if (w16) {
+    PMB_TRY(gemm_bf16(st, 1, 0, d.I, d.D, d.M, w.normed16, d.I, dout, d.D, g.out_proj_weight, d.D, nullptr, 0));
+    PMB_TRY(gemm_bf16(st, 0, 1, d.M, d.I, d.D, dout, d.D, w16->out_proj, d.D, w.dnormed, d.I, nullptr, 0));
+  } else {
+    const float* df = static_cast<const float*>(dout);
+    PMB_TRY(gemm(st, 1, 0, d.I, d.D, d.M, w.normed, d.I, df, d.D, g.out_proj_weight, d.D, nullptr, 0));
+    PMB_TRY(gemm(st, 0, 1, d.M, d.I, d.D, df, d.D, p.out_proj_weight, d.D, w.dnormed, d.I, nullptr, 0));
+  }
   // gate + norm: dy (in place over dnormed), dz -> z columns of dxzd
   PMB_TRY(gated_rmsnorm_bwd(st, d.M, d.I, w.dnormed, w.y, w.xzd, d.J, p.norm_weight, w.rstd, w.dnormed, w.dxzd, d.J,
                             g.norm_weight, w.scratch, w.scratch_bytes));
@@ -125,8 +170,14 @@ pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, 
   PMB_TRY(conv_silu_bwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, w.dact, w.dxzd, g.conv1d_weight, g.conv1d_bias,
                         w.scratch, w.scratch_bytes));
   // in_proj: dW_in = x^T dxzd;  dx = dxzd W_in^T (+ accumulated residual gradient)
-  PMB_TRY(gemm(st, 1, 0, d.D, d.J, d.M, x, d.D, w.dxzd, d.J, g.in_proj_weight, d.J, nullptr, 0));
-  PMB_TRY(gemm(st, 0, 1, d.M, d.D, d.J, w.dxzd, d.J, p.in_proj_weight, d.J, dx, d.D, dx_accum, 0));
+  if (w16) {
+    PMB_TRY(cast_f32_bf16(st, w.dxzd, w.dxzd16, d.M * d.J));
+    PMB_TRY(gemm_bf16(st, 1, 0, d.D, d.J, d.M, x, d.D, w.dxzd16, d.J, g.in_proj_weight, d.J, nullptr, 0));
+    PMB_TRY(gemm_bf16(st, 0, 1, d.M, d.D, d.J, w.dxzd16, d.J, w16->in_proj, d.J, dx, d.D, dx_accum, 1));
+  } else {
+    PMB_TRY(gemm(st, 1, 0, d.D, d.J, d.M, static_cast<const float*>(x), d.D, w.dxzd, d.J, g.in_proj_weight, d.J, nullptr, 0));
+    PMB_TRY(gemm(st, 0, 1, d.M, d.D, d.J, w.dxzd, d.J, p.in_proj_weight, d.J, static_cast<float*>(dx), d.D, static_cast<const float*>(dx_accum), 0));
+  }
   return PMB_OK;
 }
 
@@ -140,7 +191,7 @@ using namespace pmb;
 extern "C" size_t pmb_mamba2_block_workspace_bytes(const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen) {
   Dims d;
   if (make_dims(cfg, batch, seqlen, &d) != PMB_OK) return 0;
-  return block_ws_bytes(d);
+  return block_ws_bytes(d, false);
 }
 
 extern "C" pmb_status pmb_mamba2_block_fwd(void* stream, const pmb_mamba2_config* cfg, const pmb_block_params* params,
@@ -149,7 +200,7 @@ extern "C" pmb_status pmb_mamba2_block_fwd(void* stream, const pmb_mamba2_config
   Dims d;
   PMB_TRY(make_dims(cfg, batch, seqlen, &d));
   if (!params || !d_x || !d_out) return fail(PMB_ERR_ARG, "block_fwd: NULL argument");
-  return block_fwd(static_cast<cudaStream_t>(stream), d, *params, d_x, d_residual, d_out, d_ws, ws_bytes);
+  return block_fwd(static_cast<cudaStream_t>(stream), d, *params, d_x, d_residual, d_out, d_ws, ws_bytes, nullptr);
 }
 
 extern "C" pmb_status pmb_mamba2_block_bwd(void* stream, const pmb_mamba2_config* cfg, const pmb_block_params* params,
@@ -159,8 +210,38 @@ extern "C" pmb_status pmb_mamba2_block_bwd(void* stream, const pmb_mamba2_config
   Dims d;
   PMB_TRY(make_dims(cfg, batch, seqlen, &d));
   if (!params || !grads || !d_x || !d_dout || !d_dx) return fail(PMB_ERR_ARG, "block_bwd: NULL argument");
-  return block_bwd(static_cast<cudaStream_t>(stream), d, *params, d_x, d_dout, d_dx_accum, d_dx, *grads, d_ws, ws_bytes);
+  return block_bwd(static_cast<cudaStream_t>(stream), d, *params, d_x, d_dout, d_dx_accum, d_dx, *grads, d_ws, ws_bytes, nullptr);
 }
+
+namespace pmb {
+
+// Residual stack with block-input checkpoints.  `saved` holds n_layers+1 slots of (M,D) in the storage dtype
+// (fp32, or bf16 when w16 != NULL); slot l = input of block l.
+pmb_status stack_fwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_block_params* layers, const Weights16* w16,
+                     void* saved, void* ws, size_t ws_bytes) {
+  size_t slot = (size_t)d.M * d.D * (w16 ? 2 : 4);
+  char* base = static_cast<char*>(saved);
+  for (int l = 0; l < n_layers; ++l) {
+    const void* h = base + (size_t)l * slot;
+    PMB_TRY(block_fwd(st, d, layers[l], h, h, base + (size_t)(l + 1) * slot, ws, ws_bytes, w16 ? &w16[l] : nullptr));
+  }
+  return PMB_OK;
+}
+
+// dh_{l-1} = dh_l + dBlock_l/dx  (checkpoint.rs:110-135 reproduces this sum through the residual adds)
+pmb_status stack_bwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_block_params* layers, const Weights16* w16,
+                     const pmb_block_grads* grads, const void* saved, void* dhidden, void* ws, size_t ws_bytes,
+                     pmb_layer_callback on_layer_done, void* user) {
+  size_t slot = (size_t)d.M * d.D * (w16 ? 2 : 4);
+  const char* base = static_cast<const char*>(saved);
+  for (int l = n_layers - 1; l >= 0; --l) {
+    PMB_TRY(block_bwd(st, d, layers[l], base + (size_t)l * slot, dhidden, dhidden, dhidden, grads[l], ws, ws_bytes, w16 ? &w16[l] : nullptr));
+    if (on_layer_done) on_layer_done(l, user);
+  }
+  return PMB_OK;
+}
+
+}  // namespace pmb
 
 extern "C" pmb_status pmb_stack_fwd_ckpt(void* stream, const pmb_mamba2_config* cfg, int32_t n_layers,
                                          const pmb_block_params* layers, int32_t batch, int32_t seqlen,
@@ -168,13 +249,7 @@ extern "C" pmb_status pmb_stack_fwd_ckpt(void* stream, const pmb_mamba2_config* 
   Dims d;
   PMB_TRY(make_dims(cfg, batch, seqlen, &d));
   if (!layers || !d_saved || n_layers <= 0) return fail(PMB_ERR_ARG, "stack_fwd: bad argument");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  size_t slot = (size_t)d.M * d.D;
-  for (int l = 0; l < n_layers; ++l) {
-    const float* h = d_saved + (size_t)l * slot;
-    PMB_TRY(block_fwd(st, d, layers[l], h, h, d_saved + (size_t)(l + 1) * slot, d_ws, ws_bytes));
-  }
-  return PMB_OK;
+  return stack_fwd(static_cast<cudaStream_t>(stream), d, n_layers, layers, nullptr, d_saved, d_ws, ws_bytes);
 }
 
 extern "C" pmb_status pmb_stack_bwd(void* stream, const pmb_mamba2_config* cfg, int32_t n_layers,
@@ -184,12 +259,48 @@ extern "C" pmb_status pmb_stack_bwd(void* stream, const pmb_mamba2_config* cfg, 
   Dims d;
   PMB_TRY(make_dims(cfg, batch, seqlen, &d));
   if (!layers || !grads || !d_saved || !d_dhidden || n_layers <= 0) return fail(PMB_ERR_ARG, "stack_bwd: bad argument");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  size_t slot = (size_t)d.M * d.D;
-  // dh_{l-1} = dh_l + dBlock_l/dx  (checkpoint.rs:110-135 reproduces this sum through the residual adds)
-  for (int l = n_layers - 1; l >= 0; --l) {
-    PMB_TRY(block_bwd(st, d, layers[l], d_saved + (size_t)l * slot, d_dhidden, d_dhidden, d_dhidden, grads[l], d_ws, ws_bytes));
-    if (on_layer_done) on_layer_done(l, user);
-  }
+  return stack_bwd(static_cast<cudaStream_t>(stream), d, n_layers, layers, nullptr, grads, d_saved, d_dhidden, d_ws, ws_bytes,
+                   on_layer_done, user);
+}
+
+// ---- bf16-storage variants (block.rs:24-42: activations and the two projections in bf16, islands in fp32)
+extern "C" pmb_status pmb_cast_f32_to_bf16(void* stream, const float* d_src, uint16_t* d_dst, int64_t n) {
+  if (!d_src || !d_dst || n <= 0) return fail(PMB_ERR_ARG, "cast_f32_to_bf16: bad argument");
+  return cast_f32_bf16(static_cast<cudaStream_t>(stream), d_src, d_dst, n);
+}
+
+extern "C" size_t pmb_mamba2_block_workspace_bytes_bf16(const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen) {
+  Dims d;
+  if (make_dims(cfg, batch, seqlen, &d) != PMB_OK) return 0;
+  return block_ws_bytes(d, true);
+}
+
+static pmb_status check_bf16_dims(const Dims& d) {
+  if ((d.D % 8) || (d.J % 8) || (d.I % 8)) return fail(PMB_ERR_SHAPE, "bf16 storage needs d_model, d_inner and in_proj_dim to be multiples of 8");
   return PMB_OK;
+}
+
+extern "C" pmb_status pmb_mamba2_block_fwd_bf16(void* stream, const pmb_mamba2_config* cfg, const pmb_block_params* params,
+                                                const uint16_t* d_in_proj_bf16, const uint16_t* d_out_proj_bf16,
+                                                int32_t batch, int32_t seqlen, const uint16_t* d_x, const uint16_t* d_residual,
+                                                uint16_t* d_out, void* d_ws, size_t ws_bytes) {
+  Dims d;
+  PMB_TRY(make_dims(cfg, batch, seqlen, &d));
+  PMB_TRY(check_bf16_dims(d));
+  if (!params || !d_in_proj_bf16 || !d_out_proj_bf16 || !d_x || !d_out) return fail(PMB_ERR_ARG, "block_fwd_bf16: NULL argument");
+  Weights16 w16{d_in_proj_bf16, d_out_proj_bf16};
+  return block_fwd(static_cast<cudaStream_t>(stream), d, *params, d_x, d_residual, d_out, d_ws, ws_bytes, &w16);
+}
+
+extern "C" pmb_status pmb_mamba2_block_bwd_bf16(void* stream, const pmb_mamba2_config* cfg, const pmb_block_params* params,
+                                                const uint16_t* d_in_proj_bf16, const uint16_t* d_out_proj_bf16,
+                                                int32_t batch, int32_t seqlen, const uint16_t* d_x, const uint16_t* d_dout,
+                                                const uint16_t* d_dx_accum, uint16_t* d_dx, const pmb_block_grads* grads,
+                                                void* d_ws, size_t ws_bytes) {
+  Dims d;
+  PMB_TRY(make_dims(cfg, batch, seqlen, &d));
+  PMB_TRY(check_bf16_dims(d));
+  if (!params || !grads || !d_in_proj_bf16 || !d_out_proj_bf16 || !d_x || !d_dout || !d_dx) return fail(PMB_ERR_ARG, "block_bwd_bf16: NULL argument");
+  Weights16 w16{d_in_proj_bf16, d_out_proj_bf16};
+  return block_bwd(static_cast<cudaStream_t>(stream), d, *params, d_x, d_dout, d_dx_accum, d_dx, *grads, d_ws, ws_bytes, &w16);
 }

@@ -1,0 +1,288 @@
+// bf16 GEMM on tcgen05 (kind::f16, fp32 accumulation in TMEM) for the bf16-storage configurations:
+// C = op(A) op(B) (+ R), A and B bf16 in HBM, C (and R) fp32 or bf16.
+//
+// CTA = one 128x128 output tile; warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = epilogue.
+// bf16 operands need no in-smem processing, so a stage is just the two landed tiles (128 x 64 bf16 each,
+// 32 KiB per stage) and the ring is 6 deep.  K-major tiles: 128-byte rows, 128-byte swizzle.  MN-major
+// tiles: blocks of 64 elements along M/N, 64 k-rows of 128 bytes per block, same swizzle.
+// Every mbarrier wait is bounded; on expiry the kernel raises the device status word and drains.
+#include <cstdlib>
+#include <map>
+#include <tuple>
+#include "tc_common.cuh"
+#include "kernels.h"
+
+namespace pmb {
+
+static __device__ unsigned int g_bf16_status = 0;
+
+pmb_status read_clear_device_status_bf16(unsigned int* word) {
+  unsigned int zero = 0;
+  PMB_CUDA(cudaMemcpyFromSymbol(word, g_bf16_status, sizeof(unsigned int)));
+  if (*word) PMB_CUDA(cudaMemcpyToSymbol(g_bf16_status, &zero, sizeof(unsigned int)));
+  return PMB_OK;
+}
+
+namespace hb {
+
+using namespace tcx;
+
+constexpr int TBM = 128, TBN = 128, TBK = 64, STAGES = 6;
+constexpr int TILE_BYTES = TBM * TBK * 2;   // 16 KiB
+constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int NTHREADS = 192;
+constexpr int TMEM_COLS = 128;
+
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+struct Params {
+  int M, N, K;
+  int a_mn_major, b_mn_major;
+  void* C; int64_t ldc; const void* R; int out_bf16;
+};
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+__device__ __forceinline__ uint16_t float_to_bf16_bits(float f) {   // round to nearest even
+  uint32_t u = __float_as_uint(f);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  uint8_t* tiles_ptr = smem_raw + (tiles - raw);
+  const uint32_t bars = tiles + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tiles_ptr + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 1));
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * TBN;
+  const int num_kt = (p.K + TBK - 1) / TBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int armed = 0;
+      for (int kt = 0; kt < num_kt; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t ph = (kt / STAGES) & 1;
+        if (!mbar_wait(empty_bar(s), ph ^ 1u)) { atomicOr(&g_bf16_status, 1u); *abort_flag = 1; break; }
+        if (*abort_flag) break;
+        const uint32_t a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + TILE_BYTES;
+        mbar_expect_tx(full_bar(s), STAGE_BYTES);
+        const int k0 = kt * TBK;
+        if (!p.a_mn_major) {
+          tma_load_2d(a_dst, &mapA, k0, m0, full_bar(s));
+        } else {
+#pragma unroll
+          for (int j = 0; j < TBM / 64; ++j) tma_load_2d(a_dst + j * (TBK * 128), &mapA, m0 + 64 * j, k0, full_bar(s));
+        }
+        if (!p.b_mn_major) {
+          tma_load_2d(b_dst, &mapB, k0, n0, full_bar(s));
+        } else {
+#pragma unroll
+          for (int j = 0; j < TBN / 64; ++j) tma_load_2d(b_dst + j * (TBK * 128), &mapB, n0 + 64 * j, k0, full_bar(s));
+        }
+        armed = kt + 1;
+      }
+      if (*abort_flag)
+        for (int kt = max(0, armed - STAGES); kt < armed; ++kt) mbar_wait(full_bar(kt % STAGES), (kt / STAGES) & 1);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // kind::f16 descriptor: fp32 accumulate (bit 4), A/B format bf16 (=1) at bits 7 and 10, majorness, N, M
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+                             ((uint32_t)(TBN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
+      // K-major: 8-row groups 1024 B apart, one MMA (K=16) advances 32 B inside the 128-byte row.
+      // MN-major: blocks of 64 elements TBK*128 B apart (LBO), 8-k-row groups 1024 B apart (SBO); K=16 spans two groups.
+      const uint32_t a_lbo = p.a_mn_major ? TBK * 128 : 16, b_lbo = p.b_mn_major ? TBK * 128 : 16;
+      const uint32_t a_kstep = p.a_mn_major ? 2048 : 32, b_kstep = p.b_mn_major ? 2048 : 32;
+      for (int kt = 0; kt < num_kt; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t ph = (kt / STAGES) & 1;
+        if (!mbar_wait(full_bar(s), ph)) { atomicOr(&g_bf16_status, 2u); *abort_flag = 1; break; }
+        if (*abort_flag) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_s = tiles + s * STAGE_BYTES, b_s = a_s + TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < TBK / 16; ++k) {
+          const uint64_t da = make_desc(a_s + k * a_kstep, a_lbo, 1024, 2), db = make_desc(b_s + k * b_kstep, b_lbo, 1024, 2);
+          mma_bf16(tmem_acc, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(empty_bar(s));
+      }
+      umma_commit(accum_bar);
+    }
+  } else {
+    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0));
+    if (!acc_ok && lane == 0) { atomicOr(&g_bf16_status, 8u); *abort_flag = 1; }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const bool aborted = __any_sync(0xffffffffu, *abort_flag != 0);
+    if (acc_ok && !aborted) {
+      const int lane_base = (warp & 3) * 32;
+      const int m = m0 + lane_base + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TBN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_acc + ((uint32_t)lane_base << 16) + (uint32_t)c0, r);
+        if (m < p.M) {
+          const int nb = n0 + c0;
+          if (p.out_bf16) {
+            uint16_t* crow = static_cast<uint16_t*>(p.C) + (int64_t)m * p.ldc + nb;
+            const uint16_t* rrow = p.R ? static_cast<const uint16_t*>(p.R) + (int64_t)m * p.ldc + nb : nullptr;
+            const bool vec = (nb + 32 <= p.N) && ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                             (!p.R || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+            if (vec) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+                if (rrow) {
+                  uint4 q = *reinterpret_cast<const uint4*>(rrow + j);
+                  const uint32_t qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) { v[2 * e] += __uint_as_float(qq[e] << 16); v[2 * e + 1] += __uint_as_float(qq[e] & 0xffff0000u); }
+                }
+                uint4 o;
+                o.x = (uint32_t)float_to_bf16_bits(v[0]) | ((uint32_t)float_to_bf16_bits(v[1]) << 16);
+                o.y = (uint32_t)float_to_bf16_bits(v[2]) | ((uint32_t)float_to_bf16_bits(v[3]) << 16);
+                o.z = (uint32_t)float_to_bf16_bits(v[4]) | ((uint32_t)float_to_bf16_bits(v[5]) << 16);
+                o.w = (uint32_t)float_to_bf16_bits(v[6]) | ((uint32_t)float_to_bf16_bits(v[7]) << 16);
+                *reinterpret_cast<uint4*>(crow + j) = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < p.N) crow[j] = float_to_bf16_bits(__uint_as_float(r[j]) + (rrow ? bf16_bits_to_float(rrow[j]) : 0.0f));
+            }
+          } else {
+            float* crow = static_cast<float*>(p.C) + (int64_t)m * p.ldc + nb;
+            const float* rrow = p.R ? static_cast<const float*>(p.R) + (int64_t)m * p.ldc + nb : nullptr;
+            const bool vec = (nb + 32 <= p.N) && ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                             (!p.R || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+            if (vec) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                if (rrow) {
+                  float4 q = *reinterpret_cast<const float4*>(rrow + j);
+                  v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+                }
+                *reinterpret_cast<float4*>(crow + j) = v;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < p.N) crow[j] = __uint_as_float(r[j]) + (rrow ? rrow[j] : 0.0f);
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+struct MapKey {
+  const void* base; int64_t inner, outer, ld; int bi, bo;
+  bool operator<(const MapKey& o) const { return std::tie(base, inner, outer, ld, bi, bo) < std::tie(o.base, o.inner, o.outer, o.ld, o.bi, o.bo); }
+};
+static std::map<MapKey, CUtensorMap> g_cache;
+
+static pmb_status make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_inner, int box_outer) {
+  MapKey key{base, inner, outer, ld, box_inner, box_outer};
+  auto it = g_cache.find(key);
+  if (it == g_cache.end()) {
+    if (g_cache.size() > 8192) g_cache.clear();
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return fail(PMB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(PMB_ERR_CUDA, "cuTensorMapEncodeTiled (bf16) failed with code %d", (int)r);
+    it = g_cache.emplace(key, m).first;
+  }
+  *map = it->second;
+  return PMB_OK;
+}
+
+}  // namespace hb
+
+// Row pitches must be multiples of 8 elements (16 bytes) and the bases 16-byte aligned (TMA rules).
+pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
+                     const void* B, int64_t ldb, void* C, int64_t ldc, const void* R, int out_bf16) {
+  using namespace hb;
+  if (M <= 0 || N <= 0 || K <= 0) return fail(PMB_ERR_SHAPE, "gemm_bf16: non-positive dimension");
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
+    return fail(PMB_ERR_SHAPE, "gemm_bf16: operands need 16-byte aligned bases and row pitches that are multiples of 8 elements");
+  if (cdiv(M, TBM) > 65535) return fail(PMB_ERR_SHAPE, "gemm_bf16: M too large");
+  static bool attr_set = false;
+  if (!attr_set) {
+    PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr_set = true;
+  }
+  CUtensorMap mapA, mapB;
+  if (!ta) PMB_TRY(make_map(&mapA, A, K, M, lda, TBK, TBM)); else PMB_TRY(make_map(&mapA, A, M, K, lda, 64, TBK));
+  if (tb) PMB_TRY(make_map(&mapB, B, K, N, ldb, TBK, TBN)); else PMB_TRY(make_map(&mapB, B, N, K, ldb, 64, TBK));
+  Params p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.a_mn_major = ta ? 1 : 0; p.b_mn_major = tb ? 0 : 1;
+  p.C = C; p.ldc = ldc; p.R = R; p.out_bf16 = out_bf16;
+  dim3 grid((unsigned)cdiv(N, TBN), (unsigned)cdiv(M, TBM));
+  ProfScope prof(st, "gemm_bf16", 2.0 * M * N * K, 2.0 * ((double)M * K + (double)K * N) + (out_bf16 ? 2.0 : 4.0) * M * N * (R ? 2 : 1));
+  gemm_bf16_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, p);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
+}  // namespace pmb
+
+extern "C" pmb_status pmb_gemm_bf16(void* stream, int32_t trans_a, int32_t trans_b, int64_t M, int64_t N, int64_t K,
+                                    const uint16_t* d_A, int64_t lda, const uint16_t* d_B, int64_t ldb,
+                                    void* d_C, int64_t ldc, const void* d_R, int32_t out_bf16) {
+  using namespace pmb;
+  if (!d_A || !d_B || !d_C) return fail(PMB_ERR_ARG, "gemm_bf16: NULL operand");
+  if (lda < (trans_a ? M : K) || ldb < (trans_b ? K : N) || ldc < N) return fail(PMB_ERR_SHAPE, "gemm_bf16: leading dimension smaller than the row length");
+  return gemm_bf16(static_cast<cudaStream_t>(stream), trans_a != 0, trans_b != 0, M, N, K, d_A, lda, d_B, ldb, d_C, ldc, d_R, out_bf16 != 0);
+}

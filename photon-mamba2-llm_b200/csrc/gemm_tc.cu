@@ -16,6 +16,7 @@
 #include <cuda.h>
 #include <cstdlib>
 #include <map>
+#include <string>
 #include <tuple>
 #include "common.cuh"
 #include "kernels.h"
@@ -387,7 +388,14 @@ pmb_status gemm_tc(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_
   static const int write_hi = [] { const char* e = getenv("PMB_TC_WRITE_HI"); return (e && e[0] == '1') ? 1 : 0; }();
   p.write_hi = write_hi;
   dim3 grid((unsigned)cdiv(N, TBN), (unsigned)cdiv(M, TBM));
-  ProfScope prof(st, "gemm_3xtf32", 2.0 * M * N * K, 4.0 * ((double)M * K + (double)K * N + (double)M * N * (R ? 2 : 1)));
+  static std::map<std::string, int> names;   // interned per-shape scope names (profiling runs only)
+  const char* pname = "gemm_3xtf32";
+  if (g_prof_on && getenv("PMB_PROFILE_SHAPES")) {
+    char buf[96];
+    snprintf(buf, sizeof(buf), "gemm_3xtf32 %c%c %lldx%lldx%lld", ta ? 'T' : 'N', tb ? 'T' : 'N', (long long)M, (long long)N, (long long)K);
+    pname = names.emplace(buf, 0).first->first.c_str();
+  }
+  ProfScope prof(st, pname, 2.0 * M * N * K, 4.0 * ((double)M * K + (double)K * N + (double)M * N * (R ? 2 : 1)));
   gemm_3xtf32_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, p);
   PMB_LAUNCHED();
   return PMB_OK;

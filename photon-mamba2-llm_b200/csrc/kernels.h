@@ -74,11 +74,25 @@ pmb_status gemm(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K
                 const float* B, int64_t ldb, float* C, int64_t ldc, const float* R, int engine);
 pmb_status read_clear_device_status(unsigned int* word);
 
-// ---- block.cu
-size_t block_ws_bytes(const Dims& d);
-pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const float* x, const float* residual,
-                     float* out, void* ws, size_t ws_bytes);
-pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const float* x, const float* dout,
-                     const float* dx_accum, float* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes);
+// ---- gemm_bf16.cu: bf16 operands, fp32 accumulation; C and R are fp32 or bf16 (out_bf16)
+pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
+                     const void* B, int64_t ldb, void* C, int64_t ldc, const void* R, int out_bf16);
+pmb_status read_clear_device_status_bf16(unsigned int* word);
+
+// ---- block.cu.  w16 != NULL selects bf16 storage: x / residual / out / dout / dx are bf16 and the two
+// projections use the bf16 weight copies; NULL = fp32 everywhere.
+struct Weights16 { const uint16_t* in_proj; const uint16_t* out_proj; };
+size_t block_ws_bytes(const Dims& d, bool bf16 = false);
+pmb_status cast_f32_bf16(cudaStream_t st, const float* src, uint16_t* dst, int64_t n);
+pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* residual,
+                     void* out, void* ws, size_t ws_bytes, const Weights16* w16);
+pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* dout,
+                     const void* dx_accum, void* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes, const Weights16* w16);
+
+pmb_status stack_fwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_block_params* layers, const Weights16* w16,
+                     void* saved, void* ws, size_t ws_bytes);
+pmb_status stack_bwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_block_params* layers, const Weights16* w16,
+                     const pmb_block_grads* grads, const void* saved, void* dhidden, void* ws, size_t ws_bytes,
+                     pmb_layer_callback on_layer_done, void* user);
 
 }  // namespace pmb

@@ -25,6 +25,30 @@ __global__ void embedding_fwd_kernel(const float* __restrict__ table, const int6
   *reinterpret_cast<float4*>(out + r * D + c) = *reinterpret_cast<const float4*>(table + id * D + c);
 }
 
+// bf16-storage variants: rows are gathered from / scattered out of bf16 activations
+__global__ void embedding_fwd_bf16_kernel(const uint16_t* __restrict__ table16, const int64_t* __restrict__ ids, uint16_t* __restrict__ out,
+                                          int64_t rows, int D, int V, unsigned int* __restrict__ bad) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t n = rows * (D / 8);
+  if (i >= n) return;
+  int64_t r = i / (D / 8);
+  int c = (int)(i % (D / 8)) * 8;
+  int64_t id = ids[r];
+  if (id < 0 || id >= V) { if (c == 0) atomicOr(bad, 1u); id = 0; }
+  *reinterpret_cast<uint4*>(out + r * D + c) = *reinterpret_cast<const uint4*>(table16 + id * D + c);
+}
+
+__global__ void embedding_bwd_bf16_kernel(float* __restrict__ dtable, const int64_t* __restrict__ ids, const uint16_t* __restrict__ dh,
+                                          int64_t rows, int D, int V) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * D) return;
+  int64_t r = i / D;
+  int c = (int)(i % D);
+  int64_t id = ids[r];
+  if (id < 0 || id >= V) return;
+  atomicAdd(dtable + id * D + c, __uint_as_float((uint32_t)dh[i] << 16));
+}
+
 __global__ void embedding_bwd_kernel(float* __restrict__ dtable, const int64_t* __restrict__ ids, const float* __restrict__ dh,
                                      int64_t rows, int D, int V) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -107,6 +131,10 @@ struct pmb_lm {
   int64_t* targets = nullptr;
   void* ws = nullptr;
   size_t ws_bytes = 0;
+  int bf16 = 0;               // storage dtype of activations / GEMM operands
+  uint16_t* params16 = nullptr;   // bf16 copy of the flat parameter buffer, refreshed every step
+  uint16_t* dlogits16 = nullptr;  // (tile_rows, Vp)
+  std::vector<Weights16> lw16;
   int64_t act_bytes = 0;
   std::vector<pmb_block_params> lp;
   std::vector<pmb_block_grads> lg;
@@ -126,14 +154,21 @@ static int64_t tensor_elems(const Dims& d, int which) {
 
 extern "C" pmb_status pmb_lm_create(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t vocab, int32_t batch,
                                     int32_t seqlen, pmb_lm** out) {
+  return pmb_lm_create_dtype(cfg, n_layers, vocab, batch, seqlen, 0, out);
+}
+
+extern "C" pmb_status pmb_lm_create_dtype(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t vocab, int32_t batch,
+                                          int32_t seqlen, int32_t bf16_storage, pmb_lm** out) {
   if (!out) return fail(PMB_ERR_ARG, "lm_create: out is NULL");
   *out = nullptr;
   Dims d;
   PMB_TRY(make_dims(cfg, batch, seqlen, &d));
+  if (bf16_storage && ((d.D % 8) || (d.J % 8) || (d.I % 8)))
+    return fail(PMB_ERR_SHAPE, "lm_create: bf16 storage needs d_model, d_inner and in_proj_dim to be multiples of 8");
   if (n_layers <= 0 || vocab <= 0) return fail(PMB_ERR_SHAPE, "lm_create: n_layers and vocab must be positive");
   if (d.D % 4 != 0) return fail(PMB_ERR_SHAPE, "lm_create: d_model must be a multiple of 4");
   pmb_lm* lm = new pmb_lm();
-  lm->cfg = *cfg; lm->d = d; lm->L = n_layers; lm->V = vocab;
+  lm->cfg = *cfg; lm->d = d; lm->L = n_layers; lm->V = vocab; lm->bf16 = bf16_storage ? 1 : 0;
   lm->Vp = (int)align_up((size_t)vocab, 64);
   lm->tile_rows = (int)(d.M < LM_TILE_ROWS ? d.M : LM_TILE_ROWS);
   int64_t o = 0;
@@ -142,8 +177,8 @@ extern "C" pmb_status pmb_lm_create(const pmb_mamba2_config* cfg, int32_t n_laye
   for (int l = 0; l < n_layers; ++l)
     for (int w = 0; w < 8; ++w) lm->off.push_back(place(tensor_elems(d, w)));
   lm->n_params = o;
-  lm->ws_bytes = block_ws_bytes(d);
-  size_t slot = (size_t)d.M * d.D * sizeof(float);
+  lm->ws_bytes = block_ws_bytes(d, lm->bf16 != 0);
+  size_t slot = (size_t)d.M * d.D * (lm->bf16 ? 2 : 4);
   auto alloc = [&](void** p, size_t bytes) -> bool { return cudaMalloc(p, bytes) == cudaSuccess; };
   bool ok = true;
   ok = ok && alloc((void**)&lm->params, (size_t)o * 4);
@@ -157,6 +192,10 @@ extern "C" pmb_status pmb_lm_create(const pmb_mamba2_config* cfg, int32_t n_laye
   ok = ok && alloc((void**)&lm->ids, (size_t)d.M * 8);
   ok = ok && alloc((void**)&lm->targets, (size_t)d.M * 8);
   ok = ok && alloc(&lm->ws, lm->ws_bytes);
+  if (lm->bf16) {
+    ok = ok && alloc((void**)&lm->params16, (size_t)o * 2);
+    ok = ok && alloc((void**)&lm->dlogits16, (size_t)lm->tile_rows * lm->Vp * 2);
+  }
   if (!ok) {
     pmb_status s = fail(PMB_ERR_CUDA, "lm_create: cudaMalloc failed: %s", cudaGetErrorString(cudaGetLastError()));
     pmb_lm_destroy(lm);
@@ -165,13 +204,14 @@ extern "C" pmb_status pmb_lm_create(const pmb_mamba2_config* cfg, int32_t n_laye
   cudaMemset(lm->params, 0, (size_t)o * 4);
   cudaMemset(lm->grads, 0, (size_t)o * 4);
   cudaMemset(lm->bad, 0, 256);
-  lm->act_bytes = (int64_t)(slot * (n_layers + 1) + slot + (size_t)lm->tile_rows * lm->Vp * 4 + (size_t)d.M * 4 + lm->ws_bytes);
-  lm->lp.resize(n_layers); lm->lg.resize(n_layers);
+  lm->act_bytes = (int64_t)(slot * (n_layers + 1) + slot + (size_t)lm->tile_rows * lm->Vp * (lm->bf16 ? 6 : 4) + (size_t)d.M * 4 + lm->ws_bytes);
+  lm->lp.resize(n_layers); lm->lg.resize(n_layers); lm->lw16.resize(n_layers);
   for (int l = 0; l < n_layers; ++l) {
     const int64_t* f = &lm->off[1 + 8 * l];
     float* P = lm->params; float* G = lm->grads;
     lm->lp[l] = pmb_block_params{P + f[0], P + f[1], P + f[2], P + f[3], P + f[4], P + f[5], P + f[6], P + f[7]};
     lm->lg[l] = pmb_block_grads{G + f[0], G + f[1], G + f[2], G + f[3], G + f[4], G + f[5], G + f[6], G + f[7]};
+    lm->lw16[l] = Weights16{lm->params16 ? lm->params16 + f[0] : nullptr, lm->params16 ? lm->params16 + f[7] : nullptr};
   }
   *out = lm;
   return PMB_OK;
@@ -180,7 +220,7 @@ extern "C" pmb_status pmb_lm_create(const pmb_mamba2_config* cfg, int32_t n_laye
 extern "C" void pmb_lm_destroy(pmb_lm* lm) {
   if (!lm) return;
   cudaFree(lm->params); cudaFree(lm->grads); cudaFree(lm->saved); cudaFree(lm->dhidden); cudaFree(lm->logits);
-  cudaFree(lm->row_loss); cudaFree(lm->loss); cudaFree(lm->bad); cudaFree(lm->ids); cudaFree(lm->targets); cudaFree(lm->ws);
+  cudaFree(lm->row_loss); cudaFree(lm->loss); cudaFree(lm->bad); cudaFree(lm->ids); cudaFree(lm->targets); cudaFree(lm->ws); cudaFree(lm->params16); cudaFree(lm->dlogits16);
   delete lm;
 }
 
@@ -206,27 +246,45 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
   float* table = lm->params + lm->off[0];
   float* dtable = lm->grads + lm->off[0];
   size_t slot = (size_t)M * D;
-  embedding_fwd_kernel<<<(unsigned)cdiv(M * (D / 4), 256), 256, 0, st>>>(table, d_ids, lm->saved, M, D, V, lm->bad);
+  const bool h16 = lm->bf16 != 0;
+  const size_t esz = h16 ? 2 : 4;
+  const uint16_t* table16 = h16 ? lm->params16 + lm->off[0] : nullptr;
+  if (h16) {
+    // the fp32 masters may have been updated by the optimizer since the last step
+    PMB_TRY(cast_f32_bf16(st, lm->params, lm->params16, lm->n_params));
+    embedding_fwd_bf16_kernel<<<(unsigned)cdiv(M * (D / 8), 256), 256, 0, st>>>(table16, d_ids, static_cast<uint16_t*>((void*)lm->saved), M, D, V, lm->bad);
+  } else {
+    embedding_fwd_kernel<<<(unsigned)cdiv(M * (D / 4), 256), 256, 0, st>>>(table, d_ids, lm->saved, M, D, V, lm->bad);
+  }
   PMB_LAUNCHED();
-  PMB_TRY(pmb_stack_fwd_ckpt(stream, &lm->cfg, lm->L, lm->lp.data(), d.B, d.T, lm->saved, lm->ws, lm->ws_bytes));
-  const float* hidden = lm->saved + (size_t)lm->L * slot;
+  PMB_TRY(stack_fwd(st, d, lm->L, lm->lp.data(), h16 ? lm->lw16.data() : nullptr, lm->saved, lm->ws, lm->ws_bytes));
+  const char* hidden = reinterpret_cast<const char*>(lm->saved) + (size_t)lm->L * slot * esz;
+  char* dhid = reinterpret_cast<char*>(lm->dhidden);
   for (int64_t r0 = 0; r0 < M; r0 += lm->tile_rows) {
     int64_t rows = M - r0 < lm->tile_rows ? M - r0 : lm->tile_rows;
-    const float* hrows = hidden + r0 * D;
-    // logits = hidden E^T   (photon/embedding.rs:54-60)
-    PMB_TRY(gemm(st, 0, 1, rows, V, D, hrows, D, table, D, lm->logits, Vp, nullptr, 0));
+    const void* hrows = hidden + (size_t)r0 * D * esz;
+    // logits = hidden E^T   (photon/embedding.rs:54-60), kept in fp32 for the softmax
+    if (h16) PMB_TRY(gemm_bf16(st, 0, 1, rows, V, D, hrows, D, table16, D, lm->logits, Vp, nullptr, 0));
+    else PMB_TRY(gemm(st, 0, 1, rows, V, D, static_cast<const float*>(hrows), D, table, D, lm->logits, Vp, nullptr, 0));
     { ProfScope prof(st, "cross_entropy", 0.0, 4.0 * rows * 3.0 * V);
     cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>(lm->logits, Vp, V, d_targets + r0, lm->row_loss + r0, 1.0f / (float)M);
     PMB_LAUNCHED(); }
     // dhidden = dlogits E ;  dE (+)= dlogits^T hidden
-    PMB_TRY(gemm(st, 0, 0, rows, D, V, lm->logits, Vp, table, D, lm->dhidden + r0 * D, D, nullptr, 0));
-    PMB_TRY(gemm(st, 1, 0, V, D, rows, lm->logits, Vp, hrows, D, dtable, D, r0 == 0 ? nullptr : dtable, 0));
+    if (h16) {
+      PMB_TRY(cast_f32_bf16(st, lm->logits, lm->dlogits16, rows * Vp));
+      PMB_TRY(gemm_bf16(st, 0, 0, rows, D, V, lm->dlogits16, Vp, table16, D, dhid + (size_t)r0 * D * 2, D, nullptr, 1));
+      PMB_TRY(gemm_bf16(st, 1, 0, V, D, rows, lm->dlogits16, Vp, hrows, D, dtable, D, r0 == 0 ? nullptr : dtable, 0));
+    } else {
+      PMB_TRY(gemm(st, 0, 0, rows, D, V, lm->logits, Vp, table, D, lm->dhidden + r0 * D, D, nullptr, 0));
+      PMB_TRY(gemm(st, 1, 0, V, D, rows, lm->logits, Vp, static_cast<const float*>(hrows), D, dtable, D, r0 == 0 ? nullptr : dtable, 0));
+    }
   }
   mean_kernel<<<1, 256, 0, st>>>(lm->row_loss, M, lm->loss);
   PMB_LAUNCHED();
-  PMB_TRY(pmb_stack_bwd(stream, &lm->cfg, lm->L, lm->lp.data(), lm->lg.data(), d.B, d.T, lm->saved, lm->dhidden, lm->ws,
-                        lm->ws_bytes, on_layer_done, user));
-  embedding_bwd_kernel<<<(unsigned)cdiv(M * D, 256), 256, 0, st>>>(dtable, d_ids, lm->dhidden, M, D, V);
+  PMB_TRY(stack_bwd(st, d, lm->L, lm->lp.data(), h16 ? lm->lw16.data() : nullptr, lm->lg.data(), lm->saved, lm->dhidden, lm->ws,
+                    lm->ws_bytes, on_layer_done, user));
+  if (h16) embedding_bwd_bf16_kernel<<<(unsigned)cdiv(M * D, 256), 256, 0, st>>>(dtable, d_ids, reinterpret_cast<const uint16_t*>(lm->dhidden), M, D, V);
+  else embedding_bwd_kernel<<<(unsigned)cdiv(M * D, 256), 256, 0, st>>>(dtable, d_ids, lm->dhidden, M, D, V);
   PMB_LAUNCHED();
   if (on_layer_done) on_layer_done(-1, user);
   return PMB_OK;

@@ -471,7 +471,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, int nsplit,
 }
 
 // above this many floats of per-head partials the per-group contractions stay on the FMA engine
-constexpr size_t TC_DG_PARTIAL_CAP = (size_t)1 << 28;
+constexpr size_t TC_DG_PARTIAL_CAP = (size_t)1 << 29;
 
 static int pick_nsplit(int batches, int tiles, int hpg) {
   int want = (int)cdiv(2 * 148, (int64_t)batches * tiles);

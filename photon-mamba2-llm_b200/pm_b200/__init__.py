@@ -58,6 +58,11 @@ def _load():
         "pmb_profile_start": (None, []),
         "pmb_profile_stop": (i32, [C.c_char_p, sz]),
         "pmb_gemm_f32": (i32, [vp, i32, i32, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp, i32]),
+        "pmb_gemm_bf16": (i32, [vp, i32, i32, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp, i32]),
+        "pmb_cast_f32_to_bf16": (i32, [vp, vp, vp, i64]),
+        "pmb_mamba2_block_workspace_bytes_bf16": (sz, [cfgp, i32, i32]),
+        "pmb_mamba2_block_fwd_bf16": (i32, [vp, cfgp, C.POINTER(_Params), vp, vp, i32, i32, vp, vp, vp, vp, sz]),
+        "pmb_mamba2_block_bwd_bf16": (i32, [vp, cfgp, C.POINTER(_Params), vp, vp, i32, i32, vp, vp, vp, vp, C.POINTER(_Params), vp, sz]),
         "pmb_conv_silu_dt_fwd": (i32, [vp, cfgp, i32, i32, vp, vp, vp, vp, vp, vp]),
         "pmb_conv_bwd_workspace_bytes": (sz, [cfgp, i32, i32]),
         "pmb_conv_silu_bwd": (i32, [vp, cfgp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, sz]),
@@ -77,6 +82,7 @@ def _load():
         "pmb_stack_fwd_ckpt": (i32, [vp, cfgp, i32, C.POINTER(_Params), i32, i32, vp, vp, sz]),
         "pmb_stack_bwd": (i32, [vp, cfgp, i32, C.POINTER(_Params), C.POINTER(_Params), i32, i32, vp, vp, vp, sz, LAYER_CALLBACK, vp]),
         "pmb_lm_create": (i32, [cfgp, i32, i32, i32, i32, C.POINTER(vp)]),
+        "pmb_lm_create_dtype": (i32, [cfgp, i32, i32, i32, i32, i32, C.POINTER(vp)]),
         "pmb_lm_destroy": (None, [vp]),
         "pmb_lm_param_count": (i64, [vp]),
         "pmb_lm_param_offset": (i64, [vp, i32, i32]),
@@ -192,6 +198,31 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, trans_a=False, trans_b=False, re
     return out
 
 
+def matmul_bf16(a: torch.Tensor, b: torch.Tensor, *, trans_a=False, trans_b=False, residual=None, out_dtype=torch.float32):
+    """bf16 x bf16 -> fp32-accumulated product; result (and residual) fp32 or bf16."""
+    for t, n in ((a, "a"), (b, "b")):
+        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()):
+            raise PmbError(2, f"{n}: expected a contiguous bfloat16 CUDA tensor, got {t.dtype}")
+    M, K = (a.shape[1], a.shape[0]) if trans_a else a.shape
+    K2, N = (b.shape[1], b.shape[0]) if trans_b else b.shape
+    if K != K2:
+        raise PmbError(1, f"matmul_bf16: inner dimensions differ ({K} vs {K2})")
+    out = torch.empty(M, N, device=a.device, dtype=out_dtype)
+    if residual is not None and residual.dtype != out_dtype:
+        raise PmbError(2, "matmul_bf16: residual dtype must equal the output dtype")
+    _check(lib.pmb_gemm_bf16(_stream(), int(trans_a), int(trans_b), M, N, K, a.data_ptr(), a.stride(0), b.data_ptr(),
+                             b.stride(0), out.data_ptr(), out.stride(0), _ptr(residual), int(out_dtype == torch.bfloat16)))
+    return out
+
+
+def to_bf16(t: torch.Tensor) -> torch.Tensor:
+    """Ops::to_dtype(F32 -> BF16) on the device."""
+    _dev(t, "t")
+    out = torch.empty(t.shape, device=t.device, dtype=torch.bfloat16)
+    _check(lib.pmb_cast_f32_to_bf16(_stream(), t.data_ptr(), out.data_ptr(), t.numel()))
+    return out
+
+
 def conv_silu_dt_fwd(cfg: Mamba2Config, xzd, conv_w, conv_b, dt_bias):
     B, T, J = xzd.shape
     act = torch.empty(B, T, cfg.xbc_dim, device=xzd.device, dtype=torch.float32)
@@ -295,16 +326,35 @@ def gated_rmsnorm_bwd_static(dout, y, z, w, rstd):
 class Mamba2Block:
     """One block: parameters are a dict of fp32 CUDA tensors in `PARAM_ORDER`."""
 
-    def __init__(self, config: Mamba2Config, params: dict):
+    def __init__(self, config: Mamba2Config, params: dict, compute_dtype=torch.float32):
+        """`compute_dtype` mirrors the reference's ambient dtype (`x.dtype()`, block.rs:137): float32, or bfloat16
+        for bf16 storage with fp32 islands.  Parameters are always fp32."""
         self.config = config
         self.params = {k: _dev(params[k], k) for k in PARAM_ORDER}
         for k, shp in config.param_shapes().items():
             if tuple(self.params[k].shape) != tuple(shp):
                 raise PmbError(1, f"{k}: shape {tuple(self.params[k].shape)} != {shp}")
+        if compute_dtype not in (torch.float32, torch.bfloat16):
+            raise PmbError(2, f"compute dtype {compute_dtype} is not supported")
+        self.bf16 = compute_dtype == torch.bfloat16
         self._ws = None
+        self.refresh_weights()
+
+    def refresh_weights(self):
+        """Re-derives the bf16 copies of the projection weights after the fp32 masters changed."""
+        if self.bf16:
+            self.w_in16 = to_bf16(self.params["in_proj_weight"])
+            self.w_out16 = to_bf16(self.params["out_proj_weight"])
+
+    def _io(self, t, name):
+        want = torch.bfloat16 if self.bf16 else torch.float32
+        if not (t.is_cuda and t.dtype == want and t.is_contiguous()):
+            raise PmbError(2, f"{name}: expected a contiguous {want} CUDA tensor, got {t.dtype}")
+        return t
 
     def _workspace(self, B, T, device):
-        n = lib.pmb_mamba2_block_workspace_bytes(C.byref(self.config.c()), B, T)
+        fn = lib.pmb_mamba2_block_workspace_bytes_bf16 if self.bf16 else lib.pmb_mamba2_block_workspace_bytes
+        n = fn(C.byref(self.config.c()), B, T)
         if n == 0:
             raise PmbError(1, lib.pmb_last_error().decode())
         if self._ws is None or self._ws.numel() < n:
@@ -316,8 +366,14 @@ class Mamba2Block:
         ws = self._workspace(B, T, x.device)
         out = torch.empty_like(x)
         ps = _params_struct(self.params)
-        _check(lib.pmb_mamba2_block_fwd(_stream(), C.byref(self.config.c()), C.byref(ps), B, T, _dev(x, "x").data_ptr(),
-                                        _ptr(residual), out.data_ptr(), ws.data_ptr(), ws.numel()))
+        self._io(x, "x")
+        if self.bf16:
+            _check(lib.pmb_mamba2_block_fwd_bf16(_stream(), C.byref(self.config.c()), C.byref(ps), self.w_in16.data_ptr(),
+                                                 self.w_out16.data_ptr(), B, T, x.data_ptr(), _ptr(residual), out.data_ptr(),
+                                                 ws.data_ptr(), ws.numel()))
+        else:
+            _check(lib.pmb_mamba2_block_fwd(_stream(), C.byref(self.config.c()), C.byref(ps), B, T, x.data_ptr(),
+                                            _ptr(residual), out.data_ptr(), ws.data_ptr(), ws.numel()))
         return out
 
     def backward(self, x, dout, dx_accum=None):
@@ -327,9 +383,15 @@ class Mamba2Block:
         dx = torch.empty_like(x)
         grads = {k: torch.empty_like(v) for k, v in self.params.items()}
         ps, gs = _params_struct(self.params), _params_struct(grads)
-        _check(lib.pmb_mamba2_block_bwd(_stream(), C.byref(self.config.c()), C.byref(ps), B, T, _dev(x, "x").data_ptr(),
-                                        _dev(dout, "dout").data_ptr(), _ptr(dx_accum), dx.data_ptr(), C.byref(gs),
-                                        ws.data_ptr(), ws.numel()))
+        self._io(x, "x"); self._io(dout, "dout")
+        if self.bf16:
+            _check(lib.pmb_mamba2_block_bwd_bf16(_stream(), C.byref(self.config.c()), C.byref(ps), self.w_in16.data_ptr(),
+                                                 self.w_out16.data_ptr(), B, T, x.data_ptr(), dout.data_ptr(), _ptr(dx_accum),
+                                                 dx.data_ptr(), C.byref(gs), ws.data_ptr(), ws.numel()))
+        else:
+            _check(lib.pmb_mamba2_block_bwd(_stream(), C.byref(self.config.c()), C.byref(ps), B, T, x.data_ptr(),
+                                            dout.data_ptr(), _ptr(dx_accum), dx.data_ptr(), C.byref(gs),
+                                            ws.data_ptr(), ws.numel()))
         return dx, grads
 
     def zero_state(self, batch, device="cuda"):
@@ -390,10 +452,13 @@ class FlatMamba:
     """Flat LM (tied embedding -> stack -> tied head -> mean CE).  Owns a library model handle whose flat
     parameter/gradient buffers are exposed as torch views."""
 
-    def __init__(self, config: Mamba2Config, n_layers: int, vocab: int, batch: int, seqlen: int):
+    def __init__(self, config: Mamba2Config, n_layers: int, vocab: int, batch: int, seqlen: int, compute_dtype=torch.float32):
         self.config, self.n_layers, self.vocab, self.batch, self.seqlen = config, n_layers, vocab, batch, seqlen
+        if compute_dtype not in (torch.float32, torch.bfloat16):
+            raise PmbError(2, f"compute dtype {compute_dtype} is not supported")
         h = C.c_void_p()
-        _check(lib.pmb_lm_create(C.byref(config.c()), n_layers, vocab, batch, seqlen, C.byref(h)))
+        _check(lib.pmb_lm_create_dtype(C.byref(config.c()), n_layers, vocab, batch, seqlen,
+                                       int(compute_dtype == torch.bfloat16), C.byref(h)))
         self._h = h
         n = lib.pmb_lm_param_count(h)
         self.flat_params = _as_tensor(lib.pmb_lm_params(h), n)

@@ -1,0 +1,95 @@
+"""bf16-storage configurations: bf16 GEMM and the bf16 block against the oracle (bound 2e-2, as stated for
+bf16 storage; the reference's own bf16 tests hold 1e-2 forward / 5e-2 gradients,
+crates/pm-candle/tests/bf16_mixed_precision_cuda.rs:58,72)."""
+import pytest
+import torch
+
+from oracle import mamba2_oracle as orc
+from util import assert_close, block_params, cuda_params, randn, rel_err, to_pm_cfg
+
+pytestmark = pytest.mark.gpu
+BF16_TOL = 2e-2
+
+
+@pytest.fixture(scope="module")
+def pm():
+    import __graft_entry__ as ge
+    ge.build()
+    import pm_b200
+    assert torch.cuda.is_available()
+    return pm_b200
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (304, 200, 104), (128, 552, 128), (64, 40, 72), (8, 8, 8), (2048, 768, 1536)])
+@pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0), (1, 1)])
+def test_gemm_bf16(pm, M, N, K, ta, tb):
+    a = randn((K, M) if ta else (M, K), 1).bfloat16()
+    b = randn((N, K) if tb else (K, N), 2).bfloat16()
+    ref = (a.T if ta else a).double() @ (b.T if tb else b).double()
+    out = pm.matmul_bf16(a.cuda(), b.cuda(), trans_a=bool(ta), trans_b=bool(tb))
+    assert rel_err(out, ref) < 1e-5          # products of bf16 values are exact in fp32; only the summation order differs
+    r = randn((M, N), 3).bfloat16()
+    out16 = pm.matmul_bf16(a.cuda(), b.cuda(), trans_a=bool(ta), trans_b=bool(tb), residual=r.cuda(), out_dtype=torch.bfloat16)
+    assert rel_err(out16.float(), ref + r.double()) < 6e-3   # one bf16 rounding of the result
+    assert pm.device_status() == 0
+
+
+def test_cast_matches_torch(pm):
+    x = randn((1000, 37), 5)
+    assert torch.equal(pm.to_bf16(x.cuda()).cpu(), x.bfloat16())
+
+
+def _oracle_block_grads(cfg, p, x, cot):
+    pr = {k: v.clone().requires_grad_(True) for k, v in p.items()}
+    xr = x.clone().requires_grad_(True)
+    out = orc.block_forward(pr, cfg, xr)
+    (out.float() * cot.float()).sum().backward()
+    return out.detach().float(), xr.grad.float(), {k: v.grad for k, v in pr.items()}
+
+
+@pytest.mark.parametrize("D,N,P,H,Q,B,T", [(128, 16, 32, 8, 64, 2, 128), (768, 64, 64, 24, 256, 1, 512)])
+def test_block_bf16_storage_vs_oracle(pm, D, N, P, H, Q, B, T):
+    cfg = orc.Mamba2Config(d_model=D, d_state=N, d_head=P, n_heads=H, block_len=Q)
+    p = block_params(cfg, seed=3)
+    x, cot = randn((B, T, D), 21).bfloat16(), randn((B, T, D), 22).bfloat16()
+    # reference 1: the oracle run in the bf16 compute dtype (bf16 matmuls and roundings, fp32 islands)
+    out16, dx16, g16 = _oracle_block_grads(cfg, p, x, cot)
+    # reference 2: the fp32 oracle on the same (bf16-representable) inputs
+    out32, dx32, g32 = _oracle_block_grads(cfg, p, x.float(), cot.float())
+    blk = pm.Mamba2Block(to_pm_cfg(cfg), cuda_params(p), compute_dtype=torch.bfloat16)
+    out = blk.forward(x.cuda())
+    dx, grads = blk.backward(x.cuda(), cot.cuda())
+    assert out.dtype == torch.bfloat16 and dx.dtype == torch.bfloat16
+    for ref_out, ref_dx, ref_g, what in ((out16, dx16, g16, "bf16 oracle"), (out32, dx32, g32, "fp32 oracle")):
+        assert_close(out.float(), ref_out, tol=BF16_TOL, what=f"out vs {what}")
+        assert_close(dx.float(), ref_dx, tol=BF16_TOL, what=f"dx vs {what}")
+        for k in p:
+            assert_close(grads[k], ref_g[k], tol=BF16_TOL, what=f"d_{k} vs {what}")
+    assert pm.device_status() == 0
+    # residual and accumulation forms
+    out_r = blk.forward(x.cuda(), residual=x.cuda())
+    assert_close(out_r.float(), (out.float() + x.cuda().float()), tol=1e-2, what="residual")
+
+
+def test_lm_step_bf16_storage(pm):
+    # flat LM with bf16 activations / GEMM operands: loss and every gradient against the fp32 oracle
+    cfg = orc.Mamba2Config(d_model=64, d_state=8, d_head=8, n_heads=8, block_len=32)   # in_proj_dim 152: a multiple of 8
+    L, B, T, V = 2, 2, 64, 301
+    layers = [block_params(cfg, seed=20 + i) for i in range(L)]
+    embed = randn((V, 64), 9, 0.5)
+    ids, tg, _ = orc.lcg_batch(7, B, T, V)
+    er = embed.clone().requires_grad_(True)
+    ls = [{k: v.clone().requires_grad_(True) for k, v in p.items()} for p in layers]
+    loss_ref = orc.lm_loss(er, ls, cfg, ids, tg)
+    loss_ref.backward()
+    lm = pm.FlatMamba(to_pm_cfg(cfg), L, V, B, T, compute_dtype=torch.bfloat16)
+    lm.load(embed.cuda(), [cuda_params(p) for p in layers])
+    loss = lm.step_host(ids.pin_memory(), tg.pin_memory())
+    assert abs(loss - float(loss_ref)) < BF16_TOL * abs(float(loss_ref))
+    g_embed, g_layers = lm.grads()
+    assert_close(g_embed, er.grad, tol=BF16_TOL, what="d_embed")
+    for l in range(L):
+        for k in layers[l]:
+            assert_close(g_layers[l][k], ls[l][k].grad, tol=2 * BF16_TOL if k in ("a_log", "dt_bias") else BF16_TOL, what=f"layer {l} d_{k}")
+    assert pm.device_status() == 0
+    lm.close()
