@@ -323,7 +323,8 @@ def run_ours(args):
             "roofline": roof,
             "cpu_baseline": cpu,
             "loss": last_loss,
-            "activation_bytes": {"ours_per_gpu": lm.activation_bytes,
+            "activation_bytes": {"ours_per_gpu": lm.activation_bytes, "ours_detail": lm.activation_detail,
+                                 "reference_policy_stored_per_gpu": 2 * 4 * B * T * D * L,
                                  "reference_policy_estimate_per_gpu": reference_policy_activation_bytes(w),
                                  "torch_peak_allocated": torch.cuda.max_memory_allocated()},
             "kernels": breakdown,

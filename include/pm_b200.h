@@ -250,6 +250,8 @@ int64_t    pmb_lm_param_offset(const pmb_lm* lm, int32_t layer, int32_t which); 
 float*     pmb_lm_params(pmb_lm* lm);                            /* device pointer, pmb_lm_param_count() floats */
 float*     pmb_lm_grads(pmb_lm* lm);                             /* device pointer, same layout */
 int64_t    pmb_lm_activation_bytes(const pmb_lm* lm);            /* stored activations + transient workspace */
+/* h_out3 = { bytes stored for backward (block inputs), one block's transient workspace, LM-head transients } */
+void       pmb_lm_activation_detail(const pmb_lm* lm, int64_t* h_out3);
 /* One fwd+bwd step with inputs already on the device.  Loss is left in a device scalar (pmb_lm_loss_device). */
 pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t* d_ids, const int64_t* d_targets,
                               pmb_layer_callback on_layer_done, void* user);

@@ -84,7 +84,9 @@ static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* 
     char* sub = ar.take<char>(need);
     if (sub) ssd_ws_layout(d.B, d.T, d.H, d.P, d.N, d.G, d.Q, sub, need, &w.ssd);
   }
-  w.dnormed = ar.take<float>((size_t)d.M * d.I);
+  // the gradient of the normalised gate output may overwrite it: dW_out (which reads `normed`, or its bf16 copy)
+  // is enqueued before the GEMM that writes `dnormed`
+  w.dnormed = w.normed;
   w.dxzd = ar.take<float>((size_t)d.M * d.J);
   w.dact = ar.take<float>((size_t)d.M * d.X);
   w.ddt = ar.take<float>((size_t)d.M * d.H);

@@ -11,7 +11,7 @@
 
 namespace pmb {
 
-constexpr int LM_TILE_ROWS = 4096;
+constexpr int LM_TILE_ROWS = 2048;
 
 __global__ void embedding_fwd_kernel(const float* __restrict__ table, const int64_t* __restrict__ ids, float* __restrict__ out,
                                      int64_t rows, int D, int V, unsigned int* __restrict__ bad) {
@@ -234,6 +234,13 @@ extern "C" int64_t pmb_lm_param_offset(const pmb_lm* lm, int32_t layer, int32_t 
 extern "C" float* pmb_lm_params(pmb_lm* lm) { return lm ? lm->params : nullptr; }
 extern "C" float* pmb_lm_grads(pmb_lm* lm) { return lm ? lm->grads : nullptr; }
 extern "C" int64_t pmb_lm_activation_bytes(const pmb_lm* lm) { return lm ? lm->act_bytes : 0; }
+extern "C" void pmb_lm_activation_detail(const pmb_lm* lm, int64_t* h_out3) {
+  if (!lm || !h_out3) return;
+  const size_t esz = lm->bf16 ? 2 : 4;
+  h_out3[0] = (int64_t)((size_t)lm->d.M * lm->d.D * esz * (lm->L + 1));                          // stored for backward: block inputs
+  h_out3[1] = (int64_t)lm->ws_bytes;                                                              // transient: one block's workspace
+  h_out3[2] = (int64_t)((size_t)lm->tile_rows * lm->Vp * (lm->bf16 ? 6 : 4) + (size_t)lm->d.M * lm->d.D * esz);  // transient: logits tile, d(hidden)
+}
 extern "C" const float* pmb_lm_loss_device(const pmb_lm* lm) { return lm ? lm->loss : nullptr; }
 
 extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t* d_ids, const int64_t* d_targets,

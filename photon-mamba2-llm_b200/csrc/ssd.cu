@@ -454,7 +454,7 @@ __global__ void ssd_chunk_finish_kernel(SsdP p, const float* __restrict__ ddt_x,
 // Sums the split-K partial tiles in a fixed order.  mode 0: dG (lower-triangular 64x64 tiles only, the
 // others were never produced); mode 1/2: dC/dB rows go to out + token * ld + g * cols.
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, int nsplit, int rows, int cols, int mode, int G, int Q,
-                                     float* __restrict__ out, int64_t ld, int64_t total, int tile) {
+                                     float* __restrict__ out, int64_t ld, int64_t total, int tile, int accumulate) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   int64_t mn = (int64_t)rows * cols;
@@ -463,15 +463,12 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, int nsplit,
   float s = 0.0f;
   for (int k = 0; k < nsplit; ++k) s += part[(batch * nsplit + k) * mn + r];
   if (mode == 0) {
-    out[batch * mn + r] = s;
+    out[batch * mn + r] = accumulate ? out[batch * mn + r] + s : s;
   } else {
     int g = (int)(batch % G); int64_t bc = batch / G;
     out[(bc * Q + m) * ld + g * cols + n] = s;
   }
 }
-
-// above this many floats of per-head partials the per-group contractions stay on the FMA engine
-constexpr size_t TC_DG_PARTIAL_CAP = (size_t)1 << 29;
 
 static int pick_nsplit(int batches, int tiles, int hpg) {
   int want = (int)cdiv(2 * 148, (int64_t)batches * tiles);
@@ -500,11 +497,11 @@ size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base
     size_t a = (size_t)pick_nsplit(nbcg, qt * (qt + 1) / 2, hpg) * nbcg * Q * Q;
     size_t b = (size_t)pick_nsplit(nbcg, qt * (int)cdiv(N, BN), hpg) * nbcg * Q * N;
     size_t need = a > b ? a : b;
-    // the tensor-core path keeps one masked (Q,Q) product per head before the per-group sum
-    size_t tcp = (size_t)B * nc * H * Q * Q;
-    if (Q % 64 == 0 && N % 32 == 0 && P % 64 == 0 && tcp <= TC_DG_PARTIAL_CAP) {
+    if (Q % 64 == 0 && N % 32 == 0 && P % 64 == 0) {
+      // tensor-core path: masked (Q,Q) products of a few heads per pass, and the head-split dB / dC partial tiles
+      size_t tcp = (size_t)ssd_tc_dg_heads_per_pass(B, T, H, G, Q) * nbcg * Q * Q;
+      size_t dbc = (size_t)ssd_tc_dbc_nsplit_dims(B, T, H, N, G, Q) * nbcg * Q * N;
       if (tcp > need) need = tcp;
-      size_t dbc = (size_t)hpg * nbcg * Q * N;   // upper bound of the head-split dB / dC partial tiles
       if (dbc > need) need = dbc;
     }
     w.splitk = ar.take<float>(need);
@@ -585,7 +582,7 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   const double tok = (double)p.B * p.T;
   const bool tc = ssd_tc_supported(in) && (lddy % 4 == 0) && (reinterpret_cast<uintptr_t>(dy) % 16 == 0) && (g.lddbc % 4 == 0) &&
                   ((reinterpret_cast<uintptr_t>(g.db) | reinterpret_cast<uintptr_t>(g.dc)) % 16 == 0);
-  const bool tc_group = tc && ssd_tc_dg_partial_floats(in) <= TC_DG_PARTIAL_CAP;
+  const bool tc_group = tc;
   if (tc) PMB_TRY(ssd_tc_dstate(st, in, dy, lddy, ws));
   else PMB_TRY(run_op(st, "ssd_bwd_dstate", make_op<OpDstate>(p, p.N, p.P), nbch, 2.0 * tok * p.H * p.N * p.P));
   {
@@ -612,16 +609,21 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   auto reduce = [&](int nsplit, int cols, int mode, float* out, int64_t ld, int tile = BM) -> pmb_status {
     if (nsplit <= 1) return PMB_OK;
     int64_t total = (int64_t)nbcg * p.Q * cols;
-    splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(ws.splitk, nsplit, p.Q, cols, mode, p.G, p.Q, out, ld, total, tile);
+    splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(ws.splitk, nsplit, p.Q, cols, mode, p.G, p.Q, out, ld, total, tile, 0);
     PMB_LAUNCHED();
     return PMB_OK;
   };
   if (tc_group) {
     {
       ProfScope prof(st, "ssd_bwd_dg_tc", 2.0 * tok * p.H * p.Q * p.P, 0.0);
-      PMB_TRY(ssd_tc_dg_partials(st, in, dy, lddy, ws));
-      PMB_TRY(reduce(p.hpg, p.Q, 0, ws.dG, 0, 128));
-      if (p.hpg == 1) PMB_CUDA(cudaMemcpyAsync(ws.dG, ws.splitk, (size_t)nbcg * p.Q * p.Q * sizeof(float), cudaMemcpyDeviceToDevice, st));
+      const int hc = ssd_tc_dg_heads_per_pass(p.B, p.T, p.H, p.G, p.Q);
+      const int64_t total = (int64_t)nbcg * p.Q * p.Q;
+      for (int h0 = 0; h0 < p.hpg; h0 += hc) {
+        const int cur = min(hc, p.hpg - h0);
+        PMB_TRY(ssd_tc_dg_partials(st, in, dy, lddy, ws, h0, cur));
+        splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(ws.splitk, cur, p.Q, p.Q, 0, p.G, p.Q, ws.dG, 0, total, 128, h0 > 0);
+        PMB_LAUNCHED();
+      }
     }
     const int ns = ssd_tc_dbc_nsplit(in);
     {

@@ -237,12 +237,14 @@ struct TcDG {
     for (int q = tid; q < p.Q; q += nthr) { aux[q] = t.sp[q]; aux[p.Q + q] = p.dtv(t.tok0 + q, t.h); }
   }
   TcP p; int Mdim, Ndim;
+  int h0, hc;                   // this pass covers heads h0 .. h0+hc-1 of every group
   HeadTile t; float* out;
   __device__ bool init(int batch, int m0, int n0) {
     if (n0 > m0 + tcb::BM - 1) return false;
-    t.set(p, batch);
-    int64_t bcg = ((int64_t)t.bb * p.nc + t.cc) * p.G + t.g;
-    out = p.part + (bcg * p.hpg + (t.h % p.hpg)) * p.Q * p.Q;
+    int hl = batch % hc; int bcg = batch / hc;
+    int g = bcg % p.G; int bc = bcg / p.G;
+    t.set(p, bc * p.H + g * p.hpg + h0 + hl);
+    out = p.part + ((int64_t)bcg * hc + hl) * p.Q * p.Q;
     return true;
   }
   __device__ int nseg() const { return 1; }
@@ -492,27 +494,38 @@ pmb_status ssd_tc_dx(cudaStream_t st, const SsdIn& in, const float* dy, int64_t 
   return tcb::launch(st, ms, mk<TcScan<1>>(p, p.Q, p.P), p.B * p.nc * p.H, status_ptr());
 }
 
-size_t ssd_tc_dg_partial_floats(const SsdIn& in) { return (size_t)in.B * (in.T / in.Q) * in.H * in.Q * in.Q; }
+// Heads per pass of the dG computation: the per-head masked products are staged in ws.splitk before the
+// per-group sum, and that staging area is capped at 2^26 floats.
+int ssd_tc_dg_heads_per_pass(int B, int T, int H, int G, int Q) {
+  int64_t per_head = (int64_t)B * (T / Q) * G * Q * Q;
+  int64_t hc = ((int64_t)1 << 26) / per_head;
+  int hpg = H / G;
+  if (hc < 1) hc = 1;
+  return (int)(hc > hpg ? hpg : hc);
+}
 
-// Writes the per-head masked products into ws.splitk (hpg tiles per group); the caller reduces them.
-pmb_status ssd_tc_dg_partials(cudaStream_t st, const SsdIn& in, const float* dy, int64_t lddy, const SsdWs& ws) {
+// Writes the masked products of heads h0..h0+hc-1 of every group into ws.splitk (hc tiles per group); the caller reduces them.
+pmb_status ssd_tc_dg_partials(cudaStream_t st, const SsdIn& in, const float* dy, int64_t lddy, const SsdWs& ws, int h0, int hc) {
   TcP p = make_p(in, ws);
   MapSet ms{};
   int64_t tok = (int64_t)p.B * p.T;
   PMB_TRY(get_map(&ms.m[0], dy, p.P, tok, p.H, lddy, p.P, 32, 128, false));
   PMB_TRY(get_map(&ms.m[1], in.x, p.P, tok, p.H, in.ldx, p.P, 32, 128, false));
   ms.m[2] = ms.m[0]; ms.m[3] = ms.m[0];
-  return tcb::launch(st, ms, mk<TcDG>(p, p.Q, p.Q), p.B * p.nc * p.H, status_ptr());
+  TcDG op = mk<TcDG>(p, p.Q, p.Q);
+  op.h0 = h0; op.hc = hc;
+  return tcb::launch(st, ms, op, p.B * p.nc * p.G * hc, status_ptr());
 }
 
 // Number of head splits for the per-group dB / dC contractions: enough CTAs to fill the GPU twice.
-int ssd_tc_dbc_nsplit(const SsdIn& in) {
-  int nbcg = in.B * (in.T / in.Q) * in.G, hpg = in.H / in.G;
-  int tiles = (int)(cdiv(in.Q, tcb::BM) * cdiv(in.N, in.N <= 64 ? 64 : 128));
+int ssd_tc_dbc_nsplit_dims(int B, int T, int H, int N, int G, int Q) {
+  int nbcg = B * (T / Q) * G, hpg = H / G;
+  int tiles = (int)(cdiv(Q, tcb::BM) * cdiv(N, N <= 64 ? 64 : 128));
   int want = (int)cdiv(2 * 148, (int64_t)nbcg * tiles);
   if (want < 1) want = 1;
   return want > hpg ? hpg : want;
 }
+int ssd_tc_dbc_nsplit(const SsdIn& in) { return ssd_tc_dbc_nsplit_dims(in.B, in.T, in.H, in.N, in.G, in.Q); }
 
 template <int MODE, int BN>
 static pmb_status dbc_launch(cudaStream_t st, const SsdIn& in, const SsdWs& ws, float* out, int64_t lddbc, int nsplit) {

@@ -89,6 +89,7 @@ def _load():
         "pmb_lm_params": (vp, [vp]),
         "pmb_lm_grads": (vp, [vp]),
         "pmb_lm_activation_bytes": (i64, [vp]),
+        "pmb_lm_activation_detail": (None, [vp, C.POINTER(i64)]),
         "pmb_lm_step_device": (i32, [vp, vp, vp, vp, LAYER_CALLBACK, vp]),
         "pmb_lm_loss_device": (vp, [vp]),
         "pmb_lm_step_host": (i32, [vp, vp, vp, vp, C.POINTER(f32), LAYER_CALLBACK, vp]),
@@ -491,6 +492,12 @@ class FlatMamba:
     @property
     def activation_bytes(self):
         return int(lib.pmb_lm_activation_bytes(self._h))
+
+    @property
+    def activation_detail(self):
+        out = (C.c_int64 * 3)()
+        lib.pmb_lm_activation_detail(self._h, out)
+        return {"stored_for_backward": out[0], "block_workspace": out[1], "lm_head_transient": out[2]}
 
     def step_device(self, ids, targets, on_layer_done=None):
         cb = LAYER_CALLBACK(on_layer_done) if on_layer_done else C.cast(None, LAYER_CALLBACK)
