@@ -165,7 +165,7 @@ pmb_status pmb_gated_rmsnorm_bwd(void* stream, int64_t rows, int32_t width,
  * Hosts that gave the whole GPU to their own pool at start-up, or that must keep out of the driver's
  * allocator on a latency-critical path, have no workspace to pass.  This variant takes none: the
  * weight-gradient partials go to a 4 MiB array built into the library image (held by every GPU that
- * loads the library until exit), so ceil(rows/16) * width * 4 bytes must not exceed
+ * loads the library until exit), so ceil(rows/4) * width * 4 bytes must not exceed
  * pmb_gated_rmsnorm_bwd_static_max_bytes(); larger problems get PMB_ERR_SHAPE.  It calls no cudaMalloc /
  * cudaFree.  The first call on each device resolves the array's device address (make that call outside
  * stream capture).  All calls share the array: calls that may overlap on the GPU race and must be

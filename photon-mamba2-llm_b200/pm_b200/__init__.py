@@ -310,7 +310,7 @@ def gated_rmsnorm_bwd(dout, y, z, w, rstd):
 def gated_rmsnorm_bwd_static(dout, y, z, w, rstd):
     """Gated RMSNorm backward without any device allocation by the library: for hosts that cannot
     call cudaMalloc where they need it (all memory already in their own pool, or an allocator-free
-    hot loop).  The scratch is a fixed 4 MiB array inside the library, so ceil(rows/16)*width*4 bytes
+    hot loop).  The scratch is a fixed 4 MiB array inside the library, so ceil(rows/4)*width*4 bytes
     must fit; calls share it and must not overlap on the GPU.  Output buffers are the caller's."""
     rows, width = y.shape
     dy, dz, dw = torch.empty_like(y), torch.empty(rows, width, device=y.device, dtype=torch.float32), torch.empty_like(w)

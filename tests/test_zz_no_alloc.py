@@ -49,7 +49,7 @@ def test_static_scratch_variant_matches_workspace_variant_twice_in_a_row(pm):
 def test_static_scratch_limit_is_enforced(pm):
     limit = pm.lib.pmb_gated_rmsnorm_bwd_static_max_bytes()
     assert limit == 4 << 20
-    rows, width = 16 * 1024 + 16, 1024           # ceil(rows/16) * width * 4 = 4 MiB + 4 KiB
+    rows, width = 4 * 1024 + 4, 1024             # ceil(rows/4) * width * 4 = 4 MiB + 4 KiB
     args = _case(pm, rows, width, 3)
     with pytest.raises(pm.PmbError) as ei:
         pm.gated_rmsnorm_bwd_static(*args)
