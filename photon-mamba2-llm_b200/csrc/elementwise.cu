@@ -5,6 +5,8 @@
 
 namespace pmb {
 
+__global__ void column_sum_kernel(const float* __restrict__ partial, int64_t rows, int cols, float* __restrict__ out);
+
 // ---------------------------------------------------------------------------------------------
 // conv1d (causal, depthwise) + bias + SiLU, forward.   u[t,c] = b[c] + sum_k w[c,k] * xbc[t-(K-1)+k, c]
 // Layout stays (B,T,channels): a thread owns VEC adjacent channels and walks TT consecutive time steps
@@ -195,27 +197,15 @@ __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restr
       else ddst[(int64_t)tp * ldx] = g[0];
     }
   }
-  float* prow = partial + (int64_t)blockIdx.y * X * (K + 1);
+  // partial = [gridDim.y rows of X*K weight partials][gridDim.y rows of X bias partials]
+  float* prow = partial + (int64_t)blockIdx.y * X * K;
+  float* pbias = partial + (int64_t)gridDim.y * X * K + (int64_t)blockIdx.y * X;
 #pragma unroll
   for (int v = 0; v < VEC; ++v) {
 #pragma unroll
-    for (int k = 0; k < K; ++k) prow[(int64_t)(c + v) * (K + 1) + k] = dwacc[v][k];
-    prow[(int64_t)(c + v) * (K + 1) + K] = dbacc[v];
+    for (int k = 0; k < K; ++k) prow[(int64_t)(c + v) * K + k] = dwacc[v][k];
+    pbias[c + v] = dbacc[v];
   }
-}
-
-// out[j] = sum_r partial[r*cols + j] in fixed order; optional second destination with a stride split
-// is handled by the caller through `map`: element j of the sum goes to out_a[j / (K+1) * K + j % (K+1)]
-// when j % (K+1) < K, else to out_b[j / (K+1)].
-__global__ void conv_partial_reduce_kernel(const float* __restrict__ partial, int rows, int X, int K,
-                                           float* __restrict__ dw, float* __restrict__ db) {
-  int j = blockIdx.x * blockDim.x + threadIdx.x;
-  int cols = X * (K + 1);
-  if (j >= cols) return;
-  float s = 0.0f;
-  for (int r = 0; r < rows; ++r) s += partial[(int64_t)r * cols + j];
-  int c = j / (K + 1), k = j % (K + 1);
-  if (k < K) dw[c * K + k] = s; else db[c] = s;
 }
 
 static const int CONV_BWD_TT = 32;
@@ -258,8 +248,10 @@ pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const
     default: return fail(PMB_ERR_SHAPE, "d_conv %d unsupported", d.K);
   }
   int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;
-  int cols = d.X * (d.K + 1);
-  conv_partial_reduce_kernel<<<(unsigned)cdiv(cols, 256), 256, 0, st>>>(partial, d.B * tblocks, d.X, d.K, dw, db);
+  int64_t rows = (int64_t)d.B * tblocks;
+  column_sum_kernel<<<(unsigned)cdiv(d.X * d.K, 32), 256, 0, st>>>(partial, rows, d.X * d.K, dw);
+  PMB_LAUNCHED();
+  column_sum_kernel<<<(unsigned)cdiv(d.X, 32), 256, 0, st>>>(partial + rows * d.X * d.K, rows, d.X, db);
   PMB_LAUNCHED();
   return PMB_OK;
 }

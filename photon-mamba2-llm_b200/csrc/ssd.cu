@@ -330,49 +330,76 @@ __global__ void chunk_cumsum_kernel(SsdP p) {
   }
 }
 
-// In place: buffer holds states[c] on entry, h_prev[c] (state entering chunk c) on exit; hlast = final state.
-__global__ void state_pass_kernel(SsdP p, const float* __restrict__ init) {
-  int64_t NP = (int64_t)p.N * p.P;
+// Exclusive scan over chunks, in place, forward or reverse.  One thread owns VEC adjacent p of one (b,h,n).
+//   forward: buf[c] holds states[c] on entry and h_prev[c] (state entering chunk c) on exit; last = final state.
+//            run_{c+1} = exp(S_end[c]) run_c + states[c],  run_0 = init (or 0)
+//   reverse: buf[c] holds contrib[c] on entry and dh[c] (adjoint of the state leaving chunk c) on exit.
+//            run_{c-1} = exp(S_end[c]) run_c + contrib[c], run_{nc-1} = 0
+// The chunk values are fetched four at a time before the dependent chain so the loads overlap.
+template <int VEC>
+__global__ void __launch_bounds__(256) state_scan_kernel(SsdP p, float* __restrict__ buf, const float* __restrict__ init,
+                                                         float* __restrict__ last, int reverse) {
+  const int64_t NP = (int64_t)p.N * p.P;
+  const int64_t per = NP / VEC;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (int64_t)p.B * p.H * NP) return;
-  int64_t e = i % NP; int64_t bh = i / NP; int h = (int)(bh % p.H); int bb = (int)(bh / p.H);
-  float run = init ? init[i] : 0.0f;
-  for (int cc = 0; cc < p.nc; ++cc) {
-    float* slot = p.hprev + (((int64_t)bb * p.nc + cc) * p.H + h) * NP + e;
-    float tmp = *slot;
-    *slot = run;
-    run = fmaf(expf(p.Sv(bb, h, cc, p.Q - 1)), run, tmp);
+  if (i >= (int64_t)p.B * p.H * per) return;
+  const int64_t e = (i % per) * VEC; const int64_t bh = i / per; const int h = (int)(bh % p.H); const int bb = (int)(bh / p.H);
+  float run[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) run[v] = (init && !reverse) ? init[bh * NP + e + v] : 0.0f;
+  const float* send = p.S + ((int64_t)bb * p.H + h) * p.T + p.Q - 1;
+  for (int c0 = 0; c0 < p.nc; c0 += 4) {
+    float tmp[4][VEC]; float dec[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int cc = reverse ? p.nc - 1 - (c0 + j) : c0 + j;
+      if (c0 + j < p.nc) {
+        const float* slot = buf + (((int64_t)bb * p.nc + cc) * p.H + h) * NP + e;
+        if (VEC == 4) { float4 q = *reinterpret_cast<const float4*>(slot); tmp[j][0] = q.x; tmp[j][1 % VEC] = q.y; tmp[j][2 % VEC] = q.z; tmp[j][3 % VEC] = q.w; }
+        else tmp[j][0] = slot[0];
+        dec[j] = expf(send[(int64_t)cc * p.Q]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int cc = reverse ? p.nc - 1 - (c0 + j) : c0 + j;
+      if (c0 + j < p.nc) {
+        float* slot = buf + (((int64_t)bb * p.nc + cc) * p.H + h) * NP + e;
+        if (VEC == 4) *reinterpret_cast<float4*>(slot) = make_float4(run[0], run[1 % VEC], run[2 % VEC], run[3 % VEC]);
+        else slot[0] = run[0];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) run[v] = fmaf(dec[j], run[v], tmp[j][v]);
+      }
+    }
   }
-  p.hlast[i] = run;
+  if (last && !reverse) {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) last[bh * NP + e + v] = run[v];
+  }
 }
 
-// Reverse scan.  On entry dh[c] holds contrib[c]; on exit dh[c] = adjoint of the state leaving chunk c.
-// dsend[b,c,h] = <dh[c], h_next[c]> with h_next[c] = h_prev[c+1] (the last chunk's dh is zero).
-constexpr int SPB_THREADS = 256;
-constexpr int SPB_MAX_PER_THREAD = 64;  // N*P <= 16384
-__global__ void __launch_bounds__(SPB_THREADS) state_pass_bwd_kernel(SsdP p, float* __restrict__ dsend) {
+// dsend[b,c,h] = <dh[c], h_next[c]> with h_next[c] = h_prev[c+1], or the final state for the last chunk.
+__global__ void __launch_bounds__(256) state_dot_kernel(SsdP p, float* __restrict__ dsend) {
   __shared__ float red[32];
-  int bh = blockIdx.x, h = bh % p.H, bb = bh / p.H;
-  int NP = p.N * p.P;
-  float run[SPB_MAX_PER_THREAD];
-#pragma unroll
-  for (int k = 0; k < SPB_MAX_PER_THREAD; ++k) run[k] = 0.0f;
-  for (int cc = p.nc - 1; cc >= 0; --cc) {
-    float* slot = p.dh + (((int64_t)bb * p.nc + cc) * p.H + h) * NP;
-    const float* hnext = (cc + 1 < p.nc) ? p.hprev + (((int64_t)bb * p.nc + cc + 1) * p.H + h) * NP : p.hlast + ((int64_t)bb * p.H + h) * NP;
-    float decay = expf(p.Sv(bb, h, cc, p.Q - 1));
-    float dot = 0.0f;
-    int k = 0;
-    for (int e = threadIdx.x; e < NP; e += SPB_THREADS, ++k) {
-      float tmp = slot[e];
-      float r = run[k];
-      slot[e] = r;
-      dot = fmaf(r, hnext[e], dot);
-      run[k] = fmaf(decay, r, tmp);
-    }
-    float tot = block_sum(dot, red);
-    if (threadIdx.x == 0) dsend[((int64_t)bb * p.nc + cc) * p.H + h] = tot;
-  }
+  const int bch = blockIdx.x;
+  const int h = bch % p.H; const int bc = bch / p.H; const int cc = bc % p.nc; const int bb = bc / p.nc;
+  const int NP = p.N * p.P;
+  const float* a = p.dh + (int64_t)bch * NP;
+  const float* b = (cc + 1 < p.nc) ? p.hprev + (((int64_t)bb * p.nc + cc + 1) * p.H + h) * NP : p.hlast + ((int64_t)bb * p.H + h) * NP;
+  float dot = 0.0f;
+  for (int e = threadIdx.x; e < NP; e += blockDim.x) dot = fmaf(a[e], b[e], dot);
+  float tot = block_sum(dot, red);
+  if (threadIdx.x == 0) dsend[bch] = tot;
+}
+
+static pmb_status launch_state_scan(cudaStream_t st, const SsdP& p, float* buf, const float* init, float* last, int reverse) {
+  const int64_t NP = (int64_t)p.N * p.P;
+  const bool vec = (p.P % 4 == 0);
+  const int64_t n = (int64_t)p.B * p.H * (vec ? NP / 4 : NP);
+  if (vec) state_scan_kernel<4><<<(unsigned)cdiv(n, 256), 256, 0, st>>>(p, buf, init, last, reverse);
+  else state_scan_kernel<1><<<(unsigned)cdiv(n, 256), 256, 0, st>>>(p, buf, init, last, reverse);
+  PMB_LAUNCHED();
+  return PMB_OK;
 }
 
 // One warp per (b,t,h): row dot products and dx.
@@ -516,8 +543,6 @@ size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base
 static pmb_status fill_params(const SsdIn& in, const SsdWs& ws, SsdP* pp) {
   if (in.Q <= 0 || in.T % in.Q != 0) return fail(PMB_ERR_SHAPE, "ssd: T=%d is not a multiple of block_len=%d", in.T, in.Q);
   if (!(in.G == 1 || in.G == in.H)) return fail(PMB_ERR_SHAPE, "ssd: n_groups must be 1 or n_heads");
-  if ((int64_t)in.N * in.P > (int64_t)SPB_THREADS * SPB_MAX_PER_THREAD)
-    return fail(PMB_ERR_SHAPE, "ssd: d_state*d_head=%lld exceeds %d", (long long)in.N * in.P, SPB_THREADS * SPB_MAX_PER_THREAD);
   SsdP p{};
   p.B = in.B; p.T = in.T; p.H = in.H; p.P = in.P; p.N = in.N; p.G = in.G; p.Q = in.Q; p.nc = in.T / in.Q; p.hpg = in.H / in.G;
   p.x = in.x; p.ldx = in.ldx; p.dt = in.dt; p.A = in.A; p.a = in.a; p.b = in.b; p.c = in.c; p.ldbc = in.ldbc; p.D = in.D;
@@ -562,8 +587,7 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
   int64_t nel = (int64_t)p.B * p.H * p.N * p.P;
   {
     ProfScope prof(st, "ssd_state_pass", 0.0, 8.0 * nel * p.nc);
-    state_pass_kernel<<<(unsigned)cdiv(nel, 256), 256, 0, st>>>(p, init_state);
-    PMB_LAUNCHED();
+    PMB_TRY(launch_state_scan(st, p, p.hprev, init_state, p.hlast, 0));
   }
   if (tc) PMB_TRY(ssd_tc_scan(st, in, y, ldy, ws));
   else PMB_TRY(run_op(st, "ssd_chunk_scan", make_op<OpScan>(p, p.Q, p.P), nbch, 2.0 * tok * p.H * p.P * (p.Q + p.N)));
@@ -587,7 +611,8 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   else PMB_TRY(run_op(st, "ssd_bwd_dstate", make_op<OpDstate>(p, p.N, p.P), nbch, 2.0 * tok * p.H * p.N * p.P));
   {
     ProfScope prof(st, "ssd_bwd_state_pass", 0.0, 12.0 * p.B * p.H * p.N * p.P * p.nc);
-    state_pass_bwd_kernel<<<(unsigned)(p.B * p.H), SPB_THREADS, 0, st>>>(p, dsend);
+    PMB_TRY(launch_state_scan(st, p, p.dh, nullptr, nullptr, 1));
+    state_dot_kernel<<<(unsigned)nbch, 256, 0, st>>>(p, dsend);
     PMB_LAUNCHED();
   }
   if (tc) PMB_TRY(ssd_tc_dx(st, in, dy, lddy, ws));

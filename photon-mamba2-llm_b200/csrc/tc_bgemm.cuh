@@ -35,12 +35,16 @@ namespace tcb {
 
 using namespace tcx;
 
-constexpr int BM = 128, BK = 32, STAGES = 3, NTHREADS = 192;
+constexpr int BM = 128, BK = 32, NTHREADS = 192;
+// Ring depth: 3 stages and one CTA per SM for 128-wide tiles; 2 stages for 64-wide tiles so that two CTAs share
+// an SM (the small per-(batch,chunk,head) problems are latency-bound: a second resident CTA fills the bubbles).
+template <int BN> struct RingDepth { static constexpr int STAGES = BN <= 64 ? 2 : 3; static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1; };
 
 struct MapSet { CUtensorMap m[4]; };
 
 template <int BN>
 struct Geometry {
+  static constexpr int STAGES = RingDepth<BN>::STAGES;
   static constexpr int A_BYTES = BM * BK * 4;
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int HALF = A_BYTES + B_BYTES;       // hi (or lo) part of one stage
@@ -65,10 +69,11 @@ __device__ __forceinline__ void decode_mnmajor(int i, int& mn, int& k) {
 }
 
 template <class Op>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(NTHREADS, RingDepth<Op::BN>::CTAS_PER_SM)
 tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __restrict__ status) {
   constexpr int BN = Op::BN;
   using G = Geometry<BN>;
+  constexpr int STAGES = G::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
