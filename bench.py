@@ -346,6 +346,9 @@ MICRO = {
     "gemm_out_proj_fwd": ("gemm", dict(M=65536, N=768, K=1536, ta=0, tb=0)),
     "gemm_small_c2_in_proj": ("gemm", dict(M=2048, N=3224, K=768, ta=0, tb=0)),
     "ssd_scan_fp32": ("ssd", dict(B=4, T=8192, H=32, P=64, N=128, G=1, Q=256)),
+    # BASELINE configs[4]: scan microbench, bf16 inputs / fp32 state, at a quarter of the batch (B=16 in the config)
+    "ssd_scan_bf16_in": ("ssd16", dict(B=4, T=8192, H=32, P=64, N=128, G=1, Q=256)),
+    "ssd_scan_bf16_in_full": ("ssd16", dict(B=16, T=8192, H=32, P=64, N=128, G=1, Q=256)),
     "decode_step_fp32": ("decode", dict(B=256, D=2048, H=32, P=64, N=128)),
 }
 
@@ -367,6 +370,16 @@ def run_micro(args):
         out = torch.empty(M, N, device="cuda")
         fn = lambda: pm_b200.matmul(A, Bm, trans_a=bool(ta), trans_b=bool(tb), out=out, engine=args.engine)
         flops, nbytes = 2.0 * M * N * K, 4.0 * (M * K + K * N + M * N)
+    elif kind == "ssd16":
+        B, T, H, P, N, G, Q = (a[k] for k in "BTHPNGQ")
+        x, dy = rnd(B, T, H, P).bfloat16(), rnd(B, T, H, P).bfloat16()
+        av = -torch.nn.functional.softplus(rnd(B, T, H) * 0.5 - 2.0) * 4.0
+        bm, cm = rnd(B, T, G, N).bfloat16(), rnd(B, T, G, N).bfloat16()
+        scan = pm_b200.SsdScanBf16(x, av, bm, cm, Q)
+        fn = lambda: (scan.forward(), scan.backward(dy))
+        fwd = 2.0 * Q * N * G + H * (2.0 * Q * P + 4.0 * N * P)
+        bwd = H * (4.0 * Q * P + 8.0 * N * P) + 6.0 * Q * N * G
+        flops, nbytes = B * T * (fwd + bwd), 2.0 * B * T * (H * P * 5 + 2 * G * N * 2) + 8.0 * B * T * H
     elif kind == "ssd":
         B, T, H, P, N, G, Q = (a[k] for k in "BTHPNGQ")
         x, dy = rnd(B, T, H, P), rnd(B, T, H, P)
@@ -398,11 +411,15 @@ def run_micro(args):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
+    pm_b200.profile_start()
+    fn()
+    prof = pm_b200.profile_stop()
     line = {"micro": args.micro, "args": a, "ms": ms, "steps": steps, "engine": args.engine,
             "tflops": flops / (ms * 1e-3) / 1e12 if flops else None, "gbs": nbytes / (ms * 1e-3) / 1e9,
             "frac_of_bf16_burst": (flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"]) if flops else None,
             "frac_of_hbm": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "peaks": peaks["source"],
-            "device_status": pm_b200.device_status()}
+            "device_status": pm_b200.device_status(),
+            "kernels": [{"name": k["name"], "launches": k["launches"], "ms": round(k["ms"], 4)} for k in sorted(prof, key=lambda k: -k["ms"])]}
     print(json.dumps(line))
 
 

@@ -96,7 +96,9 @@ pmb_status pmb_device_status(int32_t* h_word_out);
  * trans_a = 0: A is (M,K) row-major with leading dimension lda; 1: A is stored (K,M).
  * trans_b = 0: B is (K,N) row-major with ldb;                   1: B is stored (N,K).
  * d_R (may be NULL) is added to the product (same shape/ld as C); d_R may equal d_C.
- * engine: 0 = auto (tcgen05 3xTF32 when alignment allows, else SIMT), 1 = SIMT fp32, 2 = tcgen05 only. */
+ * engine: 0 = auto (tcgen05 3xTF32 when alignment allows, else fp32 FMA; among the tcgen05 kernels the 128x64-tile
+ * variant with two CTAs per SM is taken when the problem has few output tiles), 1 = fp32 FMA, 2 = tcgen05 128x128
+ * tiles, 3 = tcgen05 128x64 tiles. */
 pmb_status pmb_gemm_f32(void* stream, int32_t trans_a, int32_t trans_b, int64_t M, int64_t N, int64_t K,
                         const float* d_A, int64_t lda, const float* d_B, int64_t ldb,
                         float* d_C, int64_t ldc, const float* d_R, int32_t engine);
@@ -148,6 +150,22 @@ pmb_status pmb_ssd_scan_bwd(void* stream, int32_t batch, int32_t seqlen, int32_t
                             const float* d_y, int64_t ldy, const float* d_dy, int64_t lddy,
                             float* d_dx, int64_t lddx, float* d_da, float* d_db, float* d_dc, int64_t lddbc,
                             void* d_ws, size_t ws_bytes);
+
+/* Scan with bf16 inputs and fp32 state (the reference upcasts to F32 around Ops::ssd_scan, block.rs:203-208):
+ * x, b, c, y and dy, dx, db, dc are contiguous bf16 (B,T,H,P) / (B,T,G,N); a, da and the states are fp32.
+ * The backward reads x, b, c, y from the workspace the forward left behind (keep it untouched in between). */
+size_t pmb_ssd_workspace_bytes_bf16(int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
+                                    int32_t d_state, int32_t n_groups, int32_t block_len);
+pmb_status pmb_ssd_scan_fwd_bf16(void* stream, int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
+                                 int32_t d_state, int32_t n_groups, int32_t block_len,
+                                 const uint16_t* d_x, const float* d_a, const uint16_t* d_b, const uint16_t* d_c,
+                                 const float* d_init_state, uint16_t* d_y, float* d_final_state,
+                                 void* d_ws, size_t ws_bytes);
+pmb_status pmb_ssd_scan_bwd_bf16(void* stream, int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
+                                 int32_t d_state, int32_t n_groups, int32_t block_len,
+                                 const float* d_a, const uint16_t* d_dy,
+                                 uint16_t* d_dx, float* d_da, uint16_t* d_db, uint16_t* d_dc,
+                                 void* d_ws, size_t ws_bytes);
 
 /* ---- gated RMSNorm (block.rs:216-222): out = rmsnorm(y * silu(z), w, eps) over the last axis (I).
  * z has token stride ldz (it lives inside xzd).  d_rstd (rows) receives 1/sqrt(mean+eps). */

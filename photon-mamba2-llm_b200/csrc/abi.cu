@@ -20,8 +20,16 @@ pmb_status gemm(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K
   if (engine == 0 && forced) engine = 1;
   if (engine == 1) return gemm_simt(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
   bool ok = gemm_tc_supported(ta, tb, M, N, K, A, lda, B, ldb, C, ldc);
-  if (engine == 2 && !ok) return fail(PMB_ERR_UNSUPPORTED, "gemm: tcgen05 engine needs 16-byte aligned operands and leading dimensions");
-  if (ok) return gemm_tc(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
+  if ((engine == 2 || engine == 3) && !ok) return fail(PMB_ERR_UNSUPPORTED, "gemm: tcgen05 engine needs 16-byte aligned operands and leading dimensions");
+  if (ok) {
+    // The 128x64 / two-CTAs-per-SM variant (engine 3, or problems with fewer 128x128 tiles than PMB_GEMM_SMALL_TILES)
+    // measured slower than the 128x128 kernel on every GEMM of the LM step (the loop is bound by shared-memory
+    // traffic, not by per-tile latency), so it is off by default.
+    static const int small_env = [] { const char* e = getenv("PMB_GEMM_SMALL_TILES"); return e ? atoi(e) : 0; }();
+    const int64_t tiles = cdiv(M, 128) * cdiv(N, 128);
+    if (engine == 3 || (engine == 0 && tiles < small_env)) return gemm_tc_small(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
+    return gemm_tc(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
+  }
   return gemm_simt(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
 }
 
@@ -72,6 +80,8 @@ extern "C" pmb_status pmb_device_status(int32_t* h_word_out) {
   w |= w2 << 8;
   PMB_TRY(read_clear_device_status_bf16(&w2));
   w |= w2 << 16;
+  PMB_TRY(read_clear_device_status_small(&w2));
+  w |= w2 << 24;
   if (h_word_out) *h_word_out = (int32_t)w;
   return PMB_OK;
 }
@@ -81,7 +91,7 @@ extern "C" pmb_status pmb_gemm_f32(void* stream, int32_t trans_a, int32_t trans_
                                    float* d_C, int64_t ldc, const float* d_R, int32_t engine) {
   if (M <= 0 || N <= 0 || K <= 0) return fail(PMB_ERR_SHAPE, "gemm: M, N, K must be positive (got %lld, %lld, %lld)", (long long)M, (long long)N, (long long)K);
   if (lda < (trans_a ? M : K) || ldb < (trans_b ? K : N) || ldc < N) return fail(PMB_ERR_SHAPE, "gemm: leading dimension smaller than the row length");
-  if (engine < 0 || engine > 2) return fail(PMB_ERR_ARG, "gemm: engine must be 0, 1 or 2");
+  if (engine < 0 || engine > 3) return fail(PMB_ERR_ARG, "gemm: engine must be 0..3");
   return gemm(static_cast<cudaStream_t>(stream), trans_a != 0, trans_b != 0, M, N, K, d_A, lda, d_B, ldb, d_C, ldc, d_R, engine);
 }
 
@@ -184,4 +194,81 @@ extern "C" pmb_status pmb_gated_rmsnorm_bwd(void* stream, int64_t rows, int32_t 
   if (rows <= 0 || width <= 0 || ldz < width || lddz < width) return fail(PMB_ERR_SHAPE, "gated_rmsnorm_bwd: bad shape");
   if (!d_dout || !d_y || !d_z || !d_w || !d_rstd || !d_dy || !d_dz || !d_dw || !d_ws) return fail(PMB_ERR_ARG, "gated_rmsnorm_bwd: NULL argument");
   return gated_rmsnorm_bwd(static_cast<cudaStream_t>(stream), rows, width, d_dout, d_y, d_z, ldz, d_w, d_rstd, d_dy, d_dz, lddz, d_dw, d_ws, ws_bytes);
+}
+
+// ---- scan with bf16 inputs / fp32 state (x, B, C, y and their gradients bf16; a, da and the states fp32).
+// The operands are widened into a staging area at the end of the workspace and the fp32 (3xTF32) path runs on them.
+namespace pmb {
+__global__ void cast_bf16_f32_kernel(const uint16_t* __restrict__ src, float* __restrict__ dst, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = __uint_as_float((uint32_t)src[i] << 16);
+}
+static pmb_status widen(cudaStream_t st, const uint16_t* src, float* dst, int64_t n) {
+  ProfScope prof(st, "cast_bf16_f32", 0.0, 6.0 * n);
+  cast_bf16_f32_kernel<<<(unsigned)cdiv(n, 256), 256, 0, st>>>(src, dst, n);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+struct Bf16Stage { float *x, *b, *c, *y, *dy, *dx, *db, *dc; };
+static size_t bf16_stage_layout(int B, int T, int H, int P, int N, int G, int Q, void* base, size_t bytes, SsdWs* ws, Bf16Stage* sg) {
+  size_t core = ssd_ws_layout(B, T, H, P, N, G, Q, nullptr, 0, nullptr);
+  if (base && ssd_ws_layout(B, T, H, P, N, G, Q, base, bytes, ws) == 0) return 0;
+  Arena ar(base ? static_cast<char*>(base) + core : nullptr, base ? (bytes > core ? bytes - core : 0) : 0);
+  size_t hp = (size_t)B * T * H * P, gn = (size_t)B * T * G * N;
+  Bf16Stage s;
+  s.x = ar.take<float>(hp); s.b = ar.take<float>(gn); s.c = ar.take<float>(gn); s.y = ar.take<float>(hp);
+  s.dy = ar.take<float>(hp); s.dx = ar.take<float>(hp); s.db = ar.take<float>(gn); s.dc = ar.take<float>(gn);
+  if (sg) *sg = s;
+  return ar.ok ? core + ar.used() : 0;
+}
+}  // namespace pmb
+
+extern "C" size_t pmb_ssd_workspace_bytes_bf16(int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
+                                               int32_t d_state, int32_t n_groups, int32_t block_len) {
+  if (ssd_check(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len) != PMB_OK) return 0;
+  return bf16_stage_layout(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, nullptr, 0, nullptr, nullptr);
+}
+
+extern "C" pmb_status pmb_ssd_scan_fwd_bf16(void* stream, int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
+                                            int32_t d_state, int32_t n_groups, int32_t block_len,
+                                            const uint16_t* d_x, const float* d_a, const uint16_t* d_b, const uint16_t* d_c,
+                                            const float* d_init_state, uint16_t* d_y, float* d_final_state,
+                                            void* d_ws, size_t ws_bytes) {
+  PMB_TRY(ssd_check(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len));
+  if (!d_x || !d_a || !d_b || !d_c || !d_y || !d_ws) return fail(PMB_ERR_ARG, "ssd_scan_fwd_bf16: NULL argument");
+  SsdWs ws; Bf16Stage sg;
+  if (bf16_stage_layout(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, d_ws, ws_bytes, &ws, &sg) == 0)
+    return fail(PMB_ERR_WORKSPACE, "ssd bf16 workspace too small");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int64_t hp = (int64_t)batch * seqlen * n_heads * d_head, gn = (int64_t)batch * seqlen * n_groups * d_state;
+  PMB_TRY(widen(st, d_x, sg.x, hp)); PMB_TRY(widen(st, d_b, sg.b, gn)); PMB_TRY(widen(st, d_c, sg.c, gn));
+  SsdIn in{};
+  in.B = batch; in.T = seqlen; in.H = n_heads; in.P = d_head; in.N = d_state; in.G = n_groups; in.Q = block_len;
+  in.x = sg.x; in.ldx = (int64_t)n_heads * d_head; in.a = d_a; in.b = sg.b; in.c = sg.c; in.ldbc = (int64_t)n_groups * d_state;
+  PMB_TRY(ssd_fwd(st, in, d_init_state, sg.y, in.ldx, d_final_state, ws));
+  return cast_f32_bf16(st, sg.y, d_y, hp);
+}
+
+extern "C" pmb_status pmb_ssd_scan_bwd_bf16(void* stream, int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
+                                            int32_t d_state, int32_t n_groups, int32_t block_len,
+                                            const float* d_a, const uint16_t* d_dy,
+                                            uint16_t* d_dx, float* d_da, uint16_t* d_db, uint16_t* d_dc,
+                                            void* d_ws, size_t ws_bytes) {
+  PMB_TRY(ssd_check(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len));
+  if (!d_a || !d_dy || !d_dx || !d_da || !d_db || !d_dc || !d_ws) return fail(PMB_ERR_ARG, "ssd_scan_bwd_bf16: NULL argument");
+  SsdWs ws; Bf16Stage sg;
+  if (bf16_stage_layout(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, d_ws, ws_bytes, &ws, &sg) == 0)
+    return fail(PMB_ERR_WORKSPACE, "ssd bf16 workspace too small");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int64_t hp = (int64_t)batch * seqlen * n_heads * d_head, gn = (int64_t)batch * seqlen * n_groups * d_state;
+  PMB_TRY(widen(st, d_dy, sg.dy, hp));
+  SsdIn in{};
+  in.B = batch; in.T = seqlen; in.H = n_heads; in.P = d_head; in.N = d_state; in.G = n_groups; in.Q = block_len;
+  in.x = sg.x; in.ldx = (int64_t)n_heads * d_head; in.a = d_a; in.b = sg.b; in.c = sg.c; in.ldbc = (int64_t)n_groups * d_state;
+  SsdGrads g{};
+  g.dx = sg.dx; g.lddx = in.ldx; g.db = sg.db; g.dc = sg.dc; g.lddbc = in.ldbc; g.da = d_da;
+  PMB_TRY(ssd_bwd(st, in, sg.y, in.ldx, sg.dy, in.ldx, g, ws));
+  PMB_TRY(cast_f32_bf16(st, sg.dx, d_dx, hp));
+  PMB_TRY(cast_f32_bf16(st, sg.db, d_db, gn));
+  return cast_f32_bf16(st, sg.dc, d_dc, gn);
 }

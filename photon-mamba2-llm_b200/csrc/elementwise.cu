@@ -75,7 +75,8 @@ __global__ void dt_softplus_kernel(const float* __restrict__ xzd, int64_t ldx, i
 
 template <int K>
 static pmb_status launch_conv_fwd_k(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b, float* act) {
-  const int TT = 32;
+  // time steps per thread: short runs keep enough threads in flight for small token counts
+  const int TT = d.M >= 32768 ? 32 : 8;
   bool vec = (d.X % 4 == 0) && (d.J % 4 == 0) && (d.I % 4 == 0) && ((reinterpret_cast<uintptr_t>(xzd) | reinterpret_cast<uintptr_t>(act)) % 16 == 0);
   int tblocks = (d.T + TT - 1) / TT;
   if (vec) {
@@ -208,7 +209,7 @@ __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restr
   }
 }
 
-static const int CONV_BWD_TT = 32;
+static const int CONV_BWD_TT = 16;
 
 size_t conv_bwd_ws_bytes(const Dims& d) {
   int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;

@@ -68,6 +68,9 @@ pmb_status gemm_simt(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
 // returns PMB_ERR_UNSUPPORTED (without touching the error text) when alignment rules are not met
 pmb_status gemm_tc(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                    const float* B, int64_t ldb, float* C, int64_t ldc, const float* R);
+pmb_status gemm_tc_small(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                         const float* B, int64_t ldb, float* C, int64_t ldc, const float* R);
+pmb_status read_clear_device_status_small(unsigned int* word);
 bool gemm_tc_supported(int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                        const float* B, int64_t ldb, const float* C, int64_t ldc);
 pmb_status gemm(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,

@@ -69,6 +69,9 @@ def _load():
         "pmb_ssd_workspace_bytes": (sz, [i32] * 7),
         "pmb_ssd_scan_fwd": (i32, [vp] + [i32] * 7 + [vp, i64, vp, vp, vp, i64, vp, vp, i64, vp, vp, sz]),
         "pmb_ssd_scan_bwd": (i32, [vp] + [i32] * 7 + [vp, i64, vp, vp, vp, i64, vp, i64, vp, i64, vp, i64, vp, vp, vp, i64, vp, sz]),
+        "pmb_ssd_workspace_bytes_bf16": (sz, [i32] * 7),
+        "pmb_ssd_scan_fwd_bf16": (i32, [vp] + [i32] * 7 + [vp, vp, vp, vp, vp, vp, vp, vp, sz]),
+        "pmb_ssd_scan_bwd_bf16": (i32, [vp] + [i32] * 7 + [vp, vp, vp, vp, vp, vp, vp, sz]),
         "pmb_gated_rmsnorm_fwd": (i32, [vp, i64, i32, f32, vp, vp, i64, vp, vp, vp]),
         "pmb_gated_rmsnorm_bwd_workspace_bytes": (sz, [i64, i32]),
         "pmb_gated_rmsnorm_bwd": (i32, [vp, i64, i32, vp, vp, vp, i64, vp, vp, vp, vp, i64, vp, vp, sz]),
@@ -280,6 +283,39 @@ class SsdScan:
                                     self.c.data_ptr(), gn, self.y.data_ptr(), hp, _dev(dy, "dy").data_ptr(), hp,
                                     dx.data_ptr(), hp, da.data_ptr(), db.data_ptr(), dc.data_ptr(), gn,
                                     self.ws.data_ptr(), self.ws.numel()))
+        return dx, da, db, dc
+
+
+class SsdScanBf16:
+    """`Ops::ssd_scan` with bf16 x/B/C/y (and gradients) and fp32 a / state."""
+
+    def __init__(self, x, a, b, c, block_len):
+        for t, n in ((x, "x"), (b, "b"), (c, "c")):
+            if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()):
+                raise PmbError(2, f"{n}: expected a contiguous bfloat16 CUDA tensor, got {t.dtype}")
+        self.x, self.a, self.b, self.c = x, _dev(a, "a"), b, c
+        self.B, self.T, self.H, self.P = x.shape
+        self.G, self.N = b.shape[2], b.shape[3]
+        q = block_len
+        if q <= 0 or q >= self.T or self.T % q != 0:
+            q = self.T
+        self.dims = (self.B, self.T, self.H, self.P, self.N, self.G, q)
+        n = lib.pmb_ssd_workspace_bytes_bf16(*self.dims)
+        if n == 0:
+            raise PmbError(1, lib.pmb_last_error().decode())
+        self.ws = torch.empty(n, device=x.device, dtype=torch.uint8)
+
+    def forward(self, init_state=None, want_final_state=False):
+        y = torch.empty_like(self.x)
+        fs = torch.empty(self.B, self.H, self.N, self.P, device=y.device, dtype=torch.float32) if want_final_state else None
+        _check(lib.pmb_ssd_scan_fwd_bf16(_stream(), *self.dims, self.x.data_ptr(), self.a.data_ptr(), self.b.data_ptr(),
+                                         self.c.data_ptr(), _ptr(init_state), y.data_ptr(), _ptr(fs), self.ws.data_ptr(), self.ws.numel()))
+        return (y, fs) if want_final_state else y
+
+    def backward(self, dy):
+        dx, da, db, dc = torch.empty_like(self.x), torch.empty_like(self.a), torch.empty_like(self.b), torch.empty_like(self.c)
+        _check(lib.pmb_ssd_scan_bwd_bf16(_stream(), *self.dims, self.a.data_ptr(), dy.data_ptr(), dx.data_ptr(), da.data_ptr(),
+                                         db.data_ptr(), dc.data_ptr(), self.ws.data_ptr(), self.ws.numel()))
         return dx, da, db, dc
 
 

@@ -93,3 +93,27 @@ def test_lm_step_bf16_storage(pm):
             assert_close(g_layers[l][k], ls[l][k].grad, tol=2 * BF16_TOL if k in ("a_log", "dt_bias") else BF16_TOL, what=f"layer {l} d_{k}")
     assert pm.device_status() == 0
     lm.close()
+
+
+@pytest.mark.parametrize("B,T,H,P,N,G,Q", [(1, 512, 4, 64, 128, 1, 256), (2, 128, 4, 16, 8, 4, 32)])
+def test_ssd_scan_bf16_inputs_fp32_state(pm, B, T, H, P, N, G, Q):
+    # BASELINE configs[4] dims at reduced batch/heads: bf16 x, B, C; dt = softplus(N(-2, 0.5)); A = -exp(U[log 1, log 16])
+    x = randn((B, T, H, P), 1).bfloat16(); b = randn((B, T, G, N), 2).bfloat16(); c = randn((B, T, G, N), 3).bfloat16()
+    dt = torch.nn.functional.softplus(randn((B, T, H), 4, 0.5) - 2.0)
+    A = -torch.exp(torch.rand(H, generator=torch.Generator().manual_seed(5)) * 2.7726)
+    a = (dt * A).contiguous()
+    xr, ar = x.float().requires_grad_(True), a.clone().requires_grad_(True)
+    br, cr = b.float().requires_grad_(True), c.float().requires_grad_(True)
+    be, ce = (br.expand(B, T, H, N), cr.expand(B, T, H, N)) if G == 1 else (br, cr)
+    y_ref = orc.ssd_scan_ops_default(xr, ar, be, ce, Q)
+    dy = randn((B, T, H, P), 6).bfloat16()
+    (y_ref * dy.float()).sum().backward()
+    scan = pm.SsdScanBf16(x.cuda(), a.cuda(), b.cuda(), c.cuda(), Q)
+    y, fs = scan.forward(want_final_state=True)
+    assert y.dtype == torch.bfloat16 and fs.dtype == torch.float32
+    assert_close(y.float(), y_ref, tol=BF16_TOL, what="y")
+    dx, da, db, dc = scan.backward(dy.cuda())
+    assert_close(dx.float(), xr.grad, tol=BF16_TOL, what="dx")
+    assert_close(da, ar.grad, tol=BF16_TOL, what="da")
+    assert_close(db.float(), br.grad, tol=BF16_TOL, what="db")
+    assert_close(dc.float(), cr.grad, tol=BF16_TOL, what="dc")

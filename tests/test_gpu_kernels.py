@@ -44,8 +44,9 @@ def test_gemm_simt(pm, M, N, K, ta, tb):
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (300, 200, 100), (128, 552, 128), (64, 40, 36), (4, 8, 4),
                                    (516, 132, 260), (2048, 384, 768)])
 @pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0), (1, 1)])
-def test_gemm_tcgen05_3xtf32(pm, M, N, K, ta, tb):
-    e = _gemm_case(pm, M, N, K, ta, tb, 2, residual=(M + tb) % 2 == 0)
+@pytest.mark.parametrize("engine", [2, 3])      # 128x128 tiles / 128x64 tiles with two CTAs per SM
+def test_gemm_tcgen05_3xtf32(pm, M, N, K, ta, tb, engine):
+    e = _gemm_case(pm, M, N, K, ta, tb, engine, residual=(M + tb) % 2 == 0)
     assert pm.device_status() == 0
     assert e < 1e-5, e
 
