@@ -23,7 +23,7 @@ namespace {
 
 struct OpGemm64 {
   static constexpr int BN = 64;
-  static constexpr bool A_SCALE = false, B_SCALE = false;
+  static constexpr bool A_SCALE = false, B_SCALE = false, SEG_EPI = false;
   static constexpr int AUX_FLOATS = 0;
   float* aux;
   __device__ void stage(int, int) {}
@@ -44,6 +44,8 @@ struct OpGemm64 {
   }
   __device__ void a_scale4(int, int, int, int, float (&)[4]) const {}
   __device__ float b_scale(int, int, int) const { return 1.0f; }
+  __device__ void seg_accumulate(int, int, int, const float (&)[32], float (&)[32]) const {}
+  __device__ void stage_seg(int, int, int) {}
   __device__ void store(int m, int nb, const float (&v)[32]) const {
     float* crow = C + (int64_t)m * ldc + nb;
     const float* rrow = R ? R + (int64_t)m * ldc + nb : nullptr;

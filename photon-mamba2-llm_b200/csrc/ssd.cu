@@ -525,11 +525,11 @@ size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base
     size_t b = (size_t)pick_nsplit(nbcg, qt * (int)cdiv(N, BN), hpg) * nbcg * Q * N;
     size_t need = a > b ? a : b;
     if (Q % 64 == 0 && N % 32 == 0 && P % 64 == 0) {
-      // tensor-core path: masked (Q,Q) products of a few heads per pass, and the head-split dB / dC partial tiles
-      size_t tcp = (size_t)ssd_tc_dg_heads_per_pass(B, T, H, G, Q) * nbcg * Q * Q;
+      // tensor-core path: the head-split dB / dC partial tiles
       size_t dbc = (size_t)ssd_tc_dbc_nsplit_dims(B, T, H, N, G, Q) * nbcg * Q * N;
-      if (tcp > need) need = tcp;
       if (dbc > need) need = dbc;
+      size_t dgp = (size_t)ssd_tc_dg_nsplit_dims(B, T, H, G, Q) * nbcg * Q * Q;
+      if (dgp > need) need = dgp;
     }
     w.splitk = ar.take<float>(need);
     bool tcshape = Q % 64 == 0 && N % 32 == 0 && P % 64 == 0;
@@ -641,14 +641,9 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   if (tc_group) {
     {
       ProfScope prof(st, "ssd_bwd_dg_tc", 2.0 * tok * p.H * p.Q * p.P, 0.0);
-      const int hc = ssd_tc_dg_heads_per_pass(p.B, p.T, p.H, p.G, p.Q);
-      const int64_t total = (int64_t)nbcg * p.Q * p.Q;
-      for (int h0 = 0; h0 < p.hpg; h0 += hc) {
-        const int cur = min(hc, p.hpg - h0);
-        PMB_TRY(ssd_tc_dg_partials(st, in, dy, lddy, ws, h0, cur));
-        splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(ws.splitk, cur, p.Q, p.Q, 0, p.G, p.Q, ws.dG, 0, total, 128, h0 > 0);
-        PMB_LAUNCHED();
-      }
+      const int nsg = ssd_tc_dg_nsplit_dims(p.B, p.T, p.H, p.G, p.Q);
+      PMB_TRY(ssd_tc_dg(st, in, dy, lddy, ws, nsg));
+      PMB_TRY(reduce(nsg, p.Q, 0, ws.dG, 0, 128));
     }
     const int ns = ssd_tc_dbc_nsplit(in);
     {

@@ -46,7 +46,7 @@ struct TcP {
 // ------------------------------------------------------------------------------------------------
 struct TcCB {
   static constexpr int BN = 128;
-  static constexpr bool A_SCALE = false, B_SCALE = false;
+  static constexpr bool A_SCALE = false, B_SCALE = false, SEG_EPI = false;
   static constexpr int AUX_FLOATS = 0;
   float* aux;
   __device__ void stage(int, int) {}
@@ -67,6 +67,8 @@ struct TcCB {
   __device__ void b_coord(int, int kt, int n0, int& c0, int& c1, int& c2) const { c0 = kt * 32; c1 = (int)(tok0 + n0); c2 = g; }
   __device__ void a_scale4(int, int, int, int, float (&)[4]) const {}
   __device__ float b_scale(int, int, int) const { return 1.0f; }
+  __device__ void seg_accumulate(int, int, int, const float (&)[32], float (&)[32]) const {}
+  __device__ void stage_seg(int, int, int) {}
   __device__ void store(int m, int nb, const float (&v)[32]) const {
     float4* dst = reinterpret_cast<float4*>(out + (int64_t)m * p.Q + nb);
 #pragma unroll
@@ -95,7 +97,7 @@ struct HeadTile {
 template <int MODE>
 struct TcState {
   static constexpr int BN = 64;
-  static constexpr bool A_SCALE = false, B_SCALE = false;
+  static constexpr bool A_SCALE = false, B_SCALE = false, SEG_EPI = false;
   static constexpr int AUX_FLOATS = 0;
   float* aux;
   __device__ void stage(int, int) {}
@@ -115,6 +117,8 @@ struct TcState {
   __device__ void b_coord(int, int kt, int n0, int& c0, int& c1, int& c2) const { c0 = n0; c1 = (int)(tok0 + kt * 32); c2 = h; }
   __device__ void a_scale4(int, int, int, int, float (&)[4]) const {}
   __device__ float b_scale(int, int, int) const { return 1.0f; }
+  __device__ void seg_accumulate(int, int, int, const float (&)[32], float (&)[32]) const {}
+  __device__ void stage_seg(int, int, int) {}
   __device__ void store(int m, int nb, const float (&v)[32]) const {
     float4* dst = reinterpret_cast<float4*>(out + (int64_t)m * p.P + nb);
 #pragma unroll
@@ -132,7 +136,7 @@ struct TcState {
 template <int MODE>
 struct TcScan {
   static constexpr int BN = 64;
-  static constexpr bool A_SCALE = true, B_SCALE = false;
+  static constexpr bool A_SCALE = true, B_SCALE = false, SEG_EPI = false;
   static constexpr int AUX_FLOATS = 2 * TC_MAX_Q;   // [0,Q): S of this (b,c,h);  [Q,2Q): dt (1 when absent)
   float* aux;
   __device__ void stage(int tid, int nthr) {
@@ -199,6 +203,8 @@ struct TcScan {
     }
   }
   __device__ float b_scale(int, int, int) const { return 1.0f; }
+  __device__ void seg_accumulate(int, int, int, const float (&)[32], float (&)[32]) const {}
+  __device__ void stage_seg(int, int, int) {}
   __device__ void store(int m, int nb, const float (&v)[32]) const {
     if (MODE == 0) {
       const int64_t row = t.tok0 + m;
@@ -224,50 +230,65 @@ struct TcScan {
 };
 
 // ------------------------------------------------------------------------------------------------
-// R_h[t,s] = exp(S_t - S_s) [s<=t] sum_p dY_h[t,p] x_h[s,p] dt_s  per (b,c,h) into part[(b,c,g),h_local];
-// the per-group sum over heads is done by ssd's split-K reduce kernel.
+// dG[t,s] = sum_{h in group} exp(S_h,t - S_h,s) dt_h,s [s<=t] sum_p dY_h[t,p] x_h[s,p]  per (b,c,g).
+// One segment per head: its product lands in a fresh TMEM accumulator and is folded, scaled by that head's
+// decay mask, into register sums while the tensor core computes the next head (SEG_EPI).
 //   maps: 0 = dY (K-major rows t), 1 = x (K-major rows s)
 // ------------------------------------------------------------------------------------------------
 struct TcDG {
   static constexpr int BN = 128;
-  static constexpr bool A_SCALE = false, B_SCALE = false;
-  static constexpr int AUX_FLOATS = 2 * TC_MAX_Q;
+  static constexpr bool A_SCALE = false, B_SCALE = false, SEG_EPI = true;
+  static constexpr int AUX_FLOATS = 4 * TC_MAX_Q;   // two halves of [S (Q) | dt (Q)], one per segment in flight
   float* aux;
-  __device__ void stage(int tid, int nthr) {
-    for (int q = tid; q < p.Q; q += nthr) { aux[q] = t.sp[q]; aux[p.Q + q] = p.dtv(t.tok0 + q, t.h); }
+  __device__ void stage(int, int) {}
+  __device__ void stage_seg(int s, int tid, int nthr) {
+    const int h = head_of(s);
+    float* dst = aux + (s & 1) * 2 * p.Q;
+    const float* sp = p.S + ((int64_t)bb * p.H + h) * p.T + (int64_t)cc * p.Q;
+    for (int q = tid; q < p.Q; q += nthr) { dst[q] = sp[q]; dst[p.Q + q] = p.dtv(tok0 + q, h); }
   }
   TcP p; int Mdim, Ndim;
-  int h0, hc;                   // this pass covers heads h0 .. h0+hc-1 of every group
-  HeadTile t; float* out;
+  int bb, cc, g, split; int64_t tok0; float* out;
+  // with few (batch, chunk) pairs the heads of a group are dealt round-robin to p.nsplit CTAs whose partial
+  // tiles are summed afterwards in a fixed order
   __device__ bool init(int batch, int m0, int n0) {
     if (n0 > m0 + tcb::BM - 1) return false;
-    int hl = batch % hc; int bcg = batch / hc;
-    int g = bcg % p.G; int bc = bcg / p.G;
-    t.set(p, bc * p.H + g * p.hpg + h0 + hl);
-    out = p.part + ((int64_t)bcg * hc + hl) * p.Q * p.Q;
+    split = batch % p.nsplit; batch /= p.nsplit;
+    g = batch % p.G; int bc = batch / p.G; cc = bc % p.nc; bb = bc / p.nc;
+    tok0 = (int64_t)bc * p.Q;
+    out = p.nsplit > 1 ? p.part + (int64_t)blockIdx.z * p.Q * p.Q : p.dG + (int64_t)batch * p.Q * p.Q;
     return true;
   }
-  __device__ int nseg() const { return 1; }
+  __device__ int nseg() const { return (p.hpg - split + p.nsplit - 1) / p.nsplit; }
+  __device__ int head_of(int s) const { return g * p.hpg + split + s * p.nsplit; }
   __device__ void seg(int, int, int, int& kt0, int& kt1, int& am, int& bm, int& amn, int& bmn) const {
     kt0 = 0; kt1 = p.P / 32; am = 0; bm = 1; amn = 0; bmn = 0;
   }
-  __device__ void a_coord(int, int kt, int m0, int& c0, int& c1, int& c2) const { c0 = kt * 32; c1 = (int)(t.tok0 + m0); c2 = t.h; }
-  __device__ void b_coord(int, int kt, int n0, int& c0, int& c1, int& c2) const { c0 = kt * 32; c1 = (int)(t.tok0 + n0); c2 = t.h; }
+  __device__ void a_coord(int s, int kt, int m0, int& c0, int& c1, int& c2) const { c0 = kt * 32; c1 = (int)(tok0 + m0); c2 = head_of(s); }
+  __device__ void b_coord(int s, int kt, int n0, int& c0, int& c1, int& c2) const { c0 = kt * 32; c1 = (int)(tok0 + n0); c2 = head_of(s); }
   __device__ void a_scale4(int, int, int, int, float (&)[4]) const {}
   __device__ float b_scale(int, int, int) const { return 1.0f; }
-  __device__ void store(int m, int nb, const float (&v)[32]) const {
-    float* dst = out + (int64_t)m * p.Q + nb;
-    const float sm = aux[m];
+  __device__ void seg_accumulate(int s, int m, int nb, const float (&v)[32], float (&acc)[32]) const {
+    if (m >= p.Q || nb > m) return;
+    const float* sv = aux + (s & 1) * 2 * p.Q;
+    const float* dv = sv + p.Q;
+    const float sm = sv[m];
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
-      float o[4];
+      const float4 s4 = *reinterpret_cast<const float4*>(sv + nb + j);
+      const float4 d4 = *reinterpret_cast<const float4*>(dv + nb + j);
+      const float ss[4] = {s4.x, s4.y, s4.z, s4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        int s = nb + j + e;
-        o[e] = (s <= m) ? v[j + e] * __expf(sm - aux[s]) * aux[p.Q + s] : 0.0f;
+        const float w = (nb + j + e <= m) ? __expf(sm - ss[e]) * dd[e] : 0.0f;
+        acc[j + e] = fmaf(v[j + e], w, acc[j + e]);
       }
-      *reinterpret_cast<float4*>(dst + j) = make_float4(o[0], o[1], o[2], o[3]);
     }
+  }
+  __device__ void store(int m, int nb, const float (&v)[32]) const {
+    float4* dst = reinterpret_cast<float4*>(out + (int64_t)m * p.Q + nb);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
   }
 };
 
@@ -282,7 +303,7 @@ struct TcDG {
 template <int MODE, int BN_>
 struct TcDBC {
   static constexpr int BN = BN_;
-  static constexpr bool A_SCALE = false, B_SCALE = false;
+  static constexpr bool A_SCALE = false, B_SCALE = false, SEG_EPI = false;
   static constexpr int AUX_FLOATS = 0;
   float* aux;
   __device__ void stage(int, int) {}
@@ -322,6 +343,8 @@ struct TcDBC {
   }
   __device__ void a_scale4(int, int, int, int, float (&)[4]) const {}
   __device__ float b_scale(int, int, int) const { return 1.0f; }
+  __device__ void seg_accumulate(int, int, int, const float (&)[32], float (&)[32]) const {}
+  __device__ void stage_seg(int, int, int) {}
   __device__ void store(int m, int nb, const float (&v)[32]) const {
     float* base = p.nsplit > 1 ? pout + (int64_t)m * Ndim + nb
                                : (MODE == 0 ? p.dc : p.db) + (tok0 + m) * p.lddbc + g * p.N + nb;
@@ -494,27 +517,24 @@ pmb_status ssd_tc_dx(cudaStream_t st, const SsdIn& in, const float* dy, int64_t 
   return tcb::launch(st, ms, mk<TcScan<1>>(p, p.Q, p.P), p.B * p.nc * p.H, status_ptr());
 }
 
-// Heads per pass of the dG computation: the per-head masked products are staged in ws.splitk before the
-// per-group sum, and that staging area is capped at 2^26 floats.
-int ssd_tc_dg_heads_per_pass(int B, int T, int H, int G, int Q) {
-  int64_t per_head = (int64_t)B * (T / Q) * G * Q * Q;
-  int64_t hc = ((int64_t)1 << 26) / per_head;
-  int hpg = H / G;
-  if (hc < 1) hc = 1;
-  return (int)(hc > hpg ? hpg : hc);
+int ssd_tc_dg_nsplit_dims(int B, int T, int H, int G, int Q) {
+  int nbcg = B * (T / Q) * G, hpg = H / G;
+  int qt = (int)cdiv(Q, tcb::BM);
+  int want = (int)cdiv(2 * 148, (int64_t)nbcg * (qt * (qt + 1) / 2));
+  if (want < 1) want = 1;
+  return want > hpg ? hpg : want;
 }
 
-// Writes the masked products of heads h0..h0+hc-1 of every group into ws.splitk (hc tiles per group); the caller reduces them.
-pmb_status ssd_tc_dg_partials(cudaStream_t st, const SsdIn& in, const float* dy, int64_t lddy, const SsdWs& ws, int h0, int hc) {
+// dG for every (b,c,g): heads are summed inside the CTA (nsplit CTAs per group, partial tiles in ws.splitk when > 1).
+pmb_status ssd_tc_dg(cudaStream_t st, const SsdIn& in, const float* dy, int64_t lddy, const SsdWs& ws, int nsplit) {
   TcP p = make_p(in, ws);
+  p.nsplit = nsplit;
   MapSet ms{};
   int64_t tok = (int64_t)p.B * p.T;
   PMB_TRY(get_map(&ms.m[0], dy, p.P, tok, p.H, lddy, p.P, 32, 128, false));
   PMB_TRY(get_map(&ms.m[1], in.x, p.P, tok, p.H, in.ldx, p.P, 32, 128, false));
   ms.m[2] = ms.m[0]; ms.m[3] = ms.m[0];
-  TcDG op = mk<TcDG>(p, p.Q, p.Q);
-  op.h0 = h0; op.hc = hc;
-  return tcb::launch(st, ms, op, p.B * p.nc * p.G * hc, status_ptr());
+  return tcb::launch(st, ms, mk<TcDG>(p, p.Q, p.Q), p.B * p.nc * p.G * nsplit, status_ptr());
 }
 
 // Number of head splits for the per-group dB / dC contractions: enough CTAs to fill the GPU twice.

@@ -24,6 +24,11 @@
 //        an element that must not contribute is set to exactly 0 whatever was loaded
 //   float b_scale(int s, int n, int k)                            (only if B_SCALE)
 //   void store(int m, int nb, const float (&v)[32])  row m, columns nb..nb+31 (caller-checked m < Mdim)
+//   static constexpr bool SEG_EPI: when true every segment gets a fresh TMEM accumulator (two are alternated) and the
+//        transform warps fold it into per-thread registers with
+//        void seg_accumulate(int s, int m, int nb, const float (&v)[32], float (&acc)[32])
+//        while the tensor core already works on the next segment; store() then receives the register sums;
+//        void stage_seg(int s, int tid, int nthreads) fills the segment's half of `aux` (two halves alternate)
 //   static constexpr int AUX_FLOATS; float* aux; void stage(int tid, int nthreads)
 //        per-CTA vectors (cumulative sums, dt) copied once into shared memory at `aux` before the pipeline
 //        starts, so that the scale functors and the epilogue read them with shared-memory latency
@@ -83,7 +88,9 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
   auto split_bar = [&](int s) { return bars + 8u * (STAGES + s); };
   auto empty_bar = [&](int s) { return bars + 8u * (2 * STAGES + s); };
   const uint32_t accum_bar = bars + 8u * (3 * STAGES);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tiles_ptr + STAGES * G::STAGE_BYTES + 8 * (3 * STAGES + 1));
+  auto seg_bar = [&](int b) { return bars + 8u * (3 * STAGES + 1 + b); };    // segment's MMAs complete (SEG_EPI)
+  auto free_bar = [&](int b) { return bars + 8u * (3 * STAGES + 3 + b); };   // TMEM buffer drained (SEG_EPI)
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tiles_ptr + STAGES * G::STAGE_BYTES + 8 * (3 * STAGES + 5));
   volatile uint32_t* abort_flag = tmem_slot + 1;
   op.aux = reinterpret_cast<float*>(tiles_ptr + G::RING_BYTES + 256);
 
@@ -100,11 +107,12 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(seg_bar(b), 1); mbar_init(free_bar(b), 4); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr int TMEM_COLS = (BN < 32 ? 32 : BN) * (Op::SEG_EPI ? 2 : 1);
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -164,6 +172,12 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
         const uint32_t a_kstep = a_mn ? 1024 : 32, b_kstep = b_mn ? 1024 : 32;
         const uint32_t a_sbo = a_mn ? 512 : 1024, b_sbo = b_mn ? 512 : 1024;
         const uint32_t a_lt = a_mn ? 1 : 2, b_lt = b_mn ? 1 : 2;
+        uint32_t tmem_d = tmem_acc;
+        if (Op::SEG_EPI) {
+          tmem_d = tmem_acc + (uint32_t)((sg & 1) * BN);
+          if (sg >= 2 && !mbar_wait(free_bar(sg & 1), (uint32_t)(((sg >> 1) - 1) & 1))) { atomicOr(status, 32u); *abort_flag = 1; stop = true; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
         for (int kt = kt0; kt < kt1; ++kt, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -175,12 +189,14 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
           for (int k = 0; k < BK / 8; ++k) {
             const uint64_t dah = make_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lt), dbh = make_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lt);
             const uint64_t dal = make_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lt), dbl = make_desc(b_lo + k * b_kstep, b_lbo, b_sbo, b_lt);
-            mma_tf32(tmem_acc, dal, dbh, idesc, (it > 0 || k > 0) ? 1u : 0u);
-            mma_tf32(tmem_acc, dah, dbl, idesc, 1u);
-            mma_tf32(tmem_acc, dah, dbh, idesc, 1u);
+            const bool first = Op::SEG_EPI ? (kt == kt0 && k == 0) : (it == 0 && k == 0);
+            mma_tf32(tmem_d, dal, dbh, idesc, first ? 0u : 1u);
+            mma_tf32(tmem_d, dah, dbl, idesc, 1u);
+            mma_tf32(tmem_d, dah, dbh, idesc, 1u);
           }
           umma_commit(empty_bar(s));
         }
+        if (Op::SEG_EPI && !stop) umma_commit(seg_bar(sg & 1));
       }
       umma_commit(accum_bar);
     }
@@ -189,9 +205,45 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
     const int st = threadIdx.x - 64;
     bool ok = true;
     int it = 0;
+    const int lane_base = (warp & 3) * 32;
+    const int m = m0 + lane_base + lane;
+    float racc[Op::SEG_EPI ? BN / 32 : 1][32];
+    if (Op::SEG_EPI) {
+#pragma unroll
+      for (int c = 0; c < (Op::SEG_EPI ? BN / 32 : 1); ++c)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) racc[c][j] = 0.0f;
+    }
+    // folds the finished accumulator of segment j into the register sums and hands its TMEM buffer back
+    auto seg_epilogue = [&](int j) -> bool {
+      const int b = j & 1;
+      const bool done = __all_sync(0xffffffffu, mbar_wait(seg_bar(b), (uint32_t)((j >> 1) & 1)));
+      if (!done) { if (lane == 0) { atomicOr(status, 64u); *abort_flag = 1; } return false; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < (Op::SEG_EPI ? BN / 32 : 1); ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_acc + (uint32_t)(b * BN) + ((uint32_t)lane_base << 16) + (uint32_t)(c * 32), r);
+        float v[32];
+#pragma unroll
+        for (int q = 0; q < 32; ++q) v[q] = __uint_as_float(r[q]);
+        op.seg_accumulate(j, m, n0 + c * 32, v, racc[c]);
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(free_bar(b));
+      return true;
+    };
     for (int sg = 0; sg < nseg && ok; ++sg) {
       int kt0, kt1, amap, bmap, a_mn, b_mn;
       op.seg(sg, m0, n0, kt0, kt1, amap, bmap, a_mn, b_mn);
+      if (Op::SEG_EPI) {
+        // per-segment vectors for seg_accumulate go to one of two aux buffers; the barriers (transform warps only)
+        // keep a fast warp from overwriting a buffer that a slower warp still reads for segment sg-2
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        op.stage_seg(sg, st, 128);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
       for (int kt = kt0; kt < kt1; ++kt, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
@@ -251,23 +303,30 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
         __syncwarp();
         if (lane == 0) mbar_arrive(split_bar(s));
       }
+      // while the tensor core works on segment sg, fold segment sg-1
+      if (Op::SEG_EPI && ok && sg >= 1) ok = seg_epilogue(sg - 1);
     }
+    if (Op::SEG_EPI && ok && nseg >= 1) ok = seg_epilogue(nseg - 1);
     const bool acc_ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0));
     if (!acc_ok && lane == 0) { atomicOr(status, 8u); *abort_flag = 1; }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const bool aborted = __any_sync(0xffffffffu, *abort_flag != 0);
     if (ok && acc_ok && !aborted) {
-      const int lane_base = (warp & 3) * 32;
-      const int m = m0 + lane_base + lane;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_acc + ((uint32_t)lane_base << 16) + (uint32_t)c0, r);
-        if (m < op.Mdim && n0 + c0 < op.Ndim) {
-          float v[32];
+      if (Op::SEG_EPI) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          op.store(m, n0 + c0, v);
+        for (int c = 0; c < (Op::SEG_EPI ? BN / 32 : 1); ++c)
+          if (m < op.Mdim && n0 + c * 32 < op.Ndim) op.store(m, n0 + c * 32, racc[c]);
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_acc + ((uint32_t)lane_base << 16) + (uint32_t)c0, r);
+          if (m < op.Mdim && n0 + c0 < op.Ndim) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            op.store(m, n0 + c0, v);
+          }
         }
       }
     }
