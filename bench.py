@@ -32,7 +32,10 @@ WORKLOADS = {
     "c4_flat100m_bf16_b8_t2048": (24, 768, 64, 24, 64, 256, 50257, 8, 2048),
     "c4_flat100m_bf16_b8_t8192": (24, 768, 64, 24, 64, 256, 50257, 8, 8192),
 }
-BF16_WORKLOADS = {"c4_flat100m_bf16_b8_t2048", "c4_flat100m_bf16_b8_t8192"}
+# BASELINE configs[2]: two 12-layer stacks (token rate and 1/4 rate), bf16 storage, batch 8 x seq 1024
+HIER_WORKLOADS = {"c3_two_level_100m_bf16_b8_t1024": (12, 12, 4)}
+WORKLOADS["c3_two_level_100m_bf16_b8_t1024"] = (12, 768, 64, 24, 64, 256, 50257, 8, 1024)
+BF16_WORKLOADS = {"c3_two_level_100m_bf16_b8_t1024", "c4_flat100m_bf16_b8_t2048", "c4_flat100m_bf16_b8_t8192"}
 DEFAULT_WORKLOAD = "c2_flat100m_fp32_b4_t512"
 
 
@@ -200,9 +203,20 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = pm_b200.Mamba2Config(d_model=D, d_state=N, d_head=P, n_heads=H, n_groups=1, d_conv=4, block_len=Q)
     bf16 = w in BF16_WORKLOADS
-    lm = pm_b200.FlatMamba(cfg, L, V, B, T, compute_dtype=torch.bfloat16 if bf16 else torch.float32)
-    embed, layers = make_weights(w)
-    lm.load(embed.cuda(), [{k: v.cuda() for k, v in p.items()} for p in layers])
+    hier = HIER_WORKLOADS.get(w)
+    if hier:
+        L0, L1, grp = hier
+        lm = pm_b200.FlatMamba(cfg, L0, V, B, T, compute_dtype=torch.bfloat16 if bf16 else torch.float32, level1_layers=L1, group=grp)
+        L = L0 + L1
+        WORKLOADS[w] = (L,) + WORKLOADS[w][1:]
+        embed, layers = make_weights(w)
+        gw = torch.Generator(); gw.manual_seed(4321)
+        wproj = (torch.rand(D, D, generator=gw) * 2 - 1) / D ** 0.5
+        lm.load(embed.cuda(), [{k: v.cuda() for k, v in p.items()} for p in layers], wproj=wproj.cuda())
+    else:
+        lm = pm_b200.FlatMamba(cfg, L, V, B, T, compute_dtype=torch.bfloat16 if bf16 else torch.float32)
+        embed, layers = make_weights(w)
+        lm.load(embed.cuda(), [{k: v.cuda() for k, v in p.items()} for p in layers])
     del embed, layers
 
     # data-parallel gradient averaging: one bucket per layer, enqueued on a side stream from the library's

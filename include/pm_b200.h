@@ -262,9 +262,18 @@ pmb_status pmb_lm_create(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t
  * flat.rs:74-78); parameters and gradients stay fp32. */
 pmb_status pmb_lm_create_dtype(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t vocab,
                                int32_t batch, int32_t seqlen, int32_t bf16_storage, pmb_lm** out);
+/* Two-level variant (BASELINE config 3; built from the same blocks, no counterpart wiring in the reference, whose
+ * PHOTON glue is crates/pm-core/src/model.rs): level 0 = n_layers_level0 blocks at token rate; groups of `group`
+ * hidden states are mean-pooled and projected by a (D,D) matrix into level 1 (n_layers_level1 blocks at 1/group
+ * rate); level-1 outputs are repeated `group` times, shifted by one group, and added back before the tied head.
+ * Flat parameter layout: embedding, level-0 layers, projection, level-1 layers; pmb_lm_param_offset(lm, -2, 0)
+ * gives the projection, layer indices run over both levels.  seqlen/group must satisfy the block's chunk rules. */
+pmb_status pmb_lm_create_hier(const pmb_mamba2_config* cfg, int32_t n_layers_level0, int32_t n_layers_level1,
+                              int32_t group, int32_t vocab, int32_t batch, int32_t seqlen, int32_t bf16_storage,
+                              pmb_lm** out);
 void       pmb_lm_destroy(pmb_lm* lm);
 int64_t    pmb_lm_param_count(const pmb_lm* lm);                 /* elements in the flat buffer (with padding) */
-int64_t    pmb_lm_param_offset(const pmb_lm* lm, int32_t layer, int32_t which); /* layer=-1: embedding; which 0..7 */
+int64_t    pmb_lm_param_offset(const pmb_lm* lm, int32_t layer, int32_t which); /* layer=-1: embedding, -2: level-1 projection; which 0..7 */
 float*     pmb_lm_params(pmb_lm* lm);                            /* device pointer, pmb_lm_param_count() floats */
 float*     pmb_lm_grads(pmb_lm* lm);                             /* device pointer, same layout */
 int64_t    pmb_lm_activation_bytes(const pmb_lm* lm);            /* stored activations + transient workspace */

@@ -376,6 +376,26 @@ def lm_loss(embed: torch.Tensor, layers: list, cfg: Mamba2Config, ids: torch.Ten
     return loss
 
 
+def hier_lm_loss(embed, wproj, layers0, layers1, cfg, ids, targets, group=4, cdt=torch.float32):
+    """Two-level LM of BASELINE config 3 (defined by the benchmark spec, not by the reference's PHOTON glue):
+    level 0 = Mamba2 stack at token rate; groups of `group` hidden states are mean-pooled and linearly projected
+    into level 1, a Mamba2 stack at 1/group rate; its outputs are repeated `group` times, shifted by one group
+    (causal), and added to the level-0 output before the tied LM head.  Blocks and stacks are the reference's
+    (block.rs:118-226, encoder.rs:52-62); the loss is the mean CE of pm-train/src/loss.rs:39-69."""
+    x = embed[ids].to(cdt)
+    h0 = stack_forward(layers0, cfg, x)
+    Bn, T, D = h0.shape
+    pooled = h0.float().reshape(Bn, T // group, group, D).mean(2).to(cdt)
+    u = pooled @ wproj.to(cdt)
+    h1 = stack_forward(layers1, cfg, u)
+    up = torch.repeat_interleave(h1, group, dim=1)
+    up = torch.cat([torch.zeros(Bn, group, D, dtype=up.dtype), up[:, : T - group]], dim=1)
+    hidden = (h0.float() + up.float()).to(cdt)
+    logits = hidden @ embed.to(cdt).transpose(0, 1)
+    logp = torch.log_softmax(logits.float(), dim=-1)
+    return -logp.gather(-1, targets.unsqueeze(-1)).mean()
+
+
 def lcg_batch(state: int, b: int, t: int, vocab: int):
     """Seeded uniform token batch, targets = ids rotated left by one within each row
     (crates/pm-cli/src/train_cmd.rs:523-539).  Returns (ids, targets, new_state)."""

@@ -101,6 +101,50 @@ __global__ void __launch_bounds__(256) cross_entropy_kernel(float* __restrict__ 
   }
 }
 
+// ---- BASELINE config 3 wiring: mean-pool groups of GROUP tokens down, repeat up with a one-group causal shift.
+// Storage type T is float or bf16 bits (uint16_t); arithmetic in fp32.
+template <class T> __device__ __forceinline__ float ld_act(const T* p);
+template <> __device__ __forceinline__ float ld_act<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ld_act<uint16_t>(const uint16_t* p) { return __uint_as_float((uint32_t)(*p) << 16); }
+template <class T> __device__ __forceinline__ void st_act(T* p, float v);
+template <> __device__ __forceinline__ void st_act<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void st_act<uint16_t>(uint16_t* p, float v) {
+  uint32_t u = __float_as_uint(v);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  *p = (uint16_t)(u >> 16);
+}
+
+// mode 0: out[b,g,:] = mean_j in[b,GROUP*g+j,:]                      (pool, out has T/GROUP rows per sequence)
+// mode 1: out[b,t,:] = a[b,t,:] + (t/GROUP >= 1 ? in[b,t/GROUP-1,:] : 0)   (shifted repeat, added to a)
+// mode 2: out[b,g,:] = (g+1 < T/GROUP) ? sum_j in[b,GROUP*(g+1)+j,:] : 0   (adjoint of mode 1 w.r.t. `in`)
+// mode 3: out[b,t,:] = a[b,t,:] + in[b,t/GROUP,:] / GROUP                   (adjoint of mode 0, accumulated onto a)
+template <class T>
+__global__ void hier_kernel(const T* __restrict__ in, const T* __restrict__ a, T* __restrict__ out, int B, int Tfull, int D, int GROUP, int mode) {
+  const int Tg = Tfull / GROUP;
+  const bool coarse_out = (mode == 0 || mode == 2);
+  const int64_t rows = (int64_t)B * (coarse_out ? Tg : Tfull);
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * D) return;
+  const int c = (int)(i % D); const int64_t r = i / D;
+  const int per = coarse_out ? Tg : Tfull;
+  const int b = (int)(r / per), t = (int)(r % per);
+  float v = 0.0f;
+  if (mode == 0) {
+    for (int j = 0; j < GROUP; ++j) v += ld_act(in + ((int64_t)b * Tfull + (int64_t)t * GROUP + j) * D + c);
+    v /= (float)GROUP;
+  } else if (mode == 1) {
+    v = ld_act(a + i);
+    const int g = t / GROUP;
+    if (g >= 1) v += ld_act(in + ((int64_t)b * Tg + g - 1) * D + c);
+  } else if (mode == 2) {
+    if (t + 1 < Tg)
+      for (int j = 0; j < GROUP; ++j) v += ld_act(in + ((int64_t)b * Tfull + (int64_t)(t + 1) * GROUP + j) * D + c);
+  } else {
+    v = ld_act(a + i) + ld_act(in + ((int64_t)b * Tg + t / GROUP) * D + c) / (float)GROUP;
+  }
+  st_act(out + i, v);
+}
+
 __global__ void __launch_bounds__(256) mean_kernel(const float* __restrict__ v, int64_t n, float* __restrict__ out) {
   __shared__ float red[32];
   float s = 0.0f;
@@ -135,6 +179,15 @@ struct pmb_lm {
   uint16_t* params16 = nullptr;   // bf16 copy of the flat parameter buffer, refreshed every step
   uint16_t* dlogits16 = nullptr;  // (tile_rows, Vp)
   std::vector<Weights16> lw16;
+  // hierarchical variant (L1 > 0): level 0 = layers [0,L0) at token rate, level 1 = layers [L0,L0+L1) at 1/group rate
+  int L0 = 0, L1 = 0, group = 1;
+  Dims d1;                    // level-1 dims (seqlen / group)
+  int64_t off_proj = -1;      // (D,D) projection into level 1
+  void* saved1 = nullptr;     // (L1+1) x (M/group, D)
+  void* pooled = nullptr;     // (M/group, D)  mean-pooled level-0 output
+  void* dpool = nullptr;      // (M/group, D)  gradient w.r.t. pooled
+  void* dh1 = nullptr;        // (M/group, D)
+  void* hsum = nullptr;       // (M, D)  h0 + shifted repeat of h1
   int64_t act_bytes = 0;
   std::vector<pmb_block_params> lp;
   std::vector<pmb_block_grads> lg;
@@ -152,38 +205,41 @@ static int64_t tensor_elems(const Dims& d, int which) {
   return 0;
 }
 
-extern "C" pmb_status pmb_lm_create(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t vocab, int32_t batch,
-                                    int32_t seqlen, pmb_lm** out) {
-  return pmb_lm_create_dtype(cfg, n_layers, vocab, batch, seqlen, 0, out);
-}
-
-extern "C" pmb_status pmb_lm_create_dtype(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t vocab, int32_t batch,
-                                          int32_t seqlen, int32_t bf16_storage, pmb_lm** out) {
+static pmb_status lm_create_impl(const pmb_mamba2_config* cfg, int L0, int L1, int group, int vocab, int batch, int seqlen,
+                                 int bf16_storage, pmb_lm** out) {
   if (!out) return fail(PMB_ERR_ARG, "lm_create: out is NULL");
   *out = nullptr;
   Dims d;
   PMB_TRY(make_dims(cfg, batch, seqlen, &d));
   if (bf16_storage && ((d.D % 8) || (d.J % 8) || (d.I % 8)))
     return fail(PMB_ERR_SHAPE, "lm_create: bf16 storage needs d_model, d_inner and in_proj_dim to be multiples of 8");
-  if (n_layers <= 0 || vocab <= 0) return fail(PMB_ERR_SHAPE, "lm_create: n_layers and vocab must be positive");
+  if (L0 <= 0 || L1 < 0 || vocab <= 0) return fail(PMB_ERR_SHAPE, "lm_create: layer counts and vocab must be positive");
   if (d.D % 4 != 0) return fail(PMB_ERR_SHAPE, "lm_create: d_model must be a multiple of 4");
+  if (L1 > 0 && (group < 2 || seqlen % group != 0)) return fail(PMB_ERR_SHAPE, "lm_create: seqlen %d is not a multiple of the pooling group %d", seqlen, group);
+  const int n_layers = L0 + L1;
   pmb_lm* lm = new pmb_lm();
-  lm->cfg = *cfg; lm->d = d; lm->L = n_layers; lm->V = vocab; lm->bf16 = bf16_storage ? 1 : 0;
+  lm->cfg = *cfg; lm->d = d; lm->L = n_layers; lm->L0 = L0; lm->L1 = L1; lm->group = L1 > 0 ? group : 1;
+  lm->V = vocab; lm->bf16 = bf16_storage ? 1 : 0;
+  if (L1 > 0) PMB_TRY(make_dims(cfg, batch, seqlen / group, &lm->d1));
   lm->Vp = (int)align_up((size_t)vocab, 64);
   lm->tile_rows = (int)(d.M < LM_TILE_ROWS ? d.M : LM_TILE_ROWS);
   int64_t o = 0;
   auto place = [&](int64_t n) { int64_t at = o; o += (int64_t)align_up((size_t)n, 64); return at; };
   lm->off.push_back(place((int64_t)vocab * d.D));
-  for (int l = 0; l < n_layers; ++l)
+  for (int l = 0; l < n_layers; ++l) {
+    if (L1 > 0 && l == L0) lm->off_proj = place((int64_t)d.D * d.D);
     for (int w = 0; w < 8; ++w) lm->off.push_back(place(tensor_elems(d, w)));
+  }
   lm->n_params = o;
   lm->ws_bytes = block_ws_bytes(d, lm->bf16 != 0);
-  size_t slot = (size_t)d.M * d.D * (lm->bf16 ? 2 : 4);
+  const size_t esz = lm->bf16 ? 2 : 4;
+  size_t slot = (size_t)d.M * d.D * esz;
+  size_t slot1 = L1 > 0 ? (size_t)lm->d1.M * d.D * esz : 0;
   auto alloc = [&](void** p, size_t bytes) -> bool { return cudaMalloc(p, bytes) == cudaSuccess; };
   bool ok = true;
   ok = ok && alloc((void**)&lm->params, (size_t)o * 4);
   ok = ok && alloc((void**)&lm->grads, (size_t)o * 4);
-  ok = ok && alloc((void**)&lm->saved, slot * (n_layers + 1));
+  ok = ok && alloc((void**)&lm->saved, slot * (L0 + 1));
   ok = ok && alloc((void**)&lm->dhidden, slot);
   ok = ok && alloc((void**)&lm->logits, (size_t)lm->tile_rows * lm->Vp * 4);
   ok = ok && alloc((void**)&lm->row_loss, (size_t)d.M * 4);
@@ -196,6 +252,13 @@ extern "C" pmb_status pmb_lm_create_dtype(const pmb_mamba2_config* cfg, int32_t 
     ok = ok && alloc((void**)&lm->params16, (size_t)o * 2);
     ok = ok && alloc((void**)&lm->dlogits16, (size_t)lm->tile_rows * lm->Vp * 2);
   }
+  if (L1 > 0) {
+    ok = ok && alloc(&lm->saved1, slot1 * (L1 + 1));
+    ok = ok && alloc(&lm->pooled, slot1);
+    ok = ok && alloc(&lm->dpool, slot1);
+    ok = ok && alloc(&lm->dh1, slot1);
+    ok = ok && alloc(&lm->hsum, slot);
+  }
   if (!ok) {
     pmb_status s = fail(PMB_ERR_CUDA, "lm_create: cudaMalloc failed: %s", cudaGetErrorString(cudaGetLastError()));
     pmb_lm_destroy(lm);
@@ -204,7 +267,8 @@ extern "C" pmb_status pmb_lm_create_dtype(const pmb_mamba2_config* cfg, int32_t 
   cudaMemset(lm->params, 0, (size_t)o * 4);
   cudaMemset(lm->grads, 0, (size_t)o * 4);
   cudaMemset(lm->bad, 0, 256);
-  lm->act_bytes = (int64_t)(slot * (n_layers + 1) + slot + (size_t)lm->tile_rows * lm->Vp * (lm->bf16 ? 6 : 4) + (size_t)d.M * 4 + lm->ws_bytes);
+  lm->act_bytes = (int64_t)(slot * (L0 + 1) + slot1 * (L1 + 1) + slot + 3 * slot1 + (L1 > 0 ? slot : 0) +
+                            (size_t)lm->tile_rows * lm->Vp * (lm->bf16 ? 6 : 4) + (size_t)d.M * 4 + lm->ws_bytes);
   lm->lp.resize(n_layers); lm->lg.resize(n_layers); lm->lw16.resize(n_layers);
   for (int l = 0; l < n_layers; ++l) {
     const int64_t* f = &lm->off[1 + 8 * l];
@@ -217,16 +281,35 @@ extern "C" pmb_status pmb_lm_create_dtype(const pmb_mamba2_config* cfg, int32_t 
   return PMB_OK;
 }
 
+extern "C" pmb_status pmb_lm_create(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t vocab, int32_t batch,
+                                    int32_t seqlen, pmb_lm** out) {
+  return lm_create_impl(cfg, n_layers, 0, 1, vocab, batch, seqlen, 0, out);
+}
+
+extern "C" pmb_status pmb_lm_create_dtype(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t vocab, int32_t batch,
+                                          int32_t seqlen, int32_t bf16_storage, pmb_lm** out) {
+  return lm_create_impl(cfg, n_layers, 0, 1, vocab, batch, seqlen, bf16_storage, out);
+}
+
+extern "C" pmb_status pmb_lm_create_hier(const pmb_mamba2_config* cfg, int32_t n_layers_level0, int32_t n_layers_level1,
+                                         int32_t group, int32_t vocab, int32_t batch, int32_t seqlen, int32_t bf16_storage,
+                                         pmb_lm** out) {
+  if (n_layers_level1 <= 0) return fail(PMB_ERR_SHAPE, "lm_create_hier: level 1 needs at least one layer");
+  return lm_create_impl(cfg, n_layers_level0, n_layers_level1, group, vocab, batch, seqlen, bf16_storage, out);
+}
+
 extern "C" void pmb_lm_destroy(pmb_lm* lm) {
   if (!lm) return;
   cudaFree(lm->params); cudaFree(lm->grads); cudaFree(lm->saved); cudaFree(lm->dhidden); cudaFree(lm->logits);
   cudaFree(lm->row_loss); cudaFree(lm->loss); cudaFree(lm->bad); cudaFree(lm->ids); cudaFree(lm->targets); cudaFree(lm->ws); cudaFree(lm->params16); cudaFree(lm->dlogits16);
+  cudaFree(lm->saved1); cudaFree(lm->pooled); cudaFree(lm->dpool); cudaFree(lm->dh1); cudaFree(lm->hsum);
   delete lm;
 }
 
 extern "C" int64_t pmb_lm_param_count(const pmb_lm* lm) { return lm ? lm->n_params : 0; }
 extern "C" int64_t pmb_lm_param_offset(const pmb_lm* lm, int32_t layer, int32_t which) {
   if (!lm) return -1;
+  if (layer == -2) return lm->off_proj;   // (D,D) projection into level 1 (hierarchical variant), else -1
   if (layer < 0) return lm->off[0];
   if (layer >= lm->L || which < 0 || which > 7) return -1;
   return lm->off[1 + 8 * layer + which];
@@ -237,11 +320,30 @@ extern "C" int64_t pmb_lm_activation_bytes(const pmb_lm* lm) { return lm ? lm->a
 extern "C" void pmb_lm_activation_detail(const pmb_lm* lm, int64_t* h_out3) {
   if (!lm || !h_out3) return;
   const size_t esz = lm->bf16 ? 2 : 4;
-  h_out3[0] = (int64_t)((size_t)lm->d.M * lm->d.D * esz * (lm->L + 1));                          // stored for backward: block inputs
+  h_out3[0] = (int64_t)((size_t)lm->d.M * lm->d.D * esz * (lm->L0 + 1) + (lm->L1 > 0 ? (size_t)lm->d1.M * lm->d.D * esz * (lm->L1 + 1) : 0));                          // stored for backward: block inputs
   h_out3[1] = (int64_t)lm->ws_bytes;                                                              // transient: one block's workspace
   h_out3[2] = (int64_t)((size_t)lm->tile_rows * lm->Vp * (lm->bf16 ? 6 : 4) + (size_t)lm->d.M * lm->d.D * esz);  // transient: logits tile, d(hidden)
 }
 extern "C" const float* pmb_lm_loss_device(const pmb_lm* lm) { return lm ? lm->loss : nullptr; }
+
+// hier_kernel launcher on the model's storage dtype
+static pmb_status hier_op(pmb_lm* lm, cudaStream_t st, const void* in, const void* a, void* out, int mode) {
+  const Dims& d = lm->d;
+  const bool coarse = (mode == 0 || mode == 2);
+  int64_t n = (coarse ? lm->d1.M : d.M) * (int64_t)d.D;
+  ProfScope prof(st, "hier_pool_repeat", 0.0, (lm->bf16 ? 2.0 : 4.0) * 3.0 * d.M * d.D / (coarse ? lm->group : 1));
+  if (lm->bf16) hier_kernel<uint16_t><<<(unsigned)cdiv(n, 256), 256, 0, st>>>((const uint16_t*)in, (const uint16_t*)a, (uint16_t*)out, d.B, d.T, d.D, lm->group, mode);
+  else hier_kernel<float><<<(unsigned)cdiv(n, 256), 256, 0, st>>>((const float*)in, (const float*)a, (float*)out, d.B, d.T, d.D, lm->group, mode);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
+// storage-dtype GEMM: C = op(A) op(B) with A, B, C in the model's activation dtype except where noted
+static pmb_status lm_gemm(pmb_lm* lm, cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
+                          const void* B16_or_f32, int64_t ldb, void* C, int64_t ldc, int out_storage) {
+  if (lm->bf16) return gemm_bf16(st, ta, tb, M, N, K, A, lda, B16_or_f32, ldb, C, ldc, nullptr, out_storage);
+  return gemm(st, ta, tb, M, N, K, (const float*)A, lda, (const float*)B16_or_f32, ldb, (float*)C, ldc, nullptr, 0);
+}
 
 extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t* d_ids, const int64_t* d_targets,
                                          pmb_layer_callback on_layer_done, void* user) {
@@ -255,7 +357,10 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
   size_t slot = (size_t)M * D;
   const bool h16 = lm->bf16 != 0;
   const size_t esz = h16 ? 2 : 4;
+  const bool hier = lm->L1 > 0;
+  const int L0 = lm->L0, L1 = lm->L1;
   const uint16_t* table16 = h16 ? lm->params16 + lm->off[0] : nullptr;
+  const Weights16* w16 = h16 ? lm->lw16.data() : nullptr;
   if (h16) {
     // the fp32 masters may have been updated by the optimizer since the last step
     PMB_TRY(cast_f32_bf16(st, lm->params, lm->params16, lm->n_params));
@@ -264,8 +369,21 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
     embedding_fwd_kernel<<<(unsigned)cdiv(M * (D / 4), 256), 256, 0, st>>>(table, d_ids, lm->saved, M, D, V, lm->bad);
   }
   PMB_LAUNCHED();
-  PMB_TRY(stack_fwd(st, d, lm->L, lm->lp.data(), h16 ? lm->lw16.data() : nullptr, lm->saved, lm->ws, lm->ws_bytes));
-  const char* hidden = reinterpret_cast<const char*>(lm->saved) + (size_t)lm->L * slot * esz;
+  PMB_TRY(stack_fwd(st, d, L0, lm->lp.data(), w16, lm->saved, lm->ws, lm->ws_bytes));
+  const char* hidden = reinterpret_cast<const char*>(lm->saved) + (size_t)L0 * slot * esz;
+  const void* wproj = nullptr;
+  if (hier) {
+    // level 1: mean-pool groups of tokens, project, run the second stack at 1/group rate, add its output back
+    // shifted by one group so that no token sees its own group's future (BASELINE config 3 wiring)
+    const int64_t M1 = lm->d1.M;
+    wproj = h16 ? (const void*)(lm->params16 + lm->off_proj) : (const void*)(lm->params + lm->off_proj);
+    PMB_TRY(hier_op(lm, st, hidden, nullptr, lm->pooled, 0));
+    PMB_TRY(lm_gemm(lm, st, 0, 0, M1, D, D, lm->pooled, D, wproj, D, lm->saved1, D, 1));
+    PMB_TRY(stack_fwd(st, lm->d1, L1, lm->lp.data() + L0, w16 ? w16 + L0 : nullptr, lm->saved1, lm->ws, lm->ws_bytes));
+    const char* h1 = reinterpret_cast<const char*>(lm->saved1) + (size_t)L1 * M1 * D * esz;
+    PMB_TRY(hier_op(lm, st, h1, hidden, lm->hsum, 1));
+    hidden = reinterpret_cast<const char*>(lm->hsum);
+  }
   char* dhid = reinterpret_cast<char*>(lm->dhidden);
   for (int64_t r0 = 0; r0 < M; r0 += lm->tile_rows) {
     int64_t rows = M - r0 < lm->tile_rows ? M - r0 : lm->tile_rows;
@@ -288,8 +406,26 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
   }
   mean_kernel<<<1, 256, 0, st>>>(lm->row_loss, M, lm->loss);
   PMB_LAUNCHED();
-  PMB_TRY(stack_bwd(st, d, lm->L, lm->lp.data(), h16 ? lm->lw16.data() : nullptr, lm->lg.data(), lm->saved, lm->dhidden, lm->ws,
-                    lm->ws_bytes, on_layer_done, user));
+  if (hier) {
+    const int64_t M1 = lm->d1.M;
+    // adjoint of the shifted repeat, level-1 backward, projection gradients, adjoint of the pooling
+    PMB_TRY(hier_op(lm, st, lm->dhidden, nullptr, lm->dh1, 2));
+    struct Shift { pmb_layer_callback cb; void* user; int base; } sh{on_layer_done, user, L0};
+    auto shifted = [](int32_t layer, void* u) { Shift* s = static_cast<Shift*>(u); if (s->cb) s->cb(layer + s->base, s->user); };
+    PMB_TRY(stack_bwd(st, lm->d1, L1, lm->lp.data() + L0, w16 ? w16 + L0 : nullptr, lm->lg.data() + L0, lm->saved1, lm->dh1, lm->ws,
+                      lm->ws_bytes, on_layer_done ? +shifted : nullptr, &sh));
+    float* dproj = lm->grads + lm->off_proj;
+    // dW_proj = pooled^T du (fp32) ;  dpool = du W_proj^T
+    if (h16) {
+      PMB_TRY(gemm_bf16(st, 1, 0, D, D, M1, lm->pooled, D, lm->dh1, D, dproj, D, nullptr, 0));
+      PMB_TRY(gemm_bf16(st, 0, 1, M1, D, D, lm->dh1, D, wproj, D, lm->dpool, D, nullptr, 1));
+    } else {
+      PMB_TRY(gemm(st, 1, 0, D, D, M1, (const float*)lm->pooled, D, (const float*)lm->dh1, D, dproj, D, nullptr, 0));
+      PMB_TRY(gemm(st, 0, 1, M1, D, D, (const float*)lm->dh1, D, (const float*)wproj, D, (float*)lm->dpool, D, nullptr, 0));
+    }
+    PMB_TRY(hier_op(lm, st, lm->dpool, lm->dhidden, lm->dhidden, 3));
+  }
+  PMB_TRY(stack_bwd(st, d, L0, lm->lp.data(), w16, lm->lg.data(), lm->saved, lm->dhidden, lm->ws, lm->ws_bytes, on_layer_done, user));
   if (h16) embedding_bwd_bf16_kernel<<<(unsigned)cdiv(M * D, 256), 256, 0, st>>>(dtable, d_ids, reinterpret_cast<const uint16_t*>(lm->dhidden), M, D, V);
   else embedding_bwd_kernel<<<(unsigned)cdiv(M * D, 256), 256, 0, st>>>(dtable, d_ids, lm->dhidden, M, D, V);
   PMB_LAUNCHED();

@@ -86,6 +86,7 @@ def _load():
         "pmb_stack_bwd": (i32, [vp, cfgp, i32, C.POINTER(_Params), C.POINTER(_Params), i32, i32, vp, vp, vp, sz, LAYER_CALLBACK, vp]),
         "pmb_lm_create": (i32, [cfgp, i32, i32, i32, i32, C.POINTER(vp)]),
         "pmb_lm_create_dtype": (i32, [cfgp, i32, i32, i32, i32, i32, C.POINTER(vp)]),
+        "pmb_lm_create_hier": (i32, [cfgp, i32, i32, i32, i32, i32, i32, i32, C.POINTER(vp)]),
         "pmb_lm_destroy": (None, [vp]),
         "pmb_lm_param_count": (i64, [vp]),
         "pmb_lm_param_offset": (i64, [vp, i32, i32]),
@@ -489,13 +490,21 @@ class FlatMamba:
     """Flat LM (tied embedding -> stack -> tied head -> mean CE).  Owns a library model handle whose flat
     parameter/gradient buffers are exposed as torch views."""
 
-    def __init__(self, config: Mamba2Config, n_layers: int, vocab: int, batch: int, seqlen: int, compute_dtype=torch.float32):
-        self.config, self.n_layers, self.vocab, self.batch, self.seqlen = config, n_layers, vocab, batch, seqlen
+    def __init__(self, config: Mamba2Config, n_layers: int, vocab: int, batch: int, seqlen: int, compute_dtype=torch.float32,
+                 level1_layers: int = 0, group: int = 4):
+        """`level1_layers > 0` selects the two-level wiring (n_layers blocks at token rate, level1_layers blocks at
+        1/group rate); layer indices then run over both levels and `view(flat, -2)` is the (D,D) projection."""
+        self.config, self.vocab, self.batch, self.seqlen = config, vocab, batch, seqlen
+        self.n_layers = n_layers + level1_layers
         if compute_dtype not in (torch.float32, torch.bfloat16):
             raise PmbError(2, f"compute dtype {compute_dtype} is not supported")
         h = C.c_void_p()
-        _check(lib.pmb_lm_create_dtype(C.byref(config.c()), n_layers, vocab, batch, seqlen,
-                                       int(compute_dtype == torch.bfloat16), C.byref(h)))
+        if level1_layers > 0:
+            _check(lib.pmb_lm_create_hier(C.byref(config.c()), n_layers, level1_layers, group, vocab, batch, seqlen,
+                                          int(compute_dtype == torch.bfloat16), C.byref(h)))
+        else:
+            _check(lib.pmb_lm_create_dtype(C.byref(config.c()), n_layers, vocab, batch, seqlen,
+                                           int(compute_dtype == torch.bfloat16), C.byref(h)))
         self._h = h
         n = lib.pmb_lm_param_count(h)
         self.flat_params = _as_tensor(lib.pmb_lm_params(h), n)
@@ -505,7 +514,9 @@ class FlatMamba:
     def view(self, flat, layer, which=0):
         """Tensor view of one parameter (layer=-1: embedding (V,D))."""
         off = lib.pmb_lm_param_offset(self._h, layer, which)
-        if layer < 0:
+        if layer == -2:
+            shp = (self.config.d_model, self.config.d_model)
+        elif layer < 0:
             shp = (self.vocab, self.config.d_model)
         else:
             shp = self.config.param_shapes()[PARAM_ORDER[which]]
@@ -514,8 +525,10 @@ class FlatMamba:
             n *= s
         return flat[off:off + n].view(*shp)
 
-    def load(self, embed, layers):
+    def load(self, embed, layers, wproj=None):
         self.view(self.flat_params, -1).copy_(embed)
+        if wproj is not None:
+            self.view(self.flat_params, -2).copy_(wproj)
         for l, p in enumerate(layers):
             for w, name in enumerate(PARAM_ORDER):
                 self.view(self.flat_params, l, w).copy_(p[name])
