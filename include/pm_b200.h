@@ -288,6 +288,17 @@ const float* pmb_lm_loss_device(const pmb_lm* lm);
 pmb_status pmb_lm_step_host(pmb_lm* lm, void* stream, const int64_t* h_ids, const int64_t* h_targets,
                             float* h_loss, pmb_layer_callback on_layer_done, void* user);
 
+/* ---- optimizer on the flat parameter buffer (outside the benchmarked metric; pm-train/src/clip.rs:13-53,
+ * pm-train/src/optim.rs:104-157).  pmb_grad_sumsq leaves sum(g^2) in a device scalar (two passes, fixed order, no
+ * host sync); pmb_adamw_step applies global-norm clipping (when max_norm > 0: g *= max_norm/norm if norm > max_norm,
+ * read from d_sumsq on the device), decoupled weight decay, the moment updates and the parameter update for all n
+ * elements in one kernel.  `step` is 1-based.  Gradients are not rewritten. */
+size_t pmb_grad_sumsq_workspace_bytes(void);
+pmb_status pmb_grad_sumsq(void* stream, int64_t n, const float* d_grads, float* d_sumsq_out, void* d_ws, size_t ws_bytes);
+pmb_status pmb_adamw_step(void* stream, int64_t n, float* d_params, const float* d_grads, float* d_m, float* d_v,
+                          float lr, float beta1, float beta2, float eps, float weight_decay, int32_t step,
+                          float max_norm, const float* d_sumsq);
+
 #ifdef __cplusplus
 }
 #endif

@@ -407,3 +407,30 @@ def lcg_batch(state: int, b: int, t: int, vocab: int):
     ids = ids.reshape(b, t)
     targets = np.roll(ids, -1, axis=1)
     return torch.from_numpy(ids), torch.from_numpy(targets.copy()), state
+
+
+# --------------------------------------------------------------------------
+# Optimizer (crates/pm-train/src/clip.rs:13-53, crates/pm-train/src/optim.rs:104-157)
+# --------------------------------------------------------------------------
+
+def clip_grad_norm(grads: list, max_norm: float) -> float:
+    """Global L2 norm over all tensors; scales them in place by max_norm / norm when the norm exceeds max_norm.
+    Returns the unclipped norm."""
+    total = sum(float((g.double() ** 2).sum()) for g in grads)
+    norm = total ** 0.5
+    if norm > max_norm and norm > 0:
+        for g in grads:
+            g.mul_(max_norm / norm)
+    return norm
+
+
+def adamw_step(params: list, grads: list, m: list, v: list, step: int, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0):
+    """One AdamW step in the reference's operation order; all tensors updated in place; `step` is 1-based."""
+    bc1, bc2 = 1.0 - beta1 ** step, 1.0 - beta2 ** step
+    for p, g, mi, vi in zip(params, grads, m, v):
+        if wd > 0.0:
+            p.mul_(1.0 - lr * wd)
+        mi.mul_(beta1).add_(g * (1.0 - beta1))
+        vi.mul_(beta2).add_(g * g * (1.0 - beta2))
+        update = (mi * (1.0 / bc1)) / (torch.sqrt(vi * (1.0 / bc2)) + eps)
+        p.sub_(update * lr)

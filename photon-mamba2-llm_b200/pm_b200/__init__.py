@@ -84,6 +84,9 @@ def _load():
         "pmb_mamba2_step": (i32, [vp, cfgp, C.POINTER(_Params), i32, vp, vp, vp, vp, vp, sz]),
         "pmb_stack_fwd_ckpt": (i32, [vp, cfgp, i32, C.POINTER(_Params), i32, i32, vp, vp, sz]),
         "pmb_stack_bwd": (i32, [vp, cfgp, i32, C.POINTER(_Params), C.POINTER(_Params), i32, i32, vp, vp, vp, sz, LAYER_CALLBACK, vp]),
+        "pmb_grad_sumsq_workspace_bytes": (sz, []),
+        "pmb_grad_sumsq": (i32, [vp, i64, vp, vp, vp, sz]),
+        "pmb_adamw_step": (i32, [vp, i64, vp, vp, vp, vp, f32, f32, f32, f32, f32, i32, f32, vp]),
         "pmb_lm_create": (i32, [cfgp, i32, i32, i32, i32, C.POINTER(vp)]),
         "pmb_lm_create_dtype": (i32, [cfgp, i32, i32, i32, i32, i32, C.POINTER(vp)]),
         "pmb_lm_create_hier": (i32, [cfgp, i32, i32, i32, i32, i32, i32, i32, C.POINTER(vp)]),
@@ -570,6 +573,29 @@ class FlatMamba:
             self.close()
         except Exception:
             pass
+
+
+class AdamW:
+    """`AdamW` + `clip_grad_norm` of the reference (pm-train/src/optim.rs:104-157, clip.rs:13-53) over one flat
+    fp32 parameter buffer; the gradient norm never leaves the device."""
+
+    def __init__(self, flat_params, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0):
+        self.p = _dev(flat_params, "flat_params")
+        self.m, self.v = torch.zeros_like(self.p), torch.zeros_like(self.p)
+        self.lr, self.beta1, self.beta2, self.eps, self.weight_decay = lr, beta1, beta2, eps, weight_decay
+        self.t = 0
+        self.sumsq = torch.zeros(1, device=self.p.device, dtype=torch.float32)
+        self._ws = torch.empty(lib.pmb_grad_sumsq_workspace_bytes(), device=self.p.device, dtype=torch.uint8)
+
+    def step(self, flat_grads, max_norm=0.0):
+        """Returns the device scalar holding sum(g^2) (its square root is the unclipped global norm)."""
+        g = _dev(flat_grads, "flat_grads")
+        self.t += 1
+        _check(lib.pmb_grad_sumsq(_stream(), g.numel(), g.data_ptr(), self.sumsq.data_ptr(), self._ws.data_ptr(), self._ws.numel()))
+        _check(lib.pmb_adamw_step(_stream(), g.numel(), self.p.data_ptr(), g.data_ptr(), self.m.data_ptr(), self.v.data_ptr(),
+                                  self.lr, self.beta1, self.beta2, self.eps, self.weight_decay, self.t, max_norm,
+                                  self.sumsq.data_ptr()))
+        return self.sumsq
 
 
 def _as_tensor(ptr: int, n: int) -> torch.Tensor:

@@ -222,3 +222,22 @@ def test_bad_arguments_raise(pm):
         pm.matmul(x.reshape(100, 16), a.reshape(100, 2))  # inner dimensions differ
     with pytest.raises(pm.PmbError):
         pm.matmul(x.reshape(100, 16).double(), x.reshape(16, 100))  # unsupported dtype is an error, never a fallback
+
+
+def test_adamw_with_global_norm_clipping(pm):
+    # three steps over a flat buffer against the oracle restatement of optim.rs / clip.rs
+    n = 100_003
+    p0 = randn((n,), 1)
+    p_ref, m_ref, v_ref = [p0.clone()], [torch.zeros(n)], [torch.zeros(n)]
+    p_dev = p0.clone().cuda()
+    opt = pm.AdamW(p_dev, lr=3e-3, weight_decay=0.1)
+    for step in range(1, 4):
+        g = randn((n,), 10 + step, 2.0 if step == 2 else 0.001)     # step 2 exceeds the clip threshold, the others do not
+        sumsq = opt.step(g.clone().cuda(), max_norm=1.0)
+        g_ref = [g.clone()]
+        norm = orc.clip_grad_norm(g_ref, 1.0)
+        orc.adamw_step(p_ref, g_ref, m_ref, v_ref, step, lr=3e-3, wd=0.1)
+        assert abs(float(sumsq.item()) ** 0.5 - norm) < 1e-4 * norm
+        assert_close(p_dev, p_ref[0], tol=1e-5, what=f"params after step {step}")
+    assert_close(opt.m, m_ref[0], what="m")       # the clip factor is formed in fp32 on the device, in fp64 by the oracle
+    assert_close(opt.v, v_ref[0], what="v")

@@ -147,3 +147,19 @@ def test_lcg_batch_targets_are_rotated_ids():
     ids, tg, _ = orc.lcg_batch(1, 2, 8, 100)
     assert ids.min() >= 0 and ids.max() < 100
     assert torch.equal(tg[:, :-1], ids[:, 1:]) and torch.equal(tg[:, -1], ids[:, 0])
+
+
+def test_adamw_restatement_matches_torch_adamw():
+    # the reference's AdamW (pm-train/src/optim.rs:104-157) is the textbook decoupled-decay form
+    p0 = _rand((1000,), 1)
+    p_ref = torch.nn.Parameter(p0.clone())
+    opt = torch.optim.AdamW([p_ref], lr=3e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.1)
+    p, m, v = [p0.clone()], [torch.zeros(1000)], [torch.zeros(1000)]
+    for step in range(1, 4):
+        g = _rand((1000,), 10 + step)
+        p_ref.grad = g.clone()
+        opt.step()
+        orc.adamw_step(p, [g.clone()], m, v, step, lr=3e-3, wd=0.1)
+    assert (p[0] - p_ref.detach()).abs().max() < 1e-6
+    g = [torch.full((4,), 3.0)]
+    assert abs(orc.clip_grad_norm(g, 1.0) - 6.0) < 1e-6 and abs(float(g[0].norm()) - 1.0) < 1e-6
