@@ -96,9 +96,15 @@ pmb_status pmb_device_status(int32_t* h_word_out);
  * trans_a = 0: A is (M,K) row-major with leading dimension lda; 1: A is stored (K,M).
  * trans_b = 0: B is (K,N) row-major with ldb;                   1: B is stored (N,K).
  * d_R (may be NULL) is added to the product (same shape/ld as C); d_R may equal d_C.
- * engine: 0 = auto (tcgen05 3xTF32 when alignment allows, else fp32 FMA; among the tcgen05 kernels the 128x64-tile
- * variant with two CTAs per SM is taken when the problem has few output tiles), 1 = fp32 FMA, 2 = tcgen05 128x128
- * tiles, 3 = tcgen05 128x64 tiles. */
+ * engine: 0 = auto, 1 = fp32 FMA, 2 = tcgen05 3xTF32 with 128x128 tiles, 3 = tcgen05 3xTF32 with 128x64 tiles,
+ * 4 = tcgen05 bf16 pairs: both operands are split into (hi, lo) bf16 pairs (hi + lo carries 16 mantissa bits) and each
+ * k-step issues hi*hi + lo*hi + hi*lo with kind::f16, fp32 accumulation.  Error ~1e-5 of the result's scale (the
+ * 3xTF32 kernels: ~1e-6), about 1.7x their speed.  Auto takes engine 4 when the operands are 16-byte aligned with row
+ * lengths that are multiples of 8, else 3xTF32 when its alignment rules hold, else FMA; the environment variable
+ * PMB_GEMM_ENGINE=tf32 keeps auto off engine 4, =simt forces FMA.  Engine 4 keeps the split operands in a
+ * library-owned scratch buffer that grows on demand (cudaMalloc inside the call); pmb_gemm_reserve_scratch() sizes it
+ * ahead of time: 4*(|A| + |B|) bytes of the largest product. */
+pmb_status pmb_gemm_reserve_scratch(size_t bytes);
 pmb_status pmb_gemm_f32(void* stream, int32_t trans_a, int32_t trans_b, int64_t M, int64_t N, int64_t K,
                         const float* d_A, int64_t lda, const float* d_B, int64_t ldb,
                         float* d_C, int64_t ldc, const float* d_R, int32_t engine);

@@ -27,10 +27,16 @@ namespace hb {
 
 using namespace tcx;
 
-constexpr int TBM = 128, TBN = 128, TBK = 64, STAGES = 6;
+constexpr int TBM = 128, TBN = 128, TBK = 64;
 constexpr int TILE_BYTES = TBM * TBK * 2;   // 16 KiB
-constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+// SPLIT = false: plain bf16 operands, a stage holds A and B (32 KiB), 6 stages.
+// SPLIT = true : every operand is a pair (hi, lo) of bf16 arrays with hi + lo ~= an fp32 value (16 mantissa bits);
+//                a stage holds A_hi, B_hi, A_lo, B_lo (64 KiB), 3 stages, and each k-step issues hi*hi + lo*hi + hi*lo.
+template <bool SPLIT> struct Cfg {
+  static constexpr int STAGES = SPLIT ? 3 : 6;
+  static constexpr int STAGE_BYTES = (SPLIT ? 4 : 2) * TILE_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
 constexpr int NTHREADS = 192;
 constexpr int TMEM_COLS = 128;
 
@@ -57,8 +63,12 @@ __device__ __forceinline__ uint16_t float_to_bf16_bits(float f) {   // round to 
   return (uint16_t)(u >> 16);
 }
 
+template <bool SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, Params p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                 const __grid_constant__ CUtensorMap mapAlo, const __grid_constant__ CUtensorMap mapBlo, Params p) {
+  constexpr int STAGES = Cfg<SPLIT>::STAGES;
+  constexpr int STAGE_BYTES = Cfg<SPLIT>::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -113,6 +123,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 #pragma unroll
           for (int j = 0; j < TBN / 64; ++j) tma_load_2d(b_dst + j * (TBK * 128), &mapB, n0 + 64 * j, k0, full_bar(s));
         }
+        if (SPLIT) {
+          const uint32_t al_dst = a_dst + 2 * TILE_BYTES, bl_dst = al_dst + TILE_BYTES;
+          if (!p.a_mn_major) {
+            tma_load_2d(al_dst, &mapAlo, k0, m0, full_bar(s));
+          } else {
+#pragma unroll
+            for (int j = 0; j < TBM / 64; ++j) tma_load_2d(al_dst + j * (TBK * 128), &mapAlo, m0 + 64 * j, k0, full_bar(s));
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d(bl_dst, &mapBlo, k0, n0, full_bar(s));
+          } else {
+#pragma unroll
+            for (int j = 0; j < TBN / 64; ++j) tma_load_2d(bl_dst + j * (TBK * 128), &mapBlo, n0 + 64 * j, k0, full_bar(s));
+          }
+        }
         armed = kt + 1;
       }
       if (*abort_flag)
@@ -137,7 +162,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 #pragma unroll
         for (int k = 0; k < TBK / 16; ++k) {
           const uint64_t da = make_desc(a_s + k * a_kstep, a_lbo, 1024, 2), db = make_desc(b_s + k * b_kstep, b_lbo, 1024, 2);
-          mma_bf16(tmem_acc, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          if (SPLIT) {
+            const uint64_t dal = make_desc(a_s + 2 * TILE_BYTES + k * a_kstep, a_lbo, 1024, 2);
+            const uint64_t dbl = make_desc(b_s + 2 * TILE_BYTES + k * b_kstep, b_lbo, 1024, 2);
+            mma_bf16(tmem_acc, dal, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+            mma_bf16(tmem_acc, da, dbl, idesc, 1u);
+            mma_bf16(tmem_acc, da, db, idesc, 1u);
+          } else {
+            mma_bf16(tmem_acc, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          }
         }
         umma_commit(empty_bar(s));
       }
@@ -259,7 +292,7 @@ pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
   if (cdiv(M, TBM) > 65535) return fail(PMB_ERR_SHAPE, "gemm_bf16: M too large");
   static bool attr_set = false;
   if (!attr_set) {
-    PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::SMEM_BYTES));
     attr_set = true;
   }
   CUtensorMap mapA, mapB;
@@ -271,12 +304,109 @@ pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
   p.C = C; p.ldc = ldc; p.R = R; p.out_bf16 = out_bf16;
   dim3 grid((unsigned)cdiv(N, TBN), (unsigned)cdiv(M, TBM));
   ProfScope prof(st, "gemm_bf16", 2.0 * M * N * K, 2.0 * ((double)M * K + (double)K * N) + (out_bf16 ? 2.0 : 4.0) * M * N * (R ? 2 : 1));
-  gemm_bf16_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(mapA, mapB, p);
+  gemm_bf16_kernel<false><<<grid, NTHREADS, Cfg<false>::SMEM_BYTES, st>>>(mapA, mapB, mapA, mapB, p);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
+// ---- fp32 GEMM through bf16 pairs ------------------------------------------------------------------
+// a = hi + lo with hi = bf16(a), lo = bf16(a - hi): 16 mantissa bits, relative representation error <= 2^-17.
+__global__ void split_f32_bf16x2_kernel(const float* __restrict__ src, int64_t rows, int64_t cols, int64_t ld,
+                                        uint16_t* __restrict__ hi, uint16_t* __restrict__ lo, int64_t ld16) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // one thread = 4 consecutive columns
+  int64_t c4 = cols / 4;
+  if (i >= rows * c4) return;
+  int64_t r = i / c4, c = (i % c4) * 4;
+  float4 v = *reinterpret_cast<const float4*>(src + r * ld + c);
+  float f[4] = {v.x, v.y, v.z, v.w};
+  uint32_t h[4], l[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    h[e] = hb::float_to_bf16_bits(f[e]);
+    l[e] = hb::float_to_bf16_bits(f[e] - hb::bf16_bits_to_float((uint16_t)h[e]));
+  }
+  *reinterpret_cast<uint2*>(hi + r * ld16 + c) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+  *reinterpret_cast<uint2*>(lo + r * ld16 + c) = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+}
+
+// Library-owned scratch for the bf16 pairs (grow-only, one per device).  pmb_gemm_reserve_scratch() sizes it up
+// front for callers that must not allocate later (e.g. before stream capture).
+static void* g_scratch[64] = {nullptr};
+static size_t g_scratch_bytes[64] = {0};
+
+pmb_status gemm_scratch(size_t bytes, void** out) {
+  int dev = 0;
+  PMB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(PMB_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  if (g_scratch_bytes[dev] < bytes) {
+    if (g_scratch[dev]) { PMB_CUDA(cudaDeviceSynchronize()); PMB_CUDA(cudaFree(g_scratch[dev])); g_scratch[dev] = nullptr; g_scratch_bytes[dev] = 0; }
+    size_t want = align_up(bytes + bytes / 4, (size_t)1 << 20);
+    PMB_CUDA(cudaMalloc(&g_scratch[dev], want));
+    g_scratch_bytes[dev] = want;
+  }
+  *out = g_scratch[dev];
+  return PMB_OK;
+}
+
+bool gemm_f32_via_bf16x2_supported(int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                                   const float* B, int64_t ldb) {
+  (void)ta; (void)tb;
+  if (M <= 0 || N <= 0 || K <= 0 || cdiv(M, hb::TBM) > 65535) return false;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return false;
+  // stored extents: A is (M,K) or (K,M), B is (K,N) or (N,K); the contiguous extent must allow 16-byte bf16 rows
+  int64_t a_cols = ta ? M : K, b_cols = tb ? K : N;
+  if ((lda & 3) || (ldb & 3) || (a_cols & 7) || (b_cols & 7)) return false;
+  return true;
+}
+
+// C (fp32) = op(A) op(B) (+ R) with fp32 operands: both are split into bf16 pairs (one elementwise pass each, into
+// the library scratch) and multiplied with three kind::f16 MMAs per k-step.  Relative accuracy ~1e-5 of the
+// result's scale; twice the tensor-core rate and less than half the shared-memory traffic of the 3xTF32 kernel.
+pmb_status gemm_f32_via_bf16x2(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                               const float* B, int64_t ldb, float* C, int64_t ldc, const float* R) {
+  using namespace hb;
+  const int64_t a_rows = ta ? K : M, a_cols = ta ? M : K, b_rows = tb ? N : K, b_cols = tb ? K : N;
+  const size_t a_el = (size_t)a_rows * a_cols, b_el = (size_t)b_rows * b_cols;
+  void* scratch = nullptr;
+  PMB_TRY(gemm_scratch((2 * a_el + 2 * b_el) * 2 + 1024, &scratch));
+  uint16_t* a_hi = static_cast<uint16_t*>(scratch);
+  uint16_t* a_lo = a_hi + align_up(a_el, 64);
+  uint16_t* b_hi = a_lo + align_up(a_el, 64);
+  uint16_t* b_lo = b_hi + align_up(b_el, 64);
+  {
+    ProfScope prof(st, "split_f32_bf16x2", 0.0, 8.0 * (a_el + b_el));
+    split_f32_bf16x2_kernel<<<(unsigned)cdiv(a_el / 4, 256), 256, 0, st>>>(A, a_rows, a_cols, lda, a_hi, a_lo, a_cols);
+    PMB_LAUNCHED();
+    split_f32_bf16x2_kernel<<<(unsigned)cdiv(b_el / 4, 256), 256, 0, st>>>(B, b_rows, b_cols, ldb, b_hi, b_lo, b_cols);
+    PMB_LAUNCHED();
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::SMEM_BYTES));
+    attr_set = true;
+  }
+  CUtensorMap mAh, mAl, mBh, mBl;
+  if (!ta) { PMB_TRY(make_map(&mAh, a_hi, K, M, a_cols, TBK, TBM)); PMB_TRY(make_map(&mAl, a_lo, K, M, a_cols, TBK, TBM)); }
+  else { PMB_TRY(make_map(&mAh, a_hi, M, K, a_cols, 64, TBK)); PMB_TRY(make_map(&mAl, a_lo, M, K, a_cols, 64, TBK)); }
+  if (tb) { PMB_TRY(make_map(&mBh, b_hi, K, N, b_cols, TBK, TBN)); PMB_TRY(make_map(&mBl, b_lo, K, N, b_cols, TBK, TBN)); }
+  else { PMB_TRY(make_map(&mBh, b_hi, N, K, b_cols, 64, TBK)); PMB_TRY(make_map(&mBl, b_lo, N, K, b_cols, 64, TBK)); }
+  Params p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.a_mn_major = ta ? 1 : 0; p.b_mn_major = tb ? 0 : 1;
+  p.C = C; p.ldc = ldc; p.R = R; p.out_bf16 = 0;
+  dim3 grid((unsigned)cdiv(N, TBN), (unsigned)cdiv(M, TBM));
+  ProfScope prof(st, "gemm_bf16x2", 2.0 * M * N * K, 4.0 * ((double)M * K + (double)K * N + (double)M * N * (R ? 2 : 1)));
+  gemm_bf16_kernel<true><<<grid, NTHREADS, Cfg<true>::SMEM_BYTES, st>>>(mAh, mBh, mAl, mBl, p);
   PMB_LAUNCHED();
   return PMB_OK;
 }
 
 }  // namespace pmb
+
+extern "C" pmb_status pmb_gemm_reserve_scratch(size_t bytes) {
+  void* p = nullptr;
+  return pmb::gemm_scratch(bytes, &p);
+}
 
 extern "C" pmb_status pmb_gemm_bf16(void* stream, int32_t trans_a, int32_t trans_b, int64_t M, int64_t N, int64_t K,
                                     const uint16_t* d_A, int64_t lda, const uint16_t* d_B, int64_t ldb,

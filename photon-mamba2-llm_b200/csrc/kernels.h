@@ -81,6 +81,10 @@ pmb_status read_clear_device_status(unsigned int* word);
 pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
                      const void* B, int64_t ldb, void* C, int64_t ldc, const void* R, int out_bf16);
 pmb_status read_clear_device_status_bf16(unsigned int* word);
+bool gemm_f32_via_bf16x2_supported(int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                                   const float* B, int64_t ldb);
+pmb_status gemm_f32_via_bf16x2(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
+                               const float* B, int64_t ldb, float* C, int64_t ldc, const float* R);
 
 // ---- block.cu.  w16 != NULL selects bf16 storage: x / residual / out / dout / dx are bf16 and the two
 // projections use the bf16 weight copies; NULL = fp32 everywhere.

@@ -51,6 +51,17 @@ def test_gemm_tcgen05_3xtf32(pm, M, N, K, ta, tb, engine):
     assert e < 1e-5, e
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (304, 200, 104), (128, 552, 128), (64, 40, 32), (8, 8, 8),
+                                   (520, 136, 264), (2048, 384, 768)])
+@pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0), (1, 1)])
+def test_gemm_tcgen05_bf16_pairs(pm, M, N, K, ta, tb):
+    """fp32 operands split into (hi, lo) bf16 pairs, three kind::f16 MMAs per k-step: 16 mantissa bits per operand,
+    so the error bound is ~2^-16 of the result's scale instead of the 3xTF32 kernel's ~2^-21."""
+    e = _gemm_case(pm, M, N, K, ta, tb, 4, residual=(M + tb) % 2 == 0)
+    assert pm.device_status() == 0
+    assert e < 3e-5, e
+
+
 def test_gemm_unaligned_is_refused_by_tc_and_taken_by_auto(pm):
     a, b = randn((33, 7), 1).cuda(), randn((7, 5), 2).cuda()
     with pytest.raises(pm.PmbError):
