@@ -58,7 +58,7 @@ def _load():
         "pmb_profile_start": (None, []),
         "pmb_profile_stop": (i32, [C.c_char_p, sz]),
         "pmb_gemm_f32": (i32, [vp, i32, i32, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp, i32]),
-        "pmb_gemm_reserve_scratch": (i32, [ctypes.c_size_t]),
+        "pmb_gemm_reserve_scratch": (i32, [C.c_size_t]),
         "pmb_gemm_bf16": (i32, [vp, i32, i32, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp, i32]),
         "pmb_cast_f32_to_bf16": (i32, [vp, vp, vp, i64]),
         "pmb_mamba2_block_workspace_bytes_bf16": (sz, [cfgp, i32, i32]),
