@@ -67,7 +67,11 @@ struct BlockWs {
   float *dnormed, *dxzd, *dact, *ddt, *dA, *scratch;
   size_t scratch_bytes;
   uint16_t *normed16, *dxzd16;   // bf16 copies of the two GEMM operands (bf16-storage mode only)
+  // fp32 mode with pair GEMMs: (hi, lo) bf16 pairs of every GEMM operand
+  uint16_t *x_hi, *x_lo, *dout_hi, *dout_lo, *normed_hi, *normed_lo, *dxzd_hi, *dxzd_lo, *win_hi, *win_lo, *wout_hi, *wout_lo;
 };
+
+bool block_uses_pairs(const Dims& d) { return gemm_pairs_enabled() && !(d.D % 8) && !(d.J % 8) && !(d.I % 8); }
 
 static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* out, bool bf16 = false) {
   Arena ar(base, bytes);
@@ -97,6 +101,15 @@ static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* 
   w.scratch = reinterpret_cast<float*>(ar.take<char>(w.scratch_bytes));
   w.normed16 = ar.take<uint16_t>(bf16 ? (size_t)d.M * d.I : 0);
   w.dxzd16 = ar.take<uint16_t>(bf16 ? (size_t)d.M * d.J : 0);
+  if (!bf16 && block_uses_pairs(d)) {
+    const size_t md = (size_t)d.M * d.D, mi = (size_t)d.M * d.I, mj = (size_t)d.M * d.J, dj = (size_t)d.D * d.J, id = (size_t)d.I * d.D;
+    w.x_hi = ar.take<uint16_t>(md); w.x_lo = ar.take<uint16_t>(md);
+    w.dout_hi = ar.take<uint16_t>(md); w.dout_lo = ar.take<uint16_t>(md);
+    w.normed_hi = ar.take<uint16_t>(mi); w.normed_lo = ar.take<uint16_t>(mi);
+    w.dxzd_hi = ar.take<uint16_t>(mj); w.dxzd_lo = ar.take<uint16_t>(mj);
+    w.win_hi = ar.take<uint16_t>(dj); w.win_lo = ar.take<uint16_t>(dj);
+    w.wout_hi = ar.take<uint16_t>(id); w.wout_lo = ar.take<uint16_t>(id);
+  }
   if (out) *out = w;
   return ar.ok ? ar.used() : 0;
 }
@@ -117,41 +130,75 @@ static SsdIn ssd_inputs(const Dims& d, const pmb_block_params& p, const BlockWs&
 // In bf16-storage mode (w16 != NULL) x is bf16, the two projections run as bf16 GEMMs with fp32 accumulation
 // against bf16 copies of the weights, and everything between them (the reference's "fp32 islands",
 // block.rs:24-42) stays in fp32.
+// Pair of a weight matrix: the caller's pre-split copy when there is one, else split here into the workspace.
+static pmb_status weight_pair(cudaStream_t st, const Weights16* wx, bool in_proj, const float* src, int64_t rows, int64_t cols,
+                              uint16_t* hi, uint16_t* lo, Pair16* out) {
+  if (wx && wx->pairs) { *out = in_proj ? Pair16{wx->in_proj, wx->in_lo, cols} : Pair16{wx->out_proj, wx->out_lo, cols}; return PMB_OK; }
+  PMB_TRY(split_pair16(st, src, rows, cols, cols, hi, lo, cols));
+  *out = Pair16{hi, lo, cols};
+  return PMB_OK;
+}
+
 static pmb_status block_fwd_core(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const BlockWs& w,
-                                 const Weights16* w16) {
+                                 const Weights16* wx) {
+  const Weights16* w16 = storage_is_bf16(wx) ? wx : nullptr;
+  const bool pr = !w16 && block_uses_pairs(d);
   if (w16) PMB_TRY(gemm_bf16(st, 0, 0, d.M, d.J, d.D, x, d.D, w16->in_proj, d.J, w.xzd, d.J, nullptr, 0));
+  else if (pr) {
+    Pair16 win;
+    PMB_TRY(split_pair16(st, static_cast<const float*>(x), d.M, d.D, d.D, w.x_hi, w.x_lo, d.D));
+    PMB_TRY(weight_pair(st, wx, true, p.in_proj_weight, d.D, d.J, w.win_hi, w.win_lo, &win));
+    PMB_TRY(gemm_pairs(st, 0, 0, d.M, d.J, d.D, Pair16{w.x_hi, w.x_lo, d.D}, win, w.xzd, d.J, nullptr));
+  }
   else PMB_TRY(gemm(st, 0, 0, d.M, d.J, d.D, static_cast<const float*>(x), d.D, p.in_proj_weight, d.J, w.xzd, d.J, nullptr, 0));
   PMB_TRY(conv_silu_dt_fwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, p.dt_bias, w.act, w.dt));
   a_neg_kernel<<<(unsigned)cdiv(d.H, 128), 128, 0, st>>>(p.a_log, w.Aneg, d.H);
   PMB_LAUNCHED();
   PMB_TRY(ssd_fwd(st, ssd_inputs(d, p, w), nullptr, w.y, d.I, nullptr, w.ssd));
-  PMB_TRY(gated_rmsnorm_fwd(st, d.M, d.I, d.eps, w.y, w.xzd, d.J, p.norm_weight, w.normed, w.rstd));
+  // with pair GEMMs the normalised output is only ever a GEMM operand: write it as a pair, skip the fp32 copy
+  if (pr) PMB_TRY(gated_rmsnorm_fwd(st, d.M, d.I, d.eps, w.y, w.xzd, d.J, p.norm_weight, nullptr, w.rstd, w.normed_hi, w.normed_lo));
+  else PMB_TRY(gated_rmsnorm_fwd(st, d.M, d.I, d.eps, w.y, w.xzd, d.J, p.norm_weight, w.normed, w.rstd));
   if (w16) PMB_TRY(cast_f32_bf16(st, w.normed, w.normed16, d.M * d.I));
   return PMB_OK;
 }
 
 pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* residual,
-                     void* out, void* ws, size_t ws_bytes, const Weights16* w16) {
+                     void* out, void* ws, size_t ws_bytes, const Weights16* wx) {
+  const Weights16* w16 = storage_is_bf16(wx) ? wx : nullptr;
+  const bool pr = !w16 && block_uses_pairs(d);
   BlockWs w;
   if (block_ws_layout(d, ws, ws_bytes, &w, w16 != nullptr) == 0 || !ws)
     return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_bytes(d, w16 != nullptr));
-  PMB_TRY(block_fwd_core(st, d, p, x, w, w16));
+  PMB_TRY(block_fwd_core(st, d, p, x, w, wx));
   if (w16) PMB_TRY(gemm_bf16(st, 0, 0, d.M, d.D, d.I, w.normed16, d.I, w16->out_proj, d.D, out, d.D, residual, 1));
+  else if (pr) {
+    Pair16 wout;
+    PMB_TRY(weight_pair(st, wx, false, p.out_proj_weight, d.I, d.D, w.wout_hi, w.wout_lo, &wout));
+    PMB_TRY(gemm_pairs(st, 0, 0, d.M, d.D, d.I, Pair16{w.normed_hi, w.normed_lo, d.I}, wout, static_cast<float*>(out), d.D, static_cast<const float*>(residual)));
+  }
   else PMB_TRY(gemm(st, 0, 0, d.M, d.D, d.I, w.normed, d.I, p.out_proj_weight, d.D, static_cast<float*>(out), d.D, static_cast<const float*>(residual), 0));
   return PMB_OK;
 }
 
 pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* dout,
-                     const void* dx_accum, void* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes, const Weights16* w16) {
+                     const void* dx_accum, void* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes, const Weights16* wx) {
+  const Weights16* w16 = storage_is_bf16(wx) ? wx : nullptr;
+  const bool pr = !w16 && block_uses_pairs(d);
   BlockWs w;
   if (block_ws_layout(d, ws, ws_bytes, &w, w16 != nullptr) == 0 || !ws)
     return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_bytes(d, w16 != nullptr));
   // recompute (the out_proj product itself is not needed for gradients)
-  PMB_TRY(block_fwd_core(st, d, p, x, w, w16));
+  PMB_TRY(block_fwd_core(st, d, p, x, w, wx));
   // out_proj: dW_out = normed^T dout;  dnormed = dout W_out^T
   if (w16) {
     PMB_TRY(gemm_bf16(st, 1, 0, d.I, d.D, d.M, w.normed16, d.I, dout, d.D, g.out_proj_weight, d.D, nullptr, 0));
     PMB_TRY(gemm_bf16(st, 0, 1, d.M, d.I, d.D, dout, d.D, w16->out_proj, d.D, w.dnormed, d.I, nullptr, 0));
+  } else if (pr) {
+    Pair16 wout, dop{w.dout_hi, w.dout_lo, d.D};
+    PMB_TRY(split_pair16(st, static_cast<const float*>(dout), d.M, d.D, d.D, w.dout_hi, w.dout_lo, d.D));
+    PMB_TRY(weight_pair(st, wx, false, p.out_proj_weight, d.I, d.D, w.wout_hi, w.wout_lo, &wout));
+    PMB_TRY(gemm_pairs(st, 1, 0, d.I, d.D, d.M, Pair16{w.normed_hi, w.normed_lo, d.I}, dop, g.out_proj_weight, d.D, nullptr));
+    PMB_TRY(gemm_pairs(st, 0, 1, d.M, d.I, d.D, dop, wout, w.dnormed, d.I, nullptr));
   } else {
     const float* df = static_cast<const float*>(dout);
     PMB_TRY(gemm(st, 1, 0, d.I, d.D, d.M, w.normed, d.I, df, d.D, g.out_proj_weight, d.D, nullptr, 0));
@@ -176,6 +223,13 @@ pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, 
     PMB_TRY(cast_f32_bf16(st, w.dxzd, w.dxzd16, d.M * d.J));
     PMB_TRY(gemm_bf16(st, 1, 0, d.D, d.J, d.M, x, d.D, w.dxzd16, d.J, g.in_proj_weight, d.J, nullptr, 0));
     PMB_TRY(gemm_bf16(st, 0, 1, d.M, d.D, d.J, w.dxzd16, d.J, w16->in_proj, d.J, dx, d.D, dx_accum, 1));
+  } else if (pr) {
+    // x and W_in were split by the recompute above
+    const Pair16 win = (wx && wx->pairs) ? Pair16{wx->in_proj, wx->in_lo, d.J} : Pair16{w.win_hi, w.win_lo, d.J};
+    const Pair16 dxp{w.dxzd_hi, w.dxzd_lo, d.J};
+    PMB_TRY(split_pair16(st, w.dxzd, d.M, d.J, d.J, w.dxzd_hi, w.dxzd_lo, d.J));
+    PMB_TRY(gemm_pairs(st, 1, 0, d.D, d.J, d.M, Pair16{w.x_hi, w.x_lo, d.D}, dxp, g.in_proj_weight, d.J, nullptr));
+    PMB_TRY(gemm_pairs(st, 0, 1, d.M, d.D, d.J, dxp, win, static_cast<float*>(dx), d.D, static_cast<const float*>(dx_accum)));
   } else {
     PMB_TRY(gemm(st, 1, 0, d.D, d.J, d.M, static_cast<const float*>(x), d.D, w.dxzd, d.J, g.in_proj_weight, d.J, nullptr, 0));
     PMB_TRY(gemm(st, 0, 1, d.M, d.D, d.J, w.dxzd, d.J, p.in_proj_weight, d.J, static_cast<float*>(dx), d.D, static_cast<const float*>(dx_accum), 0));
@@ -221,7 +275,7 @@ namespace pmb {
 // (fp32, or bf16 when w16 != NULL); slot l = input of block l.
 pmb_status stack_fwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_block_params* layers, const Weights16* w16,
                      void* saved, void* ws, size_t ws_bytes) {
-  size_t slot = (size_t)d.M * d.D * (w16 ? 2 : 4);
+  size_t slot = (size_t)d.M * d.D * (storage_is_bf16(w16) ? 2 : 4);
   char* base = static_cast<char*>(saved);
   for (int l = 0; l < n_layers; ++l) {
     const void* h = base + (size_t)l * slot;
@@ -234,7 +288,7 @@ pmb_status stack_fwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_blo
 pmb_status stack_bwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_block_params* layers, const Weights16* w16,
                      const pmb_block_grads* grads, const void* saved, void* dhidden, void* ws, size_t ws_bytes,
                      pmb_layer_callback on_layer_done, void* user) {
-  size_t slot = (size_t)d.M * d.D * (w16 ? 2 : 4);
+  size_t slot = (size_t)d.M * d.D * (storage_is_bf16(w16) ? 2 : 4);
   const char* base = static_cast<const char*>(saved);
   for (int l = n_layers - 1; l >= 0; --l) {
     PMB_TRY(block_bwd(st, d, layers[l], base + (size_t)l * slot, dhidden, dhidden, dhidden, grads[l], ws, ws_bytes, w16 ? &w16[l] : nullptr));

@@ -267,7 +267,8 @@ constexpr int NORM_MAX_PER_THREAD = 8;   // width <= 2048 (registers hold a whol
 __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_fwd_kernel(const float* __restrict__ y, const float* __restrict__ z,
                                                                          int64_t ldz, const float* __restrict__ w,
                                                                          float* __restrict__ out, float* __restrict__ rstd,
-                                                                         int width, float eps) {
+                                                                         int width, float eps, uint16_t* __restrict__ out_hi,
+                                                                         uint16_t* __restrict__ out_lo) {
   __shared__ float red[32];
   int64_t row = blockIdx.x;
   const float* yr = y + row * width;
@@ -290,15 +291,26 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_fwd_kernel(const f
 #pragma unroll
   for (int n = 0; n < NORM_MAX_PER_THREAD; ++n) {
     int i = threadIdx.x + n * NORM_THREADS;
-    if (i < width) out[row * width + i] = g[n] * r * w[i];
+    if (i < width) {
+      float v = g[n] * r * w[i];
+      if (out) out[row * width + i] = v;
+      if (out_hi) {   // (hi, lo) bf16 pair of v for the pair GEMM: hi = bf16(v), lo = bf16(v - hi), round to nearest even
+        uint32_t u = __float_as_uint(v);
+        uint32_t h = (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+        float rem = v - __uint_as_float(h << 16);
+        uint32_t ul = __float_as_uint(rem);
+        out_hi[row * width + i] = (uint16_t)h;
+        out_lo[row * width + i] = (uint16_t)((ul + 0x7fffu + ((ul >> 16) & 1u)) >> 16);
+      }
+    }
   }
 }
 
 pmb_status gated_rmsnorm_fwd(cudaStream_t st, int64_t rows, int width, float eps, const float* y, const float* z, int64_t ldz,
-                             const float* w, float* out, float* rstd) {
+                             const float* w, float* out, float* rstd, uint16_t* out_hi, uint16_t* out_lo) {
   if (width > NORM_THREADS * NORM_MAX_PER_THREAD) return fail(PMB_ERR_SHAPE, "rmsnorm width %d > %d", width, NORM_THREADS * NORM_MAX_PER_THREAD);
   ProfScope prof(st, "gated_rmsnorm_fwd", 0.0, 4.0 * rows * 3.0 * width);
-  gated_rmsnorm_fwd_kernel<<<(unsigned)rows, NORM_THREADS, 0, st>>>(y, z, ldz, w, out, rstd, width, eps);
+  gated_rmsnorm_fwd_kernel<<<(unsigned)rows, NORM_THREADS, 0, st>>>(y, z, ldz, w, out, rstd, width, eps, out_hi, out_lo);
   PMB_LAUNCHED();
   return PMB_OK;
 }

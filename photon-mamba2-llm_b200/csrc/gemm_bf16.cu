@@ -7,6 +7,7 @@
 // tiles: blocks of 64 elements along M/N, 64 k-rows of 128 bytes per block, same swizzle.
 // Every mbarrier wait is bounded; on expiry the kernel raises the device status word and drains.
 #include <cstdlib>
+#include <cstring>
 #include <map>
 #include <tuple>
 #include "tc_common.cuh"
@@ -311,14 +312,21 @@ pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
 
 // ---- fp32 GEMM through bf16 pairs ------------------------------------------------------------------
 // a = hi + lo with hi = bf16(a), lo = bf16(a - hi): 16 mantissa bits, relative representation error <= 2^-17.
-__global__ void split_f32_bf16x2_kernel(const float* __restrict__ src, int64_t rows, int64_t cols, int64_t ld,
-                                        uint16_t* __restrict__ hi, uint16_t* __restrict__ lo, int64_t ld16) {
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // one thread = 4 consecutive columns
-  int64_t c4 = cols / 4;
+// One thread = 4 consecutive columns of the pair; columns in [cols, ld16) are written as zero.
+__global__ void split_pair16_kernel(const float* __restrict__ src, int64_t rows, int64_t cols, int64_t ld,
+                                    uint16_t* __restrict__ hi, uint16_t* __restrict__ lo, int64_t ld16, int vec) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t c4 = ld16 / 4;
   if (i >= rows * c4) return;
   int64_t r = i / c4, c = (i % c4) * 4;
-  float4 v = *reinterpret_cast<const float4*>(src + r * ld + c);
-  float f[4] = {v.x, v.y, v.z, v.w};
+  float f[4];
+  if (vec && c + 4 <= cols) {
+    float4 v = *reinterpret_cast<const float4*>(src + r * ld + c);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) f[e] = (c + e < cols) ? src[r * ld + c + e] : 0.0f;
+  }
   uint32_t h[4], l[4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
@@ -329,8 +337,56 @@ __global__ void split_f32_bf16x2_kernel(const float* __restrict__ src, int64_t r
   *reinterpret_cast<uint2*>(lo + r * ld16 + c) = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
 }
 
-// Library-owned scratch for the bf16 pairs (grow-only, one per device).  pmb_gemm_reserve_scratch() sizes it up
-// front for callers that must not allocate later (e.g. before stream capture).
+pmb_status split_pair16(cudaStream_t st, const float* src, int64_t rows, int64_t cols, int64_t ld, uint16_t* hi, uint16_t* lo,
+                        int64_t ld16) {
+  if ((ld16 & 7) || ld16 < cols || ((reinterpret_cast<uintptr_t>(hi) | reinterpret_cast<uintptr_t>(lo)) & 15))
+    return fail(PMB_ERR_ARG, "split_pair16: the pair needs 16-byte aligned bases and a row pitch that is a multiple of 8");
+  const int vec = ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (ld & 3) == 0) ? 1 : 0;
+  ProfScope prof(st, "split_f32_bf16x2", 0.0, 8.0 * rows * cols);
+  split_pair16_kernel<<<(unsigned)cdiv(rows * (ld16 / 4), 256), 256, 0, st>>>(src, rows, cols, ld, hi, lo, ld16, vec);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
+bool gemm_pairs_enabled() {
+  static const int on = [] { const char* e = getenv("PMB_GEMM_ENGINE"); return (e && (strcmp(e, "tf32") == 0 || strcmp(e, "simt") == 0)) ? 0 : 1; }();
+  return on != 0;
+}
+
+// C (fp32) = op(A) op(B) (+ R) with both operands given as bf16 pairs: three kind::f16 MMAs per k-step.
+// Relative accuracy ~1e-5 of the result's scale; twice the tensor-core rate and less than half the shared-memory
+// traffic of the 3xTF32 kernel.
+pmb_status gemm_pairs(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const Pair16& A, const Pair16& B,
+                      float* C, int64_t ldc, const float* R) {
+  using namespace hb;
+  if (M <= 0 || N <= 0 || K <= 0) return fail(PMB_ERR_SHAPE, "gemm_pairs: M, N, K must be positive");
+  if ((A.ld & 7) || (B.ld & 7) ||
+      ((reinterpret_cast<uintptr_t>(A.hi) | reinterpret_cast<uintptr_t>(A.lo) | reinterpret_cast<uintptr_t>(B.hi) | reinterpret_cast<uintptr_t>(B.lo)) & 15))
+    return fail(PMB_ERR_UNSUPPORTED, "gemm_pairs: operands need 16-byte aligned bases and row pitches that are multiples of 8");
+  if (cdiv(M, TBM) > 65535) return fail(PMB_ERR_UNSUPPORTED, "gemm_pairs: M too large for the launch grid");
+  static bool attr_set = false;
+  if (!attr_set) {
+    PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::SMEM_BYTES));
+    attr_set = true;
+  }
+  CUtensorMap mAh, mAl, mBh, mBl;
+  if (!ta) { PMB_TRY(make_map(&mAh, A.hi, K, M, A.ld, TBK, TBM)); PMB_TRY(make_map(&mAl, A.lo, K, M, A.ld, TBK, TBM)); }
+  else { PMB_TRY(make_map(&mAh, A.hi, M, K, A.ld, 64, TBK)); PMB_TRY(make_map(&mAl, A.lo, M, K, A.ld, 64, TBK)); }
+  if (tb) { PMB_TRY(make_map(&mBh, B.hi, K, N, B.ld, TBK, TBN)); PMB_TRY(make_map(&mBl, B.lo, K, N, B.ld, TBK, TBN)); }
+  else { PMB_TRY(make_map(&mBh, B.hi, N, K, B.ld, 64, TBK)); PMB_TRY(make_map(&mBl, B.lo, N, K, B.ld, 64, TBK)); }
+  Params p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.a_mn_major = ta ? 1 : 0; p.b_mn_major = tb ? 0 : 1;
+  p.C = C; p.ldc = ldc; p.R = R; p.out_bf16 = 0;
+  dim3 grid((unsigned)cdiv(N, TBN), (unsigned)cdiv(M, TBM));
+  ProfScope prof(st, "gemm_bf16x2", 2.0 * M * N * K, 4.0 * ((double)M * K + (double)K * N + (double)M * N * (R ? 2 : 1)));
+  gemm_bf16_kernel<true><<<grid, NTHREADS, Cfg<true>::SMEM_BYTES, st>>>(mAh, mBh, mAl, mBl, p);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
+// Library-owned scratch for the pairs of callers that hand in fp32 operands (grow-only, one per device).
+// pmb_gemm_reserve_scratch() sizes it up front for callers that must not allocate later.
 static void* g_scratch[64] = {nullptr};
 static size_t g_scratch_bytes[64] = {0};
 
@@ -350,55 +406,26 @@ pmb_status gemm_scratch(size_t bytes, void** out) {
 
 bool gemm_f32_via_bf16x2_supported(int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                                    const float* B, int64_t ldb) {
-  (void)ta; (void)tb;
-  if (M <= 0 || N <= 0 || K <= 0 || cdiv(M, hb::TBM) > 65535) return false;
-  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return false;
-  // stored extents: A is (M,K) or (K,M), B is (K,N) or (N,K); the contiguous extent must allow 16-byte bf16 rows
-  int64_t a_cols = ta ? M : K, b_cols = tb ? K : N;
-  if ((lda & 3) || (ldb & 3) || (a_cols & 7) || (b_cols & 7)) return false;
-  return true;
+  (void)ta; (void)tb; (void)A; (void)B; (void)lda; (void)ldb;
+  return M > 0 && N > 0 && K > 0 && cdiv(M, hb::TBM) <= 65535;
 }
 
-// C (fp32) = op(A) op(B) (+ R) with fp32 operands: both are split into bf16 pairs (one elementwise pass each, into
-// the library scratch) and multiplied with three kind::f16 MMAs per k-step.  Relative accuracy ~1e-5 of the
-// result's scale; twice the tensor-core rate and less than half the shared-memory traffic of the 3xTF32 kernel.
+// fp32 operands: one elementwise pass each into the scratch (rows compacted to a pitch that is a multiple of 8),
+// then gemm_pairs.
 pmb_status gemm_f32_via_bf16x2(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                                const float* B, int64_t ldb, float* C, int64_t ldc, const float* R) {
-  using namespace hb;
   const int64_t a_rows = ta ? K : M, a_cols = ta ? M : K, b_rows = tb ? N : K, b_cols = tb ? K : N;
-  const size_t a_el = (size_t)a_rows * a_cols, b_el = (size_t)b_rows * b_cols;
+  const int64_t a_ld = (int64_t)align_up((size_t)a_cols, 8), b_ld = (int64_t)align_up((size_t)b_cols, 8);
+  const size_t a_el = align_up((size_t)a_rows * a_ld, 64), b_el = align_up((size_t)b_rows * b_ld, 64);
   void* scratch = nullptr;
   PMB_TRY(gemm_scratch((2 * a_el + 2 * b_el) * 2 + 1024, &scratch));
   uint16_t* a_hi = static_cast<uint16_t*>(scratch);
-  uint16_t* a_lo = a_hi + align_up(a_el, 64);
-  uint16_t* b_hi = a_lo + align_up(a_el, 64);
-  uint16_t* b_lo = b_hi + align_up(b_el, 64);
-  {
-    ProfScope prof(st, "split_f32_bf16x2", 0.0, 8.0 * (a_el + b_el));
-    split_f32_bf16x2_kernel<<<(unsigned)cdiv(a_el / 4, 256), 256, 0, st>>>(A, a_rows, a_cols, lda, a_hi, a_lo, a_cols);
-    PMB_LAUNCHED();
-    split_f32_bf16x2_kernel<<<(unsigned)cdiv(b_el / 4, 256), 256, 0, st>>>(B, b_rows, b_cols, ldb, b_hi, b_lo, b_cols);
-    PMB_LAUNCHED();
-  }
-  static bool attr_set = false;
-  if (!attr_set) {
-    PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::SMEM_BYTES));
-    attr_set = true;
-  }
-  CUtensorMap mAh, mAl, mBh, mBl;
-  if (!ta) { PMB_TRY(make_map(&mAh, a_hi, K, M, a_cols, TBK, TBM)); PMB_TRY(make_map(&mAl, a_lo, K, M, a_cols, TBK, TBM)); }
-  else { PMB_TRY(make_map(&mAh, a_hi, M, K, a_cols, 64, TBK)); PMB_TRY(make_map(&mAl, a_lo, M, K, a_cols, 64, TBK)); }
-  if (tb) { PMB_TRY(make_map(&mBh, b_hi, K, N, b_cols, TBK, TBN)); PMB_TRY(make_map(&mBl, b_lo, K, N, b_cols, TBK, TBN)); }
-  else { PMB_TRY(make_map(&mBh, b_hi, N, K, b_cols, 64, TBK)); PMB_TRY(make_map(&mBl, b_lo, N, K, b_cols, 64, TBK)); }
-  Params p{};
-  p.M = (int)M; p.N = (int)N; p.K = (int)K;
-  p.a_mn_major = ta ? 1 : 0; p.b_mn_major = tb ? 0 : 1;
-  p.C = C; p.ldc = ldc; p.R = R; p.out_bf16 = 0;
-  dim3 grid((unsigned)cdiv(N, TBN), (unsigned)cdiv(M, TBM));
-  ProfScope prof(st, "gemm_bf16x2", 2.0 * M * N * K, 4.0 * ((double)M * K + (double)K * N + (double)M * N * (R ? 2 : 1)));
-  gemm_bf16_kernel<true><<<grid, NTHREADS, Cfg<true>::SMEM_BYTES, st>>>(mAh, mBh, mAl, mBl, p);
-  PMB_LAUNCHED();
-  return PMB_OK;
+  uint16_t* a_lo = a_hi + a_el;
+  uint16_t* b_hi = a_lo + a_el;
+  uint16_t* b_lo = b_hi + b_el;
+  PMB_TRY(split_pair16(st, A, a_rows, a_cols, lda, a_hi, a_lo, a_ld));
+  PMB_TRY(split_pair16(st, B, b_rows, b_cols, ldb, b_hi, b_lo, b_ld));
+  return gemm_pairs(st, ta, tb, M, N, K, Pair16{a_hi, a_lo, a_ld}, Pair16{b_hi, b_lo, b_ld}, C, ldc, R);
 }
 
 }  // namespace pmb

@@ -11,7 +11,8 @@ size_t conv_bwd_ws_bytes(const Dims& d);
 pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
                          const float* dact, float* dxzd, float* dw, float* db, void* ws, size_t ws_bytes);
 pmb_status gated_rmsnorm_fwd(cudaStream_t st, int64_t rows, int width, float eps, const float* y, const float* z,
-                             int64_t ldz, const float* w, float* out, float* rstd);
+                             int64_t ldz, const float* w, float* out, float* rstd, uint16_t* out_hi = nullptr,
+                             uint16_t* out_lo = nullptr);   // out_hi/out_lo: optional (hi, lo) bf16 pair of the output; out may then be NULL
 size_t gated_rmsnorm_bwd_ws_bytes(int64_t rows, int width);
 pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const float* dout, const float* y, const float* z,
                              int64_t ldz, const float* w, const float* rstd, float* dy, float* dz, int64_t lddz,
@@ -81,6 +82,13 @@ pmb_status read_clear_device_status(unsigned int* word);
 pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
                      const void* B, int64_t ldb, void* C, int64_t ldc, const void* R, int out_bf16);
 pmb_status read_clear_device_status_bf16(unsigned int* word);
+// fp32 matrices as (hi, lo) bf16 pairs: hi = bf16(a), lo = bf16(a - hi); ld = row pitch in elements (multiple of 8)
+struct Pair16 { const uint16_t* hi; const uint16_t* lo; int64_t ld; };
+pmb_status split_pair16(cudaStream_t st, const float* src, int64_t rows, int64_t cols, int64_t ld, uint16_t* hi, uint16_t* lo,
+                        int64_t ld16);
+pmb_status gemm_pairs(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const Pair16& A, const Pair16& B,
+                      float* C, int64_t ldc, const float* R);
+bool gemm_pairs_enabled();   // false when PMB_GEMM_ENGINE is tf32 or simt
 bool gemm_f32_via_bf16x2_supported(int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                                    const float* B, int64_t ldb);
 pmb_status gemm_f32_via_bf16x2(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
@@ -88,7 +96,15 @@ pmb_status gemm_f32_via_bf16x2(cudaStream_t st, int ta, int tb, int64_t M, int64
 
 // ---- block.cu.  w16 != NULL selects bf16 storage: x / residual / out / dout / dx are bf16 and the two
 // projections use the bf16 weight copies; NULL = fp32 everywhere.
-struct Weights16 { const uint16_t* in_proj; const uint16_t* out_proj; };
+// With pairs == true the struct instead carries pre-split (hi, lo) bf16 pairs of the fp32 weights (hi in in_proj /
+// out_proj, lo in in_lo / out_lo) and storage stays fp32.
+struct Weights16 {
+  const uint16_t* in_proj; const uint16_t* out_proj;
+  const uint16_t* in_lo = nullptr; const uint16_t* out_lo = nullptr;
+  bool pairs = false;
+};
+inline bool storage_is_bf16(const Weights16* w) { return w && !w->pairs; }
+bool block_uses_pairs(const Dims& d);   // fp32 blocks route their four projections' GEMMs through bf16 pairs
 size_t block_ws_bytes(const Dims& d, bool bf16 = false);
 pmb_status cast_f32_bf16(cudaStream_t st, const float* src, uint16_t* dst, int64_t n);
 pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* residual,

@@ -6,6 +6,7 @@
 // place, so the (tokens, vocab) matrix never exists as a whole (the reference tiles for the same reason,
 // crates/pm-core/src/loss.rs:73-209).
 #include <vector>
+#include <cstdlib>
 #include "common.cuh"
 #include "kernels.h"
 
@@ -64,7 +65,7 @@ __global__ void embedding_bwd_kernel(float* __restrict__ dtable, const int64_t* 
 // row_loss[r] = logsumexp - logit[target].
 __global__ void __launch_bounds__(256) cross_entropy_kernel(float* __restrict__ logits, int64_t ld, int V,
                                                             const int64_t* __restrict__ targets, float* __restrict__ row_loss,
-                                                            float inv_rows) {
+                                                            float inv_rows, uint16_t* __restrict__ d_hi, uint16_t* __restrict__ d_lo) {
   __shared__ float red[32];
   __shared__ float sh_max;
   int64_t r = blockIdx.x;
@@ -97,7 +98,75 @@ __global__ void __launch_bounds__(256) cross_entropy_kernel(float* __restrict__ 
   float inv = 1.0f / tot;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
     float pr = expf(row[i] - m) * inv;
-    row[i] = (pr - (i == tg ? 1.0f : 0.0f)) * inv_rows;
+    float gl = (pr - (i == tg ? 1.0f : 0.0f)) * inv_rows;
+    if (d_hi) {   // the gradient is only ever a GEMM operand: emit it as a (hi, lo) bf16 pair, same pitch as the logits
+      uint32_t u = __float_as_uint(gl);
+      uint32_t h = (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+      uint32_t ul = __float_as_uint(gl - __uint_as_float(h << 16));
+      d_hi[r * ld + i] = (uint16_t)h;
+      d_lo[r * ld + i] = (uint16_t)((ul + 0x7fffu + ((ul >> 16) & 1u)) >> 16);
+    } else {
+      row[i] = gl;
+    }
+  }
+}
+
+// Same loss, with the row staged in shared memory (one read of the logits) and the gradient written back over
+// the row as a (hi, lo) bf16 pair: hi[i] at uint16 index i of the row, lo[i] at uint16 index ld + i, i.e. the pair
+// matrices have a pitch of 2*ld uint16 and share the logits buffer.  Needs V floats of dynamic shared memory.
+constexpr int CE_THREADS = 1024;
+__global__ void __launch_bounds__(CE_THREADS) cross_entropy_pair_inplace_kernel(float* __restrict__ logits, int64_t ld, int V,
+                                                                                const int64_t* __restrict__ targets,
+                                                                                float* __restrict__ row_loss, float inv_rows) {
+  extern __shared__ float srow[];
+  __shared__ float red[32];
+  const int64_t r = blockIdx.x;
+  float* row = logits + r * ld;
+  const int V4 = V >> 2;
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < V4; i += CE_THREADS) {
+    float4 v = reinterpret_cast<const float4*>(row)[i];
+    reinterpret_cast<float4*>(srow)[i] = v;
+    m = fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+  }
+  for (int i = 4 * V4 + threadIdx.x; i < V; i += CE_THREADS) { float v = row[i]; srow[i] = v; m = fmaxf(m, v); }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = red[threadIdx.x & 31];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  const int64_t tg = targets[r];
+  const float tlogit = (tg >= 0 && tg < V) ? srow[tg] : 0.0f;
+  __syncthreads();                         // every thread has read srow[tg] before the loop below overwrites the row
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < V; i += CE_THREADS) { float e = expf(srow[i] - m); srow[i] = e; s += e; }
+  const float tot = block_sum(s, red);
+  if (threadIdx.x == 0) row_loss[r] = (tg >= 0 && tg < V) ? m + logf(tot) - tlogit : 0.0f;
+  const float inv = 1.0f / tot;
+  uint16_t* hi = reinterpret_cast<uint16_t*>(row);
+  uint16_t* lo = hi + ld;
+  auto split = [](float v, uint32_t& h, uint32_t& l) {
+    uint32_t u = __float_as_uint(v);
+    h = (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+    uint32_t ul = __float_as_uint(v - __uint_as_float(h << 16));
+    l = (ul + 0x7fffu + ((ul >> 16) & 1u)) >> 16;
+  };
+  for (int i = threadIdx.x; i < V4; i += CE_THREADS) {
+    float4 e = reinterpret_cast<const float4*>(srow)[i];
+    const int c = 4 * i;
+    float g[4] = {e.x * inv, e.y * inv, e.z * inv, e.w * inv};
+    uint32_t h[4], l4[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { if (c + k == tg) g[k] -= 1.0f; split(g[k] * inv_rows, h[k], l4[k]); }
+    *reinterpret_cast<uint2*>(hi + c) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+    *reinterpret_cast<uint2*>(lo + c) = make_uint2(l4[0] | (l4[1] << 16), l4[2] | (l4[3] << 16));
+  }
+  for (int i = 4 * V4 + threadIdx.x; i < V; i += CE_THREADS) {
+    uint32_t h, l1;
+    split((srow[i] * inv - (i == tg ? 1.0f : 0.0f)) * inv_rows, h, l1);
+    hi[i] = (uint16_t)h; lo[i] = (uint16_t)l1;
   }
 }
 
@@ -178,6 +247,11 @@ struct pmb_lm {
   int bf16 = 0;               // storage dtype of activations / GEMM operands
   uint16_t* params16 = nullptr;   // bf16 copy of the flat parameter buffer, refreshed every step
   uint16_t* dlogits16 = nullptr;  // (tile_rows, Vp)
+  // fp32 storage with pair GEMMs: (hi, lo) bf16 pairs of the flat parameters (refreshed every step), of the
+  // logits gradient tile and of the final hidden rows
+  int pairs = 0;
+  int ce_inplace = 0;         // the logits row fits in shared memory: the gradient pair overwrites the logits tile
+  uint16_t *params_hi = nullptr, *params_lo = nullptr, *dlog_hi = nullptr, *dlog_lo = nullptr, *hid_hi = nullptr, *hid_lo = nullptr;
   std::vector<Weights16> lw16;
   // hierarchical variant (L1 > 0): level 0 = layers [0,L0) at token rate, level 1 = layers [L0,L0+L1) at 1/group rate
   int L0 = 0, L1 = 0, group = 1;
@@ -222,7 +296,9 @@ static pmb_status lm_create_impl(const pmb_mamba2_config* cfg, int L0, int L1, i
   lm->V = vocab; lm->bf16 = bf16_storage ? 1 : 0;
   if (L1 > 0) PMB_TRY(make_dims(cfg, batch, seqlen / group, &lm->d1));
   lm->Vp = (int)align_up((size_t)vocab, 64);
-  lm->tile_rows = (int)(d.M < LM_TILE_ROWS ? d.M : LM_TILE_ROWS);
+  int tile_cap = LM_TILE_ROWS;
+  if (const char* e = getenv("PMB_LM_TILE_ROWS")) { int v = atoi(e); if (v >= 128) tile_cap = v; }
+  lm->tile_rows = (int)(d.M < tile_cap ? d.M : tile_cap);
   int64_t o = 0;
   auto place = [&](int64_t n) { int64_t at = o; o += (int64_t)align_up((size_t)n, 64); return at; };
   lm->off.push_back(place((int64_t)vocab * d.D));
@@ -248,6 +324,19 @@ static pmb_status lm_create_impl(const pmb_mamba2_config* cfg, int L0, int L1, i
   ok = ok && alloc((void**)&lm->ids, (size_t)d.M * 8);
   ok = ok && alloc((void**)&lm->targets, (size_t)d.M * 8);
   ok = ok && alloc(&lm->ws, lm->ws_bytes);
+  lm->pairs = (!lm->bf16 && block_uses_pairs(d)) ? 1 : 0;
+  size_t pair_bytes = 0;
+  if (lm->pairs) {
+    const size_t tv = (size_t)lm->tile_rows * lm->Vp * 2, td = (size_t)lm->tile_rows * d.D * 2;
+    ok = ok && alloc((void**)&lm->params_hi, (size_t)o * 2) && alloc((void**)&lm->params_lo, (size_t)o * 2);
+    lm->ce_inplace = ((size_t)vocab * 4 <= (size_t)200 * 1024) ? 1 : 0;
+    if (lm->ce_inplace)
+      ok = ok && cudaFuncSetAttribute(cross_entropy_pair_inplace_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, vocab * 4) == cudaSuccess;
+    else
+      ok = ok && alloc((void**)&lm->dlog_hi, tv) && alloc((void**)&lm->dlog_lo, tv);
+    ok = ok && alloc((void**)&lm->hid_hi, td) && alloc((void**)&lm->hid_lo, td);
+    pair_bytes = (lm->ce_inplace ? 0 : 2 * tv) + 2 * td;
+  }
   if (lm->bf16) {
     ok = ok && alloc((void**)&lm->params16, (size_t)o * 2);
     ok = ok && alloc((void**)&lm->dlogits16, (size_t)lm->tile_rows * lm->Vp * 2);
@@ -268,7 +357,7 @@ static pmb_status lm_create_impl(const pmb_mamba2_config* cfg, int L0, int L1, i
   cudaMemset(lm->grads, 0, (size_t)o * 4);
   cudaMemset(lm->bad, 0, 256);
   lm->act_bytes = (int64_t)(slot * (L0 + 1) + slot1 * (L1 + 1) + slot + 3 * slot1 + (L1 > 0 ? slot : 0) +
-                            (size_t)lm->tile_rows * lm->Vp * (lm->bf16 ? 6 : 4) + (size_t)d.M * 4 + lm->ws_bytes);
+                            (size_t)lm->tile_rows * lm->Vp * (lm->bf16 ? 6 : 4) + pair_bytes + (size_t)d.M * 4 + lm->ws_bytes);
   lm->lp.resize(n_layers); lm->lg.resize(n_layers); lm->lw16.resize(n_layers);
   for (int l = 0; l < n_layers; ++l) {
     const int64_t* f = &lm->off[1 + 8 * l];
@@ -276,6 +365,7 @@ static pmb_status lm_create_impl(const pmb_mamba2_config* cfg, int L0, int L1, i
     lm->lp[l] = pmb_block_params{P + f[0], P + f[1], P + f[2], P + f[3], P + f[4], P + f[5], P + f[6], P + f[7]};
     lm->lg[l] = pmb_block_grads{G + f[0], G + f[1], G + f[2], G + f[3], G + f[4], G + f[5], G + f[6], G + f[7]};
     lm->lw16[l] = Weights16{lm->params16 ? lm->params16 + f[0] : nullptr, lm->params16 ? lm->params16 + f[7] : nullptr};
+    if (lm->pairs) lm->lw16[l] = Weights16{lm->params_hi + f[0], lm->params_hi + f[7], lm->params_lo + f[0], lm->params_lo + f[7], true};
   }
   *out = lm;
   return PMB_OK;
@@ -302,6 +392,7 @@ extern "C" void pmb_lm_destroy(pmb_lm* lm) {
   if (!lm) return;
   cudaFree(lm->params); cudaFree(lm->grads); cudaFree(lm->saved); cudaFree(lm->dhidden); cudaFree(lm->logits);
   cudaFree(lm->row_loss); cudaFree(lm->loss); cudaFree(lm->bad); cudaFree(lm->ids); cudaFree(lm->targets); cudaFree(lm->ws); cudaFree(lm->params16); cudaFree(lm->dlogits16);
+  cudaFree(lm->params_hi); cudaFree(lm->params_lo); cudaFree(lm->dlog_hi); cudaFree(lm->dlog_lo); cudaFree(lm->hid_hi); cudaFree(lm->hid_lo);
   cudaFree(lm->saved1); cudaFree(lm->pooled); cudaFree(lm->dpool); cudaFree(lm->dh1); cudaFree(lm->hsum);
   delete lm;
 }
@@ -322,7 +413,8 @@ extern "C" void pmb_lm_activation_detail(const pmb_lm* lm, int64_t* h_out3) {
   const size_t esz = lm->bf16 ? 2 : 4;
   h_out3[0] = (int64_t)((size_t)lm->d.M * lm->d.D * esz * (lm->L0 + 1) + (lm->L1 > 0 ? (size_t)lm->d1.M * lm->d.D * esz * (lm->L1 + 1) : 0));                          // stored for backward: block inputs
   h_out3[1] = (int64_t)lm->ws_bytes;                                                              // transient: one block's workspace
-  h_out3[2] = (int64_t)((size_t)lm->tile_rows * lm->Vp * (lm->bf16 ? 6 : 4) + (size_t)lm->d.M * lm->d.D * esz);  // transient: logits tile, d(hidden)
+  h_out3[2] = (int64_t)((size_t)lm->tile_rows * lm->Vp * (lm->bf16 ? 6 : ((lm->pairs && !lm->ce_inplace) ? 8 : 4)) + (size_t)lm->d.M * lm->d.D * esz +
+                        (lm->pairs ? (size_t)lm->tile_rows * lm->d.D * 4 : 0));  // transient: logits tile (+ its gradient's pair), d(hidden)
 }
 extern "C" const float* pmb_lm_loss_device(const pmb_lm* lm) { return lm ? lm->loss : nullptr; }
 
@@ -360,7 +452,11 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
   const bool hier = lm->L1 > 0;
   const int L0 = lm->L0, L1 = lm->L1;
   const uint16_t* table16 = h16 ? lm->params16 + lm->off[0] : nullptr;
-  const Weights16* w16 = h16 ? lm->lw16.data() : nullptr;
+  const bool prs = lm->pairs != 0;
+  const Weights16* w16 = (h16 || prs) ? lm->lw16.data() : nullptr;
+  // the fp32 masters may have been updated by the optimizer since the last step: refresh their pairs
+  if (prs) PMB_TRY(split_pair16(st, lm->params, 1, lm->n_params, lm->n_params, lm->params_hi, lm->params_lo, lm->n_params));
+  const Pair16 table_p{prs ? lm->params_hi + lm->off[0] : nullptr, prs ? lm->params_lo + lm->off[0] : nullptr, D};
   if (h16) {
     // the fp32 masters may have been updated by the optimizer since the last step
     PMB_TRY(cast_f32_bf16(st, lm->params, lm->params16, lm->n_params));
@@ -389,16 +485,30 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
     int64_t rows = M - r0 < lm->tile_rows ? M - r0 : lm->tile_rows;
     const void* hrows = hidden + (size_t)r0 * D * esz;
     // logits = hidden E^T   (photon/embedding.rs:54-60), kept in fp32 for the softmax
+    const Pair16 hid_p{lm->hid_hi, lm->hid_lo, D};
+    const Pair16 dlog_p = lm->ce_inplace ? Pair16{reinterpret_cast<uint16_t*>(lm->logits), reinterpret_cast<uint16_t*>(lm->logits) + Vp, 2 * (int64_t)Vp}
+                                         : Pair16{lm->dlog_hi, lm->dlog_lo, Vp};
     if (h16) PMB_TRY(gemm_bf16(st, 0, 1, rows, V, D, hrows, D, table16, D, lm->logits, Vp, nullptr, 0));
+    else if (prs) {
+      PMB_TRY(split_pair16(st, static_cast<const float*>(hrows), rows, D, D, lm->hid_hi, lm->hid_lo, D));
+      PMB_TRY(gemm_pairs(st, 0, 1, rows, V, D, hid_p, table_p, lm->logits, Vp, nullptr));
+    }
     else PMB_TRY(gemm(st, 0, 1, rows, V, D, static_cast<const float*>(hrows), D, table, D, lm->logits, Vp, nullptr, 0));
     { ProfScope prof(st, "cross_entropy", 0.0, 4.0 * rows * 3.0 * V);
-    cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>(lm->logits, Vp, V, d_targets + r0, lm->row_loss + r0, 1.0f / (float)M);
+    if (prs && lm->ce_inplace)
+      cross_entropy_pair_inplace_kernel<<<(unsigned)rows, CE_THREADS, (size_t)V * 4, st>>>(lm->logits, Vp, V, d_targets + r0, lm->row_loss + r0, 1.0f / (float)M);
+    else
+      cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>(lm->logits, Vp, V, d_targets + r0, lm->row_loss + r0, 1.0f / (float)M,
+                                                           prs ? lm->dlog_hi : nullptr, prs ? lm->dlog_lo : nullptr);
     PMB_LAUNCHED(); }
     // dhidden = dlogits E ;  dE (+)= dlogits^T hidden
     if (h16) {
       PMB_TRY(cast_f32_bf16(st, lm->logits, lm->dlogits16, rows * Vp));
       PMB_TRY(gemm_bf16(st, 0, 0, rows, D, V, lm->dlogits16, Vp, table16, D, dhid + (size_t)r0 * D * 2, D, nullptr, 1));
       PMB_TRY(gemm_bf16(st, 1, 0, V, D, rows, lm->dlogits16, Vp, hrows, D, dtable, D, r0 == 0 ? nullptr : dtable, 0));
+    } else if (prs) {
+      PMB_TRY(gemm_pairs(st, 0, 0, rows, D, V, dlog_p, table_p, lm->dhidden + r0 * D, D, nullptr));
+      PMB_TRY(gemm_pairs(st, 1, 0, V, D, rows, dlog_p, hid_p, dtable, D, r0 == 0 ? nullptr : dtable));
     } else {
       PMB_TRY(gemm(st, 0, 0, rows, D, V, lm->logits, Vp, table, D, lm->dhidden + r0 * D, D, nullptr, 0));
       PMB_TRY(gemm(st, 1, 0, V, D, rows, lm->logits, Vp, static_cast<const float*>(hrows), D, dtable, D, r0 == 0 ? nullptr : dtable, 0));

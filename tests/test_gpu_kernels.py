@@ -67,7 +67,7 @@ def test_gemm_unaligned_is_refused_by_tc_and_taken_by_auto(pm):
     with pytest.raises(pm.PmbError):
         pm.matmul(a, b, engine=2)
     out = pm.matmul(a, b, engine=0)
-    assert rel_err(out, a.cpu().double() @ b.cpu().double()) < 2e-6
+    assert rel_err(out, a.cpu().double() @ b.cpu().double()) < 3e-5    # auto: bf16 pairs through the library scratch
 
 
 def test_gemm_inplace_residual(pm):
