@@ -197,8 +197,9 @@ pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, 
     Pair16 wout, dop{w.dout_hi, w.dout_lo, d.D};
     PMB_TRY(split_pair16(st, static_cast<const float*>(dout), d.M, d.D, d.D, w.dout_hi, w.dout_lo, d.D));
     PMB_TRY(weight_pair(st, wx, false, p.out_proj_weight, d.I, d.D, w.wout_hi, w.wout_lo, &wout));
-    PMB_TRY(gemm_pairs(st, 1, 0, d.I, d.D, d.M, Pair16{w.normed_hi, w.normed_lo, d.I}, dop, g.out_proj_weight, d.D, nullptr));
-    PMB_TRY(gemm_pairs(st, 0, 1, d.M, d.I, d.D, dop, wout, w.dnormed, d.I, nullptr));
+    const PairGemm both[2] = {{1, 0, d.I, d.D, d.M, Pair16{w.normed_hi, w.normed_lo, d.I}, dop, g.out_proj_weight, d.D, nullptr},
+                              {0, 1, d.M, d.I, d.D, dop, wout, w.dnormed, d.I, nullptr}};
+    PMB_TRY(gemm_pairs_group(st, both, 2));
   } else {
     const float* df = static_cast<const float*>(dout);
     PMB_TRY(gemm(st, 1, 0, d.I, d.D, d.M, w.normed, d.I, df, d.D, g.out_proj_weight, d.D, nullptr, 0));
@@ -228,8 +229,11 @@ pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, 
     const Pair16 win = (wx && wx->pairs) ? Pair16{wx->in_proj, wx->in_lo, d.J} : Pair16{w.win_hi, w.win_lo, d.J};
     const Pair16 dxp{w.dxzd_hi, w.dxzd_lo, d.J};
     PMB_TRY(split_pair16(st, w.dxzd, d.M, d.J, d.J, w.dxzd_hi, w.dxzd_lo, d.J));
-    PMB_TRY(gemm_pairs(st, 1, 0, d.D, d.J, d.M, Pair16{w.x_hi, w.x_lo, d.D}, dxp, g.in_proj_weight, d.J, nullptr));
-    PMB_TRY(gemm_pairs(st, 0, 1, d.M, d.D, d.J, dxp, win, static_cast<float*>(dx), d.D, static_cast<const float*>(dx_accum)));
+    // the two gradients of in_proj as one launch, longer K first
+    const PairGemm gx{0, 1, d.M, d.D, d.J, dxp, win, static_cast<float*>(dx), d.D, static_cast<const float*>(dx_accum)};
+    const PairGemm gw{1, 0, d.D, d.J, d.M, Pair16{w.x_hi, w.x_lo, d.D}, dxp, g.in_proj_weight, d.J, nullptr};
+    const PairGemm both[2] = {d.J >= d.M ? gx : gw, d.J >= d.M ? gw : gx};
+    PMB_TRY(gemm_pairs_group(st, both, 2));
   } else {
     PMB_TRY(gemm(st, 1, 0, d.D, d.J, d.M, static_cast<const float*>(x), d.D, w.dxzd, d.J, g.in_proj_weight, d.J, nullptr, 0));
     PMB_TRY(gemm(st, 0, 1, d.M, d.D, d.J, w.dxzd, d.J, p.in_proj_weight, d.J, static_cast<float*>(dx), d.D, static_cast<const float*>(dx_accum), 0));

@@ -64,10 +64,19 @@ __device__ __forceinline__ uint16_t float_to_bf16_bits(float f) {   // round to 
   return (uint16_t)(u >> 16);
 }
 
+// One launch carries up to two independent products: CTAs [0, pr[0].tiles) work on the first, the rest on the second.
+// Two products whose tile counts each fill the 148 SMs badly (weight-gradient and data-gradient of one projection)
+// then share the machine instead of running as two ragged waves.
+struct Problem { CUtensorMap mA, mB, mAlo, mBlo; Params p; int tiles_n; int tiles; };
+struct Group { Problem pr[2]; };
+
 template <bool SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                 const __grid_constant__ CUtensorMap mapAlo, const __grid_constant__ CUtensorMap mapBlo, Params p) {
+gemm_bf16_kernel(const __grid_constant__ Group g) {
+  const int which = ((int)blockIdx.x >= g.pr[0].tiles) ? 1 : 0;
+  const Problem& q = g.pr[which];
+  const Params& p = q.p;
+  const int tile = (int)blockIdx.x - (which ? g.pr[0].tiles : 0);
   constexpr int STAGES = Cfg<SPLIT>::STAGES;
   constexpr int STAGE_BYTES = Cfg<SPLIT>::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -82,7 +91,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * TBN;
+  const int m0 = (tile / q.tiles_n) * TBM, n0 = (tile % q.tiles_n) * TBN;
   const int num_kt = (p.K + TBK - 1) / TBK;
 
   if (threadIdx.x == 0) {
@@ -113,30 +122,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         mbar_expect_tx(full_bar(s), STAGE_BYTES);
         const int k0 = kt * TBK;
         if (!p.a_mn_major) {
-          tma_load_2d(a_dst, &mapA, k0, m0, full_bar(s));
+          tma_load_2d(a_dst, &q.mA, k0, m0, full_bar(s));
         } else {
 #pragma unroll
-          for (int j = 0; j < TBM / 64; ++j) tma_load_2d(a_dst + j * (TBK * 128), &mapA, m0 + 64 * j, k0, full_bar(s));
+          for (int j = 0; j < TBM / 64; ++j) tma_load_2d(a_dst + j * (TBK * 128), &q.mA, m0 + 64 * j, k0, full_bar(s));
         }
         if (!p.b_mn_major) {
-          tma_load_2d(b_dst, &mapB, k0, n0, full_bar(s));
+          tma_load_2d(b_dst, &q.mB, k0, n0, full_bar(s));
         } else {
 #pragma unroll
-          for (int j = 0; j < TBN / 64; ++j) tma_load_2d(b_dst + j * (TBK * 128), &mapB, n0 + 64 * j, k0, full_bar(s));
+          for (int j = 0; j < TBN / 64; ++j) tma_load_2d(b_dst + j * (TBK * 128), &q.mB, n0 + 64 * j, k0, full_bar(s));
         }
         if (SPLIT) {
           const uint32_t al_dst = a_dst + 2 * TILE_BYTES, bl_dst = al_dst + TILE_BYTES;
           if (!p.a_mn_major) {
-            tma_load_2d(al_dst, &mapAlo, k0, m0, full_bar(s));
+            tma_load_2d(al_dst, &q.mAlo, k0, m0, full_bar(s));
           } else {
 #pragma unroll
-            for (int j = 0; j < TBM / 64; ++j) tma_load_2d(al_dst + j * (TBK * 128), &mapAlo, m0 + 64 * j, k0, full_bar(s));
+            for (int j = 0; j < TBM / 64; ++j) tma_load_2d(al_dst + j * (TBK * 128), &q.mAlo, m0 + 64 * j, k0, full_bar(s));
           }
           if (!p.b_mn_major) {
-            tma_load_2d(bl_dst, &mapBlo, k0, n0, full_bar(s));
+            tma_load_2d(bl_dst, &q.mBlo, k0, n0, full_bar(s));
           } else {
 #pragma unroll
-            for (int j = 0; j < TBN / 64; ++j) tma_load_2d(bl_dst + j * (TBK * 128), &mapBlo, n0 + 64 * j, k0, full_bar(s));
+            for (int j = 0; j < TBN / 64; ++j) tma_load_2d(bl_dst + j * (TBK * 128), &q.mBlo, n0 + 64 * j, k0, full_bar(s));
           }
         }
         armed = kt + 1;
@@ -290,22 +299,24 @@ pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
   if (M <= 0 || N <= 0 || K <= 0) return fail(PMB_ERR_SHAPE, "gemm_bf16: non-positive dimension");
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return fail(PMB_ERR_SHAPE, "gemm_bf16: operands need 16-byte aligned bases and row pitches that are multiples of 8 elements");
-  if (cdiv(M, TBM) > 65535) return fail(PMB_ERR_SHAPE, "gemm_bf16: M too large");
+  if (cdiv(M, TBM) * cdiv(N, TBN) > 0x7fffffff) return fail(PMB_ERR_SHAPE, "gemm_bf16: too many tiles");
   static bool attr_set = false;
   if (!attr_set) {
     PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::SMEM_BYTES));
     attr_set = true;
   }
-  CUtensorMap mapA, mapB;
-  if (!ta) PMB_TRY(make_map(&mapA, A, K, M, lda, TBK, TBM)); else PMB_TRY(make_map(&mapA, A, M, K, lda, 64, TBK));
-  if (tb) PMB_TRY(make_map(&mapB, B, K, N, ldb, TBK, TBN)); else PMB_TRY(make_map(&mapB, B, N, K, ldb, 64, TBK));
-  Params p{};
+  Group g{};
+  Problem& q = g.pr[0];
+  if (!ta) PMB_TRY(make_map(&q.mA, A, K, M, lda, TBK, TBM)); else PMB_TRY(make_map(&q.mA, A, M, K, lda, 64, TBK));
+  if (tb) PMB_TRY(make_map(&q.mB, B, K, N, ldb, TBK, TBN)); else PMB_TRY(make_map(&q.mB, B, N, K, ldb, 64, TBK));
+  Params& p = q.p;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.a_mn_major = ta ? 1 : 0; p.b_mn_major = tb ? 0 : 1;
   p.C = C; p.ldc = ldc; p.R = R; p.out_bf16 = out_bf16;
-  dim3 grid((unsigned)cdiv(N, TBN), (unsigned)cdiv(M, TBM));
+  q.tiles_n = (int)cdiv(N, TBN); q.tiles = (int)(cdiv(M, TBM) * cdiv(N, TBN));
+  g.pr[1].tiles_n = 1; g.pr[1].tiles = 0;
   ProfScope prof(st, "gemm_bf16", 2.0 * M * N * K, 2.0 * ((double)M * K + (double)K * N) + (out_bf16 ? 2.0 : 4.0) * M * N * (R ? 2 : 1));
-  gemm_bf16_kernel<false><<<grid, NTHREADS, Cfg<false>::SMEM_BYTES, st>>>(mapA, mapB, mapA, mapB, p);
+  gemm_bf16_kernel<false><<<(unsigned)q.tiles, NTHREADS, Cfg<false>::SMEM_BYTES, st>>>(g);
   PMB_LAUNCHED();
   return PMB_OK;
 }
@@ -355,34 +366,54 @@ bool gemm_pairs_enabled() {
 
 // C (fp32) = op(A) op(B) (+ R) with both operands given as bf16 pairs: three kind::f16 MMAs per k-step.
 // Relative accuracy ~1e-5 of the result's scale; twice the tensor-core rate and less than half the shared-memory
-// traffic of the 3xTF32 kernel.
-pmb_status gemm_pairs(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const Pair16& A, const Pair16& B,
-                      float* C, int64_t ldc, const float* R) {
+// traffic of the 3xTF32 kernel.  Up to two independent products go out as one launch; the tiles of g[0] are
+// scheduled first, so put the product with the longer K there.
+pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n) {
   using namespace hb;
-  if (M <= 0 || N <= 0 || K <= 0) return fail(PMB_ERR_SHAPE, "gemm_pairs: M, N, K must be positive");
-  if ((A.ld & 7) || (B.ld & 7) ||
-      ((reinterpret_cast<uintptr_t>(A.hi) | reinterpret_cast<uintptr_t>(A.lo) | reinterpret_cast<uintptr_t>(B.hi) | reinterpret_cast<uintptr_t>(B.lo)) & 15))
-    return fail(PMB_ERR_UNSUPPORTED, "gemm_pairs: operands need 16-byte aligned bases and row pitches that are multiples of 8");
-  if (cdiv(M, TBM) > 65535) return fail(PMB_ERR_UNSUPPORTED, "gemm_pairs: M too large for the launch grid");
+  if (n < 1 || n > 2) return fail(PMB_ERR_ARG, "gemm_pairs_group: 1 or 2 products per launch");
   static bool attr_set = false;
   if (!attr_set) {
     PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::SMEM_BYTES));
     attr_set = true;
   }
-  CUtensorMap mAh, mAl, mBh, mBl;
-  if (!ta) { PMB_TRY(make_map(&mAh, A.hi, K, M, A.ld, TBK, TBM)); PMB_TRY(make_map(&mAl, A.lo, K, M, A.ld, TBK, TBM)); }
-  else { PMB_TRY(make_map(&mAh, A.hi, M, K, A.ld, 64, TBK)); PMB_TRY(make_map(&mAl, A.lo, M, K, A.ld, 64, TBK)); }
-  if (tb) { PMB_TRY(make_map(&mBh, B.hi, K, N, B.ld, TBK, TBN)); PMB_TRY(make_map(&mBl, B.lo, K, N, B.ld, TBK, TBN)); }
-  else { PMB_TRY(make_map(&mBh, B.hi, N, K, B.ld, 64, TBK)); PMB_TRY(make_map(&mBl, B.lo, N, K, B.ld, 64, TBK)); }
-  Params p{};
-  p.M = (int)M; p.N = (int)N; p.K = (int)K;
-  p.a_mn_major = ta ? 1 : 0; p.b_mn_major = tb ? 0 : 1;
-  p.C = C; p.ldc = ldc; p.R = R; p.out_bf16 = 0;
-  dim3 grid((unsigned)cdiv(N, TBN), (unsigned)cdiv(M, TBM));
-  ProfScope prof(st, "gemm_bf16x2", 2.0 * M * N * K, 4.0 * ((double)M * K + (double)K * N + (double)M * N * (R ? 2 : 1)));
-  gemm_bf16_kernel<true><<<grid, NTHREADS, Cfg<true>::SMEM_BYTES, st>>>(mAh, mBh, mAl, mBl, p);
+  Group g{};
+  g.pr[1].tiles_n = 1; g.pr[1].tiles = 0;
+  double flops = 0.0, bytes = 0.0;
+  int64_t total = 0;
+  for (int i = 0; i < n; ++i) {
+    const PairGemm& e = gs[i];
+    const int64_t M = e.M, N = e.N, K = e.K;
+    if (M <= 0 || N <= 0 || K <= 0) return fail(PMB_ERR_SHAPE, "gemm_pairs: M, N, K must be positive");
+    if ((e.A.ld & 7) || (e.B.ld & 7) ||
+        ((reinterpret_cast<uintptr_t>(e.A.hi) | reinterpret_cast<uintptr_t>(e.A.lo) | reinterpret_cast<uintptr_t>(e.B.hi) | reinterpret_cast<uintptr_t>(e.B.lo)) & 15))
+      return fail(PMB_ERR_UNSUPPORTED, "gemm_pairs: operands need 16-byte aligned bases and row pitches that are multiples of 8");
+    Problem& q = g.pr[i];
+    if (!e.ta) { PMB_TRY(make_map(&q.mA, e.A.hi, K, M, e.A.ld, TBK, TBM)); PMB_TRY(make_map(&q.mAlo, e.A.lo, K, M, e.A.ld, TBK, TBM)); }
+    else { PMB_TRY(make_map(&q.mA, e.A.hi, M, K, e.A.ld, 64, TBK)); PMB_TRY(make_map(&q.mAlo, e.A.lo, M, K, e.A.ld, 64, TBK)); }
+    if (e.tb) { PMB_TRY(make_map(&q.mB, e.B.hi, K, N, e.B.ld, TBK, TBN)); PMB_TRY(make_map(&q.mBlo, e.B.lo, K, N, e.B.ld, TBK, TBN)); }
+    else { PMB_TRY(make_map(&q.mB, e.B.hi, N, K, e.B.ld, 64, TBK)); PMB_TRY(make_map(&q.mBlo, e.B.lo, N, K, e.B.ld, 64, TBK)); }
+    Params& p = q.p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.a_mn_major = e.ta ? 1 : 0; p.b_mn_major = e.tb ? 0 : 1;
+    p.C = e.C; p.ldc = e.ldc; p.R = e.R; p.out_bf16 = 0;
+    q.tiles_n = (int)cdiv(N, TBN);
+    const int64_t t = cdiv(M, TBM) * cdiv(N, TBN);
+    total += t;
+    if (total > 0x7fffffff) return fail(PMB_ERR_UNSUPPORTED, "gemm_pairs: too many tiles");
+    q.tiles = (int)t;
+    flops += 2.0 * M * N * K;
+    bytes += 4.0 * ((double)M * K + (double)K * N + (double)M * N * (e.R ? 2 : 1));
+  }
+  ProfScope prof(st, "gemm_bf16x2", flops, bytes);
+  gemm_bf16_kernel<true><<<(unsigned)total, NTHREADS, Cfg<true>::SMEM_BYTES, st>>>(g);
   PMB_LAUNCHED();
   return PMB_OK;
+}
+
+pmb_status gemm_pairs(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const Pair16& A, const Pair16& B,
+                      float* C, int64_t ldc, const float* R) {
+  PairGemm e{ta, tb, M, N, K, A, B, C, ldc, R};
+  return gemm_pairs_group(st, &e, 1);
 }
 
 // Library-owned scratch for the pairs of callers that hand in fp32 operands (grow-only, one per device).
@@ -407,7 +438,7 @@ pmb_status gemm_scratch(size_t bytes, void** out) {
 bool gemm_f32_via_bf16x2_supported(int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                                    const float* B, int64_t ldb) {
   (void)ta; (void)tb; (void)A; (void)B; (void)lda; (void)ldb;
-  return M > 0 && N > 0 && K > 0 && cdiv(M, hb::TBM) <= 65535;
+  return M > 0 && N > 0 && K > 0;
 }
 
 // fp32 operands: one elementwise pass each into the scratch (rows compacted to a pitch that is a multiple of 8),

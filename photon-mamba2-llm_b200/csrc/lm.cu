@@ -507,8 +507,10 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
       PMB_TRY(gemm_bf16(st, 0, 0, rows, D, V, lm->dlogits16, Vp, table16, D, dhid + (size_t)r0 * D * 2, D, nullptr, 1));
       PMB_TRY(gemm_bf16(st, 1, 0, V, D, rows, lm->dlogits16, Vp, hrows, D, dtable, D, r0 == 0 ? nullptr : dtable, 0));
     } else if (prs) {
-      PMB_TRY(gemm_pairs(st, 0, 0, rows, D, V, dlog_p, table_p, lm->dhidden + r0 * D, D, nullptr));
-      PMB_TRY(gemm_pairs(st, 1, 0, V, D, rows, dlog_p, hid_p, dtable, D, r0 == 0 ? nullptr : dtable));
+      // one launch: the few long-K tiles of dhidden first, the many short tiles of dE fill the other SMs
+      const PairGemm both[2] = {{0, 0, rows, D, V, dlog_p, table_p, lm->dhidden + r0 * D, D, nullptr},
+                                {1, 0, V, D, rows, dlog_p, hid_p, dtable, D, r0 == 0 ? nullptr : dtable}};
+      PMB_TRY(gemm_pairs_group(st, both, 2));
     } else {
       PMB_TRY(gemm(st, 0, 0, rows, D, V, lm->logits, Vp, table, D, lm->dhidden + r0 * D, D, nullptr, 0));
       PMB_TRY(gemm(st, 1, 0, V, D, rows, lm->logits, Vp, static_cast<const float*>(hrows), D, dtable, D, r0 == 0 ? nullptr : dtable, 0));
