@@ -360,6 +360,7 @@ MICRO = {
     "gemm_out_proj_fwd": ("gemm", dict(M=65536, N=768, K=1536, ta=0, tb=0)),
     "gemm_small_c2_in_proj": ("gemm", dict(M=2048, N=3224, K=768, ta=0, tb=0)),
     "ssd_scan_fp32": ("ssd", dict(B=4, T=8192, H=32, P=64, N=128, G=1, Q=256)),
+    "ssd_scan_c2": ("ssd", dict(B=4, T=512, H=24, P=64, N=64, G=1, Q=256)),   # the scan as one layer of configs[1] sees it
     # BASELINE configs[4]: scan microbench, bf16 inputs / fp32 state, at a quarter of the batch (B=16 in the config)
     "ssd_scan_bf16_in": ("ssd16", dict(B=4, T=8192, H=32, P=64, N=128, G=1, Q=256)),
     "ssd_scan_bf16_in_full": ("ssd16", dict(B=16, T=8192, H=32, P=64, N=128, G=1, Q=256)),

@@ -13,10 +13,10 @@ __global__ void column_sum_kernel(const float* __restrict__ partial, int64_t row
 // with the K-1 previous inputs in registers, so every global access is a coalesced vector access and
 // each input row is read (TT+K-1)/TT times.
 // ---------------------------------------------------------------------------------------------
-template <int K, int VEC>
+template <int K, int VEC, int TT>
 __global__ void __launch_bounds__(128) conv_silu_fwd_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
                                                             const float* __restrict__ w, const float* __restrict__ bias,
-                                                            float* __restrict__ act, int X, int T, int TT) {
+                                                            float* __restrict__ act, int X, int T) {
   int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (c >= X) return;
   int tblocks = (T + TT - 1) / TT;
@@ -42,16 +42,25 @@ __global__ void __launch_bounds__(128) conv_silu_fwd_kernel(const float* __restr
     }
   }
   float* dst = act + (int64_t)b * T * X + c;
-  for (int t = t0; t < t1; ++t) {
+  // TT is a compile-time constant: all TT rows are requested before the first one is used
+  float cur[TT][VEC];
+#pragma unroll
+  for (int i = 0; i < TT; ++i) {
+    const int t = t0 + i;
     if (VEC == 4) {
-      float4 q = *reinterpret_cast<const float4*>(src + (int64_t)t * ldx);
-      win[0][K - 1] = q.x; win[1 % VEC][K - 1] = q.y; win[2 % VEC][K - 1] = q.z; win[3 % VEC][K - 1] = q.w;
+      float4 q = t < t1 ? *reinterpret_cast<const float4*>(src + (int64_t)t * ldx) : make_float4(0, 0, 0, 0);
+      cur[i][0] = q.x; cur[i][1 % VEC] = q.y; cur[i][2 % VEC] = q.z; cur[i][3 % VEC] = q.w;
     } else {
-      win[0][K - 1] = src[(int64_t)t * ldx];
+      cur[i][0] = t < t1 ? src[(int64_t)t * ldx] : 0.0f;
     }
+  }
+#pragma unroll
+  for (int i = 0; i < TT; ++i) {
+    const int t = t0 + i;
     float o[VEC];
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
+      win[v][K - 1] = cur[i][v];
       float u = br[v];
 #pragma unroll
       for (int k = 0; k < K; ++k) u = fmaf(wr[v][k], win[v][k], u);
@@ -59,8 +68,10 @@ __global__ void __launch_bounds__(128) conv_silu_fwd_kernel(const float* __restr
 #pragma unroll
       for (int k = 0; k < K - 1; ++k) win[v][k] = win[v][k + 1];
     }
-    if (VEC == 4) *reinterpret_cast<float4*>(dst + (int64_t)t * X) = make_float4(o[0], o[1 % VEC], o[2 % VEC], o[3 % VEC]);
-    else dst[(int64_t)t * X] = o[0];
+    if (t < t1) {
+      if (VEC == 4) *reinterpret_cast<float4*>(dst + (int64_t)t * X) = make_float4(o[0], o[1 % VEC], o[2 % VEC], o[3 % VEC]);
+      else dst[(int64_t)t * X] = o[0];
+    }
   }
 }
 
@@ -76,15 +87,18 @@ __global__ void dt_softplus_kernel(const float* __restrict__ xzd, int64_t ldx, i
 template <int K>
 static pmb_status launch_conv_fwd_k(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b, float* act) {
   // time steps per thread: short runs keep enough threads in flight for small token counts
-  const int TT = d.M >= 32768 ? 32 : 8;
+  const bool long_runs = d.M >= 32768;
+  const int TT = long_runs ? 16 : 8;
   bool vec = (d.X % 4 == 0) && (d.J % 4 == 0) && (d.I % 4 == 0) && ((reinterpret_cast<uintptr_t>(xzd) | reinterpret_cast<uintptr_t>(act)) % 16 == 0);
   int tblocks = (d.T + TT - 1) / TT;
   if (vec) {
     dim3 grid((unsigned)cdiv(d.X / 4, 128), (unsigned)(d.B * tblocks));
-    conv_silu_fwd_kernel<K, 4><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T, TT);
+    if (long_runs) conv_silu_fwd_kernel<K, 4, 16><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T);
+    else conv_silu_fwd_kernel<K, 4, 8><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T);
   } else {
     dim3 grid((unsigned)cdiv(d.X, 128), (unsigned)(d.B * tblocks));
-    conv_silu_fwd_kernel<K, 1><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T, TT);
+    if (long_runs) conv_silu_fwd_kernel<K, 1, 16><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T);
+    else conv_silu_fwd_kernel<K, 1, 8><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T);
   }
   PMB_LAUNCHED();
   return PMB_OK;
@@ -117,11 +131,11 @@ pmb_status conv_silu_dt_fwd(cudaStream_t st, const Dims& d, const float* xzd, co
 // A thread owns one channel and TT time steps; per-(block-row) partial dw/db go to `partial`
 // (rows = gridDim.y, K+1 values per channel) and are summed by column_sum_kernel (fixed order).
 // ---------------------------------------------------------------------------------------------
-template <int K, int VEC>
+template <int K, int VEC, int TT>
 __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
                                                             const float* __restrict__ w, const float* __restrict__ bias,
                                                             const float* __restrict__ dact, float* __restrict__ dxzd,
-                                                            float* __restrict__ partial, int X, int T, int TT) {
+                                                            float* __restrict__ partial, int X, int T) {
   int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (c >= X) return;
   int tblocks = (T + TT - 1) / TT;
@@ -162,11 +176,21 @@ __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restr
   }
   // Walk t from t0 to t1-1+(K-1): du[t] is needed by dxbc[t-(K-1) .. t]; du beyond the sequence end is 0.
   int tend = min(t1 + K - 1, T + K - 1);
-  for (int t = t0; t < tend; ++t) {
+  // all rows of the run are requested before the first one is used (TT is a compile-time constant)
+  float xall[TT + K - 1][VEC], dall[TT + K - 1][VEC];
+#pragma unroll
+  for (int i = 0; i < TT + K - 1; ++i) {
+    const int t = t0 + i;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) { xall[i][v] = 0.0f; dall[i][v] = 0.0f; }
+    if (t < tend && t < T) { load(src + (int64_t)t * ldx, xall[i]); load(dsrc + (int64_t)t * X, dall[i]); }
+  }
+#pragma unroll
+  for (int i = 0; i < TT + K - 1; ++i) {
+    const int t = t0 + i;
     float xn[VEC], dn[VEC];
 #pragma unroll
-    for (int v = 0; v < VEC; ++v) { xn[v] = 0.0f; dn[v] = 0.0f; }
-    if (t < T) { load(src + (int64_t)t * ldx, xn); load(dsrc + (int64_t)t * X, dn); }
+    for (int v = 0; v < VEC; ++v) { xn[v] = xall[i][v]; dn[v] = dall[i][v]; }
     float g[VEC];
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
@@ -193,7 +217,7 @@ __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restr
       g[v] = acc;
     }
     int tp = t - (K - 1);
-    if (tp >= t0 && tp < t1) {
+    if (t < tend && tp >= t0 && tp < t1) {
       if (VEC == 4) *reinterpret_cast<float4*>(ddst + (int64_t)tp * ldx) = make_float4(g[0], g[1 % VEC], g[2 % VEC], g[3 % VEC]);
       else ddst[(int64_t)tp * ldx] = g[0];
     }
@@ -209,7 +233,7 @@ __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restr
   }
 }
 
-static const int CONV_BWD_TT = 16;
+constexpr int CONV_BWD_TT = 16;
 
 size_t conv_bwd_ws_bytes(const Dims& d) {
   int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;
@@ -224,10 +248,10 @@ static pmb_status launch_conv_bwd_k(cudaStream_t st, const Dims& d, const float*
              ((reinterpret_cast<uintptr_t>(xzd) | reinterpret_cast<uintptr_t>(dact) | reinterpret_cast<uintptr_t>(dxzd)) % 16 == 0);
   if (vec) {
     dim3 grid((unsigned)cdiv(d.X / 4, 128), (unsigned)(d.B * tblocks));
-    conv_silu_bwd_kernel<K, 4><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, CONV_BWD_TT);
+    conv_silu_bwd_kernel<K, 4, CONV_BWD_TT><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T);
   } else {
     dim3 grid((unsigned)cdiv(d.X, 128), (unsigned)(d.B * tblocks));
-    conv_silu_bwd_kernel<K, 1><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, CONV_BWD_TT);
+    conv_silu_bwd_kernel<K, 1, CONV_BWD_TT><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T);
   }
   PMB_LAUNCHED();
   return PMB_OK;
@@ -306,10 +330,81 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_fwd_kernel(const f
   }
 }
 
+// float4 variant: width % 4 == 0, 16-byte aligned rows.  PER float4 per thread, blockDim.x * PER >= width / 4.
+template <int PER>
+__global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_fwd_vec_kernel(const float* __restrict__ y, const float* __restrict__ z,
+                                                                             int64_t ldz, const float* __restrict__ w,
+                                                                             float* __restrict__ out, float* __restrict__ rstd,
+                                                                             int width, float eps, uint16_t* __restrict__ out_hi,
+                                                                             uint16_t* __restrict__ out_lo) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const int nvec = width >> 2;
+  const float4* y4 = reinterpret_cast<const float4*>(y + row * width);
+  const float4* z4 = reinterpret_cast<const float4*>(z + row * ldz);
+  float4 g[PER];
+  float ss = 0.0f;
+#pragma unroll
+  for (int n = 0; n < PER; ++n) {
+    const int i = threadIdx.x + n * blockDim.x;
+    g[n] = make_float4(0, 0, 0, 0);
+    if (i < nvec) {
+      const float4 yv = y4[i], zv = z4[i];
+      g[n] = make_float4(yv.x * zv.x * sigmoid_acc(zv.x), yv.y * zv.y * sigmoid_acc(zv.y), yv.z * zv.z * sigmoid_acc(zv.z),
+                         yv.w * zv.w * sigmoid_acc(zv.w));
+      ss = fmaf(g[n].x, g[n].x, fmaf(g[n].y, g[n].y, fmaf(g[n].z, g[n].z, fmaf(g[n].w, g[n].w, ss))));
+    }
+  }
+  const float tot = block_sum(ss, red);
+  const float r = 1.0f / sqrtf(tot / (float)width + eps);
+  if (threadIdx.x == 0 && rstd) rstd[row] = r;
+  auto split = [](float v, uint32_t& h, uint32_t& l) {   // (hi, lo) bf16 pair, round to nearest even
+    const uint32_t u = __float_as_uint(v);
+    h = (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+    const uint32_t ul = __float_as_uint(v - __uint_as_float(h << 16));
+    l = (ul + 0x7fffu + ((ul >> 16) & 1u)) >> 16;
+  };
+#pragma unroll
+  for (int n = 0; n < PER; ++n) {
+    const int i = threadIdx.x + n * blockDim.x;
+    if (i < nvec) {
+      const float4 wv = reinterpret_cast<const float4*>(w)[i];
+      const float4 v = make_float4(g[n].x * r * wv.x, g[n].y * r * wv.y, g[n].z * r * wv.z, g[n].w * r * wv.w);
+      if (out) reinterpret_cast<float4*>(out + row * width)[i] = v;
+      if (out_hi) {
+        uint32_t h[4], l[4];
+        split(v.x, h[0], l[0]); split(v.y, h[1], l[1]); split(v.z, h[2], l[2]); split(v.w, h[3], l[3]);
+        reinterpret_cast<uint2*>(out_hi + row * width)[i] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+        reinterpret_cast<uint2*>(out_lo + row * width)[i] = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+      }
+    }
+  }
+}
+
+// threads per block for the float4 kernels: every thread owns exactly `per` float4 when width/4 divides evenly
+static inline int norm_vec_threads(int width, int* per) {
+  const int nvec = width / 4;
+  *per = (nvec + NORM_THREADS - 1) / NORM_THREADS;
+  int t = (nvec + *per - 1) / *per;
+  return ((t + 31) / 32) * 32;
+}
+static inline bool norm_vec_ok(int width, int64_t ldz, const void* a, const void* b, const void* c, const void* d2 = nullptr, const void* e2 = nullptr) {
+  auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return (width % 4 == 0) && (ldz % 4 == 0) && width / 4 <= 2 * NORM_THREADS && al(a) && al(b) && al(c) && al(d2) && al(e2);
+}
+
 pmb_status gated_rmsnorm_fwd(cudaStream_t st, int64_t rows, int width, float eps, const float* y, const float* z, int64_t ldz,
                              const float* w, float* out, float* rstd, uint16_t* out_hi, uint16_t* out_lo) {
   if (width > NORM_THREADS * NORM_MAX_PER_THREAD) return fail(PMB_ERR_SHAPE, "rmsnorm width %d > %d", width, NORM_THREADS * NORM_MAX_PER_THREAD);
   ProfScope prof(st, "gated_rmsnorm_fwd", 0.0, 4.0 * rows * 3.0 * width);
+  if (norm_vec_ok(width, ldz, y, z, w, out, out_hi) && (!out_lo || (reinterpret_cast<uintptr_t>(out_lo) & 15) == 0)) {
+    int per = 1;
+    const int threads = norm_vec_threads(width, &per);
+    if (per == 1) gated_rmsnorm_fwd_vec_kernel<1><<<(unsigned)rows, threads, 0, st>>>(y, z, ldz, w, out, rstd, width, eps, out_hi, out_lo);
+    else gated_rmsnorm_fwd_vec_kernel<2><<<(unsigned)rows, threads, 0, st>>>(y, z, ldz, w, out, rstd, width, eps, out_hi, out_lo);
+    PMB_LAUNCHED();
+    return PMB_OK;
+  }
   gated_rmsnorm_fwd_kernel<<<(unsigned)rows, NORM_THREADS, 0, st>>>(y, z, ldz, w, out, rstd, width, eps, out_hi, out_lo);
   PMB_LAUNCHED();
   return PMB_OK;
@@ -368,6 +463,71 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_bwd_kernel(const f
   }
 }
 
+// float4 variant of the backward (same row blocking and partial layout).
+template <int PER>
+__global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_bwd_vec_kernel(const float* __restrict__ dout, const float* __restrict__ y,
+                                                                             const float* __restrict__ z, int64_t ldz,
+                                                                             const float* __restrict__ w, const float* __restrict__ rstd,
+                                                                             float* __restrict__ dy, float* __restrict__ dz, int64_t lddz,
+                                                                             float* __restrict__ dw_partial, int64_t rows, int width) {
+  __shared__ float red[32];
+  const int nvec = width >> 2;
+  float4 dwacc[PER], wv[PER];
+#pragma unroll
+  for (int n = 0; n < PER; ++n) {
+    const int i = threadIdx.x + n * blockDim.x;
+    dwacc[n] = make_float4(0, 0, 0, 0);
+    wv[n] = i < nvec ? reinterpret_cast<const float4*>(w)[i] : make_float4(0, 0, 0, 0);
+  }
+  const int64_t r0 = (int64_t)blockIdx.x * NORM_ROWS;
+  for (int rr = 0; rr < NORM_ROWS; ++rr) {
+    const int64_t row = r0 + rr;
+    if (row >= rows) break;  // uniform across the block
+    const float r = rstd[row];
+    float4 zv[PER], yv[PER], dn[PER], gv[PER], sv[PER];
+    float dot = 0.0f;
+#pragma unroll
+    for (int n = 0; n < PER; ++n) {
+      const int i = threadIdx.x + n * blockDim.x;
+      zv[n] = yv[n] = dn[n] = gv[n] = sv[n] = make_float4(0, 0, 0, 0);
+      if (i < nvec) {
+        zv[n] = reinterpret_cast<const float4*>(z + row * ldz)[i];
+        yv[n] = reinterpret_cast<const float4*>(y + row * width)[i];
+        dn[n] = reinterpret_cast<const float4*>(dout + row * width)[i];
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < PER; ++n) {
+      sv[n] = make_float4(sigmoid_acc(zv[n].x), sigmoid_acc(zv[n].y), sigmoid_acc(zv[n].z), sigmoid_acc(zv[n].w));
+      gv[n] = make_float4(yv[n].x * zv[n].x * sv[n].x, yv[n].y * zv[n].y * sv[n].y, yv[n].z * zv[n].z * sv[n].z, yv[n].w * zv[n].w * sv[n].w);
+      dot = fmaf(dn[n].x * gv[n].x, wv[n].x, fmaf(dn[n].y * gv[n].y, wv[n].y, fmaf(dn[n].z * gv[n].z, wv[n].z, fmaf(dn[n].w * gv[n].w, wv[n].w, dot))));
+    }
+    const float tot = block_sum(dot, red);
+    const float coef = r * r * r * tot / (float)width;
+#pragma unroll
+    for (int n = 0; n < PER; ++n) {
+      const int i = threadIdx.x + n * blockDim.x;
+      if (i < nvec) {
+        float4 dg, o_dy, o_dz;
+#define PMB_NORM_LANE(c)                                                        \
+        dg.c = wv[n].c * r * dn[n].c - gv[n].c * coef;                           \
+        dwacc[n].c = fmaf(dn[n].c * gv[n].c, r, dwacc[n].c);                     \
+        o_dy.c = dg.c * zv[n].c * sv[n].c;                                       \
+        o_dz.c = dg.c * yv[n].c * (sv[n].c + zv[n].c * sv[n].c * (1.0f - sv[n].c));
+        PMB_NORM_LANE(x) PMB_NORM_LANE(y) PMB_NORM_LANE(z) PMB_NORM_LANE(w)
+#undef PMB_NORM_LANE
+        reinterpret_cast<float4*>(dy + row * width)[i] = o_dy;
+        reinterpret_cast<float4*>(dz + row * lddz)[i] = o_dz;
+      }
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < PER; ++n) {
+    const int i = threadIdx.x + n * blockDim.x;
+    if (i < nvec) reinterpret_cast<float4*>(dw_partial + (int64_t)blockIdx.x * width)[i] = dwacc[n];
+  }
+}
+
 // out[j] = sum_r partial[r*cols + j].  Block = 32 columns x 8 row lanes; each lane sums rows ty, ty+8, ...
 // and the 8 lane sums are added in a fixed order (deterministic).
 __global__ void __launch_bounds__(256) column_sum_kernel(const float* __restrict__ partial, int64_t rows, int cols, float* __restrict__ out) {
@@ -398,7 +558,14 @@ pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const flo
   float* partial = static_cast<float*>(ws);
   int64_t nblk = cdiv(rows, NORM_ROWS);
   ProfScope prof(st, "gated_rmsnorm_bwd", 0.0, 4.0 * rows * 5.0 * width);
-  gated_rmsnorm_bwd_kernel<<<(unsigned)nblk, NORM_THREADS, 0, st>>>(dout, y, z, ldz, w, rstd, dy, dz, lddz, partial, rows, width);
+  if (norm_vec_ok(width, ldz, dout, y, z, w, dy) && (lddz % 4 == 0) && ((reinterpret_cast<uintptr_t>(dz) | reinterpret_cast<uintptr_t>(partial)) & 15) == 0) {
+    int per = 1;
+    const int threads = norm_vec_threads(width, &per);
+    if (per == 1) gated_rmsnorm_bwd_vec_kernel<1><<<(unsigned)nblk, threads, 0, st>>>(dout, y, z, ldz, w, rstd, dy, dz, lddz, partial, rows, width);
+    else gated_rmsnorm_bwd_vec_kernel<2><<<(unsigned)nblk, threads, 0, st>>>(dout, y, z, ldz, w, rstd, dy, dz, lddz, partial, rows, width);
+  } else {
+    gated_rmsnorm_bwd_kernel<<<(unsigned)nblk, NORM_THREADS, 0, st>>>(dout, y, z, ldz, w, rstd, dy, dz, lddz, partial, rows, width);
+  }
   PMB_LAUNCHED();
   column_sum_kernel<<<(unsigned)cdiv(width, 32), 256, 0, st>>>(partial, nblk, width, dw);
   PMB_LAUNCHED();

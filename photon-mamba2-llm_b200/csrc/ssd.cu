@@ -312,13 +312,24 @@ __global__ void chunk_cumsum_kernel(SsdP p) {
   int h = w % p.H, bc = w / p.H, cc = bc % p.nc, bb = bc / p.nc;
   float carry = 0.0f;
   float* out = p.S + ((int64_t)bb * p.H + h) * p.T + (int64_t)cc * p.Q;
+  // the strided loads of up to 8 rounds are requested together, ahead of the dependent scan chain
+  constexpr int AHEAD = 8;
+  const float Ah = p.dt ? p.A[h] : 1.0f;
+  const float* srcv = p.dt ? p.dt : p.a;
+  float pre[AHEAD];
   for (int q0 = 0; q0 < p.Q; q0 += 32) {
+    const int r = (q0 >> 5) % AHEAD;
+    if (r == 0) {
+#pragma unroll
+      for (int j = 0; j < AHEAD; ++j) {
+        const int qq = q0 + 32 * j + lane;
+        pre[j] = (qq < p.Q) ? Ah * srcv[p.tok(bb, cc, qq) * p.H + h] : 0.0f;
+      }
+    }
     int q = q0 + lane;
     float v = 0.0f;
-    if (q < p.Q) {
-      int64_t tk = p.tok(bb, cc, q);
-      v = p.dt ? p.A[h] * p.dt[tk * p.H + h] : p.a[tk * p.H + h];
-    }
+#pragma unroll
+    for (int j = 0; j < AHEAD; ++j) if (j == r) v = pre[j];
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       float u = __shfl_up_sync(0xffffffffu, v, o);

@@ -434,34 +434,44 @@ pmb_status ssd_tc_cb(cudaStream_t st, const SsdIn& in, const SsdWs& ws) {
 }
 
 // xs[b,t,h,:] = x[b,t,h,:] * dt * exp(S_end - S_t)  (mode 0)   or   dYs[b,t,h,:] = dY[b,t,h,:] * exp(S_t)  (mode 1).
-// One warp per (b,t,h) row; float4 lanes.  HBM-bound: reads and writes (B,T,H,P) once.
-__global__ void prescale_rows_kernel(const float* __restrict__ src, int64_t ld, const float* __restrict__ S,
-                                     const float* __restrict__ dt, float* __restrict__ dst, int B, int T, int H, int P, int Q, int mode) {
-  int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  int lane = threadIdx.x & 31;
-  int64_t total = (int64_t)B * T * H;
-  if (w >= total) return;
-  int h = (int)(w % H); int64_t tk = w / H; int b = (int)(tk / T); int t = (int)(tk % T);
-  const float* sp = S + ((int64_t)b * H + h) * T;
-  float f;
-  if (mode == 0) {
-    int cend = (t / Q) * Q + Q - 1;
-    f = __expf(sp[cend] - sp[t]) * (dt ? dt[tk * H + h] : 1.0f);
-  } else {
-    f = __expf(sp[t]);
+// A thread owns one float4 of four (b,t,h) rows a grid stride apart and requests all four before using any.
+// HBM-bound: reads and writes (B,T,H,P) once.
+constexpr int PRESCALE_UNROLL = 4;
+__global__ void __launch_bounds__(256) prescale_rows_kernel(const float* __restrict__ src, int64_t ld, const float* __restrict__ S,
+                                                            const float* __restrict__ dt, float* __restrict__ dst, int B, int T, int H, int P,
+                                                            int Q, int mode) {
+  const int P4 = P >> 2;
+  const int64_t total = (int64_t)B * T * H * P4;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  float4 v[PRESCALE_UNROLL]; float f[PRESCALE_UNROLL]; float4* out[PRESCALE_UNROLL];
+#pragma unroll
+  for (int u = 0; u < PRESCALE_UNROLL; ++u) {
+    const int64_t idx = i0 + u * stride;
+    out[u] = nullptr; f[u] = 0.0f; v[u] = make_float4(0, 0, 0, 0);
+    if (idx < total) {
+      const int i = (int)(idx % P4); const int64_t w = idx / P4;
+      const int h = (int)(w % H); const int64_t tk = w / H; const int b = (int)(tk / T); const int t = (int)(tk % T);
+      const float* sp = S + ((int64_t)b * H + h) * T;
+      if (mode == 0) {
+        const int cend = (t / Q) * Q + Q - 1;
+        f[u] = __expf(sp[cend] - sp[t]) * (dt ? dt[tk * H + h] : 1.0f);
+      } else {
+        f[u] = __expf(sp[t]);
+      }
+      v[u] = reinterpret_cast<const float4*>(src + tk * ld + h * P)[i];
+      out[u] = reinterpret_cast<float4*>(dst + tk * (int64_t)(H * P) + h * P) + i;
+    }
   }
-  const float4* s4 = reinterpret_cast<const float4*>(src + tk * ld + h * P);
-  float4* d4 = reinterpret_cast<float4*>(dst + tk * (int64_t)(H * P) + h * P);
-  for (int i = lane; i < P / 4; i += 32) {
-    float4 v = s4[i];
-    d4[i] = make_float4(v.x * f, v.y * f, v.z * f, v.w * f);
-  }
+#pragma unroll
+  for (int u = 0; u < PRESCALE_UNROLL; ++u)
+    if (out[u]) *out[u] = make_float4(v[u].x * f[u], v[u].y * f[u], v[u].z * f[u], v[u].w * f[u]);
 }
 
 static pmb_status prescale(cudaStream_t st, const char* name, const float* src, int64_t ld, const SsdIn& in, const SsdWs& ws, float* dst, int mode) {
   int64_t rows = (int64_t)in.B * in.T * in.H;
   ProfScope prof(st, name, 0.0, 8.0 * rows * in.P);
-  prescale_rows_kernel<<<(unsigned)cdiv(rows * 32, 256), 256, 0, st>>>(src, ld, ws.S, in.dt, dst, in.B, in.T, in.H, in.P, in.Q, mode);
+  prescale_rows_kernel<<<(unsigned)cdiv(rows * (in.P / 4), 256 * PRESCALE_UNROLL), 256, 0, st>>>(src, ld, ws.S, in.dt, dst, in.B, in.T, in.H, in.P, in.Q, mode);
   PMB_LAUNCHED();
   return PMB_OK;
 }
