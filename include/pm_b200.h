@@ -97,7 +97,7 @@ pmb_status pmb_device_status(int32_t* h_word_out);
  * trans_b = 0: B is (K,N) row-major with ldb;                   1: B is stored (N,K).
  * d_R (may be NULL) is added to the product (same shape/ld as C); d_R may equal d_C.
  * engine: 0 = auto, 1 = fp32 FMA, 2 = tcgen05 3xTF32 with 128x128 tiles, 3 = tcgen05 3xTF32 with 128x64 tiles,
- * 4 = tcgen05 bf16 pairs: both operands are split into (hi, lo) bf16 pairs (hi + lo carries 16 mantissa bits) and each
+ * 4 / 5 / 6 = tcgen05 bf16 pairs with 128x128 single-CTA tiles / 256x256 / 256x128 CTA-pair tiles (cta_group::2): both operands are split into (hi, lo) bf16 pairs (hi + lo carries 16 mantissa bits) and each
  * k-step issues hi*hi + lo*hi + hi*lo with kind::f16, fp32 accumulation.  Error ~1e-5 of the result's scale (the
  * 3xTF32 kernels: ~1e-6), about 1.7x their speed.  Auto takes engine 4 when the operands are 16-byte aligned with row
  * lengths that are multiples of 8, else 3xTF32 when its alignment rules hold, else FMA; the environment variable

@@ -21,9 +21,14 @@ pmb_status gemm(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K
   if (engine == 1) return gemm_simt(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
   // engine 4, and "auto" unless PMB_GEMM_ENGINE=tf32: split both operands into bf16 pairs and use the kind::f16 kernel
   static const int no_x2 = [] { const char* e = getenv("PMB_GEMM_ENGINE"); return (e && strcmp(e, "tf32") == 0) ? 1 : 0; }();
-  if (engine == 4 || (engine == 0 && !no_x2)) {
-    if (gemm_f32_via_bf16x2_supported(ta, tb, M, N, K, A, lda, B, ldb)) return gemm_f32_via_bf16x2(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
-    if (engine == 4) return fail(PMB_ERR_UNSUPPORTED, "gemm: the bf16-pair engine needs 16-byte aligned operands and row lengths that are multiples of 8");
+  if (engine == 4 || engine == 5 || engine == 6 || (engine == 0 && !no_x2)) {
+    if (gemm_f32_via_bf16x2_supported(ta, tb, M, N, K, A, lda, B, ldb)) {
+      set_pair_override(engine == 4 ? 0 : engine == 5 ? 2 : engine == 6 ? 1 : -1);
+      pmb_status r = gemm_f32_via_bf16x2(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
+      set_pair_override(-1);
+      return r;
+    }
+    if (engine >= 4) return fail(PMB_ERR_UNSUPPORTED, "gemm: the bf16-pair engine needs 16-byte aligned operands and row lengths that are multiples of 8");
   }
   bool ok = gemm_tc_supported(ta, tb, M, N, K, A, lda, B, ldb, C, ldc);
   if ((engine == 2 || engine == 3) && !ok) return fail(PMB_ERR_UNSUPPORTED, "gemm: tcgen05 engine needs 16-byte aligned operands and leading dimensions");
@@ -97,7 +102,7 @@ extern "C" pmb_status pmb_gemm_f32(void* stream, int32_t trans_a, int32_t trans_
                                    float* d_C, int64_t ldc, const float* d_R, int32_t engine) {
   if (M <= 0 || N <= 0 || K <= 0) return fail(PMB_ERR_SHAPE, "gemm: M, N, K must be positive (got %lld, %lld, %lld)", (long long)M, (long long)N, (long long)K);
   if (lda < (trans_a ? M : K) || ldb < (trans_b ? K : N) || ldc < N) return fail(PMB_ERR_SHAPE, "gemm: leading dimension smaller than the row length");
-  if (engine < 0 || engine > 4) return fail(PMB_ERR_ARG, "gemm: engine must be 0..4");
+  if (engine < 0 || engine > 6) return fail(PMB_ERR_ARG, "gemm: engine must be 0..6");
   return gemm(static_cast<cudaStream_t>(stream), trans_a != 0, trans_b != 0, M, N, K, d_A, lda, d_B, ldb, d_C, ldc, d_R, engine);
 }
 

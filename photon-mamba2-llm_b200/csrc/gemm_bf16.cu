@@ -262,6 +262,254 @@ gemm_bf16_kernel(const __grid_constant__ Group g) {
   }
 }
 
+// ---- CTA-pair variant ------------------------------------------------------------------------------------
+// Two CTAs of a cluster (a CTA pair) own one 256x256 output tile.  Each loads its 128 rows of A and its 128
+// columns of B (64 KiB per k-tile with pairs, 32 KiB without, exactly what a 128x128 single-CTA tile loads) and
+// the leader issues tcgen05.mma.cta_group::2 with M = 256, N = 256: each SM multiplies its A rows by the B
+// columns of both, so a byte fetched from L2 feeds twice the tensor work.  The 128x128 kernel above is bound by
+// L2 -> shared-memory traffic at these shapes; this one halves that traffic per flop.
+//   full_bar[s]  (leader's copy): both CTAs' loads complete their bytes on it
+//   empty_bar[s] (one per CTA):   the leader commits the k-tile's MMAs to both, freeing the stage in both CTAs
+//   accum_bar    (one per CTA):   the leader commits the last MMAs to both; each CTA drains its own 128 TMEM lanes
+// Every wait is bounded; a CTA that gives up records it, stops issuing work and still joins the closing
+// cluster barrier, so its peer never waits for it unboundedly.
+// stage = A tile (128 x 64) + B tile (BN2/2 x 64), twice that with pairs; as many stages as fit in 192 KiB
+template <bool SPLIT, int BN2> struct PairCfg {
+  static constexpr int STAGE_BYTES = (SPLIT ? 2 : 1) * (TILE_BYTES + (BN2 / 2) * TBK * 2);
+  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank)); return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// tile load issued by either CTA of the pair, completing bytes on a barrier given as a cluster address
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
+      : "memory");
+}
+__device__ __forceinline__ void mma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+// BN2 = width of the pair's tile (256 or 128); each CTA loads BN2/2 columns of B.
+template <bool SPLIT, int BN2>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ Group g) {
+  const uint32_t rank = cluster_rank();
+  const int cluster_id = (int)(blockIdx.x >> 1);
+  const int which = (cluster_id >= g.pr[0].tiles) ? 1 : 0;
+  const Problem& q = g.pr[which];
+  const Params& p = q.p;
+  const int tile = cluster_id - (which ? g.pr[0].tiles : 0);
+  constexpr int BNH = BN2 / 2;                       // B columns (rows of the K-major tile) per CTA
+  constexpr int TILE_B = BNH * TBK * 2;
+  constexpr int HALF_BYTES = TILE_BYTES + TILE_B;    // one A tile + one B tile
+  constexpr int STAGE_BYTES = PairCfg<SPLIT, BN2>::STAGE_BYTES;
+  constexpr int STAGES = PairCfg<SPLIT, BN2>::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  uint8_t* tiles_ptr = smem_raw + (tiles - raw);
+  const uint32_t bars = tiles + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tiles_ptr + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 1));
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = (tile / q.tiles_n) * 256 + (int)rank * TBM;     // this CTA's rows of A and of the output
+  const int n0 = (tile % q.tiles_n) * BN2;                      // the pair's columns; this CTA loads B columns n0 + rank*128 ..
+  const int nb0 = n0 + (int)rank * BNH;
+  const int num_kt = (p.K + TBK - 1) / TBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(BN2) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();     // both CTAs' barriers are initialised before either signals the other's
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int armed = 0;
+      for (int kt = 0; kt < num_kt; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t ph = (kt / STAGES) & 1;
+        if (!mbar_wait(empty_bar(s), ph ^ 1u)) { atomicOr(&g_bf16_status, 1u); *abort_flag = 1; break; }
+        if (*abort_flag) break;
+        const uint32_t a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + TILE_BYTES;
+        const uint32_t fb = map_to_cta(full_bar(s), 0);            // the leader's barrier collects both CTAs' bytes
+        if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);
+        const int k0 = kt * TBK;
+        if (!p.a_mn_major) {
+          tma_load_2d_pair(a_dst, &q.mA, k0, m0, fb);
+        } else {
+#pragma unroll
+          for (int j = 0; j < TBM / 64; ++j) tma_load_2d_pair(a_dst + j * (TBK * 128), &q.mA, m0 + 64 * j, k0, fb);
+        }
+        if (!p.b_mn_major) {
+          tma_load_2d_pair(b_dst, &q.mB, k0, nb0, fb);
+        } else {
+#pragma unroll
+          for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(b_dst + j * (TBK * 128), &q.mB, nb0 + 64 * j, k0, fb);
+        }
+        if (SPLIT) {
+          const uint32_t al_dst = a_dst + HALF_BYTES, bl_dst = al_dst + TILE_BYTES;
+          if (!p.a_mn_major) {
+            tma_load_2d_pair(al_dst, &q.mAlo, k0, m0, fb);
+          } else {
+#pragma unroll
+            for (int j = 0; j < TBM / 64; ++j) tma_load_2d_pair(al_dst + j * (TBK * 128), &q.mAlo, m0 + 64 * j, k0, fb);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d_pair(bl_dst, &q.mBlo, k0, nb0, fb);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(bl_dst + j * (TBK * 128), &q.mBlo, nb0 + 64 * j, k0, fb);
+          }
+        }
+        armed = kt + 1;
+      }
+      // after giving up, the leader still waits (bounded) for the loads both CTAs have in flight
+      if (*abort_flag && rank == 0)
+        for (int kt = max(0, armed - STAGES); kt < armed; ++kt) mbar_wait(full_bar(kt % STAGES), (kt / STAGES) & 1);
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // M = 256 (two CTAs x 128 rows), N = 256
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+                             ((uint32_t)(BN2 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+      const uint32_t a_lbo = p.a_mn_major ? TBK * 128 : 16, b_lbo = p.b_mn_major ? TBK * 128 : 16;
+      const uint32_t a_kstep = p.a_mn_major ? 2048 : 32, b_kstep = p.b_mn_major ? 2048 : 32;
+      for (int kt = 0; kt < num_kt; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t ph = (kt / STAGES) & 1;
+        if (!mbar_wait(full_bar(s), ph)) { atomicOr(&g_bf16_status, 2u); *abort_flag = 1; break; }
+        if (*abort_flag) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_s = tiles + s * STAGE_BYTES, b_s = a_s + TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < TBK / 16; ++k) {
+          const uint64_t da = make_desc(a_s + k * a_kstep, a_lbo, 1024, 2), db = make_desc(b_s + k * b_kstep, b_lbo, 1024, 2);
+          if (SPLIT) {
+            const uint64_t dal = make_desc(a_s + HALF_BYTES + k * a_kstep, a_lbo, 1024, 2);
+            const uint64_t dbl = make_desc(b_s + HALF_BYTES + k * b_kstep, b_lbo, 1024, 2);
+            mma_bf16_pair(tmem_acc, dal, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+            mma_bf16_pair(tmem_acc, da, dbl, idesc, 1u);
+            mma_bf16_pair(tmem_acc, da, db, idesc, 1u);
+          } else {
+            mma_bf16_pair(tmem_acc, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit_pair(map_to_cta(empty_bar(s), 0));
+        umma_commit_pair(map_to_cta(empty_bar(s), 1));
+      }
+      umma_commit_pair(map_to_cta(accum_bar, 0));
+      umma_commit_pair(map_to_cta(accum_bar, 1));
+    }
+  } else {
+    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0));
+    if (!acc_ok && lane == 0) { atomicOr(&g_bf16_status, 8u); *abort_flag = 1; }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const bool aborted = __any_sync(0xffffffffu, *abort_flag != 0);
+    if (acc_ok && !aborted) {
+      const int lane_base = (warp & 3) * 32;
+      const int m = m0 + lane_base + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN2; c0 += 32) {
+        if (n0 + c0 >= p.N) break;      // uniform
+        uint32_t r[32];
+        tmem_ld32(tmem_acc + ((uint32_t)lane_base << 16) + (uint32_t)c0, r);
+        if (m < p.M) {
+          const int nb = n0 + c0;
+          if (p.out_bf16) {
+            uint16_t* crow = static_cast<uint16_t*>(p.C) + (int64_t)m * p.ldc + nb;
+            const uint16_t* rrow = p.R ? static_cast<const uint16_t*>(p.R) + (int64_t)m * p.ldc + nb : nullptr;
+            const bool vec = (nb + 32 <= p.N) && ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                             (!p.R || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+            if (vec) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+                if (rrow) {
+                  uint4 qv = *reinterpret_cast<const uint4*>(rrow + j);
+                  const uint32_t qq[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) { v[2 * e] += __uint_as_float(qq[e] << 16); v[2 * e + 1] += __uint_as_float(qq[e] & 0xffff0000u); }
+                }
+                uint4 o;
+                o.x = (uint32_t)float_to_bf16_bits(v[0]) | ((uint32_t)float_to_bf16_bits(v[1]) << 16);
+                o.y = (uint32_t)float_to_bf16_bits(v[2]) | ((uint32_t)float_to_bf16_bits(v[3]) << 16);
+                o.z = (uint32_t)float_to_bf16_bits(v[4]) | ((uint32_t)float_to_bf16_bits(v[5]) << 16);
+                o.w = (uint32_t)float_to_bf16_bits(v[6]) | ((uint32_t)float_to_bf16_bits(v[7]) << 16);
+                *reinterpret_cast<uint4*>(crow + j) = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < p.N) crow[j] = float_to_bf16_bits(__uint_as_float(r[j]) + (rrow ? bf16_bits_to_float(rrow[j]) : 0.0f));
+            }
+          } else {
+            float* crow = static_cast<float*>(p.C) + (int64_t)m * p.ldc + nb;
+            const float* rrow = p.R ? static_cast<const float*>(p.R) + (int64_t)m * p.ldc + nb : nullptr;
+            const bool vec = (nb + 32 <= p.N) && ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                             (!p.R || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+            if (vec) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                if (rrow) {
+                  float4 qv = *reinterpret_cast<const float4*>(rrow + j);
+                  v.x += qv.x; v.y += qv.y; v.z += qv.z; v.w += qv.w;
+                }
+                *reinterpret_cast<float4*>(crow + j) = v;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < p.N) crow[j] = __uint_as_float(r[j]) + (rrow ? rrow[j] : 0.0f);
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();     // neither CTA leaves (or frees TMEM) while the other may still read its shared memory or signal its barriers
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(BN2) : "memory");
+  }
+}
+
 struct MapKey {
   const void* base; int64_t inner, outer, ld; int bi, bo;
   bool operator<(const MapKey& o) const { return std::tie(base, inner, outer, ld, bi, bo) < std::tie(o.base, o.inner, o.outer, o.ld, o.bi, o.bo); }
@@ -315,6 +563,23 @@ pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
   p.C = C; p.ldc = ldc; p.R = R; p.out_bf16 = out_bf16;
   q.tiles_n = (int)cdiv(N, TBN); q.tiles = (int)(cdiv(M, TBM) * cdiv(N, TBN));
   g.pr[1].tiles_n = 1; g.pr[1].tiles = 0;
+  {
+    static const int env = [] { const char* e = getenv("PMB_GEMM_PAIR"); return e ? atoi(e) : -1; }();
+    const int64_t clusters = cdiv(M, 256) * cdiv(N, 256);
+    const bool pair = env >= 0 ? env != 0 : (M > 128 && clusters >= 4 * 74);
+    if (pair) {
+      static bool attr2 = false;
+      if (!attr2) {
+        PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_pair_kernel<false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<false, 256>::SMEM_BYTES));
+        attr2 = true;
+      }
+      q.tiles_n = (int)cdiv(N, 256); q.tiles = (int)clusters;
+      ProfScope prof(st, "gemm_bf16_pair256", 2.0 * M * N * K, 2.0 * ((double)M * K + (double)K * N) + (out_bf16 ? 2.0 : 4.0) * M * N * (R ? 2 : 1));
+      gemm_bf16_pair_kernel<false, 256><<<(unsigned)(2 * clusters), NTHREADS, PairCfg<false, 256>::SMEM_BYTES, st>>>(g);
+      PMB_LAUNCHED();
+      return PMB_OK;
+    }
+  }
   ProfScope prof(st, "gemm_bf16", 2.0 * M * N * K, 2.0 * ((double)M * K + (double)K * N) + (out_bf16 ? 2.0 : 4.0) * M * N * (R ? 2 : 1));
   gemm_bf16_kernel<false><<<(unsigned)q.tiles, NTHREADS, Cfg<false>::SMEM_BYTES, st>>>(g);
   PMB_LAUNCHED();
@@ -364,6 +629,24 @@ bool gemm_pairs_enabled() {
   return on != 0;
 }
 
+// Tile shape of the pair GEMM.  PMB_GEMM_PAIR=0/1/2 forces it.
+static int g_pair_override = -1;   // engine 4 / 5 of the public GEMM entry force the tile shape for one call
+void set_pair_override(int v) { g_pair_override = v; }
+// 0 = 128x128 single-CTA tiles, 1 = 256x128 CTA-pair tiles, 2 = 256x256 CTA-pair tiles
+static int pick_pair_mode(const PairGemm* gs, int n) {
+  static const int env = [] { const char* e = getenv("PMB_GEMM_PAIR"); return e ? atoi(e) : -1; }();
+  const int forced = g_pair_override >= 0 ? g_pair_override : env;
+  if (forced >= 0 && forced <= 2) return forced;
+  int64_t clusters = 0;
+  for (int i = 0; i < n; ++i) {
+    if (gs[i].M <= 128) return 0;        // a pair tile would be half empty
+    clusters += cdiv(gs[i].M, 256) * cdiv(gs[i].N, 256);
+  }
+  // 256x256 pair tiles read 96 bytes of shared memory per tensor-core clock instead of 128 and win once there are
+  // several full waves of the 74 CTA pairs; 256x128 pair tiles measured no faster than single-CTA tiles
+  return clusters >= 4 * 74 ? 2 : 0;
+}
+
 // C (fp32) = op(A) op(B) (+ R) with both operands given as bf16 pairs: three kind::f16 MMAs per k-step.
 // Relative accuracy ~1e-5 of the result's scale; twice the tensor-core rate and less than half the shared-memory
 // traffic of the 3xTF32 kernel.  Up to two independent products go out as one launch; the tiles of g[0] are
@@ -403,6 +686,31 @@ pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n) {
     q.tiles = (int)t;
     flops += 2.0 * M * N * K;
     bytes += 4.0 * ((double)M * K + (double)K * N + (double)M * N * (e.R ? 2 : 1));
+  }
+  const int pair_mode = pick_pair_mode(gs, n);
+  if (pair_mode) {
+    const int bn2 = pair_mode == 2 ? 256 : 128;
+    static bool attr2 = false;
+    if (!attr2) {
+      PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_pair_kernel<true, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<true, 256>::SMEM_BYTES));
+      PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_pair_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<true, 128>::SMEM_BYTES));
+      attr2 = true;
+    }
+    int64_t clusters = 0;
+    for (int i = 0; i < n; ++i) {
+      const PairGemm& e = gs[i];
+      Problem& q = g.pr[i];
+      // B boxes of the pair kernel are BN2/2 rows tall (K-major tiles); MN-major boxes stay 64 columns wide
+      if (e.tb) { PMB_TRY(make_map(&q.mB, e.B.hi, e.K, e.N, e.B.ld, TBK, bn2 / 2)); PMB_TRY(make_map(&q.mBlo, e.B.lo, e.K, e.N, e.B.ld, TBK, bn2 / 2)); }
+      q.tiles_n = (int)cdiv(e.N, bn2);
+      q.tiles = (int)(cdiv(e.M, 256) * cdiv(e.N, bn2));
+      clusters += q.tiles;
+    }
+    ProfScope prof(st, pair_mode == 2 ? "gemm_bf16x2_pair256" : "gemm_bf16x2_pair128", flops, bytes);
+    if (pair_mode == 2) gemm_bf16_pair_kernel<true, 256><<<(unsigned)(2 * clusters), NTHREADS, PairCfg<true, 256>::SMEM_BYTES, st>>>(g);
+    else gemm_bf16_pair_kernel<true, 128><<<(unsigned)(2 * clusters), NTHREADS, PairCfg<true, 128>::SMEM_BYTES, st>>>(g);
+    PMB_LAUNCHED();
+    return PMB_OK;
   }
   ProfScope prof(st, "gemm_bf16x2", flops, bytes);
   gemm_bf16_kernel<true><<<(unsigned)total, NTHREADS, Cfg<true>::SMEM_BYTES, st>>>(g);

@@ -54,10 +54,19 @@ def test_gemm_tcgen05_3xtf32(pm, M, N, K, ta, tb, engine):
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (304, 200, 104), (128, 552, 128), (64, 40, 32), (8, 8, 8),
                                    (520, 136, 264), (2048, 384, 768)])
 @pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0), (1, 1)])
-def test_gemm_tcgen05_bf16_pairs(pm, M, N, K, ta, tb):
+@pytest.mark.parametrize("engine", [4, 5, 6])      # 128x128 single-CTA tiles / 256x256 / 256x128 CTA-pair tiles
+def test_gemm_tcgen05_bf16_pairs(pm, M, N, K, ta, tb, engine):
     """fp32 operands split into (hi, lo) bf16 pairs, three kind::f16 MMAs per k-step: 16 mantissa bits per operand,
     so the error bound is ~2^-16 of the result's scale instead of the 3xTF32 kernel's ~2^-21."""
-    e = _gemm_case(pm, M, N, K, ta, tb, 4, residual=(M + tb) % 2 == 0)
+    e = _gemm_case(pm, M, N, K, ta, tb, engine, residual=(M + tb) % 2 == 0)
+    assert pm.device_status() == 0
+    assert e < 3e-5, e
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 0), (1, 1)])
+def test_gemm_auto_takes_pair_tiles_for_many_tiles(pm, ta, tb):
+    """17 x 18 = 306 tiles of 256x256 is above the threshold at which engine 0 switches to the CTA-pair kernel."""
+    e = _gemm_case(pm, 4344, 4600, 136, ta, tb, 0, residual=bool(ta))
     assert pm.device_status() == 0
     assert e < 3e-5, e
 
