@@ -15,6 +15,7 @@
 //
 // This file holds the SIMT (fp32 FMA) engine: one 64x64-tile kernel template, specialised by small functor
 // structs that say how to read operand elements and where results go.
+#include <cstdlib>
 #include "common.cuh"
 #include "kernels.h"
 #include "bgemm.cuh"
@@ -575,6 +576,39 @@ static Op make_op(const SsdP& p, int Mdim, int Ndim) {
   return op;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Independent kernels of one scan run side by side.  At training sizes of a few thousand tokens every kernel
+// of the scan occupies the GPU for tens of microseconds with one or two ragged waves of latency-bound CTAs, so
+// the chains that do not depend on each other (forward: C B^T next to x~ -> chunk states -> state pass;
+// backward: dG -> dC -> dB next to dstates -> reverse pass -> dx~ -> row sums) go to two streams joined by events.
+// One side stream and a handful of events per device, created on first use (make the first call outside stream
+// capture).  PMB_SSD_CONCURRENT=0 keeps everything on the caller's stream.
+// ---------------------------------------------------------------------------------------------
+struct SideLane { cudaStream_t s = nullptr; cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr}; };
+static SideLane g_side[64];
+
+static pmb_status side_lane(SideLane** out) {
+  *out = nullptr;
+  static const int on = [] { const char* e = getenv("PMB_SSD_CONCURRENT"); return (e && e[0] == '0') ? 0 : 1; }();
+  if (!on) return PMB_OK;
+  int dev = 0;
+  PMB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return PMB_OK;
+  SideLane& l = g_side[dev];
+  if (!l.s) {
+    PMB_CUDA(cudaStreamCreateWithFlags(&l.s, cudaStreamNonBlocking));
+    for (int i = 0; i < 4; ++i) PMB_CUDA(cudaEventCreateWithFlags(&l.ev[i], cudaEventDisableTiming));
+  }
+  *out = &l;
+  return PMB_OK;
+}
+// `to` waits for everything enqueued on `from` so far
+static pmb_status order_after(cudaStream_t from, cudaEvent_t ev, cudaStream_t to) {
+  PMB_CUDA(cudaEventRecord(ev, from));
+  PMB_CUDA(cudaStreamWaitEvent(to, ev, 0));
+  return PMB_OK;
+}
+
 pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, float* y, int64_t ldy, float* final_state,
                    const SsdWs& ws) {
   SsdP p;
@@ -588,8 +622,12 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
     PMB_LAUNCHED();
   }
   const bool tc = ssd_tc_supported(in) && (ldy % 4 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0);
+  SideLane* lane = nullptr;
+  if (tc) PMB_TRY(side_lane(&lane));
   if (tc) {
-    PMB_TRY(ssd_tc_cb(st, in, ws));
+    cudaStream_t sb = lane ? lane->s : st;
+    if (lane) PMB_TRY(order_after(st, lane->ev[0], sb));     // S is ready
+    PMB_TRY(ssd_tc_cb(sb, in, ws));
     PMB_TRY(ssd_tc_state(st, in, ws));
   } else {
     PMB_TRY(run_op(st, "ssd_cb", make_op<OpCB>(p, p.Q, p.Q), nbcg, 2.0 * tok * p.Q * p.N * p.G));
@@ -600,6 +638,7 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
     ProfScope prof(st, "ssd_state_pass", 0.0, 8.0 * nel * p.nc);
     PMB_TRY(launch_state_scan(st, p, p.hprev, init_state, p.hlast, 0));
   }
+  if (lane) PMB_TRY(order_after(lane->s, lane->ev[1], st));   // C B^T is ready
   if (tc) PMB_TRY(ssd_tc_scan(st, in, y, ldy, ws));
   else PMB_TRY(run_op(st, "ssd_chunk_scan", make_op<OpScan>(p, p.Q, p.P), nbch, 2.0 * tok * p.H * p.P * (p.Q + p.N)));
   if (final_state) PMB_CUDA(cudaMemcpyAsync(final_state, ws.hlast, (size_t)nel * sizeof(float), cudaMemcpyDeviceToDevice, st));
@@ -618,7 +657,12 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   const bool tc = ssd_tc_supported(in) && (lddy % 4 == 0) && (reinterpret_cast<uintptr_t>(dy) % 16 == 0) && (g.lddbc % 4 == 0) &&
                   ((reinterpret_cast<uintptr_t>(g.db) | reinterpret_cast<uintptr_t>(g.dc)) % 16 == 0);
   const bool tc_group = tc;
+  SideLane* lane = nullptr;
+  if (tc) PMB_TRY(side_lane(&lane));
+  cudaStream_t sb = lane ? lane->s : st;                      // stream of the dG -> dC -> dB chain
+  if (lane) PMB_TRY(order_after(st, lane->ev[0], sb));        // inputs of the scan are ready
   if (tc) PMB_TRY(ssd_tc_dstate(st, in, dy, lddy, ws));
+  if (lane) PMB_CUDA(cudaEventRecord(lane->ev[1], st));       // dY exp(S) is ready (dC reads it)
   else PMB_TRY(run_op(st, "ssd_bwd_dstate", make_op<OpDstate>(p, p.N, p.P), nbch, 2.0 * tok * p.H * p.N * p.P));
   {
     ProfScope prof(st, "ssd_bwd_state_pass", 0.0, 12.0 * p.B * p.H * p.N * p.P * p.nc);
@@ -626,6 +670,7 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
     state_dot_kernel<<<(unsigned)nbch, 256, 0, st>>>(p, dsend);
     PMB_LAUNCHED();
   }
+  if (lane) PMB_CUDA(cudaEventRecord(lane->ev[2], st));       // dh is ready (dB reads it)
   if (tc) PMB_TRY(ssd_tc_dx(st, in, dy, lddy, ws));
   else PMB_TRY(run_op(st, "ssd_bwd_dx", make_op<OpDx>(p, p.Q, p.P), nbch, 2.0 * tok * p.H * p.P * (p.Q + p.N)));
   {
@@ -645,28 +690,31 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   auto reduce = [&](int nsplit, int cols, int mode, float* out, int64_t ld, int tile = BM) -> pmb_status {
     if (nsplit <= 1) return PMB_OK;
     int64_t total = (int64_t)nbcg * p.Q * cols;
-    splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(ws.splitk, nsplit, p.Q, cols, mode, p.G, p.Q, out, ld, total, tile, 0);
+    splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, tc_group ? sb : st>>>(ws.splitk, nsplit, p.Q, cols, mode, p.G, p.Q, out, ld, total, tile, 0);
     PMB_LAUNCHED();
     return PMB_OK;
   };
   if (tc_group) {
     {
-      ProfScope prof(st, "ssd_bwd_dg_tc", 2.0 * tok * p.H * p.Q * p.P, 0.0);
+      ProfScope prof(sb, "ssd_bwd_dg_tc", 2.0 * tok * p.H * p.Q * p.P, 0.0);
       const int nsg = ssd_tc_dg_nsplit_dims(p.B, p.T, p.H, p.G, p.Q);
-      PMB_TRY(ssd_tc_dg(st, in, dy, lddy, ws, nsg));
+      PMB_TRY(ssd_tc_dg(sb, in, dy, lddy, ws, nsg));
       PMB_TRY(reduce(nsg, p.Q, 0, ws.dG, 0, 128));
     }
     const int ns = ssd_tc_dbc_nsplit(in);
     {
-      ProfScope prof(st, "ssd_bwd_dc_tc", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
-      PMB_TRY(ssd_tc_dc(st, in, g.dc, g.lddbc, ws, ns));
+      if (lane) PMB_CUDA(cudaStreamWaitEvent(sb, lane->ev[1], 0));
+      ProfScope prof(sb, "ssd_bwd_dc_tc", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
+      PMB_TRY(ssd_tc_dc(sb, in, g.dc, g.lddbc, ws, ns));
       PMB_TRY(reduce(ns, p.N, 1, g.dc, g.lddbc));
     }
     {
-      ProfScope prof(st, "ssd_bwd_db_tc", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
-      PMB_TRY(ssd_tc_db(st, in, g.db, g.lddbc, ws, ns));
+      if (lane) PMB_CUDA(cudaStreamWaitEvent(sb, lane->ev[2], 0));
+      ProfScope prof(sb, "ssd_bwd_db_tc", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
+      PMB_TRY(ssd_tc_db(sb, in, g.db, g.lddbc, ws, ns));
       PMB_TRY(reduce(ns, p.N, 2, g.db, g.lddbc));
     }
+    if (lane) PMB_TRY(order_after(sb, lane->ev[3], st));       // join
     return PMB_OK;
   }
   {

@@ -3,7 +3,7 @@
 //   OUT[batch](m, n) = sum over segments s, k:  (A_s[m,k] * a_scale_s(m,k)) * (B_s[k,n] * b_scale_s(n,k))
 //
 // Each CTA owns one 128 x BN output tile of one batch entry.  Operand tiles arrive by TMA (rank-3 tensor
-// maps: contiguous axis, token/row axis, head/group axis) into a 3-stage ring; four "transform" warps
+// maps: contiguous axis, token/row axis, head/group axis) into a 3-stage ring; eight "transform" warps
 // rescale the landed tile in shared memory (decay factors, dt, causal mask) and split it into TF32-exact
 // high and low parts; one lane issues three kind::tf32 MMAs per k-step into a TMEM accumulator that lives
 // across all segments; the transform warps then drain TMEM and hand 32-column row pieces to Op::store.
@@ -40,7 +40,9 @@ namespace tcb {
 
 using namespace tcx;
 
-constexpr int BM = 128, BK = 32, NTHREADS = 192;
+// warp 0: TMA producer, warp 1: MMA issuer, warps 2..9: transform + epilogue.  Eight transform warps (two per
+// scheduler and CTA) because the scale/split work, not the tensor core, paces the small per-chunk problems.
+constexpr int BM = 128, BK = 32, NXF_WARPS = 8, NXF = NXF_WARPS * 32, NTHREADS = 64 + NXF;
 // Ring depth: 3 stages and one CTA per SM for 128-wide tiles; 2 stages for 64-wide tiles so that two CTAs share
 // an SM (the small per-(batch,chunk,head) problems are latency-bound: a second resident CTA fills the bubbles).
 template <int BN> struct RingDepth { static constexpr int STAGES = BN <= 64 ? 2 : 3; static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1; };
@@ -103,11 +105,11 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(split_bar(s), 4);
+      mbar_init(split_bar(s), NXF_WARPS);
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(accum_bar, 1);
-    for (int b = 0; b < 2; ++b) { mbar_init(seg_bar(b), 1); mbar_init(free_bar(b), 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(seg_bar(b), 1); mbar_init(free_bar(b), NXF_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -205,12 +207,15 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
     const int st = threadIdx.x - 64;
     bool ok = true;
     int it = 0;
-    const int lane_base = (warp & 3) * 32;
+    const int lane_base = (warp & 3) * 32;       // the TMEM lane quarter this warp may read
+    const int grp = (warp - 2) >> 2;             // two warps share a quarter: they take alternate 32-column chunks
     const int m = m0 + lane_base + lane;
-    float racc[Op::SEG_EPI ? BN / 32 : 1][32];
+    constexpr int NCHUNK = BN / 32 > 0 ? BN / 32 : 1;
+    constexpr int MYCH = (NCHUNK + 1) / 2;       // chunks per warp
+    float racc[Op::SEG_EPI ? MYCH : 1][32];
     if (Op::SEG_EPI) {
 #pragma unroll
-      for (int c = 0; c < (Op::SEG_EPI ? BN / 32 : 1); ++c)
+      for (int c = 0; c < (Op::SEG_EPI ? MYCH : 1); ++c)
 #pragma unroll
         for (int j = 0; j < 32; ++j) racc[c][j] = 0.0f;
     }
@@ -221,13 +226,16 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
       if (!done) { if (lane == 0) { atomicOr(status, 64u); *abort_flag = 1; } return false; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-      for (int c = 0; c < (Op::SEG_EPI ? BN / 32 : 1); ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_acc + (uint32_t)(b * BN) + ((uint32_t)lane_base << 16) + (uint32_t)(c * 32), r);
-        float v[32];
+      for (int cc = 0; cc < (Op::SEG_EPI ? MYCH : 1); ++cc) {
+        const int c = 2 * cc + grp;
+        if (c < NCHUNK) {
+          uint32_t r[32];
+          tmem_ld32(tmem_acc + (uint32_t)(b * BN) + ((uint32_t)lane_base << 16) + (uint32_t)(c * 32), r);
+          float v[32];
 #pragma unroll
-        for (int q = 0; q < 32; ++q) v[q] = __uint_as_float(r[q]);
-        op.seg_accumulate(j, m, n0 + c * 32, v, racc[c]);
+          for (int q = 0; q < 32; ++q) v[q] = __uint_as_float(r[q]);
+          op.seg_accumulate(j, m, n0 + c * 32, v, racc[cc]);
+        }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -240,9 +248,9 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
       if (Op::SEG_EPI) {
         // per-segment vectors for seg_accumulate go to one of two aux buffers; the barriers (transform warps only)
         // keep a fast warp from overwriting a buffer that a slower warp still reads for segment sg-2
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        op.stage_seg(sg, st, 128);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(NXF) : "memory");
+        op.stage_seg(sg, st, NXF);
+        asm volatile("bar.sync 1, %0;" ::"n"(NXF) : "memory");
       }
       for (int kt = kt0; kt < kt1; ++kt, ++it) {
         const int s = it % STAGES;
@@ -255,7 +263,7 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
         const int kbase = kt * BK;
         // A tile
 #pragma unroll 2
-        for (int i = st; i < G::A_BYTES / 16; i += 128) {
+        for (int i = st; i < G::A_BYTES / 16; i += NXF) {
           uint4 v = hi[i];
           float f[4] = {__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w)};
           if (Op::A_SCALE) {
@@ -276,7 +284,7 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
         uint4* bhi = hi + G::A_BYTES / 16;
         uint4* blo = lo + G::A_BYTES / 16;
 #pragma unroll 2
-        for (int i = st; i < G::B_BYTES / 16; i += 128) {
+        for (int i = st; i < G::B_BYTES / 16; i += NXF) {
           uint4 v = bhi[i];
           float f[4] = {__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w)};
           if (Op::B_SCALE) {
@@ -314,11 +322,13 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
     if (ok && acc_ok && !aborted) {
       if (Op::SEG_EPI) {
 #pragma unroll
-        for (int c = 0; c < (Op::SEG_EPI ? BN / 32 : 1); ++c)
-          if (m < op.Mdim && n0 + c * 32 < op.Ndim) op.store(m, n0 + c * 32, racc[c]);
+        for (int cc = 0; cc < (Op::SEG_EPI ? MYCH : 1); ++cc) {
+          const int c = 2 * cc + grp;
+          if (c < NCHUNK && m < op.Mdim && n0 + c * 32 < op.Ndim) op.store(m, n0 + c * 32, racc[cc]);
+        }
       } else {
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c0 = grp * 32; c0 < BN; c0 += 64) {
           uint32_t r[32];
           tmem_ld32(tmem_acc + ((uint32_t)lane_base << 16) + (uint32_t)c0, r);
           if (m < op.Mdim && n0 + c0 < op.Ndim) {
