@@ -187,16 +187,36 @@ pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, 
   BlockWs w;
   if (block_ws_layout(d, ws, ws_bytes, &w, w16 != nullptr) == 0 || !ws)
     return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_bytes(d, w16 != nullptr));
+  // The out_proj gradients do not wait for the recompute (dnormed = dout W_out^T needs neither x nor the recomputed
+  // activations) and dW_out is needed only when the block is done: with pair GEMMs both go to a side stream, where
+  // their CTAs fill the SMs that the latency-bound recompute and scan kernels leave idle.
+  SideLane* gl = nullptr;
+  if (pr) {
+    static const int on = [] { const char* e = getenv("PMB_BLOCK_CONCURRENT"); return (e && e[0] == '0') ? 0 : 1; }();
+    if (on) PMB_TRY(get_side_lane(1, &gl));
+  }
+  Pair16 wout{}, dop{w.dout_hi, w.dout_lo, d.D};
+  if (pr) {
+    cudaStream_t sg = gl ? gl->s : st;
+    if (gl) PMB_TRY(order_after(st, gl->ev[0], sg));            // dout is ready
+    PMB_TRY(split_pair16(sg, static_cast<const float*>(dout), d.M, d.D, d.D, w.dout_hi, w.dout_lo, d.D));
+    PMB_TRY(weight_pair(sg, wx, false, p.out_proj_weight, d.I, d.D, w.wout_hi, w.wout_lo, &wout));
+    if (gl) {
+      PMB_TRY(gemm_pairs(sg, 0, 1, d.M, d.I, d.D, dop, wout, w.dnormed, d.I, nullptr));
+      PMB_CUDA(cudaEventRecord(gl->ev[1], sg));                 // dnormed is ready
+    }
+  }
   // recompute (the out_proj product itself is not needed for gradients)
   PMB_TRY(block_fwd_core(st, d, p, x, w, wx));
   // out_proj: dW_out = normed^T dout;  dnormed = dout W_out^T
   if (w16) {
     PMB_TRY(gemm_bf16(st, 1, 0, d.I, d.D, d.M, w.normed16, d.I, dout, d.D, g.out_proj_weight, d.D, nullptr, 0));
     PMB_TRY(gemm_bf16(st, 0, 1, d.M, d.I, d.D, dout, d.D, w16->out_proj, d.D, w.dnormed, d.I, nullptr, 0));
+  } else if (pr && gl) {
+    PMB_TRY(order_after(st, gl->ev[2], gl->s));                 // the recomputed normed pair is ready
+    PMB_TRY(gemm_pairs(gl->s, 1, 0, d.I, d.D, d.M, Pair16{w.normed_hi, w.normed_lo, d.I}, dop, g.out_proj_weight, d.D, nullptr));
+    PMB_CUDA(cudaStreamWaitEvent(st, gl->ev[1], 0));
   } else if (pr) {
-    Pair16 wout, dop{w.dout_hi, w.dout_lo, d.D};
-    PMB_TRY(split_pair16(st, static_cast<const float*>(dout), d.M, d.D, d.D, w.dout_hi, w.dout_lo, d.D));
-    PMB_TRY(weight_pair(st, wx, false, p.out_proj_weight, d.I, d.D, w.wout_hi, w.wout_lo, &wout));
     const PairGemm both[2] = {{1, 0, d.I, d.D, d.M, Pair16{w.normed_hi, w.normed_lo, d.I}, dop, g.out_proj_weight, d.D, nullptr},
                               {0, 1, d.M, d.I, d.D, dop, wout, w.dnormed, d.I, nullptr}};
     PMB_TRY(gemm_pairs_group(st, both, 2));
@@ -225,6 +245,7 @@ pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, 
     PMB_TRY(gemm_bf16(st, 1, 0, d.D, d.J, d.M, x, d.D, w.dxzd16, d.J, g.in_proj_weight, d.J, nullptr, 0));
     PMB_TRY(gemm_bf16(st, 0, 1, d.M, d.D, d.J, w.dxzd16, d.J, w16->in_proj, d.J, dx, d.D, dx_accum, 1));
   } else if (pr) {
+    if (gl) PMB_TRY(order_after(gl->s, gl->ev[3], st));           // dW_out is done before this block returns
     // x and W_in were split by the recompute above
     const Pair16 win = (wx && wx->pairs) ? Pair16{wx->in_proj, wx->in_lo, d.J} : Pair16{w.win_hi, w.win_lo, d.J};
     const Pair16 dxp{w.dxzd_hi, w.dxzd_lo, d.J};

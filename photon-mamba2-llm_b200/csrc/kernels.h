@@ -98,6 +98,14 @@ bool gemm_f32_via_bf16x2_supported(int ta, int tb, int64_t M, int64_t N, int64_t
 pmb_status gemm_f32_via_bf16x2(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                                const float* B, int64_t ldb, float* C, int64_t ldc, const float* R);
 
+// ---- abi.cu: side streams for kernels that do not depend on each other.  One stream and four events per (device,
+// lane index), created on first use (so the first call should come before any stream capture).  lane 0: scan
+// chains; lane 1: gradient GEMMs of a block that are off the critical path.  *out stays NULL past device 63.
+struct SideLane { cudaStream_t s = nullptr; cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr}; };
+pmb_status get_side_lane(int idx, SideLane** out);
+// `to` waits for everything enqueued on `from` so far
+pmb_status order_after(cudaStream_t from, cudaEvent_t ev, cudaStream_t to);
+
 // ---- block.cu.  w16 != NULL selects bf16 storage: x / residual / out / dout / dx are bf16 and the two
 // projections use the bf16 weight copies; NULL = fp32 everywhere.
 // With pairs == true the struct instead carries pre-split (hi, lo) bf16 pairs of the fp32 weights (hi in in_proj /

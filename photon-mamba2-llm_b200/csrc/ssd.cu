@@ -584,31 +584,12 @@ static Op make_op(const SsdP& p, int Mdim, int Ndim) {
 // One side stream and a handful of events per device, created on first use (make the first call outside stream
 // capture).  PMB_SSD_CONCURRENT=0 keeps everything on the caller's stream.
 // ---------------------------------------------------------------------------------------------
-struct SideLane { cudaStream_t s = nullptr; cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr}; };
-static SideLane g_side[64];
-
 static pmb_status side_lane(SideLane** out) {
-  *out = nullptr;
   static const int on = [] { const char* e = getenv("PMB_SSD_CONCURRENT"); return (e && e[0] == '0') ? 0 : 1; }();
+  *out = nullptr;
   if (!on) return PMB_OK;
-  int dev = 0;
-  PMB_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return PMB_OK;
-  SideLane& l = g_side[dev];
-  if (!l.s) {
-    PMB_CUDA(cudaStreamCreateWithFlags(&l.s, cudaStreamNonBlocking));
-    for (int i = 0; i < 4; ++i) PMB_CUDA(cudaEventCreateWithFlags(&l.ev[i], cudaEventDisableTiming));
-  }
-  *out = &l;
-  return PMB_OK;
+  return get_side_lane(0, out);
 }
-// `to` waits for everything enqueued on `from` so far
-static pmb_status order_after(cudaStream_t from, cudaEvent_t ev, cudaStream_t to) {
-  PMB_CUDA(cudaEventRecord(ev, from));
-  PMB_CUDA(cudaStreamWaitEvent(to, ev, 0));
-  return PMB_OK;
-}
-
 pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, float* y, int64_t ldy, float* final_state,
                    const SsdWs& ws) {
   SsdP p;
