@@ -244,8 +244,13 @@ pmb_status pmb_mamba2_step(void* stream, const pmb_mamba2_config* cfg, const pmb
  * d_dhidden (B,T,D) is the gradient w.r.t. the stack output and is overwritten with the gradient
  * w.r.t. the stack input.  `on_layer_done(layer, user)` (may be NULL) is called on the host right
  * after layer `layer`'s gradient kernels have been enqueued (data-parallel callers enqueue that
- * layer's gradient all-reduce from it). */
+ * layer's gradient all-reduce from it).
+ * Workspace: pmb_mamba2_block_workspace_bytes() is enough.  With pmb_stack_workspace_bytes() (a second copy of the
+ * forward part of the block workspace) pmb_stack_bwd enqueues the recompute of block l-1 on an internal second
+ * stream while block l's gradient kernels run; results are identical.  The internal streams and events are
+ * created on the first call on a device (make that call outside stream capture).  One host thread per device. */
 typedef void (*pmb_layer_callback)(int32_t layer, void* user);
+size_t pmb_stack_workspace_bytes(const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen);
 pmb_status pmb_stack_fwd_ckpt(void* stream, const pmb_mamba2_config* cfg, int32_t n_layers,
                               const pmb_block_params* layers, int32_t batch, int32_t seqlen,
                               float* d_saved, void* d_ws, size_t ws_bytes);

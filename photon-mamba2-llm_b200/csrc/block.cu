@@ -73,25 +73,41 @@ struct BlockWs {
 
 bool block_uses_pairs(const Dims& d) { return gemm_pairs_enabled() && !(d.D % 8) && !(d.J % 8) && !(d.I % 8); }
 
-static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* out, bool bf16 = false) {
+// The workspace has a forward part (everything the recompute produces and the gradient kernels read) and a
+// backward part.  With nslots == 2 the forward part exists twice, so that the recompute of the next block can run
+// (on another stream) while the gradient kernels of the current block still read the other copy; `slot` selects
+// the copy this BlockWs points at.
+static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* out, bool bf16 = false, int nslots = 1, int slot = 0) {
   Arena ar(base, bytes);
   BlockWs w{};
-  w.xzd = ar.take<float>((size_t)d.M * d.J);
-  w.act = ar.take<float>((size_t)d.M * d.X);
-  w.dt = ar.take<float>((size_t)d.M * d.H);
-  w.y = ar.take<float>((size_t)d.M * d.I);
-  w.rstd = ar.take<float>((size_t)d.M);
-  w.normed = ar.take<float>((size_t)d.M * d.I);
-  w.Aneg = ar.take<float>((size_t)d.H);
-  {
-    size_t need = ssd_ws_layout(d.B, d.T, d.H, d.P, d.N, d.G, d.Q, nullptr, 0, nullptr);
-    char* sub = ar.take<char>(need);
-    if (sub) ssd_ws_layout(d.B, d.T, d.H, d.P, d.N, d.G, d.Q, sub, need, &w.ssd);
+  const bool pairs = !bf16 && block_uses_pairs(d);
+  const size_t md = (size_t)d.M * d.D, mi = (size_t)d.M * d.I, mj = (size_t)d.M * d.J, dj = (size_t)d.D * d.J, id = (size_t)d.I * d.D;
+  for (int sl = 0; sl < nslots; ++sl) {
+    BlockWs f{};
+    f.xzd = ar.take<float>(mj);
+    f.act = ar.take<float>((size_t)d.M * d.X);
+    f.dt = ar.take<float>((size_t)d.M * d.H);
+    f.y = ar.take<float>(mi);
+    f.rstd = ar.take<float>((size_t)d.M);
+    f.normed = ar.take<float>(pairs ? 0 : mi);       // with pair GEMMs the normalised output only exists as a pair
+    f.Aneg = ar.take<float>((size_t)d.H);
+    {
+      size_t need = ssd_ws_layout(d.B, d.T, d.H, d.P, d.N, d.G, d.Q, nullptr, 0, nullptr);
+      char* sub = ar.take<char>(need);
+      if (sub) ssd_ws_layout(d.B, d.T, d.H, d.P, d.N, d.G, d.Q, sub, need, &f.ssd);
+    }
+    f.normed16 = ar.take<uint16_t>(bf16 ? mi : 0);
+    if (pairs) {
+      f.x_hi = ar.take<uint16_t>(md); f.x_lo = ar.take<uint16_t>(md);
+      f.normed_hi = ar.take<uint16_t>(mi); f.normed_lo = ar.take<uint16_t>(mi);
+      f.win_hi = ar.take<uint16_t>(dj); f.win_lo = ar.take<uint16_t>(dj);
+    }
+    if (sl == slot) w = f;
   }
   // the gradient of the normalised gate output may overwrite it: dW_out (which reads `normed`, or its bf16 copy)
-  // is enqueued before the GEMM that writes `dnormed`
-  w.dnormed = w.normed;
-  w.dxzd = ar.take<float>((size_t)d.M * d.J);
+  // is enqueued before the GEMM that writes `dnormed`.  With pair GEMMs there is no fp32 `normed` to reuse.
+  w.dnormed = pairs ? ar.take<float>(mi) : w.normed;
+  w.dxzd = ar.take<float>(mj);
   w.dact = ar.take<float>((size_t)d.M * d.X);
   w.ddt = ar.take<float>((size_t)d.M * d.H);
   w.dA = ar.take<float>((size_t)d.H);
@@ -99,15 +115,10 @@ static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* 
   size_t nb = gated_rmsnorm_bwd_ws_bytes(d.M, d.I);
   if (nb > w.scratch_bytes) w.scratch_bytes = nb;
   w.scratch = reinterpret_cast<float*>(ar.take<char>(w.scratch_bytes));
-  w.normed16 = ar.take<uint16_t>(bf16 ? (size_t)d.M * d.I : 0);
-  w.dxzd16 = ar.take<uint16_t>(bf16 ? (size_t)d.M * d.J : 0);
-  if (!bf16 && block_uses_pairs(d)) {
-    const size_t md = (size_t)d.M * d.D, mi = (size_t)d.M * d.I, mj = (size_t)d.M * d.J, dj = (size_t)d.D * d.J, id = (size_t)d.I * d.D;
-    w.x_hi = ar.take<uint16_t>(md); w.x_lo = ar.take<uint16_t>(md);
+  w.dxzd16 = ar.take<uint16_t>(bf16 ? mj : 0);
+  if (pairs) {
     w.dout_hi = ar.take<uint16_t>(md); w.dout_lo = ar.take<uint16_t>(md);
-    w.normed_hi = ar.take<uint16_t>(mi); w.normed_lo = ar.take<uint16_t>(mi);
     w.dxzd_hi = ar.take<uint16_t>(mj); w.dxzd_lo = ar.take<uint16_t>(mj);
-    w.win_hi = ar.take<uint16_t>(dj); w.win_lo = ar.take<uint16_t>(dj);
     w.wout_hi = ar.take<uint16_t>(id); w.wout_lo = ar.take<uint16_t>(id);
   }
   if (out) *out = w;
@@ -115,6 +126,7 @@ static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* 
 }
 
 size_t block_ws_bytes(const Dims& d, bool bf16) { return block_ws_layout(d, nullptr, 0, nullptr, bf16); }
+size_t stack_ws_bytes(const Dims& d, bool bf16) { return block_ws_layout(d, nullptr, 0, nullptr, bf16, 2, 0); }
 
 static SsdIn ssd_inputs(const Dims& d, const pmb_block_params& p, const BlockWs& w) {
   SsdIn in{};
@@ -180,13 +192,26 @@ pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, 
   return PMB_OK;
 }
 
-pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* dout,
-                     const void* dx_accum, void* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes, const Weights16* wx) {
+// Backward of one block = recompute of steps 1-8 into forward slot `slot`, then the gradient kernels reading it.
+// block_bwd runs both on one stream; stack_bwd runs the recompute of block l-1 on a second stream while the
+// gradient kernels of block l are in flight (two forward slots).
+static pmb_status block_recompute(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, void* ws, size_t ws_bytes,
+                                  const Weights16* wx, int nslots, int slot) {
+  const bool bf = storage_is_bf16(wx);
+  BlockWs w;
+  if (block_ws_layout(d, ws, ws_bytes, &w, bf, nslots, slot) == 0 || !ws)
+    return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_layout(d, nullptr, 0, nullptr, bf, nslots, 0));
+  return block_fwd_core(st, d, p, x, w, wx);
+}
+
+static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* dout,
+                              const void* dx_accum, void* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes, const Weights16* wx,
+                              int nslots, int slot, cudaEvent_t recompute_done) {
   const Weights16* w16 = storage_is_bf16(wx) ? wx : nullptr;
   const bool pr = !w16 && block_uses_pairs(d);
   BlockWs w;
-  if (block_ws_layout(d, ws, ws_bytes, &w, w16 != nullptr) == 0 || !ws)
-    return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_bytes(d, w16 != nullptr));
+  if (block_ws_layout(d, ws, ws_bytes, &w, w16 != nullptr, nslots, slot) == 0 || !ws)
+    return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_layout(d, nullptr, 0, nullptr, w16 != nullptr, nslots, 0));
   // The out_proj gradients do not wait for the recompute (dnormed = dout W_out^T needs neither x nor the recomputed
   // activations) and dW_out is needed only when the block is done: with pair GEMMs both go to a side stream, where
   // their CTAs fill the SMs that the latency-bound recompute and scan kernels leave idle.
@@ -206,8 +231,8 @@ pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, 
       PMB_CUDA(cudaEventRecord(gl->ev[1], sg));                 // dnormed is ready
     }
   }
-  // recompute (the out_proj product itself is not needed for gradients)
-  PMB_TRY(block_fwd_core(st, d, p, x, w, wx));
+  // the recomputed activations (enqueued by the caller, possibly on another stream) are needed from here on
+  if (recompute_done) PMB_CUDA(cudaStreamWaitEvent(st, recompute_done, 0));
   // out_proj: dW_out = normed^T dout;  dnormed = dout W_out^T
   if (w16) {
     PMB_TRY(gemm_bf16(st, 1, 0, d.I, d.D, d.M, w.normed16, d.I, dout, d.D, g.out_proj_weight, d.D, nullptr, 0));
@@ -262,6 +287,12 @@ pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, 
   return PMB_OK;
 }
 
+pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* dout,
+                     const void* dx_accum, void* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes, const Weights16* wx) {
+  PMB_TRY(block_recompute(st, d, p, x, ws, ws_bytes, wx, 1, 0));
+  return block_grads(st, d, p, x, dout, dx_accum, dx, g, ws, ws_bytes, wx, 1, 0, nullptr);
+}
+
 }  // namespace pmb
 
 // -----------------------------------------------------------------------------------------------
@@ -309,20 +340,59 @@ pmb_status stack_fwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_blo
   return PMB_OK;
 }
 
-// dh_{l-1} = dh_l + dBlock_l/dx  (checkpoint.rs:110-135 reproduces this sum through the residual adds)
+// dh_{l-1} = dh_l + dBlock_l/dx  (checkpoint.rs:110-135 reproduces this sum through the residual adds).
+// With a workspace of stack_ws_bytes() the recompute of block l-1 is enqueued on a second stream before the
+// gradient kernels of block l, into the other forward slot: it needs only the saved block input, and at a few
+// thousand tokens both halves are latency-bound chains that leave most SMs idle, so they overlap well.
+// PMB_RECOMPUTE_AHEAD=0 turns it off.
 pmb_status stack_bwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_block_params* layers, const Weights16* w16,
                      const pmb_block_grads* grads, const void* saved, void* dhidden, void* ws, size_t ws_bytes,
                      pmb_layer_callback on_layer_done, void* user) {
-  size_t slot = (size_t)d.M * d.D * (storage_is_bf16(w16) ? 2 : 4);
+  const bool bf = storage_is_bf16(w16);
+  size_t slot = (size_t)d.M * d.D * (bf ? 2 : 4);
   const char* base = static_cast<const char*>(saved);
+  static const int ahead_on = [] { const char* e = getenv("PMB_RECOMPUTE_AHEAD"); return (e && e[0] == '0') ? 0 : 1; }();
+  SideLane* rl = nullptr;
+  // (fp32 blocks whose dimensions rule out pre-split pairs send their GEMMs through the library's one scratch
+  // buffer, which two streams must not share: those stay serial)
+  if (ahead_on && n_layers > 1 && (bf || block_uses_pairs(d)) && ws_bytes >= stack_ws_bytes(d, bf)) PMB_TRY(get_side_lane(3, &rl));
+  if (!rl) {
+    for (int l = n_layers - 1; l >= 0; --l) {
+      PMB_TRY(block_bwd(st, d, layers[l], base + (size_t)l * slot, dhidden, dhidden, dhidden, grads[l], ws, ws_bytes, w16 ? &w16[l] : nullptr));
+      if (on_layer_done) on_layer_done(l, user);
+    }
+    return PMB_OK;
+  }
+  // events: ev[0], ev[1] = recompute into slot 0 / 1 finished;  ev[2], ev[3] = gradient kernels reading slot 0 / 1 finished
+  cudaStream_t sr = rl->s;
+  PMB_CUDA(cudaEventRecord(rl->ev[2], st));            // everything before this call (saved inputs, weights) is ready,
+  PMB_CUDA(cudaEventRecord(rl->ev[3], st));            // and both slots are free
+  auto recompute = [&](int l) -> pmb_status {
+    const int sl = l & 1;
+    PMB_CUDA(cudaStreamWaitEvent(sr, rl->ev[2 + sl], 0));
+    PMB_TRY(block_recompute(sr, d, layers[l], base + (size_t)l * slot, ws, ws_bytes, w16 ? &w16[l] : nullptr, 2, sl));
+    PMB_CUDA(cudaEventRecord(rl->ev[sl], sr));
+    return PMB_OK;
+  };
+  PMB_TRY(recompute(n_layers - 1));
   for (int l = n_layers - 1; l >= 0; --l) {
-    PMB_TRY(block_bwd(st, d, layers[l], base + (size_t)l * slot, dhidden, dhidden, dhidden, grads[l], ws, ws_bytes, w16 ? &w16[l] : nullptr));
+    const int sl = l & 1;
+    if (l > 0) PMB_TRY(recompute(l - 1));                // into the other slot, whose last readers were block l+1's kernels
+    PMB_TRY(block_grads(st, d, layers[l], base + (size_t)l * slot, dhidden, dhidden, dhidden, grads[l], ws, ws_bytes,
+                        w16 ? &w16[l] : nullptr, 2, sl, rl->ev[sl]));
+    PMB_CUDA(cudaEventRecord(rl->ev[2 + sl], st));
     if (on_layer_done) on_layer_done(l, user);
   }
   return PMB_OK;
 }
 
 }  // namespace pmb
+
+extern "C" size_t pmb_stack_workspace_bytes(const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen) {
+  Dims d;
+  if (make_dims(cfg, batch, seqlen, &d) != PMB_OK) return 0;
+  return stack_ws_bytes(d, false);
+}
 
 extern "C" pmb_status pmb_stack_fwd_ckpt(void* stream, const pmb_mamba2_config* cfg, int32_t n_layers,
                                          const pmb_block_params* layers, int32_t batch, int32_t seqlen,

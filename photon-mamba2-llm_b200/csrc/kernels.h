@@ -100,7 +100,7 @@ pmb_status gemm_f32_via_bf16x2(cudaStream_t st, int ta, int tb, int64_t M, int64
 
 // ---- abi.cu: side streams for kernels that do not depend on each other.  One stream and four events per (device,
 // lane index), created on first use (so the first call should come before any stream capture).  lane 0: scan
-// chains; lane 1: gradient GEMMs of a block that are off the critical path.  *out stays NULL past device 63.
+// backward chains; 1: gradient GEMMs of a block that are off the critical path; 2: scan forward; 3: recompute-ahead.  *out stays NULL past device 63.
 struct SideLane { cudaStream_t s = nullptr; cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr}; };
 pmb_status get_side_lane(int idx, SideLane** out);
 // `to` waits for everything enqueued on `from` so far
@@ -118,6 +118,7 @@ struct Weights16 {
 inline bool storage_is_bf16(const Weights16* w) { return w && !w->pairs; }
 bool block_uses_pairs(const Dims& d);   // fp32 blocks route their four projections' GEMMs through bf16 pairs
 size_t block_ws_bytes(const Dims& d, bool bf16 = false);
+size_t stack_ws_bytes(const Dims& d, bool bf16 = false);   // two forward slots: lets stack_bwd recompute one block ahead
 pmb_status cast_f32_bf16(cudaStream_t st, const float* src, uint16_t* dst, int64_t n);
 pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* residual,
                      void* out, void* ws, size_t ws_bytes, const Weights16* w16);

@@ -584,11 +584,13 @@ static Op make_op(const SsdP& p, int Mdim, int Ndim) {
 // One side stream and a handful of events per device, created on first use (make the first call outside stream
 // capture).  PMB_SSD_CONCURRENT=0 keeps everything on the caller's stream.
 // ---------------------------------------------------------------------------------------------
-static pmb_status side_lane(SideLane** out) {
+// lane 0 serves the backward, lane 2 the forward: a recompute may be in flight on another stream while the
+// backward of the block above it runs, and the two must not share events
+static pmb_status side_lane(int idx, SideLane** out) {
   static const int on = [] { const char* e = getenv("PMB_SSD_CONCURRENT"); return (e && e[0] == '0') ? 0 : 1; }();
   *out = nullptr;
   if (!on) return PMB_OK;
-  return get_side_lane(0, out);
+  return get_side_lane(idx, out);
 }
 pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, float* y, int64_t ldy, float* final_state,
                    const SsdWs& ws) {
@@ -604,7 +606,7 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
   }
   const bool tc = ssd_tc_supported(in) && (ldy % 4 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0);
   SideLane* lane = nullptr;
-  if (tc) PMB_TRY(side_lane(&lane));
+  if (tc) PMB_TRY(side_lane(2, &lane));
   if (tc) {
     cudaStream_t sb = lane ? lane->s : st;
     if (lane) PMB_TRY(order_after(st, lane->ev[0], sb));     // S is ready
@@ -639,7 +641,7 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
                   ((reinterpret_cast<uintptr_t>(g.db) | reinterpret_cast<uintptr_t>(g.dc)) % 16 == 0);
   const bool tc_group = tc;
   SideLane* lane = nullptr;
-  if (tc) PMB_TRY(side_lane(&lane));
+  if (tc) PMB_TRY(side_lane(0, &lane));
   cudaStream_t sb = lane ? lane->s : st;                      // stream of the dG -> dC -> dB chain
   if (lane) PMB_TRY(order_after(st, lane->ev[0], sb));        // inputs of the scan are ready
   if (tc) PMB_TRY(ssd_tc_dstate(st, in, dy, lddy, ws));

@@ -79,6 +79,7 @@ def _load():
         "pmb_gated_rmsnorm_bwd_static_max_bytes": (sz, []),
         "pmb_gated_rmsnorm_bwd_static": (i32, [vp, i64, i32, vp, vp, vp, i64, vp, vp, vp, vp, i64, vp]),
         "pmb_mamba2_block_workspace_bytes": (sz, [cfgp, i32, i32]),
+        "pmb_stack_workspace_bytes": (sz, [cfgp, i32, i32]),
         "pmb_mamba2_block_fwd": (i32, [vp, cfgp, C.POINTER(_Params), i32, i32, vp, vp, vp, vp, sz]),
         "pmb_mamba2_block_bwd": (i32, [vp, cfgp, C.POINTER(_Params), i32, i32, vp, vp, vp, vp, C.POINTER(_Params), vp, sz]),
         "pmb_mamba2_step_workspace_bytes": (sz, [cfgp, i32]),
@@ -471,7 +472,7 @@ class ContextEncoder:
     def forward_checkpointed(self, x):
         B, T, D = x.shape
         L = len(self.layers)
-        n = lib.pmb_mamba2_block_workspace_bytes(C.byref(self.config.c()), B, T)
+        n = lib.pmb_stack_workspace_bytes(C.byref(self.config.c()), B, T)   # two forward slots: recompute one block ahead
         if self._ws is None or self._ws.numel() < n:
             self._ws = torch.empty(n, device=x.device, dtype=torch.uint8)
         saved = torch.empty(L + 1, B, T, D, device=x.device, dtype=torch.float32)
