@@ -44,17 +44,17 @@ pmb_status gemm(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K
   return gemm_simt(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
 }
 
-static SideLane g_lanes[64][4];
+static SideLane g_lanes[64][6];
 
 pmb_status get_side_lane(int idx, SideLane** out) {
   *out = nullptr;
   int dev = 0;
   PMB_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || idx < 0 || idx >= 4) return PMB_OK;
+  if (dev < 0 || dev >= 64 || idx < 0 || idx >= 6) return PMB_OK;
   SideLane& l = g_lanes[dev][idx];
   if (!l.s) {
     PMB_CUDA(cudaStreamCreateWithFlags(&l.s, cudaStreamNonBlocking));
-    for (int i = 0; i < 4; ++i) PMB_CUDA(cudaEventCreateWithFlags(&l.ev[i], cudaEventDisableTiming));
+    for (int i = 0; i < 6; ++i) PMB_CUDA(cudaEventCreateWithFlags(&l.ev[i], cudaEventDisableTiming));
   }
   *out = &l;
   return PMB_OK;

@@ -64,8 +64,8 @@ pmb_status cast_f32_bf16(cudaStream_t st, const float* src, uint16_t* dst, int64
 struct BlockWs {
   float *xzd, *act, *dt, *y, *rstd, *normed, *Aneg;
   SsdWs ssd;
-  float *dnormed, *dxzd, *dact, *ddt, *dA, *scratch;
-  size_t scratch_bytes;
+  float *dnormed, *dxzd, *dact, *ddt, *dA, *scratch, *scratch2;   // scratch: conv partials; scratch2: norm partials
+  size_t scratch_bytes, scratch2_bytes;
   uint16_t *normed16, *dxzd16;   // bf16 copies of the two GEMM operands (bf16-storage mode only)
   // fp32 mode with pair GEMMs: (hi, lo) bf16 pairs of every GEMM operand
   uint16_t *x_hi, *x_lo, *dout_hi, *dout_lo, *normed_hi, *normed_lo, *dxzd_hi, *dxzd_lo, *win_hi, *win_lo, *wout_hi, *wout_lo;
@@ -111,10 +111,11 @@ static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* 
   w.dact = ar.take<float>((size_t)d.M * d.X);
   w.ddt = ar.take<float>((size_t)d.M * d.H);
   w.dA = ar.take<float>((size_t)d.H);
+  // separate partial buffers: the reductions over them run on a side stream, next to later kernels of the block
   w.scratch_bytes = conv_bwd_ws_bytes(d);
-  size_t nb = gated_rmsnorm_bwd_ws_bytes(d.M, d.I);
-  if (nb > w.scratch_bytes) w.scratch_bytes = nb;
   w.scratch = reinterpret_cast<float*>(ar.take<char>(w.scratch_bytes));
+  w.scratch2_bytes = gated_rmsnorm_bwd_ws_bytes(d.M, d.I);
+  w.scratch2 = reinterpret_cast<float*>(ar.take<char>(w.scratch2_bytes));
   w.dxzd16 = ar.take<uint16_t>(bf16 ? mj : 0);
   if (pairs) {
     w.dout_hi = ar.take<uint16_t>(md); w.dout_lo = ar.take<uint16_t>(md);
@@ -252,7 +253,7 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   }
   // gate + norm: dy (in place over dnormed), dz -> z columns of dxzd
   PMB_TRY(gated_rmsnorm_bwd(st, d.M, d.I, w.dnormed, w.y, w.xzd, d.J, p.norm_weight, w.rstd, w.dnormed, w.dxzd, d.J,
-                            g.norm_weight, w.scratch, w.scratch_bytes));
+                            g.norm_weight, w.scratch2, w.scratch2_bytes, gl));
   // scan
   SsdGrads sg{};
   sg.dx = w.dact; sg.lddx = d.X;
@@ -263,14 +264,13 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   PMB_LAUNCHED();
   // conv + SiLU
   PMB_TRY(conv_silu_bwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, w.dact, w.dxzd, g.conv1d_weight, g.conv1d_bias,
-                        w.scratch, w.scratch_bytes));
+                        w.scratch, w.scratch_bytes, gl));
   // in_proj: dW_in = x^T dxzd;  dx = dxzd W_in^T (+ accumulated residual gradient)
   if (w16) {
     PMB_TRY(cast_f32_bf16(st, w.dxzd, w.dxzd16, d.M * d.J));
     PMB_TRY(gemm_bf16(st, 1, 0, d.D, d.J, d.M, x, d.D, w.dxzd16, d.J, g.in_proj_weight, d.J, nullptr, 0));
     PMB_TRY(gemm_bf16(st, 0, 1, d.M, d.D, d.J, w.dxzd16, d.J, w16->in_proj, d.J, dx, d.D, dx_accum, 1));
   } else if (pr) {
-    if (gl) PMB_TRY(order_after(gl->s, gl->ev[3], st));           // dW_out is done before this block returns
     // x and W_in were split by the recompute above
     const Pair16 win = (wx && wx->pairs) ? Pair16{wx->in_proj, wx->in_lo, d.J} : Pair16{w.win_hi, w.win_lo, d.J};
     const Pair16 dxp{w.dxzd_hi, w.dxzd_lo, d.J};
@@ -280,6 +280,7 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
     const PairGemm gw{1, 0, d.D, d.J, d.M, Pair16{w.x_hi, w.x_lo, d.D}, dxp, g.in_proj_weight, d.J, nullptr};
     const PairGemm both[2] = {d.J >= d.M ? gx : gw, d.J >= d.M ? gw : gx};
     PMB_TRY(gemm_pairs_group(st, both, 2));
+    if (gl) PMB_TRY(order_after(gl->s, gl->ev[3], st));           // dW_out and the small reductions are done when this block is
   } else {
     PMB_TRY(gemm(st, 1, 0, d.D, d.J, d.M, static_cast<const float*>(x), d.D, w.dxzd, d.J, g.in_proj_weight, d.J, nullptr, 0));
     PMB_TRY(gemm(st, 0, 1, d.M, d.D, d.J, w.dxzd, d.J, p.in_proj_weight, d.J, static_cast<float*>(dx), d.D, static_cast<const float*>(dx_accum), 0));

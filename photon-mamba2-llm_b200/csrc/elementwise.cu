@@ -258,7 +258,7 @@ static pmb_status launch_conv_bwd_k(cudaStream_t st, const Dims& d, const float*
 }
 
 pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
-                         const float* dact, float* dxzd, float* dw, float* db, void* ws, size_t ws_bytes) {
+                         const float* dact, float* dxzd, float* dw, float* db, void* ws, size_t ws_bytes, SideLane* red) {
   if (ws_bytes < conv_bwd_ws_bytes(d)) return fail(PMB_ERR_WORKSPACE, "conv bwd workspace too small");
   float* partial = static_cast<float*>(ws);
   ProfScope prof(st, "conv_silu_bwd", 0.0, 4.0 * d.M * 3.0 * d.X);
@@ -274,9 +274,11 @@ pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const
   }
   int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;
   int64_t rows = (int64_t)d.B * tblocks;
-  column_sum_kernel<<<(unsigned)cdiv(d.X * d.K, 32), 256, 0, st>>>(partial, rows, d.X * d.K, dw);
+  cudaStream_t rs = st;
+  if (red) { PMB_TRY(order_after(st, red->ev[4], red->s)); rs = red->s; }
+  column_sum_kernel<<<(unsigned)cdiv(d.X * d.K, 32), 256, 0, rs>>>(partial, rows, d.X * d.K, dw);
   PMB_LAUNCHED();
-  column_sum_kernel<<<(unsigned)cdiv(d.X, 32), 256, 0, st>>>(partial + rows * d.X * d.K, rows, d.X, db);
+  column_sum_kernel<<<(unsigned)cdiv(d.X, 32), 256, 0, rs>>>(partial + rows * d.X * d.K, rows, d.X, db);
   PMB_LAUNCHED();
   return PMB_OK;
 }
@@ -552,7 +554,8 @@ size_t gated_rmsnorm_bwd_ws_bytes(int64_t rows, int width) {
 }
 
 pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const float* dout, const float* y, const float* z, int64_t ldz,
-                             const float* w, const float* rstd, float* dy, float* dz, int64_t lddz, float* dw, void* ws, size_t ws_bytes) {
+                             const float* w, const float* rstd, float* dy, float* dz, int64_t lddz, float* dw, void* ws, size_t ws_bytes,
+                             SideLane* red) {
   if (width > NORM_THREADS * NORM_MAX_PER_THREAD) return fail(PMB_ERR_SHAPE, "rmsnorm width %d too large", width);
   if (ws_bytes < gated_rmsnorm_bwd_ws_bytes(rows, width)) return fail(PMB_ERR_WORKSPACE, "rmsnorm bwd workspace too small");
   float* partial = static_cast<float*>(ws);
@@ -567,7 +570,9 @@ pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const flo
     gated_rmsnorm_bwd_kernel<<<(unsigned)nblk, NORM_THREADS, 0, st>>>(dout, y, z, ldz, w, rstd, dy, dz, lddz, partial, rows, width);
   }
   PMB_LAUNCHED();
-  column_sum_kernel<<<(unsigned)cdiv(width, 32), 256, 0, st>>>(partial, nblk, width, dw);
+  cudaStream_t rs = st;
+  if (red) { PMB_TRY(order_after(st, red->ev[4], red->s)); rs = red->s; }
+  column_sum_kernel<<<(unsigned)cdiv(width, 32), 256, 0, rs>>>(partial, nblk, width, dw);
   PMB_LAUNCHED();
   return PMB_OK;
 }

@@ -4,19 +4,29 @@
 
 namespace pmb {
 
+// ---- abi.cu: side streams for kernels that do not depend on each other.  One stream and six events per (device,
+// lane index), created on first use (so the first call should come before any stream capture).  lane 0: scan
+// backward chains; 1: gradient GEMMs of a block that are off the critical path; 2: scan forward; 3: recompute-ahead;
+// 4: embedding-table gradient of the LM head; 5: in_proj weight gradient.  *out stays NULL past device 63.
+struct SideLane { cudaStream_t s = nullptr; cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}; };
+pmb_status get_side_lane(int idx, SideLane** out);
+// `to` waits for everything enqueued on `from` so far
+pmb_status order_after(cudaStream_t from, cudaEvent_t ev, cudaStream_t to);
+
 // ---- elementwise.cu
 pmb_status conv_silu_dt_fwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
                             const float* dt_bias, float* act, float* dt);
 size_t conv_bwd_ws_bytes(const Dims& d);
 pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
-                         const float* dact, float* dxzd, float* dw, float* db, void* ws, size_t ws_bytes);
+                         const float* dact, float* dxzd, float* dw, float* db, void* ws, size_t ws_bytes,
+                         SideLane* red = nullptr);   // red: the two small column reductions go to this lane (caller joins it)
 pmb_status gated_rmsnorm_fwd(cudaStream_t st, int64_t rows, int width, float eps, const float* y, const float* z,
                              int64_t ldz, const float* w, float* out, float* rstd, uint16_t* out_hi = nullptr,
                              uint16_t* out_lo = nullptr);   // out_hi/out_lo: optional (hi, lo) bf16 pair of the output; out may then be NULL
 size_t gated_rmsnorm_bwd_ws_bytes(int64_t rows, int width);
 pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const float* dout, const float* y, const float* z,
                              int64_t ldz, const float* w, const float* rstd, float* dy, float* dz, int64_t lddz,
-                             float* dw, void* ws, size_t ws_bytes);
+                             float* dw, void* ws, size_t ws_bytes, SideLane* red = nullptr);
 pmb_status column_sum(cudaStream_t st, const float* partial, int64_t rows, int cols, float* out);
 
 // ---- ssd.cu
@@ -97,14 +107,6 @@ bool gemm_f32_via_bf16x2_supported(int ta, int tb, int64_t M, int64_t N, int64_t
                                    const float* B, int64_t ldb);
 pmb_status gemm_f32_via_bf16x2(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                                const float* B, int64_t ldb, float* C, int64_t ldc, const float* R);
-
-// ---- abi.cu: side streams for kernels that do not depend on each other.  One stream and four events per (device,
-// lane index), created on first use (so the first call should come before any stream capture).  lane 0: scan
-// backward chains; 1: gradient GEMMs of a block that are off the critical path; 2: scan forward; 3: recompute-ahead.  *out stays NULL past device 63.
-struct SideLane { cudaStream_t s = nullptr; cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr}; };
-pmb_status get_side_lane(int idx, SideLane** out);
-// `to` waits for everything enqueued on `from` so far
-pmb_status order_after(cudaStream_t from, cudaEvent_t ev, cudaStream_t to);
 
 // ---- block.cu.  w16 != NULL selects bf16 storage: x / residual / out / dout / dx are bf16 and the two
 // projections use the bf16 weight copies; NULL = fp32 everywhere.

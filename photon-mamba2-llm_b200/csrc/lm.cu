@@ -481,6 +481,11 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
     hidden = reinterpret_cast<const char*>(lm->hsum);
   }
   char* dhid = reinterpret_cast<char*>(lm->dhidden);
+  SideLane* table_lane = nullptr;
+  if (prs && M <= lm->tile_rows) {
+    static const int on = [] { const char* e = getenv("PMB_HEAD_CONCURRENT"); return (e && e[0] == '0') ? 0 : 1; }();
+    if (on) PMB_TRY(get_side_lane(4, &table_lane));
+  }
   for (int64_t r0 = 0; r0 < M; r0 += lm->tile_rows) {
     int64_t rows = M - r0 < lm->tile_rows ? M - r0 : lm->tile_rows;
     const void* hrows = hidden + (size_t)r0 * D * esz;
@@ -506,6 +511,12 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
       PMB_TRY(cast_f32_bf16(st, lm->logits, lm->dlogits16, rows * Vp));
       PMB_TRY(gemm_bf16(st, 0, 0, rows, D, V, lm->dlogits16, Vp, table16, D, dhid + (size_t)r0 * D * 2, D, nullptr, 1));
       PMB_TRY(gemm_bf16(st, 1, 0, V, D, rows, lm->dlogits16, Vp, hrows, D, dtable, D, r0 == 0 ? nullptr : dtable, 0));
+    } else if (prs && table_lane) {
+      // single row tile: only dhidden is needed now; the embedding-table gradient runs on its own stream next to
+      // the first blocks of the stack backward and is joined before the embedding scatter
+      PMB_TRY(gemm_pairs(st, 0, 0, rows, D, V, dlog_p, table_p, lm->dhidden + r0 * D, D, nullptr));
+      PMB_TRY(order_after(st, table_lane->ev[0], table_lane->s));
+      PMB_TRY(gemm_pairs(table_lane->s, 1, 0, V, D, rows, dlog_p, hid_p, dtable, D, nullptr));
     } else if (prs) {
       // one launch: the few long-K tiles of dhidden first, the many short tiles of dE fill the other SMs
       const PairGemm both[2] = {{0, 0, rows, D, V, dlog_p, table_p, lm->dhidden + r0 * D, D, nullptr},
@@ -538,6 +549,7 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
     PMB_TRY(hier_op(lm, st, lm->dpool, lm->dhidden, lm->dhidden, 3));
   }
   PMB_TRY(stack_bwd(st, d, L0, lm->lp.data(), w16, lm->lg.data(), lm->saved, lm->dhidden, lm->ws, lm->ws_bytes, on_layer_done, user));
+  if (table_lane) PMB_TRY(order_after(table_lane->s, table_lane->ev[1], st));
   if (h16) embedding_bwd_bf16_kernel<<<(unsigned)cdiv(M * D, 256), 256, 0, st>>>(dtable, d_ids, reinterpret_cast<const uint16_t*>(lm->dhidden), M, D, V);
   else embedding_bwd_kernel<<<(unsigned)cdiv(M * D, 256), 256, 0, st>>>(dtable, d_ids, lm->dhidden, M, D, V);
   PMB_LAUNCHED();

@@ -663,10 +663,15 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
     ssd_chunk_finish_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p, ddt_x, dS, dDrow, dsend, g.da, g.ddt, ws.part);
     PMB_LAUNCHED();
   }
-  if (in.dt) {  // part = [dA partials (B*nc,H)] [dD partials (B*nc,H)]
-    PMB_TRY(column_sum(st, ws.part, (int64_t)p.B * p.nc, p.H, g.dA));
-    if (g.dD) PMB_TRY(column_sum(st, ws.part + (int64_t)p.B * p.nc * p.H, (int64_t)p.B * p.nc, p.H, g.dD));
-  }
+  auto head_sums = [&](cudaStream_t s) -> pmb_status {   // part = [dA partials (B*nc,H)] [dD partials (B*nc,H)]
+    if (!in.dt) return PMB_OK;
+    PMB_TRY(column_sum(s, ws.part, (int64_t)p.B * p.nc, p.H, g.dA));
+    if (g.dD) PMB_TRY(column_sum(s, ws.part + (int64_t)p.B * p.nc * p.H, (int64_t)p.B * p.nc, p.H, g.dD));
+    return PMB_OK;
+  };
+  // the two tiny per-head reductions ride at the end of the side chain instead of holding up the caller's stream
+  if (lane && tc_group) PMB_CUDA(cudaEventRecord(lane->ev[4], st));
+  else PMB_TRY(head_sums(st));
   // The three per-group contractions sum over the heads of the group; with few (batch, chunk) pairs the
   // head loop is split across CTAs and the partial tiles are summed in a fixed order afterwards.
   const int qt = (int)cdiv(p.Q, BM);
@@ -697,7 +702,11 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
       PMB_TRY(ssd_tc_db(sb, in, g.db, g.lddbc, ws, ns));
       PMB_TRY(reduce(ns, p.N, 2, g.db, g.lddbc));
     }
-    if (lane) PMB_TRY(order_after(sb, lane->ev[3], st));       // join
+    if (lane) {
+      PMB_CUDA(cudaStreamWaitEvent(sb, lane->ev[4], 0));
+      PMB_TRY(head_sums(sb));
+      PMB_TRY(order_after(sb, lane->ev[3], st));               // join
+    }
     return PMB_OK;
   }
   {
