@@ -310,6 +310,20 @@ pmb_status pmb_adamw_step(void* stream, int64_t n, float* d_params, const float*
                           float lr, float beta1, float beta2, float eps, float weight_decay, int32_t step,
                           float max_norm, const float* d_sumsq);
 
+/* ---- weights checkpoint I/O in the reference's format (pm-train/src/checkpoint.rs:25-97): a safetensors file with
+ * the parameters by position, "p_0000", "p_0001", ... in append_params order (embedding (V,D), then per block
+ * in_proj (D,J), conv1d_weight (X,1,K), conv1d_bias (X), a_log (H), d_skip (H), dt_bias (H), norm_weight (I),
+ * out_proj (I,D); the two-level model has its (D,D) projection between the two stacks), all F32.  Load requires
+ * the same tensor count, dtype and shapes and changes nothing when it fails.  Host-side file code; the stream is
+ * synchronised before the device copy.  The two *_f32 entry points are the format code alone, on host buffers:
+ * shapes_flat holds the extents of all tensors back to back, ranks[i] how many belong to tensor i. */
+pmb_status pmb_lm_save_safetensors(pmb_lm* lm, void* stream, const char* path);
+pmb_status pmb_lm_load_safetensors(pmb_lm* lm, void* stream, const char* path);
+pmb_status pmb_safetensors_save_f32(const char* path, int32_t n_tensors, const int64_t* shapes_flat, const int32_t* ranks,
+                                    const float* const* h_data);
+pmb_status pmb_safetensors_load_f32(const char* path, int32_t n_tensors, const int64_t* shapes_flat, const int32_t* ranks,
+                                    float* const* h_data);
+
 #ifdef __cplusplus
 }
 #endif

@@ -4,27 +4,25 @@
 // transient workspace that every layer reuses.
 #include "common.cuh"
 #include "kernels.h"
+#include "ssd_tc.h"
 
 namespace pmb {
-
-__global__ void a_neg_kernel(const float* __restrict__ a_log, float* __restrict__ A, int H) {
-  int h = blockIdx.x * blockDim.x + threadIdx.x;
-  if (h < H) A[h] = -expf(a_log[h]);
-}
 
 // One block per head: ddt_raw = ddt * sigmoid(dt_raw + bias) written into the dt columns of dxzd;
 // ddt_bias[h] = sum over tokens; da_log[h] = A[h] * dA[h]  (A = -exp(a_log)).
 __global__ void __launch_bounds__(256) dt_bwd_kernel(const float* __restrict__ xzd, float* __restrict__ dxzd, int64_t ld, int col0,
                                                      const float* __restrict__ dt_bias, const float* __restrict__ ddt,
                                                      const float* __restrict__ A, const float* __restrict__ dA,
-                                                     float* __restrict__ ddt_bias, float* __restrict__ da_log, int64_t rows, int H) {
+                                                     float* __restrict__ ddt_bias, float* __restrict__ da_log, int64_t rows, int H,
+                                                     uint16_t* __restrict__ pair_hi, uint16_t* __restrict__ pair_lo) {
   __shared__ float red[32];
   int h = blockIdx.x;
   float bias = dt_bias[h], acc = 0.0f;
   for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) {
     float s = sigmoid_acc(xzd[r * ld + col0 + h] + bias);
     float g = ddt[r * H + h] * s;
-    dxzd[r * ld + col0 + h] = g;
+    if (pair_hi) { uint32_t hh, ll; split_bf16_pair(g, hh, ll); pair_hi[r * ld + col0 + h] = (uint16_t)hh; pair_lo[r * ld + col0 + h] = (uint16_t)ll; }
+    else dxzd[r * ld + col0 + h] = g;
     acc += g;
   }
   float tot = block_sum(acc, red);
@@ -164,10 +162,11 @@ static pmb_status block_fwd_core(cudaStream_t st, const Dims& d, const pmb_block
     PMB_TRY(gemm_pairs(st, 0, 0, d.M, d.J, d.D, Pair16{w.x_hi, w.x_lo, d.D}, win, w.xzd, d.J, nullptr));
   }
   else PMB_TRY(gemm(st, 0, 0, d.M, d.J, d.D, static_cast<const float*>(x), d.D, p.in_proj_weight, d.J, w.xzd, d.J, nullptr, 0));
-  PMB_TRY(conv_silu_dt_fwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, p.dt_bias, w.act, w.dt));
-  a_neg_kernel<<<(unsigned)cdiv(d.H, 128), 128, 0, st>>>(p.a_log, w.Aneg, d.H);
-  PMB_LAUNCHED();
-  PMB_TRY(ssd_fwd(st, ssd_inputs(d, p, w), nullptr, w.y, d.I, nullptr, w.ssd));
+  // dt = softplus(dt_raw + bias) and A = -exp(a_log) are formed by the scan's first kernel (the chunk cumsum)
+  PMB_TRY(conv_silu_dt_fwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, p.dt_bias, w.act, nullptr));
+  SsdIn sin = ssd_inputs(d, p, w);
+  sin.dt_raw = w.xzd + d.I + d.X; sin.ld_raw = d.J; sin.dt_bias = p.dt_bias; sin.a_log = p.a_log;
+  PMB_TRY(ssd_fwd(st, sin, nullptr, w.y, d.I, nullptr, w.ssd));
   // with pair GEMMs the normalised output is only ever a GEMM operand: write it as a pair, skip the fp32 copy
   if (pr) PMB_TRY(gated_rmsnorm_fwd(st, d.M, d.I, d.eps, w.y, w.xzd, d.J, p.norm_weight, nullptr, w.rstd, w.normed_hi, w.normed_lo));
   else PMB_TRY(gated_rmsnorm_fwd(st, d.M, d.I, d.eps, w.y, w.xzd, d.J, p.norm_weight, w.normed, w.rstd));
@@ -252,19 +251,28 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
     PMB_TRY(gemm(st, 0, 1, d.M, d.I, d.D, df, d.D, p.out_proj_weight, d.D, w.dnormed, d.I, nullptr, 0));
   }
   // gate + norm: dy (in place over dnormed), dz -> z columns of dxzd
+  // With pair GEMMs the three producers of dxzd (this kernel: dz; the scan's dt path: ddt_raw; the conv backward:
+  // dxBC) write the (hi, lo) pair directly and the fp32 dxzd is never formed.  The norm backward also emits
+  // dY exp(S) for the scan backward when the tensor-core scan will run.
+  uint16_t* ph = pr ? w.dxzd_hi : nullptr;
+  uint16_t* pl = pr ? w.dxzd_lo : nullptr;
+  SsdIn sin = ssd_inputs(d, p, w);
+  NormBwdExtra ex{};
+  ex.dz_hi = ph; ex.dz_lo = pl;
+  if (pr && ssd_tc_supported(sin) && (d.P % 4 == 0)) { ex.dys = w.ssd.dys; ex.S = w.ssd.S; ex.H = d.H; ex.P = d.P; ex.T = d.T; sin.dys_ready = true; }
   PMB_TRY(gated_rmsnorm_bwd(st, d.M, d.I, w.dnormed, w.y, w.xzd, d.J, p.norm_weight, w.rstd, w.dnormed, w.dxzd, d.J,
-                            g.norm_weight, w.scratch2, w.scratch2_bytes, gl));
+                            g.norm_weight, w.scratch2, w.scratch2_bytes, gl, &ex));
   // scan
   SsdGrads sg{};
   sg.dx = w.dact; sg.lddx = d.X;
   sg.db = w.dact + d.I; sg.dc = w.dact + d.I + d.G * d.N; sg.lddbc = d.X;
   sg.da = nullptr; sg.ddt = w.ddt; sg.dA = w.dA; sg.dD = g.d_skip;
-  PMB_TRY(ssd_bwd(st, ssd_inputs(d, p, w), w.y, d.I, w.dnormed, d.I, sg, w.ssd));
-  dt_bwd_kernel<<<(unsigned)d.H, 256, 0, st>>>(w.xzd, w.dxzd, d.J, d.I + d.X, p.dt_bias, w.ddt, w.Aneg, w.dA, g.dt_bias, g.a_log, d.M, d.H);
+  PMB_TRY(ssd_bwd(st, sin, w.y, d.I, w.dnormed, d.I, sg, w.ssd));
+  dt_bwd_kernel<<<(unsigned)d.H, 256, 0, st>>>(w.xzd, w.dxzd, d.J, d.I + d.X, p.dt_bias, w.ddt, w.Aneg, w.dA, g.dt_bias, g.a_log, d.M, d.H, ph, pl);
   PMB_LAUNCHED();
   // conv + SiLU
   PMB_TRY(conv_silu_bwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, w.dact, w.dxzd, g.conv1d_weight, g.conv1d_bias,
-                        w.scratch, w.scratch_bytes, gl));
+                        w.scratch, w.scratch_bytes, gl, ph, pl));
   // in_proj: dW_in = x^T dxzd;  dx = dxzd W_in^T (+ accumulated residual gradient)
   if (w16) {
     PMB_TRY(cast_f32_bf16(st, w.dxzd, w.dxzd16, d.M * d.J));
@@ -274,7 +282,6 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
     // x and W_in were split by the recompute above
     const Pair16 win = (wx && wx->pairs) ? Pair16{wx->in_proj, wx->in_lo, d.J} : Pair16{w.win_hi, w.win_lo, d.J};
     const Pair16 dxp{w.dxzd_hi, w.dxzd_lo, d.J};
-    PMB_TRY(split_pair16(st, w.dxzd, d.M, d.J, d.J, w.dxzd_hi, w.dxzd_lo, d.J));
     // the two gradients of in_proj as one launch, longer K first
     const PairGemm gx{0, 1, d.M, d.D, d.J, dxp, win, static_cast<float*>(dx), d.D, static_cast<const float*>(dx_accum)};
     const PairGemm gw{1, 0, d.D, d.J, d.M, Pair16{w.x_hi, w.x_lo, d.D}, dxp, g.in_proj_weight, d.J, nullptr};

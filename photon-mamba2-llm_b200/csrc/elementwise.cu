@@ -135,7 +135,8 @@ template <int K, int VEC, int TT>
 __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
                                                             const float* __restrict__ w, const float* __restrict__ bias,
                                                             const float* __restrict__ dact, float* __restrict__ dxzd,
-                                                            float* __restrict__ partial, int X, int T) {
+                                                            float* __restrict__ partial, int X, int T,
+                                                            uint16_t* __restrict__ pair_hi, uint16_t* __restrict__ pair_lo) {
   int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (c >= X) return;
   int tblocks = (T + TT - 1) / TT;
@@ -218,7 +219,11 @@ __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restr
     }
     int tp = t - (K - 1);
     if (t < tend && tp >= t0 && tp < t1) {
-      if (VEC == 4) *reinterpret_cast<float4*>(ddst + (int64_t)tp * ldx) = make_float4(g[0], g[1 % VEC], g[2 % VEC], g[3 % VEC]);
+      const int64_t off = ((int64_t)b * T + tp) * ldx + col0 + c;
+      if (pair_hi) {       // the gradient is only a GEMM operand: write it as a (hi, lo) bf16 pair with the same pitch
+        if (VEC == 4) store_pair4(pair_hi + off, pair_lo + off, g[0], g[1 % VEC], g[2 % VEC], g[3 % VEC]);
+        else { uint32_t h, l; split_bf16_pair(g[0], h, l); pair_hi[off] = (uint16_t)h; pair_lo[off] = (uint16_t)l; }
+      } else if (VEC == 4) *reinterpret_cast<float4*>(ddst + (int64_t)tp * ldx) = make_float4(g[0], g[1 % VEC], g[2 % VEC], g[3 % VEC]);
       else ddst[(int64_t)tp * ldx] = g[0];
     }
   }
@@ -242,34 +247,35 @@ size_t conv_bwd_ws_bytes(const Dims& d) {
 
 template <int K>
 static pmb_status launch_conv_bwd_k(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
-                                    const float* dact, float* dxzd, float* partial) {
+                                    const float* dact, float* dxzd, float* partial, uint16_t* pair_hi, uint16_t* pair_lo) {
   int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;
   bool vec = (d.X % 4 == 0) && (d.J % 4 == 0) && (d.I % 4 == 0) &&
              ((reinterpret_cast<uintptr_t>(xzd) | reinterpret_cast<uintptr_t>(dact) | reinterpret_cast<uintptr_t>(dxzd)) % 16 == 0);
   if (vec) {
     dim3 grid((unsigned)cdiv(d.X / 4, 128), (unsigned)(d.B * tblocks));
-    conv_silu_bwd_kernel<K, 4, CONV_BWD_TT><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T);
+    conv_silu_bwd_kernel<K, 4, CONV_BWD_TT><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
   } else {
     dim3 grid((unsigned)cdiv(d.X, 128), (unsigned)(d.B * tblocks));
-    conv_silu_bwd_kernel<K, 1, CONV_BWD_TT><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T);
+    conv_silu_bwd_kernel<K, 1, CONV_BWD_TT><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
   }
   PMB_LAUNCHED();
   return PMB_OK;
 }
 
 pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
-                         const float* dact, float* dxzd, float* dw, float* db, void* ws, size_t ws_bytes, SideLane* red) {
+                         const float* dact, float* dxzd, float* dw, float* db, void* ws, size_t ws_bytes, SideLane* red,
+                         uint16_t* pair_hi, uint16_t* pair_lo) {
   if (ws_bytes < conv_bwd_ws_bytes(d)) return fail(PMB_ERR_WORKSPACE, "conv bwd workspace too small");
   float* partial = static_cast<float*>(ws);
   ProfScope prof(st, "conv_silu_bwd", 0.0, 4.0 * d.M * 3.0 * d.X);
   switch (d.K) {
-    case 2: PMB_TRY(launch_conv_bwd_k<2>(st, d, xzd, w, b, dact, dxzd, partial)); break;
-    case 3: PMB_TRY(launch_conv_bwd_k<3>(st, d, xzd, w, b, dact, dxzd, partial)); break;
-    case 4: PMB_TRY(launch_conv_bwd_k<4>(st, d, xzd, w, b, dact, dxzd, partial)); break;
-    case 5: PMB_TRY(launch_conv_bwd_k<5>(st, d, xzd, w, b, dact, dxzd, partial)); break;
-    case 6: PMB_TRY(launch_conv_bwd_k<6>(st, d, xzd, w, b, dact, dxzd, partial)); break;
-    case 7: PMB_TRY(launch_conv_bwd_k<7>(st, d, xzd, w, b, dact, dxzd, partial)); break;
-    case 8: PMB_TRY(launch_conv_bwd_k<8>(st, d, xzd, w, b, dact, dxzd, partial)); break;
+    case 2: PMB_TRY(launch_conv_bwd_k<2>(st, d, xzd, w, b, dact, dxzd, partial, pair_hi, pair_lo)); break;
+    case 3: PMB_TRY(launch_conv_bwd_k<3>(st, d, xzd, w, b, dact, dxzd, partial, pair_hi, pair_lo)); break;
+    case 4: PMB_TRY(launch_conv_bwd_k<4>(st, d, xzd, w, b, dact, dxzd, partial, pair_hi, pair_lo)); break;
+    case 5: PMB_TRY(launch_conv_bwd_k<5>(st, d, xzd, w, b, dact, dxzd, partial, pair_hi, pair_lo)); break;
+    case 6: PMB_TRY(launch_conv_bwd_k<6>(st, d, xzd, w, b, dact, dxzd, partial, pair_hi, pair_lo)); break;
+    case 7: PMB_TRY(launch_conv_bwd_k<7>(st, d, xzd, w, b, dact, dxzd, partial, pair_hi, pair_lo)); break;
+    case 8: PMB_TRY(launch_conv_bwd_k<8>(st, d, xzd, w, b, dact, dxzd, partial, pair_hi, pair_lo)); break;
     default: return fail(PMB_ERR_SHAPE, "d_conv %d unsupported", d.K);
   }
   int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;
@@ -465,13 +471,15 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_bwd_kernel(const f
   }
 }
 
-// float4 variant of the backward (same row blocking and partial layout).
+// float4 variant of the backward (same row blocking and partial layout).  Optional extras (see NormBwdExtra):
+// dz as a (hi, lo) bf16 pair instead of fp32, and dY exp(S) for the scan backward.
 template <int PER>
 __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_bwd_vec_kernel(const float* __restrict__ dout, const float* __restrict__ y,
                                                                              const float* __restrict__ z, int64_t ldz,
                                                                              const float* __restrict__ w, const float* __restrict__ rstd,
                                                                              float* __restrict__ dy, float* __restrict__ dz, int64_t lddz,
-                                                                             float* __restrict__ dw_partial, int64_t rows, int width) {
+                                                                             float* __restrict__ dw_partial, int64_t rows, int width,
+                                                                             NormBwdExtra ex) {
   __shared__ float red[32];
   const int nvec = width >> 2;
   float4 dwacc[PER], wv[PER];
@@ -519,7 +527,14 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_bwd_vec_kernel(con
         PMB_NORM_LANE(x) PMB_NORM_LANE(y) PMB_NORM_LANE(z) PMB_NORM_LANE(w)
 #undef PMB_NORM_LANE
         reinterpret_cast<float4*>(dy + row * width)[i] = o_dy;
-        reinterpret_cast<float4*>(dz + row * lddz)[i] = o_dz;
+        if (ex.dz_hi) store_pair4(ex.dz_hi + row * lddz + 4 * i, ex.dz_lo + row * lddz + 4 * i, o_dz.x, o_dz.y, o_dz.z, o_dz.w);
+        else reinterpret_cast<float4*>(dz + row * lddz)[i] = o_dz;
+        if (ex.dys) {    // dys[t, h, :] = dy[t, h, :] * exp(S[b, h, t]) for the scan backward (head width ex.P is a multiple of 4)
+          const int h = (4 * i) / ex.P;
+          const int64_t bb = row / ex.T, tt = row % ex.T;
+          const float f = __expf(ex.S[(bb * ex.H + h) * ex.T + tt]);
+          reinterpret_cast<float4*>(ex.dys + row * width)[i] = make_float4(o_dy.x * f, o_dy.y * f, o_dy.z * f, o_dy.w * f);
+        }
       }
     }
   }
@@ -555,17 +570,22 @@ size_t gated_rmsnorm_bwd_ws_bytes(int64_t rows, int width) {
 
 pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const float* dout, const float* y, const float* z, int64_t ldz,
                              const float* w, const float* rstd, float* dy, float* dz, int64_t lddz, float* dw, void* ws, size_t ws_bytes,
-                             SideLane* red) {
+                             SideLane* red, const NormBwdExtra* extra) {
+  NormBwdExtra ex{};
+  if (extra) ex = *extra;
   if (width > NORM_THREADS * NORM_MAX_PER_THREAD) return fail(PMB_ERR_SHAPE, "rmsnorm width %d too large", width);
   if (ws_bytes < gated_rmsnorm_bwd_ws_bytes(rows, width)) return fail(PMB_ERR_WORKSPACE, "rmsnorm bwd workspace too small");
   float* partial = static_cast<float*>(ws);
   int64_t nblk = cdiv(rows, NORM_ROWS);
   ProfScope prof(st, "gated_rmsnorm_bwd", 0.0, 4.0 * rows * 5.0 * width);
-  if (norm_vec_ok(width, ldz, dout, y, z, w, dy) && (lddz % 4 == 0) && ((reinterpret_cast<uintptr_t>(dz) | reinterpret_cast<uintptr_t>(partial)) & 15) == 0) {
+  const bool vec_ok = norm_vec_ok(width, ldz, dout, y, z, w, dy) && (lddz % 4 == 0) &&
+                      ((reinterpret_cast<uintptr_t>(dz) | reinterpret_cast<uintptr_t>(partial)) & 15) == 0;
+  if ((ex.dz_hi || ex.dys) && !vec_ok) return fail(PMB_ERR_UNSUPPORTED, "gated_rmsnorm_bwd: pair / scaled outputs need the vector kernel's alignment");
+  if (vec_ok) {
     int per = 1;
     const int threads = norm_vec_threads(width, &per);
-    if (per == 1) gated_rmsnorm_bwd_vec_kernel<1><<<(unsigned)nblk, threads, 0, st>>>(dout, y, z, ldz, w, rstd, dy, dz, lddz, partial, rows, width);
-    else gated_rmsnorm_bwd_vec_kernel<2><<<(unsigned)nblk, threads, 0, st>>>(dout, y, z, ldz, w, rstd, dy, dz, lddz, partial, rows, width);
+    if (per == 1) gated_rmsnorm_bwd_vec_kernel<1><<<(unsigned)nblk, threads, 0, st>>>(dout, y, z, ldz, w, rstd, dy, dz, lddz, partial, rows, width, ex);
+    else gated_rmsnorm_bwd_vec_kernel<2><<<(unsigned)nblk, threads, 0, st>>>(dout, y, z, ldz, w, rstd, dy, dz, lddz, partial, rows, width, ex);
   } else {
     gated_rmsnorm_bwd_kernel<<<(unsigned)nblk, NORM_THREADS, 0, st>>>(dout, y, z, ldz, w, rstd, dy, dz, lddz, partial, rows, width);
   }

@@ -19,14 +19,18 @@ pmb_status conv_silu_dt_fwd(cudaStream_t st, const Dims& d, const float* xzd, co
 size_t conv_bwd_ws_bytes(const Dims& d);
 pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
                          const float* dact, float* dxzd, float* dw, float* db, void* ws, size_t ws_bytes,
-                         SideLane* red = nullptr);   // red: the two small column reductions go to this lane (caller joins it)
+                         SideLane* red = nullptr,    // red: the two small column reductions go to this lane (caller joins it)
+                         uint16_t* pair_hi = nullptr, uint16_t* pair_lo = nullptr);   // pair: dxBC as a bf16 pair (pitch J) instead of fp32
 pmb_status gated_rmsnorm_fwd(cudaStream_t st, int64_t rows, int width, float eps, const float* y, const float* z,
                              int64_t ldz, const float* w, float* out, float* rstd, uint16_t* out_hi = nullptr,
                              uint16_t* out_lo = nullptr);   // out_hi/out_lo: optional (hi, lo) bf16 pair of the output; out may then be NULL
 size_t gated_rmsnorm_bwd_ws_bytes(int64_t rows, int width);
+// optional outputs of the gated RMSNorm backward: dz as a (hi, lo) bf16 pair (pitch lddz) instead of fp32, and
+// dys = dy * exp(S[b,h,t]) (S laid out (B,H,T), heads of width P, rows = B*T) for the scan backward
+struct NormBwdExtra { uint16_t* dz_hi = nullptr; uint16_t* dz_lo = nullptr; float* dys = nullptr; const float* S = nullptr; int H = 0, P = 1, T = 1; };
 pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const float* dout, const float* y, const float* z,
                              int64_t ldz, const float* w, const float* rstd, float* dy, float* dz, int64_t lddz,
-                             float* dw, void* ws, size_t ws_bytes, SideLane* red = nullptr);
+                             float* dw, void* ws, size_t ws_bytes, SideLane* red = nullptr, const NormBwdExtra* extra = nullptr);
 pmb_status column_sum(cudaStream_t st, const float* partial, int64_t rows, int cols, float* out);
 
 // ---- ssd.cu
@@ -40,6 +44,10 @@ struct SsdIn {
   const float* a;         // (B,T,H), used when dt == NULL
   const float* b; const float* c; int64_t ldbc;
   const float* D;         // (H) skip weights or NULL:  y += D[h] * x
+  bool dys_ready = false; // backward: ws.dys = dY exp(S) was already written by the caller
+  // forward only, optional: form dt and A inside the cumsum kernel.  dt = softplus(dt_raw[token*ld_raw + h] + dt_bias[h])
+  // is written to `dt` and A[h] = -exp(a_log[h]) to `A` (both must then point at writable buffers).
+  const float* dt_raw = nullptr; int64_t ld_raw = 0; const float* dt_bias = nullptr; const float* a_log = nullptr;
 };
 struct SsdWs {            // persistent between fwd and bwd of one scan
   float* S;               // (B,H,T) inclusive cumsum of a within each chunk

@@ -7,6 +7,8 @@
 // crates/pm-core/src/loss.rs:73-209).
 #include <vector>
 #include <cstdlib>
+#include <initializer_list>
+#include <vector>
 #include "common.cuh"
 #include "kernels.h"
 
@@ -554,6 +556,53 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
   else embedding_bwd_kernel<<<(unsigned)cdiv(M * D, 256), 256, 0, st>>>(dtable, d_ids, lm->dhidden, M, D, V);
   PMB_LAUNCHED();
   if (on_layer_done) on_layer_done(-1, user);
+  return PMB_OK;
+}
+
+// ---- weights checkpoint I/O (crates/pm-train/src/checkpoint.rs:25-97): parameters by position, "p_0000"...
+namespace pmb {
+pmb_status safetensors_save_f32(const char* path, int n, const int64_t* shapes, const int32_t* ranks, const float* const* data);
+pmb_status safetensors_load_f32(const char* path, int n, const int64_t* shapes, const int32_t* ranks, float* const* data);
+}
+
+// tensors of the handle in `append_params` order: offsets into the flat buffer, shapes, ranks
+static void lm_tensor_table(const pmb_lm* lm, std::vector<int64_t>* offs, std::vector<int64_t>* shapes, std::vector<int32_t>* ranks) {
+  const Dims& d = lm->d;
+  auto add = [&](int64_t off, std::initializer_list<int64_t> sh) {
+    offs->push_back(off); ranks->push_back((int32_t)sh.size());
+    for (int64_t x : sh) shapes->push_back(x);
+  };
+  add(lm->off[0], {lm->V, d.D});
+  for (int l = 0; l < lm->L; ++l) {
+    if (lm->L1 > 0 && l == lm->L0) add(lm->off_proj, {d.D, d.D});
+    const int64_t* f = &lm->off[1 + 8 * l];
+    add(f[0], {d.D, d.J}); add(f[1], {d.X, 1, d.K}); add(f[2], {d.X}); add(f[3], {d.H}); add(f[4], {d.H}); add(f[5], {d.H});
+    add(f[6], {d.I}); add(f[7], {d.I, d.D});
+  }
+}
+
+extern "C" pmb_status pmb_lm_save_safetensors(pmb_lm* lm, void* stream, const char* path) {
+  if (!lm || !path) return fail(PMB_ERR_ARG, "lm_save: NULL argument");
+  std::vector<int64_t> offs, shapes; std::vector<int32_t> ranks;
+  lm_tensor_table(lm, &offs, &shapes, &ranks);
+  std::vector<float> host((size_t)lm->n_params);
+  PMB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  PMB_CUDA(cudaMemcpy(host.data(), lm->params, host.size() * 4, cudaMemcpyDeviceToHost));
+  std::vector<const float*> ptrs;
+  for (int64_t o : offs) ptrs.push_back(host.data() + o);
+  return safetensors_save_f32(path, (int)offs.size(), shapes.data(), ranks.data(), ptrs.data());
+}
+
+extern "C" pmb_status pmb_lm_load_safetensors(pmb_lm* lm, void* stream, const char* path) {
+  if (!lm || !path) return fail(PMB_ERR_ARG, "lm_load: NULL argument");
+  std::vector<int64_t> offs, shapes; std::vector<int32_t> ranks;
+  lm_tensor_table(lm, &offs, &shapes, &ranks);
+  std::vector<float> host((size_t)lm->n_params, 0.0f);
+  std::vector<float*> ptrs;
+  for (int64_t o : offs) ptrs.push_back(host.data() + o);
+  PMB_TRY(safetensors_load_f32(path, (int)offs.size(), shapes.data(), ranks.data(), ptrs.data()));   // nothing is touched on error
+  PMB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  PMB_CUDA(cudaMemcpy(lm->params, host.data(), host.size() * 4, cudaMemcpyHostToDevice));
   return PMB_OK;
 }
 

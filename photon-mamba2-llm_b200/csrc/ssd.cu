@@ -305,8 +305,10 @@ struct OpDB {
 // Small kernels
 // ---------------------------------------------------------------------------------------------
 
-// S[b,h,c*Q+q] = inclusive cumsum over q of a.  One warp per (b,c,h).
-__global__ void chunk_cumsum_kernel(SsdP p) {
+// S[b,h,c*Q+q] = inclusive cumsum over q of a.  One warp per (b,c,h).  With raw.dt_raw the warp first forms
+// dt = softplus(dt_raw + bias) (written out for the later kernels) and A = -exp(a_log).
+struct CumsumRaw { const float* dt_raw; int64_t ld_raw; const float* dt_bias; const float* a_log; float* dt_out; float* A_out; };
+__global__ void chunk_cumsum_kernel(SsdP p, CumsumRaw raw) {
   int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   int total = p.B * p.nc * p.H;
   if (w >= total) return;
@@ -315,7 +317,9 @@ __global__ void chunk_cumsum_kernel(SsdP p) {
   float* out = p.S + ((int64_t)bb * p.H + h) * p.T + (int64_t)cc * p.Q;
   // the strided loads of up to 8 rounds are requested together, ahead of the dependent scan chain
   constexpr int AHEAD = 8;
-  const float Ah = p.dt ? p.A[h] : 1.0f;
+  const float Ah = raw.dt_raw ? -expf(raw.a_log[h]) : (p.dt ? p.A[h] : 1.0f);
+  const float bias = raw.dt_raw ? raw.dt_bias[h] : 0.0f;
+  if (raw.dt_raw && bc == 0 && lane == 0) raw.A_out[h] = Ah;
   const float* srcv = p.dt ? p.dt : p.a;
   float pre[AHEAD];
   for (int q0 = 0; q0 < p.Q; q0 += 32) {
@@ -324,7 +328,17 @@ __global__ void chunk_cumsum_kernel(SsdP p) {
 #pragma unroll
       for (int j = 0; j < AHEAD; ++j) {
         const int qq = q0 + 32 * j + lane;
-        pre[j] = (qq < p.Q) ? Ah * srcv[p.tok(bb, cc, qq) * p.H + h] : 0.0f;
+        pre[j] = 0.0f;
+        if (qq < p.Q) {
+          const int64_t tk = p.tok(bb, cc, qq);
+          if (raw.dt_raw) {
+            const float dtv = softplus_acc(raw.dt_raw[tk * raw.ld_raw + h] + bias);
+            raw.dt_out[tk * p.H + h] = dtv;
+            pre[j] = Ah * dtv;
+          } else {
+            pre[j] = Ah * srcv[tk * p.H + h];
+          }
+        }
       }
     }
     int q = q0 + lane;
@@ -455,14 +469,29 @@ __global__ void ssd_chunk_finish_kernel(SsdP p, const float* __restrict__ ddt_x,
   float carry = 0.0f, pA = 0.0f, pD = 0.0f;
   float Ah = p.dt ? p.A[h] : 0.0f;
   int nblk = (p.Q + 31) / 32;
+  // the strided loads of up to 8 rounds are requested together, ahead of the dependent scan chain
+  constexpr int AHEAD = 8;
+  float pre[AHEAD];
+  const float send = dsend[w];
   for (int blk = nblk - 1; blk >= 0; --blk) {
+    const int r = (nblk - 1 - blk) % AHEAD;
+    if (r == 0) {
+#pragma unroll
+      for (int j = 0; j < AHEAD; ++j) {
+        const int qq = (blk - j) * 32 + lane;
+        pre[j] = (blk - j >= 0 && qq < p.Q) ? dS[p.tok(bb, cc, qq) * p.H + h] : 0.0f;
+      }
+    }
     int q = blk * 32 + lane;
     float v = 0.0f;
     int64_t idx = 0;
+#pragma unroll
+    for (int j = 0; j < AHEAD; ++j) if (j == r) v = pre[j];
     if (q < p.Q) {
       idx = p.tok(bb, cc, q) * p.H + h;
-      v = dS[idx];
-      if (q == p.Q - 1) v += dsend[w];
+      if (q == p.Q - 1) v += send;
+    } else {
+      v = 0.0f;
     }
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -601,7 +630,9 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
   const double tok = (double)p.B * p.T;
   {
     ProfScope prof(st, "ssd_chunk_cumsum", 0.0, 8.0 * tok * p.H);
-    chunk_cumsum_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p);
+    CumsumRaw raw{in.dt_raw, in.ld_raw, in.dt_bias, in.a_log, const_cast<float*>(in.dt), const_cast<float*>(in.A)};
+    if (in.dt_raw && (!in.dt || !in.A || !in.dt_bias || !in.a_log)) return fail(PMB_ERR_ARG, "ssd: dt_raw needs dt, A, dt_bias and a_log");
+    chunk_cumsum_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p, raw);
     PMB_LAUNCHED();
   }
   const bool tc = ssd_tc_supported(in) && (ldy % 4 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0);

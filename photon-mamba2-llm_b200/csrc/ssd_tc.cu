@@ -505,7 +505,7 @@ pmb_status ssd_tc_scan(cudaStream_t st, const SsdIn& in, float* y, int64_t ldy, 
 // the forward and the backward of a block may be separated by other layers reusing the workspace).
 pmb_status ssd_tc_dstate(cudaStream_t st, const SsdIn& in, const float* dy, int64_t lddy, const SsdWs& ws) {
   TcP p = make_p(in, ws);
-  PMB_TRY(prescale(st, "ssd_prescale_dy", dy, lddy, in, ws, ws.dys, 1));
+  if (!in.dys_ready) PMB_TRY(prescale(st, "ssd_prescale_dy", dy, lddy, in, ws, ws.dys, 1));
   MapSet ms{};
   int64_t tok = (int64_t)p.B * p.T;
   PMB_TRY(get_map(&ms.m[0], in.c, p.N, tok, p.G, in.ldbc, p.N, 32, 32, true));

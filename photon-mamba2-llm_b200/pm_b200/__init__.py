@@ -80,6 +80,10 @@ def _load():
         "pmb_gated_rmsnorm_bwd_static": (i32, [vp, i64, i32, vp, vp, vp, i64, vp, vp, vp, vp, i64, vp]),
         "pmb_mamba2_block_workspace_bytes": (sz, [cfgp, i32, i32]),
         "pmb_stack_workspace_bytes": (sz, [cfgp, i32, i32]),
+        "pmb_lm_save_safetensors": (i32, [vp, vp, C.c_char_p]),
+        "pmb_lm_load_safetensors": (i32, [vp, vp, C.c_char_p]),
+        "pmb_safetensors_save_f32": (i32, [C.c_char_p, i32, C.POINTER(i64), C.POINTER(i32), C.POINTER(vp)]),
+        "pmb_safetensors_load_f32": (i32, [C.c_char_p, i32, C.POINTER(i64), C.POINTER(i32), C.POINTER(vp)]),
         "pmb_mamba2_block_fwd": (i32, [vp, cfgp, C.POINTER(_Params), i32, i32, vp, vp, vp, vp, sz]),
         "pmb_mamba2_block_bwd": (i32, [vp, cfgp, C.POINTER(_Params), i32, i32, vp, vp, vp, vp, C.POINTER(_Params), vp, sz]),
         "pmb_mamba2_step_workspace_bytes": (sz, [cfgp, i32]),
@@ -565,6 +569,14 @@ class FlatMamba:
         _check(lib.pmb_lm_step_host(self._h, _stream(), ids_host.data_ptr(), targets_host.data_ptr(), C.byref(loss), cb, None))
         return loss.value
 
+    def save_checkpoint(self, path: str):
+        """Write the parameters as the reference's positional safetensors checkpoint (pm-train/src/checkpoint.rs:25-52)."""
+        _check(lib.pmb_lm_save_safetensors(self._h, _stream(), str(path).encode()))
+
+    def load_checkpoint(self, path: str):
+        """Read such a checkpoint; count, dtype and shapes must match (pm-train/src/checkpoint.rs:56-97)."""
+        _check(lib.pmb_lm_load_safetensors(self._h, _stream(), str(path).encode()))
+
     def close(self):
         if self._h:
             lib.pmb_lm_destroy(self._h)
@@ -575,6 +587,32 @@ class FlatMamba:
             self.close()
         except Exception:
             pass
+
+
+def _tensor_table(arrays):
+    n = len(arrays)
+    shapes = [int(s) for a in arrays for s in a.shape]
+    sh = (C.c_int64 * max(1, len(shapes)))(*shapes)
+    rk = (C.c_int32 * max(1, n))(*[a.ndim for a in arrays])
+    ptrs = (C.c_void_p * max(1, n))(*[a.ctypes.data for a in arrays])
+    return n, sh, rk, ptrs
+
+
+def save_checkpoint_f32(path: str, arrays):
+    """Host-side format code alone: `arrays` (C-contiguous float32 numpy arrays) become p_0000, p_0001, ..."""
+    import numpy as np
+    arrays = [np.ascontiguousarray(a, dtype=np.float32) for a in arrays]
+    n, sh, rk, ptrs = _tensor_table(arrays)
+    _check(lib.pmb_safetensors_save_f32(str(path).encode(), n, sh, rk, ptrs))
+
+
+def load_checkpoint_f32(path: str, shapes):
+    """Reads p_0000.. into new float32 arrays of the given shapes; raises PmbError on any count / dtype / shape mismatch."""
+    import numpy as np
+    arrays = [np.zeros(s, dtype=np.float32) for s in shapes]
+    n, sh, rk, ptrs = _tensor_table(arrays)
+    _check(lib.pmb_safetensors_load_f32(str(path).encode(), n, sh, rk, ptrs))
+    return arrays
 
 
 class AdamW:

@@ -163,6 +163,40 @@ def test_lm_step_loss_and_gradients(pm):
     lm.close()
 
 
+def test_lm_checkpoint_round_trip_in_reference_format(pm, tmp_path):
+    """save -> the safetensors package reads p_0000.. with the append_params shapes; a second model loads the file
+    and computes the same loss; a model of another shape refuses it (pm-train/src/checkpoint.rs:25-97)."""
+    sf = pytest.importorskip("safetensors.numpy")
+    cfg = orc.Mamba2Config(d_model=64, d_state=8, d_head=16, n_heads=4, block_len=32)
+    L, B, T, V = 2, 2, 64, 301
+    layers = [block_params(cfg, seed=40 + i) for i in range(L)]
+    embed = randn((V, 64), 11, 0.5)
+    ids, tg, _ = orc.lcg_batch(3, B, T, V)
+    lm = pm.FlatMamba(to_pm_cfg(cfg), L, V, B, T)
+    lm.load(embed.cuda(), [cuda_params(p) for p in layers])
+    loss0 = float(lm.step_device(ids.cuda(), tg.cuda()).item())
+    path = tmp_path / "model.safetensors"
+    lm.save_checkpoint(path)
+    got = sf.load_file(str(path))
+    order = ["in_proj_weight", "conv1d_weight", "conv1d_bias", "a_log", "d_skip", "dt_bias", "norm_weight", "out_proj_weight"]
+    assert len(got) == 1 + 8 * L
+    assert np.array_equal(got["p_0000"], embed.numpy())
+    for l in range(L):
+        for j, k in enumerate(order):
+            t = got[f"p_{1 + 8 * l + j:04d}"]
+            ref = layers[l][k].numpy()
+            assert t.shape == (ref.shape if k != "conv1d_weight" else (cfg.xbc_dim, 1, cfg.d_conv))
+            assert np.array_equal(t.reshape(ref.shape), ref), k
+    lm2 = pm.FlatMamba(to_pm_cfg(cfg), L, V, B, T)
+    lm2.load_checkpoint(path)
+    assert float(lm2.step_device(ids.cuda(), tg.cuda()).item()) == loss0
+    lm3 = pm.FlatMamba(to_pm_cfg(cfg), L + 1, V, B, T)
+    with pytest.raises(pm.PmbError, match="tensors, model has"):
+        lm3.load_checkpoint(path)
+    for m in (lm, lm2, lm3):
+        m.close()
+
+
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, None), (torch.bfloat16, 2e-2)])
 def test_two_level_lm_config3_wiring(pm, dtype, tol):
     # BASELINE config 3 wiring at small dims: 2 + 2 layers, pool 4, one-group causal shift
