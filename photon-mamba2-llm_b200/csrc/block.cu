@@ -21,7 +21,7 @@ __global__ void __launch_bounds__(256) dt_bwd_kernel(const float* __restrict__ x
   for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) {
     float s = sigmoid_acc(xzd[r * ld + col0 + h] + bias);
     float g = ddt[r * H + h] * s;
-    if (pair_hi) { uint32_t hh, ll; split_bf16_pair(g, hh, ll); pair_hi[r * ld + col0 + h] = (uint16_t)hh; pair_lo[r * ld + col0 + h] = (uint16_t)ll; }
+    if (pair_hi) { uint32_t hh, ll; split_bf16_pair(g, hh, ll); pair_hi[r * ld + col0 + h] = (uint16_t)hh; if (pair_lo) pair_lo[r * ld + col0 + h] = (uint16_t)ll; }
     else dxzd[r * ld + col0 + h] = g;
     acc += g;
   }
@@ -168,9 +168,10 @@ static pmb_status block_fwd_core(cudaStream_t st, const Dims& d, const pmb_block
   sin.dt_raw = w.xzd + d.I + d.X; sin.ld_raw = d.J; sin.dt_bias = p.dt_bias; sin.a_log = p.a_log;
   PMB_TRY(ssd_fwd(st, sin, nullptr, w.y, d.I, nullptr, w.ssd));
   // with pair GEMMs the normalised output is only ever a GEMM operand: write it as a pair, skip the fp32 copy
+  // (bf16 storage: the same with a plain bf16 rounding, lo == NULL)
   if (pr) PMB_TRY(gated_rmsnorm_fwd(st, d.M, d.I, d.eps, w.y, w.xzd, d.J, p.norm_weight, nullptr, w.rstd, w.normed_hi, w.normed_lo));
+  else if (w16) PMB_TRY(gated_rmsnorm_fwd(st, d.M, d.I, d.eps, w.y, w.xzd, d.J, p.norm_weight, nullptr, w.rstd, w.normed16, nullptr));
   else PMB_TRY(gated_rmsnorm_fwd(st, d.M, d.I, d.eps, w.y, w.xzd, d.J, p.norm_weight, w.normed, w.rstd));
-  if (w16) PMB_TRY(cast_f32_bf16(st, w.normed, w.normed16, d.M * d.I));
   return PMB_OK;
 }
 
@@ -254,12 +255,12 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   // With pair GEMMs the three producers of dxzd (this kernel: dz; the scan's dt path: ddt_raw; the conv backward:
   // dxBC) write the (hi, lo) pair directly and the fp32 dxzd is never formed.  The norm backward also emits
   // dY exp(S) for the scan backward when the tensor-core scan will run.
-  uint16_t* ph = pr ? w.dxzd_hi : nullptr;
+  uint16_t* ph = pr ? w.dxzd_hi : (w16 ? w.dxzd16 : nullptr);   // bf16 storage: plain bf16 rounding, no low part
   uint16_t* pl = pr ? w.dxzd_lo : nullptr;
   SsdIn sin = ssd_inputs(d, p, w);
   NormBwdExtra ex{};
   ex.dz_hi = ph; ex.dz_lo = pl;
-  if (pr && ssd_tc_supported(sin) && (d.P % 4 == 0)) { ex.dys = w.ssd.dys; ex.S = w.ssd.S; ex.H = d.H; ex.P = d.P; ex.T = d.T; sin.dys_ready = true; }
+  if ((pr || w16) && ssd_tc_supported(sin) && (d.P % 4 == 0)) { ex.dys = w.ssd.dys; ex.S = w.ssd.S; ex.H = d.H; ex.P = d.P; ex.T = d.T; sin.dys_ready = true; }
   PMB_TRY(gated_rmsnorm_bwd(st, d.M, d.I, w.dnormed, w.y, w.xzd, d.J, p.norm_weight, w.rstd, w.dnormed, w.dxzd, d.J,
                             g.norm_weight, w.scratch2, w.scratch2_bytes, gl, &ex));
   // scan
@@ -275,7 +276,6 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
                         w.scratch, w.scratch_bytes, gl, ph, pl));
   // in_proj: dW_in = x^T dxzd;  dx = dxzd W_in^T (+ accumulated residual gradient)
   if (w16) {
-    PMB_TRY(cast_f32_bf16(st, w.dxzd, w.dxzd16, d.M * d.J));
     PMB_TRY(gemm_bf16(st, 1, 0, d.D, d.J, d.M, x, d.D, w.dxzd16, d.J, g.in_proj_weight, d.J, nullptr, 0));
     PMB_TRY(gemm_bf16(st, 0, 1, d.M, d.D, d.J, w.dxzd16, d.J, w16->in_proj, d.J, dx, d.D, dx_accum, 1));
   } else if (pr) {

@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restr
       const int64_t off = ((int64_t)b * T + tp) * ldx + col0 + c;
       if (pair_hi) {       // the gradient is only a GEMM operand: write it as a (hi, lo) bf16 pair with the same pitch
         if (VEC == 4) store_pair4(pair_hi + off, pair_lo + off, g[0], g[1 % VEC], g[2 % VEC], g[3 % VEC]);
-        else { uint32_t h, l; split_bf16_pair(g[0], h, l); pair_hi[off] = (uint16_t)h; pair_lo[off] = (uint16_t)l; }
+        else { uint32_t h, l; split_bf16_pair(g[0], h, l); pair_hi[off] = (uint16_t)h; if (pair_lo) pair_lo[off] = (uint16_t)l; }
       } else if (VEC == 4) *reinterpret_cast<float4*>(ddst + (int64_t)tp * ldx) = make_float4(g[0], g[1 % VEC], g[2 % VEC], g[3 % VEC]);
       else ddst[(int64_t)tp * ldx] = g[0];
     }
@@ -332,7 +332,7 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_fwd_kernel(const f
         float rem = v - __uint_as_float(h << 16);
         uint32_t ul = __float_as_uint(rem);
         out_hi[row * width + i] = (uint16_t)h;
-        out_lo[row * width + i] = (uint16_t)((ul + 0x7fffu + ((ul >> 16) & 1u)) >> 16);
+        if (out_lo) out_lo[row * width + i] = (uint16_t)((ul + 0x7fffu + ((ul >> 16) & 1u)) >> 16);
       }
     }
   }
@@ -383,7 +383,7 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_fwd_vec_kernel(con
         uint32_t h[4], l[4];
         split(v.x, h[0], l[0]); split(v.y, h[1], l[1]); split(v.z, h[2], l[2]); split(v.w, h[3], l[3]);
         reinterpret_cast<uint2*>(out_hi + row * width)[i] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
-        reinterpret_cast<uint2*>(out_lo + row * width)[i] = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+        if (out_lo) reinterpret_cast<uint2*>(out_lo + row * width)[i] = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
       }
     }
   }
