@@ -1,4 +1,6 @@
 // C ABI entry points for the individual kernels, library-wide state, and the GEMM engine dispatch.
+#include <cstdio>
+#include <cstdlib>
 #include "common.cuh"
 #include <cstdlib>
 #include "kernels.h"
@@ -44,16 +46,21 @@ pmb_status gemm(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K
   return gemm_simt(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
 }
 
-static SideLane g_lanes[64][6];
+static SideLane g_lanes[64][7];
 
 pmb_status get_side_lane(int idx, SideLane** out) {
   *out = nullptr;
   int dev = 0;
   PMB_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || idx < 0 || idx >= 6) return PMB_OK;
+  if (dev < 0 || dev >= 64 || idx < 0 || idx >= 7) return PMB_OK;
   SideLane& l = g_lanes[dev][idx];
   if (!l.s) {
-    PMB_CUDA(cudaStreamCreateWithFlags(&l.s, cudaStreamNonBlocking));
+    // lanes that carry the critical chain of the stack backward (6: gradient kernels of the current block, 0: the
+    // scan backward's second chain) get the highest stream priority, so that their CTAs are placed ahead of the
+    // recompute-ahead and the deferred GEMMs whenever an SM frees up
+    int least = 0, greatest = 0;
+    PMB_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+    PMB_CUDA(cudaStreamCreateWithPriority(&l.s, cudaStreamNonBlocking, (idx == 0 || idx == 6) ? greatest : least));
     for (int i = 0; i < 6; ++i) PMB_CUDA(cudaEventCreateWithFlags(&l.ev[i], cudaEventDisableTiming));
   }
   *out = &l;
@@ -86,6 +93,19 @@ extern "C" pmb_status pmb_profile_stop(char* h_json, size_t capacity) {
   PMB_CUDA(cudaDeviceSynchronize());
   struct Agg { const char* name; long n; double ms, flops, bytes; };
   std::vector<Agg> agg;
+  // PMB_PROFILE_TIMELINE=<file>: also write "name,start_ms,end_ms" per scope, relative to the first scope's start,
+  // so that overlap between the internal streams can be read off
+  if (const char* tl = getenv("PMB_PROFILE_TIMELINE")) {
+    if (FILE* f = g_prof.empty() ? nullptr : fopen(tl, "w")) {
+      for (auto& r : g_prof) {
+        float t0 = 0.0f, t1 = 0.0f;
+        cudaEventElapsedTime(&t0, g_prof[0].e0, r.e0);
+        cudaEventElapsedTime(&t1, g_prof[0].e0, r.e1);
+        fprintf(f, "%s,%.4f,%.4f\n", r.name, t0, t1);
+      }
+      fclose(f);
+    }
+  }
   for (auto& r : g_prof) {
     float ms = 0.0f;
     cudaEventElapsedTime(&ms, r.e0, r.e1);

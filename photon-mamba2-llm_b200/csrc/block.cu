@@ -223,14 +223,10 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   }
   Pair16 wout{}, dop{w.dout_hi, w.dout_lo, d.D};
   if (pr) {
-    cudaStream_t sg = gl ? gl->s : st;
-    if (gl) PMB_TRY(order_after(st, gl->ev[0], sg));            // dout is ready
-    PMB_TRY(split_pair16(sg, static_cast<const float*>(dout), d.M, d.D, d.D, w.dout_hi, w.dout_lo, d.D));
-    PMB_TRY(weight_pair(sg, wx, false, p.out_proj_weight, d.I, d.D, w.wout_hi, w.wout_lo, &wout));
-    if (gl) {
-      PMB_TRY(gemm_pairs(sg, 0, 1, d.M, d.I, d.D, dop, wout, w.dnormed, d.I, nullptr));
-      PMB_CUDA(cudaEventRecord(gl->ev[1], sg));                 // dnormed is ready
-    }
+    PMB_TRY(split_pair16(st, static_cast<const float*>(dout), d.M, d.D, d.D, w.dout_hi, w.dout_lo, d.D));
+    PMB_TRY(weight_pair(st, wx, false, p.out_proj_weight, d.I, d.D, w.wout_hi, w.wout_lo, &wout));
+    // dnormed heads the critical chain of this block: it stays on the caller's stream; only dW_out is deferred
+    if (gl) PMB_TRY(gemm_pairs(st, 0, 1, d.M, d.I, d.D, dop, wout, w.dnormed, d.I, nullptr));
   }
   // the recomputed activations (enqueued by the caller, possibly on another stream) are needed from here on
   if (recompute_done) PMB_CUDA(cudaStreamWaitEvent(st, recompute_done, 0));
@@ -241,7 +237,6 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   } else if (pr && gl) {
     PMB_TRY(order_after(st, gl->ev[2], gl->s));                 // the recomputed normed pair is ready
     PMB_TRY(gemm_pairs(gl->s, 1, 0, d.I, d.D, d.M, Pair16{w.normed_hi, w.normed_lo, d.I}, dop, g.out_proj_weight, d.D, nullptr));
-    PMB_CUDA(cudaStreamWaitEvent(st, gl->ev[1], 0));
   } else if (pr) {
     const PairGemm both[2] = {{1, 0, d.I, d.D, d.M, Pair16{w.normed_hi, w.normed_lo, d.I}, dop, g.out_proj_weight, d.D, nullptr},
                               {0, 1, d.M, d.I, d.D, dop, wout, w.dnormed, d.I, nullptr}};
@@ -373,6 +368,16 @@ pmb_status stack_bwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_blo
   }
   // events: ev[0], ev[1] = recompute into slot 0 / 1 finished;  ev[2], ev[3] = gradient kernels reading slot 0 / 1 finished
   cudaStream_t sr = rl->s;
+  // The gradient kernels run on a high-priority internal stream (the caller's stream has the lowest priority a
+  // stream can have, the same as the recompute's): when an SM frees up, the chain every later block waits for
+  // goes first.  `user_st` only waits for that stream before each callback and at the end.
+  cudaStream_t user_st = st;
+  SideLane* cl = nullptr;
+  {
+    static const int prio_on = [] { const char* e = getenv("PMB_PRIORITY_LANE"); return (e && e[0] == '0') ? 0 : 1; }();
+    if (prio_on) PMB_TRY(get_side_lane(6, &cl));
+  }
+  if (cl) { PMB_TRY(order_after(user_st, cl->ev[0], cl->s)); st = cl->s; }
   PMB_CUDA(cudaEventRecord(rl->ev[2], st));            // everything before this call (saved inputs, weights) is ready,
   PMB_CUDA(cudaEventRecord(rl->ev[3], st));            // and both slots are free
   auto recompute = [&](int l) -> pmb_status {
@@ -389,8 +394,12 @@ pmb_status stack_bwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_blo
     PMB_TRY(block_grads(st, d, layers[l], base + (size_t)l * slot, dhidden, dhidden, dhidden, grads[l], ws, ws_bytes,
                         w16 ? &w16[l] : nullptr, 2, sl, rl->ev[sl]));
     PMB_CUDA(cudaEventRecord(rl->ev[2 + sl], st));
-    if (on_layer_done) on_layer_done(l, user);
+    if (on_layer_done) {
+      if (cl) PMB_TRY(order_after(st, cl->ev[1], user_st));   // the callback orders its work after the caller's stream
+      on_layer_done(l, user);
+    }
   }
+  if (cl) PMB_TRY(order_after(st, cl->ev[1], user_st));
   return PMB_OK;
 }
 

@@ -7,7 +7,8 @@ namespace pmb {
 // ---- abi.cu: side streams for kernels that do not depend on each other.  One stream and six events per (device,
 // lane index), created on first use (so the first call should come before any stream capture).  lane 0: scan
 // backward chains; 1: gradient GEMMs of a block that are off the critical path; 2: scan forward; 3: recompute-ahead;
-// 4: embedding-table gradient of the LM head; 5: in_proj weight gradient.  *out stays NULL past device 63.
+// 4: embedding-table gradient of the LM head; 5: unused; 6: the gradient kernels of the stack backward (high priority,
+// like lane 0).  *out stays NULL past device 63.
 struct SideLane { cudaStream_t s = nullptr; cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}; };
 pmb_status get_side_lane(int idx, SideLane** out);
 // `to` waits for everything enqueued on `from` so far
