@@ -498,7 +498,7 @@ pmb_status ssd_tc_scan(cudaStream_t st, const SsdIn& in, float* y, int64_t ldy, 
   PMB_TRY(get_map(&ms.m[2], in.c, p.N, tok, p.G, in.ldbc, p.N, 32, 128, false));
   PMB_TRY(get_map(&ms.m[3], ws.hprev, p.P, (int64_t)p.B * p.nc * p.H * p.N, 1, p.P, (int64_t)p.N * p.P, 32, 32, true));
   ProfScope prof(st, "ssd_chunk_scan_tc", 2.0 * tok * p.H * p.P * (p.Q + p.N), 0.0);
-  return tcb::launch(st, ms, mk<TcScan<0>>(p, p.Q, p.P), p.B * p.nc * p.H, status_ptr());
+  return tcb::launch(st, ms, mk<TcScan<0>>(p, p.Q, p.P), p.B * p.nc * p.H, status_ptr(), +1);
 }
 
 // Backward contractions.  Expects ws.xs from the forward of the same scan (it is recomputed here because

@@ -77,7 +77,7 @@ __device__ __forceinline__ void decode_mnmajor(int i, int& mn, int& k) {
 
 template <class Op>
 __global__ void __launch_bounds__(NTHREADS, RingDepth<Op::BN>::CTAS_PER_SM)
-tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __restrict__ status) {
+tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __restrict__ status, int grid_mode) {
   constexpr int BN = Op::BN;
   using G = Geometry<BN>;
   constexpr int STAGES = G::STAGES;
@@ -97,8 +97,12 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
   op.aux = reinterpret_cast<float*>(tiles_ptr + G::RING_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  if (!op.init(blockIdx.z, m0, n0)) return;   // uniform per CTA
+  // grid_mode 0: (n tile, m tile, batch).  1 / 2: (n tile, batch, m tile) with the m tiles in ascending / descending
+  // order, so that the tiles with the most k-steps of every batch entry are scheduled first (causal operands).
+  const int mt = grid_mode == 0 ? (int)blockIdx.y : (grid_mode == 1 ? (int)blockIdx.z : (int)(gridDim.z - 1 - blockIdx.z));
+  const int batch_id = grid_mode == 0 ? (int)blockIdx.z : (int)blockIdx.y;
+  const int m0 = mt * BM, n0 = blockIdx.x * BN;
+  if (!op.init(batch_id, m0, n0)) return;   // uniform per CTA
   const int nseg = op.nseg();
   op.stage(threadIdx.x, NTHREADS);
 
@@ -350,15 +354,18 @@ tc_bgemm_kernel(const __grid_constant__ MapSet maps, Op op, unsigned int* __rest
 }
 
 template <class Op>
-static pmb_status launch(cudaStream_t st, const MapSet& maps, const Op& op, int batches, unsigned int* status) {
+// heavy_m: +1 = the last m tile of a batch entry has the most k-steps, -1 = the first one, 0 = all alike
+static pmb_status launch(cudaStream_t st, const MapSet& maps, const Op& op, int batches, unsigned int* status, int heavy_m = 0) {
   using G = Geometry<Op::BN>;
   static bool attr_set = false;
   if (!attr_set) {
     PMB_CUDA(cudaFuncSetAttribute(tc_bgemm_kernel<Op>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BASE + Op::AUX_FLOATS * 4));
     attr_set = true;
   }
-  dim3 grid((unsigned)cdiv(op.Ndim, Op::BN), (unsigned)cdiv(op.Mdim, BM), (unsigned)batches);
-  tc_bgemm_kernel<Op><<<grid, NTHREADS, G::SMEM_BASE + Op::AUX_FLOATS * 4, st>>>(maps, op, status);
+  const unsigned mtiles = (unsigned)cdiv(op.Mdim, BM);
+  const int mode = (heavy_m == 0 || batches > 65535 || mtiles < 2) ? 0 : (heavy_m > 0 ? 2 : 1);
+  dim3 grid((unsigned)cdiv(op.Ndim, Op::BN), mode ? (unsigned)batches : mtiles, mode ? mtiles : (unsigned)batches);
+  tc_bgemm_kernel<Op><<<grid, NTHREADS, G::SMEM_BASE + Op::AUX_FLOATS * 4, st>>>(maps, op, status, mode);
   PMB_LAUNCHED();
   return PMB_OK;
 }
