@@ -64,19 +64,28 @@ __device__ __forceinline__ uint16_t float_to_bf16_bits(float f) {   // round to 
   return (uint16_t)(u >> 16);
 }
 
-// One launch carries up to two independent products: CTAs [0, pr[0].tiles) work on the first, the rest on the second.
+// One launch carries up to MAX_GROUP independent products: CTAs [0, pr[0].tiles) work on the first, the next
+// pr[1].tiles on the second, and so on (unused entries have tiles == 0).
 // Two products whose tile counts each fill the 148 SMs badly (weight-gradient and data-gradient of one projection)
 // then share the machine instead of running as two ragged waves.
 struct Problem { CUtensorMap mA, mB, mAlo, mBlo; Params p; int tiles_n; int tiles; };
-struct Group { Problem pr[2]; };
+constexpr int MAX_GROUP = 4;
+struct Group { Problem pr[MAX_GROUP]; };
+__device__ __forceinline__ int pick_problem(const Group& g, int id, int* local) {
+  int which = 0, base = 0;
+#pragma unroll
+  for (int i = 0; i + 1 < MAX_GROUP; ++i) if (id >= base + g.pr[i].tiles && which == i) { base += g.pr[i].tiles; which = i + 1; }
+  *local = id - base;
+  return which;
+}
 
 template <bool SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ Group g) {
-  const int which = ((int)blockIdx.x >= g.pr[0].tiles) ? 1 : 0;
+  int tile;
+  const int which = pick_problem(g, (int)blockIdx.x, &tile);
   const Problem& q = g.pr[which];
   const Params& p = q.p;
-  const int tile = (int)blockIdx.x - (which ? g.pr[0].tiles : 0);
   constexpr int STAGES = Cfg<SPLIT>::STAGES;
   constexpr int STAGE_BYTES = Cfg<SPLIT>::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -311,10 +320,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ Group g) {
   const uint32_t rank = cluster_rank();
   const int cluster_id = (int)(blockIdx.x >> 1);
-  const int which = (cluster_id >= g.pr[0].tiles) ? 1 : 0;
+  int tile;
+  const int which = pick_problem(g, cluster_id, &tile);
   const Problem& q = g.pr[which];
   const Params& p = q.p;
-  const int tile = cluster_id - (which ? g.pr[0].tiles : 0);
   constexpr int BNH = BN2 / 2;                       // B columns (rows of the K-major tile) per CTA
   constexpr int TILE_B = BNH * TBK * 2;
   constexpr int HALF_BYTES = TILE_BYTES + TILE_B;    // one A tile + one B tile
@@ -562,7 +571,7 @@ pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
   p.a_mn_major = ta ? 1 : 0; p.b_mn_major = tb ? 0 : 1;
   p.C = C; p.ldc = ldc; p.R = R; p.out_bf16 = out_bf16;
   q.tiles_n = (int)cdiv(N, TBN); q.tiles = (int)(cdiv(M, TBM) * cdiv(N, TBN));
-  g.pr[1].tiles_n = 1; g.pr[1].tiles = 0;
+  for (int i = 1; i < MAX_GROUP; ++i) { g.pr[i].tiles_n = 1; g.pr[i].tiles = 0; }
   {
     static const int env = [] { const char* e = getenv("PMB_GEMM_PAIR"); return e ? atoi(e) : -1; }();
     const int64_t clusters = cdiv(M, 256) * cdiv(N, 256);
@@ -653,14 +662,14 @@ static int pick_pair_mode(const PairGemm* gs, int n) {
 // scheduled first, so put the product with the longer K there.
 pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n) {
   using namespace hb;
-  if (n < 1 || n > 2) return fail(PMB_ERR_ARG, "gemm_pairs_group: 1 or 2 products per launch");
+  if (n < 1 || n > MAX_GROUP) return fail(PMB_ERR_ARG, "gemm_pairs_group: 1 to %d products per launch", MAX_GROUP);
   static bool attr_set = false;
   if (!attr_set) {
     PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::SMEM_BYTES));
     attr_set = true;
   }
   Group g{};
-  g.pr[1].tiles_n = 1; g.pr[1].tiles = 0;
+  for (int i = 1; i < MAX_GROUP; ++i) { g.pr[i].tiles_n = 1; g.pr[i].tiles = 0; }
   double flops = 0.0, bytes = 0.0;
   int64_t total = 0;
   for (int i = 0; i < n; ++i) {

@@ -108,7 +108,7 @@ pmb_status split_pair16(cudaStream_t st, const float* src, int64_t rows, int64_t
 pmb_status gemm_pairs(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const Pair16& A, const Pair16& B,
                       float* C, int64_t ldc, const float* R);
 struct PairGemm { int ta, tb; int64_t M, N, K; Pair16 A, B; float* C; int64_t ldc; const float* R; };
-// up to two independent products in one launch (tiles of g[0] first: give it the longer K)
+// up to four independent products in one launch (tiles of g[0] first: give it the longer K)
 pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* g, int n);
 bool gemm_pairs_enabled();
 void set_pair_override(int v);   // -1 = heuristic, 0 = 128x128 single-CTA tiles, 1 = 256x256 CTA-pair tiles   // false when PMB_GEMM_ENGINE is tf32 or simt

@@ -15,6 +15,7 @@
 namespace pmb {
 
 constexpr int LM_TILE_ROWS = 2048;
+constexpr int HEAD_SPLITK = 3;
 
 __global__ void embedding_fwd_kernel(const float* __restrict__ table, const int64_t* __restrict__ ids, float* __restrict__ out,
                                      int64_t rows, int D, int V, unsigned int* __restrict__ bad) {
@@ -216,6 +217,18 @@ __global__ void hier_kernel(const T* __restrict__ in, const T* __restrict__ a, T
   st_act(out + i, v);
 }
 
+// out = sum of n slabs of `elems` floats (split-K partial products), float4 lanes
+__global__ void sum_slabs_kernel(const float* __restrict__ part, int n, int64_t elems, float* __restrict__ out) {
+  int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= elems) return;
+  float4 a = *reinterpret_cast<const float4*>(part + i);
+  for (int s = 1; s < n; ++s) {
+    const float4 b = *reinterpret_cast<const float4*>(part + (int64_t)s * elems + i);
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+  }
+  *reinterpret_cast<float4*>(out + i) = a;
+}
+
 __global__ void __launch_bounds__(256) mean_kernel(const float* __restrict__ v, int64_t n, float* __restrict__ out) {
   __shared__ float red[32];
   float s = 0.0f;
@@ -254,6 +267,7 @@ struct pmb_lm {
   int pairs = 0;
   int ce_inplace = 0;         // the logits row fits in shared memory: the gradient pair overwrites the logits tile
   uint16_t *params_hi = nullptr, *params_lo = nullptr, *dlog_hi = nullptr, *dlog_lo = nullptr, *hid_hi = nullptr, *hid_lo = nullptr;
+  float* dh_part = nullptr;   // HEAD_SPLITK partial products of dhidden = dlogits E (few tiles, very long K)
   std::vector<Weights16> lw16;
   // hierarchical variant (L1 > 0): level 0 = layers [0,L0) at token rate, level 1 = layers [L0,L0+L1) at 1/group rate
   int L0 = 0, L1 = 0, group = 1;
@@ -337,7 +351,8 @@ static pmb_status lm_create_impl(const pmb_mamba2_config* cfg, int L0, int L1, i
     else
       ok = ok && alloc((void**)&lm->dlog_hi, tv) && alloc((void**)&lm->dlog_lo, tv);
     ok = ok && alloc((void**)&lm->hid_hi, td) && alloc((void**)&lm->hid_lo, td);
-    pair_bytes = (lm->ce_inplace ? 0 : 2 * tv) + 2 * td;
+    ok = ok && alloc((void**)&lm->dh_part, (size_t)HEAD_SPLITK * lm->tile_rows * d.D * 4);
+    pair_bytes = (lm->ce_inplace ? 0 : 2 * tv) + 2 * td + (size_t)HEAD_SPLITK * lm->tile_rows * d.D * 4;
   }
   if (lm->bf16) {
     ok = ok && alloc((void**)&lm->params16, (size_t)o * 2);
@@ -394,7 +409,7 @@ extern "C" void pmb_lm_destroy(pmb_lm* lm) {
   if (!lm) return;
   cudaFree(lm->params); cudaFree(lm->grads); cudaFree(lm->saved); cudaFree(lm->dhidden); cudaFree(lm->logits);
   cudaFree(lm->row_loss); cudaFree(lm->loss); cudaFree(lm->bad); cudaFree(lm->ids); cudaFree(lm->targets); cudaFree(lm->ws); cudaFree(lm->params16); cudaFree(lm->dlogits16);
-  cudaFree(lm->params_hi); cudaFree(lm->params_lo); cudaFree(lm->dlog_hi); cudaFree(lm->dlog_lo); cudaFree(lm->hid_hi); cudaFree(lm->hid_lo);
+  cudaFree(lm->params_hi); cudaFree(lm->params_lo); cudaFree(lm->dlog_hi); cudaFree(lm->dlog_lo); cudaFree(lm->hid_hi); cudaFree(lm->hid_lo); cudaFree(lm->dh_part);
   cudaFree(lm->saved1); cudaFree(lm->pooled); cudaFree(lm->dpool); cudaFree(lm->dh1); cudaFree(lm->hsum);
   delete lm;
 }
@@ -516,7 +531,22 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
     } else if (prs && table_lane) {
       // single row tile: only dhidden is needed now; the embedding-table gradient runs on its own stream next to
       // the first blocks of the stack backward and is joined before the embedding scatter
-      PMB_TRY(gemm_pairs(st, 0, 0, rows, D, V, dlog_p, table_p, lm->dhidden + r0 * D, D, nullptr));
+      // dhidden has 16 x 6 tiles and K = vocab: split K three ways (one launch, three products into three slabs)
+      // so that the product the whole backward waits for uses the machine, then add the slabs
+      {
+        PairGemm parts[HEAD_SPLITK];
+        const int64_t kstep = (int64_t)align_up((size_t)cdiv(V, HEAD_SPLITK), 64);
+        int np = 0;
+        for (int64_t k0 = 0; k0 < V && np < HEAD_SPLITK; k0 += kstep, ++np) {
+          const int64_t kk = V - k0 < kstep ? V - k0 : kstep;
+          parts[np] = PairGemm{0, 0, rows, D, kk, Pair16{dlog_p.hi + k0, dlog_p.lo + k0, dlog_p.ld},
+                               Pair16{table_p.hi + k0 * D, table_p.lo + k0 * D, table_p.ld}, lm->dh_part + (size_t)np * rows * D, D, nullptr};
+        }
+        PMB_TRY(gemm_pairs_group(st, parts, np));
+        ProfScope prof(st, "head_splitk_sum", 0.0, 4.0 * (np + 1) * rows * D);
+        sum_slabs_kernel<<<(unsigned)cdiv(rows * D / 4, 256), 256, 0, st>>>(lm->dh_part, np, rows * D, lm->dhidden + r0 * D);
+        PMB_LAUNCHED();
+      }
       PMB_TRY(order_after(st, table_lane->ev[0], table_lane->s));
       PMB_TRY(gemm_pairs(table_lane->s, 1, 0, V, D, rows, dlog_p, hid_p, dtable, D, nullptr));
     } else if (prs) {
