@@ -562,6 +562,17 @@ class FlatMamba:
         _check(lib.pmb_lm_step_device(self._h, _stream(), ids.data_ptr(), targets.data_ptr(), cb, None))
         return self.loss_dev
 
+    def capture_step(self, on_layer_done=None, after=None):
+        """One training step (forward + checkpointed backward) captured into a CUDA graph.
+
+        Returns a callable `step(ids, targets) -> loss` (0-d device tensor): it copies the int64 token tensors
+        (device, or pinned host for an asynchronous copy) into the graph's static input buffers and replays the
+        graph, so the ~1200 launches of a step cost one launch.  `on_layer_done` / `after` (e.g. the enqueue and
+        the final wait of the per-layer gradient all-reduce) are called while capturing and become part of the
+        graph.  Two warm-up steps run first on a side stream: the library creates its internal streams, events and
+        scratch on first use, which a capture must not contain."""
+        return _GraphStep(self, on_layer_done, after)
+
     def step_host(self, ids_host, targets_host, on_layer_done=None):
         """ids/targets: int64 CPU tensors (pinned for an asynchronous copy).  Returns the loss as a float."""
         loss = C.c_float(0)
@@ -587,6 +598,36 @@ class FlatMamba:
             self.close()
         except Exception:
             pass
+
+
+class _GraphStep:
+    def __init__(self, lm: "FlatMamba", on_layer_done, after):
+        dev = lm.loss_dev.device
+        self.ids = torch.zeros(lm.batch, lm.seqlen, dtype=torch.int64, device=dev)
+        self.targets = torch.zeros_like(self.ids)
+        cur = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                lm.step_device(self.ids, self.targets, on_layer_done)
+                if after:
+                    after()
+        cur.wait_stream(side)
+        torch.cuda.synchronize()
+        n0 = launch_count()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.loss = lm.step_device(self.ids, self.targets, on_layer_done)
+            if after:
+                after()
+        self.launches_per_step = launch_count() - n0     # kernels of this library inside one replay
+
+    def __call__(self, ids, targets):
+        self.ids.copy_(ids.view_as(self.ids), non_blocking=True)
+        self.targets.copy_(targets.view_as(self.targets), non_blocking=True)
+        self.graph.replay()
+        return self.loss
 
 
 def _tensor_table(arrays):

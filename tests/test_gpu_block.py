@@ -163,6 +163,31 @@ def test_lm_step_loss_and_gradients(pm):
     lm.close()
 
 
+def test_lm_step_captured_in_a_cuda_graph_equals_eager(pm):
+    cfg = orc.Mamba2Config(d_model=64, d_state=8, d_head=16, n_heads=4, block_len=32)
+    L, B, T, V = 3, 2, 64, 301
+    layers = [block_params(cfg, seed=50 + i) for i in range(L)]
+    lm = pm.FlatMamba(to_pm_cfg(cfg), L, V, B, T)
+    lm.load(randn((V, 64), 12, 0.5).cuda(), [cuda_params(p) for p in layers])
+    seen = []
+    step = lm.capture_step(on_layer_done=lambda l, u: seen.append(l))
+    assert seen[-(L + 1):] == [2, 1, 0, -1] and step.launches_per_step > 0
+    for seed in (5, 6):
+        ids, tg, _ = orc.lcg_batch(seed, B, T, V)
+        loss_e = float(lm.step_device(ids.cuda(), tg.cuda()).item())
+        ge, gl = lm.grads()
+        ge, gl = ge.clone(), [{k: v.clone() for k, v in g.items()} for g in gl]
+        loss_g = float(step(ids.pin_memory(), tg.pin_memory()).item())      # host tensors: copied into the static buffers
+        assert loss_g == loss_e
+        ge2, gl2 = lm.grads()
+        assert_close(ge2, ge, tol=1e-6, what="d_embed")     # the embedding scatter adds with atomics: order, not value, may differ
+        for a, b in zip(gl, gl2):
+            for k in a:
+                assert torch.equal(a[k], b[k]), k
+    assert pm.device_status() == 0
+    lm.close()
+
+
 def test_lm_checkpoint_round_trip_in_reference_format(pm, tmp_path):
     """save -> the safetensors package reads p_0000.. with the append_params shapes; a second model loads the file
     and computes the same loss; a model of another shape refuses it (pm-train/src/checkpoint.rs:25-97)."""
