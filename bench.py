@@ -244,16 +244,23 @@ def run_ours(args):
     # The whole step (and, at N > 1, the per-layer gradient all-reduces enqueued from the library's callback) is
     # captured once into a CUDA graph; a timed step copies that step's tokens into the graph's static input
     # buffers and replays it.  --no-graph times the eager launches instead.
-    # Only at N = 1: with the NCCL all-reduces inside the capture the 2-GPU run did not finish, so N > 1 launches eagerly.
+    # The graph holds this rank's compute only.  At N > 1 the gradient average follows the replay as one NCCL
+    # all-reduce over the flat gradient buffer (a capture that contained the per-layer all-reduces did not finish
+    # in the one 2-GPU attempt; --no-graph keeps the eager path with the overlapped per-layer buckets).
     graph_step = None
-    if not args.no_graph and world == 1:
-        graph_step = lm.capture_step(on_layer_done, finish_comm)
+    if not args.no_graph:
+        graph_step = lm.capture_step(None, None)
+
+    def average_grads():
+        if world > 1:
+            dist.all_reduce(lm.flat_grads, op=dist.ReduceOp.AVG)
 
     def step_device(s):
         if graph_step is None:
             return eager_step_device(s)
         ids, tg = dev_batches[s % n_tok]
         graph_step(ids, tg)
+        average_grads()
 
     def step_host(s):
         ids, tg = host_batches[s % n_tok]
@@ -261,7 +268,9 @@ def run_ours(args):
             loss = lm.step_host(ids, tg, on_layer_done)
             finish_comm()
             return loss
-        return float(graph_step(ids, tg).item())      # pinned host -> device copies, replay, loss back to the host
+        loss = graph_step(ids, tg)                    # pinned host -> device copies, replay
+        average_grads()
+        return float(loss.item())                     # loss back to the host
 
     def barrier():
         if world > 1:
@@ -352,7 +361,8 @@ def run_ours(args):
             "config": {"workload": w, "layers": L, "d_model": D, "d_state": N, "headdim": P, "chunk": Q, "vocab": V,
                        "per_gpu_batch": B, "seq_len": T, "global_batch": B * world, "parallelism": f"dp{world}",
                        "checkpointing": "per block; stored across the stack: block inputs only",
-                       "launch": "eager" if graph_step is None else "one CUDA graph replay per step",
+                       "launch": "eager, per-layer gradient all-reduce overlapped" if graph_step is None else
+                                 ("one CUDA graph replay per step" + (", then one gradient all-reduce" if world > 1 else "")),
                        "l2": "per-step working set (506 MB parameters + gradients + activations) exceeds the 126 MB L2; no explicit flush"},
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8, "d2h_bytes_per_step": 4,
                     "ms_per_step": ms_e2e / args.steps, "wall_ms_per_step": wall_e2e * 1e3 / args.steps},
