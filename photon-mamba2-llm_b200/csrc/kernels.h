@@ -46,6 +46,7 @@ struct SsdIn {
   const float* b; const float* c; int64_t ldbc;
   const float* D;         // (H) skip weights or NULL:  y += D[h] * x
   bool dys_ready = false; // backward: ws.dys = dY exp(S) was already written by the caller
+  bool xs_ready = false;  // forward (internal): ws.xs was already written by the fused cumsum kernel
   // forward only, optional: form dt and A inside the cumsum kernel.  dt = softplus(dt_raw[token*ld_raw + h] + dt_bias[h])
   // is written to `dt` and A[h] = -exp(a_log[h]) to `A` (both must then point at writable buffers).
   const float* dt_raw = nullptr; int64_t ld_raw = 0; const float* dt_bias = nullptr; const float* a_log = nullptr;

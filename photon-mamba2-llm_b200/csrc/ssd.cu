@@ -356,6 +356,66 @@ __global__ void chunk_cumsum_kernel(SsdP p, CumsumRaw raw) {
   }
 }
 
+// Fused variant for the tensor-core path, one 256-thread block per (b,c,h): the same cumsum (with dt and A formed
+// here when raw inputs are given), then xs[t,:] = x[t,:] * dt_t * exp(S_end - S_t), the operand that the chunk-state
+// and dB contractions share.  S and dt of the chunk stay in shared memory between the two phases.
+constexpr int PREP_THREADS = 256, PREP_MAX_Q = 1024;
+__global__ void __launch_bounds__(PREP_THREADS) chunk_prepare_kernel(SsdP p, CumsumRaw raw, float* __restrict__ xs) {
+  __shared__ float sS[PREP_MAX_Q], sdt[PREP_MAX_Q], wsum[PREP_THREADS / 32];
+  const int w = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int h = w % p.H, bc = w / p.H, cc = bc % p.nc, bb = bc / p.nc;
+  const float Ah = raw.dt_raw ? -expf(raw.a_log[h]) : (p.dt ? p.A[h] : 1.0f);
+  const float bias = raw.dt_raw ? raw.dt_bias[h] : 0.0f;
+  if (raw.dt_raw && bc == 0 && tid == 0) raw.A_out[h] = Ah;
+  float* Sout = p.S + ((int64_t)bb * p.H + h) * p.T + (int64_t)cc * p.Q;
+  float carry = 0.0f;
+  for (int q0 = 0; q0 < p.Q; q0 += PREP_THREADS) {
+    const int q = q0 + tid;
+    float v = 0.0f, dtv = 1.0f;
+    if (q < p.Q) {
+      const int64_t tk = p.tok(bb, cc, q);
+      if (raw.dt_raw) { dtv = softplus_acc(raw.dt_raw[tk * raw.ld_raw + h] + bias); raw.dt_out[tk * p.H + h] = dtv; v = Ah * dtv; }
+      else if (p.dt) { dtv = p.dt[tk * p.H + h]; v = Ah * dtv; }
+      else v = p.a[tk * p.H + h];
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const float u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+    if (lane == 31) wsum[wid] = v;
+    __syncthreads();
+    float off = carry;
+    for (int j = 0; j < wid; ++j) off += wsum[j];          // fixed order: the same sums for every launch
+    v += off;
+    if (q < p.Q) { sS[q] = v; sdt[q] = dtv; Sout[q] = v; }
+    float tot = carry;
+    for (int j = 0; j < PREP_THREADS / 32; ++j) tot += wsum[j];
+    carry = tot;
+    __syncthreads();
+  }
+  const float send = sS[p.Q - 1];
+  const int P4 = p.P >> 2, total = p.Q * P4;
+  const int64_t tok0 = p.tok(bb, cc, 0);
+  constexpr int U = 4;
+  for (int i0 = tid; i0 < total; i0 += U * PREP_THREADS) {
+    float4 v[U]; float f[U]; int tt[U], jj[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * PREP_THREADS;
+      tt[u] = i / P4; jj[u] = i % P4;
+      if (i < total) {
+        v[u] = reinterpret_cast<const float4*>(p.x + (tok0 + tt[u]) * p.ldx + h * p.P)[jj[u]];
+        f[u] = __expf(send - sS[tt[u]]) * sdt[tt[u]];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * PREP_THREADS;
+      if (i < total)
+        reinterpret_cast<float4*>(xs + (tok0 + tt[u]) * (int64_t)(p.H * p.P) + h * p.P)[jj[u]] =
+            make_float4(v[u].x * f[u], v[u].y * f[u], v[u].z * f[u], v[u].w * f[u]);
+    }
+  }
+}
+
 // Exclusive scan over chunks, in place, forward or reverse.  One thread owns VEC adjacent p of one (b,h,n).
 //   forward: buf[c] holds states[c] on entry and h_prev[c] (state entering chunk c) on exit; last = final state.
 //            run_{c+1} = exp(S_end[c]) run_c + states[c],  run_0 = init (or 0)
@@ -628,21 +688,31 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
   p.yout = y; p.ldyo = ldy;
   int nbch = p.B * p.nc * p.H, nbcg = p.B * p.nc * p.G;
   const double tok = (double)p.B * p.T;
+  const bool tc = ssd_tc_supported(in) && (ldy % 4 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0);
+  SsdIn in_tc = in;
   {
-    ProfScope prof(st, "ssd_chunk_cumsum", 0.0, 8.0 * tok * p.H);
     CumsumRaw raw{in.dt_raw, in.ld_raw, in.dt_bias, in.a_log, const_cast<float*>(in.dt), const_cast<float*>(in.A)};
     if (in.dt_raw && (!in.dt || !in.A || !in.dt_bias || !in.a_log)) return fail(PMB_ERR_ARG, "ssd: dt_raw needs dt, A, dt_bias and a_log");
-    chunk_cumsum_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p, raw);
-    PMB_LAUNCHED();
+    // (one block per (b,c,h): worth it while those blocks fit the machine at once; beyond that the two separate,
+    // finer-grained kernels use the memory system better)
+    if (tc && nbch <= 4 * 148 && p.Q <= PREP_MAX_Q && (in.ldx % 4 == 0) && (reinterpret_cast<uintptr_t>(in.x) % 16 == 0)) {
+      ProfScope prof(st, "ssd_chunk_prepare", 0.0, 8.0 * tok * p.H * (1.0 + p.P));
+      chunk_prepare_kernel<<<(unsigned)nbch, PREP_THREADS, 0, st>>>(p, raw, ws.xs);
+      PMB_LAUNCHED();
+      in_tc.xs_ready = true;
+    } else {
+      ProfScope prof(st, "ssd_chunk_cumsum", 0.0, 8.0 * tok * p.H);
+      chunk_cumsum_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p, raw);
+      PMB_LAUNCHED();
+    }
   }
-  const bool tc = ssd_tc_supported(in) && (ldy % 4 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0);
   SideLane* lane = nullptr;
   if (tc) PMB_TRY(side_lane(2, &lane));
   if (tc) {
     cudaStream_t sb = lane ? lane->s : st;
     if (lane) PMB_TRY(order_after(st, lane->ev[0], sb));     // S is ready
     PMB_TRY(ssd_tc_cb(sb, in, ws));
-    PMB_TRY(ssd_tc_state(st, in, ws));
+    PMB_TRY(ssd_tc_state(st, in_tc, ws));
   } else {
     PMB_TRY(run_op(st, "ssd_cb", make_op<OpCB>(p, p.Q, p.Q), nbcg, 2.0 * tok * p.Q * p.N * p.G));
     PMB_TRY(run_op(st, "ssd_chunk_state", make_op<OpState>(p, p.N, p.P), nbch, 2.0 * tok * p.H * p.N * p.P));

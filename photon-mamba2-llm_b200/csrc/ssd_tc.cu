@@ -478,7 +478,7 @@ static pmb_status prescale(cudaStream_t st, const char* name, const float* src, 
 
 pmb_status ssd_tc_state(cudaStream_t st, const SsdIn& in, const SsdWs& ws) {
   TcP p = make_p(in, ws);
-  PMB_TRY(prescale(st, "ssd_prescale_x", in.x, in.ldx, in, ws, ws.xs, 0));
+  if (!in.xs_ready) PMB_TRY(prescale(st, "ssd_prescale_x", in.x, in.ldx, in, ws, ws.xs, 0));
   MapSet ms{};
   int64_t tok = (int64_t)p.B * p.T;
   PMB_TRY(get_map(&ms.m[0], in.b, p.N, tok, p.G, in.ldbc, p.N, 32, 32, true));
