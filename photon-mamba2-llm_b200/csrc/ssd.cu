@@ -579,6 +579,80 @@ __global__ void ssd_chunk_finish_kernel(SsdP p, const float* __restrict__ ddt_x,
   }
 }
 
+// Fused variant of the two kernels above, one 256-thread block per (b,c,h), for launches whose blocks fit the
+// machine at once: the row dot products stay in shared memory and feed the reverse cumsum directly.
+__global__ void __launch_bounds__(PREP_THREADS) chunk_rows_finish_kernel(SsdP p, float* __restrict__ dx, int64_t lddx,
+                                                                         const float* __restrict__ dsend, float* __restrict__ da_out,
+                                                                         float* __restrict__ ddt_out, float* __restrict__ part) {
+  __shared__ float s_ddtx[PREP_MAX_Q], s_dS[PREP_MAX_Q], s_dD[PREP_MAX_Q], s_dt[PREP_MAX_Q], wsum[PREP_THREADS / 32], red[32];
+  const int w = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int h = w % p.H, bc = w / p.H, cc = bc % p.nc, bb = bc / p.nc;
+  const float Dv = p.D ? p.D[h] : 0.0f;
+  const int64_t tok0 = p.tok(bb, cc, 0);
+  const int P4 = p.P >> 2;
+  // phase 1: a half-warp per row, float4 lanes (P <= 64) or strided lanes beyond
+  const int sub = lane >> 4, l16 = lane & 15;
+  for (int t0 = wid * 2; t0 < p.Q; t0 += (PREP_THREADS / 32) * 2) {
+    const int t = t0 + sub;
+    float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f, dtv = 1.0f;
+    if (t < p.Q) {
+      const int64_t tk = tok0 + t;
+      dtv = p.dtv(tk, h);
+      for (int j = l16; j < P4; j += 16) {
+        const float4 xv = reinterpret_cast<const float4*>(p.x + tk * p.ldx + h * p.P)[j];
+        const float4 dxt = reinterpret_cast<const float4*>(p.dxt + tk * (int64_t)(p.H * p.P) + h * p.P)[j];
+        const float4 dyv = reinterpret_cast<const float4*>(p.dy + tk * p.lddy + h * p.P)[j];
+        float4 yv = reinterpret_cast<const float4*>(p.y + tk * p.ldy + h * p.P)[j];
+        yv.x -= Dv * xv.x; yv.y -= Dv * xv.y; yv.z -= Dv * xv.z; yv.w -= Dv * xv.w;
+        s1 = fmaf(dxt.x, xv.x, fmaf(dxt.y, xv.y, fmaf(dxt.z, xv.z, fmaf(dxt.w, xv.w, s1))));
+        s2 = fmaf(dyv.x, yv.x, fmaf(dyv.y, yv.y, fmaf(dyv.z, yv.z, fmaf(dyv.w, yv.w, s2))));
+        s3 = fmaf(dyv.x, xv.x, fmaf(dyv.y, xv.y, fmaf(dyv.z, xv.z, fmaf(dyv.w, xv.w, s3))));
+        reinterpret_cast<float4*>(dx + tk * lddx + h * p.P)[j] =
+            make_float4(fmaf(dxt.x, dtv, Dv * dyv.x), fmaf(dxt.y, dtv, Dv * dyv.y), fmaf(dxt.z, dtv, Dv * dyv.z), fmaf(dxt.w, dtv, Dv * dyv.w));
+      }
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) {        // sums within each half-warp
+      s1 += __shfl_xor_sync(0xffffffffu, s1, o); s2 += __shfl_xor_sync(0xffffffffu, s2, o); s3 += __shfl_xor_sync(0xffffffffu, s3, o);
+    }
+    if (t < p.Q && l16 == 0) { s_ddtx[t] = s1; s_dS[t] = s2 - dtv * s1; s_dD[t] = s3; s_dt[t] = dtv; }
+  }
+  __syncthreads();
+  if (tid == 0) s_dS[p.Q - 1] += dsend[w];
+  __syncthreads();
+  // phase 2: reverse inclusive cumsum of dS over the chunk, rounds of 256 from the end
+  const float Ah = p.dt ? p.A[h] : 0.0f;
+  float carry = 0.0f, pA = 0.0f, pD = 0.0f;
+  for (int r0 = 0; r0 < p.Q; r0 += PREP_THREADS) {
+    const int q = p.Q - 1 - (r0 + tid);                 // thread 0 owns the last element of the chunk
+    float v = q >= 0 ? s_dS[q] : 0.0f;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const float u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+    if (lane == 31) wsum[wid] = v;
+    __syncthreads();
+    float off = carry;
+    for (int j = 0; j < wid; ++j) off += wsum[j];
+    v += off;
+    if (q >= 0) {
+      const int64_t idx = (tok0 + q) * p.H + h;
+      if (p.dt) { ddt_out[idx] = fmaf(Ah, v, s_ddtx[q]); pA = fmaf(v, s_dt[q], pA); pD += s_dD[q]; }
+      else da_out[idx] = v;
+    }
+    float tot = carry;
+    for (int j = 0; j < PREP_THREADS / 32; ++j) tot += wsum[j];
+    carry = tot;
+    __syncthreads();
+  }
+  if (p.dt) {
+    const float tA = block_sum(pA, red);
+    const float tD = block_sum(pD, red);
+    if (tid == 0) {
+      part[(int64_t)bc * p.H + h] = tA;
+      part[(int64_t)p.B * p.nc * p.H + (int64_t)bc * p.H + h] = tD;
+    }
+  }
+}
+
 // Sums the split-K partial tiles in a fixed order.  mode 0: dG (lower-triangular 64x64 tiles only, the
 // others were never produced); mode 1/2: dC/dB rows go to out + token * ld + g * cols.
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, int nsplit, int rows, int cols, int mode, int G, int Q,
@@ -759,10 +833,18 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   else PMB_TRY(run_op(st, "ssd_bwd_dx", make_op<OpDx>(p, p.Q, p.P), nbch, 2.0 * tok * p.H * p.P * (p.Q + p.N)));
   {
     ProfScope prof(st, "ssd_bwd_rows", 0.0, 4.0 * tok * p.H * (5.0 * p.P + 8.0));
-    ssd_rowdots_kernel<<<(unsigned)cdiv(rows * 32, 256), 256, 0, st>>>(p, g.dx, g.lddx, ddt_x, dS, dDrow);
-    PMB_LAUNCHED();
-    ssd_chunk_finish_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p, ddt_x, dS, dDrow, dsend, g.da, g.ddt, ws.part);
-    PMB_LAUNCHED();
+    const bool vec_ok = (p.P % 4 == 0) && (p.ldx % 4 == 0) && (p.ldy % 4 == 0) && (p.lddy % 4 == 0) && (g.lddx % 4 == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.y) | reinterpret_cast<uintptr_t>(p.dy) |
+                          reinterpret_cast<uintptr_t>(g.dx) | reinterpret_cast<uintptr_t>(p.dxt)) % 16 == 0);
+    if (vec_ok && nbch <= 4 * 148 && p.Q <= PREP_MAX_Q) {
+      chunk_rows_finish_kernel<<<(unsigned)nbch, PREP_THREADS, 0, st>>>(p, g.dx, g.lddx, dsend, g.da, g.ddt, ws.part);
+      PMB_LAUNCHED();
+    } else {
+      ssd_rowdots_kernel<<<(unsigned)cdiv(rows * 32, 256), 256, 0, st>>>(p, g.dx, g.lddx, ddt_x, dS, dDrow);
+      PMB_LAUNCHED();
+      ssd_chunk_finish_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p, ddt_x, dS, dDrow, dsend, g.da, g.ddt, ws.part);
+      PMB_LAUNCHED();
+    }
   }
   auto head_sums = [&](cudaStream_t s) -> pmb_status {   // part = [dA partials (B*nc,H)] [dD partials (B*nc,H)]
     if (!in.dt) return PMB_OK;
