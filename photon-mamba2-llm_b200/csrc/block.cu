@@ -264,8 +264,12 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   sg.db = w.dact + d.I; sg.dc = w.dact + d.I + d.G * d.N; sg.lddbc = d.X;
   sg.da = nullptr; sg.ddt = w.ddt; sg.dA = w.dA; sg.dD = g.d_skip;
   PMB_TRY(ssd_bwd(st, sin, w.y, d.I, w.dnormed, d.I, sg, w.ssd));
-  dt_bwd_kernel<<<(unsigned)d.H, 256, 0, st>>>(w.xzd, w.dxzd, d.J, d.I + d.X, p.dt_bias, w.ddt, w.Aneg, w.dA, g.dt_bias, g.a_log, d.M, d.H, ph, pl);
+  // the dt columns (one block per head: a latency-bound loop over the tokens) run next to the conv backward
+  cudaStream_t sdt = st;
+  if (gl) { PMB_TRY(order_after(st, gl->ev[4], gl->s)); sdt = gl->s; }
+  dt_bwd_kernel<<<(unsigned)d.H, 256, 0, sdt>>>(w.xzd, w.dxzd, d.J, d.I + d.X, p.dt_bias, w.ddt, w.Aneg, w.dA, g.dt_bias, g.a_log, d.M, d.H, ph, pl);
   PMB_LAUNCHED();
+  if (gl) PMB_CUDA(cudaEventRecord(gl->ev[5], gl->s));
   // conv + SiLU
   PMB_TRY(conv_silu_bwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, w.dact, w.dxzd, g.conv1d_weight, g.conv1d_bias,
                         w.scratch, w.scratch_bytes, gl, ph, pl));
@@ -281,6 +285,7 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
     const PairGemm gx{0, 1, d.M, d.D, d.J, dxp, win, static_cast<float*>(dx), d.D, static_cast<const float*>(dx_accum)};
     const PairGemm gw{1, 0, d.D, d.J, d.M, Pair16{w.x_hi, w.x_lo, d.D}, dxp, g.in_proj_weight, d.J, nullptr};
     const PairGemm both[2] = {d.J >= d.M ? gx : gw, d.J >= d.M ? gw : gx};
+    if (gl) PMB_CUDA(cudaStreamWaitEvent(st, gl->ev[5], 0));      // the dt columns of the dxzd pair
     PMB_TRY(gemm_pairs_group(st, both, 2));
     if (gl) PMB_TRY(order_after(gl->s, gl->ev[3], st));           // dW_out and the small reductions are done when this block is
   } else {
