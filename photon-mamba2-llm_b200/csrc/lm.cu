@@ -117,10 +117,11 @@ __global__ void __launch_bounds__(256) cross_entropy_kernel(float* __restrict__ 
 // Same loss, with the row staged in shared memory (one read of the logits) and the gradient written back over
 // the row as a (hi, lo) bf16 pair: hi[i] at uint16 index i of the row, lo[i] at uint16 index ld + i, i.e. the pair
 // matrices have a pitch of 2*ld uint16 and share the logits buffer.  Needs V floats of dynamic shared memory.
+// write_lo == 0 (bf16 storage): only the bf16-rounded gradient is written (same place, same pitch).
 constexpr int CE_THREADS = 1024;
 __global__ void __launch_bounds__(CE_THREADS) cross_entropy_pair_inplace_kernel(float* __restrict__ logits, int64_t ld, int V,
                                                                                 const int64_t* __restrict__ targets,
-                                                                                float* __restrict__ row_loss, float inv_rows) {
+                                                                                float* __restrict__ row_loss, float inv_rows, int write_lo) {
   extern __shared__ float srow[];
   __shared__ float red[32];
   const int64_t r = blockIdx.x;
@@ -164,12 +165,12 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_pair_inplace_kernel(
 #pragma unroll
     for (int k = 0; k < 4; ++k) { if (c + k == tg) g[k] -= 1.0f; split(g[k] * inv_rows, h[k], l4[k]); }
     *reinterpret_cast<uint2*>(hi + c) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
-    *reinterpret_cast<uint2*>(lo + c) = make_uint2(l4[0] | (l4[1] << 16), l4[2] | (l4[3] << 16));
+    if (write_lo) *reinterpret_cast<uint2*>(lo + c) = make_uint2(l4[0] | (l4[1] << 16), l4[2] | (l4[3] << 16));
   }
   for (int i = 4 * V4 + threadIdx.x; i < V; i += CE_THREADS) {
     uint32_t h, l1;
     split((srow[i] * inv - (i == tg ? 1.0f : 0.0f)) * inv_rows, h, l1);
-    hi[i] = (uint16_t)h; lo[i] = (uint16_t)l1;
+    hi[i] = (uint16_t)h; if (write_lo) lo[i] = (uint16_t)l1;
   }
 }
 
@@ -356,7 +357,11 @@ static pmb_status lm_create_impl(const pmb_mamba2_config* cfg, int L0, int L1, i
   }
   if (lm->bf16) {
     ok = ok && alloc((void**)&lm->params16, (size_t)o * 2);
-    ok = ok && alloc((void**)&lm->dlogits16, (size_t)lm->tile_rows * lm->Vp * 2);
+    lm->ce_inplace = ((size_t)vocab * 4 <= (size_t)200 * 1024) ? 1 : 0;
+    if (lm->ce_inplace)
+      ok = ok && cudaFuncSetAttribute(cross_entropy_pair_inplace_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, vocab * 4) == cudaSuccess;
+    else
+      ok = ok && alloc((void**)&lm->dlogits16, (size_t)lm->tile_rows * lm->Vp * 2);
   }
   if (L1 > 0) {
     ok = ok && alloc(&lm->saved1, slot1 * (L1 + 1));
@@ -374,7 +379,7 @@ static pmb_status lm_create_impl(const pmb_mamba2_config* cfg, int L0, int L1, i
   cudaMemset(lm->grads, 0, (size_t)o * 4);
   cudaMemset(lm->bad, 0, 256);
   lm->act_bytes = (int64_t)(slot * (L0 + 1) + slot1 * (L1 + 1) + slot + 3 * slot1 + (L1 > 0 ? slot : 0) +
-                            (size_t)lm->tile_rows * lm->Vp * (lm->bf16 ? 6 : 4) + pair_bytes + (size_t)d.M * 4 + lm->ws_bytes);
+                            (size_t)lm->tile_rows * lm->Vp * ((lm->bf16 && !lm->ce_inplace) ? 6 : 4) + pair_bytes + (size_t)d.M * 4 + lm->ws_bytes);
   lm->lp.resize(n_layers); lm->lg.resize(n_layers); lm->lw16.resize(n_layers);
   for (int l = 0; l < n_layers; ++l) {
     const int64_t* f = &lm->off[1 + 8 * l];
@@ -430,7 +435,7 @@ extern "C" void pmb_lm_activation_detail(const pmb_lm* lm, int64_t* h_out3) {
   const size_t esz = lm->bf16 ? 2 : 4;
   h_out3[0] = (int64_t)((size_t)lm->d.M * lm->d.D * esz * (lm->L0 + 1) + (lm->L1 > 0 ? (size_t)lm->d1.M * lm->d.D * esz * (lm->L1 + 1) : 0));                          // stored for backward: block inputs
   h_out3[1] = (int64_t)lm->ws_bytes;                                                              // transient: one block's workspace
-  h_out3[2] = (int64_t)((size_t)lm->tile_rows * lm->Vp * (lm->bf16 ? 6 : ((lm->pairs && !lm->ce_inplace) ? 8 : 4)) + (size_t)lm->d.M * lm->d.D * esz +
+  h_out3[2] = (int64_t)((size_t)lm->tile_rows * lm->Vp * (lm->ce_inplace ? 4 : (lm->bf16 ? 6 : (lm->pairs ? 8 : 4))) + (size_t)lm->d.M * lm->d.D * esz +
                         (lm->pairs ? (size_t)lm->tile_rows * lm->d.D * 4 : 0));  // transient: logits tile (+ its gradient's pair), d(hidden)
 }
 extern "C" const float* pmb_lm_loss_device(const pmb_lm* lm) { return lm ? lm->loss : nullptr; }
@@ -517,17 +522,20 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
     }
     else PMB_TRY(gemm(st, 0, 1, rows, V, D, static_cast<const float*>(hrows), D, table, D, lm->logits, Vp, nullptr, 0));
     { ProfScope prof(st, "cross_entropy", 0.0, 4.0 * rows * 3.0 * V);
-    if (prs && lm->ce_inplace)
-      cross_entropy_pair_inplace_kernel<<<(unsigned)rows, CE_THREADS, (size_t)V * 4, st>>>(lm->logits, Vp, V, d_targets + r0, lm->row_loss + r0, 1.0f / (float)M);
+    if ((prs || h16) && lm->ce_inplace)
+      cross_entropy_pair_inplace_kernel<<<(unsigned)rows, CE_THREADS, (size_t)V * 4, st>>>(lm->logits, Vp, V, d_targets + r0, lm->row_loss + r0, 1.0f / (float)M, prs ? 1 : 0);
     else
       cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>(lm->logits, Vp, V, d_targets + r0, lm->row_loss + r0, 1.0f / (float)M,
                                                            prs ? lm->dlog_hi : nullptr, prs ? lm->dlog_lo : nullptr);
     PMB_LAUNCHED(); }
     // dhidden = dlogits E ;  dE (+)= dlogits^T hidden
     if (h16) {
-      PMB_TRY(cast_f32_bf16(st, lm->logits, lm->dlogits16, rows * Vp));
-      PMB_TRY(gemm_bf16(st, 0, 0, rows, D, V, lm->dlogits16, Vp, table16, D, dhid + (size_t)r0 * D * 2, D, nullptr, 1));
-      PMB_TRY(gemm_bf16(st, 1, 0, V, D, rows, lm->dlogits16, Vp, hrows, D, dtable, D, r0 == 0 ? nullptr : dtable, 0));
+      // in place: the bf16 gradient sits at the start of each logits row (pitch 2*Vp bf16 elements)
+      const uint16_t* dl16 = lm->ce_inplace ? reinterpret_cast<const uint16_t*>(lm->logits) : lm->dlogits16;
+      const int64_t ldl = lm->ce_inplace ? 2 * (int64_t)Vp : Vp;
+      if (!lm->ce_inplace) PMB_TRY(cast_f32_bf16(st, lm->logits, lm->dlogits16, rows * Vp));
+      PMB_TRY(gemm_bf16(st, 0, 0, rows, D, V, dl16, ldl, table16, D, dhid + (size_t)r0 * D * 2, D, nullptr, 1));
+      PMB_TRY(gemm_bf16(st, 1, 0, V, D, rows, dl16, ldl, hrows, D, dtable, D, r0 == 0 ? nullptr : dtable, 0));
     } else if (prs && table_lane) {
       // single row tile: only dhidden is needed now; the embedding-table gradient runs on its own stream next to
       // the first blocks of the stack backward and is joined before the embedding scatter
