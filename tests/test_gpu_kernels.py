@@ -165,6 +165,7 @@ SSD_CASES = [  # B, T, H, P, N, G, Q
     (1, 256, 2, 128, 128, 1, 128),  # wide head, large state
     (2, 512, 8, 64, 64, 1, 128),
     (1, 768, 3, 64, 64, 1, 256),    # three chunks of the production length
+    (1, 1024, 2, 64, 32, 1, 512),   # chunk longer than one 256-thread round of the fused cumsum / row-sum kernels
 ]
 
 
