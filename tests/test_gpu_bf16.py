@@ -49,7 +49,8 @@ def _oracle_block_grads(cfg, p, x, cot):
     return out.detach().float(), xr.grad.float(), {k: v.grad for k, v in pr.items()}
 
 
-@pytest.mark.parametrize("D,N,P,H,Q,B,T", [(128, 16, 32, 8, 64, 2, 128), (768, 64, 64, 24, 256, 1, 512)])
+# the last case has 4096 tokens (long K for the two weight-gradient products)
+@pytest.mark.parametrize("D,N,P,H,Q,B,T", [(128, 16, 32, 8, 64, 2, 128), (768, 64, 64, 24, 256, 1, 512), (128, 16, 32, 8, 64, 4, 1024)])
 def test_block_bf16_storage_vs_oracle(pm, D, N, P, H, Q, B, T):
     cfg = orc.Mamba2Config(d_model=D, d_state=N, d_head=P, n_heads=H, block_len=Q)
     p = block_params(cfg, seed=3)
