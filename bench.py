@@ -314,11 +314,16 @@ def run_ours(args):
         raise SystemExit(f"bench.py: device status word {status}: a kernel gave up on a bounded wait; the numbers are void")
 
     # per-kernel totals of the same steps, CUDA events on the launching stream (rank 0, N=1 semantics)
+    # (eager and on one stream, so that a scope's duration is that kernel alone and not its share of an overlapped stretch)
     prof_steps = min(args.steps, 3)
+    pm_b200.set_concurrency(False)
+    eager_step_device(0)
+    torch.cuda.synchronize()
     pm_b200.profile_start()
     for s in range(prof_steps):
         eager_step_device(s)
     prof = pm_b200.profile_stop()
+    pm_b200.set_concurrency(True)
     peaks = load_peaks()
     tot_ms = sum(p["ms"] for p in prof) or 1.0
     prof.sort(key=lambda p: -p["ms"])

@@ -89,6 +89,11 @@ int64_t pmb_launch_count(void);
  * [{"name","launches","ms","flops","bytes"}] of per-name totals (algorithmic FLOPs / bytes) into h_json. */
 void pmb_profile_start(void);
 pmb_status pmb_profile_stop(char* h_json, size_t capacity);
+/* on = 0: the library stops using its internal side streams (recompute-ahead, concurrent scan chains, deferred
+ * gradient GEMMs and reductions) and enqueues everything on the caller's stream, in the same order; results do not
+ * change.  For per-kernel timing and for callers that want plain single-stream behaviour.  Default on. */
+void pmb_set_concurrency(int32_t on);
+
 /* Reads and clears the device status word (0 = no kernel gave up on a bounded wait). */
 pmb_status pmb_device_status(int32_t* h_word_out);
 

@@ -47,9 +47,11 @@ pmb_status gemm(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K
 }
 
 static SideLane g_lanes[64][7];
+static int g_lanes_enabled = 1;   // pmb_set_concurrency(0): every caller gets no lane and runs its chains on the one stream
 
 pmb_status get_side_lane(int idx, SideLane** out) {
   *out = nullptr;
+  if (!g_lanes_enabled) return PMB_OK;
   int dev = 0;
   PMB_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64 || idx < 0 || idx >= 7) return PMB_OK;
@@ -66,6 +68,8 @@ pmb_status get_side_lane(int idx, SideLane** out) {
   *out = &l;
   return PMB_OK;
 }
+
+void set_lanes_enabled(int on) { g_lanes_enabled = on ? 1 : 0; }
 
 pmb_status order_after(cudaStream_t from, cudaEvent_t ev, cudaStream_t to) {
   PMB_CUDA(cudaEventRecord(ev, from));
@@ -125,6 +129,8 @@ extern "C" pmb_status pmb_profile_stop(char* h_json, size_t capacity) {
   snprintf(h_json + off, capacity - off, "]");
   return PMB_OK;
 }
+
+extern "C" void pmb_set_concurrency(int32_t on) { pmb::set_lanes_enabled(on); }
 
 extern "C" pmb_status pmb_device_status(int32_t* h_word_out) {
   unsigned int w = 0, w2 = 0;

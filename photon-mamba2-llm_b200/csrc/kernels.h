@@ -11,6 +11,7 @@ namespace pmb {
 // like lane 0).  *out stays NULL past device 63.
 struct SideLane { cudaStream_t s = nullptr; cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}; };
 pmb_status get_side_lane(int idx, SideLane** out);
+void set_lanes_enabled(int on);
 // `to` waits for everything enqueued on `from` so far
 pmb_status order_after(cudaStream_t from, cudaEvent_t ev, cudaStream_t to);
 

@@ -819,9 +819,12 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   if (tc) PMB_TRY(side_lane(0, &lane));
   cudaStream_t sb = lane ? lane->s : st;                      // stream of the dG -> dC -> dB chain
   if (lane) PMB_TRY(order_after(st, lane->ev[0], sb));        // inputs of the scan are ready
-  if (tc) PMB_TRY(ssd_tc_dstate(st, in, dy, lddy, ws));
+  if (tc) {
+    PMB_TRY(ssd_tc_dstate(st, in, dy, lddy, ws));
+  } else {
+    PMB_TRY(run_op(st, "ssd_bwd_dstate", make_op<OpDstate>(p, p.N, p.P), nbch, 2.0 * tok * p.H * p.N * p.P));
+  }
   if (lane) PMB_CUDA(cudaEventRecord(lane->ev[1], st));       // dY exp(S) is ready (dC reads it)
-  else PMB_TRY(run_op(st, "ssd_bwd_dstate", make_op<OpDstate>(p, p.N, p.P), nbch, 2.0 * tok * p.H * p.N * p.P));
   {
     ProfScope prof(st, "ssd_bwd_state_pass", 0.0, 12.0 * p.B * p.H * p.N * p.P * p.nc);
     PMB_TRY(launch_state_scan(st, p, p.dh, nullptr, nullptr, 1));

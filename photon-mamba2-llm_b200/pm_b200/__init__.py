@@ -59,6 +59,7 @@ def _load():
         "pmb_profile_stop": (i32, [C.c_char_p, sz]),
         "pmb_gemm_f32": (i32, [vp, i32, i32, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp, i32]),
         "pmb_gemm_reserve_scratch": (i32, [C.c_size_t]),
+        "pmb_set_concurrency": (None, [i32]),
         "pmb_gemm_bf16": (i32, [vp, i32, i32, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp, i32]),
         "pmb_cast_f32_to_bf16": (i32, [vp, vp, vp, i64]),
         "pmb_mamba2_block_workspace_bytes_bf16": (sz, [cfgp, i32, i32]),
@@ -144,6 +145,11 @@ def device_status() -> int:
     w = C.c_int32(0)
     _check(lib.pmb_device_status(C.byref(w)))
     return w.value
+
+
+def set_concurrency(on: bool):
+    """False: everything runs on the caller's stream (no internal side streams); results are unchanged."""
+    lib.pmb_set_concurrency(1 if on else 0)
 
 
 def profile_start():
