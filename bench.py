@@ -1,5 +1,5 @@
 """Benchmark of the Mamba2 SSD block training path (forward + backward with per-block checkpoint
-recompute, optimizer excluded) on the flat Mamba2 LM of BASELINE.json configs[1]:
+recompute, optimizer excluded) on the flat ~100 M parameter Mamba2 LM the headline metric is quoted on:
 24 layers, d_model 768, expand 2, headdim 64, d_state 64, chunk 256, conv 4, vocab 50257 (tied),
 batch 4 x seq 512 per GPU, fp32, seeded uniform tokens.
 
@@ -28,11 +28,11 @@ WORKLOADS = {
     # name: (layers, d_model, headdim, heads, d_state, chunk, vocab, batch per GPU, seq)
     "c2_flat100m_fp32_b4_t512": (24, 768, 64, 24, 64, 256, 50257, 4, 512),
     "c1_single_block_dims_lm": (2, 128, 32, 8, 16, 64, 1000, 2, 128),   # tiny, for quick checks only
-    # BASELINE configs[3]: same model, bf16 storage / fp32 accumulation, batch 8, long context
+    # long-context memory stress: same model, bf16 storage / fp32 accumulation, batch 8
     "c4_flat100m_bf16_b8_t2048": (24, 768, 64, 24, 64, 256, 50257, 8, 2048),
     "c4_flat100m_bf16_b8_t8192": (24, 768, 64, 24, 64, 256, 50257, 8, 8192),
 }
-# BASELINE configs[2]: two 12-layer stacks (token rate and 1/4 rate), bf16 storage, batch 8 x seq 1024
+# two-level model: two 12-layer stacks (token rate and 1/4 rate), bf16 storage, batch 8 x seq 1024
 HIER_WORKLOADS = {"c3_two_level_100m_bf16_b8_t1024": (12, 12, 4)}
 WORKLOADS["c3_two_level_100m_bf16_b8_t1024"] = (12, 768, 64, 24, 64, 256, 50257, 8, 1024)
 BF16_WORKLOADS = {"c3_two_level_100m_bf16_b8_t1024", "c4_flat100m_bf16_b8_t2048", "c4_flat100m_bf16_b8_t8192"}
@@ -45,15 +45,22 @@ def oracle_cfg(w):
     return orc.Mamba2Config(d_model=D, d_state=N, d_head=P, n_heads=H, n_groups=1, d_conv=4, block_len=Q)
 
 
-def make_weights(w, seed=1234):
-    """Random-init weights of the named architecture (same on every rank)."""
-    from oracle import mamba2_oracle as orc
+def make_weights(w, init_block_params, cfg, seed=1234):
+    """Random-init weights of the named architecture (same on every rank).  `init_block_params(cfg, seed)` is the
+    package's initialiser on the CUDA arm and the oracle's on the CPU legs (neither arm imports the other's)."""
     L, D, P, H, N, Q, V, B, T = WORKLOADS[w]
-    cfg = oracle_cfg(w)
     g = torch.Generator(); g.manual_seed(seed)
     embed = torch.randn(V, D, generator=g) * 0.02
-    layers = [orc.init_block_params(cfg, seed=seed + 1 + i) for i in range(L)]
+    layers = [init_block_params(cfg, seed=seed + 1 + i) for i in range(L)]
     return embed, layers
+
+
+def config_dict(w, world):
+    """The `config` object of the JSON line: identical on the CUDA arm and the reference arm."""
+    L, D, P, H, N, Q, V, B, T = WORKLOADS[w]
+    return {"workload": w, "layers": L, "d_model": D, "d_state": N, "headdim": P, "chunk": Q, "vocab": V,
+            "per_gpu_batch": B, "seq_len": T, "global_batch": B * world, "parallelism": f"dp{world}",
+            "checkpointing": "per block"}
 
 
 def make_tokens(w, rank, step, pin):
@@ -139,7 +146,7 @@ def cpu_step_tokens_per_s(w, steps, warmup, sample_batch=1):
     cfg = oracle_cfg(w)
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    embed, layers = make_weights(w)
+    embed, layers = make_weights(w, orc.init_block_params, cfg)
     embed.requires_grad_(True)
     for p in layers:
         for v in p.values():
@@ -166,15 +173,19 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 3))
-    val, avg, cores, sample = cpu_step_tokens_per_s(w, steps, 1)
+    # the same per-GPU batch as the CUDA arm (one rank's worth: the CPU arm has no ranks); a step of the headline
+    # workload takes a few seconds on the host cores, so up to 20 timed steps still end within a few minutes
     L, D, P, H, N, Q, V, B, T = WORKLOADS[w]
+    steps = max(1, min(args.steps, 20))
+    warm = max(1, min(args.warmup, 2))
+    val, avg, cores, sample = cpu_step_tokens_per_s(w, steps, warm, sample_batch=B)
     line = {
         "impl": "reference", "metric": "train tokens/sec (fwd+bwd, ckpt)", "value": val, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": 1, "ms_per_step": avg * 1e3, "higher_is_better": True,
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": avg * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w, "layers": L, "d_model": D, "vocab": V, "per_gpu_batch": B, "seq_len": T,
-                   "note": "CPU restatement of the reference's pm-candle graph (no Rust toolchain to build the reference itself)"},
+        "config": config_dict(w, max(1, args.gpus)),
+        "arm_note": "CPU restatement of the reference's pm-candle graph on the host cores (no Rust toolchain to build the "
+                    "reference itself); rank 0 alone runs it, one per-GPU batch per step",
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -209,13 +220,13 @@ def run_ours(args):
         lm = pm_b200.FlatMamba(cfg, L0, V, B, T, compute_dtype=torch.bfloat16 if bf16 else torch.float32, level1_layers=L1, group=grp)
         L = L0 + L1
         WORKLOADS[w] = (L,) + WORKLOADS[w][1:]
-        embed, layers = make_weights(w)
+        embed, layers = make_weights(w, pm_b200.init_block_params, cfg)
         gw = torch.Generator(); gw.manual_seed(4321)
         wproj = (torch.rand(D, D, generator=gw) * 2 - 1) / D ** 0.5
         lm.load(embed.cuda(), [{k: v.cuda() for k, v in p.items()} for p in layers], wproj=wproj.cuda())
     else:
         lm = pm_b200.FlatMamba(cfg, L, V, B, T, compute_dtype=torch.bfloat16 if bf16 else torch.float32)
-        embed, layers = make_weights(w)
+        embed, layers = make_weights(w, pm_b200.init_block_params, cfg)
         lm.load(embed.cuda(), [{k: v.cuda() for k, v in p.items()} for p in layers])
     del embed, layers
 
@@ -312,6 +323,9 @@ def run_ours(args):
     status = pm_b200.device_status()
     if status != 0:
         raise SystemExit(f"bench.py: device status word {status}: a kernel gave up on a bounded wait; the numbers are void")
+    bad = lm.bad_tokens()
+    if bad != 0:
+        raise SystemExit(f"bench.py: token ids or targets outside [0, vocab) were fed to the step (flags {bad}); the numbers are void")
 
     # per-kernel totals of the same steps, CUDA events on the launching stream (rank 0, N=1 semantics)
     # (eager and on one stream, so that a scope's duration is that kernel alone and not its share of an overlapped stretch)
@@ -363,12 +377,11 @@ def run_ours(args):
             "metric": "train tokens/sec (fwd+bwd, ckpt)", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage / f32 accumulate" if bf16 else "f32", "data": "synthetic",
-            "config": {"workload": w, "layers": L, "d_model": D, "d_state": N, "headdim": P, "chunk": Q, "vocab": V,
-                       "per_gpu_batch": B, "seq_len": T, "global_batch": B * world, "parallelism": f"dp{world}",
-                       "checkpointing": "per block; stored across the stack: block inputs only",
-                       "launch": "eager, per-layer gradient all-reduce overlapped" if graph_step is None else
-                                 ("one CUDA graph replay per step" + (", then one gradient all-reduce" if world > 1 else "")),
-                       "l2": "per-step working set (506 MB parameters + gradients + activations) exceeds the 126 MB L2; no explicit flush"},
+            "config": config_dict(w, world),
+            "arm_note": {"checkpointing": "stored across the stack: block inputs only",
+                         "launch": "eager, per-layer gradient all-reduce overlapped" if graph_step is None else
+                                   ("one CUDA graph replay per step" + (", then one gradient all-reduce" if world > 1 else "")),
+                         "l2": "per-step working set (506 MB parameters + gradients + activations) exceeds the 126 MB L2; no explicit flush"},
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8, "d2h_bytes_per_step": 4,
                     "ms_per_step": ms_e2e / args.steps, "wall_ms_per_step": wall_e2e * 1e3 / args.steps},
             "gpu_launches": int(launches),
@@ -403,7 +416,7 @@ MICRO = {
     "gemm_small_c2_in_proj": ("gemm", dict(M=2048, N=3224, K=768, ta=0, tb=0)),
     "ssd_scan_fp32": ("ssd", dict(B=4, T=8192, H=32, P=64, N=128, G=1, Q=256)),
     "ssd_scan_c2": ("ssd", dict(B=4, T=512, H=24, P=64, N=64, G=1, Q=256)),   # the scan as one layer of configs[1] sees it
-    # BASELINE configs[4]: scan microbench, bf16 inputs / fp32 state, at a quarter of the batch (B=16 in the config)
+    # scan microbench, bf16 inputs / fp32 state: a quarter of the batch, then the full B=16
     "ssd_scan_bf16_in": ("ssd16", dict(B=4, T=8192, H=32, P=64, N=128, G=1, Q=256)),
     "ssd_scan_bf16_in_full": ("ssd16", dict(B=16, T=8192, H=32, P=64, N=128, G=1, Q=256)),
     "decode_step_fp32": ("decode", dict(B=256, D=2048, H=32, P=64, N=128)),
@@ -449,10 +462,8 @@ def run_micro(args):
         flops, nbytes = B * T * (fwd + bwd), 4.0 * B * T * (H * P * 5 + 2 * G * N * 2 + 2 * H)
     else:
         B, D, H, P, N = (a[k] for k in "BDHPN")
-        from oracle import mamba2_oracle as orc
-        ocfg = orc.Mamba2Config(d_model=D, d_state=N, d_head=P, n_heads=H, n_groups=1, block_len=256)
         cfg = pm_b200.Mamba2Config(d_model=D, d_state=N, d_head=P, n_heads=H, n_groups=1, block_len=256)
-        blk = pm_b200.Mamba2Block(cfg, {k: v.cuda() for k, v in orc.init_block_params(ocfg, 1).items()})
+        blk = pm_b200.Mamba2Block(cfg, {k: v.cuda() for k, v in pm_b200.init_block_params(cfg, 1).items()})
         st = blk.zero_state(B)
         st["ssm_state"].normal_()
         xt = rnd(B, 1, D)

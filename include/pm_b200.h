@@ -96,6 +96,13 @@ void pmb_set_concurrency(int32_t on);
 
 /* Reads and clears the device status word (0 = no kernel gave up on a bounded wait). */
 pmb_status pmb_device_status(int32_t* h_word_out);
+/* Self-tests (no reference counterpart; the reference guards its GPU tests with host-side deadlines,
+ * crates/pm-cuda/tests/conv1d_depthwise_bwd_gpu.rs:186-212).  pmb_selftest_bounded_wait launches one thread that
+ * waits on a barrier nothing arms, gives up after `polls` polls (1..2^20) and raises bit 15 of the status word
+ * (0x8000): the path every tensor-core kernel here takes instead of hanging.  pmb_selftest_device_once checks the
+ * per-device "done once" table on the host and returns the number of failed checks (no GPU needed). */
+pmb_status pmb_selftest_bounded_wait(void* stream, uint32_t polls);
+int32_t pmb_selftest_device_once(void);
 
 /* ---- GEMM (Ops::matmul).  C[M,N] = op(A)·op(B) (+ R).  fp32 storage.
  * trans_a = 0: A is (M,K) row-major with leading dimension lda; 1: A is stored (K,M).
@@ -278,7 +285,7 @@ pmb_status pmb_lm_create(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t
  * flat.rs:74-78); parameters and gradients stay fp32. */
 pmb_status pmb_lm_create_dtype(const pmb_mamba2_config* cfg, int32_t n_layers, int32_t vocab,
                                int32_t batch, int32_t seqlen, int32_t bf16_storage, pmb_lm** out);
-/* Two-level variant (BASELINE config 3; built from the same blocks, no counterpart wiring in the reference, whose
+/* Two-level variant (built from the same blocks; no counterpart wiring in the reference, whose
  * PHOTON glue is crates/pm-core/src/model.rs): level 0 = n_layers_level0 blocks at token rate; groups of `group`
  * hidden states are mean-pooled and projected by a (D,D) matrix into level 1 (n_layers_level1 blocks at 1/group
  * rate); level-1 outputs are repeated `group` times, shifted by one group, and added back before the tied head.
@@ -299,6 +306,12 @@ void       pmb_lm_activation_detail(const pmb_lm* lm, int64_t* h_out3);
 pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t* d_ids, const int64_t* d_targets,
                               pmb_layer_callback on_layer_done, void* user);
 const float* pmb_lm_loss_device(const pmb_lm* lm);
+/* Token ids or targets outside [0, vocab) (on which the reference's gather / cross-entropy fail, photon/embedding.rs:
+ * 54-66, pm-train/src/loss.rs:39-69) do not fault here: a bad id reads embedding row 0, a bad target contributes no
+ * loss and no one-hot term, and a flag word on the device records it (bit 0: an id, bit 1: a target).
+ * pmb_lm_step_host checks the word after every step; callers of pmb_lm_step_device and of captured graphs poll it
+ * here (waits for `stream`, reads and clears the word). */
+pmb_status pmb_lm_bad_tokens(pmb_lm* lm, void* stream, int32_t* h_flags_out);
 /* Same step through host buffers: copies ids/targets (pinned or pageable host memory) to the device,
  * runs the step, copies the loss back and synchronises the stream.  This is the call a host trainer makes. */
 pmb_status pmb_lm_step_host(pmb_lm* lm, void* stream, const int64_t* h_ids, const int64_t* h_targets,

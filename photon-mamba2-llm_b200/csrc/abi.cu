@@ -1,8 +1,8 @@
 // C ABI entry points for the individual kernels, library-wide state, and the GEMM engine dispatch.
 #include <cstdio>
 #include <cstdlib>
+#include <initializer_list>
 #include "common.cuh"
-#include <cstdlib>
 #include "kernels.h"
 #include "ssd_tc.h"
 
@@ -24,13 +24,8 @@ pmb_status gemm(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K
   // engine 4, and "auto" unless PMB_GEMM_ENGINE=tf32: split both operands into bf16 pairs and use the kind::f16 kernel
   static const int no_x2 = [] { const char* e = getenv("PMB_GEMM_ENGINE"); return (e && strcmp(e, "tf32") == 0) ? 1 : 0; }();
   if (engine == 4 || engine == 5 || engine == 6 || (engine == 0 && !no_x2)) {
-    if (gemm_f32_via_bf16x2_supported(ta, tb, M, N, K, A, lda, B, ldb)) {
-      set_pair_override(engine == 4 ? 0 : engine == 5 ? 2 : engine == 6 ? 1 : -1);
-      pmb_status r = gemm_f32_via_bf16x2(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R);
-      set_pair_override(-1);
-      return r;
-    }
-    if (engine >= 4) return fail(PMB_ERR_UNSUPPORTED, "gemm: the bf16-pair engine needs 16-byte aligned operands and row lengths that are multiples of 8");
+    // (the split pass compacts rows to a pitch that meets TMA's 16-byte rules, so every fp32 operand qualifies)
+    return gemm_f32_via_bf16x2(st, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, R, engine == 4 ? 0 : engine == 5 ? 2 : engine == 6 ? 1 : -1);
   }
   bool ok = gemm_tc_supported(ta, tb, M, N, K, A, lda, B, ldb, C, ldc);
   if ((engine == 2 || engine == 3) && !ok) return fail(PMB_ERR_UNSUPPORTED, "gemm: tcgen05 engine needs 16-byte aligned operands and leading dimensions");
@@ -143,6 +138,28 @@ extern "C" pmb_status pmb_device_status(int32_t* h_word_out) {
   w |= w2 << 24;
   if (h_word_out) *h_word_out = (int32_t)w;
   return PMB_OK;
+}
+
+namespace pmb { pmb_status bounded_wait_selftest(cudaStream_t st, uint32_t polls); }
+
+extern "C" pmb_status pmb_selftest_bounded_wait(void* stream, uint32_t polls) {
+  if (polls == 0 || polls > (1u << 20)) return fail(PMB_ERR_ARG, "selftest_bounded_wait: polls must be in 1..2^20");
+  return bounded_wait_selftest(static_cast<cudaStream_t>(stream), polls);
+}
+
+extern "C" int32_t pmb_selftest_device_once(void) {
+  DeviceOnce f;
+  int bad = 0;
+  for (int d : {0, 1, PMB_MAX_DEVICES - 1}) {
+    if (!f.pending(d)) ++bad;          // every ordinal starts pending
+    f.mark(d);
+    if (f.pending(d)) ++bad;           // and is done after its own mark
+  }
+  if (!f.pending(2)) ++bad;            // marking one ordinal leaves the others pending
+  if (!f.pending(-1) || !f.pending(PMB_MAX_DEVICES)) ++bad;   // ordinals outside the table are never skipped
+  f.mark(PMB_MAX_DEVICES);             // ... and marking them is a no-op, not an out-of-bounds write
+  if (!f.pending(PMB_MAX_DEVICES)) ++bad;
+  return bad;
 }
 
 extern "C" pmb_status pmb_gemm_f32(void* stream, int32_t trans_a, int32_t trans_b, int64_t M, int64_t N, int64_t K,

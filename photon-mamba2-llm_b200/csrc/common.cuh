@@ -67,6 +67,29 @@ struct ProfScope {
   }
 };
 
+// "Done once per device" flags.  Function attributes such as the opt-in dynamic shared-memory size belong to
+// the (kernel, device) pair, so a process that drives several GPUs has to set them on each; the table is indexed
+// by device ordinal like the library's other per-device state.  claim() returns true exactly once per ordinal
+// (always true for ordinals outside the table, which costs a repeated call but never skips one).
+constexpr int PMB_MAX_DEVICES = 64;
+struct DeviceOnce {
+  bool done[PMB_MAX_DEVICES] = {};
+  bool pending(int dev) const { return dev < 0 || dev >= PMB_MAX_DEVICES || !done[dev]; }
+  void mark(int dev) { if (dev >= 0 && dev < PMB_MAX_DEVICES) done[dev] = true; }
+};
+// Sets the dynamic shared-memory limit of `kernel` (given last, so template arguments with commas are fine)
+// the first time the calling site runs on the current device.
+#define PMB_SMEM_OPT_IN(bytes, ...)                                                                              \
+  do {                                                                                                           \
+    static pmb::DeviceOnce once__;                                                                               \
+    int dev__ = 0;                                                                                               \
+    PMB_CUDA(cudaGetDevice(&dev__));                                                                             \
+    if (once__.pending(dev__)) {                                                                                 \
+      PMB_CUDA(cudaFuncSetAttribute(__VA_ARGS__, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes)));    \
+      once__.mark(dev__);                                                                                        \
+    }                                                                                                            \
+  } while (0)
+
 inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 

@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <tuple>
 #include "tc_common.cuh"
 #include "kernels.h"
@@ -62,6 +63,61 @@ __device__ __forceinline__ uint16_t float_to_bf16_bits(float f) {   // round to 
   if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
   u += 0x7fffu + ((u >> 16) & 1u);
   return (uint16_t)(u >> 16);
+}
+
+// Epilogue of one 32-column piece of an output row: adds R when given and stores fp32 or bf16, 16-byte vectors
+// when the row is aligned and the piece lies inside the matrix, element by element otherwise.
+__device__ __forceinline__ void store_row_piece(const Params& p, int m, int nb, const uint32_t (&r)[32]) {
+  if (p.out_bf16) {
+    uint16_t* crow = static_cast<uint16_t*>(p.C) + (int64_t)m * p.ldc + nb;
+    const uint16_t* rrow = p.R ? static_cast<const uint16_t*>(p.R) + (int64_t)m * p.ldc + nb : nullptr;
+    const bool vec = (nb + 32 <= p.N) && ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                     (!p.R || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+    if (vec) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+        if (rrow) {
+          uint4 q = *reinterpret_cast<const uint4*>(rrow + j);
+          const uint32_t qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { v[2 * e] += __uint_as_float(qq[e] << 16); v[2 * e + 1] += __uint_as_float(qq[e] & 0xffff0000u); }
+        }
+        uint4 o;
+        o.x = (uint32_t)float_to_bf16_bits(v[0]) | ((uint32_t)float_to_bf16_bits(v[1]) << 16);
+        o.y = (uint32_t)float_to_bf16_bits(v[2]) | ((uint32_t)float_to_bf16_bits(v[3]) << 16);
+        o.z = (uint32_t)float_to_bf16_bits(v[4]) | ((uint32_t)float_to_bf16_bits(v[5]) << 16);
+        o.w = (uint32_t)float_to_bf16_bits(v[6]) | ((uint32_t)float_to_bf16_bits(v[7]) << 16);
+        *reinterpret_cast<uint4*>(crow + j) = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N) crow[j] = float_to_bf16_bits(__uint_as_float(r[j]) + (rrow ? bf16_bits_to_float(rrow[j]) : 0.0f));
+    }
+  } else {
+    float* crow = static_cast<float*>(p.C) + (int64_t)m * p.ldc + nb;
+    const float* rrow = p.R ? static_cast<const float*>(p.R) + (int64_t)m * p.ldc + nb : nullptr;
+    const bool vec = (nb + 32 <= p.N) && ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                     (!p.R || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+    if (vec) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        if (rrow) {
+          float4 q = *reinterpret_cast<const float4*>(rrow + j);
+          v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+        }
+        *reinterpret_cast<float4*>(crow + j) = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N) crow[j] = __uint_as_float(r[j]) + (rrow ? rrow[j] : 0.0f);
+    }
+  }
 }
 
 // One launch carries up to MAX_GROUP independent products: CTAs [0, pr[0].tiles) work on the first, the next
@@ -207,59 +263,7 @@ gemm_bf16_kernel(const __grid_constant__ Group g) {
       for (int c0 = 0; c0 < TBN; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_acc + ((uint32_t)lane_base << 16) + (uint32_t)c0, r);
-        if (m < p.M) {
-          const int nb = n0 + c0;
-          if (p.out_bf16) {
-            uint16_t* crow = static_cast<uint16_t*>(p.C) + (int64_t)m * p.ldc + nb;
-            const uint16_t* rrow = p.R ? static_cast<const uint16_t*>(p.R) + (int64_t)m * p.ldc + nb : nullptr;
-            const bool vec = (nb + 32 <= p.N) && ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                             (!p.R || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
-            if (vec) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                float v[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
-                if (rrow) {
-                  uint4 q = *reinterpret_cast<const uint4*>(rrow + j);
-                  const uint32_t qq[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) { v[2 * e] += __uint_as_float(qq[e] << 16); v[2 * e + 1] += __uint_as_float(qq[e] & 0xffff0000u); }
-                }
-                uint4 o;
-                o.x = (uint32_t)float_to_bf16_bits(v[0]) | ((uint32_t)float_to_bf16_bits(v[1]) << 16);
-                o.y = (uint32_t)float_to_bf16_bits(v[2]) | ((uint32_t)float_to_bf16_bits(v[3]) << 16);
-                o.z = (uint32_t)float_to_bf16_bits(v[4]) | ((uint32_t)float_to_bf16_bits(v[5]) << 16);
-                o.w = (uint32_t)float_to_bf16_bits(v[6]) | ((uint32_t)float_to_bf16_bits(v[7]) << 16);
-                *reinterpret_cast<uint4*>(crow + j) = o;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < p.N) crow[j] = float_to_bf16_bits(__uint_as_float(r[j]) + (rrow ? bf16_bits_to_float(rrow[j]) : 0.0f));
-            }
-          } else {
-            float* crow = static_cast<float*>(p.C) + (int64_t)m * p.ldc + nb;
-            const float* rrow = p.R ? static_cast<const float*>(p.R) + (int64_t)m * p.ldc + nb : nullptr;
-            const bool vec = (nb + 32 <= p.N) && ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                             (!p.R || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
-            if (vec) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                if (rrow) {
-                  float4 q = *reinterpret_cast<const float4*>(rrow + j);
-                  v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
-                }
-                *reinterpret_cast<float4*>(crow + j) = v;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < p.N) crow[j] = __uint_as_float(r[j]) + (rrow ? rrow[j] : 0.0f);
-            }
-          }
-        }
+        if (m < p.M) store_row_piece(p, m, n0 + c0, r);
       }
     }
   }
@@ -454,59 +458,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ Group g) {
         if (n0 + c0 >= p.N) break;      // uniform
         uint32_t r[32];
         tmem_ld32(tmem_acc + ((uint32_t)lane_base << 16) + (uint32_t)c0, r);
-        if (m < p.M) {
-          const int nb = n0 + c0;
-          if (p.out_bf16) {
-            uint16_t* crow = static_cast<uint16_t*>(p.C) + (int64_t)m * p.ldc + nb;
-            const uint16_t* rrow = p.R ? static_cast<const uint16_t*>(p.R) + (int64_t)m * p.ldc + nb : nullptr;
-            const bool vec = (nb + 32 <= p.N) && ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                             (!p.R || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
-            if (vec) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                float v[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
-                if (rrow) {
-                  uint4 qv = *reinterpret_cast<const uint4*>(rrow + j);
-                  const uint32_t qq[4] = {qv.x, qv.y, qv.z, qv.w};
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) { v[2 * e] += __uint_as_float(qq[e] << 16); v[2 * e + 1] += __uint_as_float(qq[e] & 0xffff0000u); }
-                }
-                uint4 o;
-                o.x = (uint32_t)float_to_bf16_bits(v[0]) | ((uint32_t)float_to_bf16_bits(v[1]) << 16);
-                o.y = (uint32_t)float_to_bf16_bits(v[2]) | ((uint32_t)float_to_bf16_bits(v[3]) << 16);
-                o.z = (uint32_t)float_to_bf16_bits(v[4]) | ((uint32_t)float_to_bf16_bits(v[5]) << 16);
-                o.w = (uint32_t)float_to_bf16_bits(v[6]) | ((uint32_t)float_to_bf16_bits(v[7]) << 16);
-                *reinterpret_cast<uint4*>(crow + j) = o;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < p.N) crow[j] = float_to_bf16_bits(__uint_as_float(r[j]) + (rrow ? bf16_bits_to_float(rrow[j]) : 0.0f));
-            }
-          } else {
-            float* crow = static_cast<float*>(p.C) + (int64_t)m * p.ldc + nb;
-            const float* rrow = p.R ? static_cast<const float*>(p.R) + (int64_t)m * p.ldc + nb : nullptr;
-            const bool vec = (nb + 32 <= p.N) && ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                             (!p.R || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
-            if (vec) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                if (rrow) {
-                  float4 qv = *reinterpret_cast<const float4*>(rrow + j);
-                  v.x += qv.x; v.y += qv.y; v.z += qv.z; v.w += qv.w;
-                }
-                *reinterpret_cast<float4*>(crow + j) = v;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < p.N) crow[j] = __uint_as_float(r[j]) + (rrow ? rrow[j] : 0.0f);
-            }
-          }
-        }
+        if (m < p.M) store_row_piece(p, m, n0 + c0, r);
       }
     }
   }
@@ -523,10 +475,12 @@ struct MapKey {
   const void* base; int64_t inner, outer, ld; int bi, bo;
   bool operator<(const MapKey& o) const { return std::tie(base, inner, outer, ld, bi, bo) < std::tie(o.base, o.inner, o.outer, o.ld, o.bi, o.bo); }
 };
-static std::map<MapKey, CUtensorMap> g_cache;
+static std::map<MapKey, CUtensorMap> g_cache;   // shared by every device and host thread: guarded by g_cache_mu
+static std::mutex g_cache_mu;
 
 static pmb_status make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_inner, int box_outer) {
   MapKey key{base, inner, outer, ld, box_inner, box_outer};
+  std::lock_guard<std::mutex> lock(g_cache_mu);
   auto it = g_cache.find(key);
   if (it == g_cache.end()) {
     if (g_cache.size() > 8192) g_cache.clear();
@@ -557,11 +511,7 @@ pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return fail(PMB_ERR_SHAPE, "gemm_bf16: operands need 16-byte aligned bases and row pitches that are multiples of 8 elements");
   if (cdiv(M, TBM) * cdiv(N, TBN) > 0x7fffffff) return fail(PMB_ERR_SHAPE, "gemm_bf16: too many tiles");
-  static bool attr_set = false;
-  if (!attr_set) {
-    PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::SMEM_BYTES));
-    attr_set = true;
-  }
+  PMB_SMEM_OPT_IN(Cfg<false>::SMEM_BYTES, gemm_bf16_kernel<false>);
   Group g{};
   Problem& q = g.pr[0];
   if (!ta) PMB_TRY(make_map(&q.mA, A, K, M, lda, TBK, TBM)); else PMB_TRY(make_map(&q.mA, A, M, K, lda, 64, TBK));
@@ -577,11 +527,7 @@ pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
     const int64_t clusters = cdiv(M, 256) * cdiv(N, 256);
     const bool pair = env >= 0 ? env != 0 : (M > 128 && clusters >= 4 * 74);
     if (pair) {
-      static bool attr2 = false;
-      if (!attr2) {
-        PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_pair_kernel<false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<false, 256>::SMEM_BYTES));
-        attr2 = true;
-      }
+      PMB_SMEM_OPT_IN((PairCfg<false, 256>::SMEM_BYTES), gemm_bf16_pair_kernel<false, 256>);
       q.tiles_n = (int)cdiv(N, 256); q.tiles = (int)clusters;
       ProfScope prof(st, "gemm_bf16_pair256", 2.0 * M * N * K, 2.0 * ((double)M * K + (double)K * N) + (out_bf16 ? 2.0 : 4.0) * M * N * (R ? 2 : 1));
       gemm_bf16_pair_kernel<false, 256><<<(unsigned)(2 * clusters), NTHREADS, PairCfg<false, 256>::SMEM_BYTES, st>>>(g);
@@ -638,13 +584,11 @@ bool gemm_pairs_enabled() {
   return on != 0;
 }
 
-// Tile shape of the pair GEMM.  PMB_GEMM_PAIR=0/1/2 forces it.
-static int g_pair_override = -1;   // engine 4 / 5 of the public GEMM entry force the tile shape for one call
-void set_pair_override(int v) { g_pair_override = v; }
-// 0 = 128x128 single-CTA tiles, 1 = 256x128 CTA-pair tiles, 2 = 256x256 CTA-pair tiles
-static int pick_pair_mode(const PairGemm* gs, int n) {
+// Tile shape of the pair GEMM: 0 = 128x128 single-CTA tiles, 1 = 256x128 CTA-pair tiles, 2 = 256x256 CTA-pair tiles.
+// `tile_mode` >= 0 (engines 4 / 5 / 6 of the public GEMM entry) or PMB_GEMM_PAIR=0/1/2 force it.
+static int pick_pair_mode(const PairGemm* gs, int n, int tile_mode) {
   static const int env = [] { const char* e = getenv("PMB_GEMM_PAIR"); return e ? atoi(e) : -1; }();
-  const int forced = g_pair_override >= 0 ? g_pair_override : env;
+  const int forced = tile_mode >= 0 ? tile_mode : env;
   if (forced >= 0 && forced <= 2) return forced;
   int64_t clusters = 0;
   for (int i = 0; i < n; ++i) {
@@ -660,14 +604,10 @@ static int pick_pair_mode(const PairGemm* gs, int n) {
 // Relative accuracy ~1e-5 of the result's scale; twice the tensor-core rate and less than half the shared-memory
 // traffic of the 3xTF32 kernel.  Up to two independent products go out as one launch; the tiles of g[0] are
 // scheduled first, so put the product with the longer K there.
-pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n) {
+pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n, int tile_mode) {
   using namespace hb;
   if (n < 1 || n > MAX_GROUP) return fail(PMB_ERR_ARG, "gemm_pairs_group: 1 to %d products per launch", MAX_GROUP);
-  static bool attr_set = false;
-  if (!attr_set) {
-    PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::SMEM_BYTES));
-    attr_set = true;
-  }
+  PMB_SMEM_OPT_IN(Cfg<true>::SMEM_BYTES, gemm_bf16_kernel<true>);
   Group g{};
   for (int i = 1; i < MAX_GROUP; ++i) { g.pr[i].tiles_n = 1; g.pr[i].tiles = 0; }
   double flops = 0.0, bytes = 0.0;
@@ -696,15 +636,11 @@ pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n) {
     flops += 2.0 * M * N * K;
     bytes += 4.0 * ((double)M * K + (double)K * N + (double)M * N * (e.R ? 2 : 1));
   }
-  const int pair_mode = pick_pair_mode(gs, n);
+  const int pair_mode = pick_pair_mode(gs, n, tile_mode);
   if (pair_mode) {
     const int bn2 = pair_mode == 2 ? 256 : 128;
-    static bool attr2 = false;
-    if (!attr2) {
-      PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_pair_kernel<true, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<true, 256>::SMEM_BYTES));
-      PMB_CUDA(cudaFuncSetAttribute(gemm_bf16_pair_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<true, 128>::SMEM_BYTES));
-      attr2 = true;
-    }
+    PMB_SMEM_OPT_IN((PairCfg<true, 256>::SMEM_BYTES), gemm_bf16_pair_kernel<true, 256>);
+    PMB_SMEM_OPT_IN((PairCfg<true, 128>::SMEM_BYTES), gemm_bf16_pair_kernel<true, 128>);
     int64_t clusters = 0;
     for (int i = 0; i < n; ++i) {
       const PairGemm& e = gs[i];
@@ -728,59 +664,62 @@ pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n) {
 }
 
 pmb_status gemm_pairs(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const Pair16& A, const Pair16& B,
-                      float* C, int64_t ldc, const float* R) {
+                      float* C, int64_t ldc, const float* R, int tile_mode) {
   PairGemm e{ta, tb, M, N, K, A, B, C, ldc, R};
-  return gemm_pairs_group(st, &e, 1);
+  return gemm_pairs_group(st, &e, 1, tile_mode);
 }
 
-// Library-owned scratch for the pairs of callers that hand in fp32 operands (grow-only, one per device).
+// Library-owned scratch for the pairs of callers that hand in fp32 operands (one per device).
 // pmb_gemm_reserve_scratch() sizes it up front for callers that must not allocate later.
-static void* g_scratch[64] = {nullptr};
-static size_t g_scratch_bytes[64] = {0};
+// A block that has been handed out is never freed or moved: kernels already enqueued, and CUDA graphs that
+// captured a call, keep using its address.  When a larger product arrives a new, larger block is allocated
+// beside the old ones (the old ones stay until the process ends); there is no device-wide synchronisation.
+static void* g_scratch[PMB_MAX_DEVICES] = {nullptr};
+static size_t g_scratch_bytes[PMB_MAX_DEVICES] = {0};
+static std::mutex g_scratch_mu;
 
-pmb_status gemm_scratch(size_t bytes, void** out) {
+pmb_status gemm_scratch(size_t bytes, void** out, cudaStream_t user_stream, bool check_capture) {
   int dev = 0;
   PMB_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(PMB_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  if (dev < 0 || dev >= PMB_MAX_DEVICES) return fail(PMB_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
   if (g_scratch_bytes[dev] < bytes) {
-    if (g_scratch[dev]) { PMB_CUDA(cudaDeviceSynchronize()); PMB_CUDA(cudaFree(g_scratch[dev])); g_scratch[dev] = nullptr; g_scratch_bytes[dev] = 0; }
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (check_capture && cudaStreamIsCapturing(user_stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+      return fail(PMB_ERR_WORKSPACE, "gemm: the pair scratch would have to grow during stream capture; call pmb_gemm_reserve_scratch(%zu) first", bytes);
     size_t want = align_up(bytes + bytes / 4, (size_t)1 << 20);
-    PMB_CUDA(cudaMalloc(&g_scratch[dev], want));
+    void* fresh = nullptr;
+    PMB_CUDA(cudaMalloc(&fresh, want));
+    g_scratch[dev] = fresh;          // the previous block is deliberately kept alive
     g_scratch_bytes[dev] = want;
   }
   *out = g_scratch[dev];
   return PMB_OK;
 }
 
-bool gemm_f32_via_bf16x2_supported(int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
-                                   const float* B, int64_t ldb) {
-  (void)ta; (void)tb; (void)A; (void)B; (void)lda; (void)ldb;
-  return M > 0 && N > 0 && K > 0;
-}
-
 // fp32 operands: one elementwise pass each into the scratch (rows compacted to a pitch that is a multiple of 8),
 // then gemm_pairs.
 pmb_status gemm_f32_via_bf16x2(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
-                               const float* B, int64_t ldb, float* C, int64_t ldc, const float* R) {
+                               const float* B, int64_t ldb, float* C, int64_t ldc, const float* R, int tile_mode) {
   const int64_t a_rows = ta ? K : M, a_cols = ta ? M : K, b_rows = tb ? N : K, b_cols = tb ? K : N;
   const int64_t a_ld = (int64_t)align_up((size_t)a_cols, 8), b_ld = (int64_t)align_up((size_t)b_cols, 8);
   const size_t a_el = align_up((size_t)a_rows * a_ld, 64), b_el = align_up((size_t)b_rows * b_ld, 64);
   void* scratch = nullptr;
-  PMB_TRY(gemm_scratch((2 * a_el + 2 * b_el) * 2 + 1024, &scratch));
+  PMB_TRY(gemm_scratch((2 * a_el + 2 * b_el) * 2 + 1024, &scratch, st, true));
   uint16_t* a_hi = static_cast<uint16_t*>(scratch);
   uint16_t* a_lo = a_hi + a_el;
   uint16_t* b_hi = a_lo + a_el;
   uint16_t* b_lo = b_hi + b_el;
   PMB_TRY(split_pair16(st, A, a_rows, a_cols, lda, a_hi, a_lo, a_ld));
   PMB_TRY(split_pair16(st, B, b_rows, b_cols, ldb, b_hi, b_lo, b_ld));
-  return gemm_pairs(st, ta, tb, M, N, K, Pair16{a_hi, a_lo, a_ld}, Pair16{b_hi, b_lo, b_ld}, C, ldc, R);
+  return gemm_pairs(st, ta, tb, M, N, K, Pair16{a_hi, a_lo, a_ld}, Pair16{b_hi, b_lo, b_ld}, C, ldc, R, tile_mode);
 }
 
 }  // namespace pmb
 
 extern "C" pmb_status pmb_gemm_reserve_scratch(size_t bytes) {
   void* p = nullptr;
-  return pmb::gemm_scratch(bytes, &p);
+  return pmb::gemm_scratch(bytes, &p, nullptr, false);
 }
 
 extern "C" pmb_status pmb_gemm_bf16(void* stream, int32_t trans_a, int32_t trans_b, int64_t M, int64_t N, int64_t K,

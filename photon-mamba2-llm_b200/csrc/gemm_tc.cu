@@ -370,11 +370,7 @@ bool gemm_tc_supported(int ta, int tb, int64_t M, int64_t N, int64_t K, const fl
 pmb_status gemm_tc(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
                    const float* B, int64_t ldb, float* C, int64_t ldc, const float* R) {
   using namespace tc;
-  static bool attr_set = false;
-  if (!attr_set) {
-    PMB_CUDA(cudaFuncSetAttribute(gemm_3xtf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    attr_set = true;
-  }
+  PMB_SMEM_OPT_IN(SMEM_BYTES, gemm_3xtf32_kernel);
   CUtensorMap mapA, mapB;
   // A: ta=0 -> stored (M,K), K contiguous (K-major);  ta=1 -> stored (K,M), M contiguous (MN-major)
   const CUtensorMapSwizzle kmaj = CU_TENSOR_MAP_SWIZZLE_128B, mnmaj = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;

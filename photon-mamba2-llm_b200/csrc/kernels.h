@@ -107,17 +107,16 @@ pmb_status read_clear_device_status_bf16(unsigned int* word);
 struct Pair16 { const uint16_t* hi; const uint16_t* lo; int64_t ld; };
 pmb_status split_pair16(cudaStream_t st, const float* src, int64_t rows, int64_t cols, int64_t ld, uint16_t* hi, uint16_t* lo,
                         int64_t ld16);
+// tile_mode: -1 = chosen by tile count, 0 = 128x128 single-CTA tiles, 1 = 256x128 / 2 = 256x256 CTA-pair tiles
 pmb_status gemm_pairs(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const Pair16& A, const Pair16& B,
-                      float* C, int64_t ldc, const float* R);
+                      float* C, int64_t ldc, const float* R, int tile_mode = -1);
 struct PairGemm { int ta, tb; int64_t M, N, K; Pair16 A, B; float* C; int64_t ldc; const float* R; };
 // up to four independent products in one launch (tiles of g[0] first: give it the longer K)
-pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* g, int n);
-bool gemm_pairs_enabled();
-void set_pair_override(int v);   // -1 = heuristic, 0 = 128x128 single-CTA tiles, 1 = 256x256 CTA-pair tiles   // false when PMB_GEMM_ENGINE is tf32 or simt
-bool gemm_f32_via_bf16x2_supported(int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
-                                   const float* B, int64_t ldb);
+pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* g, int n, int tile_mode = -1);
+bool gemm_pairs_enabled();   // false when PMB_GEMM_ENGINE is tf32 or simt
+// fp32 operands of any alignment: split into the library's pair scratch (compacted row pitch), then gemm_pairs
 pmb_status gemm_f32_via_bf16x2(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda,
-                               const float* B, int64_t ldb, float* C, int64_t ldc, const float* R);
+                               const float* B, int64_t ldb, float* C, int64_t ldc, const float* R, int tile_mode = -1);
 
 // ---- block.cu.  w16 != NULL selects bf16 storage: x / residual / out / dout / dx are bf16 and the two
 // projections use the bf16 weight copies; NULL = fp32 everywhere.

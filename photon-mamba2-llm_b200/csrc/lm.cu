@@ -25,7 +25,7 @@ __global__ void embedding_fwd_kernel(const float* __restrict__ table, const int6
   int64_t r = i / (D / 4);
   int c = (int)(i % (D / 4)) * 4;
   int64_t id = ids[r];
-  if (id < 0 || id >= V) { if (c == 0) atomicOr(bad, 1u); id = 0; }
+  if (id < 0 || id >= V) { if (c == 0) atomicOr(bad, 1u); id = 0; }   // flagged; row 0 stands in so that nothing reads out of bounds
   *reinterpret_cast<float4*>(out + r * D + c) = *reinterpret_cast<const float4*>(table + id * D + c);
 }
 
@@ -68,7 +68,8 @@ __global__ void embedding_bwd_kernel(float* __restrict__ dtable, const int64_t* 
 // row_loss[r] = logsumexp - logit[target].
 __global__ void __launch_bounds__(256) cross_entropy_kernel(float* __restrict__ logits, int64_t ld, int V,
                                                             const int64_t* __restrict__ targets, float* __restrict__ row_loss,
-                                                            float inv_rows, uint16_t* __restrict__ d_hi, uint16_t* __restrict__ d_lo) {
+                                                            float inv_rows, uint16_t* __restrict__ d_hi, uint16_t* __restrict__ d_lo,
+                                                            unsigned int* __restrict__ bad) {
   __shared__ float red[32];
   __shared__ float sh_max;
   int64_t r = blockIdx.x;
@@ -96,7 +97,10 @@ __global__ void __launch_bounds__(256) cross_entropy_kernel(float* __restrict__ 
   float tot = block_sum(s, red);
   float lse = m + logf(tot);
   int64_t tg = targets[r];
-  if (threadIdx.x == 0) row_loss[r] = (tg >= 0 && tg < V) ? lse - row[tg] : 0.0f;
+  if (threadIdx.x == 0) {
+    row_loss[r] = (tg >= 0 && tg < V) ? lse - row[tg] : 0.0f;
+    if (tg < 0 || tg >= V) atomicOr(bad, 2u);     // the reference's gather fails on such a target; here the row is flagged
+  }
   __syncthreads();
   float inv = 1.0f / tot;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
@@ -119,9 +123,13 @@ __global__ void __launch_bounds__(256) cross_entropy_kernel(float* __restrict__ 
 // matrices have a pitch of 2*ld uint16 and share the logits buffer.  Needs V floats of dynamic shared memory.
 // write_lo == 0 (bf16 storage): only the bf16-rounded gradient is written (same place, same pitch).
 constexpr int CE_THREADS = 1024;
+// The kernel's dynamic shared-memory limit is raised to this fixed maximum (once per device, at the first launch)
+// whatever the model's vocabulary, so that handles with different vocabularies can coexist in one process.
+constexpr int CE_MAX_SMEM = 200 * 1024;
 __global__ void __launch_bounds__(CE_THREADS) cross_entropy_pair_inplace_kernel(float* __restrict__ logits, int64_t ld, int V,
                                                                                 const int64_t* __restrict__ targets,
-                                                                                float* __restrict__ row_loss, float inv_rows, int write_lo) {
+                                                                                float* __restrict__ row_loss, float inv_rows, int write_lo,
+                                                                                unsigned int* __restrict__ bad) {
   extern __shared__ float srow[];
   __shared__ float red[32];
   const int64_t r = blockIdx.x;
@@ -147,7 +155,10 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_pair_inplace_kernel(
   float s = 0.0f;
   for (int i = threadIdx.x; i < V; i += CE_THREADS) { float e = expf(srow[i] - m); srow[i] = e; s += e; }
   const float tot = block_sum(s, red);
-  if (threadIdx.x == 0) row_loss[r] = (tg >= 0 && tg < V) ? m + logf(tot) - tlogit : 0.0f;
+  if (threadIdx.x == 0) {
+    row_loss[r] = (tg >= 0 && tg < V) ? m + logf(tot) - tlogit : 0.0f;
+    if (tg < 0 || tg >= V) atomicOr(bad, 2u);
+  }
   const float inv = 1.0f / tot;
   uint16_t* hi = reinterpret_cast<uint16_t*>(row);
   uint16_t* lo = hi + ld;
@@ -174,7 +185,7 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_pair_inplace_kernel(
   }
 }
 
-// ---- BASELINE config 3 wiring: mean-pool groups of GROUP tokens down, repeat up with a one-group causal shift.
+// ---- two-level wiring: mean-pool groups of GROUP tokens down, repeat up with a one-group causal shift.
 // Storage type T is float or bf16 bits (uint16_t); arithmetic in fp32.
 template <class T> __device__ __forceinline__ float ld_act(const T* p);
 template <> __device__ __forceinline__ float ld_act<float>(const float* p) { return *p; }
@@ -269,6 +280,7 @@ struct pmb_lm {
   int ce_inplace = 0;         // the logits row fits in shared memory: the gradient pair overwrites the logits tile
   uint16_t *params_hi = nullptr, *params_lo = nullptr, *dlog_hi = nullptr, *dlog_lo = nullptr, *hid_hi = nullptr, *hid_lo = nullptr;
   float* dh_part = nullptr;   // HEAD_SPLITK partial products of dhidden = dlogits E (few tiles, very long K)
+  uint16_t* l1_pair = nullptr; // two-level fp32 model: (hi, lo) pairs of `pooled` and `dh1`, 4 x (M/group, D) bf16
   std::vector<Weights16> lw16;
   // hierarchical variant (L1 > 0): level 0 = layers [0,L0) at token rate, level 1 = layers [L0,L0+L1) at 1/group rate
   int L0 = 0, L1 = 0, group = 1;
@@ -311,7 +323,10 @@ static pmb_status lm_create_impl(const pmb_mamba2_config* cfg, int L0, int L1, i
   pmb_lm* lm = new pmb_lm();
   lm->cfg = *cfg; lm->d = d; lm->L = n_layers; lm->L0 = L0; lm->L1 = L1; lm->group = L1 > 0 ? group : 1;
   lm->V = vocab; lm->bf16 = bf16_storage ? 1 : 0;
-  if (L1 > 0) PMB_TRY(make_dims(cfg, batch, seqlen / group, &lm->d1));
+  if (L1 > 0) {
+    pmb_status s1 = make_dims(cfg, batch, seqlen / group, &lm->d1);
+    if (s1 != PMB_OK) { delete lm; return s1; }
+  }
   lm->Vp = (int)align_up((size_t)vocab, 64);
   int tile_cap = LM_TILE_ROWS;
   if (const char* e = getenv("PMB_LM_TILE_ROWS")) { int v = atoi(e); if (v >= 128) tile_cap = v; }
@@ -346,22 +361,16 @@ static pmb_status lm_create_impl(const pmb_mamba2_config* cfg, int L0, int L1, i
   if (lm->pairs) {
     const size_t tv = (size_t)lm->tile_rows * lm->Vp * 2, td = (size_t)lm->tile_rows * d.D * 2;
     ok = ok && alloc((void**)&lm->params_hi, (size_t)o * 2) && alloc((void**)&lm->params_lo, (size_t)o * 2);
-    lm->ce_inplace = ((size_t)vocab * 4 <= (size_t)200 * 1024) ? 1 : 0;
-    if (lm->ce_inplace)
-      ok = ok && cudaFuncSetAttribute(cross_entropy_pair_inplace_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, vocab * 4) == cudaSuccess;
-    else
-      ok = ok && alloc((void**)&lm->dlog_hi, tv) && alloc((void**)&lm->dlog_lo, tv);
+    lm->ce_inplace = ((size_t)vocab * 4 <= (size_t)CE_MAX_SMEM) ? 1 : 0;
+    if (!lm->ce_inplace) ok = ok && alloc((void**)&lm->dlog_hi, tv) && alloc((void**)&lm->dlog_lo, tv);
     ok = ok && alloc((void**)&lm->hid_hi, td) && alloc((void**)&lm->hid_lo, td);
     ok = ok && alloc((void**)&lm->dh_part, (size_t)HEAD_SPLITK * lm->tile_rows * d.D * 4);
     pair_bytes = (lm->ce_inplace ? 0 : 2 * tv) + 2 * td + (size_t)HEAD_SPLITK * lm->tile_rows * d.D * 4;
   }
   if (lm->bf16) {
     ok = ok && alloc((void**)&lm->params16, (size_t)o * 2);
-    lm->ce_inplace = ((size_t)vocab * 4 <= (size_t)200 * 1024) ? 1 : 0;
-    if (lm->ce_inplace)
-      ok = ok && cudaFuncSetAttribute(cross_entropy_pair_inplace_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, vocab * 4) == cudaSuccess;
-    else
-      ok = ok && alloc((void**)&lm->dlogits16, (size_t)lm->tile_rows * lm->Vp * 2);
+    lm->ce_inplace = ((size_t)vocab * 4 <= (size_t)CE_MAX_SMEM) ? 1 : 0;
+    if (!lm->ce_inplace) ok = ok && alloc((void**)&lm->dlogits16, (size_t)lm->tile_rows * lm->Vp * 2);
   }
   if (L1 > 0) {
     ok = ok && alloc(&lm->saved1, slot1 * (L1 + 1));
@@ -369,6 +378,7 @@ static pmb_status lm_create_impl(const pmb_mamba2_config* cfg, int L0, int L1, i
     ok = ok && alloc(&lm->dpool, slot1);
     ok = ok && alloc(&lm->dh1, slot1);
     ok = ok && alloc(&lm->hsum, slot);
+    if (lm->pairs) ok = ok && alloc((void**)&lm->l1_pair, (size_t)4 * lm->d1.M * d.D * 2);
   }
   if (!ok) {
     pmb_status s = fail(PMB_ERR_CUDA, "lm_create: cudaMalloc failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -415,7 +425,7 @@ extern "C" void pmb_lm_destroy(pmb_lm* lm) {
   cudaFree(lm->params); cudaFree(lm->grads); cudaFree(lm->saved); cudaFree(lm->dhidden); cudaFree(lm->logits);
   cudaFree(lm->row_loss); cudaFree(lm->loss); cudaFree(lm->bad); cudaFree(lm->ids); cudaFree(lm->targets); cudaFree(lm->ws); cudaFree(lm->params16); cudaFree(lm->dlogits16);
   cudaFree(lm->params_hi); cudaFree(lm->params_lo); cudaFree(lm->dlog_hi); cudaFree(lm->dlog_lo); cudaFree(lm->hid_hi); cudaFree(lm->hid_lo); cudaFree(lm->dh_part);
-  cudaFree(lm->saved1); cudaFree(lm->pooled); cudaFree(lm->dpool); cudaFree(lm->dh1); cudaFree(lm->hsum);
+  cudaFree(lm->l1_pair); cudaFree(lm->saved1); cudaFree(lm->pooled); cudaFree(lm->dpool); cudaFree(lm->dh1); cudaFree(lm->hsum);
   delete lm;
 }
 
@@ -440,6 +450,17 @@ extern "C" void pmb_lm_activation_detail(const pmb_lm* lm, int64_t* h_out3) {
 }
 extern "C" const float* pmb_lm_loss_device(const pmb_lm* lm) { return lm ? lm->loss : nullptr; }
 
+extern "C" pmb_status pmb_lm_bad_tokens(pmb_lm* lm, void* stream, int32_t* h_flags_out) {
+  if (!lm || !h_flags_out) return fail(PMB_ERR_ARG, "lm_bad_tokens: NULL argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned int bad = 0;
+  PMB_CUDA(cudaMemcpyAsync(&bad, lm->bad, sizeof(bad), cudaMemcpyDeviceToHost, st));
+  PMB_CUDA(cudaStreamSynchronize(st));
+  if (bad) PMB_CUDA(cudaMemsetAsync(lm->bad, 0, sizeof(bad), st));
+  *h_flags_out = (int32_t)bad;
+  return PMB_OK;
+}
+
 // hier_kernel launcher on the model's storage dtype
 static pmb_status hier_op(pmb_lm* lm, cudaStream_t st, const void* in, const void* a, void* out, int mode) {
   const Dims& d = lm->d;
@@ -457,6 +478,18 @@ static pmb_status lm_gemm(pmb_lm* lm, cudaStream_t st, int ta, int tb, int64_t M
                           const void* B16_or_f32, int64_t ldb, void* C, int64_t ldc, int out_storage) {
   if (lm->bf16) return gemm_bf16(st, ta, tb, M, N, K, A, lda, B16_or_f32, ldb, C, ldc, nullptr, out_storage);
   return gemm(st, ta, tb, M, N, K, (const float*)A, lda, (const float*)B16_or_f32, ldb, (float*)C, ldc, nullptr, 0);
+}
+
+// (hi, lo) pair of a level-1 activation (M/group, D) in the handle's own buffer (slot 0: pooled, slot 1: dh1), so that
+// the two-level fp32 model never touches the library-wide GEMM scratch: a captured step keeps valid addresses
+// whatever other GEMM calls the process makes later.
+static pmb_status l1_split(pmb_lm* lm, cudaStream_t st, const void* src, int slot, Pair16* out) {
+  const int64_t M1 = lm->d1.M; const int D = lm->d.D;
+  uint16_t* hi = lm->l1_pair + (size_t)(2 * slot) * M1 * D;
+  uint16_t* lo = hi + (size_t)M1 * D;
+  PMB_TRY(split_pair16(st, static_cast<const float*>(src), M1, D, D, hi, lo, D));
+  *out = Pair16{hi, lo, D};
+  return PMB_OK;
 }
 
 extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t* d_ids, const int64_t* d_targets,
@@ -496,7 +529,14 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
     const int64_t M1 = lm->d1.M;
     wproj = h16 ? (const void*)(lm->params16 + lm->off_proj) : (const void*)(lm->params + lm->off_proj);
     PMB_TRY(hier_op(lm, st, hidden, nullptr, lm->pooled, 0));
-    PMB_TRY(lm_gemm(lm, st, 0, 0, M1, D, D, lm->pooled, D, wproj, D, lm->saved1, D, 1));
+    if (prs) {
+      Pair16 pooled_p;
+      PMB_TRY(l1_split(lm, st, lm->pooled, 0, &pooled_p));
+      PMB_TRY(gemm_pairs(st, 0, 0, M1, D, D, pooled_p, Pair16{lm->params_hi + lm->off_proj, lm->params_lo + lm->off_proj, D},
+                         static_cast<float*>(lm->saved1), D, nullptr));
+    } else {
+      PMB_TRY(lm_gemm(lm, st, 0, 0, M1, D, D, lm->pooled, D, wproj, D, lm->saved1, D, 1));
+    }
     PMB_TRY(stack_fwd(st, lm->d1, L1, lm->lp.data() + L0, w16 ? w16 + L0 : nullptr, lm->saved1, lm->ws, lm->ws_bytes));
     const char* h1 = reinterpret_cast<const char*>(lm->saved1) + (size_t)L1 * M1 * D * esz;
     PMB_TRY(hier_op(lm, st, h1, hidden, lm->hsum, 1));
@@ -522,11 +562,12 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
     }
     else PMB_TRY(gemm(st, 0, 1, rows, V, D, static_cast<const float*>(hrows), D, table, D, lm->logits, Vp, nullptr, 0));
     { ProfScope prof(st, "cross_entropy", 0.0, 4.0 * rows * 3.0 * V);
-    if ((prs || h16) && lm->ce_inplace)
-      cross_entropy_pair_inplace_kernel<<<(unsigned)rows, CE_THREADS, (size_t)V * 4, st>>>(lm->logits, Vp, V, d_targets + r0, lm->row_loss + r0, 1.0f / (float)M, prs ? 1 : 0);
-    else
+    if ((prs || h16) && lm->ce_inplace) {
+      PMB_SMEM_OPT_IN(CE_MAX_SMEM, cross_entropy_pair_inplace_kernel);
+      cross_entropy_pair_inplace_kernel<<<(unsigned)rows, CE_THREADS, (size_t)V * 4, st>>>(lm->logits, Vp, V, d_targets + r0, lm->row_loss + r0, 1.0f / (float)M, prs ? 1 : 0, lm->bad);
+    } else
       cross_entropy_kernel<<<(unsigned)rows, 256, 0, st>>>(lm->logits, Vp, V, d_targets + r0, lm->row_loss + r0, 1.0f / (float)M,
-                                                           prs ? lm->dlog_hi : nullptr, prs ? lm->dlog_lo : nullptr);
+                                                           prs ? lm->dlog_hi : nullptr, prs ? lm->dlog_lo : nullptr, lm->bad);
     PMB_LAUNCHED(); }
     // dhidden = dlogits E ;  dE (+)= dlogits^T hidden
     if (h16) {
@@ -582,6 +623,13 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
     if (h16) {
       PMB_TRY(gemm_bf16(st, 1, 0, D, D, M1, lm->pooled, D, lm->dh1, D, dproj, D, nullptr, 0));
       PMB_TRY(gemm_bf16(st, 0, 1, M1, D, D, lm->dh1, D, wproj, D, lm->dpool, D, nullptr, 1));
+    } else if (prs) {
+      Pair16 pooled_p, dh1_p;
+      PMB_TRY(l1_split(lm, st, lm->pooled, 0, &pooled_p));
+      PMB_TRY(l1_split(lm, st, lm->dh1, 1, &dh1_p));
+      PMB_TRY(gemm_pairs(st, 1, 0, D, D, M1, pooled_p, dh1_p, dproj, D, nullptr));
+      PMB_TRY(gemm_pairs(st, 0, 1, M1, D, D, dh1_p, Pair16{lm->params_hi + lm->off_proj, lm->params_lo + lm->off_proj, D},
+                         static_cast<float*>(lm->dpool), D, nullptr));
     } else {
       PMB_TRY(gemm(st, 1, 0, D, D, M1, (const float*)lm->pooled, D, (const float*)lm->dh1, D, dproj, D, nullptr, 0));
       PMB_TRY(gemm(st, 0, 1, M1, D, D, (const float*)lm->dh1, D, (const float*)wproj, D, (float*)lm->dpool, D, nullptr, 0));
@@ -658,7 +706,7 @@ extern "C" pmb_status pmb_lm_step_host(pmb_lm* lm, void* stream, const int64_t* 
   PMB_CUDA(cudaMemcpy(&bad, lm->bad, sizeof(bad), cudaMemcpyDeviceToHost));
   if (bad) {
     cudaMemset(lm->bad, 0, sizeof(bad));
-    return fail(PMB_ERR_ARG, "lm_step_host: a token id was outside [0, vocab)");
+    return fail(PMB_ERR_ARG, "lm_step_host: %s outside [0, vocab)", (bad & 1u) ? ((bad & 2u) ? "token ids and targets were" : "a token id was") : "a target was");
   }
   return PMB_OK;
 }

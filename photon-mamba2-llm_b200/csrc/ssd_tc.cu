@@ -5,6 +5,7 @@
 // Shapes taken here: block_len % 64 == 0, d_state % 32 == 0, d_head % 64 == 0 (the production shapes);
 // other shapes run on the fp32 FMA tile engine of ssd.cu.
 #include <unordered_map>
+#include <mutex>
 #include <cstdlib>
 #include "common.cuh"
 #include "kernels.h"
@@ -369,11 +370,13 @@ struct MapKeyHash {
     return h;
   }
 };
-std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;   // shared by all devices and host threads
+std::mutex g_maps_mu;
 
 // rank-3 map: dims (d0 contiguous, d1 rows with pitch s0 floats, d2 with pitch s1 floats), box (b0, b1, 1)
 pmb_status get_map(CUtensorMap* out, const float* base, int64_t d0, int64_t d1, int64_t d2, int64_t s0, int64_t s1, int b0, int b1, bool mn) {
   MapKey key{base, d0, d1, d2, s0, s1, b0, b1, mn};
+  std::lock_guard<std::mutex> lock(g_maps_mu);
   auto it = g_maps.find(key);
   if (it == g_maps.end()) {
     if (g_maps.size() > 4096) g_maps.clear();
@@ -410,6 +413,23 @@ unsigned int* status_ptr() {
 }
 
 }  // namespace
+
+// Self-test of the bounded-wait path every tcgen05 kernel of this library relies on: one thread waits on an
+// mbarrier that nothing ever arms, gives up after `polls` polls, raises bit 128 of the scan's device status word
+// and returns.  No copy, no tensor-memory allocation and no other thread is involved, so the launch ends by itself.
+__global__ void bounded_wait_selftest_kernel(unsigned int* __restrict__ status, uint32_t polls) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t b = tcx::smem_u32(&bar);
+  tcx::mbar_init(b, 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  if (!tcx::mbar_wait(b, 0, polls)) atomicOr(status, 128u);
+}
+
+pmb_status bounded_wait_selftest(cudaStream_t st, uint32_t polls) {
+  bounded_wait_selftest_kernel<<<1, 1, 0, st>>>(status_ptr(), polls);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
 
 bool ssd_tc_supported(const SsdIn& in) {
   static const bool off = [] { const char* e = getenv("PMB_SSD_ENGINE"); return e && strcmp(e, "simt") == 0; }();

@@ -357,11 +357,7 @@ template <class Op>
 // heavy_m: +1 = the last m tile of a batch entry has the most k-steps, -1 = the first one, 0 = all alike
 static pmb_status launch(cudaStream_t st, const MapSet& maps, const Op& op, int batches, unsigned int* status, int heavy_m = 0) {
   using G = Geometry<Op::BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    PMB_CUDA(cudaFuncSetAttribute(tc_bgemm_kernel<Op>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BASE + Op::AUX_FLOATS * 4));
-    attr_set = true;
-  }
+  PMB_SMEM_OPT_IN(G::SMEM_BASE + Op::AUX_FLOATS * 4, tc_bgemm_kernel<Op>);
   const unsigned mtiles = (unsigned)cdiv(op.Mdim, BM);
   const int mode = (heavy_m == 0 || batches > 65535 || mtiles < 2) ? 0 : (heavy_m > 0 ? 2 : 1);
   dim3 grid((unsigned)cdiv(op.Ndim, Op::BN), mode ? (unsigned)batches : mtiles, mode ? mtiles : (unsigned)batches);

@@ -107,6 +107,9 @@ def _load():
         "pmb_lm_step_device": (i32, [vp, vp, vp, vp, LAYER_CALLBACK, vp]),
         "pmb_lm_loss_device": (vp, [vp]),
         "pmb_lm_step_host": (i32, [vp, vp, vp, vp, C.POINTER(f32), LAYER_CALLBACK, vp]),
+        "pmb_lm_bad_tokens": (i32, [vp, vp, C.POINTER(i32)]),
+        "pmb_selftest_bounded_wait": (i32, [vp, C.c_uint32]),
+        "pmb_selftest_device_once": (i32, []),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)   # AttributeError here = the library does not export a declared symbol
@@ -191,6 +194,39 @@ class Mamba2Config:
         return {"in_proj_weight": (self.d_model, self.in_proj_dim), "conv1d_weight": (self.xbc_dim, 1, self.d_conv),
                 "conv1d_bias": (self.xbc_dim,), "a_log": (self.n_heads,), "d_skip": (self.n_heads,),
                 "dt_bias": (self.n_heads,), "norm_weight": (self.d_inner,), "out_proj_weight": (self.d_inner, self.d_model)}
+
+
+def init_block_params(config: Mamba2Config, seed: int) -> dict:
+    """Random-init block parameters (CPU float32 tensors) with the distributions the benchmark configurations
+    name: projection and conv weights uniform in +-1/sqrt(fan_in) (fan_in = d_model, d_inner, d_conv),
+    conv bias 0, A = -exp(U[log 1, log 16]) (so a_log = U[0, log 16]), dt_bias = softplus^-1(U[1e-3, 1e-1]),
+    D = 1, norm weight 1.  One torch.Generator per tensor, seeded from `seed`."""
+    import math
+    sh = config.param_shapes()
+
+    def gen(k):
+        g = torch.Generator(); g.manual_seed(seed * 1000003 + k)
+        return g
+
+    def uni(shape, bound, k):
+        return (torch.rand(shape, generator=gen(k)) * 2 - 1) * bound
+
+    dt = torch.rand(sh["dt_bias"], generator=gen(5)) * (1e-1 - 1e-3) + 1e-3
+    return {
+        "in_proj_weight": uni(sh["in_proj_weight"], 1 / math.sqrt(config.d_model), 0),
+        "conv1d_weight": uni(sh["conv1d_weight"], 1 / math.sqrt(config.d_conv), 1),
+        "conv1d_bias": torch.zeros(sh["conv1d_bias"]),
+        "a_log": torch.rand(sh["a_log"], generator=gen(3)) * math.log(16.0),
+        "d_skip": torch.ones(sh["d_skip"]),
+        "dt_bias": dt + torch.log(-torch.expm1(-dt)),          # softplus^-1(dt)
+        "norm_weight": torch.ones(sh["norm_weight"]),
+        "out_proj_weight": uni(sh["out_proj_weight"], 1 / math.sqrt(config.d_inner), 7),
+    }
+
+
+def selftest_bounded_wait(polls: int = 4096):
+    """Launches the library's one-thread bounded-wait self-test on the current stream."""
+    _check(lib.pmb_selftest_bounded_wait(_stream(), polls))
 
 
 def _params_struct(p: dict) -> _Params:
@@ -573,11 +609,27 @@ class FlatMamba:
 
         Returns a callable `step(ids, targets) -> loss` (0-d device tensor): it copies the int64 token tensors
         (device, or pinned host for an asynchronous copy) into the graph's static input buffers and replays the
-        graph, so the ~1200 launches of a step cost one launch.  `on_layer_done` / `after` (e.g. the enqueue and
-        the final wait of the per-layer gradient all-reduce) are called while capturing and become part of the
-        graph.  Two warm-up steps run first on a side stream: the library creates its internal streams, events and
-        scratch on first use, which a capture must not contain."""
+        graph, so the ~1000 launches of a step cost one launch.  The graph holds this rank's compute only.
+        `on_layer_done` / `after` are called while capturing; whatever they enqueue on the capturing stream becomes
+        part of the graph.  They must not issue collectives: asynchronous NCCL work enqueued from these callbacks
+        on another stream, with its `Work.wait()` and the process group's watchdog polling events of a stream that is
+        still capturing, did not finish when it was tried, so with an initialised process group of more than one
+        rank a callback is refused here.  Average the gradients after the replay instead (see `bench.py`).
+        Two warm-up steps run first on a side stream: the library creates its internal streams, events and scratch
+        on first use, which a capture must not contain."""
+        if on_layer_done is not None or after is not None:
+            import torch.distributed as dist
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                raise PmbError(2, "capture_step: callbacks are refused while a process group with more than one rank is "
+                                  "initialised (collectives inside the capture are not supported); all-reduce after the replay")
         return _GraphStep(self, on_layer_done, after)
+
+    def bad_tokens(self) -> int:
+        """Reads and clears the flag word for out-of-range input (bit 0: a token id, bit 1: a target); the step
+        entry points other than `step_host` do not check it themselves."""
+        w = C.c_int32(0)
+        _check(lib.pmb_lm_bad_tokens(self._h, _stream(), C.byref(w)))
+        return w.value
 
     def step_host(self, ids_host, targets_host, on_layer_done=None):
         """ids/targets: int64 CPU tensors (pinned for an asynchronous copy).  Returns the loss as a float."""

@@ -1,4 +1,4 @@
-"""Regenerates the golden vectors under tests/golden/ (run in the build container only).
+"""Regenerates the golden vectors under tests/golden/ (needs a checkout of the reference repository).
 
 1. ssd_q64.npz: the reference's own SSD fixture (reference/fixtures/ssd_q64: B=1, T=128,
    H=2, P=8, N=16, Q=64, seed 42).  The inputs are re-drawn exactly as
@@ -8,7 +8,7 @@
 2. block_c1.npz: the oracle's output and gradients for the single-block fp32 case
    (B=2, T=128, D=128, H=8, P=32, N=16, Q=64) so a drift of the oracle itself is caught.
 
-Usage: python tests/golden/make_golden.py [--reference /path/to/reference]
+Usage: python tests/golden/make_golden.py --reference /path/to/reference-checkout
 """
 import argparse
 import pathlib
@@ -23,7 +23,7 @@ sys.path.insert(0, str(HERE.parent.parent))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference repository")
     args = ap.parse_args()
     ref = pathlib.Path(args.reference)
     sys.path.insert(0, str(ref / "reference"))

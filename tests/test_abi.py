@@ -57,3 +57,9 @@ def test_null_arguments_are_errors_not_crashes(pm):
     assert st == 6
     st = pm.lib.pmb_gemm_f32(None, 0, 0, 0, 4, 4, None, 4, None, 4, None, 4, None, 0)
     assert st == 1
+
+
+def test_per_device_once_table():
+    """The "set once per device" flags behind cudaFuncSetAttribute are per device ordinal (host logic, no GPU)."""
+    import pm_b200
+    assert pm_b200.lib.pmb_selftest_device_once() == 0

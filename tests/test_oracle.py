@@ -163,3 +163,24 @@ def test_adamw_restatement_matches_torch_adamw():
     assert (p[0] - p_ref.detach()).abs().max() < 1e-6
     g = [torch.full((4,), 3.0)]
     assert abs(orc.clip_grad_norm(g, 1.0) - 6.0) < 1e-6 and abs(float(g[0].norm()) - 1.0) < 1e-6
+
+
+def test_elementwise_metric_noise_floor_of_fp32():
+    """Under the element-wise metric |d| / max(|ref|, 1e-3 max|ref|) the fp32 oracle is already above 1e-4 from its
+    own fp64 run (different rounding of the same graph), while it is below 5e-6 in the max-norm metric: the
+    element-wise bar of the GPU tests (util.ELEM_TOL) cannot be 1e-4 for any fp32 implementation."""
+    from util import block_params, elem_err, rel_err
+    cfg = orc.Mamba2Config(d_model=128, d_state=16, d_head=32, n_heads=8, block_len=64)
+    p = block_params(cfg, seed=3)
+    g = torch.Generator(); g.manual_seed(21)
+    x = torch.randn(2, 128, 128, generator=g); cot = torch.randn(2, 128, 128, generator=g)
+    outs = {}
+    for dt in (torch.float32, torch.float64):
+        pr = {k: v.to(dt).clone().requires_grad_(True) for k, v in p.items()}
+        xr = x.to(dt).clone().requires_grad_(True)
+        out = orc.block_forward(pr, cfg, xr)
+        (out * cot.to(dt)).sum().backward()
+        outs[dt] = {"out": out.detach(), "dx": xr.grad, "d_in_proj_weight": pr["in_proj_weight"].grad}
+    for k in outs[torch.float32]:
+        assert rel_err(outs[torch.float32][k], outs[torch.float64][k]) < 5e-6, k
+        assert elem_err(outs[torch.float32][k], outs[torch.float64][k]) > 1e-4, k
