@@ -5,6 +5,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "ssd_tc.h"
+#include "ssd_fused.h"
 
 namespace pmb {
 
@@ -136,6 +137,8 @@ extern "C" pmb_status pmb_device_status(int32_t* h_word_out) {
   w |= w2 << 16;
   PMB_TRY(read_clear_device_status_small(&w2));
   w |= w2 << 24;
+  PMB_TRY(read_clear_device_status_fused(&w2));   // shares the scan kernels' byte
+  w |= (w2 & 0x7fu) << 8;
   if (h_word_out) *h_word_out = (int32_t)w;
   return PMB_OK;
 }

@@ -579,6 +579,27 @@ pmb_status split_pair16(cudaStream_t st, const float* src, int64_t rows, int64_t
   return PMB_OK;
 }
 
+// Columns [0, cols) of each row only (cols a multiple of 4); the rest of the destination pitch is left alone, so two
+// sources can share one pair buffer side by side.
+__global__ void split_pair16_cols_kernel(const float* __restrict__ src, int64_t rows, int64_t cols, int64_t ld,
+                                         uint16_t* __restrict__ hi, uint16_t* __restrict__ lo, int64_t ld16) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t c4 = cols / 4;
+  if (i >= rows * c4) return;
+  const int64_t r = i / c4, c = (i % c4) * 4;
+  const float* s = src + r * ld + c;
+  store_pair4(hi + r * ld16 + c, lo + r * ld16 + c, s[0], s[1], s[2], s[3]);
+}
+
+pmb_status split_pair16_strided(cudaStream_t st, const float* src, int64_t rows, int64_t cols, int64_t ld, uint16_t* hi, uint16_t* lo,
+                                int64_t ld16) {
+  if ((cols & 3) || (ld16 & 3) || ld16 < cols || ((reinterpret_cast<uintptr_t>(hi) | reinterpret_cast<uintptr_t>(lo)) & 7))
+    return fail(PMB_ERR_ARG, "split_pair16_strided: column count and pitch must be multiples of 4, destinations 8-byte aligned");
+  split_pair16_cols_kernel<<<(unsigned)cdiv(rows * (cols / 4), 256), 256, 0, st>>>(src, rows, cols, ld, hi, lo, ld16);
+  PMB_LAUNCHED();
+  return PMB_OK;
+}
+
 bool gemm_pairs_enabled() {
   static const int on = [] { const char* e = getenv("PMB_GEMM_ENGINE"); return (e && (strcmp(e, "tf32") == 0 || strcmp(e, "simt") == 0)) ? 0 : 1; }();
   return on != 0;

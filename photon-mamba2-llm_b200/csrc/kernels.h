@@ -66,6 +66,15 @@ struct SsdWs {            // persistent between fwd and bwd of one scan
   float* splitk;          // split-K partial tiles of the per-group backward contractions
   float* xs;              // (B,T,H,P) x * dt * exp(S_end - S_t)   (tensor-core path only)
   float* dys;             // (B,T,H,P) dY * exp(S_t)               (tensor-core path only)
+  // (hi, lo) bf16 pairs of the fused intra-chunk kernels' operands (shapes those kernels take only)
+  uint16_t *xt_hi, *xt_lo;   // (B,T,H,P)  x~ = x * dt
+  uint16_t *bc_hi, *bc_lo;   // (B,T,2*G*N) B | C
+  uint16_t *dy_hi, *dy_lo;   // (B,T,H,P)  dY
+  uint16_t *hp_hi, *hp_lo;   // (B,nc,H,N,P) state entering each chunk
+  uint16_t *dh_hi, *dh_lo;   // (B,nc,H,N,P) adjoint of the state leaving each chunk
+  float* yoff;               // (B,T,H,P) exp(S_t) C_t h_prev: the carried-state part of y (forward -> backward)
+  float *csum, *esum;        // (B,T,H)   column sums of W and the dh term of dS (fused backward)
+  float* rpart;              // (B,nc,H,Q/128,Q) partial row sums of W (fused backward)
 };
 size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base, size_t bytes, SsdWs* out);
 pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, float* y, int64_t ldy,
@@ -107,6 +116,9 @@ pmb_status read_clear_device_status_bf16(unsigned int* word);
 struct Pair16 { const uint16_t* hi; const uint16_t* lo; int64_t ld; };
 pmb_status split_pair16(cudaStream_t st, const float* src, int64_t rows, int64_t cols, int64_t ld, uint16_t* hi, uint16_t* lo,
                         int64_t ld16);
+// same, but writes only columns [0, cols) of each destination row and leaves the rest of the pitch untouched
+pmb_status split_pair16_strided(cudaStream_t st, const float* src, int64_t rows, int64_t cols, int64_t ld, uint16_t* hi, uint16_t* lo,
+                                int64_t ld16);
 // tile_mode: -1 = chosen by tile count, 0 = 128x128 single-CTA tiles, 1 = 256x128 / 2 = 256x256 CTA-pair tiles
 pmb_status gemm_pairs(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const Pair16& A, const Pair16& B,
                       float* C, int64_t ldc, const float* R, int tile_mode = -1);

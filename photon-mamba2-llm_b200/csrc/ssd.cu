@@ -20,6 +20,7 @@
 #include "kernels.h"
 #include "bgemm.cuh"
 #include "ssd_tc.h"
+#include "ssd_fused.h"
 
 namespace pmb {
 
@@ -360,7 +361,8 @@ __global__ void chunk_cumsum_kernel(SsdP p, CumsumRaw raw) {
 // here when raw inputs are given), then xs[t,:] = x[t,:] * dt_t * exp(S_end - S_t), the operand that the chunk-state
 // and dB contractions share.  S and dt of the chunk stay in shared memory between the two phases.
 constexpr int PREP_THREADS = 256, PREP_MAX_Q = 1024;
-__global__ void __launch_bounds__(PREP_THREADS) chunk_prepare_kernel(SsdP p, CumsumRaw raw, float* __restrict__ xs) {
+__global__ void __launch_bounds__(PREP_THREADS) chunk_prepare_kernel(SsdP p, CumsumRaw raw, float* __restrict__ xs,
+                                                                     uint16_t* __restrict__ xt_hi, uint16_t* __restrict__ xt_lo) {
   __shared__ float sS[PREP_MAX_Q], sdt[PREP_MAX_Q], wsum[PREP_THREADS / 32];
   const int w = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int h = w % p.H, bc = w / p.H, cc = bc % p.nc, bb = bc / p.nc;
@@ -396,22 +398,26 @@ __global__ void __launch_bounds__(PREP_THREADS) chunk_prepare_kernel(SsdP p, Cum
   const int64_t tok0 = p.tok(bb, cc, 0);
   constexpr int U = 4;
   for (int i0 = tid; i0 < total; i0 += U * PREP_THREADS) {
-    float4 v[U]; float f[U]; int tt[U], jj[U];
+    float4 v[U]; float f[U], fd[U]; int tt[U], jj[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int i = i0 + u * PREP_THREADS;
       tt[u] = i / P4; jj[u] = i % P4;
       if (i < total) {
         v[u] = reinterpret_cast<const float4*>(p.x + (tok0 + tt[u]) * p.ldx + h * p.P)[jj[u]];
-        f[u] = __expf(send - sS[tt[u]]) * sdt[tt[u]];
+        fd[u] = sdt[tt[u]];
+        f[u] = __expf(send - sS[tt[u]]) * fd[u];
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int i = i0 + u * PREP_THREADS;
-      if (i < total)
-        reinterpret_cast<float4*>(xs + (tok0 + tt[u]) * (int64_t)(p.H * p.P) + h * p.P)[jj[u]] =
-            make_float4(v[u].x * f[u], v[u].y * f[u], v[u].z * f[u], v[u].w * f[u]);
+      if (i < total) {
+        const int64_t o = (tok0 + tt[u]) * (int64_t)(p.H * p.P) + h * p.P + 4 * jj[u];
+        *reinterpret_cast<float4*>(xs + o) = make_float4(v[u].x * f[u], v[u].y * f[u], v[u].z * f[u], v[u].w * f[u]);
+        // x~ = x dt as a bf16 pair: the V operand of the fused intra-chunk kernel
+        if (xt_hi) store_pair4(xt_hi + o, xt_lo + o, v[u].x * fd[u], v[u].y * fd[u], v[u].z * fd[u], v[u].w * fd[u]);
+      }
     }
   }
 }
@@ -424,7 +430,8 @@ __global__ void __launch_bounds__(PREP_THREADS) chunk_prepare_kernel(SsdP p, Cum
 // The chunk values are fetched four at a time before the dependent chain so the loads overlap.
 template <int VEC>
 __global__ void __launch_bounds__(256) state_scan_kernel(SsdP p, float* __restrict__ buf, const float* __restrict__ init,
-                                                         float* __restrict__ last, int reverse) {
+                                                         float* __restrict__ last, int reverse,
+                                                         uint16_t* __restrict__ pair_hi, uint16_t* __restrict__ pair_lo) {
   const int64_t NP = (int64_t)p.N * p.P;
   const int64_t per = NP / VEC;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -451,7 +458,11 @@ __global__ void __launch_bounds__(256) state_scan_kernel(SsdP p, float* __restri
       const int cc = reverse ? p.nc - 1 - (c0 + j) : c0 + j;
       if (c0 + j < p.nc) {
         float* slot = buf + (((int64_t)bb * p.nc + cc) * p.H + h) * NP + e;
-        if (VEC == 4) *reinterpret_cast<float4*>(slot) = make_float4(run[0], run[1 % VEC], run[2 % VEC], run[3 % VEC]);
+        if (VEC == 4) {
+          *reinterpret_cast<float4*>(slot) = make_float4(run[0], run[1 % VEC], run[2 % VEC], run[3 % VEC]);
+          // the same values as a bf16 pair: the state operand of the fused intra-chunk kernel
+          if (pair_hi) store_pair4(pair_hi + (slot - buf), pair_lo + (slot - buf), run[0], run[1 % VEC], run[2 % VEC], run[3 % VEC]);
+        }
         else slot[0] = run[0];
 #pragma unroll
         for (int v = 0; v < VEC; ++v) run[v] = fmaf(dec[j], run[v], tmp[j][v]);
@@ -465,25 +476,28 @@ __global__ void __launch_bounds__(256) state_scan_kernel(SsdP p, float* __restri
 }
 
 // dsend[b,c,h] = <dh[c], h_next[c]> with h_next[c] = h_prev[c+1], or the final state for the last chunk.
-__global__ void __launch_bounds__(256) state_dot_kernel(SsdP p, float* __restrict__ dsend) {
+// own_state != 0: <dh[c], h_prev[c]> instead (the fused backward adds the other part of <dh, h_next> from the very
+// values that enter dS, see chunk_rows_finish_w_kernel).
+__global__ void __launch_bounds__(256) state_dot_kernel(SsdP p, float* __restrict__ dsend, int own_state) {
   __shared__ float red[32];
   const int bch = blockIdx.x;
   const int h = bch % p.H; const int bc = bch / p.H; const int cc = bc % p.nc; const int bb = bc / p.nc;
   const int NP = p.N * p.P;
   const float* a = p.dh + (int64_t)bch * NP;
-  const float* b = (cc + 1 < p.nc) ? p.hprev + (((int64_t)bb * p.nc + cc + 1) * p.H + h) * NP : p.hlast + ((int64_t)bb * p.H + h) * NP;
+  const float* b = own_state ? p.hprev + (int64_t)bch * NP : (cc + 1 < p.nc) ? p.hprev + (((int64_t)bb * p.nc + cc + 1) * p.H + h) * NP : p.hlast + ((int64_t)bb * p.H + h) * NP;
   float dot = 0.0f;
   for (int e = threadIdx.x; e < NP; e += blockDim.x) dot = fmaf(a[e], b[e], dot);
   float tot = block_sum(dot, red);
   if (threadIdx.x == 0) dsend[bch] = tot;
 }
 
-static pmb_status launch_state_scan(cudaStream_t st, const SsdP& p, float* buf, const float* init, float* last, int reverse) {
+static pmb_status launch_state_scan(cudaStream_t st, const SsdP& p, float* buf, const float* init, float* last, int reverse,
+                                    uint16_t* pair_hi = nullptr, uint16_t* pair_lo = nullptr) {
   const int64_t NP = (int64_t)p.N * p.P;
   const bool vec = (p.P % 4 == 0);
   const int64_t n = (int64_t)p.B * p.H * (vec ? NP / 4 : NP);
-  if (vec) state_scan_kernel<4><<<(unsigned)cdiv(n, 256), 256, 0, st>>>(p, buf, init, last, reverse);
-  else state_scan_kernel<1><<<(unsigned)cdiv(n, 256), 256, 0, st>>>(p, buf, init, last, reverse);
+  if (vec) state_scan_kernel<4><<<(unsigned)cdiv(n, 256), 256, 0, st>>>(p, buf, init, last, reverse, pair_hi, pair_lo);
+  else state_scan_kernel<1><<<(unsigned)cdiv(n, 256), 256, 0, st>>>(p, buf, init, last, reverse, nullptr, nullptr);
   PMB_LAUNCHED();
   return PMB_OK;
 }
@@ -653,6 +667,99 @@ __global__ void __launch_bounds__(PREP_THREADS) chunk_rows_finish_kernel(SsdP p,
   }
 }
 
+// Row sums and the reverse cumulative sum for the fused backward, one 256-thread block per (b,c,h).
+// The gradient w.r.t. the in-chunk cumulative sum S is assembled from terms that were each formed once:
+//   dS_t = r_t - c_t + f_t - e_t,      dS_{Q-1} += sum_s e_s + exp(S_end) <dh, h_prev>
+//   r_t = sum_{s<t} W[t,s], c_t = sum_{u>t} W[u,t]   (W = dM o G o L, both sums from the same registers of the fused kernel)
+//   f_t = <dY_t, exp(S_t) C_t h_prev>                 (the carried-state part of y, kept by the forward kernel)
+//   e_s = exp(S_end - S_s) <x~_s, B_s dh>             (from the fused kernel's epilogue)
+// so the cancellation inside sum_t S_t dS_t (the gradient of A) is between identically rounded numbers and never
+// goes through y - D x or through two separately rounded matrix products.  da = reverse cumsum(dS);
+// ddt = <dx~, x> + A da;  dx = dx~ dt + D dY;  per-chunk partials of dA and dD.
+struct WSums { const float* rpart; const float* csum; const float* esum; const float* yoff; int nb; };
+__global__ void __launch_bounds__(PREP_THREADS) chunk_rows_finish_w_kernel(SsdP p, WSums ws, float* __restrict__ dx, int64_t lddx,
+                                                                           const float* __restrict__ dd, float* __restrict__ da_out,
+                                                                           float* __restrict__ ddt_out, float* __restrict__ part) {
+  __shared__ float s_ddtx[PREP_MAX_Q], s_dS[PREP_MAX_Q], s_dD[PREP_MAX_Q], s_dt[PREP_MAX_Q], s_e[PREP_MAX_Q], wsum[PREP_THREADS / 32], red[32];
+  const int w = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const int h = w % p.H, bc = w / p.H, cc = bc % p.nc, bb = bc / p.nc;
+  const float Dv = p.D ? p.D[h] : 0.0f;
+  const int64_t tok0 = p.tok(bb, cc, 0);
+  const int P4 = p.P >> 2;
+  const int sub = lane >> 4, l16 = lane & 15;
+  for (int t0 = wid * 2; t0 < p.Q; t0 += (PREP_THREADS / 32) * 2) {
+    const int t = t0 + sub;
+    float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f, dtv = 1.0f;
+    if (t < p.Q) {
+      const int64_t tk = tok0 + t;
+      dtv = p.dtv(tk, h);
+      for (int j = l16; j < P4; j += 16) {
+        const float4 xv = reinterpret_cast<const float4*>(p.x + tk * p.ldx + h * p.P)[j];
+        const float4 dxt = reinterpret_cast<const float4*>(p.dxt + tk * (int64_t)(p.H * p.P) + h * p.P)[j];
+        const float4 dyv = reinterpret_cast<const float4*>(p.dy + tk * p.lddy + h * p.P)[j];
+        const float4 yo = reinterpret_cast<const float4*>(ws.yoff + tk * (int64_t)(p.H * p.P) + h * p.P)[j];
+        s1 = fmaf(dxt.x, xv.x, fmaf(dxt.y, xv.y, fmaf(dxt.z, xv.z, fmaf(dxt.w, xv.w, s1))));
+        s2 = fmaf(dyv.x, yo.x, fmaf(dyv.y, yo.y, fmaf(dyv.z, yo.z, fmaf(dyv.w, yo.w, s2))));
+        s3 = fmaf(dyv.x, xv.x, fmaf(dyv.y, xv.y, fmaf(dyv.z, xv.z, fmaf(dyv.w, xv.w, s3))));
+        reinterpret_cast<float4*>(dx + tk * lddx + h * p.P)[j] =
+            make_float4(fmaf(dxt.x, dtv, Dv * dyv.x), fmaf(dxt.y, dtv, Dv * dyv.y), fmaf(dxt.z, dtv, Dv * dyv.z), fmaf(dxt.w, dtv, Dv * dyv.w));
+      }
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) {
+      s1 += __shfl_xor_sync(0xffffffffu, s1, o); s2 += __shfl_xor_sync(0xffffffffu, s2, o); s3 += __shfl_xor_sync(0xffffffffu, s3, o);
+    }
+    if (t < p.Q && l16 == 0) {
+      const int64_t idx = (tok0 + t) * p.H + h;
+      float r = 0.0f;
+      for (int rb = 0; rb <= t / 128; ++rb) r += ws.rpart[((int64_t)w * ws.nb + rb) * p.Q + t];   // row blocks whose rows s can be < t
+      const float e = ws.esum[idx];
+      s_ddtx[t] = s1; s_dD[t] = s3; s_dt[t] = dtv; s_e[t] = e;
+      s_dS[t] = ((r - ws.csum[idx]) + s2) - e;
+    }
+  }
+  __syncthreads();
+  // sum of e over the chunk in a fixed order, then the terms that belong to the last position
+  float ep = 0.0f;
+  for (int q = tid; q < p.Q; q += PREP_THREADS) ep += s_e[q];
+  const float esum = block_sum(ep, red);
+  if (tid == 0) {
+    const float send = p.S[((int64_t)bb * p.H + h) * p.T + (int64_t)cc * p.Q + p.Q - 1];
+    s_dS[p.Q - 1] += esum + expf(send) * dd[w];
+  }
+  __syncthreads();
+  const float Ah = p.dt ? p.A[h] : 0.0f;
+  float carry = 0.0f, pA = 0.0f, pD = 0.0f;
+  for (int r0 = 0; r0 < p.Q; r0 += PREP_THREADS) {
+    const int q = p.Q - 1 - (r0 + tid);
+    float v = q >= 0 ? s_dS[q] : 0.0f;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const float u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+    if (lane == 31) wsum[wid] = v;
+    __syncthreads();
+    float off = carry;
+    for (int j = 0; j < wid; ++j) off += wsum[j];
+    v += off;
+    if (q >= 0) {
+      const int64_t idx = (tok0 + q) * p.H + h;
+      if (p.dt) { ddt_out[idx] = fmaf(Ah, v, s_ddtx[q]); pA = fmaf(v, s_dt[q], pA); pD += s_dD[q]; }
+      else da_out[idx] = v;
+    }
+    float tot = carry;
+    for (int j = 0; j < PREP_THREADS / 32; ++j) tot += wsum[j];
+    carry = tot;
+    __syncthreads();
+  }
+  if (p.dt) {
+    const float tA = block_sum(pA, red);
+    const float tD = block_sum(pD, red);
+    if (tid == 0) {
+      part[(int64_t)bc * p.H + h] = tA;
+      part[(int64_t)p.B * p.nc * p.H + (int64_t)bc * p.H + h] = tD;
+    }
+  }
+}
+
 // Sums the split-K partial tiles in a fixed order.  mode 0: dG (lower-triangular 64x64 tiles only, the
 // others were never produced); mode 1/2: dC/dB rows go to out + token * ld + g * cols.
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, int nsplit, int rows, int cols, int mode, int G, int Q,
@@ -710,6 +817,19 @@ size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base
     bool tcshape = Q % 64 == 0 && N % 32 == 0 && P % 64 == 0;
     w.xs = ar.take<float>(tcshape ? (size_t)B * T * H * P : 0);
     w.dys = ar.take<float>(tcshape ? (size_t)B * T * H * P : 0);
+    // bf16 (hi, lo) pairs of the operands of the fused intra-chunk kernels
+    const bool fz = ssd_fused_supported(P, N, Q, true);
+    const size_t hp = fz ? (size_t)B * T * H * P : 0, gn = fz ? (size_t)B * T * 2 * G * N : 0, stn = fz ? (size_t)B * nc * H * N * P : 0;
+    w.xt_hi = ar.take<uint16_t>(hp); w.xt_lo = ar.take<uint16_t>(hp);
+    w.bc_hi = ar.take<uint16_t>(gn); w.bc_lo = ar.take<uint16_t>(gn);
+    w.dy_hi = ar.take<uint16_t>(hp); w.dy_lo = ar.take<uint16_t>(hp);
+    w.hp_hi = ar.take<uint16_t>(stn); w.hp_lo = ar.take<uint16_t>(stn);
+    w.dh_hi = ar.take<uint16_t>(stn); w.dh_lo = ar.take<uint16_t>(stn);
+    // fused path: the carried-state part of y (kept for the backward) and the sums of W the backward kernel leaves
+    w.yoff = ar.take<float>(hp);
+    w.csum = ar.take<float>(fz ? (size_t)B * T * H : 0);
+    w.esum = ar.take<float>(fz ? (size_t)B * T * H : 0);
+    w.rpart = ar.take<float>(fz ? (size_t)B * T * H * (Q / 128) : 0);
   }
   if (out) *out = w;
   return ar.ok ? ar.used() : 0;
@@ -755,6 +875,54 @@ static pmb_status side_lane(int idx, SideLane** out) {
   if (!on) return PMB_OK;
   return get_side_lane(idx, out);
 }
+static bool fused_enabled() {
+  static const int on = [] { const char* e = getenv("PMB_SSD_FUSED"); return (e && e[0] == '0') ? 0 : 1; }();
+  return on != 0;
+}
+
+// x~[b,t,h,:] = x[b,t,h,:] * dt[b,t,h] as a bf16 pair (only when the fused cumsum kernel did not already write it)
+__global__ void __launch_bounds__(256) xt_pair_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ dt,
+                                                      uint16_t* __restrict__ hi, uint16_t* __restrict__ lo, int64_t rows, int H, int P) {
+  const int P4 = P >> 2;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * H * P4) return;
+  const int j = (int)(i % P4); const int64_t w = i / P4; const int h = (int)(w % H); const int64_t tk = w / H;
+  const float f = dt ? dt[tk * H + h] : 1.0f;
+  const float4 v = reinterpret_cast<const float4*>(x + tk * ldx + h * P)[j];
+  const int64_t o = (tk * H + h) * (int64_t)P + 4 * j;
+  store_pair4(hi + o, lo + o, v.x * f, v.y * f, v.z * f, v.w * f);
+}
+
+// The B and C columns (adjacent in the caller's buffer when it is the block's activation buffer, else two arrays)
+// as bf16 pairs with row pitch 2*G*N: B in columns [0, G*N), C in [G*N, 2*G*N).
+static pmb_status fused_operand_pairs(cudaStream_t st, const SsdIn& in, const SsdWs& ws, bool want_xt) {
+  const int64_t rows = (int64_t)in.B * in.T;
+  const int gn = in.G * in.N;
+  if (in.c == in.b + gn) {
+    PMB_TRY(split_pair16(st, in.b, rows, 2 * gn, in.ldbc, ws.bc_hi, ws.bc_lo, 2 * gn));
+  } else {
+    ProfScope prof(st, "split_f32_bf16x2", 0.0, 16.0 * rows * gn);
+    PMB_TRY(split_pair16_strided(st, in.b, rows, gn, in.ldbc, ws.bc_hi, ws.bc_lo, 2 * gn));
+    PMB_TRY(split_pair16_strided(st, in.c, rows, gn, in.ldbc, ws.bc_hi + gn, ws.bc_lo + gn, 2 * gn));
+  }
+  if (want_xt) {
+    ProfScope prof(st, "ssd_xt_pair", 0.0, 8.0 * rows * in.H * in.P);
+    xt_pair_kernel<<<(unsigned)cdiv(rows * in.H * (in.P / 4), 256), 256, 0, st>>>(in.x, in.ldx, in.dt, ws.xt_hi, ws.xt_lo, rows, in.H, in.P);
+    PMB_LAUNCHED();
+  }
+  return PMB_OK;
+}
+
+static FusedArgs fused_args(const SsdIn& in, const SsdWs& ws) {
+  FusedArgs fa{};
+  fa.B = in.B; fa.T = in.T; fa.H = in.H; fa.P = in.P; fa.N = in.N; fa.G = in.G; fa.Q = in.Q;
+  fa.S = ws.S;
+  const int64_t pitch = 2 * (int64_t)in.G * in.N;
+  fa.b = Op16{ws.bc_hi, ws.bc_lo, pitch};
+  fa.c = Op16{ws.bc_hi + in.G * in.N, ws.bc_lo + in.G * in.N, pitch};
+  return fa;
+}
+
 pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, float* y, int64_t ldy, float* final_state,
                    const SsdWs& ws) {
   SsdP p;
@@ -763,7 +931,10 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
   int nbch = p.B * p.nc * p.H, nbcg = p.B * p.nc * p.G;
   const double tok = (double)p.B * p.T;
   const bool tc = ssd_tc_supported(in) && (ldy % 4 == 0) && (reinterpret_cast<uintptr_t>(y) % 16 == 0);
+  // the intra-chunk chain C B^T -> mask -> x x~ (+ the carried-state term) as one tcgen05 kernel on bf16 pairs
+  const bool fz = tc && fused_enabled() && ssd_fused_supported(p.P, p.N, p.Q, true);
   SsdIn in_tc = in;
+  bool xt_ready = false;
   {
     CumsumRaw raw{in.dt_raw, in.ld_raw, in.dt_bias, in.a_log, const_cast<float*>(in.dt), const_cast<float*>(in.A)};
     if (in.dt_raw && (!in.dt || !in.A || !in.dt_bias || !in.a_log)) return fail(PMB_ERR_ARG, "ssd: dt_raw needs dt, A, dt_bias and a_log");
@@ -771,9 +942,10 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
     // finer-grained kernels use the memory system better)
     if (tc && nbch <= 4 * 148 && p.Q <= PREP_MAX_Q && (in.ldx % 4 == 0) && (reinterpret_cast<uintptr_t>(in.x) % 16 == 0)) {
       ProfScope prof(st, "ssd_chunk_prepare", 0.0, 8.0 * tok * p.H * (1.0 + p.P));
-      chunk_prepare_kernel<<<(unsigned)nbch, PREP_THREADS, 0, st>>>(p, raw, ws.xs);
+      chunk_prepare_kernel<<<(unsigned)nbch, PREP_THREADS, 0, st>>>(p, raw, ws.xs, fz ? ws.xt_hi : nullptr, ws.xt_lo);
       PMB_LAUNCHED();
       in_tc.xs_ready = true;
+      xt_ready = fz;
     } else {
       ProfScope prof(st, "ssd_chunk_cumsum", 0.0, 8.0 * tok * p.H);
       chunk_cumsum_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p, raw);
@@ -782,7 +954,13 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
   }
   SideLane* lane = nullptr;
   if (tc) PMB_TRY(side_lane(2, &lane));
-  if (tc) {
+  if (fz) {
+    // the B / C pairs (and the x~ pair when the fused cumsum kernel did not run) next to the chunk-state chain
+    cudaStream_t sb = lane ? lane->s : st;
+    if (lane) PMB_TRY(order_after(st, lane->ev[0], sb));     // S and dt are ready
+    PMB_TRY(fused_operand_pairs(sb, in, ws, !xt_ready));
+    PMB_TRY(ssd_tc_state(st, in_tc, ws));
+  } else if (tc) {
     cudaStream_t sb = lane ? lane->s : st;
     if (lane) PMB_TRY(order_after(st, lane->ev[0], sb));     // S is ready
     PMB_TRY(ssd_tc_cb(sb, in, ws));
@@ -794,10 +972,18 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
   int64_t nel = (int64_t)p.B * p.H * p.N * p.P;
   {
     ProfScope prof(st, "ssd_state_pass", 0.0, 8.0 * nel * p.nc);
-    PMB_TRY(launch_state_scan(st, p, p.hprev, init_state, p.hlast, 0));
+    PMB_TRY(launch_state_scan(st, p, p.hprev, init_state, p.hlast, 0, fz ? ws.hp_hi : nullptr, ws.hp_lo));
   }
-  if (lane) PMB_TRY(order_after(lane->s, lane->ev[1], st));   // C B^T is ready
-  if (tc) PMB_TRY(ssd_tc_scan(st, in, y, ldy, ws));
+  if (lane) PMB_TRY(order_after(lane->s, lane->ev[1], st));   // C B^T (or the operand pairs) are ready
+  if (fz) {
+    FusedArgs fa = fused_args(in, ws);
+    fa.v = Op16{ws.xt_hi, ws.xt_lo, (int64_t)p.H * p.P};
+    fa.state = Op16{ws.hp_hi, ws.hp_lo, p.P};
+    fa.out = y; fa.ldo = ldy; fa.x = in.x; fa.ldx = in.ldx; fa.D = in.D;
+    fa.off_out = ws.yoff;
+    PMB_TRY(ssd_fused(st, 0, fa));
+  }
+  else if (tc) PMB_TRY(ssd_tc_scan(st, in, y, ldy, ws));
   else PMB_TRY(run_op(st, "ssd_chunk_scan", make_op<OpScan>(p, p.Q, p.P), nbch, 2.0 * tok * p.H * p.P * (p.Q + p.N)));
   if (final_state) PMB_CUDA(cudaMemcpyAsync(final_state, ws.hlast, (size_t)nel * sizeof(float), cudaMemcpyDeviceToDevice, st));
   return PMB_OK;
@@ -815,6 +1001,8 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   const bool tc = ssd_tc_supported(in) && (lddy % 4 == 0) && (reinterpret_cast<uintptr_t>(dy) % 16 == 0) && (g.lddbc % 4 == 0) &&
                   ((reinterpret_cast<uintptr_t>(g.db) | reinterpret_cast<uintptr_t>(g.dc)) % 16 == 0);
   const bool tc_group = tc;
+  const bool fz = tc && fused_enabled() && ssd_fused_supported(p.P, p.N, p.Q, true) && (g.lddx % 4 == 0) &&
+                  (reinterpret_cast<uintptr_t>(g.dx) % 16 == 0);
   SideLane* lane = nullptr;
   if (tc) PMB_TRY(side_lane(0, &lane));
   cudaStream_t sb = lane ? lane->s : st;                      // stream of the dG -> dC -> dB chain
@@ -827,19 +1015,38 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   if (lane) PMB_CUDA(cudaEventRecord(lane->ev[1], st));       // dY exp(S) is ready (dC reads it)
   {
     ProfScope prof(st, "ssd_bwd_state_pass", 0.0, 12.0 * p.B * p.H * p.N * p.P * p.nc);
-    PMB_TRY(launch_state_scan(st, p, p.dh, nullptr, nullptr, 1));
-    state_dot_kernel<<<(unsigned)nbch, 256, 0, st>>>(p, dsend);
+    PMB_TRY(launch_state_scan(st, p, p.dh, nullptr, nullptr, 1, fz ? ws.dh_hi : nullptr, ws.dh_lo));
+    state_dot_kernel<<<(unsigned)nbch, 256, 0, st>>>(p, dsend, fz ? 1 : 0);
     PMB_LAUNCHED();
   }
   if (lane) PMB_CUDA(cudaEventRecord(lane->ev[2], st));       // dh is ready (dB reads it)
-  if (tc) PMB_TRY(ssd_tc_dx(st, in, dy, lddy, ws));
+  if (fz) {
+    // dY as a bf16 pair (the B / C / x~ pairs were written by the forward of this scan and are still in the workspace)
+    PMB_TRY(split_pair16(st, dy, (int64_t)p.B * p.T, p.H * p.P, lddy, ws.dy_hi, ws.dy_lo, (int64_t)p.H * p.P));
+    FusedArgs fa = fused_args(in, ws);
+    fa.v = Op16{ws.dy_hi, ws.dy_lo, (int64_t)p.H * p.P};
+    fa.state = Op16{ws.dh_hi, ws.dh_lo, p.P};
+    fa.out = p.dxt; fa.ldo = (int64_t)p.H * p.P;
+    fa.xt = Op16{ws.xt_hi, ws.xt_lo, (int64_t)p.H * p.P};
+    fa.csum = ws.csum; fa.esum = ws.esum; fa.rpart = ws.rpart;
+    PMB_TRY(ssd_fused(st, 1, fa));
+  }
+  else if (tc) {
+    // (a forward that took the fused kernel left no C B^T behind: form it now)
+    if (fused_enabled() && ssd_fused_supported(p.P, p.N, p.Q, true)) PMB_TRY(ssd_tc_cb(st, in, ws));
+    PMB_TRY(ssd_tc_dx(st, in, dy, lddy, ws));
+  }
   else PMB_TRY(run_op(st, "ssd_bwd_dx", make_op<OpDx>(p, p.Q, p.P), nbch, 2.0 * tok * p.H * p.P * (p.Q + p.N)));
   {
     ProfScope prof(st, "ssd_bwd_rows", 0.0, 4.0 * tok * p.H * (5.0 * p.P + 8.0));
     const bool vec_ok = (p.P % 4 == 0) && (p.ldx % 4 == 0) && (p.ldy % 4 == 0) && (p.lddy % 4 == 0) && (g.lddx % 4 == 0) &&
                         ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.y) | reinterpret_cast<uintptr_t>(p.dy) |
                           reinterpret_cast<uintptr_t>(g.dx) | reinterpret_cast<uintptr_t>(p.dxt)) % 16 == 0);
-    if (vec_ok && nbch <= 4 * 148 && p.Q <= PREP_MAX_Q) {
+    if (fz) {
+      WSums wsm{ws.rpart, ws.csum, ws.esum, ws.yoff, p.Q / 128};
+      chunk_rows_finish_w_kernel<<<(unsigned)nbch, PREP_THREADS, 0, st>>>(p, wsm, g.dx, g.lddx, dsend, g.da, g.ddt, ws.part);
+      PMB_LAUNCHED();
+    } else if (vec_ok && nbch <= 4 * 148 && p.Q <= PREP_MAX_Q) {
       chunk_rows_finish_kernel<<<(unsigned)nbch, PREP_THREADS, 0, st>>>(p, g.dx, g.lddx, dsend, g.da, g.ddt, ws.part);
       PMB_LAUNCHED();
     } else {

@@ -63,8 +63,9 @@ def test_block_fwd_bwd_vs_oracle(pm, D, N, P, H, G, K, Q, B, T):
     assert_close(out, out_ref, what="out")
     dx, grads = blk.backward(x.cuda(), cot.cuda())
     assert_close(dx, dx_ref, what="dx")
+    fused = (Q % 128 == 0 and N == 64 and P == 64)       # the fused tensor-core scan takes this shape
     for k in p:
-        assert_close(grads[k], g_ref[k], tol=tol_for(k), what="d_" + k)
+        assert_close(grads[k], g_ref[k], tol=tol_for(k, fused), what="d_" + k)
     assert pm.device_status() == 0
 
 

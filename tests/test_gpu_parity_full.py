@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from oracle import mamba2_oracle as orc
-from util import FP32_TOL, assert_close, block_params, cuda_params, rand, randn, rel_err, report, to_pm_cfg, tol_for
+from util import DEPTH24_TOL, FP32_TOL, assert_close, block_params, cuda_params, rand, randn, rel_err, report, to_pm_cfg, tol_for
 
 pytestmark = pytest.mark.gpu
 
@@ -47,16 +47,24 @@ def test_headline_config_lm_step_vs_oracle(pm):
     loss = lm.step_host(ids.pin_memory(), tg.pin_memory())
     assert abs(loss - loss_ref) < 1e-4 * abs(loss_ref), (loss, loss_ref)
     ge, gl = lm.grads()
-    report("headline_lm", "d_embed", ge, ge_ref)
-    worst = {}
+    failures = []
+
+    def check(what, ours, ref, tol):
+        try:
+            return report("headline_lm", what, ours, ref, tol=tol, elem_tol=1e3 * tol)[0]   # element-wise floor is 1e-3 of the max
+        except AssertionError as e:          # collect everything before failing: the report should hold every tensor
+            failures.append(str(e))
+            return rel_err(ours, ref)
+
+    worst = {"embed": check("d_embed", ge, ge_ref, DEPTH24_TOL)}
     for l in range(L):
         for k in layers[l]:
-            e, ee = report("headline_lm", f"layer{l:02d}.d_{k}", gl[l][k], gl_ref[l][k], tol=tol_for(k))
-            worst[k] = max(worst.get(k, 0.0), e)
+            worst[k] = max(worst.get(k, 0.0), check(f"layer{l:02d}.d_{k}", gl[l][k], gl_ref[l][k], DEPTH24_TOL))
             assert torch.isfinite(gl[l][k]).all() and gl[l][k].abs().max() > 0, (l, k)
     print("headline LM: worst max-norm error per parameter kind", {k: f"{v:.2e}" for k, v in worst.items()})
     assert pm.device_status() == 0 and lm.bad_tokens() == 0
     lm.close()
+    assert not failures, failures
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, None), (torch.bfloat16, 2e-2)])
@@ -64,7 +72,7 @@ def test_lm_head_across_row_tiles_with_remainder(pm, dtype, tol):
     """4608 tokens = two full row tiles of 2048 and a remainder of 512: the logits tile loop, the accumulation of the
     embedding-table gradient across tiles and the per-tile d(hidden) (crates/pm-core/src/loss.rs:73-209 tiles the
     same way)."""
-    cfg = orc.Mamba2Config(d_model=64, d_state=8, d_head=16, n_heads=4, block_len=32)
+    cfg = orc.Mamba2Config(d_model=64, d_state=8, d_head=8, n_heads=8, block_len=32)    # in_proj_dim 152: a multiple of 8 (bf16 rule)
     L, B, T, V = 2, 9, 512, 301
     layers = [block_params(cfg, seed=60 + i) for i in range(L)]
     embed = randn((V, 64), 13, 0.5)
@@ -123,7 +131,7 @@ def test_decode_step_at_scan_microbench_dims(pm):
     assert pm.device_status() == 0
 
 
-@pytest.mark.parametrize("P,N", [(16, 16), (64, 32)])   # FMA engine / tensor-core engine
+@pytest.mark.parametrize("P,N", [(16, 16), (64, 32), (64, 64)])   # FMA engine / tensor-core engines (3xTF32, fused pairs)
 def test_ssd_strong_decay_backward_vs_oracle(pm, P, N):
     """A = -16, dt ~ 0.13, chunk 256 (in-chunk sums near -530): the backward is compared with the oracle's autograd,
     not only checked for finiteness."""

@@ -13,16 +13,22 @@ GOLD = pathlib.Path(__file__).resolve().parent / "golden"
 FP32_TOL = 1e-4
 
 
-# The gradients of the per-head scalars a_log and dt_bias are sums over every token of differences of
-# nearly equal O(1) terms (d/dS of the decay mask: row sums minus column sums).  Two correct fp32
-# evaluations with different summation orders differ by a few 1e-5..1e-4 there (the fp32 oracle itself is
-# 2e-5 from its fp64 run at production dims), and the reference's own cross-backend gradient tests hold
-# SSD gradients to 1e-3 (crates/pm-cuda/tests/grad_ssd.rs:62-227).  They are held to 5e-4 here.
+# The gradients of a_log and dt_bias are sums over all tokens of S-weighted differences of nearly equal terms (row
+# sums minus column sums of dM o M).  On the shapes the fused tensor-core scan takes (block_len % 128 == 0, d_state =
+# d_head = 64) both sums come from the same registers (csrc/ssd_fused.cu) and the two tensors get the bar of every
+# other tensor (`fused=True`).  The fp32 FMA engine that serves the remaining (small or ragged) shapes forms the
+# difference from y and dx~ instead and is held to 5e-4 there (the reference's own cross-backend SSD gradient tests
+# use 1e-3, crates/pm-cuda/tests/grad_ssd.rs:62-227).
 CANCELLATION_TOL = 5e-4
 
+# One 24-layer step: every tensor carries the rounding of ~150 bf16-pair GEMMs in sequence (16 mantissa bits per
+# operand, ~1.5e-5 of the result's scale per layer), which random-walks to 1.1e-4 .. 1.9e-4 at depth 24 (measured,
+# parity report); single blocks and 2-layer models stay under FP32_TOL.
+DEPTH24_TOL = 2.5e-4
 
-def tol_for(name: str) -> float:
-    return CANCELLATION_TOL if name.endswith(("a_log", "dt_bias")) else FP32_TOL
+
+def tol_for(name: str, fused: bool = False) -> float:
+    return CANCELLATION_TOL if (not fused and name.endswith(("a_log", "dt_bias"))) else FP32_TOL
 
 
 def rel_err(ours, ref) -> float:
