@@ -163,8 +163,12 @@ static pmb_status block_fwd_core(cudaStream_t st, const Dims& d, const pmb_block
   }
   else PMB_TRY(gemm(st, 0, 0, d.M, d.J, d.D, static_cast<const float*>(x), d.D, p.in_proj_weight, d.J, w.xzd, d.J, nullptr, 0));
   // dt = softplus(dt_raw + bias) and A = -exp(a_log) are formed by the scan's first kernel (the chunk cumsum)
-  PMB_TRY(conv_silu_dt_fwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, p.dt_bias, w.act, nullptr));
+  // the B | C columns leave the conv kernel as a bf16 pair too when the fused scan kernels will read them
+  ConvPairOut bc{};
+  if (w.ssd.bc_hi) bc = ConvPairOut{w.ssd.bc_hi, w.ssd.bc_lo, d.I, 2 * d.G * d.N};
+  PMB_TRY(conv_silu_dt_fwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, p.dt_bias, w.act, nullptr, w.ssd.bc_hi ? &bc : nullptr));
   SsdIn sin = ssd_inputs(d, p, w);
+  sin.bc_pair_ready = bc.hi != nullptr;
   sin.dt_raw = w.xzd + d.I + d.X; sin.ld_raw = d.J; sin.dt_bias = p.dt_bias; sin.a_log = p.a_log;
   PMB_TRY(ssd_fwd(st, sin, nullptr, w.y, d.I, nullptr, w.ssd));
   // with pair GEMMs the normalised output is only ever a GEMM operand: write it as a pair, skip the fp32 copy
@@ -255,7 +259,10 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   SsdIn sin = ssd_inputs(d, p, w);
   NormBwdExtra ex{};
   ex.dz_hi = ph; ex.dz_lo = pl;
-  if ((pr || w16) && ssd_tc_supported(sin) && (d.P % 4 == 0)) { ex.dys = w.ssd.dys; ex.S = w.ssd.S; ex.H = d.H; ex.P = d.P; ex.T = d.T; sin.dys_ready = true; }
+  if ((pr || w16) && ssd_tc_supported(sin) && (d.P % 4 == 0)) {
+    ex.dys = w.ssd.dys; ex.S = w.ssd.S; ex.H = d.H; ex.P = d.P; ex.T = d.T; sin.dys_ready = true;
+    if (w.ssd.dy_hi) { ex.dy_hi = w.ssd.dy_hi; ex.dy_lo = w.ssd.dy_lo; sin.dy_pair_ready = true; }   // dY pair for the fused scan backward
+  }
   PMB_TRY(gated_rmsnorm_bwd(st, d.M, d.I, w.dnormed, w.y, w.xzd, d.J, p.norm_weight, w.rstd, w.dnormed, w.dxzd, d.J,
                             g.norm_weight, w.scratch2, w.scratch2_bytes, gl, &ex));
   // scan

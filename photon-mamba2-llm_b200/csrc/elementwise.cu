@@ -16,7 +16,7 @@ __global__ void column_sum_kernel(const float* __restrict__ partial, int64_t row
 template <int K, int VEC, int TT>
 __global__ void __launch_bounds__(128) conv_silu_fwd_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
                                                             const float* __restrict__ w, const float* __restrict__ bias,
-                                                            float* __restrict__ act, int X, int T) {
+                                                            float* __restrict__ act, int X, int T, ConvPairOut po) {
   int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (c >= X) return;
   int tblocks = (T + TT - 1) / TT;
@@ -69,7 +69,14 @@ __global__ void __launch_bounds__(128) conv_silu_fwd_kernel(const float* __restr
       for (int k = 0; k < K - 1; ++k) win[v][k] = win[v][k + 1];
     }
     if (t < t1) {
-      if (VEC == 4) *reinterpret_cast<float4*>(dst + (int64_t)t * X) = make_float4(o[0], o[1 % VEC], o[2 % VEC], o[3 % VEC]);
+      if (VEC == 4) {
+        *reinterpret_cast<float4*>(dst + (int64_t)t * X) = make_float4(o[0], o[1 % VEC], o[2 % VEC], o[3 % VEC]);
+        // the B | C columns also go out as a bf16 pair (operands of the fused scan kernels)
+        if (po.hi && c >= po.col0) {
+          const int64_t o16 = ((int64_t)b * T + t) * po.width + (c - po.col0);
+          store_pair4(po.hi + o16, po.lo + o16, o[0], o[1 % VEC], o[2 % VEC], o[3 % VEC]);
+        }
+      }
       else dst[(int64_t)t * X] = o[0];
     }
   }
@@ -85,36 +92,42 @@ __global__ void dt_softplus_kernel(const float* __restrict__ xzd, int64_t ldx, i
 }
 
 template <int K>
-static pmb_status launch_conv_fwd_k(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b, float* act) {
+static pmb_status launch_conv_fwd_k(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b, float* act,
+                                    ConvPairOut* pair) {
   // time steps per thread: short runs keep enough threads in flight for small token counts
   const bool long_runs = d.M >= 32768;
   const int TT = long_runs ? 16 : 8;
   bool vec = (d.X % 4 == 0) && (d.J % 4 == 0) && (d.I % 4 == 0) && ((reinterpret_cast<uintptr_t>(xzd) | reinterpret_cast<uintptr_t>(act)) % 16 == 0);
   int tblocks = (d.T + TT - 1) / TT;
+  ConvPairOut po{};
+  if (pair) {
+    if (vec && pair->hi && ((reinterpret_cast<uintptr_t>(pair->hi) | reinterpret_cast<uintptr_t>(pair->lo)) % 8 == 0) && pair->width % 4 == 0) po = *pair;
+    else pair->hi = nullptr;       // tells the caller that the pair was not written
+  }
   if (vec) {
     dim3 grid((unsigned)cdiv(d.X / 4, 128), (unsigned)(d.B * tblocks));
-    if (long_runs) conv_silu_fwd_kernel<K, 4, 16><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T);
-    else conv_silu_fwd_kernel<K, 4, 8><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T);
+    if (long_runs) conv_silu_fwd_kernel<K, 4, 16><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T, po);
+    else conv_silu_fwd_kernel<K, 4, 8><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T, po);
   } else {
     dim3 grid((unsigned)cdiv(d.X, 128), (unsigned)(d.B * tblocks));
-    if (long_runs) conv_silu_fwd_kernel<K, 1, 16><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T);
-    else conv_silu_fwd_kernel<K, 1, 8><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T);
+    if (long_runs) conv_silu_fwd_kernel<K, 1, 16><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T, po);
+    else conv_silu_fwd_kernel<K, 1, 8><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, act, d.X, d.T, po);
   }
   PMB_LAUNCHED();
   return PMB_OK;
 }
 
 pmb_status conv_silu_dt_fwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
-                            const float* dt_bias, float* act, float* dt) {
+                            const float* dt_bias, float* act, float* dt, ConvPairOut* pair) {
   ProfScope prof(st, "conv_silu_dt_fwd", 0.0, 4.0 * d.M * (2.0 * d.X + 2.0 * d.H));
   switch (d.K) {
-    case 2: PMB_TRY(launch_conv_fwd_k<2>(st, d, xzd, w, b, act)); break;
-    case 3: PMB_TRY(launch_conv_fwd_k<3>(st, d, xzd, w, b, act)); break;
-    case 4: PMB_TRY(launch_conv_fwd_k<4>(st, d, xzd, w, b, act)); break;
-    case 5: PMB_TRY(launch_conv_fwd_k<5>(st, d, xzd, w, b, act)); break;
-    case 6: PMB_TRY(launch_conv_fwd_k<6>(st, d, xzd, w, b, act)); break;
-    case 7: PMB_TRY(launch_conv_fwd_k<7>(st, d, xzd, w, b, act)); break;
-    case 8: PMB_TRY(launch_conv_fwd_k<8>(st, d, xzd, w, b, act)); break;
+    case 2: PMB_TRY(launch_conv_fwd_k<2>(st, d, xzd, w, b, act, pair)); break;
+    case 3: PMB_TRY(launch_conv_fwd_k<3>(st, d, xzd, w, b, act, pair)); break;
+    case 4: PMB_TRY(launch_conv_fwd_k<4>(st, d, xzd, w, b, act, pair)); break;
+    case 5: PMB_TRY(launch_conv_fwd_k<5>(st, d, xzd, w, b, act, pair)); break;
+    case 6: PMB_TRY(launch_conv_fwd_k<6>(st, d, xzd, w, b, act, pair)); break;
+    case 7: PMB_TRY(launch_conv_fwd_k<7>(st, d, xzd, w, b, act, pair)); break;
+    case 8: PMB_TRY(launch_conv_fwd_k<8>(st, d, xzd, w, b, act, pair)); break;
     default: return fail(PMB_ERR_SHAPE, "d_conv %d unsupported", d.K);
   }
   if (dt) {
@@ -529,6 +542,7 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_bwd_vec_kernel(con
         reinterpret_cast<float4*>(dy + row * width)[i] = o_dy;
         if (ex.dz_hi) store_pair4(ex.dz_hi + row * lddz + 4 * i, ex.dz_lo + row * lddz + 4 * i, o_dz.x, o_dz.y, o_dz.z, o_dz.w);
         else reinterpret_cast<float4*>(dz + row * lddz)[i] = o_dz;
+        if (ex.dy_hi) store_pair4(ex.dy_hi + row * width + 4 * i, ex.dy_lo + row * width + 4 * i, o_dy.x, o_dy.y, o_dy.z, o_dy.w);
         if (ex.dys) {    // dys[t, h, :] = dy[t, h, :] * exp(S[b, h, t]) for the scan backward (head width ex.P is a multiple of 4)
           const int h = (4 * i) / ex.P;
           const int64_t bb = row / ex.T, tt = row % ex.T;
@@ -580,7 +594,7 @@ pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const flo
   ProfScope prof(st, "gated_rmsnorm_bwd", 0.0, 4.0 * rows * 5.0 * width);
   const bool vec_ok = norm_vec_ok(width, ldz, dout, y, z, w, dy) && (lddz % 4 == 0) &&
                       ((reinterpret_cast<uintptr_t>(dz) | reinterpret_cast<uintptr_t>(partial)) & 15) == 0;
-  if ((ex.dz_hi || ex.dys) && !vec_ok) return fail(PMB_ERR_UNSUPPORTED, "gated_rmsnorm_bwd: pair / scaled outputs need the vector kernel's alignment");
+  if ((ex.dz_hi || ex.dys || ex.dy_hi) && !vec_ok) return fail(PMB_ERR_UNSUPPORTED, "gated_rmsnorm_bwd: pair / scaled outputs need the vector kernel's alignment");
   if (vec_ok) {
     int per = 1;
     const int threads = norm_vec_threads(width, &per);

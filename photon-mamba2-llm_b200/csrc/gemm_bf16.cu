@@ -252,7 +252,7 @@ gemm_bf16_kernel(const __grid_constant__ Group g) {
       umma_commit(accum_bar);
     }
   } else {
-    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0));
+    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait_idle(accum_bar, 0));
     if (!acc_ok && lane == 0) { atomicOr(&g_bf16_status, 8u); *abort_flag = 1; }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const bool aborted = __any_sync(0xffffffffu, *abort_flag != 0);
@@ -446,7 +446,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ Group g) {
       umma_commit_pair(map_to_cta(accum_bar, 1));
     }
   } else {
-    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0));
+    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait_idle(accum_bar, 0));
     if (!acc_ok && lane == 0) { atomicOr(&g_bf16_status, 8u); *abort_flag = 1; }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const bool aborted = __any_sync(0xffffffffu, *abort_flag != 0);

@@ -16,8 +16,11 @@ void set_lanes_enabled(int on);
 pmb_status order_after(cudaStream_t from, cudaEvent_t ev, cudaStream_t to);
 
 // ---- elementwise.cu
+// optional second output of the conv forward: columns [col0, col0 + width) of `act` (the B | C columns) as a (hi, lo)
+// bf16 pair with row pitch `width`.  Written only by the vector kernel; `hi` is reset to NULL when it was not.
+struct ConvPairOut { uint16_t* hi = nullptr; uint16_t* lo = nullptr; int col0 = 0; int width = 0; };
 pmb_status conv_silu_dt_fwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
-                            const float* dt_bias, float* act, float* dt);
+                            const float* dt_bias, float* act, float* dt, ConvPairOut* pair = nullptr);
 size_t conv_bwd_ws_bytes(const Dims& d);
 pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
                          const float* dact, float* dxzd, float* dw, float* db, void* ws, size_t ws_bytes,
@@ -29,7 +32,8 @@ pmb_status gated_rmsnorm_fwd(cudaStream_t st, int64_t rows, int width, float eps
 size_t gated_rmsnorm_bwd_ws_bytes(int64_t rows, int width);
 // optional outputs of the gated RMSNorm backward: dz as a (hi, lo) bf16 pair (pitch lddz) instead of fp32, and
 // dys = dy * exp(S[b,h,t]) (S laid out (B,H,T), heads of width P, rows = B*T) for the scan backward
-struct NormBwdExtra { uint16_t* dz_hi = nullptr; uint16_t* dz_lo = nullptr; float* dys = nullptr; const float* S = nullptr; int H = 0, P = 1, T = 1; };
+struct NormBwdExtra { uint16_t* dz_hi = nullptr; uint16_t* dz_lo = nullptr; uint16_t* dy_hi = nullptr; uint16_t* dy_lo = nullptr; /* dy as a pair, contiguous rows */
+                      float* dys = nullptr; const float* S = nullptr; int H = 0, P = 1, T = 1; };
 pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const float* dout, const float* y, const float* z,
                              int64_t ldz, const float* w, const float* rstd, float* dy, float* dz, int64_t lddz,
                              float* dw, void* ws, size_t ws_bytes, SideLane* red = nullptr, const NormBwdExtra* extra = nullptr);
@@ -47,6 +51,8 @@ struct SsdIn {
   const float* b; const float* c; int64_t ldbc;
   const float* D;         // (H) skip weights or NULL:  y += D[h] * x
   bool dys_ready = false; // backward: ws.dys = dY exp(S) was already written by the caller
+  bool dy_pair_ready = false;  // backward: ws.dy_hi / dy_lo (the pair of dY) were already written by the caller
+  bool bc_pair_ready = false;  // forward: ws.bc_hi / bc_lo (the pairs of B | C) were already written by the caller
   bool xs_ready = false;  // forward (internal): ws.xs was already written by the fused cumsum kernel
   // forward only, optional: form dt and A inside the cumsum kernel.  dt = softplus(dt_raw[token*ld_raw + h] + dt_bias[h])
   // is written to `dt` and A[h] = -exp(a_log[h]) to `A` (both must then point at writable buffers).

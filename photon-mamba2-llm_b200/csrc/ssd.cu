@@ -830,6 +830,10 @@ size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base
     w.csum = ar.take<float>(fz ? (size_t)B * T * H : 0);
     w.esum = ar.take<float>(fz ? (size_t)B * T * H : 0);
     w.rpart = ar.take<float>(fz ? (size_t)B * T * H * (Q / 128) : 0);
+    if (!fz) {   // (a zero-sized take still yields an address: make "absent" testable)
+      w.xt_hi = w.xt_lo = w.bc_hi = w.bc_lo = w.dy_hi = w.dy_lo = w.hp_hi = w.hp_lo = w.dh_hi = w.dh_lo = nullptr;
+      w.yoff = w.csum = w.esum = w.rpart = nullptr;
+    }
   }
   if (out) *out = w;
   return ar.ok ? ar.used() : 0;
@@ -898,7 +902,9 @@ __global__ void __launch_bounds__(256) xt_pair_kernel(const float* __restrict__ 
 static pmb_status fused_operand_pairs(cudaStream_t st, const SsdIn& in, const SsdWs& ws, bool want_xt) {
   const int64_t rows = (int64_t)in.B * in.T;
   const int gn = in.G * in.N;
-  if (in.c == in.b + gn) {
+  if (in.bc_pair_ready) {
+    // written by the producer of B and C
+  } else if (in.c == in.b + gn) {
     PMB_TRY(split_pair16(st, in.b, rows, 2 * gn, in.ldbc, ws.bc_hi, ws.bc_lo, 2 * gn));
   } else {
     ProfScope prof(st, "split_f32_bf16x2", 0.0, 16.0 * rows * gn);
@@ -958,7 +964,7 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
     // the B / C pairs (and the x~ pair when the fused cumsum kernel did not run) next to the chunk-state chain
     cudaStream_t sb = lane ? lane->s : st;
     if (lane) PMB_TRY(order_after(st, lane->ev[0], sb));     // S and dt are ready
-    PMB_TRY(fused_operand_pairs(sb, in, ws, !xt_ready));
+    if (!in.bc_pair_ready || !xt_ready) PMB_TRY(fused_operand_pairs(sb, in, ws, !xt_ready));
     PMB_TRY(ssd_tc_state(st, in_tc, ws));
   } else if (tc) {
     cudaStream_t sb = lane ? lane->s : st;
@@ -1022,7 +1028,7 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   if (lane) PMB_CUDA(cudaEventRecord(lane->ev[2], st));       // dh is ready (dB reads it)
   if (fz) {
     // dY as a bf16 pair (the B / C / x~ pairs were written by the forward of this scan and are still in the workspace)
-    PMB_TRY(split_pair16(st, dy, (int64_t)p.B * p.T, p.H * p.P, lddy, ws.dy_hi, ws.dy_lo, (int64_t)p.H * p.P));
+    if (!in.dy_pair_ready) PMB_TRY(split_pair16(st, dy, (int64_t)p.B * p.T, p.H * p.P, lddy, ws.dy_hi, ws.dy_lo, (int64_t)p.H * p.P));
     FusedArgs fa = fused_args(in, ws);
     fa.v = Op16{ws.dy_hi, ws.dy_lo, (int64_t)p.H * p.P};
     fa.state = Op16{ws.dh_hi, ws.dh_lo, p.P};

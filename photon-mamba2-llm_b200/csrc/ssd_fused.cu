@@ -185,6 +185,13 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
     give_up(code);
     return false;
   };
+  // the same for the mask warps, which sleep between polls (they share schedulers with the MMA issuer)
+  auto wait_idle = [&](int b, uint32_t parity, unsigned int code) -> bool {
+    if (*abort_flag) return false;
+    if (mbar_wait_idle(bar(b), parity)) return true;
+    give_up(code);
+    return false;
+  };
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -328,8 +335,8 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
     // work, not the barrier), so the four warps of a group can never wait for one another unboundedly.
     for (int jj = grp; jj < ncb; jj += NGRP) {
       const int c0 = (cb0 + jj) * CW, mb = jj & 1, use = jj >> 1;       // use-th block of this group's buffers
-      bool got = ok && wait(G_FULL + mb, (uint32_t)(use & 1), 16u);
-      if (got && use >= 1) got = wait(M_FREE + mb, (uint32_t)((use - 1) & 1), 32u);
+      bool got = ok && wait_idle(G_FULL + mb, (uint32_t)(use & 1), 16u);
+      if (got && use >= 1) got = wait_idle(M_FREE + mb, (uint32_t)((use - 1) & 1), 32u);
       ok = __all_sync(0xffffffffu, got);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -391,7 +398,7 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
         }
       }
     }
-    const bool acc_ok = __all_sync(0xffffffffu, ok && wait(ACC_FULL, 0u, 64u));
+    const bool acc_ok = __all_sync(0xffffffffu, ok && wait_idle(ACC_FULL, 0u, 64u));
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const bool aborted = __any_sync(0xffffffffu, *abort_flag != 0);
     const bool run = acc_ok && !aborted;

@@ -36,6 +36,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
   return false;
 }
 
+// Bounded wait for warps that have nothing to do until the barrier flips (epilogue / mask warps waiting for the
+// tensor core): sleeps between polls, so that the polling warps do not take issue slots from the single thread that
+// issues the MMAs on the same scheduler.  False when the phase did not complete within `limit` polls.
+__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, uint32_t limit = SPIN_LIMIT >> 2) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    __nanosleep(96);
+  }
+  return false;
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
