@@ -230,41 +230,41 @@ def run_ours(args):
         lm.load(embed.cuda(), [{k: v.cuda() for k, v in p.items()} for p in layers])
     del embed, layers
 
-    # data-parallel gradient averaging: one bucket per layer, enqueued on a side stream from the library's
-    # per-layer host callback (pm_b200/dp.py) so it overlaps the remaining recompute/backward.
-    reducer = None
+    # data-parallel gradient averaging: the library's own NCCL communicator (pmb_dp_*), one all-reduce per layer
+    # bucket on its communication stream, enqueued by the step itself as each layer's gradient kernels are, so the
+    # transfer overlaps the remaining recompute / backward.  torch.distributed only carries the 128-byte id, the
+    # barriers and the max over ranks of the timing.
+    dp = None
     if world > 1:
-        from pm_b200.dp import GradAllReducer
-        offsets = [pm_b200.lib.pmb_lm_param_offset(lm._h, l, 0) for l in range(L)]
-        reducer = GradAllReducer(lm.flat_grads, offsets)
-    on_layer_done = reducer.on_layer_done if reducer else None
-
-    def finish_comm():
-        if reducer:
-            reducer.finish()
+        box = [pm_b200.DataParallel.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        dp = pm_b200.DataParallel(world, rank, box[0])
+    on_layer_done = None
 
     n_tok = 8
     host_batches = [make_tokens(w, rank, s, pin=True) for s in range(n_tok)]
     dev_batches = [(i.cuda(), t.cuda()) for i, t in host_batches]
 
-    def eager_step_device(s):
+    def eager_step_device(s, use_dp=True):
         ids, tg = dev_batches[s % n_tok]
-        lm.step_device(ids, tg, on_layer_done)
-        finish_comm()
+        if dp is not None and use_dp:
+            lm.step_device_dp(ids, tg, dp)
+        else:
+            lm.step_device(ids, tg, on_layer_done)
 
-    # The whole step (and, at N > 1, the per-layer gradient all-reduces enqueued from the library's callback) is
-    # captured once into a CUDA graph; a timed step copies that step's tokens into the graph's static input
-    # buffers and replays it.  --no-graph times the eager launches instead.
-    # The graph holds this rank's compute only.  At N > 1 the gradient average follows the replay as one NCCL
-    # all-reduce over the flat gradient buffer (a capture that contained the per-layer all-reduces did not finish
-    # in the one 2-GPU attempt; --no-graph keeps the eager path with the overlapped per-layer buckets).
+    # The whole step is captured once into a CUDA graph; a timed step copies that step's tokens into the graph's
+    # static input buffers and replays it.  --no-graph times the eager launches instead.
+    # At N > 1 the default graph holds the data-parallel step (compute + the per-layer all-reduces on the library's
+    # communication stream: NCCL's kernels are graph nodes like the rest).  --dp-after-graph keeps the graph to this
+    # rank's compute and averages the flat gradient buffer with one all-reduce after the replay.
     graph_step = None
     if not args.no_graph:
-        graph_step = lm.capture_step(None, None)
+        graph_step = lm.capture_step(dp=None if args.dp_after_graph else dp)
 
     def average_grads():
-        if world > 1:
-            dist.all_reduce(lm.flat_grads, op=dist.ReduceOp.AVG)
+        if dp is not None and args.dp_after_graph:
+            dp.all_reduce_async(lm.flat_grads)
+            dp.sync()
 
     def step_device(s):
         if graph_step is None:
@@ -276,9 +276,10 @@ def run_ours(args):
     def step_host(s):
         ids, tg = host_batches[s % n_tok]
         if graph_step is None:
-            loss = lm.step_host(ids, tg, on_layer_done)
-            finish_comm()
-            return loss
+            if dp is None:
+                return lm.step_host(ids, tg)
+            loss = lm.step_device_dp(ids.cuda(non_blocking=True), tg.cuda(non_blocking=True), dp)
+            return float(loss.item())
         loss = graph_step(ids, tg)                    # pinned host -> device copies, replay
         average_grads()
         return float(loss.item())                     # loss back to the host
@@ -331,11 +332,11 @@ def run_ours(args):
     # (eager and on one stream, so that a scope's duration is that kernel alone and not its share of an overlapped stretch)
     prof_steps = min(args.steps, 3)
     pm_b200.set_concurrency(False)
-    eager_step_device(0)
+    eager_step_device(0, use_dp=False)
     torch.cuda.synchronize()
     pm_b200.profile_start()
     for s in range(prof_steps):
-        eager_step_device(s)
+        eager_step_device(s, use_dp=False)
     prof = pm_b200.profile_stop()
     pm_b200.set_concurrency(True)
     peaks = load_peaks()
@@ -380,7 +381,9 @@ def run_ours(args):
             "config": config_dict(w, world),
             "arm_note": {"checkpointing": "stored across the stack: block inputs only",
                          "launch": "eager, per-layer gradient all-reduce overlapped" if graph_step is None else
-                                   ("one CUDA graph replay per step" + (", then one gradient all-reduce" if world > 1 else "")),
+                                   ("one CUDA graph replay per step" + ("" if world == 1 else
+                                    (", then one gradient all-reduce" if args.dp_after_graph else
+                                     " holding the per-layer gradient all-reduces (overlapped with the backward)"))),
                          "l2": "per-step working set (506 MB parameters + gradients + activations) exceeds the 126 MB L2; no explicit flush"},
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * T * 8, "d2h_bytes_per_step": 4,
                     "ms_per_step": ms_e2e / args.steps, "wall_ms_per_step": wall_e2e * 1e3 / args.steps},
@@ -398,6 +401,9 @@ def run_ours(args):
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
+        graph_step = None                  # graphs that captured the communicator go before the communicator
+        torch.cuda.synchronize()
+        dp.close()
         dist.destroy_process_group()
 
 
@@ -502,6 +508,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA-graph replays of the step")
+    ap.add_argument("--dp-after-graph", action="store_true", help="N > 1: graph of this rank's compute, then one all-reduce of all gradients")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.micro:

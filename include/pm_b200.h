@@ -317,6 +317,28 @@ pmb_status pmb_lm_bad_tokens(pmb_lm* lm, void* stream, int32_t* h_flags_out);
 pmb_status pmb_lm_step_host(pmb_lm* lm, void* stream, const int64_t* h_ids, const int64_t* h_targets,
                             float* h_loss, pmb_layer_callback on_layer_done, void* user);
 
+/* ---- data parallelism (no counterpart in the reference, which drives one device: crates/pm-cli/src/train_cmd.rs:50).
+ * The path shards over batch with no data-path collective; the one exchange per step is the average of the parameter
+ * gradients.  One process (or host thread) per GPU: rank 0 obtains an id with pmb_dp_unique_id and hands its 128 bytes
+ * to the other ranks by any host channel; every rank calls pmb_dp_init with its device current (a collective call:
+ * all ranks must enter it).  NCCL is loaded at run time (libnccl.so.2, or the name in PMB_NCCL_LIB).
+ * pmb_dp_allreduce_async orders an in-place average of `count` floats after everything already enqueued on `stream`
+ * and runs it on the communicator's own stream; pmb_dp_sync makes `stream` wait for all of them.
+ * pmb_lm_step_device_dp is pmb_lm_step_device with one such all-reduce per layer bucket (the layer's 8 gradient
+ * tensors, contiguous in the flat buffer), enqueued the moment the layer's gradient kernels are, the embedding bucket
+ * last, and the final wait: on return `stream` sees averaged gradients.  Every rank must make the same calls in the
+ * same order.  These calls may be captured into a CUDA graph (after one eager step, which lets NCCL set up its
+ * connections); NCCL then keeps the communicator alive for that graph, so destroy such graphs before pmb_dp_destroy,
+ * which otherwise waits for them. */
+typedef struct pmb_dp pmb_dp;
+pmb_status pmb_dp_unique_id(void* h_id128);
+pmb_status pmb_dp_init(int32_t nranks, int32_t rank, const void* h_id128, pmb_dp** out);
+void       pmb_dp_destroy(pmb_dp* dp);
+int32_t    pmb_dp_world_size(const pmb_dp* dp);
+pmb_status pmb_dp_allreduce_async(pmb_dp* dp, void* stream, float* d_buf, int64_t count);
+pmb_status pmb_dp_sync(pmb_dp* dp, void* stream);
+pmb_status pmb_lm_step_device_dp(pmb_lm* lm, void* stream, const int64_t* d_ids, const int64_t* d_targets, pmb_dp* dp);
+
 /* ---- optimizer on the flat parameter buffer (outside the benchmarked metric; pm-train/src/clip.rs:13-53,
  * pm-train/src/optim.rs:104-157).  pmb_grad_sumsq leaves sum(g^2) in a device scalar (two passes, fixed order, no
  * host sync); pmb_adamw_step applies global-norm clipping (when max_norm > 0: g *= max_norm/norm if norm > max_norm,

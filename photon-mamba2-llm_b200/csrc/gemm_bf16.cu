@@ -226,28 +226,31 @@ gemm_bf16_kernel(const __grid_constant__ Group g) {
       // K-major: 8-row groups 1024 B apart, one MMA (K=16) advances 32 B inside the 128-byte row.
       // MN-major: blocks of 64 elements TBK*128 B apart (LBO), 8-k-row groups 1024 B apart (SBO); K=16 spans two groups.
       const uint32_t a_lbo = p.a_mn_major ? TBK * 128 : 16, b_lbo = p.b_mn_major ? TBK * 128 : 16;
-      const uint32_t a_kstep = p.a_mn_major ? 2048 : 32, b_kstep = p.b_mn_major ? 2048 : 32;
+      // descriptor halves that do not change, and the per-k-step advance of the address field (16-byte units)
+      const uint32_t d_hi = desc_hi(1024, 2);
+      const uint32_t a_step = (p.a_mn_major ? 2048u : 32u) >> 4, b_step = (p.b_mn_major ? 2048u : 32u) >> 4;
+      constexpr uint32_t LO_OFF = (2 * TILE_BYTES) >> 4;        // from the hi tiles of a stage to its lo tiles
+      int s = 0; uint32_t ph = 0;
       for (int kt = 0; kt < num_kt; ++kt) {
-        const int s = kt % STAGES;
-        const uint32_t ph = (kt / STAGES) & 1;
         if (!mbar_wait(full_bar(s), ph)) { atomicOr(&g_bf16_status, 2u); *abort_flag = 1; break; }
         if (*abort_flag) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_s = tiles + s * STAGE_BYTES, b_s = a_s + TILE_BYTES;
+        const uint32_t a_s = tiles + s * STAGE_BYTES;
+        uint32_t al = desc_lo(a_s, a_lbo), bl = desc_lo(a_s + TILE_BYTES, b_lbo);
 #pragma unroll
         for (int k = 0; k < TBK / 16; ++k) {
-          const uint64_t da = make_desc(a_s + k * a_kstep, a_lbo, 1024, 2), db = make_desc(b_s + k * b_kstep, b_lbo, 1024, 2);
+          const uint32_t acc = (kt > 0 || k > 0) ? 1u : 0u;
           if (SPLIT) {
-            const uint64_t dal = make_desc(a_s + 2 * TILE_BYTES + k * a_kstep, a_lbo, 1024, 2);
-            const uint64_t dbl = make_desc(b_s + 2 * TILE_BYTES + k * b_kstep, b_lbo, 1024, 2);
-            mma_bf16(tmem_acc, dal, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
-            mma_bf16(tmem_acc, da, dbl, idesc, 1u);
-            mma_bf16(tmem_acc, da, db, idesc, 1u);
+            mma_f16_h(tmem_acc, al + LO_OFF, d_hi, bl, d_hi, idesc, acc);
+            mma_f16_h(tmem_acc, al, d_hi, bl + LO_OFF, d_hi, idesc, 1u);
+            mma_f16_h(tmem_acc, al, d_hi, bl, d_hi, idesc, 1u);
           } else {
-            mma_bf16(tmem_acc, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+            mma_f16_h(tmem_acc, al, d_hi, bl, d_hi, idesc, acc);
           }
+          al += a_step; bl += b_step;
         }
         umma_commit(empty_bar(s));
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
       umma_commit(accum_bar);
     }
@@ -418,29 +421,37 @@ gemm_bf16_pair_kernel(const __grid_constant__ Group g) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
                              ((uint32_t)(BN2 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
       const uint32_t a_lbo = p.a_mn_major ? TBK * 128 : 16, b_lbo = p.b_mn_major ? TBK * 128 : 16;
-      const uint32_t a_kstep = p.a_mn_major ? 2048 : 32, b_kstep = p.b_mn_major ? 2048 : 32;
+      const uint32_t d_hi = desc_hi(1024, 2);
+      const uint32_t a_step = (p.a_mn_major ? 2048u : 32u) >> 4, b_step = (p.b_mn_major ? 2048u : 32u) >> 4;
+      constexpr uint32_t LO_OFF = HALF_BYTES >> 4;
+      // the barriers of both CTAs as cluster addresses, once
+      uint32_t eb0[STAGES], eb1[STAGES];
+#pragma unroll
+      for (int i = 0; i < STAGES; ++i) { eb0[i] = map_to_cta(empty_bar(i), 0); eb1[i] = map_to_cta(empty_bar(i), 1); }
+      int s = 0; uint32_t ph = 0;
       for (int kt = 0; kt < num_kt; ++kt) {
-        const int s = kt % STAGES;
-        const uint32_t ph = (kt / STAGES) & 1;
         if (!mbar_wait(full_bar(s), ph)) { atomicOr(&g_bf16_status, 2u); *abort_flag = 1; break; }
         if (*abort_flag) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_s = tiles + s * STAGE_BYTES, b_s = a_s + TILE_BYTES;
+        const uint32_t a_s = tiles + s * STAGE_BYTES;
+        uint32_t al = desc_lo(a_s, a_lbo), bl = desc_lo(a_s + TILE_BYTES, b_lbo);
 #pragma unroll
         for (int k = 0; k < TBK / 16; ++k) {
-          const uint64_t da = make_desc(a_s + k * a_kstep, a_lbo, 1024, 2), db = make_desc(b_s + k * b_kstep, b_lbo, 1024, 2);
+          const uint32_t acc = (kt > 0 || k > 0) ? 1u : 0u;
           if (SPLIT) {
-            const uint64_t dal = make_desc(a_s + HALF_BYTES + k * a_kstep, a_lbo, 1024, 2);
-            const uint64_t dbl = make_desc(b_s + HALF_BYTES + k * b_kstep, b_lbo, 1024, 2);
-            mma_bf16_pair(tmem_acc, dal, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
-            mma_bf16_pair(tmem_acc, da, dbl, idesc, 1u);
-            mma_bf16_pair(tmem_acc, da, db, idesc, 1u);
+            mma_f16_pair_h(tmem_acc, al + LO_OFF, d_hi, bl, d_hi, idesc, acc);
+            mma_f16_pair_h(tmem_acc, al, d_hi, bl + LO_OFF, d_hi, idesc, 1u);
+            mma_f16_pair_h(tmem_acc, al, d_hi, bl, d_hi, idesc, 1u);
           } else {
-            mma_bf16_pair(tmem_acc, da, db, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+            mma_f16_pair_h(tmem_acc, al, d_hi, bl, d_hi, idesc, acc);
           }
+          al += a_step; bl += b_step;
         }
-        umma_commit_pair(map_to_cta(empty_bar(s), 0));
-        umma_commit_pair(map_to_cta(empty_bar(s), 1));
+        // the commits go through a switch on the stage so that the cluster addresses stay in registers
+#pragma unroll
+        for (int i = 0; i < STAGES; ++i)
+          if (i == s) { umma_commit_pair(eb0[i]); umma_commit_pair(eb1[i]); }
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
       umma_commit_pair(map_to_cta(accum_bar, 0));
       umma_commit_pair(map_to_cta(accum_bar, 1));

@@ -645,6 +645,36 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
   return PMB_OK;
 }
 
+// ---- data-parallel step: the same step with each layer's gradient bucket all-reduced (averaged) over the
+// communicator as soon as that layer's gradient kernels are enqueued, the embedding (and projection) bucket last.
+struct DpStep { pmb_lm* lm; pmb_dp* dp; void* stream; pmb_status status; };
+
+static void dp_layer_done(int32_t layer, void* user) {
+  DpStep* c = static_cast<DpStep*>(user);
+  if (c->status != PMB_OK) return;
+  pmb_lm* lm = c->lm;
+  auto reduce = [&](int64_t a, int64_t b) { if (b > a && c->status == PMB_OK) c->status = pmb_dp_allreduce_async(c->dp, c->stream, lm->grads + a, b - a); };
+  if (layer >= 0) {
+    // the layer's 8 tensors are contiguous; the bucket ends where the next item of the flat buffer starts
+    const int64_t a = lm->off[1 + 8 * layer];
+    int64_t b = lm->n_params;
+    if (layer + 1 < lm->L) b = lm->off[1 + 8 * (layer + 1)];
+    if (lm->off_proj >= a && lm->off_proj < b) b = lm->off_proj;    // the projection sits between the two stacks
+    reduce(a, b);
+  } else {
+    if (lm->off_proj >= 0) reduce(lm->off_proj, lm->off_proj + (int64_t)align_up((size_t)lm->d.D * lm->d.D, 64));
+    reduce(lm->off[0], lm->off[1]);
+  }
+}
+
+extern "C" pmb_status pmb_lm_step_device_dp(pmb_lm* lm, void* stream, const int64_t* d_ids, const int64_t* d_targets, pmb_dp* dp) {
+  if (!dp) return fail(PMB_ERR_ARG, "lm_step_device_dp: NULL communicator");
+  DpStep c{lm, dp, stream, PMB_OK};
+  PMB_TRY(pmb_lm_step_device(lm, stream, d_ids, d_targets, dp_layer_done, &c));
+  PMB_TRY(c.status);
+  return pmb_dp_sync(dp, stream);
+}
+
 // ---- weights checkpoint I/O (crates/pm-train/src/checkpoint.rs:25-97): parameters by position, "p_0000"...
 namespace pmb {
 pmb_status safetensors_save_f32(const char* path, int n, const int64_t* shapes, const int32_t* ranks, const float* const* data);

@@ -250,27 +250,31 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
     if (lane == 0) {
       const uint32_t id_g = idesc_bf16(0, 0, RB, CW);       // G: both operands K-major
       const uint32_t id_v = idesc_bf16(0, 1, RB, P);        // x V and x state: B operand MN-major
-      auto kmaj = [](uint32_t a) { return make_desc(a, 16, 1024, 2); };
-      auto mnmaj = [](uint32_t a) { return make_desc(a, T64, 1024, 2); };   // 64-wide blocks along N are T64 apart
-      // one k-step (16) of a product whose operands are split NS ways: A parts `as` bytes apart, B parts `bs` apart
-      auto kstep = [&](uint32_t d, uint32_t a, uint32_t as, uint32_t b, uint32_t bs, bool b_mn, uint32_t idesc, uint32_t acc) {
+      // Operand descriptors as (lo, hi) halves: hi never changes, lo = address field | leading offset.  A product
+      // walks its tiles by adding byte offsets >> 4 to lo, so one MMA costs the issuing thread a few integer adds.
+      const uint32_t dh = desc_hi(1024, 2);
+      auto lo_k = [](uint32_t a) { return desc_lo(a, 16); };          // K-major tile (128-byte rows)
+      auto lo_mn = [](uint32_t a) { return desc_lo(a, T64); };        // MN-major: 64-wide blocks along N are T64 apart
+      // one k-step (16) of a product whose operands are split NS ways: A parts `as` apart, B parts `bs` apart (16-byte units)
+      auto kstep = [&](uint32_t d, uint32_t alo, uint32_t as, uint32_t blo, uint32_t bs, uint32_t idesc, uint32_t acc) {
         if (NS == 2) {
-          mma_f16(d, kmaj(a + as), b_mn ? mnmaj(b) : kmaj(b), idesc, acc);        // lo x hi
-          mma_f16(d, kmaj(a), b_mn ? mnmaj(b + bs) : kmaj(b + bs), idesc, 1u);    // hi x lo
-          mma_f16(d, kmaj(a), b_mn ? mnmaj(b) : kmaj(b), idesc, 1u);              // hi x hi
+          mma_f16_h(d, alo + as, dh, blo, dh, idesc, acc);        // lo x hi
+          mma_f16_h(d, alo, dh, blo + bs, dh, idesc, 1u);         // hi x lo
+          mma_f16_h(d, alo, dh, blo, dh, idesc, 1u);              // hi x hi
         } else {
-          mma_f16(d, kmaj(a), b_mn ? mnmaj(b) : kmaj(b), idesc, acc);
+          mma_f16_h(d, alo, dh, blo, dh, idesc, acc);
         }
       };
       bool ok = wait(R_FULL, 0u, 2u) && wait(LD_FULL + 0, 0u, 2u);
       if (ok) {
         // carried-state term: acc2 = R x state  (K = d_state)
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t r0 = lo_k(rop_s), s0 = lo_mn(ring_s);
 #pragma unroll
         for (int kt = 0; kt < NK; ++kt)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            kstep(tA2, rop_s + kt * T128 + k * 32, NK * T128, ring_s + kt * PB * T64 + k * 2048, NK * PB * T64, true, id_v, (kt | k) ? 1u : 0u);
+            kstep(tA2, r0 + ((kt * T128 + k * 32) >> 4), (NK * T128) >> 4, s0 + ((kt * PB * T64 + k * 2048) >> 4), (NK * PB * T64) >> 4, id_v, (kt | k) ? 1u : 0u);
         umma_commit(bar(LD_EMPTY + 0));
       }
       // G of column block jj into TMEM buffer jj & 1
@@ -280,11 +284,12 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
         if (jj >= 2 && !wait(G_FREE + (jj & 1), (uint32_t)(((jj >> 1) - 1) & 1), 4u)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t cop = ring_s + s * GE::STAGE;
+        const uint32_t r0 = lo_k(rop_s), c0d = lo_k(cop);
 #pragma unroll
         for (int kt = 0; kt < NK; ++kt)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            kstep(tG + (uint32_t)((jj & 1) * CW), rop_s + kt * T128 + k * 32, NK * T128, cop + kt * T64 + k * 32, NK * T64, false, id_g, (kt | k) ? 1u : 0u);
+            kstep(tG + (uint32_t)((jj & 1) * CW), r0 + ((kt * T128 + k * 32) >> 4), (NK * T128) >> 4, c0d + ((kt * T64 + k * 32) >> 4), (NK * T64) >> 4, id_g, (kt | k) ? 1u : 0u);
         if (MODE == 1) {
           // dM^T[s,t] = <x~_s, dY_t>: the resident x~ rows times the dY tile of this block read as a K-major operand
           // (its 64 rows of 128 bytes are the same bytes that the product with the masked tile reads MN-major)
@@ -292,8 +297,8 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
           for (int pb = 0; pb < PB; ++pb)
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-              kstep(tDM + (uint32_t)((jj & 1) * CW), rop_s + GE::XR_OFF + pb * T128 + k * 32, PB * T128, cop + GE::COP + pb * T64 + k * 32, PB * T64,
-                    false, id_g, (pb | k) ? 1u : 0u);
+              kstep(tDM + (uint32_t)((jj & 1) * CW), r0 + ((GE::XR_OFF + pb * T128 + k * 32) >> 4), (PB * T128) >> 4,
+                    c0d + ((GE::COP + pb * T64 + k * 32) >> 4), (PB * T64) >> 4, id_g, (pb | k) ? 1u : 0u);
         }
         umma_commit(bar(G_FULL + (jj & 1)));
         return true;
@@ -305,10 +310,10 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
         const int mb = jj % MB, s = (jj + 1) % STAGES;
         if (!wait(M_READY + mb, (uint32_t)((jj / MB) & 1), 8u)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t vb = ring_s + s * GE::STAGE + GE::COP;
+        const uint32_t m0d = lo_k(mop_s + mb * GE::MOP1), v0d = lo_mn(ring_s + s * GE::STAGE + GE::COP);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          kstep(tA1, mop_s + mb * GE::MOP1 + k * 32, T128, vb + k * 2048, PB * T64, true, id_v, (jj | k) ? 1u : 0u);
+          kstep(tA1, m0d + ((k * 32) >> 4), T128 >> 4, v0d + ((k * 2048) >> 4), (PB * T64) >> 4, id_v, (jj | k) ? 1u : 0u);
         umma_commit(bar(LD_EMPTY + s));
         umma_commit(bar(M_FREE + mb));
         if (jj + 2 < ncb && !mma_g(jj + 2)) { ok = false; break; }

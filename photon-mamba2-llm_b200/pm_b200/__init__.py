@@ -108,6 +108,13 @@ def _load():
         "pmb_lm_loss_device": (vp, [vp]),
         "pmb_lm_step_host": (i32, [vp, vp, vp, vp, C.POINTER(f32), LAYER_CALLBACK, vp]),
         "pmb_lm_bad_tokens": (i32, [vp, vp, C.POINTER(i32)]),
+        "pmb_dp_unique_id": (i32, [vp]),
+        "pmb_dp_init": (i32, [i32, i32, vp, C.POINTER(vp)]),
+        "pmb_dp_destroy": (None, [vp]),
+        "pmb_dp_world_size": (i32, [vp]),
+        "pmb_dp_allreduce_async": (i32, [vp, vp, vp, i64]),
+        "pmb_dp_sync": (i32, [vp, vp]),
+        "pmb_lm_step_device_dp": (i32, [vp, vp, vp, vp, vp]),
         "pmb_selftest_bounded_wait": (i32, [vp, C.c_uint32]),
         "pmb_selftest_device_once": (i32, []),
     }
@@ -604,7 +611,13 @@ class FlatMamba:
         _check(lib.pmb_lm_step_device(self._h, _stream(), ids.data_ptr(), targets.data_ptr(), cb, None))
         return self.loss_dev
 
-    def capture_step(self, on_layer_done=None, after=None):
+    def step_device_dp(self, ids, targets, dp: "DataParallel"):
+        """The step with the per-layer gradient all-reduce over `dp` (NCCL behind the C ABI) overlapped with the
+        backward; on return the current stream sees averaged gradients."""
+        _check(lib.pmb_lm_step_device_dp(self._h, _stream(), ids.data_ptr(), targets.data_ptr(), dp._h))
+        return self.loss_dev
+
+    def capture_step(self, on_layer_done=None, after=None, dp=None):
         """One training step (forward + checkpointed backward) captured into a CUDA graph.
 
         Returns a callable `step(ids, targets) -> loss` (0-d device tensor): it copies the int64 token tensors
@@ -622,7 +635,7 @@ class FlatMamba:
             if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
                 raise PmbError(2, "capture_step: callbacks are refused while a process group with more than one rank is "
                                   "initialised (collectives inside the capture are not supported); all-reduce after the replay")
-        return _GraphStep(self, on_layer_done, after)
+        return _GraphStep(self, on_layer_done, after, dp)
 
     def bad_tokens(self) -> int:
         """Reads and clears the flag word for out-of-range input (bit 0: a token id, bit 1: a target); the step
@@ -658,8 +671,42 @@ class FlatMamba:
             pass
 
 
+class DataParallel:
+    """NCCL communicator of the library (pmb_dp_*).  `unique_id()` on rank 0, hand the 128 bytes to the other ranks,
+    then every rank constructs `DataParallel(nranks, rank, id)` with its device current."""
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        _check(lib.pmb_dp_unique_id(buf))
+        return buf.raw
+
+    def __init__(self, nranks: int, rank: int, unique_id: bytes):
+        h = C.c_void_p()
+        buf = C.create_string_buffer(bytes(unique_id), 128)
+        _check(lib.pmb_dp_init(nranks, rank, buf, C.byref(h)))
+        self._h, self.nranks, self.rank = h, nranks, rank
+
+    def all_reduce_async(self, t: torch.Tensor):
+        _check(lib.pmb_dp_allreduce_async(self._h, _stream(), _dev(t, "tensor").data_ptr(), t.numel()))
+
+    def sync(self):
+        _check(lib.pmb_dp_sync(self._h, _stream()))
+
+    def close(self):
+        if self._h:
+            lib.pmb_dp_destroy(self._h)
+            self._h = None
+
+
 class _GraphStep:
-    def __init__(self, lm: "FlatMamba", on_layer_done, after):
+    def __init__(self, lm: "FlatMamba", on_layer_done, after, dp=None):
+        if dp is not None:
+            # the whole data-parallel step is one library call: no host callback and no torch process group inside
+            # the capture, only this library's streams, events and NCCL's own kernels
+            step_fn = lambda: lm.step_device_dp(self.ids, self.targets, dp)
+        else:
+            step_fn = lambda: lm.step_device(self.ids, self.targets, on_layer_done)
         dev = lm.loss_dev.device
         self.ids = torch.zeros(lm.batch, lm.seqlen, dtype=torch.int64, device=dev)
         self.targets = torch.zeros_like(self.ids)
@@ -668,7 +715,7 @@ class _GraphStep:
         side.wait_stream(cur)
         with torch.cuda.stream(side):
             for _ in range(2):
-                lm.step_device(self.ids, self.targets, on_layer_done)
+                step_fn()
                 if after:
                     after()
         cur.wait_stream(side)
@@ -676,7 +723,7 @@ class _GraphStep:
         n0 = launch_count()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
-            self.loss = lm.step_device(self.ids, self.targets, on_layer_done)
+            self.loss = step_fn()
             if after:
                 after()
         self.launches_per_step = launch_count() - n0     # kernels of this library inside one replay
