@@ -317,6 +317,36 @@ pmb_status pmb_lm_bad_tokens(pmb_lm* lm, void* stream, int32_t* h_flags_out);
 pmb_status pmb_lm_step_host(pmb_lm* lm, void* stream, const int64_t* h_ids, const int64_t* h_targets,
                             float* h_loss, pmb_layer_callback on_layer_done, void* user);
 
+/* ---- primitive ops: what the rest of pm_core::Ops needs on the device when an op sequence is not the fused block
+ * (crates/pm-core/src/ops.rs): contiguous fp32 tensors unless a stride is given; every result is a new buffer the
+ * caller owns.  Views (Ops::narrow / transpose / broadcast_as / reshape / concat, ops.rs:123-148) are one strided
+ * copy: describe the source view by extents, element strides (0 broadcasts) and a start offset; concat is one copy
+ * per input into an offset of the output.  pmb_unary_f32 serves neg / exp / sqrt / silu / sigmoid / softplus /
+ * mul_scalar / add_scalar (ops.rs:80,98-100,166,310-319) and plain copies; pmb_binary_f32 serves add / sub / mul /
+ * div (ops.rs:77-79,316) on equal shapes (broadcast the smaller operand with pmb_strided_copy_f32 first). */
+enum { PMB_MAX_RANK = 6 };
+enum { PMB_OP_COPY = 0, PMB_OP_NEG = 1, PMB_OP_EXP = 2, PMB_OP_SQRT = 3, PMB_OP_SILU = 4, PMB_OP_SIGMOID = 5, PMB_OP_SOFTPLUS = 6,
+       PMB_OP_MUL_SCALAR = 7, PMB_OP_ADD_SCALAR = 8,
+       PMB_OP_ADD = 16, PMB_OP_SUB = 17, PMB_OP_MUL = 18, PMB_OP_DIV = 19 };
+pmb_status pmb_unary_f32(void* stream, int32_t op, const float* d_x, float scalar, float* d_out, int64_t n);
+pmb_status pmb_binary_f32(void* stream, int32_t op, const float* d_a, const float* d_b, float* d_out, int64_t n);
+pmb_status pmb_strided_copy_f32(void* stream, const float* d_src, int32_t rank, const int64_t* h_shape,
+                                const int64_t* h_strides, int64_t offset, float* d_out);
+/* Ops::embedding (ops.rs:158-164): out[r,:] = table[ids[r],:]; an id outside [0, vocab) yields a zero row and sets
+ * *d_bad_flag (a device word the caller clears and polls), since the reference fails on such input. */
+pmb_status pmb_embedding_f32(void* stream, const float* d_table, int64_t vocab, int64_t width, const int64_t* d_ids,
+                             int64_t rows, float* d_out, uint32_t* d_bad_flag);
+/* Ops::gather along the last axis with one index per row (ops.rs:296-302): out[r] = x[r, index[r]]. */
+pmb_status pmb_gather_last_f32(void* stream, const float* d_x, const int64_t* d_index, int64_t rows, int64_t width,
+                               float* d_out, uint32_t* d_bad_flag);
+/* Ops::log_softmax over the last axis (ops.rs:292). */
+pmb_status pmb_log_softmax_f32(void* stream, const float* d_x, int64_t rows, int64_t width, float* d_out);
+/* Ops::sum_all / mean_all (ops.rs:304-307): a device scalar, two fixed-order passes. */
+size_t     pmb_sum_workspace_bytes(void);
+pmb_status pmb_sum_all_f32(void* stream, const float* d_x, int64_t n, int32_t mean, float* d_out, void* d_ws, size_t ws_bytes);
+/* Ops::cumsum (ops.rs:120) along an axis of length `len` of a tensor viewed as (outer, len, inner). */
+pmb_status pmb_cumsum_f32(void* stream, const float* d_x, int64_t outer, int64_t len, int64_t inner, float* d_out);
+
 /* ---- data parallelism (no counterpart in the reference, which drives one device: crates/pm-cli/src/train_cmd.rs:50).
  * The path shards over batch with no data-path collective; the one exchange per step is the average of the parameter
  * gradients.  One process (or host thread) per GPU: rank 0 obtains an id with pmb_dp_unique_id and hands its 128 bytes

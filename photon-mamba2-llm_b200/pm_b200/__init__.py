@@ -108,6 +108,15 @@ def _load():
         "pmb_lm_loss_device": (vp, [vp]),
         "pmb_lm_step_host": (i32, [vp, vp, vp, vp, C.POINTER(f32), LAYER_CALLBACK, vp]),
         "pmb_lm_bad_tokens": (i32, [vp, vp, C.POINTER(i32)]),
+        "pmb_unary_f32": (i32, [vp, i32, vp, f32, vp, i64]),
+        "pmb_binary_f32": (i32, [vp, i32, vp, vp, vp, i64]),
+        "pmb_strided_copy_f32": (i32, [vp, vp, i32, C.POINTER(i64), C.POINTER(i64), i64, vp]),
+        "pmb_embedding_f32": (i32, [vp, vp, i64, i64, vp, i64, vp, vp]),
+        "pmb_gather_last_f32": (i32, [vp, vp, vp, i64, i64, vp, vp]),
+        "pmb_log_softmax_f32": (i32, [vp, vp, i64, i64, vp]),
+        "pmb_sum_workspace_bytes": (sz, []),
+        "pmb_sum_all_f32": (i32, [vp, vp, i64, i32, vp, vp, sz]),
+        "pmb_cumsum_f32": (i32, [vp, vp, i64, i64, i64, vp]),
         "pmb_dp_unique_id": (i32, [vp]),
         "pmb_dp_init": (i32, [i32, i32, vp, C.POINTER(vp)]),
         "pmb_dp_destroy": (None, [vp]),
@@ -229,6 +238,78 @@ def init_block_params(config: Mamba2Config, seed: int) -> dict:
         "norm_weight": torch.ones(sh["norm_weight"]),
         "out_proj_weight": uni(sh["out_proj_weight"], 1 / math.sqrt(config.d_inner), 7),
     }
+
+
+# ---- primitive ops (the rest of pm_core::Ops; see include/pm_b200.h)
+UNARY = {"copy": 0, "neg": 1, "exp": 2, "sqrt": 3, "silu": 4, "sigmoid": 5, "softplus": 6, "mul_scalar": 7, "add_scalar": 8}
+BINARY = {"add": 16, "sub": 17, "mul": 18, "div": 19}
+
+
+def unary(op: str, x: torch.Tensor, scalar: float = 0.0) -> torch.Tensor:
+    x = _dev(x, "x"); out = torch.empty_like(x)
+    _check(lib.pmb_unary_f32(_stream(), UNARY[op], x.data_ptr(), scalar, out.data_ptr(), x.numel()))
+    return out
+
+
+def binary(op: str, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    a, b = _dev(a, "a"), _dev(b, "b")
+    if a.shape != b.shape:
+        raise PmbError(1, f"binary {op}: shapes differ {tuple(a.shape)} vs {tuple(b.shape)}")
+    out = torch.empty_like(a)
+    _check(lib.pmb_binary_f32(_stream(), BINARY[op], a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel()))
+    return out
+
+
+def strided_copy(src: torch.Tensor, shape, strides, offset: int = 0) -> torch.Tensor:
+    """narrow / transpose / broadcast_as as one copy: `shape`, element `strides` (0 broadcasts) and start `offset`
+    describe the view of the contiguous fp32 buffer `src`."""
+    src = _dev(src, "src")
+    out = torch.empty(tuple(shape), device=src.device, dtype=torch.float32)
+    sh = (C.c_int64 * len(shape))(*shape); st = (C.c_int64 * len(shape))(*strides)
+    _check(lib.pmb_strided_copy_f32(_stream(), src.data_ptr(), len(shape), sh, st, offset, out.data_ptr()))
+    return out
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor):
+    table = _dev(table, "table")
+    out = torch.empty(ids.numel(), table.shape[1], device=table.device, dtype=torch.float32)
+    bad = torch.zeros(1, device=table.device, dtype=torch.int32)
+    _check(lib.pmb_embedding_f32(_stream(), table.data_ptr(), table.shape[0], table.shape[1], ids.data_ptr(), ids.numel(), out.data_ptr(), bad.data_ptr()))
+    return out.reshape(*ids.shape, table.shape[1]), bad
+
+
+def gather_last(x: torch.Tensor, index: torch.Tensor):
+    x = _dev(x, "x")
+    out = torch.empty(x.shape[0], device=x.device, dtype=torch.float32)
+    bad = torch.zeros(1, device=x.device, dtype=torch.int32)
+    _check(lib.pmb_gather_last_f32(_stream(), x.data_ptr(), index.data_ptr(), x.shape[0], x.shape[1], out.data_ptr(), bad.data_ptr()))
+    return out, bad
+
+
+def log_softmax(x: torch.Tensor) -> torch.Tensor:
+    x = _dev(x, "x"); out = torch.empty_like(x)
+    _check(lib.pmb_log_softmax_f32(_stream(), x.data_ptr(), x.numel() // x.shape[-1], x.shape[-1], out.data_ptr()))
+    return out
+
+
+def sum_all(x: torch.Tensor, mean: bool = False) -> torch.Tensor:
+    x = _dev(x, "x")
+    out = torch.empty(1, device=x.device, dtype=torch.float32)
+    ws = torch.empty(lib.pmb_sum_workspace_bytes(), device=x.device, dtype=torch.uint8)
+    _check(lib.pmb_sum_all_f32(_stream(), x.data_ptr(), x.numel(), int(mean), out.data_ptr(), ws.data_ptr(), ws.numel()))
+    return out
+
+
+def cumsum(x: torch.Tensor, dim: int) -> torch.Tensor:
+    x = _dev(x, "x"); out = torch.empty_like(x)
+    outer = 1
+    for s_ in x.shape[:dim]:
+        outer *= s_
+    inner = 1
+    for s_ in x.shape[dim + 1:]:
+        inner *= s_
+    _check(lib.pmb_cumsum_f32(_stream(), x.data_ptr(), outer, x.shape[dim], inner, out.data_ptr()))
+    return out
 
 
 def selftest_bounded_wait(polls: int = 4096):

@@ -63,3 +63,13 @@ def test_per_device_once_table():
     """The "set once per device" flags behind cudaFuncSetAttribute are per device ordinal (host logic, no GPU)."""
     import pm_b200
     assert pm_b200.lib.pmb_selftest_device_once() == 0
+
+
+def test_rust_ffi_declares_every_symbol():
+    """rust/pm-b200/src/ffi.rs (uncompiled adaptor source) names exactly the functions the public header declares."""
+    header = (ROOT / "include" / "pm_b200.h").read_text()
+    body = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(pmb_[a-z0-9_]+)\s*\(", body)) - {"pmb_layer_callback"}
+    ffi = (ROOT / "rust" / "pm-b200" / "src" / "ffi.rs").read_text()
+    bound = set(re.findall(r"pub fn (pmb_[a-z0-9_]+)\s*\(", ffi))
+    assert bound == declared, sorted(bound ^ declared)
