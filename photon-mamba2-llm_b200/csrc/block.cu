@@ -75,7 +75,8 @@ bool block_uses_pairs(const Dims& d) { return gemm_pairs_enabled() && !(d.D % 8)
 // backward part.  With nslots == 2 the forward part exists twice, so that the recompute of the next block can run
 // (on another stream) while the gradient kernels of the current block still read the other copy; `slot` selects
 // the copy this BlockWs points at.
-static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* out, bool bf16 = false, int nslots = 1, int slot = 0) {
+// presplit: the caller brings (hi, lo) pairs of the two projection weights (the LM handle does), so none are kept here
+static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* out, bool bf16 = false, int nslots = 1, int slot = 0, bool presplit = false) {
   Arena ar(base, bytes);
   BlockWs w{};
   const bool pairs = !bf16 && block_uses_pairs(d);
@@ -89,23 +90,21 @@ static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* 
     f.rstd = ar.take<float>((size_t)d.M);
     f.normed = ar.take<float>(pairs ? 0 : mi);       // with pair GEMMs the normalised output only exists as a pair
     f.Aneg = ar.take<float>((size_t)d.H);
-    {
-      size_t need = ssd_ws_layout(d.B, d.T, d.H, d.P, d.N, d.G, d.Q, nullptr, 0, nullptr);
-      char* sub = ar.take<char>(need);
-      if (sub) ssd_ws_layout(d.B, d.T, d.H, d.P, d.N, d.G, d.Q, sub, need, &f.ssd);
-    }
+    ssd_ws_take(ar, d.B, d.T, d.H, d.P, d.N, d.G, d.Q, &f.ssd, 1);     // what the scan's forward leaves for its backward
     f.normed16 = ar.take<uint16_t>(bf16 ? mi : 0);
     if (pairs) {
       f.x_hi = ar.take<uint16_t>(md); f.x_lo = ar.take<uint16_t>(md);
       f.normed_hi = ar.take<uint16_t>(mi); f.normed_lo = ar.take<uint16_t>(mi);
-      f.win_hi = ar.take<uint16_t>(dj); f.win_lo = ar.take<uint16_t>(dj);
+      if (!presplit) { f.win_hi = ar.take<uint16_t>(dj); f.win_lo = ar.take<uint16_t>(dj); }
     }
     if (sl == slot) w = f;
   }
   // the gradient of the normalised gate output may overwrite it: dW_out (which reads `normed`, or its bf16 copy)
   // is enqueued before the GEMM that writes `dnormed`.  With pair GEMMs there is no fp32 `normed` to reuse.
+  ssd_ws_take(ar, d.B, d.T, d.H, d.P, d.N, d.G, d.Q, &w.ssd, 2);       // the scan's backward-only buffers: one copy
   w.dnormed = pairs ? ar.take<float>(mi) : w.normed;
-  w.dxzd = ar.take<float>(mj);
+  // (with pair GEMMs the three producers of dxzd write the pair directly and the fp32 copy is never formed)
+  w.dxzd = pairs ? nullptr : ar.take<float>(mj);
   w.dact = ar.take<float>((size_t)d.M * d.X);
   w.ddt = ar.take<float>((size_t)d.M * d.H);
   w.dA = ar.take<float>((size_t)d.H);
@@ -118,14 +117,14 @@ static size_t block_ws_layout(const Dims& d, void* base, size_t bytes, BlockWs* 
   if (pairs) {
     w.dout_hi = ar.take<uint16_t>(md); w.dout_lo = ar.take<uint16_t>(md);
     w.dxzd_hi = ar.take<uint16_t>(mj); w.dxzd_lo = ar.take<uint16_t>(mj);
-    w.wout_hi = ar.take<uint16_t>(id); w.wout_lo = ar.take<uint16_t>(id);
+    if (!presplit) { w.wout_hi = ar.take<uint16_t>(id); w.wout_lo = ar.take<uint16_t>(id); }
   }
   if (out) *out = w;
   return ar.ok ? ar.used() : 0;
 }
 
 size_t block_ws_bytes(const Dims& d, bool bf16) { return block_ws_layout(d, nullptr, 0, nullptr, bf16); }
-size_t stack_ws_bytes(const Dims& d, bool bf16) { return block_ws_layout(d, nullptr, 0, nullptr, bf16, 2, 0); }
+size_t stack_ws_bytes(const Dims& d, bool bf16, bool presplit) { return block_ws_layout(d, nullptr, 0, nullptr, bf16, 2, 0, presplit); }
 
 static SsdIn ssd_inputs(const Dims& d, const pmb_block_params& p, const BlockWs& w) {
   SsdIn in{};
@@ -184,7 +183,7 @@ pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, 
   const Weights16* w16 = storage_is_bf16(wx) ? wx : nullptr;
   const bool pr = !w16 && block_uses_pairs(d);
   BlockWs w;
-  if (block_ws_layout(d, ws, ws_bytes, &w, w16 != nullptr) == 0 || !ws)
+  if (block_ws_layout(d, ws, ws_bytes, &w, w16 != nullptr, 1, 0, wx && wx->pairs) == 0 || !ws)
     return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_bytes(d, w16 != nullptr));
   PMB_TRY(block_fwd_core(st, d, p, x, w, wx));
   if (w16) PMB_TRY(gemm_bf16(st, 0, 0, d.M, d.D, d.I, w.normed16, d.I, w16->out_proj, d.D, out, d.D, residual, 1));
@@ -204,7 +203,7 @@ static pmb_status block_recompute(cudaStream_t st, const Dims& d, const pmb_bloc
                                   const Weights16* wx, int nslots, int slot) {
   const bool bf = storage_is_bf16(wx);
   BlockWs w;
-  if (block_ws_layout(d, ws, ws_bytes, &w, bf, nslots, slot) == 0 || !ws)
+  if (block_ws_layout(d, ws, ws_bytes, &w, bf, nslots, slot, wx && wx->pairs) == 0 || !ws)
     return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_layout(d, nullptr, 0, nullptr, bf, nslots, 0));
   return block_fwd_core(st, d, p, x, w, wx);
 }
@@ -215,7 +214,7 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   const Weights16* w16 = storage_is_bf16(wx) ? wx : nullptr;
   const bool pr = !w16 && block_uses_pairs(d);
   BlockWs w;
-  if (block_ws_layout(d, ws, ws_bytes, &w, w16 != nullptr, nslots, slot) == 0 || !ws)
+  if (block_ws_layout(d, ws, ws_bytes, &w, w16 != nullptr, nslots, slot, wx && wx->pairs) == 0 || !ws)
     return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_layout(d, nullptr, 0, nullptr, w16 != nullptr, nslots, 0));
   // The out_proj gradients do not wait for the recompute (dnormed = dout W_out^T needs neither x nor the recomputed
   // activations) and dW_out is needed only when the block is done: with pair GEMMs both go to a side stream, where
@@ -370,7 +369,7 @@ pmb_status stack_bwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_blo
   SideLane* rl = nullptr;
   // (fp32 blocks whose dimensions rule out pre-split pairs send their GEMMs through the library's one scratch
   // buffer, which two streams must not share: those stay serial)
-  if (ahead_on && n_layers > 1 && (bf || block_uses_pairs(d)) && ws_bytes >= stack_ws_bytes(d, bf)) PMB_TRY(get_side_lane(3, &rl));
+  if (ahead_on && n_layers > 1 && (bf || block_uses_pairs(d)) && ws_bytes >= stack_ws_bytes(d, bf, w16 && w16->pairs)) PMB_TRY(get_side_lane(3, &rl));
   if (!rl) {
     for (int l = n_layers - 1; l >= 0; --l) {
       PMB_TRY(block_bwd(st, d, layers[l], base + (size_t)l * slot, dhidden, dhidden, dhidden, grads[l], ws, ws_bytes, w16 ? &w16[l] : nullptr));
@@ -420,7 +419,7 @@ pmb_status stack_bwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_blo
 extern "C" size_t pmb_stack_workspace_bytes(const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen) {
   Dims d;
   if (make_dims(cfg, batch, seqlen, &d) != PMB_OK) return 0;
-  return stack_ws_bytes(d, false);
+  return stack_ws_bytes(d, false, false);
 }
 
 extern "C" pmb_status pmb_stack_fwd_ckpt(void* stream, const pmb_mamba2_config* cfg, int32_t n_layers,

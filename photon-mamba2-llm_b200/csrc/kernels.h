@@ -83,6 +83,9 @@ struct SsdWs {            // persistent between fwd and bwd of one scan
   float* rpart;              // (B,nc,H,Q/128,Q) partial row sums of W (fused backward)
 };
 size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base, size_t bytes, SsdWs* out);
+// the same buffers taken from a caller's arena in two parts: bit 0 = forward-written / backward-read, bit 1 = backward only
+struct Arena;
+void ssd_ws_take(Arena& ar, int B, int T, int H, int P, int N, int G, int Q, SsdWs* w, int part);
 pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, float* y, int64_t ldy,
                    float* final_state, const SsdWs& ws);
 // Backward.  dy (stride lddy) is the gradient w.r.t. y (skip term included when in.D != NULL).
@@ -148,7 +151,7 @@ struct Weights16 {
 inline bool storage_is_bf16(const Weights16* w) { return w && !w->pairs; }
 bool block_uses_pairs(const Dims& d);   // fp32 blocks route their four projections' GEMMs through bf16 pairs
 size_t block_ws_bytes(const Dims& d, bool bf16 = false);
-size_t stack_ws_bytes(const Dims& d, bool bf16 = false);   // two forward slots: lets stack_bwd recompute one block ahead
+size_t stack_ws_bytes(const Dims& d, bool bf16 = false, bool presplit = false);   // two forward slots: lets stack_bwd recompute one block ahead
 pmb_status cast_f32_bf16(cudaStream_t st, const float* src, uint16_t* dst, int64_t n);
 pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* residual,
                      void* out, void* ws, size_t ws_bytes, const Weights16* w16);

@@ -339,7 +339,7 @@ static pmb_status lm_create_impl(const pmb_mamba2_config* cfg, int L0, int L1, i
     for (int w = 0; w < 8; ++w) lm->off.push_back(place(tensor_elems(d, w)));
   }
   lm->n_params = o;
-  lm->ws_bytes = stack_ws_bytes(d, lm->bf16 != 0);   // two forward slots: the backward recomputes one block ahead
+  lm->ws_bytes = stack_ws_bytes(d, lm->bf16 != 0, !bf16_storage && block_uses_pairs(d));   // two forward slots: the backward recomputes one block ahead
   const size_t esz = lm->bf16 ? 2 : 4;
   size_t slot = (size_t)d.M * d.D * esz;
   size_t slot1 = L1 > 0 ? (size_t)lm->d1.M * d.D * esz : 0;

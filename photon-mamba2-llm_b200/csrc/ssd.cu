@@ -788,53 +788,63 @@ static int pick_nsplit(int batches, int tiles, int hpg) {
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
+static bool fused_enabled();
+
+// Buffers of one scan.  part bit 0: what the forward writes and the backward reads (kept per forward slot by the
+// block workspace); bit 1: what only the backward touches (one copy).  Fields of the other part are left alone.
+void ssd_ws_take(Arena& ar, int B, int T, int H, int P, int N, int G, int Q, SsdWs* wp, int part) {
+  SsdWs& w = *wp;
+  const int nc = T / Q;
+  const bool tcshape = Q % 64 == 0 && N % 32 == 0 && P % 64 == 0;
+  const bool fz = ssd_fused_supported(P, N, Q, true) && fused_enabled();
+  const size_t hp = (size_t)B * T * H * P, gn = (size_t)B * T * 2 * G * N, stn = (size_t)B * nc * H * N * P, qq = (size_t)B * nc * G * Q * Q;
+  if (part & 1) {
+    w.S = ar.take<float>((size_t)B * H * T);
+    w.hprev = ar.take<float>(stn);
+    w.hlast = ar.take<float>((size_t)B * H * N * P);
+    if (!fz) w.CB = ar.take<float>(qq);
+    w.xs = ar.take<float>(tcshape ? hp : 0);
+    // bf16 (hi, lo) pairs of the operands of the fused intra-chunk kernels, and the carried-state part of y
+    w.xt_hi = fz ? ar.take<uint16_t>(hp) : nullptr; w.xt_lo = fz ? ar.take<uint16_t>(hp) : nullptr;
+    w.bc_hi = fz ? ar.take<uint16_t>(gn) : nullptr; w.bc_lo = fz ? ar.take<uint16_t>(gn) : nullptr;
+    w.hp_hi = fz ? ar.take<uint16_t>(stn) : nullptr; w.hp_lo = fz ? ar.take<uint16_t>(stn) : nullptr;
+    w.yoff = fz ? ar.take<float>(hp) : nullptr;
+  }
+  if (part & 2) {
+    if (fz) w.CB = ar.take<float>(qq);     // only for a backward that cannot take the fused kernel after a forward that did
+    w.dh = ar.take<float>(stn);
+    w.dG = ar.take<float>(qq);
+    w.dxt = ar.take<float>(hp);
+    w.rows = ar.take<float>((size_t)4 * B * T * H);
+    w.part = ar.take<float>((size_t)B * nc * 2 * H);
+    {
+      int nbcg = B * nc * G, hpg = H / G, qt = (int)cdiv(Q, BM);
+      size_t a = (size_t)pick_nsplit(nbcg, qt * (qt + 1) / 2, hpg) * nbcg * Q * Q;
+      size_t b = (size_t)pick_nsplit(nbcg, qt * (int)cdiv(N, BN), hpg) * nbcg * Q * N;
+      size_t need = a > b ? a : b;
+      if (tcshape) {
+        // tensor-core path: the head-split dB / dC partial tiles
+        size_t dbc = (size_t)ssd_tc_dbc_nsplit_dims(B, T, H, N, G, Q) * nbcg * Q * N;
+        if (dbc > need) need = dbc;
+        size_t dgp = (size_t)ssd_tc_dg_nsplit_dims(B, T, H, G, Q) * nbcg * Q * Q;
+        if (dgp > need) need = dgp;
+      }
+      w.splitk = ar.take<float>(need);
+    }
+    w.dys = ar.take<float>(tcshape ? hp : 0);
+    w.dy_hi = fz ? ar.take<uint16_t>(hp) : nullptr; w.dy_lo = fz ? ar.take<uint16_t>(hp) : nullptr;
+    w.dh_hi = fz ? ar.take<uint16_t>(stn) : nullptr; w.dh_lo = fz ? ar.take<uint16_t>(stn) : nullptr;
+    // the sums of W that the fused backward kernel leaves for the row-sum kernel
+    w.csum = fz ? ar.take<float>((size_t)B * T * H) : nullptr;
+    w.esum = fz ? ar.take<float>((size_t)B * T * H) : nullptr;
+    w.rpart = fz ? ar.take<float>((size_t)B * T * H * (Q / 128)) : nullptr;
+  }
+}
+
 size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base, size_t bytes, SsdWs* out) {
   Arena ar(base, bytes);
-  int nc = T / Q;
-  SsdWs w;
-  w.S = ar.take<float>((size_t)B * H * T);
-  w.hprev = ar.take<float>((size_t)B * nc * H * N * P);
-  w.hlast = ar.take<float>((size_t)B * H * N * P);
-  w.CB = ar.take<float>((size_t)B * nc * G * Q * Q);
-  w.dh = ar.take<float>((size_t)B * nc * H * N * P);
-  w.dG = ar.take<float>((size_t)B * nc * G * Q * Q);
-  w.dxt = ar.take<float>((size_t)B * T * H * P);
-  w.rows = ar.take<float>((size_t)4 * B * T * H);
-  w.part = ar.take<float>((size_t)B * nc * 2 * H);
-  {
-    int nbcg = B * nc * G, hpg = H / G, qt = (int)cdiv(Q, BM);
-    size_t a = (size_t)pick_nsplit(nbcg, qt * (qt + 1) / 2, hpg) * nbcg * Q * Q;
-    size_t b = (size_t)pick_nsplit(nbcg, qt * (int)cdiv(N, BN), hpg) * nbcg * Q * N;
-    size_t need = a > b ? a : b;
-    if (Q % 64 == 0 && N % 32 == 0 && P % 64 == 0) {
-      // tensor-core path: the head-split dB / dC partial tiles
-      size_t dbc = (size_t)ssd_tc_dbc_nsplit_dims(B, T, H, N, G, Q) * nbcg * Q * N;
-      if (dbc > need) need = dbc;
-      size_t dgp = (size_t)ssd_tc_dg_nsplit_dims(B, T, H, G, Q) * nbcg * Q * Q;
-      if (dgp > need) need = dgp;
-    }
-    w.splitk = ar.take<float>(need);
-    bool tcshape = Q % 64 == 0 && N % 32 == 0 && P % 64 == 0;
-    w.xs = ar.take<float>(tcshape ? (size_t)B * T * H * P : 0);
-    w.dys = ar.take<float>(tcshape ? (size_t)B * T * H * P : 0);
-    // bf16 (hi, lo) pairs of the operands of the fused intra-chunk kernels
-    const bool fz = ssd_fused_supported(P, N, Q, true);
-    const size_t hp = fz ? (size_t)B * T * H * P : 0, gn = fz ? (size_t)B * T * 2 * G * N : 0, stn = fz ? (size_t)B * nc * H * N * P : 0;
-    w.xt_hi = ar.take<uint16_t>(hp); w.xt_lo = ar.take<uint16_t>(hp);
-    w.bc_hi = ar.take<uint16_t>(gn); w.bc_lo = ar.take<uint16_t>(gn);
-    w.dy_hi = ar.take<uint16_t>(hp); w.dy_lo = ar.take<uint16_t>(hp);
-    w.hp_hi = ar.take<uint16_t>(stn); w.hp_lo = ar.take<uint16_t>(stn);
-    w.dh_hi = ar.take<uint16_t>(stn); w.dh_lo = ar.take<uint16_t>(stn);
-    // fused path: the carried-state part of y (kept for the backward) and the sums of W the backward kernel leaves
-    w.yoff = ar.take<float>(hp);
-    w.csum = ar.take<float>(fz ? (size_t)B * T * H : 0);
-    w.esum = ar.take<float>(fz ? (size_t)B * T * H : 0);
-    w.rpart = ar.take<float>(fz ? (size_t)B * T * H * (Q / 128) : 0);
-    if (!fz) {   // (a zero-sized take still yields an address: make "absent" testable)
-      w.xt_hi = w.xt_lo = w.bc_hi = w.bc_lo = w.dy_hi = w.dy_lo = w.hp_hi = w.hp_lo = w.dh_hi = w.dh_lo = nullptr;
-      w.yoff = w.csum = w.esum = w.rpart = nullptr;
-    }
-  }
+  SsdWs w{};
+  ssd_ws_take(ar, B, T, H, P, N, G, Q, &w, 3);
   if (out) *out = w;
   return ar.ok ? ar.used() : 0;
 }
