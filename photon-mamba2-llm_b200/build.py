@@ -9,7 +9,7 @@ HERE = pathlib.Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT = HERE / "pm_b200" / "libpm_b200.so"
 OBJ = HERE / "build"
-SOURCES = ["abi.cu", "elementwise.cu", "ssd.cu", "gemm_simt.cu", "gemm_tc.cu", "block.cu", "lm.cu", "decode.cu", "ssd_tc.cu", "ssd_fused.cu", "gemm_bf16.cu", "gemm_tc_small.cu", "optim.cu", "dp.cu", "primitives.cu", "checkpoint.cu"]
+SOURCES = ["abi.cu", "elementwise.cu", "ssd.cu", "gemm_simt.cu", "gemm_tc.cu", "block.cu", "lm.cu", "decode.cu", "ssd_tc.cu", "ssd_fused.cu", "ssd_pairs.cu", "gemm_bf16.cu", "gemm_tc_small.cu", "optim.cu", "dp.cu", "primitives.cu", "checkpoint.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 
 

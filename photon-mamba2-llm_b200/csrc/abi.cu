@@ -139,6 +139,8 @@ extern "C" pmb_status pmb_device_status(int32_t* h_word_out) {
   w |= w2 << 24;
   PMB_TRY(read_clear_device_status_fused(&w2));   // shares the scan kernels' byte
   w |= (w2 & 0x7fu) << 8;
+  PMB_TRY(read_clear_device_status_pairs(&w2));
+  w |= (w2 & 0x7fu) << 8;
   if (h_word_out) *h_word_out = (int32_t)w;
   return PMB_OK;
 }

@@ -259,8 +259,13 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   NormBwdExtra ex{};
   ex.dz_hi = ph; ex.dz_lo = pl;
   if ((pr || w16) && ssd_tc_supported(sin) && (d.P % 4 == 0)) {
-    ex.dys = w.ssd.dys; ex.S = w.ssd.S; ex.H = d.H; ex.P = d.P; ex.T = d.T; sin.dys_ready = true;
-    if (w.ssd.dy_hi) { ex.dy_hi = w.ssd.dy_hi; ex.dy_lo = w.ssd.dy_lo; sin.dy_pair_ready = true; }   // dY pair for the fused scan backward
+    ex.S = w.ssd.S; ex.H = d.H; ex.P = d.P; ex.T = d.T; sin.dys_ready = true;
+    if (w.ssd.dy_hi) {   // the scan backward runs on bf16 pairs: dY and dY exp(S) leave the norm backward as pairs
+      ex.dy_hi = w.ssd.dy_hi; ex.dy_lo = w.ssd.dy_lo; sin.dy_pair_ready = true;
+      ex.dys_hi = w.ssd.dys_hi; ex.dys_lo = w.ssd.dys_lo;
+    } else {
+      ex.dys = w.ssd.dys;
+    }
   }
   PMB_TRY(gated_rmsnorm_bwd(st, d.M, d.I, w.dnormed, w.y, w.xzd, d.J, p.norm_weight, w.rstd, w.dnormed, w.dxzd, d.J,
                             g.norm_weight, w.scratch2, w.scratch2_bytes, gl, &ex));

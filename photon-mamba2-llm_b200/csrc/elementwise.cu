@@ -251,9 +251,12 @@ __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restr
   }
 }
 
-constexpr int CONV_BWD_TT = 16;
+// time steps per thread: short runs put enough threads in flight at a few thousand tokens (the kernel is
+// latency-bound there), long runs re-read fewer halo rows and write fewer partial sums at large token counts
+static int conv_bwd_tt(const Dims& d) { return d.M >= 32768 ? 16 : (d.M >= 8192 ? 8 : 4); }
 
 size_t conv_bwd_ws_bytes(const Dims& d) {
+  const int CONV_BWD_TT = conv_bwd_tt(d);
   int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;
   return align_up((size_t)d.B * tblocks * d.X * (d.K + 1) * sizeof(float), 256);
 }
@@ -261,15 +264,20 @@ size_t conv_bwd_ws_bytes(const Dims& d) {
 template <int K>
 static pmb_status launch_conv_bwd_k(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
                                     const float* dact, float* dxzd, float* partial, uint16_t* pair_hi, uint16_t* pair_lo) {
-  int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;
+  const int tt = conv_bwd_tt(d);
+  int tblocks = (d.T + tt - 1) / tt;
   bool vec = (d.X % 4 == 0) && (d.J % 4 == 0) && (d.I % 4 == 0) &&
              ((reinterpret_cast<uintptr_t>(xzd) | reinterpret_cast<uintptr_t>(dact) | reinterpret_cast<uintptr_t>(dxzd)) % 16 == 0);
   if (vec) {
     dim3 grid((unsigned)cdiv(d.X / 4, 128), (unsigned)(d.B * tblocks));
-    conv_silu_bwd_kernel<K, 4, CONV_BWD_TT><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
+    if (tt == 16) conv_silu_bwd_kernel<K, 4, 16><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
+    else if (tt == 8) conv_silu_bwd_kernel<K, 4, 8><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
+    else conv_silu_bwd_kernel<K, 4, 4><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
   } else {
     dim3 grid((unsigned)cdiv(d.X, 128), (unsigned)(d.B * tblocks));
-    conv_silu_bwd_kernel<K, 1, CONV_BWD_TT><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
+    if (tt == 16) conv_silu_bwd_kernel<K, 1, 16><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
+    else if (tt == 8) conv_silu_bwd_kernel<K, 1, 8><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
+    else conv_silu_bwd_kernel<K, 1, 4><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
   }
   PMB_LAUNCHED();
   return PMB_OK;
@@ -291,7 +299,8 @@ pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const
     case 8: PMB_TRY(launch_conv_bwd_k<8>(st, d, xzd, w, b, dact, dxzd, partial, pair_hi, pair_lo)); break;
     default: return fail(PMB_ERR_SHAPE, "d_conv %d unsupported", d.K);
   }
-  int tblocks = (d.T + CONV_BWD_TT - 1) / CONV_BWD_TT;
+  const int tt = conv_bwd_tt(d);
+  int tblocks = (d.T + tt - 1) / tt;
   int64_t rows = (int64_t)d.B * tblocks;
   cudaStream_t rs = st;
   if (red) { PMB_TRY(order_after(st, red->ev[4], red->s)); rs = red->s; }
@@ -543,6 +552,12 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_bwd_vec_kernel(con
         if (ex.dz_hi) store_pair4(ex.dz_hi + row * lddz + 4 * i, ex.dz_lo + row * lddz + 4 * i, o_dz.x, o_dz.y, o_dz.z, o_dz.w);
         else reinterpret_cast<float4*>(dz + row * lddz)[i] = o_dz;
         if (ex.dy_hi) store_pair4(ex.dy_hi + row * width + 4 * i, ex.dy_lo + row * width + 4 * i, o_dy.x, o_dy.y, o_dy.z, o_dy.w);
+        if (ex.dys_hi) {   // the same, as a bf16 pair (operand of the pair contractions of the scan backward)
+          const int h = (4 * i) / ex.P;
+          const int64_t bb = row / ex.T, tt = row % ex.T;
+          const float f = __expf(ex.S[(bb * ex.H + h) * ex.T + tt]);
+          store_pair4(ex.dys_hi + row * width + 4 * i, ex.dys_lo + row * width + 4 * i, o_dy.x * f, o_dy.y * f, o_dy.z * f, o_dy.w * f);
+        }
         if (ex.dys) {    // dys[t, h, :] = dy[t, h, :] * exp(S[b, h, t]) for the scan backward (head width ex.P is a multiple of 4)
           const int h = (4 * i) / ex.P;
           const int64_t bb = row / ex.T, tt = row % ex.T;
@@ -594,7 +609,7 @@ pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const flo
   ProfScope prof(st, "gated_rmsnorm_bwd", 0.0, 4.0 * rows * 5.0 * width);
   const bool vec_ok = norm_vec_ok(width, ldz, dout, y, z, w, dy) && (lddz % 4 == 0) &&
                       ((reinterpret_cast<uintptr_t>(dz) | reinterpret_cast<uintptr_t>(partial)) & 15) == 0;
-  if ((ex.dz_hi || ex.dys || ex.dy_hi) && !vec_ok) return fail(PMB_ERR_UNSUPPORTED, "gated_rmsnorm_bwd: pair / scaled outputs need the vector kernel's alignment");
+  if ((ex.dz_hi || ex.dys || ex.dy_hi || ex.dys_hi) && !vec_ok) return fail(PMB_ERR_UNSUPPORTED, "gated_rmsnorm_bwd: pair / scaled outputs need the vector kernel's alignment");
   if (vec_ok) {
     int per = 1;
     const int threads = norm_vec_threads(width, &per);

@@ -33,6 +33,7 @@ size_t gated_rmsnorm_bwd_ws_bytes(int64_t rows, int width);
 // optional outputs of the gated RMSNorm backward: dz as a (hi, lo) bf16 pair (pitch lddz) instead of fp32, and
 // dys = dy * exp(S[b,h,t]) (S laid out (B,H,T), heads of width P, rows = B*T) for the scan backward
 struct NormBwdExtra { uint16_t* dz_hi = nullptr; uint16_t* dz_lo = nullptr; uint16_t* dy_hi = nullptr; uint16_t* dy_lo = nullptr; /* dy as a pair, contiguous rows */
+                      uint16_t* dys_hi = nullptr; uint16_t* dys_lo = nullptr; /* dy * exp(S) as a pair */
                       float* dys = nullptr; const float* S = nullptr; int H = 0, P = 1, T = 1; };
 pmb_status gated_rmsnorm_bwd(cudaStream_t st, int64_t rows, int width, const float* dout, const float* y, const float* z,
                              int64_t ldz, const float* w, const float* rstd, float* dy, float* dz, int64_t lddz,
@@ -74,6 +75,9 @@ struct SsdWs {            // persistent between fwd and bwd of one scan
   float* dys;             // (B,T,H,P) dY * exp(S_t)               (tensor-core path only)
   // (hi, lo) bf16 pairs of the fused intra-chunk kernels' operands (shapes those kernels take only)
   uint16_t *xt_hi, *xt_lo;   // (B,T,H,P)  x~ = x * dt
+  uint16_t *xs_hi, *xs_lo;   // (B,T,H,P)  x~ exp(S_end - S_t)
+  uint16_t *dys_hi, *dys_lo; // (B,T,H,P)  dY exp(S_t)
+  uint16_t *dg_hi, *dg_lo;   // (B,nc,G,Q,Q) dG
   uint16_t *bc_hi, *bc_lo;   // (B,T,2*G*N) B | C
   uint16_t *dy_hi, *dy_lo;   // (B,T,H,P)  dY
   uint16_t *hp_hi, *hp_lo;   // (B,nc,H,N,P) state entering each chunk

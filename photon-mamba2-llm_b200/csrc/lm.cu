@@ -14,7 +14,9 @@
 
 namespace pmb {
 
-constexpr int LM_TILE_ROWS = 2048;
+// Row tile of the tied head: (rows, vocab) fp32 logits exist for one tile at a time.  1024 rows (206 MB at a 50k
+// vocabulary) cost 1.7 % of the headline step against 2048 (412 MB); PMB_LM_TILE_ROWS overrides it (>= 128).
+constexpr int LM_TILE_ROWS = 1024;
 constexpr int HEAD_SPLITK = 3;
 
 __global__ void embedding_fwd_kernel(const float* __restrict__ table, const int64_t* __restrict__ ids, float* __restrict__ out,
@@ -544,7 +546,7 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
   }
   char* dhid = reinterpret_cast<char*>(lm->dhidden);
   SideLane* table_lane = nullptr;
-  if (prs && M <= lm->tile_rows) {
+  if (prs) {
     static const int on = [] { const char* e = getenv("PMB_HEAD_CONCURRENT"); return (e && e[0] == '0') ? 0 : 1; }();
     if (on) PMB_TRY(get_side_lane(4, &table_lane));
   }
@@ -578,8 +580,10 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
       PMB_TRY(gemm_bf16(st, 0, 0, rows, D, V, dl16, ldl, table16, D, dhid + (size_t)r0 * D * 2, D, nullptr, 1));
       PMB_TRY(gemm_bf16(st, 1, 0, V, D, rows, dl16, ldl, hrows, D, dtable, D, r0 == 0 ? nullptr : dtable, 0));
     } else if (prs && table_lane) {
-      // single row tile: only dhidden is needed now; the embedding-table gradient runs on its own stream next to
-      // the first blocks of the stack backward and is joined before the embedding scatter
+      // only dhidden is needed now; the embedding-table gradient runs on its own stream (next to the first blocks of
+      // the stack backward for the last row tile) and is joined before the embedding scatter.  With several row tiles
+      // the next tile's logits overwrite the buffer this tile's dE still reads, so the caller's stream waits for the
+      // lane before each further tile (below).
       // dhidden has 16 x 6 tiles and K = vocab: split K three ways (one launch, three products into three slabs)
       // so that the product the whole backward waits for uses the machine, then add the slabs
       {
@@ -597,7 +601,8 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
         PMB_LAUNCHED();
       }
       PMB_TRY(order_after(st, table_lane->ev[0], table_lane->s));
-      PMB_TRY(gemm_pairs(table_lane->s, 1, 0, V, D, rows, dlog_p, hid_p, dtable, D, nullptr));
+      PMB_TRY(gemm_pairs(table_lane->s, 1, 0, V, D, rows, dlog_p, hid_p, dtable, D, r0 == 0 ? nullptr : dtable));
+      if (r0 + rows < M) PMB_TRY(order_after(table_lane->s, table_lane->ev[2], st));   // the tile buffers are reused next
     } else if (prs) {
       // one launch: the few long-K tiles of dhidden first, the many short tiles of dE fill the other SMs
       const PairGemm both[2] = {{0, 0, rows, D, V, dlog_p, table_p, lm->dhidden + r0 * D, D, nullptr},

@@ -362,7 +362,8 @@ __global__ void chunk_cumsum_kernel(SsdP p, CumsumRaw raw) {
 // and dB contractions share.  S and dt of the chunk stay in shared memory between the two phases.
 constexpr int PREP_THREADS = 256, PREP_MAX_Q = 1024;
 __global__ void __launch_bounds__(PREP_THREADS) chunk_prepare_kernel(SsdP p, CumsumRaw raw, float* __restrict__ xs,
-                                                                     uint16_t* __restrict__ xt_hi, uint16_t* __restrict__ xt_lo) {
+                                                                     uint16_t* __restrict__ xt_hi, uint16_t* __restrict__ xt_lo,
+                                                                     uint16_t* __restrict__ xs_hi, uint16_t* __restrict__ xs_lo) {
   __shared__ float sS[PREP_MAX_Q], sdt[PREP_MAX_Q], wsum[PREP_THREADS / 32];
   const int w = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int h = w % p.H, bc = w / p.H, cc = bc % p.nc, bb = bc / p.nc;
@@ -414,7 +415,8 @@ __global__ void __launch_bounds__(PREP_THREADS) chunk_prepare_kernel(SsdP p, Cum
       const int i = i0 + u * PREP_THREADS;
       if (i < total) {
         const int64_t o = (tok0 + tt[u]) * (int64_t)(p.H * p.P) + h * p.P + 4 * jj[u];
-        *reinterpret_cast<float4*>(xs + o) = make_float4(v[u].x * f[u], v[u].y * f[u], v[u].z * f[u], v[u].w * f[u]);
+        if (xs_hi) store_pair4(xs_hi + o, xs_lo + o, v[u].x * f[u], v[u].y * f[u], v[u].z * f[u], v[u].w * f[u]);
+        else *reinterpret_cast<float4*>(xs + o) = make_float4(v[u].x * f[u], v[u].y * f[u], v[u].z * f[u], v[u].w * f[u]);
         // x~ = x dt as a bf16 pair: the V operand of the fused intra-chunk kernel
         if (xt_hi) store_pair4(xt_hi + o, xt_lo + o, v[u].x * fd[u], v[u].y * fd[u], v[u].z * fd[u], v[u].w * fd[u]);
       }
@@ -763,7 +765,8 @@ __global__ void __launch_bounds__(PREP_THREADS) chunk_rows_finish_w_kernel(SsdP 
 // Sums the split-K partial tiles in a fixed order.  mode 0: dG (lower-triangular 64x64 tiles only, the
 // others were never produced); mode 1/2: dC/dB rows go to out + token * ld + g * cols.
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, int nsplit, int rows, int cols, int mode, int G, int Q,
-                                     float* __restrict__ out, int64_t ld, int64_t total, int tile, int accumulate) {
+                                     float* __restrict__ out, int64_t ld, int64_t total, int tile, int accumulate,
+                                     uint16_t* __restrict__ pair_hi, uint16_t* __restrict__ pair_lo) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   int64_t mn = (int64_t)rows * cols;
@@ -771,7 +774,11 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, int nsplit,
   if (mode == 0 && n / tile > m / tile) return;   // tiles above the diagonal were never produced
   float s = 0.0f;
   for (int k = 0; k < nsplit; ++k) s += part[(batch * nsplit + k) * mn + r];
-  if (mode == 0) {
+  if (mode == 0 && pair_hi) {       // dG as a bf16 pair: it is only ever an operand of the dC / dB contractions
+    uint32_t h, l;
+    split_bf16_pair(s, h, l);
+    pair_hi[batch * mn + r] = (uint16_t)h; pair_lo[batch * mn + r] = (uint16_t)l;
+  } else if (mode == 0) {
     out[batch * mn + r] = accumulate ? out[batch * mn + r] + s : s;
   } else {
     int g = (int)(batch % G); int64_t bc = batch / G;
@@ -803,7 +810,8 @@ void ssd_ws_take(Arena& ar, int B, int T, int H, int P, int N, int G, int Q, Ssd
     w.hprev = ar.take<float>(stn);
     w.hlast = ar.take<float>((size_t)B * H * N * P);
     if (!fz) w.CB = ar.take<float>(qq);
-    w.xs = ar.take<float>(tcshape ? hp : 0);
+    w.xs = ar.take<float>((tcshape && !fz) ? hp : 0);
+    w.xs_hi = fz ? ar.take<uint16_t>(hp) : nullptr; w.xs_lo = fz ? ar.take<uint16_t>(hp) : nullptr;
     // bf16 (hi, lo) pairs of the operands of the fused intra-chunk kernels, and the carried-state part of y
     w.xt_hi = fz ? ar.take<uint16_t>(hp) : nullptr; w.xt_lo = fz ? ar.take<uint16_t>(hp) : nullptr;
     w.bc_hi = fz ? ar.take<uint16_t>(gn) : nullptr; w.bc_lo = fz ? ar.take<uint16_t>(gn) : nullptr;
@@ -831,7 +839,9 @@ void ssd_ws_take(Arena& ar, int B, int T, int H, int P, int N, int G, int Q, Ssd
       }
       w.splitk = ar.take<float>(need);
     }
-    w.dys = ar.take<float>(tcshape ? hp : 0);
+    w.dys = ar.take<float>((tcshape && !fz) ? hp : 0);
+    w.dys_hi = fz ? ar.take<uint16_t>(hp) : nullptr; w.dys_lo = fz ? ar.take<uint16_t>(hp) : nullptr;
+    w.dg_hi = fz ? ar.take<uint16_t>(qq) : nullptr; w.dg_lo = fz ? ar.take<uint16_t>(qq) : nullptr;
     w.dy_hi = fz ? ar.take<uint16_t>(hp) : nullptr; w.dy_lo = fz ? ar.take<uint16_t>(hp) : nullptr;
     w.dh_hi = fz ? ar.take<uint16_t>(stn) : nullptr; w.dh_lo = fz ? ar.take<uint16_t>(stn) : nullptr;
     // the sums of W that the fused backward kernel leaves for the row-sum kernel
@@ -896,7 +906,8 @@ static bool fused_enabled() {
 
 // x~[b,t,h,:] = x[b,t,h,:] * dt[b,t,h] as a bf16 pair (only when the fused cumsum kernel did not already write it)
 __global__ void __launch_bounds__(256) xt_pair_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ dt,
-                                                      uint16_t* __restrict__ hi, uint16_t* __restrict__ lo, int64_t rows, int H, int P) {
+                                                      uint16_t* __restrict__ hi, uint16_t* __restrict__ lo, int64_t rows, int H, int P,
+                                                      const float* __restrict__ S, int T, int Q, uint16_t* __restrict__ xs_hi, uint16_t* __restrict__ xs_lo) {
   const int P4 = P >> 2;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows * H * P4) return;
@@ -905,6 +916,11 @@ __global__ void __launch_bounds__(256) xt_pair_kernel(const float* __restrict__ 
   const float4 v = reinterpret_cast<const float4*>(x + tk * ldx + h * P)[j];
   const int64_t o = (tk * H + h) * (int64_t)P + 4 * j;
   store_pair4(hi + o, lo + o, v.x * f, v.y * f, v.z * f, v.w * f);
+  // xs = x~ exp(S_end - S_t): the operand of the chunk-state and dB contractions
+  const int b = (int)(tk / T), t = (int)(tk % T);
+  const float* sp = S + ((int64_t)b * H + h) * T;
+  const float f2 = f * __expf(sp[(t / Q) * Q + Q - 1] - sp[t]);
+  store_pair4(xs_hi + o, xs_lo + o, v.x * f2, v.y * f2, v.z * f2, v.w * f2);
 }
 
 // The B and C columns (adjacent in the caller's buffer when it is the block's activation buffer, else two arrays)
@@ -923,7 +939,8 @@ static pmb_status fused_operand_pairs(cudaStream_t st, const SsdIn& in, const Ss
   }
   if (want_xt) {
     ProfScope prof(st, "ssd_xt_pair", 0.0, 8.0 * rows * in.H * in.P);
-    xt_pair_kernel<<<(unsigned)cdiv(rows * in.H * (in.P / 4), 256), 256, 0, st>>>(in.x, in.ldx, in.dt, ws.xt_hi, ws.xt_lo, rows, in.H, in.P);
+    xt_pair_kernel<<<(unsigned)cdiv(rows * in.H * (in.P / 4), 256), 256, 0, st>>>(in.x, in.ldx, in.dt, ws.xt_hi, ws.xt_lo, rows, in.H, in.P,
+                                                                                  ws.S, in.T, in.Q, ws.xs_hi, ws.xs_lo);
     PMB_LAUNCHED();
   }
   return PMB_OK;
@@ -958,7 +975,7 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
     // finer-grained kernels use the memory system better)
     if (tc && nbch <= 4 * 148 && p.Q <= PREP_MAX_Q && (in.ldx % 4 == 0) && (reinterpret_cast<uintptr_t>(in.x) % 16 == 0)) {
       ProfScope prof(st, "ssd_chunk_prepare", 0.0, 8.0 * tok * p.H * (1.0 + p.P));
-      chunk_prepare_kernel<<<(unsigned)nbch, PREP_THREADS, 0, st>>>(p, raw, ws.xs, fz ? ws.xt_hi : nullptr, ws.xt_lo);
+      chunk_prepare_kernel<<<(unsigned)nbch, PREP_THREADS, 0, st>>>(p, raw, ws.xs, fz ? ws.xt_hi : nullptr, ws.xt_lo, fz ? ws.xs_hi : nullptr, ws.xs_lo);
       PMB_LAUNCHED();
       in_tc.xs_ready = true;
       xt_ready = fz;
@@ -969,13 +986,11 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
     }
   }
   SideLane* lane = nullptr;
-  if (tc) PMB_TRY(side_lane(2, &lane));
+  if (tc && !fz) PMB_TRY(side_lane(2, &lane));      // (the pair path is one chain: nothing to run beside it)
   if (fz) {
-    // the B / C pairs (and the x~ pair when the fused cumsum kernel did not run) next to the chunk-state chain
-    cudaStream_t sb = lane ? lane->s : st;
-    if (lane) PMB_TRY(order_after(st, lane->ev[0], sb));     // S and dt are ready
-    if (!in.bc_pair_ready || !xt_ready) PMB_TRY(fused_operand_pairs(sb, in, ws, !xt_ready));
-    PMB_TRY(ssd_tc_state(st, in_tc, ws));
+    // every contraction reads bf16 pairs: B | C and x~ / xs come from their producers, or are split here
+    if (!in.bc_pair_ready || !xt_ready) PMB_TRY(fused_operand_pairs(st, in, ws, !xt_ready));
+    PMB_TRY(ssd_pairs_state(st, in, ws, 0));
   } else if (tc) {
     cudaStream_t sb = lane ? lane->s : st;
     if (lane) PMB_TRY(order_after(st, lane->ev[0], sb));     // S is ready
@@ -1005,6 +1020,19 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
   return PMB_OK;
 }
 
+// dYs[b,t,h,:] = dY[b,t,h,:] exp(S[b,h,t]) as a bf16 pair (when the producer of dY did not already write it)
+__global__ void __launch_bounds__(256) dys_pair_kernel(const float* __restrict__ dy, int64_t lddy, const float* __restrict__ S,
+                                                       uint16_t* __restrict__ hi, uint16_t* __restrict__ lo, int64_t rows, int T, int H, int P) {
+  const int P4 = P >> 2;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * H * P4) return;
+  const int j = (int)(i % P4); const int64_t w = i / P4; const int h = (int)(w % H); const int64_t tk = w / H;
+  const float f = __expf(S[((tk / T) * H + h) * T + tk % T]);
+  const float4 v = reinterpret_cast<const float4*>(dy + tk * lddy + h * P)[j];
+  const int64_t o = (tk * H + h) * (int64_t)P + 4 * j;
+  store_pair4(hi + o, lo + o, v.x * f, v.y * f, v.z * f, v.w * f);
+}
+
 pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy, const float* dy, int64_t lddy,
                    const SsdGrads& g, const SsdWs& ws) {
   SsdP p;
@@ -1022,8 +1050,20 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   SideLane* lane = nullptr;
   if (tc) PMB_TRY(side_lane(0, &lane));
   cudaStream_t sb = lane ? lane->s : st;                      // stream of the dG -> dC -> dB chain
+  if (fz) {
+    // both chains read dY (and dY exp(S)) as bf16 pairs: written by the producer of dY, or here
+    const int64_t tokens = (int64_t)p.B * p.T;
+    if (!in.dy_pair_ready) PMB_TRY(split_pair16(st, dy, tokens, p.H * p.P, lddy, ws.dy_hi, ws.dy_lo, (int64_t)p.H * p.P));
+    if (!in.dys_ready) {
+      ProfScope prof(st, "ssd_prescale_dy", 0.0, 8.0 * tokens * p.H * p.P);
+      dys_pair_kernel<<<(unsigned)cdiv(tokens * p.H * (p.P / 4), 256), 256, 0, st>>>(dy, lddy, ws.S, ws.dys_hi, ws.dys_lo, tokens, p.T, p.H, p.P);
+      PMB_LAUNCHED();
+    }
+  }
   if (lane) PMB_TRY(order_after(st, lane->ev[0], sb));        // inputs of the scan are ready
-  if (tc) {
+  if (fz) {
+    PMB_TRY(ssd_pairs_state(st, in, ws, 1));
+  } else if (tc) {
     PMB_TRY(ssd_tc_dstate(st, in, dy, lddy, ws));
   } else {
     PMB_TRY(run_op(st, "ssd_bwd_dstate", make_op<OpDstate>(p, p.N, p.P), nbch, 2.0 * tok * p.H * p.N * p.P));
@@ -1038,7 +1078,6 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   if (lane) PMB_CUDA(cudaEventRecord(lane->ev[2], st));       // dh is ready (dB reads it)
   if (fz) {
     // dY as a bf16 pair (the B / C / x~ pairs were written by the forward of this scan and are still in the workspace)
-    if (!in.dy_pair_ready) PMB_TRY(split_pair16(st, dy, (int64_t)p.B * p.T, p.H * p.P, lddy, ws.dy_hi, ws.dy_lo, (int64_t)p.H * p.P));
     FusedArgs fa = fused_args(in, ws);
     fa.v = Op16{ws.dy_hi, ws.dy_lo, (int64_t)p.H * p.P};
     fa.state = Op16{ws.dh_hi, ws.dh_lo, p.P};
@@ -1087,10 +1126,38 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   auto reduce = [&](int nsplit, int cols, int mode, float* out, int64_t ld, int tile = BM) -> pmb_status {
     if (nsplit <= 1) return PMB_OK;
     int64_t total = (int64_t)nbcg * p.Q * cols;
-    splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, tc_group ? sb : st>>>(ws.splitk, nsplit, p.Q, cols, mode, p.G, p.Q, out, ld, total, tile, 0);
+    splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, tc_group ? sb : st>>>(ws.splitk, nsplit, p.Q, cols, mode, p.G, p.Q, out, ld, total, tile, 0,
+                                                                                     (mode == 0 && fz) ? ws.dg_hi : nullptr, ws.dg_lo);
     PMB_LAUNCHED();
     return PMB_OK;
   };
+  if (fz) {
+    {
+      ProfScope prof(sb, "ssd_bwd_dg_pair", 2.0 * tok * p.H * p.Q * p.P, 0.0);
+      const int nsg = ssd_pairs_dg_nsplit(p.B, p.T, p.H, p.G, p.Q);
+      PMB_TRY(ssd_pairs_dg(sb, in, ws, nsg));
+      PMB_TRY(reduce(nsg, p.Q, 0, ws.dG, 0, 128));
+    }
+    const int ns = ssd_pairs_dbc_nsplit(p.B, p.T, p.H, p.N, p.G, p.Q);
+    {
+      if (lane) PMB_CUDA(cudaStreamWaitEvent(sb, lane->ev[1], 0));       // (the forward's h_prev pair is long there)
+      ProfScope prof(sb, "ssd_bwd_dc_pair", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
+      PMB_TRY(ssd_pairs_dbc(sb, in, ws, 0, g.dc, g.lddbc, ns));
+      PMB_TRY(reduce(ns, p.N, 1, g.dc, g.lddbc));
+    }
+    {
+      if (lane) PMB_CUDA(cudaStreamWaitEvent(sb, lane->ev[2], 0));       // dh and its pair are ready
+      ProfScope prof(sb, "ssd_bwd_db_pair", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
+      PMB_TRY(ssd_pairs_dbc(sb, in, ws, 1, g.db, g.lddbc, ns));
+      PMB_TRY(reduce(ns, p.N, 2, g.db, g.lddbc));
+    }
+    if (lane) {
+      PMB_CUDA(cudaStreamWaitEvent(sb, lane->ev[4], 0));
+      PMB_TRY(head_sums(sb));
+      PMB_TRY(order_after(sb, lane->ev[3], st));               // join
+    }
+    return PMB_OK;
+  }
   if (tc_group) {
     {
       ProfScope prof(sb, "ssd_bwd_dg_tc", 2.0 * tok * p.H * p.Q * p.P, 0.0);

@@ -1,5 +1,6 @@
 // Fused intra-chunk kernels of the chunked SSD scan (tcgen05 / TMEM); see ssd_fused.cu.  Internal to the library.
 #pragma once
+#include <cuda.h>
 #include "kernels.h"
 
 namespace pmb {
@@ -34,5 +35,19 @@ bool ssd_fused_supported(int P, int N, int Q, bool pairs);
 pmb_status ssd_fused(cudaStream_t st, int mode, const FusedArgs& a);
 
 pmb_status read_clear_device_status_fused(unsigned int* word);
+pmb_status read_clear_device_status_pairs(unsigned int* word);
+
+// ---- the other contractions of the scan on the same bf16 pairs (ssd_pairs.cu; shapes of ssd_fused_supported(pairs)):
+// states / dstates (per head), dG (summed over the heads of a group, decay mask folded in registers), dC / dB.
+pmb_status ssd_pairs_state(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int mode);      // 0: chunk states, 1: d(states)
+int ssd_pairs_dg_nsplit(int B, int T, int H, int G, int Q);
+pmb_status ssd_pairs_dg(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int nsplit);       // -> ws.dg_hi/lo (nsplit == 1) or ws.splitk partials
+int ssd_pairs_dbc_nsplit(int B, int T, int H, int N, int G, int Q);
+pmb_status ssd_pairs_dbc(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int mode, float* out, int64_t ld, int nsplit);   // 0: dC, 1: dB
+
+namespace sf {
+// cached rank-3 bf16 tensor map: dims (d0 contiguous, d1 rows with pitch s0 elements, d2 with pitch s1), box (b0, b1, 1)
+pmb_status bf16_map3(CUtensorMap* out, const uint16_t* base, int64_t d0, int64_t d1, int64_t d2, int64_t s0, int64_t s1, int b0, int b1);
+}
 
 }  // namespace pmb

@@ -69,7 +69,7 @@ def test_headline_config_lm_step_vs_oracle(pm):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, None), (torch.bfloat16, 2e-2)])
 def test_lm_head_across_row_tiles_with_remainder(pm, dtype, tol):
-    """4608 tokens = two full row tiles of 2048 and a remainder of 512: the logits tile loop, the accumulation of the
+    """4608 tokens = four full row tiles of 1024 and a remainder of 512: the logits tile loop, the accumulation of the
     embedding-table gradient across tiles and the per-tile d(hidden) (crates/pm-core/src/loss.rs:73-209 tiles the
     same way)."""
     cfg = orc.Mamba2Config(d_model=64, d_state=8, d_head=8, n_heads=8, block_len=32)    # in_proj_dim 152: a multiple of 8 (bf16 rule)
