@@ -37,10 +37,12 @@ constexpr int TILE_BYTES = TBM * TBK * 2;   // 16 KiB
 template <bool SPLIT> struct Cfg {
   static constexpr int STAGES = SPLIT ? 3 : 6;
   static constexpr int STAGE_BYTES = (SPLIT ? 4 : 2) * TILE_BYTES;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 4 * 2 * 4096 + 1024 + 256;   // + the epilogue's staging slots
 };
 constexpr int NTHREADS = 192;
-constexpr int TMEM_COLS = 128;
+constexpr int TMEM_COLS = 256;               // two 128-column accumulators
+constexpr int EPI_SLOT_BYTES = 32 * 32 * 4;  // 32 rows x 32 fp32 columns
+constexpr int EPI_BYTES = 4 * 2 * EPI_SLOT_BYTES;
 
 __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -55,6 +57,7 @@ struct Params {
   int M, N, K;
   int a_mn_major, b_mn_major;
   void* C; int64_t ldc; const void* R; int out_bf16;
+  int tma_out;     // fp32 result (and residual) meet the TMA rules: the epilogue stores through shared memory
 };
 
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
@@ -124,7 +127,7 @@ __device__ __forceinline__ void store_row_piece(const Params& p, int m, int nb, 
 // pr[1].tiles on the second, and so on (unused entries have tiles == 0).
 // Two products whose tile counts each fill the 148 SMs badly (weight-gradient and data-gradient of one projection)
 // then share the machine instead of running as two ragged waves.
-struct Problem { CUtensorMap mA, mB, mAlo, mBlo; Params p; int tiles_n; int tiles; };
+struct Problem { CUtensorMap mA, mB, mAlo, mBlo, mC, mR; Params p; int tiles_n; int tiles; };
 constexpr int MAX_GROUP = 4;
 struct Group { Problem pr[MAX_GROUP]; };
 __device__ __forceinline__ int pick_problem(const Group& g, int id, int* local) {
@@ -135,33 +138,51 @@ __device__ __forceinline__ int pick_problem(const Group& g, int id, int* local) 
   return which;
 }
 
+// TMA store of one 32 x 32 fp32 block (128-byte rows, 128-byte swizzle) and its bookkeeping
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(src) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// Persistent: CTA b works on tiles b, b + gridDim.x, ... of the group.  The operand ring and its phases run on
+// across tiles, so the producer is already loading the next tile while the last k-tiles of this one are
+// multiplied; the accumulator alternates between two 128-column TMEM buffers, so the epilogue warps drain tile i
+// while the tensor core fills tile i + 1.
+//   full[s] / empty[s]        operand stage s landed / consumed
+//   acc_full[b] / acc_empty[b] accumulator b complete / drained by all four epilogue warps
+//   rbar[w][slot]             residual block landed in epilogue warp w's staging slot
+// fp32 results leave through shared memory: each epilogue warp writes its 32 rows x 32 columns into a swizzled
+// 4 KiB slot (conflict-free 16-byte stores) and one lane hands the slot to a TMA store, which writes whole
+// 128-byte row segments and clips at the matrix edge; two slots per warp, so a store is in flight while the next
+// block is formed.  The residual block, when there is one, is loaded into the slot first and added in place.
 template <bool SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ Group g) {
-  int tile;
-  const int which = pick_problem(g, (int)blockIdx.x, &tile);
-  const Problem& q = g.pr[which];
-  const Params& p = q.p;
+gemm_bf16_kernel(const __grid_constant__ Group g, const int total_tiles) {
   constexpr int STAGES = Cfg<SPLIT>::STAGES;
   constexpr int STAGE_BYTES = Cfg<SPLIT>::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
   uint8_t* tiles_ptr = smem_raw + (tiles - raw);
-  const uint32_t bars = tiles + STAGES * STAGE_BYTES;
+  const uint32_t epi = tiles + STAGES * STAGE_BYTES;                 // 4 warps x 2 slots x 4 KiB
+  const uint32_t bars = epi + EPI_BYTES;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-  const uint32_t accum_bar = bars + 8u * (2 * STAGES);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tiles_ptr + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 1));
+  auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+  auto r_bar = [&](int w, int slot) { return bars + 8u * (2 * STAGES + 4 + 2 * w + slot); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tiles_ptr + STAGES * STAGE_BYTES + EPI_BYTES + 8 * (2 * STAGES + 12));
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = (tile / q.tiles_n) * TBM, n0 = (tile % q.tiles_n) * TBN;
-  const int num_kt = (p.K + TBK - 1) / TBK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
+    for (int w = 0; w < 4; ++w) { mbar_init(r_bar(w, 0), 1); mbar_init(r_bar(w, 1), 1); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -173,108 +194,203 @@ gemm_bf16_kernel(const __grid_constant__ Group g) {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_acc = *tmem_slot;
+  const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
     if (lane == 0) {
-      int armed = 0;
-      for (int kt = 0; kt < num_kt; ++kt) {
-        const int s = kt % STAGES;
-        const uint32_t ph = (kt / STAGES) & 1;
-        if (!mbar_wait(empty_bar(s), ph ^ 1u)) { atomicOr(&g_bf16_status, 1u); *abort_flag = 1; break; }
-        if (*abort_flag) break;
-        const uint32_t a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + TILE_BYTES;
-        mbar_expect_tx(full_bar(s), STAGE_BYTES);
-        const int k0 = kt * TBK;
-        if (!p.a_mn_major) {
-          tma_load_2d(a_dst, &q.mA, k0, m0, full_bar(s));
-        } else {
-#pragma unroll
-          for (int j = 0; j < TBM / 64; ++j) tma_load_2d(a_dst + j * (TBK * 128), &q.mA, m0 + 64 * j, k0, full_bar(s));
-        }
-        if (!p.b_mn_major) {
-          tma_load_2d(b_dst, &q.mB, k0, n0, full_bar(s));
-        } else {
-#pragma unroll
-          for (int j = 0; j < TBN / 64; ++j) tma_load_2d(b_dst + j * (TBK * 128), &q.mB, n0 + 64 * j, k0, full_bar(s));
-        }
-        if (SPLIT) {
-          const uint32_t al_dst = a_dst + 2 * TILE_BYTES, bl_dst = al_dst + TILE_BYTES;
+      int s = 0; uint32_t ph = 0;
+      int in_flight = 0;                       // stages armed and possibly not yet landed (for the abort drain)
+      bool stop = false;
+      for (int tid = (int)blockIdx.x; tid < total_tiles && !stop; tid += (int)gridDim.x) {
+        int tile;
+        const Problem& q = g.pr[pick_problem(g, tid, &tile)];
+        const Params& p = q.p;
+        const int m0 = (tile / q.tiles_n) * TBM, n0 = (tile % q.tiles_n) * TBN;
+        const int num_kt = (p.K + TBK - 1) / TBK;
+        for (int kt = 0; kt < num_kt; ++kt) {
+          if (!mbar_wait(empty_bar(s), ph ^ 1u)) { atomicOr(&g_bf16_status, 1u); *abort_flag = 1; stop = true; break; }
+          if (*abort_flag) { stop = true; break; }
+          const uint32_t a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + TILE_BYTES;
+          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          const int k0 = kt * TBK;
           if (!p.a_mn_major) {
-            tma_load_2d(al_dst, &q.mAlo, k0, m0, full_bar(s));
+            tma_load_2d(a_dst, &q.mA, k0, m0, full_bar(s));
           } else {
 #pragma unroll
-            for (int j = 0; j < TBM / 64; ++j) tma_load_2d(al_dst + j * (TBK * 128), &q.mAlo, m0 + 64 * j, k0, full_bar(s));
+            for (int j = 0; j < TBM / 64; ++j) tma_load_2d(a_dst + j * (TBK * 128), &q.mA, m0 + 64 * j, k0, full_bar(s));
           }
           if (!p.b_mn_major) {
-            tma_load_2d(bl_dst, &q.mBlo, k0, n0, full_bar(s));
+            tma_load_2d(b_dst, &q.mB, k0, n0, full_bar(s));
           } else {
 #pragma unroll
-            for (int j = 0; j < TBN / 64; ++j) tma_load_2d(bl_dst + j * (TBK * 128), &q.mBlo, n0 + 64 * j, k0, full_bar(s));
+            for (int j = 0; j < TBN / 64; ++j) tma_load_2d(b_dst + j * (TBK * 128), &q.mB, n0 + 64 * j, k0, full_bar(s));
           }
+          if (SPLIT) {
+            const uint32_t al_dst = a_dst + 2 * TILE_BYTES, bl_dst = al_dst + TILE_BYTES;
+            if (!p.a_mn_major) {
+              tma_load_2d(al_dst, &q.mAlo, k0, m0, full_bar(s));
+            } else {
+#pragma unroll
+              for (int j = 0; j < TBM / 64; ++j) tma_load_2d(al_dst + j * (TBK * 128), &q.mAlo, m0 + 64 * j, k0, full_bar(s));
+            }
+            if (!p.b_mn_major) {
+              tma_load_2d(bl_dst, &q.mBlo, k0, n0, full_bar(s));
+            } else {
+#pragma unroll
+              for (int j = 0; j < TBN / 64; ++j) tma_load_2d(bl_dst + j * (TBK * 128), &q.mBlo, n0 + 64 * j, k0, full_bar(s));
+            }
+          }
+          if (in_flight < STAGES) ++in_flight;
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
-        armed = kt + 1;
       }
-      if (*abort_flag)
-        for (int kt = max(0, armed - STAGES); kt < armed; ++kt) mbar_wait(full_bar(kt % STAGES), (kt / STAGES) & 1);
+      if (*abort_flag) {
+        // the copies already issued still land in this CTA's shared memory: wait (bounded) for each before leaving
+        for (int i = 0; i < in_flight; ++i) {
+          if (--s < 0) { s = STAGES - 1; ph ^= 1u; }
+          mbar_wait(full_bar(s), ph);
+        }
+      }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // kind::f16 descriptor: fp32 accumulate (bit 4), A/B format bf16 (=1) at bits 7 and 10, majorness, N, M
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
-                             ((uint32_t)(TBN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
-      // K-major: 8-row groups 1024 B apart, one MMA (K=16) advances 32 B inside the 128-byte row.
-      // MN-major: blocks of 64 elements TBK*128 B apart (LBO), 8-k-row groups 1024 B apart (SBO); K=16 spans two groups.
-      const uint32_t a_lbo = p.a_mn_major ? TBK * 128 : 16, b_lbo = p.b_mn_major ? TBK * 128 : 16;
-      // descriptor halves that do not change, and the per-k-step advance of the address field (16-byte units)
       const uint32_t d_hi = desc_hi(1024, 2);
-      const uint32_t a_step = (p.a_mn_major ? 2048u : 32u) >> 4, b_step = (p.b_mn_major ? 2048u : 32u) >> 4;
       constexpr uint32_t LO_OFF = (2 * TILE_BYTES) >> 4;        // from the hi tiles of a stage to its lo tiles
       int s = 0; uint32_t ph = 0;
-      for (int kt = 0; kt < num_kt; ++kt) {
-        if (!mbar_wait(full_bar(s), ph)) { atomicOr(&g_bf16_status, 2u); *abort_flag = 1; break; }
-        if (*abort_flag) break;
+      int it = 0;
+      bool stop = false;
+      for (int tid = (int)blockIdx.x; tid < total_tiles && !stop; tid += (int)gridDim.x, ++it) {
+        int tile;
+        const Problem& q = g.pr[pick_problem(g, tid, &tile)];
+        const Params& p = q.p;
+        const int num_kt = (p.K + TBK - 1) / TBK;
+        // kind::f16 descriptor: fp32 accumulate (bit 4), A/B format bf16 (=1) at bits 7 and 10, majorness, N, M
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+                               ((uint32_t)(TBN >> 3) << 17) | ((uint32_t)(TBM >> 4) << 24);
+        // K-major: 8-row groups 1024 B apart, one MMA (K=16) advances 32 B inside the 128-byte row.
+        // MN-major: blocks of 64 elements TBK*128 B apart (LBO), 8-k-row groups 1024 B apart (SBO); K=16 spans two groups.
+        const uint32_t a_lbo = p.a_mn_major ? TBK * 128 : 16, b_lbo = p.b_mn_major ? TBK * 128 : 16;
+        const uint32_t a_step = (p.a_mn_major ? 2048u : 32u) >> 4, b_step = (p.b_mn_major ? 2048u : 32u) >> 4;
+        const int b = it & 1;
+        if (!mbar_wait(acc_empty(b), (((uint32_t)it >> 1) & 1u) ^ 1u)) { atomicOr(&g_bf16_status, 4u); *abort_flag = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_s = tiles + s * STAGE_BYTES;
-        uint32_t al = desc_lo(a_s, a_lbo), bl = desc_lo(a_s + TILE_BYTES, b_lbo);
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(b * TBN);
+        for (int kt = 0; kt < num_kt; ++kt) {
+          if (!mbar_wait(full_bar(s), ph)) { atomicOr(&g_bf16_status, 2u); *abort_flag = 1; stop = true; break; }
+          if (*abort_flag) { stop = true; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_s = tiles + s * STAGE_BYTES;
+          uint32_t al = desc_lo(a_s, a_lbo), bl = desc_lo(a_s + TILE_BYTES, b_lbo);
 #pragma unroll
-        for (int k = 0; k < TBK / 16; ++k) {
-          const uint32_t acc = (kt > 0 || k > 0) ? 1u : 0u;
-          if (SPLIT) {
-            mma_f16_h(tmem_acc, al + LO_OFF, d_hi, bl, d_hi, idesc, acc);
-            mma_f16_h(tmem_acc, al, d_hi, bl + LO_OFF, d_hi, idesc, 1u);
-            mma_f16_h(tmem_acc, al, d_hi, bl, d_hi, idesc, 1u);
-          } else {
-            mma_f16_h(tmem_acc, al, d_hi, bl, d_hi, idesc, acc);
+          for (int k = 0; k < TBK / 16; ++k) {
+            const uint32_t acc = (kt > 0 || k > 0) ? 1u : 0u;
+            if (SPLIT) {
+              mma_f16_h(tmem_acc, al + LO_OFF, d_hi, bl, d_hi, idesc, acc);
+              mma_f16_h(tmem_acc, al, d_hi, bl + LO_OFF, d_hi, idesc, 1u);
+              mma_f16_h(tmem_acc, al, d_hi, bl, d_hi, idesc, 1u);
+            } else {
+              mma_f16_h(tmem_acc, al, d_hi, bl, d_hi, idesc, acc);
+            }
+            al += a_step; bl += b_step;
           }
-          al += a_step; bl += b_step;
+          umma_commit(empty_bar(s));
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
-        umma_commit(empty_bar(s));
-        if (++s == STAGES) { s = 0; ph ^= 1u; }
+        if (!stop) umma_commit(acc_full(b));
       }
-      umma_commit(accum_bar);
     }
   } else {
-    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait_idle(accum_bar, 0));
-    if (!acc_ok && lane == 0) { atomicOr(&g_bf16_status, 8u); *abort_flag = 1; }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const bool aborted = __any_sync(0xffffffffu, *abort_flag != 0);
-    if (acc_ok && !aborted) {
-      const int lane_base = (warp & 3) * 32;
-      const int m = m0 + lane_base + lane;
+    const int ew = warp - 2;                       // staging slots and residual barriers of this warp
+    const int quarter = warp & 3;                  // the TMEM lanes this warp may read
+    const uint32_t slot0 = epi + (uint32_t)ew * (2 * EPI_SLOT_BYTES);
+    uint32_t pc = 0;                               // blocks stored so far: slot = pc & 1
+    uint32_t rph0 = 0, rph1 = 0;                   // phases of the two residual barriers
+    int it = 0;
+    for (int tid = (int)blockIdx.x; tid < total_tiles; tid += (int)gridDim.x, ++it) {
+      int tile;
+      const Problem& q = g.pr[pick_problem(g, tid, &tile)];
+      const Params& p = q.p;
+      const int m0 = (tile / q.tiles_n) * TBM, n0 = (tile % q.tiles_n) * TBN;
+      const int b = it & 1;
+      const bool acc_ok = __all_sync(0xffffffffu, mbar_wait_idle(acc_full(b), ((uint32_t)it >> 1) & 1u));
+      if (!acc_ok && lane == 0) { atomicOr(&g_bf16_status, 8u); *abort_flag = 1; }
+      if (!acc_ok || __any_sync(0xffffffffu, *abort_flag != 0)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t tmem_acc = tmem_base + (uint32_t)(b * TBN) + ((uint32_t)(quarter * 32) << 16);
+      const int row0 = m0 + quarter * 32;
+      if (p.tma_out) {
+        if (row0 < p.M) {
+          const bool res = p.R != nullptr;
+          if (res && lane == 0) {
+            const uint32_t slot = pc & 1u;
+            mbar_expect_tx(r_bar(ew, slot), EPI_SLOT_BYTES);
+            tma_load_2d(slot0 + slot * EPI_SLOT_BYTES, &q.mR, n0, row0, r_bar(ew, slot));
+          }
 #pragma unroll 1
-      for (int c0 = 0; c0 < TBN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_acc + ((uint32_t)lane_base << 16) + (uint32_t)c0, r);
-        if (m < p.M) store_row_piece(p, m, n0 + c0, r);
+          for (int c0 = 0; c0 < TBN && n0 + c0 < p.N; c0 += 32) {
+            const uint32_t slot = pc & 1u;
+            const uint32_t sbase = slot0 + slot * EPI_SLOT_BYTES + (uint32_t)lane * 128u;
+            uint32_t r[32];
+            tmem_ld32(tmem_acc + (uint32_t)c0, r);
+            if (res) {
+              const uint32_t rp = slot ? rph1 : rph0;
+              const bool landed = __all_sync(0xffffffffu, mbar_wait(r_bar(ew, slot), rp));
+              if (slot) rph1 ^= 1u; else rph0 ^= 1u;
+              if (!landed) { if (lane == 0) { atomicOr(&g_bf16_status, 16u); *abort_flag = 1; } }
+              else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  float4 v;
+                  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                               : "r"(sbase + (uint32_t)((j ^ (lane & 7)) * 16)));
+                  r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v.x);
+                  r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
+                  r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
+                  r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+                }
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sbase + (uint32_t)((j ^ (lane & 7)) * 16)),
+                           "r"(r[4 * j]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3]) : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            ++pc;
+            if (lane == 0) {
+              tma_store_2d(&q.mC, slot0 + slot * EPI_SLOT_BYTES, n0 + c0, row0);
+              bulk_commit();
+              bulk_wait_read<1>();               // the other slot's store has read its data: the slot is free again
+              if (res && c0 + 32 < TBN && n0 + c0 + 32 < p.N) {
+                const uint32_t nslot = pc & 1u;
+                mbar_expect_tx(r_bar(ew, nslot), EPI_SLOT_BYTES);
+                tma_load_2d(slot0 + nslot * EPI_SLOT_BYTES, &q.mR, n0 + c0 + 32, row0, r_bar(ew, nslot));
+              }
+            }
+            __syncwarp();
+          }
+        }
+      } else {
+        const int m = row0 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < TBN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_acc + (uint32_t)c0, r);
+          if (m < p.M) store_row_piece(p, m, n0 + c0, r);
+        }
       }
+      // every TMEM read of this warp has completed (tcgen05.wait::ld): hand the accumulator back
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty(b));
     }
+    if (lane == 0) bulk_wait_all();
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -483,14 +599,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ Group g) {
 }
 
 struct MapKey {
-  const void* base; int64_t inner, outer, ld; int bi, bo;
-  bool operator<(const MapKey& o) const { return std::tie(base, inner, outer, ld, bi, bo) < std::tie(o.base, o.inner, o.outer, o.ld, o.bi, o.bo); }
+  const void* base; int64_t inner, outer, ld; int bi, bo, f32;
+  bool operator<(const MapKey& o) const {
+    return std::tie(base, inner, outer, ld, bi, bo, f32) < std::tie(o.base, o.inner, o.outer, o.ld, o.bi, o.bo, o.f32);
+  }
 };
 static std::map<MapKey, CUtensorMap> g_cache;   // shared by every device and host thread: guarded by g_cache_mu
 static std::mutex g_cache_mu;
 
-static pmb_status make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_inner, int box_outer) {
-  MapKey key{base, inner, outer, ld, box_inner, box_outer};
+static pmb_status make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_inner, int box_outer,
+                           bool f32 = false) {
+  MapKey key{base, inner, outer, ld, box_inner, box_outer, f32 ? 1 : 0};
   std::lock_guard<std::mutex> lock(g_cache_mu);
   auto it = g_cache.find(key);
   if (it == g_cache.end()) {
@@ -498,18 +617,43 @@ static pmb_status make_map(CUtensorMap* map, const void* base, int64_t inner, in
     EncodeTiledFn enc = get_encode();
     if (!enc) return fail(PMB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * (f32 ? 4 : 2)};
     cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
     cuuint32_t estr[2] = {1, 1};
     CUtensorMap m;
-    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+    CUresult r = enc(&m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(PMB_ERR_CUDA, "cuTensorMapEncodeTiled (bf16) failed with code %d", (int)r);
+    if (r != CUDA_SUCCESS) return fail(PMB_ERR_CUDA, "cuTensorMapEncodeTiled (%s) failed with code %d", f32 ? "fp32" : "bf16", (int)r);
     it = g_cache.emplace(key, m).first;
   }
   *map = it->second;
   return PMB_OK;
+}
+
+// Maps for the epilogue of the single-CTA kernel: 32 x 32 fp32 blocks of C (and of R, which shares C's pitch).
+// Leaves tma_out = 0 when the result is bf16 or breaks a TMA rule; the kernel then stores row by row.
+static pmb_status make_out_maps(Problem* q) {
+  Params& p = q->p;
+  p.tma_out = 0;
+  if (p.out_bf16 || (p.ldc & 3) || (reinterpret_cast<uintptr_t>(p.C) & 15) || (p.R && (reinterpret_cast<uintptr_t>(p.R) & 15))) return PMB_OK;
+  PMB_TRY(make_map(&q->mC, p.C, p.N, p.M, p.ldc, 32, 32, true));
+  if (p.R) PMB_TRY(make_map(&q->mR, p.R, p.N, p.M, p.ldc, 32, 32, true));
+  p.tma_out = 1;
+  return PMB_OK;
+}
+
+// One persistent CTA per SM, fewer when there are fewer tiles.
+static unsigned persistent_grid(int64_t tiles) {
+  static int sms[PMB_MAX_DEVICES] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int n = 148;
+  if (dev >= 0 && dev < PMB_MAX_DEVICES) {
+    if (!sms[dev]) { int v = 0; if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) sms[dev] = v; else sms[dev] = 148; }
+    n = sms[dev];
+  }
+  return (unsigned)(tiles < n ? tiles : n);
 }
 
 }  // namespace hb
@@ -532,6 +676,7 @@ pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
   p.a_mn_major = ta ? 1 : 0; p.b_mn_major = tb ? 0 : 1;
   p.C = C; p.ldc = ldc; p.R = R; p.out_bf16 = out_bf16;
   q.tiles_n = (int)cdiv(N, TBN); q.tiles = (int)(cdiv(M, TBM) * cdiv(N, TBN));
+  PMB_TRY(make_out_maps(&q));
   for (int i = 1; i < MAX_GROUP; ++i) { g.pr[i].tiles_n = 1; g.pr[i].tiles = 0; }
   {
     static const int env = [] { const char* e = getenv("PMB_GEMM_PAIR"); return e ? atoi(e) : -1; }();
@@ -547,7 +692,7 @@ pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
     }
   }
   ProfScope prof(st, "gemm_bf16", 2.0 * M * N * K, 2.0 * ((double)M * K + (double)K * N) + (out_bf16 ? 2.0 : 4.0) * M * N * (R ? 2 : 1));
-  gemm_bf16_kernel<false><<<(unsigned)q.tiles, NTHREADS, Cfg<false>::SMEM_BYTES, st>>>(g);
+  gemm_bf16_kernel<false><<<persistent_grid(q.tiles), NTHREADS, Cfg<false>::SMEM_BYTES, st>>>(g, q.tiles);
   PMB_LAUNCHED();
   return PMB_OK;
 }
@@ -660,6 +805,7 @@ pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n, int tile
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.a_mn_major = e.ta ? 1 : 0; p.b_mn_major = e.tb ? 0 : 1;
     p.C = e.C; p.ldc = e.ldc; p.R = e.R; p.out_bf16 = 0;
+    PMB_TRY(make_out_maps(&q));
     q.tiles_n = (int)cdiv(N, TBN);
     const int64_t t = cdiv(M, TBM) * cdiv(N, TBN);
     total += t;
@@ -690,7 +836,7 @@ pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n, int tile
     return PMB_OK;
   }
   ProfScope prof(st, "gemm_bf16x2", flops, bytes);
-  gemm_bf16_kernel<true><<<(unsigned)total, NTHREADS, Cfg<true>::SMEM_BYTES, st>>>(g);
+  gemm_bf16_kernel<true><<<persistent_grid(total), NTHREADS, Cfg<true>::SMEM_BYTES, st>>>(g, (int)total);
   PMB_LAUNCHED();
   return PMB_OK;
 }
