@@ -54,11 +54,11 @@ pmb_status get_side_lane(int idx, SideLane** out) {
   SideLane& l = g_lanes[dev][idx];
   if (!l.s) {
     // lanes that carry the critical chain of the stack backward (6: gradient kernels of the current block, 0: the
-    // scan backward's second chain) get the highest stream priority, so that their CTAs are placed ahead of the
+    // scan backward's second chain, 5: its dB branch) get the highest stream priority, so that their CTAs are placed ahead of the
     // recompute-ahead and the deferred GEMMs whenever an SM frees up
     int least = 0, greatest = 0;
     PMB_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest));
-    PMB_CUDA(cudaStreamCreateWithPriority(&l.s, cudaStreamNonBlocking, (idx == 0 || idx == 6) ? greatest : least));
+    PMB_CUDA(cudaStreamCreateWithPriority(&l.s, cudaStreamNonBlocking, (idx == 0 || idx == 5 || idx == 6) ? greatest : least));
     for (int i = 0; i < 6; ++i) PMB_CUDA(cudaEventCreateWithFlags(&l.ev[i], cudaEventDisableTiming));
   }
   *out = &l;

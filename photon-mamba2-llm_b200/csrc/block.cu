@@ -274,13 +274,21 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   sg.dx = w.dact; sg.lddx = d.X;
   sg.db = w.dact + d.I; sg.dc = w.dact + d.I + d.G * d.N; sg.lddbc = d.X;
   sg.da = nullptr; sg.ddt = w.ddt; sg.dA = w.dA; sg.dD = g.d_skip;
+  // the pair path of the scan backward writes the dt columns of the dxzd pair, d_dt_bias and d_a_log itself
+  const bool scan_dt = ph && ssd_bwd_takes_pairs(sin, w.dnormed, d.I, sg);
+  if (scan_dt) { sg.raw.hi = ph; sg.raw.lo = pl; sg.raw.ld = d.J; sg.raw.col0 = d.I + d.X; sg.raw.d_dt_bias = g.dt_bias; sg.raw.d_a_log = g.a_log; }
   PMB_TRY(ssd_bwd(st, sin, w.y, d.I, w.dnormed, d.I, sg, w.ssd));
-  // the dt columns (one block per head: a latency-bound loop over the tokens) run next to the conv backward
-  cudaStream_t sdt = st;
-  if (gl) { PMB_TRY(order_after(st, gl->ev[4], gl->s)); sdt = gl->s; }
-  dt_bwd_kernel<<<(unsigned)d.H, 256, 0, sdt>>>(w.xzd, w.dxzd, d.J, d.I + d.X, p.dt_bias, w.ddt, w.Aneg, w.dA, g.dt_bias, g.a_log, d.M, d.H, ph, pl);
-  PMB_LAUNCHED();
-  if (gl) PMB_CUDA(cudaEventRecord(gl->ev[5], gl->s));
+  // otherwise the dt columns (one block per head: a latency-bound loop over the tokens) run next to the conv backward
+  if (!scan_dt) {
+    cudaStream_t sdt = st;
+    if (gl) { PMB_TRY(order_after(st, gl->ev[4], gl->s)); sdt = gl->s; }
+    {
+      ProfScope prof(sdt, "dt_bwd", 0.0, 16.0 * d.M * d.H);
+      dt_bwd_kernel<<<(unsigned)d.H, 256, 0, sdt>>>(w.xzd, w.dxzd, d.J, d.I + d.X, p.dt_bias, w.ddt, w.Aneg, w.dA, g.dt_bias, g.a_log, d.M, d.H, ph, pl);
+      PMB_LAUNCHED();
+    }
+    if (gl) PMB_CUDA(cudaEventRecord(gl->ev[5], gl->s));
+  }
   // conv + SiLU
   PMB_TRY(conv_silu_bwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, w.dact, w.dxzd, g.conv1d_weight, g.conv1d_bias,
                         w.scratch, w.scratch_bytes, gl, ph, pl));
@@ -296,7 +304,7 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
     const PairGemm gx{0, 1, d.M, d.D, d.J, dxp, win, static_cast<float*>(dx), d.D, static_cast<const float*>(dx_accum)};
     const PairGemm gw{1, 0, d.D, d.J, d.M, Pair16{w.x_hi, w.x_lo, d.D}, dxp, g.in_proj_weight, d.J, nullptr};
     const PairGemm both[2] = {d.J >= d.M ? gx : gw, d.J >= d.M ? gw : gx};
-    if (gl) PMB_CUDA(cudaStreamWaitEvent(st, gl->ev[5], 0));      // the dt columns of the dxzd pair
+    if (gl && !scan_dt) PMB_CUDA(cudaStreamWaitEvent(st, gl->ev[5], 0));      // the dt columns of the dxzd pair
     PMB_TRY(gemm_pairs_group(st, both, 2));
     if (gl) PMB_TRY(order_after(gl->s, gl->ev[3], st));           // dW_out and the small reductions are done when this block is
   } else {

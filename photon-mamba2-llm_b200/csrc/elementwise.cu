@@ -144,18 +144,14 @@ pmb_status conv_silu_dt_fwd(cudaStream_t st, const Dims& d, const float* xzd, co
 // A thread owns one channel and TT time steps; per-(block-row) partial dw/db go to `partial`
 // (rows = gridDim.y, K+1 values per channel) and are summed by column_sum_kernel (fixed order).
 // ---------------------------------------------------------------------------------------------
+// The work of one thread: channels [c, c + VEC) of batch b, time steps [t0, t1); writes its rows of the data gradient
+// and leaves its share of the parameter gradients in dwacc / dbacc.
 template <int K, int VEC, int TT>
-__global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
-                                                            const float* __restrict__ w, const float* __restrict__ bias,
-                                                            const float* __restrict__ dact, float* __restrict__ dxzd,
-                                                            float* __restrict__ partial, int X, int T,
-                                                            uint16_t* __restrict__ pair_hi, uint16_t* __restrict__ pair_lo) {
-  int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
-  if (c >= X) return;
-  int tblocks = (T + TT - 1) / TT;
-  int b = blockIdx.y / tblocks;
-  int t0 = (blockIdx.y % tblocks) * TT;
-  int t1 = min(t0 + TT, T);
+__device__ __forceinline__ void conv_bwd_thread(const float* __restrict__ xzd, int64_t ldx, int col0, const float* __restrict__ w,
+                                                const float* __restrict__ bias, const float* __restrict__ dact,
+                                                float* __restrict__ dxzd, int X, int T, uint16_t* __restrict__ pair_hi,
+                                                uint16_t* __restrict__ pair_lo, int c, int b, int t0, int t1,
+                                                float (&dwacc)[VEC][K], float (&dbacc)[VEC]) {
   float wr[VEC][K], br[VEC];
 #pragma unroll
   for (int v = 0; v < VEC; ++v) {
@@ -167,7 +163,7 @@ __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restr
   const float* dsrc = dact + (int64_t)b * T * X + c;
   float* ddst = dxzd + (int64_t)b * T * ldx + col0 + c;
   // xin holds xbc[t-(K-1) .. t]; dus holds du[t-(K-1) .. t] for the current t.
-  float xin[VEC][K], dus[VEC][K], dwacc[VEC][K], dbacc[VEC];
+  float xin[VEC][K], dus[VEC][K];
 #pragma unroll
   for (int v = 0; v < VEC; ++v) {
     dbacc[v] = 0.0f;
@@ -240,7 +236,24 @@ __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restr
       else ddst[(int64_t)tp * ldx] = g[0];
     }
   }
-  // partial = [gridDim.y rows of X*K weight partials][gridDim.y rows of X bias partials]
+}
+
+// partial = [gridDim.y rows of X*K weight partials][gridDim.y rows of X bias partials]
+// One thread = one channel group and TT time steps, its own partial row (any shape, any alignment).
+template <int K, int VEC, int TT>
+__global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
+                                                            const float* __restrict__ w, const float* __restrict__ bias,
+                                                            const float* __restrict__ dact, float* __restrict__ dxzd,
+                                                            float* __restrict__ partial, int X, int T,
+                                                            uint16_t* __restrict__ pair_hi, uint16_t* __restrict__ pair_lo) {
+  int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  if (c >= X) return;
+  int tblocks = (T + TT - 1) / TT;
+  int b = blockIdx.y / tblocks;
+  int t0 = (blockIdx.y % tblocks) * TT;
+  int t1 = min(t0 + TT, T);
+  float dwacc[VEC][K], dbacc[VEC];
+  conv_bwd_thread<K, VEC, TT>(xzd, ldx, col0, w, bias, dact, dxzd, X, T, pair_hi, pair_lo, c, b, t0, t1, dwacc, dbacc);
   float* prow = partial + (int64_t)blockIdx.y * X * K;
   float* pbias = partial + (int64_t)gridDim.y * X * K + (int64_t)blockIdx.y * X;
 #pragma unroll
@@ -248,6 +261,63 @@ __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restr
 #pragma unroll
     for (int k = 0; k < K; ++k) prow[(int64_t)(c + v) * K + k] = dwacc[v][k];
     pbias[c + v] = dbacc[v];
+  }
+}
+
+// The same work with the parameter-gradient partials summed inside the CTA: 256 threads = 32 time slices x 8 channel
+// quads (a 128-byte strip of every row), so a CTA covers 32 TT time steps of 32 channels and writes ONE partial row
+// entry per channel instead of one per thread: 32 times fewer partial bytes than the kernel above, which at a few
+// thousand tokens moved more partial sums than data.  Sums run in a fixed order (shuffles, then warps 0..7).
+constexpr int CONV_SLICES = 32;
+template <int K, int TT>
+__global__ void __launch_bounds__(256) conv_silu_bwd_strip_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
+                                                                  const float* __restrict__ w, const float* __restrict__ bias,
+                                                                  const float* __restrict__ dact, float* __restrict__ dxzd,
+                                                                  float* __restrict__ partial, int X, int T,
+                                                                  uint16_t* __restrict__ pair_hi, uint16_t* __restrict__ pair_lo) {
+  constexpr int NV = 4 * K + 4;
+  __shared__ float red[8][8][NV];
+  const int tx = threadIdx.x & 7, slice = threadIdx.x >> 3, warp = threadIdx.x >> 5;
+  const int c = (blockIdx.x * 8 + tx) * 4;
+  const int tblocks = (T + CONV_SLICES * TT - 1) / (CONV_SLICES * TT);
+  const int b = blockIdx.y / tblocks;
+  const int t0 = (blockIdx.y % tblocks) * (CONV_SLICES * TT) + slice * TT;
+  const int t1 = min(t0 + TT, T);
+  float dwacc[4][K], dbacc[4];
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    dbacc[v] = 0.0f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) dwacc[v][k] = 0.0f;
+  }
+  if (c < X && t0 < T) conv_bwd_thread<K, 4, TT>(xzd, ldx, col0, w, bias, dact, dxzd, X, T, pair_hi, pair_lo, c, b, t0, t1, dwacc, dbacc);
+  float vals[NV];
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) vals[v * K + k] = dwacc[v][k];
+    vals[4 * K + v] = dbacc[v];
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {          // the four time slices of a warp that share a channel quad
+    vals[i] += __shfl_xor_sync(0xffffffffu, vals[i], 8);
+    vals[i] += __shfl_xor_sync(0xffffffffu, vals[i], 16);
+  }
+  if ((threadIdx.x & 31) < 8) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) red[warp][tx][i] = vals[i];
+  }
+  __syncthreads();
+  if (threadIdx.x < 8 * NV) {
+    const int q = threadIdx.x / NV, i = threadIdx.x % NV;
+    const int cc = (blockIdx.x * 8 + q) * 4;
+    if (cc < X) {
+      float tot = 0.0f;
+#pragma unroll
+      for (int wv = 0; wv < 8; ++wv) tot += red[wv][q][i];
+      if (i < 4 * K) partial[(int64_t)blockIdx.y * X * K + (int64_t)cc * K + i] = tot;      // (cc + v) * K + k with i = v * K + k
+      else partial[(int64_t)gridDim.y * X * K + (int64_t)blockIdx.y * X + cc + (i - 4 * K)] = tot;
+    }
   }
 }
 
@@ -261,6 +331,16 @@ size_t conv_bwd_ws_bytes(const Dims& d) {
   return align_up((size_t)d.B * tblocks * d.X * (d.K + 1) * sizeof(float), 256);
 }
 
+// Rows of `partial` the launch below writes (what column_sum has to add up).
+static int64_t conv_bwd_partial_rows(const Dims& d, bool strip) {
+  const int tt = conv_bwd_tt(d);
+  return (int64_t)d.B * (strip ? cdiv(d.T, CONV_SLICES * tt) : cdiv(d.T, tt));
+}
+static bool conv_bwd_strip_ok(const Dims& d, const float* xzd, const float* dact, const float* dxzd) {
+  return (d.X % 4 == 0) && (d.J % 4 == 0) && (d.I % 4 == 0) && d.K <= 4 &&
+         ((reinterpret_cast<uintptr_t>(xzd) | reinterpret_cast<uintptr_t>(dact) | reinterpret_cast<uintptr_t>(dxzd)) % 16 == 0);
+}
+
 template <int K>
 static pmb_status launch_conv_bwd_k(cudaStream_t st, const Dims& d, const float* xzd, const float* w, const float* b,
                                     const float* dact, float* dxzd, float* partial, uint16_t* pair_hi, uint16_t* pair_lo) {
@@ -268,7 +348,14 @@ static pmb_status launch_conv_bwd_k(cudaStream_t st, const Dims& d, const float*
   int tblocks = (d.T + tt - 1) / tt;
   bool vec = (d.X % 4 == 0) && (d.J % 4 == 0) && (d.I % 4 == 0) &&
              ((reinterpret_cast<uintptr_t>(xzd) | reinterpret_cast<uintptr_t>(dact) | reinterpret_cast<uintptr_t>(dxzd)) % 16 == 0);
-  if (vec) {
+  if (conv_bwd_strip_ok(d, xzd, dact, dxzd)) {
+    if constexpr (K <= 4) {
+      dim3 grid((unsigned)cdiv(d.X, 32), (unsigned)conv_bwd_partial_rows(d, true));
+      if (tt == 16) conv_silu_bwd_strip_kernel<K, 16><<<grid, 256, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
+      else if (tt == 8) conv_silu_bwd_strip_kernel<K, 8><<<grid, 256, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
+      else conv_silu_bwd_strip_kernel<K, 4><<<grid, 256, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
+    }
+  } else if (vec) {
     dim3 grid((unsigned)cdiv(d.X / 4, 128), (unsigned)(d.B * tblocks));
     if (tt == 16) conv_silu_bwd_kernel<K, 4, 16><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
     else if (tt == 8) conv_silu_bwd_kernel<K, 4, 8><<<grid, 128, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
@@ -299,9 +386,7 @@ pmb_status conv_silu_bwd(cudaStream_t st, const Dims& d, const float* xzd, const
     case 8: PMB_TRY(launch_conv_bwd_k<8>(st, d, xzd, w, b, dact, dxzd, partial, pair_hi, pair_lo)); break;
     default: return fail(PMB_ERR_SHAPE, "d_conv %d unsupported", d.K);
   }
-  const int tt = conv_bwd_tt(d);
-  int tblocks = (d.T + tt - 1) / tt;
-  int64_t rows = (int64_t)d.B * tblocks;
+  const int64_t rows = conv_bwd_partial_rows(d, conv_bwd_strip_ok(d, xzd, dact, dxzd));
   cudaStream_t rs = st;
   if (red) { PMB_TRY(order_after(st, red->ev[4], red->s)); rs = red->s; }
   column_sum_kernel<<<(unsigned)cdiv(d.X * d.K, 32), 256, 0, rs>>>(partial, rows, d.X * d.K, dw);

@@ -102,7 +102,13 @@ struct SsdGrads {
   float* ddt;   // dt != NULL mode: gradient w.r.t. dt (B,T,H)
   float* dA;    // (H) gradient w.r.t. A
   float* dD;    // (H) gradient w.r.t. D, or NULL
+  // Optional, honoured only when ssd_bwd_takes_pairs() is true for the call (dt != NULL mode): the gradient w.r.t. the
+  // pre-softplus dt, ddt_raw = ddt (1 - exp(-dt)), written at [token * ld + col0 + h] as a bf16 pair (lo may be NULL:
+  // plain bf16 rounding), its sum over tokens d_dt_bias (H), and d_a_log (H) = A dA.
+  struct RawDt { uint16_t* hi = nullptr; uint16_t* lo = nullptr; int64_t ld = 0; int col0 = 0; float* d_dt_bias = nullptr; float* d_a_log = nullptr; } raw;
 };
+// true when the backward with these arguments runs on bf16 pairs (fused intra-chunk kernel) and serves SsdGrads::raw
+bool ssd_bwd_takes_pairs(const SsdIn& in, const float* dy, int64_t lddy, const SsdGrads& g);
 pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy, const float* dy, int64_t lddy,
                    const SsdGrads& g, const SsdWs& ws);
 

@@ -493,6 +493,79 @@ __global__ void __launch_bounds__(256) state_dot_kernel(SsdP p, float* __restric
   if (threadIdx.x == 0) dsend[bch] = tot;
 }
 
+// Reverse scan and d[b,c,h] = <dh[c], h_prev[c]> in one launch for the pair path: one CTA per (b,h), a thread owns
+// ITEMS groups of four adjacent p; the chunk values are fetched four chunks at a time before the dependent chain.
+// Per-chunk dot products: warp sums into shared memory, then one thread per chunk adds the warps in order.
+constexpr int SCAN_DOT_MAX_NC = 64;
+template <int ITEMS>
+__global__ void __launch_bounds__(1024) state_scan_rev_dot_kernel(SsdP p, float* __restrict__ buf, uint16_t* __restrict__ pair_hi,
+                                                                  uint16_t* __restrict__ pair_lo, float* __restrict__ dsend) {
+  __shared__ float wdot[SCAN_DOT_MAX_NC][32];
+  const int bh = blockIdx.x, h = bh % p.H, bb = bh / p.H;
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nth = blockDim.x;
+  const int64_t NP = (int64_t)p.N * p.P;
+  const float* send = p.S + ((int64_t)bb * p.H + h) * p.T + p.Q - 1;
+  float4 run[ITEMS];
+#pragma unroll
+  for (int it = 0; it < ITEMS; ++it) run[it] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int c0 = 0; c0 < p.nc; c0 += 4) {
+    float4 q[4][ITEMS], hv[4][ITEMS]; float dec[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int cc = p.nc - 1 - (c0 + j);
+      if (cc >= 0) {
+        const int64_t base = (((int64_t)bb * p.nc + cc) * p.H + h) * NP;
+#pragma unroll
+        for (int it = 0; it < ITEMS; ++it) {
+          const int64_t e = ((int64_t)it * nth + tid) * 4;
+          if (e < NP) { q[j][it] = *reinterpret_cast<const float4*>(buf + base + e); hv[j][it] = *reinterpret_cast<const float4*>(p.hprev + base + e); }
+        }
+        dec[j] = expf(send[(int64_t)cc * p.Q]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int cc = p.nc - 1 - (c0 + j);
+      if (cc >= 0) {
+        const int64_t base = (((int64_t)bb * p.nc + cc) * p.H + h) * NP;
+        float dot = 0.0f;
+#pragma unroll
+        for (int it = 0; it < ITEMS; ++it) {
+          const int64_t e = ((int64_t)it * nth + tid) * 4;
+          if (e < NP) {
+            const float4 r = run[it];
+            *reinterpret_cast<float4*>(buf + base + e) = r;
+            store_pair4(pair_hi + base + e, pair_lo + base + e, r.x, r.y, r.z, r.w);
+            dot = fmaf(r.x, hv[j][it].x, fmaf(r.y, hv[j][it].y, fmaf(r.z, hv[j][it].z, fmaf(r.w, hv[j][it].w, dot))));
+            run[it] = make_float4(fmaf(dec[j], r.x, q[j][it].x), fmaf(dec[j], r.y, q[j][it].y), fmaf(dec[j], r.z, q[j][it].z), fmaf(dec[j], r.w, q[j][it].w));
+          }
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) wdot[cc][wid] = dot;
+      }
+    }
+  }
+  __syncthreads();
+  if (tid < p.nc) {
+    float tot = 0.0f;
+    for (int j = 0; j < (nth >> 5); ++j) tot += wdot[tid][j];
+    dsend[((int64_t)bb * p.nc + tid) * p.H + h] = tot;
+  }
+}
+
+// true when the merged kernel took the launch
+static bool launch_state_scan_rev_dot(cudaStream_t st, const SsdP& p, float* buf, uint16_t* pair_hi, uint16_t* pair_lo, float* dsend) {
+  const int64_t quads = (int64_t)p.N * p.P / 4;
+  if ((p.P & 3) || !pair_hi || !pair_lo || !p.hprev || p.nc > SCAN_DOT_MAX_NC || quads > 4 * 1024) return false;
+  const int items = quads <= 1024 ? 1 : (quads <= 2048 ? 2 : 4);
+  const unsigned threads = (unsigned)(((quads + items - 1) / items + 31) / 32 * 32);
+  const unsigned grid = (unsigned)(p.B * p.H);
+  if (items == 1) state_scan_rev_dot_kernel<1><<<grid, threads, 0, st>>>(p, buf, pair_hi, pair_lo, dsend);
+  else if (items == 2) state_scan_rev_dot_kernel<2><<<grid, threads, 0, st>>>(p, buf, pair_hi, pair_lo, dsend);
+  else state_scan_rev_dot_kernel<4><<<grid, threads, 0, st>>>(p, buf, pair_hi, pair_lo, dsend);
+  return true;
+}
+
 static pmb_status launch_state_scan(cudaStream_t st, const SsdP& p, float* buf, const float* init, float* last, int reverse,
                                     uint16_t* pair_hi = nullptr, uint16_t* pair_lo = nullptr) {
   const int64_t NP = (int64_t)p.N * p.P;
@@ -679,51 +752,79 @@ __global__ void __launch_bounds__(PREP_THREADS) chunk_rows_finish_kernel(SsdP p,
 // goes through y - D x or through two separately rounded matrix products.  da = reverse cumsum(dS);
 // ddt = <dx~, x> + A da;  dx = dx~ dt + D dY;  per-chunk partials of dA and dD.
 struct WSums { const float* rpart; const float* csum; const float* esum; const float* yoff; int nb; };
-__global__ void __launch_bounds__(PREP_THREADS) chunk_rows_finish_w_kernel(SsdP p, WSums ws, float* __restrict__ dx, int64_t lddx,
+// 512 threads: 32 half-warps, each with two rows in flight per pass (all loads of both rows are issued before the
+// first use), because at a few thousand tokens the launch has about one CTA per SM and is bound by loads in flight.
+constexpr int ROWS_THREADS = 512;
+__global__ void __launch_bounds__(ROWS_THREADS) chunk_rows_finish_w_kernel(SsdP p, WSums ws, float* __restrict__ dx, int64_t lddx,
                                                                            const float* __restrict__ dd, float* __restrict__ da_out,
-                                                                           float* __restrict__ ddt_out, float* __restrict__ part) {
-  __shared__ float s_ddtx[PREP_MAX_Q], s_dS[PREP_MAX_Q], s_dD[PREP_MAX_Q], s_dt[PREP_MAX_Q], s_e[PREP_MAX_Q], wsum[PREP_THREADS / 32], red[32];
+                                                                           float* __restrict__ ddt_out, float* __restrict__ part,
+                                                                           SsdGrads::RawDt raw) {
+  __shared__ float s_ddtx[PREP_MAX_Q], s_dS[PREP_MAX_Q], s_dD[PREP_MAX_Q], s_dt[PREP_MAX_Q], s_e[PREP_MAX_Q], wsum[ROWS_THREADS / 32], red[32];
+  constexpr int NHW = ROWS_THREADS / 16;
   const int w = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const int h = w % p.H, bc = w / p.H, cc = bc % p.nc, bb = bc / p.nc;
   const float Dv = p.D ? p.D[h] : 0.0f;
   const int64_t tok0 = p.tok(bb, cc, 0);
   const int P4 = p.P >> 2;
-  const int sub = lane >> 4, l16 = lane & 15;
-  for (int t0 = wid * 2; t0 < p.Q; t0 += (PREP_THREADS / 32) * 2) {
-    const int t = t0 + sub;
-    float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f, dtv = 1.0f;
-    if (t < p.Q) {
-      const int64_t tk = tok0 + t;
-      dtv = p.dtv(tk, h);
-      for (int j = l16; j < P4; j += 16) {
-        const float4 xv = reinterpret_cast<const float4*>(p.x + tk * p.ldx + h * p.P)[j];
-        const float4 dxt = reinterpret_cast<const float4*>(p.dxt + tk * (int64_t)(p.H * p.P) + h * p.P)[j];
-        const float4 dyv = reinterpret_cast<const float4*>(p.dy + tk * p.lddy + h * p.P)[j];
-        const float4 yo = reinterpret_cast<const float4*>(ws.yoff + tk * (int64_t)(p.H * p.P) + h * p.P)[j];
-        s1 = fmaf(dxt.x, xv.x, fmaf(dxt.y, xv.y, fmaf(dxt.z, xv.z, fmaf(dxt.w, xv.w, s1))));
-        s2 = fmaf(dyv.x, yo.x, fmaf(dyv.y, yo.y, fmaf(dyv.z, yo.z, fmaf(dyv.w, yo.w, s2))));
-        s3 = fmaf(dyv.x, xv.x, fmaf(dyv.y, xv.y, fmaf(dyv.z, xv.z, fmaf(dyv.w, xv.w, s3))));
-        reinterpret_cast<float4*>(dx + tk * lddx + h * p.P)[j] =
-            make_float4(fmaf(dxt.x, dtv, Dv * dyv.x), fmaf(dxt.y, dtv, Dv * dyv.y), fmaf(dxt.z, dtv, Dv * dyv.z), fmaf(dxt.w, dtv, Dv * dyv.w));
+  const int hw = tid >> 4, l16 = lane & 15;
+  const int64_t hp = (int64_t)p.H * p.P;
+  for (int tb = 0; tb < p.Q; tb += 2 * NHW) {
+    const int t[2] = {tb + hw, tb + NHW + hw};
+    float s1[2] = {0.0f, 0.0f}, s2[2] = {0.0f, 0.0f}, s3[2] = {0.0f, 0.0f}, dtv[2] = {1.0f, 1.0f};
+    float rr[2] = {0.0f, 0.0f}, cs[2] = {0.0f, 0.0f}, es[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (t[u] < p.Q) {
+        const int64_t tk = tok0 + t[u];
+        dtv[u] = p.dtv(tk, h);
+        if (l16 == 0) {
+          const int64_t idx = tk * p.H + h;
+          for (int rb = 0; rb <= t[u] / 128; ++rb) rr[u] += ws.rpart[((int64_t)w * ws.nb + rb) * p.Q + t[u]];   // row blocks whose rows s can be < t
+          cs[u] = ws.csum[idx]; es[u] = ws.esum[idx];
+        }
+      }
+    }
+    for (int j = l16; j < P4; j += 16) {
+      float4 xv[2], dxt[2], dyv[2], yo[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (t[u] < p.Q) {
+          const int64_t tk = tok0 + t[u];
+          xv[u] = reinterpret_cast<const float4*>(p.x + tk * p.ldx + h * p.P)[j];
+          dxt[u] = reinterpret_cast<const float4*>(p.dxt + tk * hp + h * p.P)[j];
+          dyv[u] = reinterpret_cast<const float4*>(p.dy + tk * p.lddy + h * p.P)[j];
+          yo[u] = reinterpret_cast<const float4*>(ws.yoff + tk * hp + h * p.P)[j];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (t[u] < p.Q) {
+          const int64_t tk = tok0 + t[u];
+          s1[u] = fmaf(dxt[u].x, xv[u].x, fmaf(dxt[u].y, xv[u].y, fmaf(dxt[u].z, xv[u].z, fmaf(dxt[u].w, xv[u].w, s1[u]))));
+          s2[u] = fmaf(dyv[u].x, yo[u].x, fmaf(dyv[u].y, yo[u].y, fmaf(dyv[u].z, yo[u].z, fmaf(dyv[u].w, yo[u].w, s2[u]))));
+          s3[u] = fmaf(dyv[u].x, xv[u].x, fmaf(dyv[u].y, xv[u].y, fmaf(dyv[u].z, xv[u].z, fmaf(dyv[u].w, xv[u].w, s3[u]))));
+          reinterpret_cast<float4*>(dx + tk * lddx + h * p.P)[j] =
+              make_float4(fmaf(dxt[u].x, dtv[u], Dv * dyv[u].x), fmaf(dxt[u].y, dtv[u], Dv * dyv[u].y), fmaf(dxt[u].z, dtv[u], Dv * dyv[u].z),
+                          fmaf(dxt[u].w, dtv[u], Dv * dyv[u].w));
+        }
       }
     }
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) {
-      s1 += __shfl_xor_sync(0xffffffffu, s1, o); s2 += __shfl_xor_sync(0xffffffffu, s2, o); s3 += __shfl_xor_sync(0xffffffffu, s3, o);
-    }
-    if (t < p.Q && l16 == 0) {
-      const int64_t idx = (tok0 + t) * p.H + h;
-      float r = 0.0f;
-      for (int rb = 0; rb <= t / 128; ++rb) r += ws.rpart[((int64_t)w * ws.nb + rb) * p.Q + t];   // row blocks whose rows s can be < t
-      const float e = ws.esum[idx];
-      s_ddtx[t] = s1; s_dD[t] = s3; s_dt[t] = dtv; s_e[t] = e;
-      s_dS[t] = ((r - ws.csum[idx]) + s2) - e;
+    for (int u = 0; u < 2; ++u) {
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) {
+        s1[u] += __shfl_xor_sync(0xffffffffu, s1[u], o); s2[u] += __shfl_xor_sync(0xffffffffu, s2[u], o); s3[u] += __shfl_xor_sync(0xffffffffu, s3[u], o);
+      }
+      if (t[u] < p.Q && l16 == 0) {
+        s_ddtx[t[u]] = s1[u]; s_dD[t[u]] = s3[u]; s_dt[t[u]] = dtv[u]; s_e[t[u]] = es[u];
+        s_dS[t[u]] = ((rr[u] - cs[u]) + s2[u]) - es[u];
+      }
     }
   }
   __syncthreads();
   // sum of e over the chunk in a fixed order, then the terms that belong to the last position
   float ep = 0.0f;
-  for (int q = tid; q < p.Q; q += PREP_THREADS) ep += s_e[q];
+  for (int q = tid; q < p.Q; q += ROWS_THREADS) ep += s_e[q];
   const float esum = block_sum(ep, red);
   if (tid == 0) {
     const float send = p.S[((int64_t)bb * p.H + h) * p.T + (int64_t)cc * p.Q + p.Q - 1];
@@ -731,8 +832,8 @@ __global__ void __launch_bounds__(PREP_THREADS) chunk_rows_finish_w_kernel(SsdP 
   }
   __syncthreads();
   const float Ah = p.dt ? p.A[h] : 0.0f;
-  float carry = 0.0f, pA = 0.0f, pD = 0.0f;
-  for (int r0 = 0; r0 < p.Q; r0 += PREP_THREADS) {
+  float carry = 0.0f, pA = 0.0f, pD = 0.0f, pB = 0.0f;
+  for (int r0 = 0; r0 < p.Q; r0 += ROWS_THREADS) {
     const int q = p.Q - 1 - (r0 + tid);
     float v = q >= 0 ? s_dS[q] : 0.0f;
 #pragma unroll
@@ -744,22 +845,54 @@ __global__ void __launch_bounds__(PREP_THREADS) chunk_rows_finish_w_kernel(SsdP 
     v += off;
     if (q >= 0) {
       const int64_t idx = (tok0 + q) * p.H + h;
-      if (p.dt) { ddt_out[idx] = fmaf(Ah, v, s_ddtx[q]); pA = fmaf(v, s_dt[q], pA); pD += s_dD[q]; }
+      if (p.dt) {
+        const float ddt = fmaf(Ah, v, s_ddtx[q]);
+        ddt_out[idx] = ddt; pA = fmaf(v, s_dt[q], pA); pD += s_dD[q];
+        if (raw.hi) {      // through the softplus: d softplus(u) / du = sigmoid(u) = 1 - exp(-softplus(u))
+          const float gr = ddt * (-expm1f(-s_dt[q]));
+          const int64_t o = (tok0 + q) * raw.ld + raw.col0 + h;
+          uint32_t hh, ll;
+          split_bf16_pair(gr, hh, ll);
+          raw.hi[o] = (uint16_t)hh;
+          if (raw.lo) raw.lo[o] = (uint16_t)ll;
+          pB += gr;
+        }
+      }
       else da_out[idx] = v;
     }
     float tot = carry;
-    for (int j = 0; j < PREP_THREADS / 32; ++j) tot += wsum[j];
+    for (int j = 0; j < ROWS_THREADS / 32; ++j) tot += wsum[j];
     carry = tot;
     __syncthreads();
   }
   if (p.dt) {
     const float tA = block_sum(pA, red);
     const float tD = block_sum(pD, red);
+    const float tB = block_sum(pB, red);
     if (tid == 0) {
       part[(int64_t)bc * p.H + h] = tA;
       part[(int64_t)p.B * p.nc * p.H + (int64_t)bc * p.H + h] = tD;
+      part[2 * (int64_t)p.B * p.nc * p.H + (int64_t)bc * p.H + h] = tB;
     }
   }
+}
+
+// The per-head sums of the pair path in one launch: thread h adds the per-(b,c) partials of dA, dD and (when asked
+// for) d_dt_bias in a fixed order; d_a_log = A dA.
+__global__ void head_finish_kernel(const float* __restrict__ part, int rows, int H, const float* __restrict__ A, float* __restrict__ dA,
+                                   float* __restrict__ dD, float* __restrict__ d_dt_bias, float* __restrict__ d_a_log) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= H) return;
+  float a = 0.0f, d = 0.0f, b = 0.0f;
+  for (int r = 0; r < rows; ++r) {
+    a += part[(int64_t)r * H + h];
+    d += part[((int64_t)rows + r) * H + h];
+    b += part[(2 * (int64_t)rows + r) * H + h];
+  }
+  dA[h] = a;
+  if (dD) dD[h] = d;
+  if (d_dt_bias) d_dt_bias[h] = b;
+  if (d_a_log) d_a_log[h] = A[h] * a;
 }
 
 // Sums the split-K partial tiles in a fixed order.  mode 0: dG (lower-triangular 64x64 tiles only, the
@@ -824,7 +957,7 @@ void ssd_ws_take(Arena& ar, int B, int T, int H, int P, int N, int G, int Q, Ssd
     w.dG = ar.take<float>(qq);
     w.dxt = ar.take<float>(hp);
     w.rows = ar.take<float>((size_t)4 * B * T * H);
-    w.part = ar.take<float>((size_t)B * nc * 2 * H);
+    w.part = ar.take<float>((size_t)B * nc * 3 * H);
     {
       int nbcg = B * nc * G, hpg = H / G, qt = (int)cdiv(Q, BM);
       size_t a = (size_t)pick_nsplit(nbcg, qt * (qt + 1) / 2, hpg) * nbcg * Q * Q;
@@ -836,6 +969,13 @@ void ssd_ws_take(Arena& ar, int B, int T, int H, int P, int N, int G, int Q, Ssd
         if (dbc > need) need = dbc;
         size_t dgp = (size_t)ssd_tc_dg_nsplit_dims(B, T, H, G, Q) * nbcg * Q * Q;
         if (dgp > need) need = dgp;
+      }
+      if (fz) {
+        // pair path: dC and dB run side by side, each with its own partial tiles
+        size_t dbc2 = (size_t)2 * ssd_pairs_dbc_nsplit(B, T, H, N, G, Q) * nbcg * Q * N;
+        if (dbc2 > need) need = dbc2;
+        size_t dgp2 = (size_t)ssd_pairs_dg_nsplit(B, T, H, G, Q) * nbcg * Q * Q;
+        if (dgp2 > need) need = dgp2;
       }
       w.splitk = ar.take<float>(need);
     }
@@ -1033,6 +1173,12 @@ __global__ void __launch_bounds__(256) dys_pair_kernel(const float* __restrict__
   store_pair4(hi + o, lo + o, v.x * f, v.y * f, v.z * f, v.w * f);
 }
 
+bool ssd_bwd_takes_pairs(const SsdIn& in, const float* dy, int64_t lddy, const SsdGrads& g) {
+  const bool tc = ssd_tc_supported(in) && (lddy % 4 == 0) && (reinterpret_cast<uintptr_t>(dy) % 16 == 0) && (g.lddbc % 4 == 0) &&
+                  ((reinterpret_cast<uintptr_t>(g.db) | reinterpret_cast<uintptr_t>(g.dc)) % 16 == 0);
+  return tc && fused_enabled() && ssd_fused_supported(in.P, in.N, in.Q, true) && (g.lddx % 4 == 0) && (reinterpret_cast<uintptr_t>(g.dx) % 16 == 0);
+}
+
 pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy, const float* dy, int64_t lddy,
                    const SsdGrads& g, const SsdWs& ws) {
   SsdP p;
@@ -1045,8 +1191,7 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   const bool tc = ssd_tc_supported(in) && (lddy % 4 == 0) && (reinterpret_cast<uintptr_t>(dy) % 16 == 0) && (g.lddbc % 4 == 0) &&
                   ((reinterpret_cast<uintptr_t>(g.db) | reinterpret_cast<uintptr_t>(g.dc)) % 16 == 0);
   const bool tc_group = tc;
-  const bool fz = tc && fused_enabled() && ssd_fused_supported(p.P, p.N, p.Q, true) && (g.lddx % 4 == 0) &&
-                  (reinterpret_cast<uintptr_t>(g.dx) % 16 == 0);
+  const bool fz = ssd_bwd_takes_pairs(in, dy, lddy, g);
   SideLane* lane = nullptr;
   if (tc) PMB_TRY(side_lane(0, &lane));
   cudaStream_t sb = lane ? lane->s : st;                      // stream of the dG -> dC -> dB chain
@@ -1071,9 +1216,13 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   if (lane) PMB_CUDA(cudaEventRecord(lane->ev[1], st));       // dY exp(S) is ready (dC reads it)
   {
     ProfScope prof(st, "ssd_bwd_state_pass", 0.0, 12.0 * p.B * p.H * p.N * p.P * p.nc);
-    PMB_TRY(launch_state_scan(st, p, p.dh, nullptr, nullptr, 1, fz ? ws.dh_hi : nullptr, ws.dh_lo));
-    state_dot_kernel<<<(unsigned)nbch, 256, 0, st>>>(p, dsend, fz ? 1 : 0);
-    PMB_LAUNCHED();
+    if (fz && launch_state_scan_rev_dot(st, p, p.dh, ws.dh_hi, ws.dh_lo, dsend)) {
+      PMB_LAUNCHED();
+    } else {
+      PMB_TRY(launch_state_scan(st, p, p.dh, nullptr, nullptr, 1, fz ? ws.dh_hi : nullptr, ws.dh_lo));
+      state_dot_kernel<<<(unsigned)nbch, 256, 0, st>>>(p, dsend, fz ? 1 : 0);
+      PMB_LAUNCHED();
+    }
   }
   if (lane) PMB_CUDA(cudaEventRecord(lane->ev[2], st));       // dh is ready (dB reads it)
   if (fz) {
@@ -1099,7 +1248,7 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
                           reinterpret_cast<uintptr_t>(g.dx) | reinterpret_cast<uintptr_t>(p.dxt)) % 16 == 0);
     if (fz) {
       WSums wsm{ws.rpart, ws.csum, ws.esum, ws.yoff, p.Q / 128};
-      chunk_rows_finish_w_kernel<<<(unsigned)nbch, PREP_THREADS, 0, st>>>(p, wsm, g.dx, g.lddx, dsend, g.da, g.ddt, ws.part);
+      chunk_rows_finish_w_kernel<<<(unsigned)nbch, ROWS_THREADS, 0, st>>>(p, wsm, g.dx, g.lddx, dsend, g.da, g.ddt, ws.part, in.dt ? g.raw : SsdGrads::RawDt{});
       PMB_LAUNCHED();
     } else if (vec_ok && nbch <= 4 * 148 && p.Q <= PREP_MAX_Q) {
       chunk_rows_finish_kernel<<<(unsigned)nbch, PREP_THREADS, 0, st>>>(p, g.dx, g.lddx, dsend, g.da, g.ddt, ws.part);
@@ -1111,8 +1260,14 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
       PMB_LAUNCHED();
     }
   }
-  auto head_sums = [&](cudaStream_t s) -> pmb_status {   // part = [dA partials (B*nc,H)] [dD partials (B*nc,H)]
+  auto head_sums = [&](cudaStream_t s) -> pmb_status {   // part = [dA partials (B*nc,H)] [dD partials (B*nc,H)] [d_dt_bias partials]
     if (!in.dt) return PMB_OK;
+    if (fz) {
+      head_finish_kernel<<<(unsigned)cdiv(p.H, 128), 128, 0, s>>>(ws.part, p.B * p.nc, p.H, in.A, g.dA, g.dD, g.raw.hi ? g.raw.d_dt_bias : nullptr,
+                                                                  g.raw.hi ? g.raw.d_a_log : nullptr);
+      PMB_LAUNCHED();
+      return PMB_OK;
+    }
     PMB_TRY(column_sum(s, ws.part, (int64_t)p.B * p.nc, p.H, g.dA));
     if (g.dD) PMB_TRY(column_sum(s, ws.part + (int64_t)p.B * p.nc * p.H, (int64_t)p.B * p.nc, p.H, g.dD));
     return PMB_OK;
@@ -1123,10 +1278,11 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   // The three per-group contractions sum over the heads of the group; with few (batch, chunk) pairs the
   // head loop is split across CTAs and the partial tiles are summed in a fixed order afterwards.
   const int qt = (int)cdiv(p.Q, BM);
-  auto reduce = [&](int nsplit, int cols, int mode, float* out, int64_t ld, int tile = BM) -> pmb_status {
+  auto reduce = [&](int nsplit, int cols, int mode, float* out, int64_t ld, int tile = BM, cudaStream_t rs = nullptr,
+                    const float* part = nullptr) -> pmb_status {
     if (nsplit <= 1) return PMB_OK;
     int64_t total = (int64_t)nbcg * p.Q * cols;
-    splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, tc_group ? sb : st>>>(ws.splitk, nsplit, p.Q, cols, mode, p.G, p.Q, out, ld, total, tile, 0,
+    splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, rs ? rs : (tc_group ? sb : st)>>>(part ? part : ws.splitk, nsplit, p.Q, cols, mode, p.G, p.Q, out, ld, total, tile, 0,
                                                                                      (mode == 0 && fz) ? ws.dg_hi : nullptr, ws.dg_lo);
     PMB_LAUNCHED();
     return PMB_OK;
@@ -1139,18 +1295,26 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
       PMB_TRY(reduce(nsg, p.Q, 0, ws.dG, 0, 128));
     }
     const int ns = ssd_pairs_dbc_nsplit(p.B, p.T, p.H, p.N, p.G, p.Q);
+    // dC and dB both wait for dG only: they run side by side, each with its own partial tiles
+    SideLane* lane_b = nullptr;
+    if (lane) PMB_TRY(side_lane(5, &lane_b));
+    if (lane_b) PMB_CUDA(cudaEventRecord(lane->ev[5], sb));               // dG and its pair are ready
     {
       if (lane) PMB_CUDA(cudaStreamWaitEvent(sb, lane->ev[1], 0));       // (the forward's h_prev pair is long there)
       ProfScope prof(sb, "ssd_bwd_dc_pair", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
-      PMB_TRY(ssd_pairs_dbc(sb, in, ws, 0, g.dc, g.lddbc, ns));
+      PMB_TRY(ssd_pairs_dbc(sb, in, ws, 0, g.dc, g.lddbc, ns, ws.splitk));
       PMB_TRY(reduce(ns, p.N, 1, g.dc, g.lddbc));
     }
     {
-      if (lane) PMB_CUDA(cudaStreamWaitEvent(sb, lane->ev[2], 0));       // dh and its pair are ready
-      ProfScope prof(sb, "ssd_bwd_db_pair", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
-      PMB_TRY(ssd_pairs_dbc(sb, in, ws, 1, g.db, g.lddbc, ns));
-      PMB_TRY(reduce(ns, p.N, 2, g.db, g.lddbc));
+      cudaStream_t sdb = lane_b ? lane_b->s : sb;
+      float* part_b = lane_b ? ws.splitk + (size_t)ns * nbcg * p.Q * p.N : ws.splitk;
+      if (lane_b) PMB_CUDA(cudaStreamWaitEvent(sdb, lane->ev[5], 0));
+      if (lane) PMB_CUDA(cudaStreamWaitEvent(sdb, lane->ev[2], 0));      // dh and its pair are ready
+      ProfScope prof(sdb, "ssd_bwd_db_pair", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
+      PMB_TRY(ssd_pairs_dbc(sdb, in, ws, 1, g.db, g.lddbc, ns, part_b));
+      PMB_TRY(reduce(ns, p.N, 2, g.db, g.lddbc, BM, sdb, part_b));
     }
+    if (lane_b) PMB_TRY(order_after(lane_b->s, lane_b->ev[0], sb));
     if (lane) {
       PMB_CUDA(cudaStreamWaitEvent(sb, lane->ev[4], 0));
       PMB_TRY(head_sums(sb));

@@ -43,7 +43,8 @@ pmb_status ssd_pairs_state(cudaStream_t st, const SsdIn& in, const SsdWs& ws, in
 int ssd_pairs_dg_nsplit(int B, int T, int H, int G, int Q);
 pmb_status ssd_pairs_dg(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int nsplit);       // -> ws.dg_hi/lo (nsplit == 1) or ws.splitk partials
 int ssd_pairs_dbc_nsplit(int B, int T, int H, int N, int G, int Q);
-pmb_status ssd_pairs_dbc(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int mode, float* out, int64_t ld, int nsplit);   // 0: dC, 1: dB
+// mode 0: dC, 1: dB; `part` = where the head-split partial tiles go (nsplit * B * nc * G * Q * N floats)
+pmb_status ssd_pairs_dbc(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int mode, float* out, int64_t ld, int nsplit, float* part);
 
 namespace sf {
 // cached rank-3 bf16 tensor map: dims (d0 contiguous, d1 rows with pitch s0 elements, d2 with pitch s1), box (b0, b1, 1)

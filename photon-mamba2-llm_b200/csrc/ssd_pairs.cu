@@ -241,9 +241,9 @@ int ssd_pairs_dbc_nsplit(int B, int T, int H, int N, int G, int Q) {
   return want > hpg ? hpg : want;
 }
 
-pmb_status ssd_pairs_dbc(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int mode, float* out, int64_t ld, int nsplit) {
+pmb_status ssd_pairs_dbc(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int mode, float* out, int64_t ld, int nsplit, float* part) {
   PP p = make_pp(in, ws);
-  p.out = out; p.ld = ld; p.nsplit = nsplit;
+  p.out = out; p.ld = ld; p.nsplit = nsplit; p.part = part;
   const int64_t tok = (int64_t)p.B * p.T, bcp = 2 * (int64_t)p.G * p.N, hp = (int64_t)p.H * p.P;
   const int64_t nbcg = (int64_t)p.B * p.nc * p.G, nbch = (int64_t)p.B * p.nc * p.H;
   MapSet ms{};
