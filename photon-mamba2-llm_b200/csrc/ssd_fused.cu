@@ -403,11 +403,18 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
         }
       }
     }
+    const int64_t trow = (int64_t)tok0 + row;
+    // the skip term's x for this thread's first output piece is requested before the wait for the accumulators
+    float4 xpre[8];
+    if (MODE == 0 && p.D) {
+      const float4* xs0 = reinterpret_cast<const float4*>(p.x + trow * p.ldx + h * P + 32 * grp);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) xpre[j] = xs0[j];
+    }
     const bool acc_ok = __all_sync(0xffffffffu, ok && wait_idle(ACC_FULL, 0u, 64u));
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const bool aborted = __any_sync(0xffffffffu, *abort_flag != 0);
     const bool run = acc_ok && !aborted;
-    const int64_t trow = (int64_t)tok0 + row;
     const float fac = MODE == 0 ? __expf(S_row) : __expf(sS[p.Q - 1] - S_row);
     float e_acc = 0.0f;       // mode 1: <x~_s, B_s dh> with x~ read back from the resident operand tile (hi + lo)
     if (run) {
@@ -453,7 +460,10 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
           o.y = fmaf(fac, __uint_as_float(a2[4 * j + 1]), __uint_as_float(a1[4 * j + 1]));
           o.z = fmaf(fac, __uint_as_float(a2[4 * j + 2]), __uint_as_float(a1[4 * j + 2]));
           o.w = fmaf(fac, __uint_as_float(a2[4 * j + 3]), __uint_as_float(a1[4 * j + 3]));
-          if (xs) { const float4 q = xs[j]; o.x = fmaf(dv, q.x, o.x); o.y = fmaf(dv, q.y, o.y); o.z = fmaf(dv, q.z, o.z); o.w = fmaf(dv, q.w, o.w); }
+          if (xs) {
+            const float4 q = (c0 == 32 * grp) ? xpre[j] : xs[j];
+            o.x = fmaf(dv, q.x, o.x); o.y = fmaf(dv, q.y, o.y); o.z = fmaf(dv, q.z, o.z); o.w = fmaf(dv, q.w, o.w);
+          }
           dst[j] = o;
         }
       }
