@@ -353,10 +353,15 @@ pmb_status pmb_cumsum_f32(void* stream, const float* d_x, int64_t outer, int64_t
  * to the other ranks by any host channel; every rank calls pmb_dp_init with its device current (a collective call:
  * all ranks must enter it).  NCCL is loaded at run time (libnccl.so.2, or the name in PMB_NCCL_LIB).
  * pmb_dp_allreduce_async orders an in-place average of `count` floats after everything already enqueued on `stream`
- * and runs it on the communicator's own stream; pmb_dp_sync makes `stream` wait for all of them.
+ * and runs it on the communicator's own stream; pmb_dp_allgather_async does the same for an all-gather of `bytes`
+ * bytes per rank (d_recv holds world_size * bytes, rank r's block at r * bytes); pmb_dp_sync makes `stream` wait for
+ * all of them.
  * pmb_lm_step_device_dp is pmb_lm_step_device with one such all-reduce per layer bucket (the layer's 8 gradient
- * tensors, contiguous in the flat buffer), enqueued the moment the layer's gradient kernels are, the embedding bucket
- * last, and the final wait: on return `stream` sees averaged gradients.  Every rank must make the same calls in the
+ * tensors, contiguous in the flat buffer), enqueued the moment the layer's gradient kernels are, and the final wait:
+ * on return `stream` sees averaged gradients.  The embedding bucket is exchanged in two parts: the tied head's share
+ * (the whole table, complete right after the head's backward) is all-reduced while the stack backward runs, and the
+ * token-lookup share, which exists only when the backward ends and touches at most batch * seqlen rows per rank,
+ * travels as an all-gather of those rows and their token ids and is scatter-added by every rank.  Every rank must make the same calls in the
  * same order.  These calls may be captured into a CUDA graph (after one eager step, which lets NCCL set up its
  * connections); NCCL then keeps the communicator alive for that graph, so destroy such graphs before pmb_dp_destroy,
  * which otherwise waits for them. */
@@ -366,6 +371,7 @@ pmb_status pmb_dp_init(int32_t nranks, int32_t rank, const void* h_id128, pmb_dp
 void       pmb_dp_destroy(pmb_dp* dp);
 int32_t    pmb_dp_world_size(const pmb_dp* dp);
 pmb_status pmb_dp_allreduce_async(pmb_dp* dp, void* stream, float* d_buf, int64_t count);
+pmb_status pmb_dp_allgather_async(pmb_dp* dp, void* stream, const void* d_send, void* d_recv, int64_t bytes);
 pmb_status pmb_dp_sync(pmb_dp* dp, void* stream);
 pmb_status pmb_lm_step_device_dp(pmb_lm* lm, void* stream, const int64_t* d_ids, const int64_t* d_targets, pmb_dp* dp);
 

@@ -20,6 +20,7 @@ struct NcclApi {
   ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
   const char* (*GetErrorString)(ncclResult_t) = nullptr;
@@ -39,10 +40,11 @@ static pmb_status load_nccl() {
   a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
   a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
   a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(h, "ncclAllReduce"));
+  a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(h, "ncclAllGather"));
   a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
   a.CommGetAsyncError = reinterpret_cast<decltype(a.CommGetAsyncError)>(dlsym(h, "ncclCommGetAsyncError"));
   a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
-  if (!a.GetUniqueId || !a.CommInitRank || !a.AllReduce || !a.CommDestroy || !a.GetErrorString)
+  if (!a.GetUniqueId || !a.CommInitRank || !a.AllReduce || !a.AllGather || !a.CommDestroy || !a.GetErrorString)
     return fail(PMB_ERR_UNSUPPORTED, "data parallel: the NCCL library lacks a required symbol");
   g_nccl = a;
   return PMB_OK;
@@ -117,6 +119,19 @@ extern "C" pmb_status pmb_dp_allreduce_async(pmb_dp* dp, void* stream, float* d_
   PMB_CUDA(cudaEventRecord(dp->ready, st));
   PMB_CUDA(cudaStreamWaitEvent(dp->comm_stream, dp->ready, 0));
   PMB_NCCL(g_nccl.AllReduce(d_buf, d_buf, (size_t)count, ncclFloat, ncclAvg, dp->comm, dp->comm_stream));
+  return PMB_OK;
+}
+
+extern "C" pmb_status pmb_dp_allgather_async(pmb_dp* dp, void* stream, const void* d_send, void* d_recv, int64_t bytes) {
+  if (!dp || !d_send || !d_recv || bytes <= 0) return fail(PMB_ERR_ARG, "dp_allgather_async: bad argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  PMB_CUDA(cudaEventRecord(dp->ready, st));
+  PMB_CUDA(cudaStreamWaitEvent(dp->comm_stream, dp->ready, 0));
+  if (dp->nranks == 1) {
+    PMB_CUDA(cudaMemcpyAsync(d_recv, d_send, (size_t)bytes, cudaMemcpyDeviceToDevice, dp->comm_stream));
+    return PMB_OK;
+  }
+  PMB_NCCL(g_nccl.AllGather(d_send, d_recv, (size_t)bytes, ncclChar, dp->comm, dp->comm_stream));
   return PMB_OK;
 }
 

@@ -56,14 +56,14 @@ __global__ void embedding_bwd_bf16_kernel(float* __restrict__ dtable, const int6
 }
 
 __global__ void embedding_bwd_kernel(float* __restrict__ dtable, const int64_t* __restrict__ ids, const float* __restrict__ dh,
-                                     int64_t rows, int D, int V) {
+                                     int64_t rows, int D, int V, float scale) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows * D) return;
   int64_t r = i / D;
   int c = (int)(i % D);
   int64_t id = ids[r];
   if (id < 0 || id >= V) return;
-  atomicAdd(dtable + id * D + c, dh[i]);
+  atomicAdd(dtable + id * D + c, dh[i] * scale);
 }
 
 // One block per row.  Pass 1: online max / sum-exp; pass 2: logits <- (softmax - onehot) * inv_rows.
@@ -296,6 +296,12 @@ struct pmb_lm {
   int64_t act_bytes = 0;
   std::vector<pmb_block_params> lp;
   std::vector<pmb_block_grads> lg;
+  // data-parallel step (fp32 storage): the token-lookup share of the embedding gradient is exchanged as rows, see
+  // pmb_lm_step_device_dp.  split_table != 0 while such a step is being enqueued.
+  int split_table = 0;
+  void* table_stream = nullptr;   // the stream on which the head's share of the table gradient completes
+  char* gather = nullptr;         // world_size x [(M, D) rows | (M) ids]
+  size_t gather_bytes = 0;
 };
 
 static int64_t tensor_elems(const Dims& d, int which) {
@@ -427,7 +433,7 @@ extern "C" void pmb_lm_destroy(pmb_lm* lm) {
   cudaFree(lm->params); cudaFree(lm->grads); cudaFree(lm->saved); cudaFree(lm->dhidden); cudaFree(lm->logits);
   cudaFree(lm->row_loss); cudaFree(lm->loss); cudaFree(lm->bad); cudaFree(lm->ids); cudaFree(lm->targets); cudaFree(lm->ws); cudaFree(lm->params16); cudaFree(lm->dlogits16);
   cudaFree(lm->params_hi); cudaFree(lm->params_lo); cudaFree(lm->dlog_hi); cudaFree(lm->dlog_lo); cudaFree(lm->hid_hi); cudaFree(lm->hid_lo); cudaFree(lm->dh_part);
-  cudaFree(lm->l1_pair); cudaFree(lm->saved1); cudaFree(lm->pooled); cudaFree(lm->dpool); cudaFree(lm->dh1); cudaFree(lm->hsum);
+  cudaFree(lm->gather); cudaFree(lm->l1_pair); cudaFree(lm->saved1); cudaFree(lm->pooled); cudaFree(lm->dpool); cudaFree(lm->dh1); cudaFree(lm->hsum);
   delete lm;
 }
 
@@ -641,18 +647,23 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
     }
     PMB_TRY(hier_op(lm, st, lm->dpool, lm->dhidden, lm->dhidden, 3));
   }
+  // the head's share of the table gradient is complete (on the lane that formed it): a data-parallel step starts its
+  // all-reduce now, next to the whole stack backward
+  if (lm->split_table && on_layer_done) { lm->table_stream = table_lane ? table_lane->s : st; on_layer_done(-2, user); }
   PMB_TRY(stack_bwd(st, d, L0, lm->lp.data(), w16, lm->lg.data(), lm->saved, lm->dhidden, lm->ws, lm->ws_bytes, on_layer_done, user));
   if (table_lane) PMB_TRY(order_after(table_lane->s, table_lane->ev[1], st));
-  if (h16) embedding_bwd_bf16_kernel<<<(unsigned)cdiv(M * D, 256), 256, 0, st>>>(dtable, d_ids, reinterpret_cast<const uint16_t*>(lm->dhidden), M, D, V);
-  else embedding_bwd_kernel<<<(unsigned)cdiv(M * D, 256), 256, 0, st>>>(dtable, d_ids, lm->dhidden, M, D, V);
-  PMB_LAUNCHED();
+  if (!lm->split_table) {      // (otherwise the callback below scatter-adds the rows of every rank)
+    if (h16) embedding_bwd_bf16_kernel<<<(unsigned)cdiv(M * D, 256), 256, 0, st>>>(dtable, d_ids, reinterpret_cast<const uint16_t*>(lm->dhidden), M, D, V);
+    else embedding_bwd_kernel<<<(unsigned)cdiv(M * D, 256), 256, 0, st>>>(dtable, d_ids, lm->dhidden, M, D, V, 1.0f);
+    PMB_LAUNCHED();
+  }
   if (on_layer_done) on_layer_done(-1, user);
   return PMB_OK;
 }
 
 // ---- data-parallel step: the same step with each layer's gradient bucket all-reduced (averaged) over the
 // communicator as soon as that layer's gradient kernels are enqueued, the embedding (and projection) bucket last.
-struct DpStep { pmb_lm* lm; pmb_dp* dp; void* stream; pmb_status status; };
+struct DpStep { pmb_lm* lm; pmb_dp* dp; void* stream; pmb_status status; const int64_t* ids; };
 
 static void dp_layer_done(int32_t layer, void* user) {
   DpStep* c = static_cast<DpStep*>(user);
@@ -666,16 +677,48 @@ static void dp_layer_done(int32_t layer, void* user) {
     if (layer + 1 < lm->L) b = lm->off[1 + 8 * (layer + 1)];
     if (lm->off_proj >= a && lm->off_proj < b) b = lm->off_proj;    // the projection sits between the two stacks
     reduce(a, b);
+  } else if (layer == -2) {
+    // the tied head's share of the embedding gradient, ordered after the stream that formed it
+    if (c->status == PMB_OK) c->status = pmb_dp_allreduce_async(c->dp, lm->table_stream, lm->grads + lm->off[0], lm->off[1] - lm->off[0]);
   } else {
     if (lm->off_proj >= 0) reduce(lm->off_proj, lm->off_proj + (int64_t)align_up((size_t)lm->d.D * lm->d.D, 64));
-    reduce(lm->off[0], lm->off[1]);
+    if (!lm->split_table) { reduce(lm->off[0], lm->off[1]); return; }
+    // token-lookup share: every rank's (M, D) rows of dhidden and its M ids, gathered, then added by every rank
+    // with weight 1 / world_size onto the averaged head share
+    if (c->status != PMB_OK) return;
+    cudaStream_t st = static_cast<cudaStream_t>(c->stream);
+    const int64_t M = lm->d.M; const int D = lm->d.D;
+    const int n = pmb_dp_world_size(c->dp);
+    const size_t row_bytes = (size_t)M * D * sizeof(float), id_bytes = (size_t)M * sizeof(int64_t);
+    char* rows_all = lm->gather; char* ids_all = lm->gather + (size_t)n * row_bytes;
+    c->status = pmb_dp_allgather_async(c->dp, st, lm->dhidden, rows_all, (int64_t)row_bytes);
+    if (c->status == PMB_OK) c->status = pmb_dp_allgather_async(c->dp, st, c->ids, ids_all, (int64_t)id_bytes);
+    if (c->status == PMB_OK) c->status = pmb_dp_sync(c->dp, st);     // (also: the head share's all-reduce has finished)
+    if (c->status != PMB_OK) return;
+    embedding_bwd_kernel<<<(unsigned)cdiv((int64_t)n * M * D, 256), 256, 0, st>>>(lm->grads + lm->off[0], reinterpret_cast<const int64_t*>(ids_all),
+                                                                                 reinterpret_cast<const float*>(rows_all), (int64_t)n * M, D, lm->V, 1.0f / (float)n);
+    if (cudaGetLastError() != cudaSuccess) c->status = fail(PMB_ERR_CUDA, "embedding scatter launch failed");
   }
 }
 
 extern "C" pmb_status pmb_lm_step_device_dp(pmb_lm* lm, void* stream, const int64_t* d_ids, const int64_t* d_targets, pmb_dp* dp) {
   if (!dp) return fail(PMB_ERR_ARG, "lm_step_device_dp: NULL communicator");
-  DpStep c{lm, dp, stream, PMB_OK};
-  PMB_TRY(pmb_lm_step_device(lm, stream, d_ids, d_targets, dp_layer_done, &c));
+  if (!lm) return fail(PMB_ERR_ARG, "lm_step_device_dp: NULL handle");
+  DpStep c{lm, dp, stream, PMB_OK, d_ids};
+  const int n = pmb_dp_world_size(dp);
+  // the row exchange of the embedding gradient: fp32 storage, more than one rank
+  lm->split_table = (n > 1 && !lm->bf16) ? 1 : 0;
+  if (lm->split_table) {
+    const size_t need = (size_t)n * ((size_t)lm->d.M * lm->d.D * sizeof(float) + (size_t)lm->d.M * sizeof(int64_t));
+    if (lm->gather_bytes < need) {     // first data-parallel step (make it outside stream capture)
+      cudaFree(lm->gather); lm->gather = nullptr; lm->gather_bytes = 0;
+      if (cudaMalloc(&lm->gather, need) != cudaSuccess) { lm->split_table = 0; return fail(PMB_ERR_CUDA, "lm_step_device_dp: cannot allocate the gather buffer"); }
+      lm->gather_bytes = need;
+    }
+  }
+  pmb_status s = pmb_lm_step_device(lm, stream, d_ids, d_targets, dp_layer_done, &c);
+  lm->split_table = 0;
+  PMB_TRY(s);
   PMB_TRY(c.status);
   return pmb_dp_sync(dp, stream);
 }

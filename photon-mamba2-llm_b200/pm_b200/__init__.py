@@ -122,6 +122,7 @@ def _load():
         "pmb_dp_destroy": (None, [vp]),
         "pmb_dp_world_size": (i32, [vp]),
         "pmb_dp_allreduce_async": (i32, [vp, vp, vp, i64]),
+        "pmb_dp_allgather_async": (i32, [vp, vp, vp, vp, i64]),
         "pmb_dp_sync": (i32, [vp, vp]),
         "pmb_lm_step_device_dp": (i32, [vp, vp, vp, vp, vp]),
         "pmb_selftest_bounded_wait": (i32, [vp, C.c_uint32]),

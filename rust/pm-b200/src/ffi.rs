@@ -134,6 +134,7 @@ extern "C" {
     pub fn pmb_dp_destroy(dp: *mut PmbDp);
     pub fn pmb_dp_world_size(dp: *const PmbDp) -> i32;
     pub fn pmb_dp_allreduce_async(dp: *mut PmbDp, stream: *mut c_void, d_buf: *mut f32, count: i64) -> i32;
+    pub fn pmb_dp_allgather_async(dp: *mut PmbDp, stream: *mut c_void, d_send: *const c_void, d_recv: *mut c_void, bytes: i64) -> i32;
     pub fn pmb_dp_sync(dp: *mut PmbDp, stream: *mut c_void) -> i32;
     pub fn pmb_lm_step_device_dp(lm: *mut PmbLm, stream: *mut c_void, d_ids: *const i64, d_targets: *const i64, dp: *mut PmbDp) -> i32;
     pub fn pmb_grad_sumsq_workspace_bytes() -> usize;
