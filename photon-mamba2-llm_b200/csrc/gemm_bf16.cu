@@ -11,6 +11,7 @@
 #include <map>
 #include <mutex>
 #include <tuple>
+#include <vector>
 #include "tc_common.cuh"
 #include "kernels.h"
 
@@ -37,12 +38,13 @@ constexpr int TILE_BYTES = TBM * TBK * 2;   // 16 KiB
 template <bool SPLIT> struct Cfg {
   static constexpr int STAGES = SPLIT ? 3 : 6;
   static constexpr int STAGE_BYTES = (SPLIT ? 4 : 2) * TILE_BYTES;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 4 * 2 * 4096 + 1024 + 256;   // + the epilogue's staging slots
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 4 * 2 * 4096 + 1024 + 512;   // + the epilogue's staging slots, barriers and the tile queue
 };
 constexpr int NTHREADS = 192;
 constexpr int TMEM_COLS = 256;               // two 128-column accumulators
 constexpr int EPI_SLOT_BYTES = 32 * 32 * 4;  // 32 rows x 32 fp32 columns
 constexpr int EPI_BYTES = 4 * 2 * EPI_SLOT_BYTES;
+constexpr int NQ = 4;                       // depth of the tile-id queue inside a CTA
 
 __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -160,7 +162,7 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 // block is formed.  The residual block, when there is one, is loaded into the slot first and added in place.
 template <bool SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ Group g, const int total_tiles) {
+gemm_bf16_kernel(const __grid_constant__ Group g, const int total_tiles, unsigned long long* __restrict__ sched, const unsigned long long ticket0) {
   constexpr int STAGES = Cfg<SPLIT>::STAGES;
   constexpr int STAGE_BYTES = Cfg<SPLIT>::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -174,8 +176,18 @@ gemm_bf16_kernel(const __grid_constant__ Group g, const int total_tiles) {
   auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
   auto acc_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
   auto r_bar = [&](int w, int slot) { return bars + 8u * (2 * STAGES + 4 + 2 * w + slot); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tiles_ptr + STAGES * STAGE_BYTES + EPI_BYTES + 8 * (2 * STAGES + 12));
+  auto tq_full = [&](int i) { return bars + 8u * (2 * STAGES + 12 + i); };
+  auto tq_empty = [&](int i) { return bars + 8u * (2 * STAGES + 12 + NQ + i); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tiles_ptr + STAGES * STAGE_BYTES + EPI_BYTES + 8 * (2 * STAGES + 12 + 2 * NQ));
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile int* tile_q = reinterpret_cast<volatile int*>(tmem_slot + 2);      // NQ tile ids handed from the producer to the other roles
+  // CTA b starts with tile b; every further tile is handed out by a device-wide ticket counter (*sched), so a CTA
+  // that starts late (its SM was busy with another stream's kernel) finds the rest of the work already taken instead
+  // of holding its share back.  A launch draws exactly total_tiles tickets (one per processed tile), so the counter
+  // is never reset: ticket t stands for tile gridDim.x + (t - ticket0) % total_tiles, where ticket0 is the counter's
+  // value before the launch (launches outside stream capture) or 0 (a captured launch, which owns its counter and
+  // advances it by total_tiles per replay).  sched == NULL: CTA b takes tiles b, b + gridDim.x, ...
+  auto ticket_tile = [&](unsigned long long t) { return (int)gridDim.x + (int)((t - ticket0) % (unsigned long long)total_tiles); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -183,6 +195,7 @@ gemm_bf16_kernel(const __grid_constant__ Group g, const int total_tiles) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
     for (int w = 0; w < 4; ++w) { mbar_init(r_bar(w, 0), 1); mbar_init(r_bar(w, 1), 1); }
+    for (int i = 0; i < NQ; ++i) { mbar_init(tq_full(i), 1); mbar_init(tq_empty(i), 5); }    // readers: the MMA thread + four epilogue warps
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -201,7 +214,17 @@ gemm_bf16_kernel(const __grid_constant__ Group g, const int total_tiles) {
       int s = 0; uint32_t ph = 0;
       int in_flight = 0;                       // stages armed and possibly not yet landed (for the abort drain)
       bool stop = false;
-      for (int tid = (int)blockIdx.x; tid < total_tiles && !stop; tid += (int)gridDim.x) {
+      int tid = (int)blockIdx.x;
+      for (int it = 0; !stop; ++it) {
+        // publish this tile (or the end mark) to the MMA and epilogue roles
+        const int qs = it % NQ;
+        if (!mbar_wait(tq_empty(qs), (((uint32_t)(it / NQ)) & 1u) ^ 1u)) { atomicOr(&g_bf16_status, 32u); *abort_flag = 1; break; }
+        tile_q[qs] = tid < total_tiles ? tid : -1;
+        mbar_arrive(tq_full(qs));
+        if (tid >= total_tiles) break;
+        // the next ticket is requested now and used after this tile's loads
+        unsigned long long next_ticket = 0;
+        if (sched) next_ticket = atomicAdd(sched, 1ull);
         int tile;
         const Problem& q = g.pr[pick_problem(g, tid, &tile)];
         const Params& p = q.p;
@@ -243,6 +266,7 @@ gemm_bf16_kernel(const __grid_constant__ Group g, const int total_tiles) {
           if (in_flight < STAGES) ++in_flight;
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
+        tid = sched ? ticket_tile(next_ticket) : tid + (int)gridDim.x;
       }
       if (*abort_flag) {
         // the copies already issued still land in this CTA's shared memory: wait (bounded) for each before leaving
@@ -257,9 +281,13 @@ gemm_bf16_kernel(const __grid_constant__ Group g, const int total_tiles) {
       const uint32_t d_hi = desc_hi(1024, 2);
       constexpr uint32_t LO_OFF = (2 * TILE_BYTES) >> 4;        // from the hi tiles of a stage to its lo tiles
       int s = 0; uint32_t ph = 0;
-      int it = 0;
       bool stop = false;
-      for (int tid = (int)blockIdx.x; tid < total_tiles && !stop; tid += (int)gridDim.x, ++it) {
+      for (int it = 0; !stop; ++it) {
+        const int qs = it % NQ;
+        if (!mbar_wait(tq_full(qs), ((uint32_t)(it / NQ)) & 1u)) { atomicOr(&g_bf16_status, 64u); *abort_flag = 1; break; }
+        const int tid = tile_q[qs];
+        mbar_arrive(tq_empty(qs));
+        if (tid < 0) break;
         int tile;
         const Problem& q = g.pr[pick_problem(g, tid, &tile)];
         const Params& p = q.p;
@@ -305,8 +333,14 @@ gemm_bf16_kernel(const __grid_constant__ Group g, const int total_tiles) {
     const uint32_t slot0 = epi + (uint32_t)ew * (2 * EPI_SLOT_BYTES);
     uint32_t pc = 0;                               // blocks stored so far: slot = pc & 1
     uint32_t rph0 = 0, rph1 = 0;                   // phases of the two residual barriers
-    int it = 0;
-    for (int tid = (int)blockIdx.x; tid < total_tiles; tid += (int)gridDim.x, ++it) {
+    for (int it = 0;; ++it) {
+      const int qs = it % NQ;
+      const bool have = __all_sync(0xffffffffu, mbar_wait_idle(tq_full(qs), ((uint32_t)(it / NQ)) & 1u));
+      if (!have) { if (lane == 0) { atomicOr(&g_bf16_status, 128u); *abort_flag = 1; } break; }
+      const int tid = tile_q[qs];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tq_empty(qs));
+      if (tid < 0) break;
       int tile;
       const Problem& q = g.pr[pick_problem(g, tid, &tile)];
       const Params& p = q.p;
@@ -643,6 +677,44 @@ static pmb_status make_out_maps(Problem* q) {
   return PMB_OK;
 }
 
+// Ticket counters of the persistent kernel (64-bit, never reset; see the kernel).  Launches outside stream capture
+// share EAGER_SLOTS counters round-robin and are told the counter's value before the launch, which the host tracks
+// (a launch draws exactly `tiles` tickets); a captured launch keeps a counter of its own for the life of the graph,
+// from a range that is never recycled.  Returns NULL (static tile order) when that range is used up, the counters
+// cannot be allocated, or PMB_GEMM_SCHED=0.
+static unsigned long long* sched_counter(cudaStream_t st, int64_t tiles, unsigned long long* ticket0) {
+  constexpr unsigned EAGER_SLOTS = 4096, GRAPH_SLOTS = 61440;
+  static unsigned long long* base[PMB_MAX_DEVICES] = {};
+  static bool failed[PMB_MAX_DEVICES] = {};
+  static unsigned eager_next[PMB_MAX_DEVICES] = {}, graph_next[PMB_MAX_DEVICES] = {};
+  static std::vector<unsigned long long> shadow[PMB_MAX_DEVICES];
+  static std::mutex mu;
+  static const int on = [] { const char* e = getenv("PMB_GEMM_SCHED"); return (e && e[0] == '0') ? 0 : 1; }();   // 0: static tile order
+  *ticket0 = 0;
+  if (!on) return nullptr;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PMB_MAX_DEVICES) return nullptr;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!base[dev]) {
+    if (failed[dev] || cap != cudaStreamCaptureStatusNone) return nullptr;      // (first use must be outside capture)
+    const size_t bytes = (size_t)(EAGER_SLOTS + GRAPH_SLOTS) * sizeof(unsigned long long);
+    if (cudaMalloc(&base[dev], bytes) != cudaSuccess || cudaMemset(base[dev], 0, bytes) != cudaSuccess) {
+      cudaGetLastError(); failed[dev] = true; base[dev] = nullptr; return nullptr;
+    }
+    shadow[dev].assign(EAGER_SLOTS, 0ull);
+  }
+  if (cap == cudaStreamCaptureStatusNone) {
+    const unsigned slot = eager_next[dev]++ % EAGER_SLOTS;
+    *ticket0 = shadow[dev][slot];
+    shadow[dev][slot] += (unsigned long long)tiles;
+    return base[dev] + slot;
+  }
+  if (graph_next[dev] >= GRAPH_SLOTS) return nullptr;
+  return base[dev] + EAGER_SLOTS + graph_next[dev]++;
+}
+
 // One persistent CTA per SM, fewer when there are fewer tiles.
 static unsigned persistent_grid(int64_t tiles) {
   static int sms[PMB_MAX_DEVICES] = {};
@@ -692,7 +764,11 @@ pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
     }
   }
   ProfScope prof(st, "gemm_bf16", 2.0 * M * N * K, 2.0 * ((double)M * K + (double)K * N) + (out_bf16 ? 2.0 : 4.0) * M * N * (R ? 2 : 1));
-  gemm_bf16_kernel<false><<<persistent_grid(q.tiles), NTHREADS, Cfg<false>::SMEM_BYTES, st>>>(g, q.tiles);
+  {
+    unsigned long long t0 = 0;
+    unsigned long long* sc = sched_counter(st, q.tiles, &t0);
+    gemm_bf16_kernel<false><<<persistent_grid(q.tiles), NTHREADS, Cfg<false>::SMEM_BYTES, st>>>(g, q.tiles, sc, t0);
+  }
   PMB_LAUNCHED();
   return PMB_OK;
 }
@@ -836,7 +912,11 @@ pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n, int tile
     return PMB_OK;
   }
   ProfScope prof(st, "gemm_bf16x2", flops, bytes);
-  gemm_bf16_kernel<true><<<persistent_grid(total), NTHREADS, Cfg<true>::SMEM_BYTES, st>>>(g, (int)total);
+  {
+    unsigned long long t0 = 0;
+    unsigned long long* sc = sched_counter(st, total, &t0);
+    gemm_bf16_kernel<true><<<persistent_grid(total), NTHREADS, Cfg<true>::SMEM_BYTES, st>>>(g, (int)total, sc, t0);
+  }
   PMB_LAUNCHED();
   return PMB_OK;
 }
