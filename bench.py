@@ -411,7 +411,7 @@ def run_ours(args):
 # single-kernel micro workloads (for ncu captures and per-kernel roofline numbers)
 # --------------------------------------------------------------------------------------------------
 # dram bytes per launch from the committed ncu capture of the step's dominant kernel (profiles/)
-NCU_DRAM_TRAFFIC = {"gemm_bf16x2": 16240384 + 6656}
+NCU_DRAM_TRAFFIC = {"gemm_bf16x2": 16261888 + 3072}
 
 MICRO = {
     # name: (kind, args)

@@ -149,14 +149,15 @@ static pmb_status weight_pair(cudaStream_t st, const Weights16* wx, bool in_proj
   return PMB_OK;
 }
 
+// x_pair_ready: the (hi, lo) pair of x is already in the workspace (written by the GEMM that produced x)
 static pmb_status block_fwd_core(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const BlockWs& w,
-                                 const Weights16* wx) {
+                                 const Weights16* wx, bool x_pair_ready = false) {
   const Weights16* w16 = storage_is_bf16(wx) ? wx : nullptr;
   const bool pr = !w16 && block_uses_pairs(d);
   if (w16) PMB_TRY(gemm_bf16(st, 0, 0, d.M, d.J, d.D, x, d.D, w16->in_proj, d.J, w.xzd, d.J, nullptr, 0));
   else if (pr) {
     Pair16 win;
-    PMB_TRY(split_pair16(st, static_cast<const float*>(x), d.M, d.D, d.D, w.x_hi, w.x_lo, d.D));
+    if (!x_pair_ready) PMB_TRY(split_pair16(st, static_cast<const float*>(x), d.M, d.D, d.D, w.x_hi, w.x_lo, d.D));
     PMB_TRY(weight_pair(st, wx, true, p.in_proj_weight, d.D, d.J, w.win_hi, w.win_lo, &win));
     PMB_TRY(gemm_pairs(st, 0, 0, d.M, d.J, d.D, Pair16{w.x_hi, w.x_lo, d.D}, win, w.xzd, d.J, nullptr));
   }
@@ -179,18 +180,22 @@ static pmb_status block_fwd_core(cudaStream_t st, const Dims& d, const pmb_block
 }
 
 pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* residual,
-                     void* out, void* ws, size_t ws_bytes, const Weights16* wx) {
+                     void* out, void* ws, size_t ws_bytes, const Weights16* wx, bool x_pair_ready, bool emit_out_pair) {
   const Weights16* w16 = storage_is_bf16(wx) ? wx : nullptr;
   const bool pr = !w16 && block_uses_pairs(d);
   BlockWs w;
   if (block_ws_layout(d, ws, ws_bytes, &w, w16 != nullptr, 1, 0, wx && wx->pairs) == 0 || !ws)
     return fail(PMB_ERR_WORKSPACE, "block workspace too small (%zu < %zu)", ws_bytes, block_ws_bytes(d, w16 != nullptr));
-  PMB_TRY(block_fwd_core(st, d, p, x, w, wx));
+  PMB_TRY(block_fwd_core(st, d, p, x, w, wx, x_pair_ready && pr));
   if (w16) PMB_TRY(gemm_bf16(st, 0, 0, d.M, d.D, d.I, w.normed16, d.I, w16->out_proj, d.D, out, d.D, residual, 1));
   else if (pr) {
     Pair16 wout;
     PMB_TRY(weight_pair(st, wx, false, p.out_proj_weight, d.I, d.D, w.wout_hi, w.wout_lo, &wout));
-    PMB_TRY(gemm_pairs(st, 0, 0, d.M, d.D, d.I, Pair16{w.normed_hi, w.normed_lo, d.I}, wout, static_cast<float*>(out), d.D, static_cast<const float*>(residual)));
+    // the next block reads this output as its in_proj operand: its pair leaves the epilogue (into the x pair of the
+    // one forward slot, which this block's own in_proj has long finished reading)
+    PairGemm e{0, 0, d.M, d.D, d.I, Pair16{w.normed_hi, w.normed_lo, d.I}, wout, static_cast<float*>(out), d.D, static_cast<const float*>(residual)};
+    if (emit_out_pair) e.emit = Pair16{w.x_hi, w.x_lo, d.D};
+    PMB_TRY(gemm_pairs_group(st, &e, 1));
   }
   else PMB_TRY(gemm(st, 0, 0, d.M, d.D, d.I, w.normed, d.I, p.out_proj_weight, d.D, static_cast<float*>(out), d.D, static_cast<const float*>(residual), 0));
   return PMB_OK;
@@ -210,7 +215,7 @@ static pmb_status block_recompute(cudaStream_t st, const Dims& d, const pmb_bloc
 
 static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* dout,
                               const void* dx_accum, void* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes, const Weights16* wx,
-                              int nslots, int slot, cudaEvent_t recompute_done) {
+                              int nslots, int slot, cudaEvent_t recompute_done, bool dout_pair_ready = false, bool emit_dx_pair = false) {
   const Weights16* w16 = storage_is_bf16(wx) ? wx : nullptr;
   const bool pr = !w16 && block_uses_pairs(d);
   BlockWs w;
@@ -226,7 +231,8 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   }
   Pair16 wout{}, dop{w.dout_hi, w.dout_lo, d.D};
   if (pr) {
-    PMB_TRY(split_pair16(st, static_cast<const float*>(dout), d.M, d.D, d.D, w.dout_hi, w.dout_lo, d.D));
+    // (the block above wrote the pair of its dx, which is this block's dout, from its last GEMM's epilogue)
+    if (!dout_pair_ready) PMB_TRY(split_pair16(st, static_cast<const float*>(dout), d.M, d.D, d.D, w.dout_hi, w.dout_lo, d.D));
     PMB_TRY(weight_pair(st, wx, false, p.out_proj_weight, d.I, d.D, w.wout_hi, w.wout_lo, &wout));
     // dnormed heads the critical chain of this block: it stays on the caller's stream; only dW_out is deferred
     if (gl) PMB_TRY(gemm_pairs(st, 0, 1, d.M, d.I, d.D, dop, wout, w.dnormed, d.I, nullptr));
@@ -240,6 +246,7 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   } else if (pr && gl) {
     PMB_TRY(order_after(st, gl->ev[2], gl->s));                 // the recomputed normed pair is ready
     PMB_TRY(gemm_pairs(gl->s, 1, 0, d.I, d.D, d.M, Pair16{w.normed_hi, w.normed_lo, d.I}, dop, g.out_proj_weight, d.D, nullptr));
+    PMB_CUDA(cudaEventRecord(gl->ev[0], gl->s));                // the last reader of the dout pair
   } else if (pr) {
     const PairGemm both[2] = {{1, 0, d.I, d.D, d.M, Pair16{w.normed_hi, w.normed_lo, d.I}, dop, g.out_proj_weight, d.D, nullptr},
                               {0, 1, d.M, d.I, d.D, dop, wout, w.dnormed, d.I, nullptr}};
@@ -301,7 +308,12 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
     const Pair16 win = (wx && wx->pairs) ? Pair16{wx->in_proj, wx->in_lo, d.J} : Pair16{w.win_hi, w.win_lo, d.J};
     const Pair16 dxp{w.dxzd_hi, w.dxzd_lo, d.J};
     // the two gradients of in_proj as one launch, longer K first
-    const PairGemm gx{0, 1, d.M, d.D, d.J, dxp, win, static_cast<float*>(dx), d.D, static_cast<const float*>(dx_accum)};
+    PairGemm gx{0, 1, d.M, d.D, d.J, dxp, win, static_cast<float*>(dx), d.D, static_cast<const float*>(dx_accum)};
+    if (emit_dx_pair) {
+      // dx is the next block's dout: its pair goes over this block's dout pair, once dW_out has read it
+      gx.emit = Pair16{w.dout_hi, w.dout_lo, d.D};
+      if (gl) PMB_CUDA(cudaStreamWaitEvent(st, gl->ev[0], 0));
+    }
     const PairGemm gw{1, 0, d.D, d.J, d.M, Pair16{w.x_hi, w.x_lo, d.D}, dxp, g.in_proj_weight, d.J, nullptr};
     const PairGemm both[2] = {d.J >= d.M ? gx : gw, d.J >= d.M ? gw : gx};
     if (gl && !scan_dt) PMB_CUDA(cudaStreamWaitEvent(st, gl->ev[5], 0));      // the dt columns of the dxzd pair
@@ -362,7 +374,7 @@ pmb_status stack_fwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_blo
   char* base = static_cast<char*>(saved);
   for (int l = 0; l < n_layers; ++l) {
     const void* h = base + (size_t)l * slot;
-    PMB_TRY(block_fwd(st, d, layers[l], h, h, base + (size_t)(l + 1) * slot, ws, ws_bytes, w16 ? &w16[l] : nullptr));
+    PMB_TRY(block_fwd(st, d, layers[l], h, h, base + (size_t)(l + 1) * slot, ws, ws_bytes, w16 ? &w16[l] : nullptr, l > 0, l + 1 < n_layers));
   }
   return PMB_OK;
 }
@@ -416,7 +428,7 @@ pmb_status stack_bwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_blo
     const int sl = l & 1;
     if (l > 0) PMB_TRY(recompute(l - 1));                // into the other slot, whose last readers were block l+1's kernels
     PMB_TRY(block_grads(st, d, layers[l], base + (size_t)l * slot, dhidden, dhidden, dhidden, grads[l], ws, ws_bytes,
-                        w16 ? &w16[l] : nullptr, 2, sl, rl->ev[sl]));
+                        w16 ? &w16[l] : nullptr, 2, sl, rl->ev[sl], l + 1 < n_layers, l > 0));
     PMB_CUDA(cudaEventRecord(rl->ev[2 + sl], st));
     if (on_layer_done) {
       if (cl) PMB_TRY(order_after(st, cl->ev[1], user_st));   // the callback orders its work after the caller's stream

@@ -60,6 +60,7 @@ struct Params {
   int a_mn_major, b_mn_major;
   void* C; int64_t ldc; const void* R; int out_bf16;
   int tma_out;     // fp32 result (and residual) meet the TMA rules: the epilogue stores through shared memory
+  uint16_t* e_hi; uint16_t* e_lo; int64_t lde;   // optional second output: the result as a bf16 pair (TMA-store epilogue only)
 };
 
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
@@ -381,6 +382,30 @@ gemm_bf16_kernel(const __grid_constant__ Group g, const int total_tiles, unsigne
                   r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
                   r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
                   r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+                }
+              }
+            }
+            if (p.e_hi) {
+              // the same values as a (hi, lo) bf16 pair, straight from registers: 64 contiguous bytes per row and array
+              const int m = row0 + lane;
+              if (m < p.M) {
+                uint16_t* eh = p.e_hi + (int64_t)m * p.lde + n0 + c0;
+                uint16_t* el = p.e_lo + (int64_t)m * p.lde + n0 + c0;
+                if (n0 + c0 + 32 <= p.N) {
+#pragma unroll
+                  for (int j = 0; j < 32; j += 8) {
+                    uint32_t h[8], l[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) split_bf16_pair(__uint_as_float(r[j + e]), h[e], l[e]);
+                    *reinterpret_cast<uint4*>(eh + j) = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+                    *reinterpret_cast<uint4*>(el + j) = make_uint4(l[0] | (l[1] << 16), l[2] | (l[3] << 16), l[4] | (l[5] << 16), l[6] | (l[7] << 16));
+                  }
+                } else {
+                  for (int j = 0; j < 32 && n0 + c0 + j < p.N; ++j) {
+                    uint32_t h, l;
+                    split_bf16_pair(__uint_as_float(r[j]), h, l);
+                    eh[j] = (uint16_t)h; el[j] = (uint16_t)l;
+                  }
                 }
               }
             }
@@ -882,6 +907,9 @@ pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n, int tile
     p.a_mn_major = e.ta ? 1 : 0; p.b_mn_major = e.tb ? 0 : 1;
     p.C = e.C; p.ldc = e.ldc; p.R = e.R; p.out_bf16 = 0;
     PMB_TRY(make_out_maps(&q));
+    p.e_hi = const_cast<uint16_t*>(e.emit.hi); p.e_lo = const_cast<uint16_t*>(e.emit.lo); p.lde = e.emit.ld;   // (Pair16 is declared for reading; this one is written)
+    if (p.e_hi && (!p.tma_out || !p.e_lo || (p.lde & 7) || ((reinterpret_cast<uintptr_t>(p.e_hi) | reinterpret_cast<uintptr_t>(p.e_lo)) & 15)))
+      return fail(PMB_ERR_UNSUPPORTED, "gemm_pairs: the pair output needs the TMA-store epilogue, 16-byte aligned arrays and a pitch that is a multiple of 8");
     q.tiles_n = (int)cdiv(N, TBN);
     const int64_t t = cdiv(M, TBM) * cdiv(N, TBN);
     total += t;
@@ -890,7 +918,8 @@ pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n, int tile
     flops += 2.0 * M * N * K;
     bytes += 4.0 * ((double)M * K + (double)K * N + (double)M * N * (e.R ? 2 : 1));
   }
-  const int pair_mode = pick_pair_mode(gs, n, tile_mode);
+  int pair_mode = pick_pair_mode(gs, n, tile_mode);
+  for (int i = 0; i < n; ++i) if (gs[i].emit.hi) pair_mode = 0;      // (only the single-CTA kernel writes the pair output)
   if (pair_mode) {
     const int bn2 = pair_mode == 2 ? 256 : 128;
     PMB_SMEM_OPT_IN((PairCfg<true, 256>::SMEM_BYTES), gemm_bf16_pair_kernel<true, 256>);

@@ -141,7 +141,9 @@ pmb_status split_pair16_strided(cudaStream_t st, const float* src, int64_t rows,
 // tile_mode: -1 = chosen by tile count, 0 = 128x128 single-CTA tiles, 1 = 256x128 / 2 = 256x256 CTA-pair tiles
 pmb_status gemm_pairs(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K, const Pair16& A, const Pair16& B,
                       float* C, int64_t ldc, const float* R, int tile_mode = -1);
-struct PairGemm { int ta, tb; int64_t M, N, K; Pair16 A, B; float* C; int64_t ldc; const float* R; };
+// `emit` (optional): the result is also written as a bf16 pair with row pitch emit.ld, for the product that reads it
+// next as an operand (needs the TMA-store epilogue: C 16-byte aligned, ldc a multiple of 4; otherwise the call fails)
+struct PairGemm { int ta, tb; int64_t M, N, K; Pair16 A, B; float* C; int64_t ldc; const float* R; Pair16 emit = Pair16{nullptr, nullptr, 0}; };
 // up to four independent products in one launch (tiles of g[0] first: give it the longer K)
 pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* g, int n, int tile_mode = -1);
 bool gemm_pairs_enabled();   // false when PMB_GEMM_ENGINE is tf32 or simt
@@ -164,7 +166,7 @@ size_t block_ws_bytes(const Dims& d, bool bf16 = false);
 size_t stack_ws_bytes(const Dims& d, bool bf16 = false, bool presplit = false);   // two forward slots: lets stack_bwd recompute one block ahead
 pmb_status cast_f32_bf16(cudaStream_t st, const float* src, uint16_t* dst, int64_t n);
 pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* residual,
-                     void* out, void* ws, size_t ws_bytes, const Weights16* w16);
+                     void* out, void* ws, size_t ws_bytes, const Weights16* w16, bool x_pair_ready = false, bool emit_out_pair = false);
 pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* dout,
                      const void* dx_accum, void* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes, const Weights16* w16);
 
