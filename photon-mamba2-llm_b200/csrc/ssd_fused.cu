@@ -72,8 +72,11 @@ struct Geo {
   static constexpr int V = NS * PB * T64;
   static constexpr int STAGE = COP + V;
   static constexpr int ST = NS * NK * PB * T64;
-  static constexpr int MOP1 = NS * T128;
-  static constexpr int BUDGET = (MODE == 1 ? 218 : 220) * 1024;
+  // TM (mode 0): the masked tile goes back into TMEM over G and is the A operand of the second product from there,
+  // so there are no masked-tile buffers in shared memory and two CTAs fit on an SM
+  static constexpr bool TM = (MODE == 0);
+  static constexpr int MOP1 = TM ? 0 : NS * T128;
+  static constexpr int BUDGET = TM ? 104 * 1024 : (MODE == 1 ? 218 : 220) * 1024;
   static constexpr int MB = (ROP + 2 * MOP1 + 2 * STAGE <= BUDGET) ? 2 : 1;
   static constexpr int REM = BUDGET - ROP - MB * MOP1;
   static constexpr int STAGES = REM / STAGE >= 4 ? 4 : REM / STAGE;
@@ -82,6 +85,7 @@ struct Geo {
   static constexpr int SMEM = TILES + 1024 /*alignment slack*/ + 256 /*barriers*/ + MAXQ * 4 /*S of the chunk*/ +
                               (MODE == 1 ? (2 * NGRP * NEPI * CW + 2 * RB) * 4 : 0) /*column sums of W, group exchange*/;
   static constexpr int TMEM_COLS = ((MODE == 1 ? 4 : 2) * CW + 2 * 64 * PB) <= 256 ? 256 : 512;
+  static constexpr int CTAS = (TM && TMEM_COLS == 256) ? 2 : 1;      // CTAs per SM the plan is sized for
 };
 
 struct Maps { CUtensorMap rop[2], cop[2], v[2], st[2], xr[2]; };   // [0] = hi (or the plain bf16 tensor), [1] = lo
@@ -125,7 +129,7 @@ __device__ __forceinline__ void split2(float a, float b, uint32_t& hi, uint32_t&
 }
 
 template <int MODE, int NS, int NK, int PB>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(NTHREADS, (Geo<MODE, NS, NK, PB>::CTAS))
 ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
   using GE = Geo<MODE, NS, NK, PB>;
   constexpr int STAGES = GE::STAGES, MB = GE::MB, P = 64 * PB;
@@ -281,7 +285,8 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
       auto mma_g = [&](int jj) -> bool {
         const int it = jj + 1, s = it % STAGES;
         if (!wait(LD_FULL + s, (uint32_t)((it / STAGES) & 1), 2u)) return false;
-        if (jj >= 2 && !wait(G_FREE + (jj & 1), (uint32_t)(((jj >> 1) - 1) & 1), 4u)) return false;
+        // (TM: the buffer's previous content, masked tile jj - 2, was read by a product issued before this one)
+        if (!GE::TM && jj >= 2 && !wait(G_FREE + (jj & 1), (uint32_t)(((jj >> 1) - 1) & 1), 4u)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t cop = ring_s + s * GE::STAGE;
         const uint32_t r0 = lo_k(rop_s), c0d = lo_k(cop);
@@ -311,9 +316,27 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
         if (!wait(M_READY + mb, (uint32_t)((jj / MB) & 1), 8u)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t m0d = lo_k(mop_s + mb * GE::MOP1), v0d = lo_mn(ring_s + s * GE::STAGE + GE::COP);
+        if (GE::TM) {
+          // masked tile in TMEM, in place of G: per 32 k of the block [hi: 16 columns | lo: 16 columns], 8 columns per k-step
+          const uint32_t bs = (PB * T64) >> 4;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          kstep(tA1, m0d + ((k * 32) >> 4), T128 >> 4, v0d + ((k * 2048) >> 4), (PB * T64) >> 4, id_v, (jj | k) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t ta = tG + (uint32_t)(mb * CW + (k >> 1) * 32 + (k & 1) * 8);
+            const uint32_t vb = v0d + ((k * 2048) >> 4);
+            const uint32_t acc = (jj | k) ? 1u : 0u;
+            if (NS == 2) {
+              mma_f16_ts_h(tA1, ta + 16u, vb, dh, id_v, acc);        // lo x hi
+              mma_f16_ts_h(tA1, ta, vb + bs, dh, id_v, 1u);          // hi x lo
+              mma_f16_ts_h(tA1, ta, vb, dh, id_v, 1u);               // hi x hi
+            } else {
+              mma_f16_ts_h(tA1, ta, vb, dh, id_v, acc);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            kstep(tA1, m0d + ((k * 32) >> 4), T128 >> 4, v0d + ((k * 2048) >> 4), (PB * T64) >> 4, id_v, (jj | k) ? 1u : 0u);
+        }
         umma_commit(bar(LD_EMPTY + s));
         umma_commit(bar(M_FREE + mb));
         if (jj + 2 < ncb && !mma_g(jj + 2)) { ok = false; break; }
@@ -341,7 +364,7 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
     for (int jj = grp; jj < ncb; jj += NGRP) {
       const int c0 = (cb0 + jj) * CW, mb = jj & 1, use = jj >> 1;       // use-th block of this group's buffers
       bool got = ok && wait_idle(G_FULL + mb, (uint32_t)(use & 1), 16u);
-      if (got && use >= 1) got = wait_idle(M_FREE + mb, (uint32_t)((use - 1) & 1), 32u);
+      if (!GE::TM && got && use >= 1) got = wait_idle(M_FREE + mb, (uint32_t)((use - 1) & 1), 32u);
       ok = __all_sync(0xffffffffu, got);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -357,6 +380,7 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
 #pragma unroll
             for (int e = 0; e < 32; ++e) wv[e] = __uint_as_float(d[e]);
           }
+          uint32_t mh[16], ml[16];                  // TM: this half's packed hi / lo values
 #pragma unroll
           for (int q8 = 0; q8 < 4; ++q8) {
             uint32_t hi[4], lo[4] = {0u, 0u, 0u, 0u};
@@ -379,19 +403,30 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
               }
               split2(m0, m1, hi[e2], lo[e2], NS == 2);
             }
-            const int sw = ((half * 4 + q8) ^ (r_local & 7)) << 4;     // 128-byte swizzle of the 16-byte chunk
-            *reinterpret_cast<uint4*>(mrow + sw) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-            if (NS == 2) *reinterpret_cast<uint4*>(mrow + T128 + sw) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            if (GE::TM) {
+#pragma unroll
+              for (int e2 = 0; e2 < 4; ++e2) { mh[q8 * 4 + e2] = hi[e2]; ml[q8 * 4 + e2] = lo[e2]; }
+            } else {
+              const int sw = ((half * 4 + q8) ^ (r_local & 7)) << 4;     // 128-byte swizzle of the 16-byte chunk
+              *reinterpret_cast<uint4*>(mrow + sw) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+              if (NS == 2) *reinterpret_cast<uint4*>(mrow + T128 + sw) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            }
+          }
+          if (GE::TM) {
+            // over the 32 columns of G just read: [hi of these 32 k | lo of these 32 k]
+            tmem_st16(tG + lane_addr + (uint32_t)(mb * CW + half * 32), mh);
+            if (NS == 2) tmem_st16(tG + lane_addr + (uint32_t)(mb * CW + half * 32 + 16), ml);
           }
           if (MODE == 1) {
             // column sums of W over this warp's 32 rows: lane l ends up with column half*32 + l
             rsum[(((grp * 2) + (use & 1)) * NEPI + quarter) * CW + half * 32 + lane] = warp_column_sums(wv, lane);
           }
         }
+        if (GE::TM) tmem_wait_st();
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (!GE::TM) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) { mbar_arrive(bar(G_FREE + mb)); mbar_arrive(bar(M_READY + mb)); }
+        if (lane == 0) { if (!GE::TM) mbar_arrive(bar(G_FREE + mb)); mbar_arrive(bar(M_READY + mb)); }
       }
       if (MODE == 1) {
         if (grp == 0) asm volatile("bar.sync 1, %0;" ::"n"(32 * NEPI) : "memory");
@@ -566,6 +601,15 @@ static pmb_status launch(cudaStream_t st, const FusedArgs& a) {
   p.off_out = a.off_out; p.csum = a.csum; p.esum = a.esum; p.rpart = a.rpart;
   p.status = status_ptr();
   PMB_SMEM_OPT_IN(GE::SMEM, ssd_fused_kernel<MODE, NS, NK, PB>);
+  if (GE::CTAS > 1) {      // two CTAs per SM need the largest shared-memory carve-out
+    static DeviceOnce once;
+    int dev = 0;
+    PMB_CUDA(cudaGetDevice(&dev));
+    if (once.pending(dev)) {
+      PMB_CUDA(cudaFuncSetAttribute(ssd_fused_kernel<MODE, NS, NK, PB>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+      once.mark(dev);
+    }
+  }
   dim3 grid((unsigned)(a.B * nc * a.H), (unsigned)p.nb);
   ssd_fused_kernel<MODE, NS, NK, PB><<<grid, NTHREADS, GE::SMEM, st>>>(ms, p);
   PMB_LAUNCHED();

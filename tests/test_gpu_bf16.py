@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from oracle import mamba2_oracle as orc
-from util import assert_close, block_params, cuda_params, randn, rel_err, to_pm_cfg
+from util import assert_close, assert_close_bf16, block_params, cuda_params, randn, rel_err, to_pm_cfg
 
 pytestmark = pytest.mark.gpu
 BF16_TOL = 2e-2
@@ -85,6 +85,10 @@ def test_lm_step_bf16_storage(pm):
     ls = [{k: v.clone().requires_grad_(True) for k, v in p.items()} for p in layers]
     loss_ref = orc.lm_loss(er, ls, cfg, ids, tg)
     loss_ref.backward()
+    # the same model evaluated by the oracle with bf16 storage: how far two correct bf16 evaluations are apart
+    e16 = embed.clone().requires_grad_(True)
+    l16 = [{k: v.clone().requires_grad_(True) for k, v in p.items()} for p in layers]
+    orc.lm_loss(e16, l16, cfg, ids, tg, cdt=torch.bfloat16).backward()
     lm = pm.FlatMamba(to_pm_cfg(cfg), L, V, B, T, compute_dtype=torch.bfloat16)
     lm.load(embed.cuda(), [cuda_params(p) for p in layers])
     loss = lm.step_host(ids.pin_memory(), tg.pin_memory())
@@ -93,7 +97,7 @@ def test_lm_step_bf16_storage(pm):
     assert_close(g_embed, er.grad, tol=BF16_TOL, what="d_embed")
     for l in range(L):
         for k in layers[l]:
-            assert_close(g_layers[l][k], ls[l][k].grad, tol=BF16_TOL, what=f"layer {l} d_{k}")
+            assert_close_bf16(g_layers[l][k], ls[l][k].grad, l16[l][k].grad, what=f"layer {l} d_{k}", tol=BF16_TOL)
     assert pm.device_status() == 0
     lm.close()
 

@@ -111,3 +111,13 @@ def report(case: str, what: str, ours, ref, tol=FP32_TOL, elem_tol=ELEM_TOL):
     assert e <= tol, f"{case} {what}: rel max err {e:.3e} > {tol:.1e}"
     assert ee <= elem_tol, f"{case} {what}: element-wise err {ee:.3e} > {elem_tol:.1e}"
     return e, ee
+
+
+def assert_close_bf16(ours, ref32, ref16, what, tol=2e-2):
+    """bf16-storage bound: 2e-2 of the fp32 oracle, or -- where two correct bf16 evaluations differ by more at the test's
+    tiny widths -- twice the distance between the oracle run in bf16 and the oracle run in fp32."""
+    e = rel_err(ours, ref32)
+    floor = rel_err(ref16, ref32)
+    bound = max(tol, 2.0 * floor)
+    assert e <= bound, f"{what}: rel max err {e:.3e} > {bound:.1e} (bf16 oracle vs fp32 oracle: {floor:.3e})"
+    return e, floor
