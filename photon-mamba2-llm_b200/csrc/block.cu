@@ -327,9 +327,10 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
 }
 
 pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* dout,
-                     const void* dx_accum, void* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes, const Weights16* wx) {
+                     const void* dx_accum, void* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes, const Weights16* wx,
+                     bool dout_pair_ready, bool emit_dx_pair) {
   PMB_TRY(block_recompute(st, d, p, x, ws, ws_bytes, wx, 1, 0));
-  return block_grads(st, d, p, x, dout, dx_accum, dx, g, ws, ws_bytes, wx, 1, 0, nullptr);
+  return block_grads(st, d, p, x, dout, dx_accum, dx, g, ws, ws_bytes, wx, 1, 0, nullptr, dout_pair_ready, emit_dx_pair);
 }
 
 }  // namespace pmb
@@ -397,7 +398,8 @@ pmb_status stack_bwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_blo
   if (ahead_on && n_layers > 1 && (bf || block_uses_pairs(d)) && ws_bytes >= stack_ws_bytes(d, bf, w16 && w16->pairs)) PMB_TRY(get_side_lane(3, &rl));
   if (!rl) {
     for (int l = n_layers - 1; l >= 0; --l) {
-      PMB_TRY(block_bwd(st, d, layers[l], base + (size_t)l * slot, dhidden, dhidden, dhidden, grads[l], ws, ws_bytes, w16 ? &w16[l] : nullptr));
+      PMB_TRY(block_bwd(st, d, layers[l], base + (size_t)l * slot, dhidden, dhidden, dhidden, grads[l], ws, ws_bytes, w16 ? &w16[l] : nullptr,
+                        l + 1 < n_layers, l > 0));
       if (on_layer_done) on_layer_done(l, user);
     }
     return PMB_OK;

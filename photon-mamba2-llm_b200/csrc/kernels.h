@@ -168,7 +168,8 @@ pmb_status cast_f32_bf16(cudaStream_t st, const float* src, uint16_t* dst, int64
 pmb_status block_fwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* residual,
                      void* out, void* ws, size_t ws_bytes, const Weights16* w16, bool x_pair_ready = false, bool emit_out_pair = false);
 pmb_status block_bwd(cudaStream_t st, const Dims& d, const pmb_block_params& p, const void* x, const void* dout,
-                     const void* dx_accum, void* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes, const Weights16* w16);
+                     const void* dx_accum, void* dx, const pmb_block_grads& g, void* ws, size_t ws_bytes, const Weights16* w16,
+                     bool dout_pair_ready = false, bool emit_dx_pair = false);
 
 pmb_status stack_fwd(cudaStream_t st, const Dims& d, int n_layers, const pmb_block_params* layers, const Weights16* w16,
                      void* saved, void* ws, size_t ws_bytes);
