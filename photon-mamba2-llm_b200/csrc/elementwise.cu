@@ -321,9 +321,13 @@ __global__ void __launch_bounds__(256) conv_silu_bwd_strip_kernel(const float* _
   }
 }
 
-// time steps per thread: short runs put enough threads in flight at a few thousand tokens (the kernel is
-// latency-bound there), long runs re-read fewer halo rows and write fewer partial sums at large token counts
-static int conv_bwd_tt(const Dims& d) { return d.M >= 32768 ? 16 : (d.M >= 8192 ? 8 : 4); }
+// time steps per thread: long runs recompute fewer halo rows (K - 1 per run) and write fewer partial sums; measured at
+// 2048 tokens with the strip kernel: 4 steps 49 us, 8 steps 42 us, 16 steps 55 us per launch (PMB_CONV_TT overrides)
+static int conv_bwd_tt(const Dims& d) {
+  static const int forced = [] { const char* e = getenv("PMB_CONV_TT"); return e ? atoi(e) : 0; }();
+  if (forced == 4 || forced == 8 || forced == 16) return forced;
+  return d.M >= 32768 ? 16 : 8;
+}
 
 size_t conv_bwd_ws_bytes(const Dims& d) {
   const int CONV_BWD_TT = conv_bwd_tt(d);

@@ -6,6 +6,8 @@
 // 32 KiB per stage) and the ring is 6 deep.  K-major tiles: 128-byte rows, 128-byte swizzle.  MN-major
 // tiles: blocks of 64 elements along M/N, 64 k-rows of 128 bytes per block, same swizzle.
 // Every mbarrier wait is bounded; on expiry the kernel raises the device status word and drains.
+#include <climits>
+#include <cstdint>
 #include <cstdlib>
 #include <cstring>
 #include <map>
@@ -868,14 +870,18 @@ static int pick_pair_mode(const PairGemm* gs, int n, int tile_mode) {
   static const int env = [] { const char* e = getenv("PMB_GEMM_PAIR"); return e ? atoi(e) : -1; }();
   const int forced = tile_mode >= 0 ? tile_mode : env;
   if (forced >= 0 && forced <= 2) return forced;
-  int64_t clusters = 0;
+  int64_t clusters = 0, min_k = INT64_MAX;
   for (int i = 0; i < n; ++i) {
     if (gs[i].M <= 128) return 0;        // a pair tile would be half empty
     clusters += cdiv(gs[i].M, 256) * cdiv(gs[i].N, 256);
+    if (gs[i].K < min_k) min_k = gs[i].K;
   }
-  // 256x256 pair tiles read 96 bytes of shared memory per tensor-core clock instead of 128 and win once there are
-  // several full waves of the 74 CTA pairs; 256x128 pair tiles measured no faster than single-CTA tiles
-  return clusters >= 4 * 74 ? 2 : 0;
+  // 256x256 pair tiles fetch half the operand bytes per flop and win where the main loop dominates: several full
+  // waves of the 74 CTA pairs and a long K (65 k tokens, K = 3224: 458 against 358 TFLOP/s).  With a short K the
+  // one-tile-per-cluster kernel spends as long in its prologue and epilogue as in the loop and the persistent
+  // single-CTA kernel is as fast or faster (K = 768, 1536 at 65 k tokens: equal; the LM head at 1024 rows, K = 768 and
+  // 1024: 6 % less GEMM time).  256x128 pair tiles measured no faster than single-CTA tiles.
+  return (clusters >= 4 * 74 && min_k >= 2048) ? 2 : 0;
 }
 
 // C (fp32) = op(A) op(B) (+ R) with both operands given as bf16 pairs: three kind::f16 MMAs per k-step.
