@@ -260,7 +260,10 @@ pmb_status pmb_mamba2_step(void* stream, const pmb_mamba2_config* cfg, const pmb
  * Workspace: pmb_mamba2_block_workspace_bytes() is enough.  With pmb_stack_workspace_bytes() (a second copy of the
  * forward part of the block workspace) pmb_stack_bwd enqueues the recompute of block l-1 on an internal second
  * stream while block l's gradient kernels run; results are identical.  The internal streams and events are
- * created on the first call on a device (make that call outside stream capture).  One host thread per device. */
+ * created on the first call on a device (make that call outside stream capture).  One host thread per device.
+ * Captured into a CUDA graph, every GEMM launch of the library keeps a tile-scheduler counter of its own for the life
+ * of the graph (a few bytes of device memory, never recycled): replay one instantiation of a captured graph at a
+ * time, not two copies of it concurrently. */
 typedef void (*pmb_layer_callback)(int32_t layer, void* user);
 size_t pmb_stack_workspace_bytes(const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen);
 pmb_status pmb_stack_fwd_ckpt(void* stream, const pmb_mamba2_config* cfg, int32_t n_layers,
