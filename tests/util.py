@@ -1,4 +1,5 @@
 """Shared helpers for the parity tests."""
+import os
 import pathlib
 
 import numpy as np
@@ -86,7 +87,9 @@ def cuda_params(p):
 # dims; tests/test_oracle.py::test_elementwise_metric_noise_floor_of_fp32 pins that), so 1e-4 is below the noise
 # floor of fp32 itself.  The GPU tests gate it at ELEM_TOL and write the measured values to PARITY_REPORT.
 ELEM_TOL = 1e-2
-PARITY_REPORT = pathlib.Path(__file__).resolve().parent.parent / "gpurun_out" / "parity_report.jsonl"
+# (PMB_PARITY_REPORT names the file; by default it goes to test_reports/ at the repository root, which git ignores)
+PARITY_REPORT = pathlib.Path(os.environ.get("PMB_PARITY_REPORT") or
+                             pathlib.Path(__file__).resolve().parent.parent / "test_reports" / "parity_report.jsonl")
 
 
 def elem_err(ours, ref) -> float:
