@@ -207,10 +207,13 @@ gemm_bf16_kernel(const __grid_constant__ Group g, const int total_tiles, unsigne
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // The producer needs the barriers (its own thread initialised them) but not the TMEM address: warp 0 only arrives at
+  // the set-up barrier and starts loading while warp 1's TMEM allocation is still under way; the other warps wait.
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
+  if (warp == 0) { __syncwarp(); asm volatile("bar.arrive 1, %0;" ::"n"(NTHREADS) : "memory"); }
+  else asm volatile("bar.sync 1, %0;" ::"n"(NTHREADS) : "memory");
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = warp == 0 ? 0u : *tmem_slot;
 
   if (warp == 0) {
     if (lane == 0) {
