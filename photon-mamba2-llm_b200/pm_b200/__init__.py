@@ -772,6 +772,16 @@ class DataParallel:
     def all_reduce_async(self, t: torch.Tensor):
         _check(lib.pmb_dp_allreduce_async(self._h, _stream(), _dev(t, "tensor").data_ptr(), t.numel()))
 
+    def all_gather_async(self, send: torch.Tensor, recv: torch.Tensor):
+        """recv (nranks * send.numel() elements of send's dtype) receives every rank's `send`, rank r's block at r."""
+        for t, name in ((send, "send"), (recv, "recv")):      # any dtype: the exchange is by bytes
+            if not (t.is_cuda and t.is_contiguous()):
+                raise PmbError(2, f"{name}: expected a contiguous CUDA tensor")
+        nbytes = send.numel() * send.element_size()
+        if recv.numel() * recv.element_size() != self.nranks * nbytes:
+            raise ValueError("all_gather_async: recv must hold nranks blocks of send's size")
+        _check(lib.pmb_dp_allgather_async(self._h, _stream(), send.data_ptr(), recv.data_ptr(), nbytes))
+
     def sync(self):
         _check(lib.pmb_dp_sync(self._h, _stream()))
 
