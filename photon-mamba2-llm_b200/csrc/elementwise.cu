@@ -14,7 +14,8 @@ __global__ void column_sum_kernel(const float* __restrict__ partial, int64_t row
 // each input row is read (TT+K-1)/TT times.
 // ---------------------------------------------------------------------------------------------
 template <int K, int VEC, int TT>
-__global__ void __launch_bounds__(128) conv_silu_fwd_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
+// (eight CTAs per SM: the 1024 CTAs of a 2048-token launch are then resident at once instead of 1.15 waves)
+__global__ void __launch_bounds__(128, 8) conv_silu_fwd_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
                                                             const float* __restrict__ w, const float* __restrict__ bias,
                                                             float* __restrict__ act, int X, int T, ConvPairOut po) {
   int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;

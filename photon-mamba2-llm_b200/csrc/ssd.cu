@@ -752,10 +752,11 @@ __global__ void __launch_bounds__(PREP_THREADS) chunk_rows_finish_kernel(SsdP p,
 // goes through y - D x or through two separately rounded matrix products.  da = reverse cumsum(dS);
 // ddt = <dx~, x> + A da;  dx = dx~ dt + D dY;  per-chunk partials of dA and dD.
 struct WSums { const float* rpart; const float* csum; const float* esum; const float* yoff; int nb; };
-// 512 threads: 32 half-warps, each with two rows in flight per pass (all loads of both rows are issued before the
-// first use), because at a few thousand tokens the launch has about one CTA per SM and is bound by loads in flight.
-constexpr int ROWS_THREADS = 512;
-__global__ void __launch_bounds__(ROWS_THREADS) chunk_rows_finish_w_kernel(SsdP p, WSums ws, float* __restrict__ dx, int64_t lddx,
+// Each half-warp has two rows in flight per pass (all loads of both rows are issued before the first use), and two
+// CTAs fit on an SM, so that the 192 CTAs of a 2048-token launch at 24 heads are resident at once (one CTA per SM
+// meant a second wave of 44 CTAs).
+constexpr int ROWS_THREADS = 256;
+__global__ void __launch_bounds__(ROWS_THREADS, 2) chunk_rows_finish_w_kernel(SsdP p, WSums ws, float* __restrict__ dx, int64_t lddx,
                                                                            const float* __restrict__ dd, float* __restrict__ da_out,
                                                                            float* __restrict__ ddt_out, float* __restrict__ part,
                                                                            SsdGrads::RawDt raw) {
