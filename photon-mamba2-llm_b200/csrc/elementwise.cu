@@ -265,19 +265,21 @@ __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const float* __restr
   }
 }
 
-// The same work with the parameter-gradient partials summed inside the CTA: 256 threads = 32 time slices x 8 channel
-// quads (a 128-byte strip of every row), so a CTA covers 32 TT time steps of 32 channels and writes ONE partial row
-// entry per channel instead of one per thread: 32 times fewer partial bytes than the kernel above, which at a few
-// thousand tokens moved more partial sums than data.  Sums run in a fixed order (shuffles, then warps 0..7).
-constexpr int CONV_SLICES = 32;
+// The same work with the parameter-gradient partials summed inside the CTA: 128 threads = 16 time slices x 8 channel
+// quads (a 128-byte strip of every row), so a CTA covers 16 TT time steps of 32 channels and writes ONE partial row
+// entry per channel instead of one per thread: 16 times fewer partial bytes than the kernel above, which at a few
+// thousand tokens moved more partial sums than data.  Sums run in a fixed order (shuffles, then the warps in order).
+// (The thread keeps TT + K - 1 rows of two tensors in registers, about 170 of them: small CTAs let three share an SM.)
+constexpr int CONV_SLICES = 16;
+constexpr int CONV_STRIP_THREADS = CONV_SLICES * 8;
 template <int K, int TT>
-__global__ void __launch_bounds__(256) conv_silu_bwd_strip_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
+__global__ void __launch_bounds__(CONV_STRIP_THREADS) conv_silu_bwd_strip_kernel(const float* __restrict__ xzd, int64_t ldx, int col0,
                                                                   const float* __restrict__ w, const float* __restrict__ bias,
                                                                   const float* __restrict__ dact, float* __restrict__ dxzd,
                                                                   float* __restrict__ partial, int X, int T,
                                                                   uint16_t* __restrict__ pair_hi, uint16_t* __restrict__ pair_lo) {
-  constexpr int NV = 4 * K + 4;
-  __shared__ float red[8][8][NV];
+  constexpr int NV = 4 * K + 4, NW = CONV_STRIP_THREADS / 32;
+  __shared__ float red[NW][8][NV];
   const int tx = threadIdx.x & 7, slice = threadIdx.x >> 3, warp = threadIdx.x >> 5;
   const int c = (blockIdx.x * 8 + tx) * 4;
   const int tblocks = (T + CONV_SLICES * TT - 1) / (CONV_SLICES * TT);
@@ -309,13 +311,13 @@ __global__ void __launch_bounds__(256) conv_silu_bwd_strip_kernel(const float* _
     for (int i = 0; i < NV; ++i) red[warp][tx][i] = vals[i];
   }
   __syncthreads();
-  if (threadIdx.x < 8 * NV) {
-    const int q = threadIdx.x / NV, i = threadIdx.x % NV;
+  for (int e = threadIdx.x; e < 8 * NV; e += CONV_STRIP_THREADS) {
+    const int q = e / NV, i = e % NV;
     const int cc = (blockIdx.x * 8 + q) * 4;
     if (cc < X) {
       float tot = 0.0f;
 #pragma unroll
-      for (int wv = 0; wv < 8; ++wv) tot += red[wv][q][i];
+      for (int wv = 0; wv < NW; ++wv) tot += red[wv][q][i];
       if (i < 4 * K) partial[(int64_t)blockIdx.y * X * K + (int64_t)cc * K + i] = tot;      // (cc + v) * K + k with i = v * K + k
       else partial[(int64_t)gridDim.y * X * K + (int64_t)blockIdx.y * X + cc + (i - 4 * K)] = tot;
     }
@@ -356,9 +358,9 @@ static pmb_status launch_conv_bwd_k(cudaStream_t st, const Dims& d, const float*
   if (conv_bwd_strip_ok(d, xzd, dact, dxzd)) {
     if constexpr (K <= 4) {
       dim3 grid((unsigned)cdiv(d.X, 32), (unsigned)conv_bwd_partial_rows(d, true));
-      if (tt == 16) conv_silu_bwd_strip_kernel<K, 16><<<grid, 256, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
-      else if (tt == 8) conv_silu_bwd_strip_kernel<K, 8><<<grid, 256, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
-      else conv_silu_bwd_strip_kernel<K, 4><<<grid, 256, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
+      if (tt == 16) conv_silu_bwd_strip_kernel<K, 16><<<grid, CONV_STRIP_THREADS, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
+      else if (tt == 8) conv_silu_bwd_strip_kernel<K, 8><<<grid, CONV_STRIP_THREADS, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
+      else conv_silu_bwd_strip_kernel<K, 4><<<grid, CONV_STRIP_THREADS, 0, st>>>(xzd, d.J, d.I, w, b, dact, dxzd, partial, d.X, d.T, pair_hi, pair_lo);
     }
   } else if (vec) {
     dim3 grid((unsigned)cdiv(d.X / 4, 128), (unsigned)(d.B * tblocks));
@@ -586,7 +588,7 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_bwd_kernel(const f
 // float4 variant of the backward (same row blocking and partial layout).  Optional extras (see NormBwdExtra):
 // dz as a (hi, lo) bf16 pair instead of fp32, and dY exp(S) for the scan backward.
 template <int PER>
-__global__ void __launch_bounds__(NORM_THREADS) gated_rmsnorm_bwd_vec_kernel(const float* __restrict__ dout, const float* __restrict__ y,
+__global__ void __launch_bounds__(NORM_THREADS, 3) gated_rmsnorm_bwd_vec_kernel(const float* __restrict__ dout, const float* __restrict__ y,
                                                                              const float* __restrict__ z, int64_t ldz,
                                                                              const float* __restrict__ w, const float* __restrict__ rstd,
                                                                              float* __restrict__ dy, float* __restrict__ dz, int64_t lddz,
