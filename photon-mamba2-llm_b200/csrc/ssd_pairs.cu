@@ -216,10 +216,10 @@ pmb_status ssd_pairs_state(cudaStream_t st, const SsdIn& in, const SsdWs& ws, in
 }
 
 // Head-split factor of a per-group contraction with `ctas` CTAs per split: as many splits as fit the machine in ONE wave
-// (two CTAs per SM; one CTA more than that costs a second wave), then the fewest splits that give the same number of
-// heads per CTA (fewer partial tiles to write and add up).
-static int pick_head_split(int64_t ctas, int hpg) {
-  int want = (int)((2 * 148) / (ctas > 0 ? ctas : 1));
+// (one CTA more than that costs a second wave), then the fewest splits that give the same number of heads per CTA
+// (fewer partial tiles to write and add up).  The 128-wide dG tiles run one CTA per SM, the 64-wide ones two.
+static int pick_head_split(int64_t ctas, int hpg, int ctas_per_sm) {
+  int want = (int)((ctas_per_sm * 148) / (ctas > 0 ? ctas : 1));
   if (want < 1) want = 1;
   if (want > hpg) want = hpg;
   const int per = (hpg + want - 1) / want;        // heads per CTA at that split
@@ -228,7 +228,7 @@ static int pick_head_split(int64_t ctas, int hpg) {
 
 int ssd_pairs_dg_nsplit(int B, int T, int H, int G, int Q) {
   const int nbcg = B * (T / Q) * G, hpg = H / G, qt = Q / pbg::BM;
-  return pick_head_split((int64_t)nbcg * (qt * (qt + 1) / 2), hpg);
+  return pick_head_split((int64_t)nbcg * (qt * (qt + 1) / 2), hpg, pbg::Geometry<PDG::BN, PDG::NS>::CTAS_PER_SM);
 }
 
 pmb_status ssd_pairs_dg(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int nsplit) {
@@ -245,7 +245,7 @@ pmb_status ssd_pairs_dg(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int n
 int ssd_pairs_dbc_nsplit(int B, int T, int H, int N, int G, int Q) {
   const int nbcg = B * (T / Q) * G, hpg = H / G;
   const int tiles = (Q / pbg::BM) * (int)cdiv(N, 64);
-  return pick_head_split((int64_t)nbcg * tiles, hpg);
+  return pick_head_split((int64_t)nbcg * tiles, hpg, pbg::Geometry<PDBC<0>::BN, PDBC<0>::NS>::CTAS_PER_SM);
 }
 
 pmb_status ssd_pairs_dbc(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int mode, float* out, int64_t ld, int nsplit, float* part) {
