@@ -365,11 +365,14 @@ __global__ void __launch_bounds__(PREP_THREADS) chunk_prepare_kernel(SsdP p, Cum
                                                                      uint16_t* __restrict__ xt_hi, uint16_t* __restrict__ xt_lo,
                                                                      uint16_t* __restrict__ xs_hi, uint16_t* __restrict__ xs_lo) {
   __shared__ float sS[PREP_MAX_Q], sdt[PREP_MAX_Q], wsum[PREP_THREADS / 32];
+  // gridDim.y CTAs share one (b,c,h): each repeats the short cumulative sum (same order, same values) and takes its
+  // slice of the rows in the second phase; the first of them writes dt, A and S
   const int w = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  const bool writer = blockIdx.y == 0;
   const int h = w % p.H, bc = w / p.H, cc = bc % p.nc, bb = bc / p.nc;
   const float Ah = raw.dt_raw ? -expf(raw.a_log[h]) : (p.dt ? p.A[h] : 1.0f);
   const float bias = raw.dt_raw ? raw.dt_bias[h] : 0.0f;
-  if (raw.dt_raw && bc == 0 && tid == 0) raw.A_out[h] = Ah;
+  if (raw.dt_raw && bc == 0 && tid == 0 && writer) raw.A_out[h] = Ah;
   float* Sout = p.S + ((int64_t)bb * p.H + h) * p.T + (int64_t)cc * p.Q;
   float carry = 0.0f;
   for (int q0 = 0; q0 < p.Q; q0 += PREP_THREADS) {
@@ -377,7 +380,7 @@ __global__ void __launch_bounds__(PREP_THREADS) chunk_prepare_kernel(SsdP p, Cum
     float v = 0.0f, dtv = 1.0f;
     if (q < p.Q) {
       const int64_t tk = p.tok(bb, cc, q);
-      if (raw.dt_raw) { dtv = softplus_acc(raw.dt_raw[tk * raw.ld_raw + h] + bias); raw.dt_out[tk * p.H + h] = dtv; v = Ah * dtv; }
+      if (raw.dt_raw) { dtv = softplus_acc(raw.dt_raw[tk * raw.ld_raw + h] + bias); if (writer) raw.dt_out[tk * p.H + h] = dtv; v = Ah * dtv; }
       else if (p.dt) { dtv = p.dt[tk * p.H + h]; v = Ah * dtv; }
       else v = p.a[tk * p.H + h];
     }
@@ -388,17 +391,20 @@ __global__ void __launch_bounds__(PREP_THREADS) chunk_prepare_kernel(SsdP p, Cum
     float off = carry;
     for (int j = 0; j < wid; ++j) off += wsum[j];          // fixed order: the same sums for every launch
     v += off;
-    if (q < p.Q) { sS[q] = v; sdt[q] = dtv; Sout[q] = v; }
+    if (q < p.Q) { sS[q] = v; sdt[q] = dtv; if (writer) Sout[q] = v; }
     float tot = carry;
     for (int j = 0; j < PREP_THREADS / 32; ++j) tot += wsum[j];
     carry = tot;
     __syncthreads();
   }
   const float send = sS[p.Q - 1];
-  const int P4 = p.P >> 2, total = p.Q * P4;
+  const int P4 = p.P >> 2;
+  const int rows_per = (p.Q + (int)gridDim.y - 1) / (int)gridDim.y;        // this CTA's rows [r0, r1) of the chunk
+  const int r0 = (int)blockIdx.y * rows_per, r1 = min(p.Q, r0 + rows_per);
+  const int total = r1 * P4;
   const int64_t tok0 = p.tok(bb, cc, 0);
   constexpr int U = 4;
-  for (int i0 = tid; i0 < total; i0 += U * PREP_THREADS) {
+  for (int i0 = r0 * P4 + tid; i0 < total; i0 += U * PREP_THREADS) {
     float4 v[U]; float f[U], fd[U]; int tt[U], jj[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -1116,7 +1122,9 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
     // finer-grained kernels use the memory system better)
     if (tc && nbch <= 4 * 148 && p.Q <= PREP_MAX_Q && (in.ldx % 4 == 0) && (reinterpret_cast<uintptr_t>(in.x) % 16 == 0)) {
       ProfScope prof(st, "ssd_chunk_prepare", 0.0, 8.0 * tok * p.H * (1.0 + p.P));
-      chunk_prepare_kernel<<<(unsigned)nbch, PREP_THREADS, 0, st>>>(p, raw, ws.xs, fz ? ws.xt_hi : nullptr, ws.xt_lo, fz ? ws.xs_hi : nullptr, ws.xs_lo);
+      // at a few hundred (b,c,h) the second phase (the only one with real traffic) is short of threads: split its rows
+      const unsigned ysplit = nbch <= 148 ? 4u : (nbch <= 2 * 148 ? 2u : 1u);
+      chunk_prepare_kernel<<<dim3((unsigned)nbch, ysplit), PREP_THREADS, 0, st>>>(p, raw, ws.xs, fz ? ws.xt_hi : nullptr, ws.xt_lo, fz ? ws.xs_hi : nullptr, ws.xs_lo);
       PMB_LAUNCHED();
       in_tc.xs_ready = true;
       xt_ready = fz;
