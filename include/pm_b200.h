@@ -109,10 +109,12 @@ int32_t pmb_selftest_device_once(void);
  * trans_b = 0: B is (K,N) row-major with ldb;                   1: B is stored (N,K).
  * d_R (may be NULL) is added to the product (same shape/ld as C); d_R may equal d_C.
  * engine: 0 = auto, 1 = fp32 FMA, 2 = tcgen05 3xTF32 with 128x128 tiles, 3 = tcgen05 3xTF32 with 128x64 tiles,
- * 4 / 5 / 6 = tcgen05 bf16 pairs with 128x128 single-CTA tiles / 256x256 / 256x128 CTA-pair tiles (cta_group::2): both operands are split into (hi, lo) bf16 pairs (hi + lo carries 16 mantissa bits) and each
+ * 4 / 5 / 6 = tcgen05 bf16 pairs with 128x128 tiles on the persistent single-CTA kernel / 256x256 / 256x128 CTA-pair
+ * tiles (cta_group::2): both operands are split into (hi, lo) bf16 pairs (hi + lo carries 16 mantissa bits) and each
  * k-step issues hi*hi + lo*hi + hi*lo with kind::f16, fp32 accumulation.  Error ~1e-5 of the result's scale (the
- * 3xTF32 kernels: ~1e-6), about 1.7x their speed.  Auto takes engine 4 when the operands are 16-byte aligned with row
- * lengths that are multiples of 8, else 3xTF32 when its alignment rules hold, else FMA; the environment variable
+ * 3xTF32 kernels: ~1e-6), about twice their speed.  Auto takes the pair engine when the operands are 16-byte aligned
+ * with row lengths that are multiples of 8 (the persistent kernel, or 256x256 CTA-pair tiles when there are at least
+ * 296 of them and K >= 2048), else 3xTF32 when its alignment rules hold, else FMA; the environment variable
  * PMB_GEMM_ENGINE=tf32 keeps auto off engine 4, =simt forces FMA.  Engine 4 keeps the split operands in a
  * library-owned scratch buffer that grows on demand (cudaMalloc inside the call); pmb_gemm_reserve_scratch() sizes it
  * ahead of time: 4*(|A| + |B|) bytes of the largest product. */
