@@ -21,10 +21,15 @@ namespace pmb {
 
 static __device__ unsigned int g_bf16_status = 0;
 
+namespace hb { static void sched_reset_current_device(); }
+
 pmb_status read_clear_device_status_bf16(unsigned int* word) {
   unsigned int zero = 0;
   PMB_CUDA(cudaMemcpyFromSymbol(word, g_bf16_status, sizeof(unsigned int)));
-  if (*word) PMB_CUDA(cudaMemcpyToSymbol(g_bf16_status, &zero, sizeof(unsigned int)));
+  if (*word) {
+    PMB_CUDA(cudaMemcpyToSymbol(g_bf16_status, &zero, sizeof(unsigned int)));
+    hb::sched_reset_current_device();      // a kernel that gave up may have left its tile-ticket counter out of step
+  }
   return PMB_OK;
 }
 
@@ -712,13 +717,29 @@ static pmb_status make_out_maps(Problem* q) {
 // (a launch draws exactly `tiles` tickets); a captured launch keeps a counter of its own for the life of the graph,
 // from a range that is never recycled.  Returns NULL (static tile order) when that range is used up, the counters
 // cannot be allocated, or PMB_GEMM_SCHED=0.
+constexpr unsigned EAGER_SLOTS = 4096, GRAPH_SLOTS = 61440;
+static unsigned long long* g_sched_base[PMB_MAX_DEVICES] = {};
+static std::vector<unsigned long long> g_sched_shadow[PMB_MAX_DEVICES];
+static std::mutex g_sched_mu;
+
+// After a kernel gave up on a bounded wait it may have drawn fewer tickets than its launch was accounted for: put
+// every counter of the current device (and the host's record of them) back to zero, so that later launches start
+// from a consistent state.  Called when the status word is read and found raised.
+static void sched_reset_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PMB_MAX_DEVICES) return;
+  std::lock_guard<std::mutex> lock(g_sched_mu);
+  if (!g_sched_base[dev]) return;
+  cudaMemset(g_sched_base[dev], 0, (size_t)(EAGER_SLOTS + GRAPH_SLOTS) * sizeof(unsigned long long));
+  g_sched_shadow[dev].assign(EAGER_SLOTS, 0ull);
+}
+
 static unsigned long long* sched_counter(cudaStream_t st, int64_t tiles, unsigned long long* ticket0) {
-  constexpr unsigned EAGER_SLOTS = 4096, GRAPH_SLOTS = 61440;
-  static unsigned long long* base[PMB_MAX_DEVICES] = {};
+  unsigned long long** base = g_sched_base;
+  std::vector<unsigned long long>* shadow = g_sched_shadow;
+  std::mutex& mu = g_sched_mu;
   static bool failed[PMB_MAX_DEVICES] = {};
   static unsigned eager_next[PMB_MAX_DEVICES] = {}, graph_next[PMB_MAX_DEVICES] = {};
-  static std::vector<unsigned long long> shadow[PMB_MAX_DEVICES];
-  static std::mutex mu;
   static const int on = [] { const char* e = getenv("PMB_GEMM_SCHED"); return (e && e[0] == '0') ? 0 : 1; }();   // 0: static tile order
   *ticket0 = 0;
   if (!on) return nullptr;
