@@ -157,6 +157,100 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// Epilogue of one tile for one epilogue warp: its 32 rows (row0 ..) x `ncols` columns (n0 ..) of the accumulator at
+// `tmem_acc` (lane offset included).  fp32 results that meet the TMA rules leave through the warp's two swizzled
+// staging slots (slot0) and TMA stores, the residual block TMA-loaded into the slot first (barriers rbar0 / rbar1);
+// everything else is stored row by row.  `st` carries the slot parity and the residual barriers' phases across tiles.
+struct EpiState { uint32_t pc = 0, rph0 = 0, rph1 = 0; };
+__device__ __forceinline__ void epilogue_rows(const Problem& q, const Params& p, uint32_t tmem_acc, int row0, int n0, int ncols, uint32_t slot0,
+                                              uint32_t rbar0, uint32_t rbar1, EpiState& st, int lane, volatile uint32_t* abort_flag) {
+  if (p.tma_out) {
+    if (row0 < p.M) {
+      const bool res = p.R != nullptr;
+      if (res && lane == 0) {
+        const uint32_t slot = st.pc & 1u;
+        mbar_expect_tx((slot ? rbar1 : rbar0), EPI_SLOT_BYTES);
+        tma_load_2d(slot0 + slot * EPI_SLOT_BYTES, &q.mR, n0, row0, (slot ? rbar1 : rbar0));
+      }
+#pragma unroll 1
+      for (int c0 = 0; c0 < ncols && n0 + c0 < p.N; c0 += 32) {
+        const uint32_t slot = st.pc & 1u;
+        const uint32_t sbase = slot0 + slot * EPI_SLOT_BYTES + (uint32_t)lane * 128u;
+        uint32_t r[32];
+        tmem_ld32(tmem_acc + (uint32_t)c0, r);
+        if (res) {
+          const uint32_t rp = slot ? st.rph1 : st.rph0;
+          const bool landed = __all_sync(0xffffffffu, mbar_wait((slot ? rbar1 : rbar0), rp));
+          if (slot) st.rph1 ^= 1u; else st.rph0 ^= 1u;
+          if (!landed) { if (lane == 0) { atomicOr(&g_bf16_status, 16u); *abort_flag = 1; } }
+          else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 v;
+              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                           : "r"(sbase + (uint32_t)((j ^ (lane & 7)) * 16)));
+              r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v.x);
+              r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
+              r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
+              r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+            }
+          }
+        }
+        if (p.e_hi) {
+          // the same values as a (hi, lo) bf16 pair, straight from registers: 64 contiguous bytes per row and array
+          const int m = row0 + lane;
+          if (m < p.M) {
+            uint16_t* eh = p.e_hi + (int64_t)m * p.lde + n0 + c0;
+            uint16_t* el = p.e_lo + (int64_t)m * p.lde + n0 + c0;
+            if (n0 + c0 + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint32_t h[8], l[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) split_bf16_pair(__uint_as_float(r[j + e]), h[e], l[e]);
+                *reinterpret_cast<uint4*>(eh + j) = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+                *reinterpret_cast<uint4*>(el + j) = make_uint4(l[0] | (l[1] << 16), l[2] | (l[3] << 16), l[4] | (l[5] << 16), l[6] | (l[7] << 16));
+              }
+            } else {
+              for (int j = 0; j < 32 && n0 + c0 + j < p.N; ++j) {
+                uint32_t h, l;
+                split_bf16_pair(__uint_as_float(r[j]), h, l);
+                eh[j] = (uint16_t)h; el[j] = (uint16_t)l;
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sbase + (uint32_t)((j ^ (lane & 7)) * 16)),
+                       "r"(r[4 * j]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3]) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        ++st.pc;
+        if (lane == 0) {
+          tma_store_2d(&q.mC, slot0 + slot * EPI_SLOT_BYTES, n0 + c0, row0);
+          bulk_commit();
+          bulk_wait_read<1>();               // the other slot's store has read its data: the slot is free again
+          if (res && c0 + 32 < ncols && n0 + c0 + 32 < p.N) {
+            const uint32_t nslot = st.pc & 1u;
+            mbar_expect_tx((nslot ? rbar1 : rbar0), EPI_SLOT_BYTES);
+            tma_load_2d(slot0 + nslot * EPI_SLOT_BYTES, &q.mR, n0 + c0 + 32, row0, (nslot ? rbar1 : rbar0));
+          }
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    const int m = row0 + lane;
+#pragma unroll 1
+    for (int c0 = 0; c0 < ncols; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(tmem_acc + (uint32_t)c0, r);
+      if (m < p.M) store_row_piece(p, m, n0 + c0, r);
+    }
+  }
+}
+
 // Persistent: CTA b works on tiles b, b + gridDim.x, ... of the group.  The operand ring and its phases run on
 // across tiles, so the producer is already loading the next tile while the last k-tiles of this one are
 // multiplied; the accumulator alternates between two 128-column TMEM buffers, so the epilogue warps drain tile i
@@ -342,8 +436,7 @@ gemm_bf16_kernel(const __grid_constant__ Group g, const int total_tiles, unsigne
     const int ew = warp - 2;                       // staging slots and residual barriers of this warp
     const int quarter = warp & 3;                  // the TMEM lanes this warp may read
     const uint32_t slot0 = epi + (uint32_t)ew * (2 * EPI_SLOT_BYTES);
-    uint32_t pc = 0;                               // blocks stored so far: slot = pc & 1
-    uint32_t rph0 = 0, rph1 = 0;                   // phases of the two residual barriers
+    EpiState est;                                  // slot parity and residual-barrier phases, carried across tiles
     for (int it = 0;; ++it) {
       const int qs = it % NQ;
       const bool have = __all_sync(0xffffffffu, mbar_wait_idle(tq_full(qs), ((uint32_t)(it / NQ)) & 1u));
@@ -363,91 +456,7 @@ gemm_bf16_kernel(const __grid_constant__ Group g, const int total_tiles, unsigne
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t tmem_acc = tmem_base + (uint32_t)(b * TBN) + ((uint32_t)(quarter * 32) << 16);
       const int row0 = m0 + quarter * 32;
-      if (p.tma_out) {
-        if (row0 < p.M) {
-          const bool res = p.R != nullptr;
-          if (res && lane == 0) {
-            const uint32_t slot = pc & 1u;
-            mbar_expect_tx(r_bar(ew, slot), EPI_SLOT_BYTES);
-            tma_load_2d(slot0 + slot * EPI_SLOT_BYTES, &q.mR, n0, row0, r_bar(ew, slot));
-          }
-#pragma unroll 1
-          for (int c0 = 0; c0 < TBN && n0 + c0 < p.N; c0 += 32) {
-            const uint32_t slot = pc & 1u;
-            const uint32_t sbase = slot0 + slot * EPI_SLOT_BYTES + (uint32_t)lane * 128u;
-            uint32_t r[32];
-            tmem_ld32(tmem_acc + (uint32_t)c0, r);
-            if (res) {
-              const uint32_t rp = slot ? rph1 : rph0;
-              const bool landed = __all_sync(0xffffffffu, mbar_wait(r_bar(ew, slot), rp));
-              if (slot) rph1 ^= 1u; else rph0 ^= 1u;
-              if (!landed) { if (lane == 0) { atomicOr(&g_bf16_status, 16u); *abort_flag = 1; } }
-              else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  float4 v;
-                  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                               : "r"(sbase + (uint32_t)((j ^ (lane & 7)) * 16)));
-                  r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v.x);
-                  r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
-                  r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
-                  r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
-                }
-              }
-            }
-            if (p.e_hi) {
-              // the same values as a (hi, lo) bf16 pair, straight from registers: 64 contiguous bytes per row and array
-              const int m = row0 + lane;
-              if (m < p.M) {
-                uint16_t* eh = p.e_hi + (int64_t)m * p.lde + n0 + c0;
-                uint16_t* el = p.e_lo + (int64_t)m * p.lde + n0 + c0;
-                if (n0 + c0 + 32 <= p.N) {
-#pragma unroll
-                  for (int j = 0; j < 32; j += 8) {
-                    uint32_t h[8], l[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) split_bf16_pair(__uint_as_float(r[j + e]), h[e], l[e]);
-                    *reinterpret_cast<uint4*>(eh + j) = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
-                    *reinterpret_cast<uint4*>(el + j) = make_uint4(l[0] | (l[1] << 16), l[2] | (l[3] << 16), l[4] | (l[5] << 16), l[6] | (l[7] << 16));
-                  }
-                } else {
-                  for (int j = 0; j < 32 && n0 + c0 + j < p.N; ++j) {
-                    uint32_t h, l;
-                    split_bf16_pair(__uint_as_float(r[j]), h, l);
-                    eh[j] = (uint16_t)h; el[j] = (uint16_t)l;
-                  }
-                }
-              }
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sbase + (uint32_t)((j ^ (lane & 7)) * 16)),
-                           "r"(r[4 * j]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3]) : "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            ++pc;
-            if (lane == 0) {
-              tma_store_2d(&q.mC, slot0 + slot * EPI_SLOT_BYTES, n0 + c0, row0);
-              bulk_commit();
-              bulk_wait_read<1>();               // the other slot's store has read its data: the slot is free again
-              if (res && c0 + 32 < TBN && n0 + c0 + 32 < p.N) {
-                const uint32_t nslot = pc & 1u;
-                mbar_expect_tx(r_bar(ew, nslot), EPI_SLOT_BYTES);
-                tma_load_2d(slot0 + nslot * EPI_SLOT_BYTES, &q.mR, n0 + c0 + 32, row0, r_bar(ew, nslot));
-              }
-            }
-            __syncwarp();
-          }
-        }
-      } else {
-        const int m = row0 + lane;
-#pragma unroll 1
-        for (int c0 = 0; c0 < TBN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(tmem_acc + (uint32_t)c0, r);
-          if (m < p.M) store_row_piece(p, m, n0 + c0, r);
-        }
-      }
+      epilogue_rows(q, p, tmem_acc, row0, n0, TBN, slot0, r_bar(ew, 0), r_bar(ew, 1), est, lane, abort_flag);
       // every TMEM read of this warp has completed (tcgen05.wait::ld): hand the accumulator back
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
