@@ -676,6 +676,209 @@ gemm_bf16_pair_kernel(const __grid_constant__ Group g) {
   }
 }
 
+// ---- persistent CTA-pair variant ----------------------------------------------------------------------------
+// The CTA-pair kernel above as a tile loop: cluster c works on tiles c, c + clusters, ...; the operand ring keeps
+// running across tiles; the accumulator alternates between two TMEM buffers of BN2 columns, so each CTA drains its
+// 128 rows of tile i (through the same TMA-store epilogue as the single-CTA kernel) while the leader issues tile
+// i + 1.  The epilogue warps of BOTH CTAs hand a buffer back by arriving on the leader's acc_empty barrier (count 8).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+template <bool SPLIT, int BN2> struct PairPCfg {
+  static constexpr int STAGE_BYTES = PairCfg<SPLIT, BN2>::STAGE_BYTES;
+  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 512;
+  static constexpr int TMEM = 2 * BN2;
+};
+
+template <bool SPLIT, int BN2>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1)
+gemm_bf16_pairp_kernel(const __grid_constant__ Group g, const int total_tiles) {
+  const uint32_t rank = cluster_rank();
+  const int cluster_id = (int)(blockIdx.x >> 1), nclusters = (int)(gridDim.x >> 1);
+  constexpr int BNH = BN2 / 2;
+  constexpr int TILE_B = BNH * TBK * 2;
+  constexpr int HALF_BYTES = TILE_BYTES + TILE_B;
+  constexpr int STAGE_BYTES = PairPCfg<SPLIT, BN2>::STAGE_BYTES;
+  constexpr int STAGES = PairPCfg<SPLIT, BN2>::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  uint8_t* tiles_ptr = smem_raw + (tiles - raw);
+  const uint32_t epi = tiles + STAGES * STAGE_BYTES;
+  const uint32_t bars = epi + EPI_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+  auto r_bar = [&](int w, int slot) { return bars + 8u * (2 * STAGES + 4 + 2 * w + slot); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tiles_ptr + STAGES * STAGE_BYTES + EPI_BYTES + 8 * (2 * STAGES + 12));
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 8); }
+    for (int w = 0; w < 4; ++w) { mbar_init(r_bar(w, 0), 1); mbar_init(r_bar(w, 1), 1); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "n"(PairPCfg<SPLIT, BN2>::TMEM) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();     // both CTAs' barriers are initialised before either signals the other's
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0;
+      int in_flight = 0;
+      bool stop = false;
+      for (int tid = cluster_id; tid < total_tiles && !stop; tid += nclusters) {
+        int tile;
+        const Problem& q = g.pr[pick_problem(g, tid, &tile)];
+        const Params& p = q.p;
+        const int m0 = (tile / q.tiles_n) * 256 + (int)rank * TBM;
+        const int nb0 = (tile % q.tiles_n) * BN2 + (int)rank * BNH;
+        const int num_kt = (p.K + TBK - 1) / TBK;
+        for (int kt = 0; kt < num_kt; ++kt) {
+          if (!mbar_wait(empty_bar(s), ph ^ 1u)) { atomicOr(&g_bf16_status, 1u); *abort_flag = 1; stop = true; break; }
+          if (*abort_flag) { stop = true; break; }
+          const uint32_t a_dst = tiles + s * STAGE_BYTES, b_dst = a_dst + TILE_BYTES;
+          const uint32_t fb = map_to_cta(full_bar(s), 0);            // the leader's barrier collects both CTAs' bytes
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);
+          const int k0 = kt * TBK;
+          if (!p.a_mn_major) {
+            tma_load_2d_pair(a_dst, &q.mA, k0, m0, fb);
+          } else {
+#pragma unroll
+            for (int j = 0; j < TBM / 64; ++j) tma_load_2d_pair(a_dst + j * (TBK * 128), &q.mA, m0 + 64 * j, k0, fb);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d_pair(b_dst, &q.mB, k0, nb0, fb);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(b_dst + j * (TBK * 128), &q.mB, nb0 + 64 * j, k0, fb);
+          }
+          if (SPLIT) {
+            const uint32_t al_dst = a_dst + HALF_BYTES, bl_dst = al_dst + TILE_BYTES;
+            if (!p.a_mn_major) {
+              tma_load_2d_pair(al_dst, &q.mAlo, k0, m0, fb);
+            } else {
+#pragma unroll
+              for (int j = 0; j < TBM / 64; ++j) tma_load_2d_pair(al_dst + j * (TBK * 128), &q.mAlo, m0 + 64 * j, k0, fb);
+            }
+            if (!p.b_mn_major) {
+              tma_load_2d_pair(bl_dst, &q.mBlo, k0, nb0, fb);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(bl_dst + j * (TBK * 128), &q.mBlo, nb0 + 64 * j, k0, fb);
+            }
+          }
+          if (in_flight < STAGES) ++in_flight;
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+      // after giving up, the leader still waits (bounded) for the loads both CTAs have in flight
+      if (*abort_flag && rank == 0) {
+        for (int i = 0; i < in_flight; ++i) {
+          if (--s < 0) { s = STAGES - 1; ph ^= 1u; }
+          mbar_wait(full_bar(s), ph);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t d_hi = desc_hi(1024, 2);
+      constexpr uint32_t LO_OFF = HALF_BYTES >> 4;
+      uint32_t eb0[STAGES], eb1[STAGES];
+#pragma unroll
+      for (int i = 0; i < STAGES; ++i) { eb0[i] = map_to_cta(empty_bar(i), 0); eb1[i] = map_to_cta(empty_bar(i), 1); }
+      const uint32_t af0[2] = {map_to_cta(acc_full(0), 0), map_to_cta(acc_full(1), 0)};
+      const uint32_t af1[2] = {map_to_cta(acc_full(0), 1), map_to_cta(acc_full(1), 1)};
+      int s = 0; uint32_t ph = 0;
+      int it = 0;
+      bool stop = false;
+      for (int tid = cluster_id; tid < total_tiles && !stop; tid += nclusters, ++it) {
+        int tile;
+        const Problem& q = g.pr[pick_problem(g, tid, &tile)];
+        const Params& p = q.p;
+        const int num_kt = (p.K + TBK - 1) / TBK;
+        // M = 256 (two CTAs x 128 rows), N = BN2
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+                               ((uint32_t)(BN2 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+        const uint32_t a_lbo = p.a_mn_major ? TBK * 128 : 16, b_lbo = p.b_mn_major ? TBK * 128 : 16;
+        const uint32_t a_step = (p.a_mn_major ? 2048u : 32u) >> 4, b_step = (p.b_mn_major ? 2048u : 32u) >> 4;
+        const int b = it & 1;
+        if (!mbar_wait(acc_empty(b), (((uint32_t)it >> 1) & 1u) ^ 1u)) { atomicOr(&g_bf16_status, 4u); *abort_flag = 1; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(b * BN2);
+        for (int kt = 0; kt < num_kt; ++kt) {
+          if (!mbar_wait(full_bar(s), ph)) { atomicOr(&g_bf16_status, 2u); *abort_flag = 1; stop = true; break; }
+          if (*abort_flag) { stop = true; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_s = tiles + s * STAGE_BYTES;
+          uint32_t al = desc_lo(a_s, a_lbo), bl = desc_lo(a_s + TILE_BYTES, b_lbo);
+#pragma unroll
+          for (int k = 0; k < TBK / 16; ++k) {
+            const uint32_t acc = (kt > 0 || k > 0) ? 1u : 0u;
+            if (SPLIT) {
+              mma_f16_pair_h(tmem_acc, al + LO_OFF, d_hi, bl, d_hi, idesc, acc);
+              mma_f16_pair_h(tmem_acc, al, d_hi, bl + LO_OFF, d_hi, idesc, 1u);
+              mma_f16_pair_h(tmem_acc, al, d_hi, bl, d_hi, idesc, 1u);
+            } else {
+              mma_f16_pair_h(tmem_acc, al, d_hi, bl, d_hi, idesc, acc);
+            }
+            al += a_step; bl += b_step;
+          }
+#pragma unroll
+          for (int i = 0; i < STAGES; ++i)
+            if (i == s) { umma_commit_pair(eb0[i]); umma_commit_pair(eb1[i]); }
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (!stop) { umma_commit_pair(af0[b]); umma_commit_pair(af1[b]); }
+      }
+    }
+  } else {
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const uint32_t slot0 = epi + (uint32_t)ew * (2 * EPI_SLOT_BYTES);
+    EpiState est;
+    const uint32_t ae[2] = {map_to_cta(acc_empty(0), 0), map_to_cta(acc_empty(1), 0)};      // the leader's barriers
+    int it = 0;
+    for (int tid = cluster_id; tid < total_tiles; tid += nclusters, ++it) {
+      int tile;
+      const Problem& q = g.pr[pick_problem(g, tid, &tile)];
+      const Params& p = q.p;
+      const int m0 = (tile / q.tiles_n) * 256 + (int)rank * TBM, n0 = (tile % q.tiles_n) * BN2;
+      const int b = it & 1;
+      const bool acc_ok = __all_sync(0xffffffffu, mbar_wait_idle(acc_full(b), ((uint32_t)it >> 1) & 1u));
+      if (!acc_ok && lane == 0) { atomicOr(&g_bf16_status, 8u); *abort_flag = 1; }
+      if (!acc_ok || __any_sync(0xffffffffu, *abort_flag != 0)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t tmem_acc = tmem_base + (uint32_t)(b * BN2) + ((uint32_t)(quarter * 32) << 16);
+      const int row0 = m0 + quarter * 32;
+      epilogue_rows(q, p, tmem_acc, row0, n0, BN2, slot0, r_bar(ew, 0), r_bar(ew, 1), est, lane, abort_flag);
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(ae[b]);
+    }
+    if (lane == 0) bulk_wait_all();
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();     // neither CTA leaves (or frees TMEM) while the other may still read its shared memory or signal its barriers
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(PairPCfg<SPLIT, BN2>::TMEM) : "memory");
+  }
+}
+
 struct MapKey {
   const void* base; int64_t inner, outer, ld; int bi, bo, f32;
   bool operator<(const MapKey& o) const {
@@ -902,19 +1105,20 @@ bool gemm_pairs_enabled() {
 static int pick_pair_mode(const PairGemm* gs, int n, int tile_mode) {
   static const int env = [] { const char* e = getenv("PMB_GEMM_PAIR"); return e ? atoi(e) : -1; }();
   const int forced = tile_mode >= 0 ? tile_mode : env;
-  if (forced >= 0 && forced <= 2) return forced;
-  int64_t clusters = 0, min_k = INT64_MAX;
+  if (forced >= 0 && forced <= 4) return forced;          // 3 / 4: the persistent CTA-pair kernel with 256x128 / 256x256 tiles
+  // 256x256 CTA-pair tiles on the persistent pair kernel fetch half the operand bytes per flop and read half as
+  // much shared memory per MMA.  Alone, at 2048 tokens, they win where there is at least half a wave of the 74
+  // cluster slots (in_proj forward 36.8 against 39.6 us, dnormed 23.1 against 28.2, dW_in 41.4 against 55.7) and lose
+  // below (out_proj forward 33.3 against 27.0 us at 24 clusters); inside the training step, where other streams'
+  // kernels fill the SMs a short launch leaves idle, the threshold that measured best is 18 clusters per product
+  // (step 13.35 ms with the single-CTA kernel everywhere, 13.05 at 37, 12.86 at 18, 12.95 at 12).
+  // 256x128 pair tiles measured no faster than single-CTA tiles.  PMB_GEMM_PAIR_MIN overrides the threshold.
+  static const int half_wave = [] { const char* e = getenv("PMB_GEMM_PAIR_MIN"); return e ? atoi(e) : 18; }();
   for (int i = 0; i < n; ++i) {
     if (gs[i].M <= 128) return 0;        // a pair tile would be half empty
-    clusters += cdiv(gs[i].M, 256) * cdiv(gs[i].N, 256);
-    if (gs[i].K < min_k) min_k = gs[i].K;
+    if (cdiv(gs[i].M, 256) * cdiv(gs[i].N, 256) < half_wave) return 0;
   }
-  // 256x256 pair tiles fetch half the operand bytes per flop and win where the main loop dominates: several full
-  // waves of the 74 CTA pairs and a long K (65 k tokens, K = 3224: 458 against 358 TFLOP/s).  With a short K the
-  // one-tile-per-cluster kernel spends as long in its prologue and epilogue as in the loop and the persistent
-  // single-CTA kernel is as fast or faster (K = 768, 1536 at 65 k tokens: equal; the LM head at 1024 rows, K = 768 and
-  // 1024: 6 % less GEMM time).  256x128 pair tiles measured no faster than single-CTA tiles.
-  return (clusters >= 4 * 74 && min_k >= 2048) ? 2 : 0;
+  return 4;
 }
 
 // C (fp32) = op(A) op(B) (+ R) with both operands given as bf16 pairs: three kind::f16 MMAs per k-step.
@@ -958,9 +1162,9 @@ pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n, int tile
     bytes += 4.0 * ((double)M * K + (double)K * N + (double)M * N * (e.R ? 2 : 1));
   }
   int pair_mode = pick_pair_mode(gs, n, tile_mode);
-  for (int i = 0; i < n; ++i) if (gs[i].emit.hi) pair_mode = 0;      // (only the single-CTA kernel writes the pair output)
+  for (int i = 0; i < n; ++i) if (gs[i].emit.hi && pair_mode <= 2) pair_mode = 0;      // (the one-tile-per-cluster kernels do not write the pair output)
   if (pair_mode) {
-    const int bn2 = pair_mode == 2 ? 256 : 128;
+    const int bn2 = (pair_mode == 2 || pair_mode == 4) ? 256 : 128;
     PMB_SMEM_OPT_IN((PairCfg<true, 256>::SMEM_BYTES), gemm_bf16_pair_kernel<true, 256>);
     PMB_SMEM_OPT_IN((PairCfg<true, 128>::SMEM_BYTES), gemm_bf16_pair_kernel<true, 128>);
     int64_t clusters = 0;
@@ -972,6 +1176,20 @@ pmb_status gemm_pairs_group(cudaStream_t st, const PairGemm* gs, int n, int tile
       q.tiles_n = (int)cdiv(e.N, bn2);
       q.tiles = (int)(cdiv(e.M, 256) * cdiv(e.N, bn2));
       clusters += q.tiles;
+    }
+    if (pair_mode >= 3) {
+      ProfScope prof(st, "gemm_bf16x2", flops, bytes);
+      const int64_t slots = persistent_grid(148) / 2;
+      const unsigned grid = 2u * (unsigned)(clusters < slots ? clusters : slots);
+      if (pair_mode == 4) {
+        PMB_SMEM_OPT_IN((PairPCfg<true, 256>::SMEM_BYTES), gemm_bf16_pairp_kernel<true, 256>);
+        gemm_bf16_pairp_kernel<true, 256><<<grid, NTHREADS, PairPCfg<true, 256>::SMEM_BYTES, st>>>(g, (int)clusters);
+      } else {
+        PMB_SMEM_OPT_IN((PairPCfg<true, 128>::SMEM_BYTES), gemm_bf16_pairp_kernel<true, 128>);
+        gemm_bf16_pairp_kernel<true, 128><<<grid, NTHREADS, PairPCfg<true, 128>::SMEM_BYTES, st>>>(g, (int)clusters);
+      }
+      PMB_LAUNCHED();
+      return PMB_OK;
     }
     ProfScope prof(st, pair_mode == 2 ? "gemm_bf16x2_pair256" : "gemm_bf16x2_pair128", flops, bytes);
     if (pair_mode == 2) gemm_bf16_pair_kernel<true, 256><<<(unsigned)(2 * clusters), NTHREADS, PairCfg<true, 256>::SMEM_BYTES, st>>>(g);
