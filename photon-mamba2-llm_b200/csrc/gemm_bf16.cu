@@ -1015,13 +1015,17 @@ pmb_status gemm_bf16(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int6
   for (int i = 1; i < MAX_GROUP; ++i) { g.pr[i].tiles_n = 1; g.pr[i].tiles = 0; }
   {
     static const int env = [] { const char* e = getenv("PMB_GEMM_PAIR"); return e ? atoi(e) : -1; }();
+    static const int min_clusters = [] { const char* e = getenv("PMB_GEMM_PAIR_MIN"); return e ? atoi(e) : 18; }();
     const int64_t clusters = cdiv(M, 256) * cdiv(N, 256);
-    const bool pair = env >= 0 ? env != 0 : (M > 128 && clusters >= 4 * 74);
+    const bool pair = env >= 0 ? env != 0 : (M > 128 && clusters >= min_clusters);
     if (pair) {
-      PMB_SMEM_OPT_IN((PairCfg<false, 256>::SMEM_BYTES), gemm_bf16_pair_kernel<false, 256>);
+      // 256x256 tiles on the persistent CTA-pair kernel (see pick_pair_mode)
+      PMB_SMEM_OPT_IN((PairPCfg<false, 256>::SMEM_BYTES), gemm_bf16_pairp_kernel<false, 256>);
       q.tiles_n = (int)cdiv(N, 256); q.tiles = (int)clusters;
-      ProfScope prof(st, "gemm_bf16_pair256", 2.0 * M * N * K, 2.0 * ((double)M * K + (double)K * N) + (out_bf16 ? 2.0 : 4.0) * M * N * (R ? 2 : 1));
-      gemm_bf16_pair_kernel<false, 256><<<(unsigned)(2 * clusters), NTHREADS, PairCfg<false, 256>::SMEM_BYTES, st>>>(g);
+      ProfScope prof(st, "gemm_bf16", 2.0 * M * N * K, 2.0 * ((double)M * K + (double)K * N) + (out_bf16 ? 2.0 : 4.0) * M * N * (R ? 2 : 1));
+      const int64_t slots = persistent_grid(148) / 2;
+      const unsigned grid = 2u * (unsigned)(clusters < slots ? clusters : slots);
+      gemm_bf16_pairp_kernel<false, 256><<<grid, NTHREADS, PairPCfg<false, 256>::SMEM_BYTES, st>>>(g, (int)clusters);
       PMB_LAUNCHED();
       return PMB_OK;
     }
