@@ -113,8 +113,9 @@ int32_t pmb_selftest_device_once(void);
  * tiles (cta_group::2): both operands are split into (hi, lo) bf16 pairs (hi + lo carries 16 mantissa bits) and each
  * k-step issues hi*hi + lo*hi + hi*lo with kind::f16, fp32 accumulation.  Error ~1e-5 of the result's scale (the
  * 3xTF32 kernels: ~1e-6), about twice their speed.  Auto takes the pair engine when the operands are 16-byte aligned
- * with row lengths that are multiples of 8 (the persistent kernel, or 256x256 CTA-pair tiles when there are at least
- * 296 of them and K >= 2048), else 3xTF32 when its alignment rules hold, else FMA; the environment variable
+ * with row lengths that are multiples of 8 (a persistent kernel of 256x256 CTA-pair tiles when M > 128 and the product
+ * has at least 18 such tiles -- PMB_GEMM_PAIR_MIN changes the 18 -- else the persistent single-CTA kernel), else 3xTF32
+ * when its alignment rules hold, else FMA; the environment variable
  * PMB_GEMM_ENGINE=tf32 keeps auto off engine 4, =simt forces FMA.  Engine 4 keeps the split operands in a
  * library-owned scratch buffer that grows on demand (cudaMalloc inside the call); pmb_gemm_reserve_scratch() sizes it
  * ahead of time: 4*(|A| + |B|) bytes of the largest product. */
