@@ -307,6 +307,8 @@ static size_t bf16_stage_layout(int B, int T, int H, int P, int N, int G, int Q,
 extern "C" size_t pmb_ssd_workspace_bytes_bf16(int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
                                                int32_t d_state, int32_t n_groups, int32_t block_len) {
   if (ssd_check(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len) != PMB_OK) return 0;
+  if (ssd16_supported(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len))
+    return ssd16_ws_layout(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, nullptr, 0, nullptr, nullptr, nullptr);
   return bf16_stage_layout(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, nullptr, 0, nullptr, nullptr);
 }
 
@@ -317,6 +319,16 @@ extern "C" pmb_status pmb_ssd_scan_fwd_bf16(void* stream, int32_t batch, int32_t
                                             void* d_ws, size_t ws_bytes) {
   PMB_TRY(ssd_check(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len));
   if (!d_x || !d_a || !d_b || !d_c || !d_y || !d_ws) return fail(PMB_ERR_ARG, "ssd_scan_fwd_bf16: NULL argument");
+  if (ssd16_supported(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len)) {
+    // the inputs go to the tensor cores as they are
+    if ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_b) | reinterpret_cast<uintptr_t>(d_c) | reinterpret_cast<uintptr_t>(d_y)) & 15)
+      return fail(PMB_ERR_SHAPE, "ssd_scan_fwd_bf16: x, b, c and y must be 16-byte aligned");
+    SsdWs w16;
+    if (ssd16_ws_layout(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, d_ws, ws_bytes, &w16, nullptr, nullptr) == 0)
+      return fail(PMB_ERR_WORKSPACE, "ssd bf16 workspace too small");
+    return ssd16_fwd(static_cast<cudaStream_t>(stream), batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, d_x, d_a, d_b, d_c,
+                     d_init_state, d_y, d_final_state, w16);
+  }
   SsdWs ws; Bf16Stage sg;
   if (bf16_stage_layout(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, d_ws, ws_bytes, &ws, &sg) == 0)
     return fail(PMB_ERR_WORKSPACE, "ssd bf16 workspace too small");
@@ -337,6 +349,15 @@ extern "C" pmb_status pmb_ssd_scan_bwd_bf16(void* stream, int32_t batch, int32_t
                                             void* d_ws, size_t ws_bytes) {
   PMB_TRY(ssd_check(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len));
   if (!d_a || !d_dy || !d_dx || !d_da || !d_db || !d_dc || !d_ws) return fail(PMB_ERR_ARG, "ssd_scan_bwd_bf16: NULL argument");
+  if (ssd16_supported(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len)) {
+    if ((reinterpret_cast<uintptr_t>(d_dy) | reinterpret_cast<uintptr_t>(d_dx) | reinterpret_cast<uintptr_t>(d_db) | reinterpret_cast<uintptr_t>(d_dc)) & 15)
+      return fail(PMB_ERR_SHAPE, "ssd_scan_bwd_bf16: dy, dx, db and dc must be 16-byte aligned");
+    SsdWs w16; float *db32 = nullptr, *dc32 = nullptr;
+    if (ssd16_ws_layout(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, d_ws, ws_bytes, &w16, &db32, &dc32) == 0)
+      return fail(PMB_ERR_WORKSPACE, "ssd bf16 workspace too small");
+    return ssd16_bwd(static_cast<cudaStream_t>(stream), batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, d_a, d_dy,
+                     d_dx, d_da, d_db, d_dc, w16, db32, dc32);
+  }
   SsdWs ws; Bf16Stage sg;
   if (bf16_stage_layout(batch, seqlen, n_heads, d_head, d_state, n_groups, block_len, d_ws, ws_bytes, &ws, &sg) == 0)
     return fail(PMB_ERR_WORKSPACE, "ssd bf16 workspace too small");

@@ -90,6 +90,14 @@ size_t ssd_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base
 // the same buffers taken from a caller's arena in two parts: bit 0 = forward-written / backward-read, bit 1 = backward only
 struct Arena;
 void ssd_ws_take(Arena& ar, int B, int T, int H, int P, int N, int G, int Q, SsdWs* w, int part);
+// The scan on bf16 inputs as they are (plain bf16 tensor-core operands, fp32 recurrence; no fp32 staging copies).
+// Shapes: d_head 64, d_state 64 or 128, block_len % 128 == 0, at most 64 chunks per sequence.
+bool ssd16_supported(int B, int T, int H, int P, int N, int G, int Q);
+size_t ssd16_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base, size_t bytes, SsdWs* out, float** db32, float** dc32);
+pmb_status ssd16_fwd(cudaStream_t st, int B, int T, int H, int P, int N, int G, int Q, const uint16_t* x, const float* a,
+                     const uint16_t* b, const uint16_t* c, const float* init_state, uint16_t* y, float* final_state, const SsdWs& ws);
+pmb_status ssd16_bwd(cudaStream_t st, int B, int T, int H, int P, int N, int G, int Q, const float* a, const uint16_t* dy,
+                     uint16_t* dx, float* da, uint16_t* db, uint16_t* dc, const SsdWs& ws, float* db32, float* dc32);
 pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, float* y, int64_t ldy,
                    float* final_state, const SsdWs& ws);
 // Backward.  dy (stride lddy) is the gradient w.r.t. y (skip term included when in.D != NULL).

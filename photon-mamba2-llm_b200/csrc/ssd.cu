@@ -16,6 +16,7 @@
 // This file holds the SIMT (fp32 FMA) engine: one 64x64-tile kernel template, specialised by small functor
 // structs that say how to read operand elements and where results go.
 #include <cstdlib>
+#include <cuda_bf16.h>
 #include "common.cuh"
 #include "kernels.h"
 #include "bgemm.cuh"
@@ -469,7 +470,7 @@ __global__ void __launch_bounds__(256) state_scan_kernel(SsdP p, float* __restri
         if (VEC == 4) {
           *reinterpret_cast<float4*>(slot) = make_float4(run[0], run[1 % VEC], run[2 % VEC], run[3 % VEC]);
           // the same values as a bf16 pair: the state operand of the fused intra-chunk kernel
-          if (pair_hi) store_pair4(pair_hi + (slot - buf), pair_lo + (slot - buf), run[0], run[1 % VEC], run[2 % VEC], run[3 % VEC]);
+          if (pair_hi) store_pair4(pair_hi + (slot - buf), pair_lo ? pair_lo + (slot - buf) : nullptr, run[0], run[1 % VEC], run[2 % VEC], run[3 % VEC]);
         }
         else slot[0] = run[0];
 #pragma unroll
@@ -541,7 +542,7 @@ __global__ void __launch_bounds__(1024) state_scan_rev_dot_kernel(SsdP p, float*
           if (e < NP) {
             const float4 r = run[it];
             *reinterpret_cast<float4*>(buf + base + e) = r;
-            store_pair4(pair_hi + base + e, pair_lo + base + e, r.x, r.y, r.z, r.w);
+            store_pair4(pair_hi + base + e, pair_lo ? pair_lo + base + e : nullptr, r.x, r.y, r.z, r.w);
             dot = fmaf(r.x, hv[j][it].x, fmaf(r.y, hv[j][it].y, fmaf(r.z, hv[j][it].z, fmaf(r.w, hv[j][it].w, dot))));
             run[it] = make_float4(fmaf(dec[j], r.x, q[j][it].x), fmaf(dec[j], r.y, q[j][it].y), fmaf(dec[j], r.z, q[j][it].z), fmaf(dec[j], r.w, q[j][it].w));
           }
@@ -562,7 +563,7 @@ __global__ void __launch_bounds__(1024) state_scan_rev_dot_kernel(SsdP p, float*
 // true when the merged kernel took the launch
 static bool launch_state_scan_rev_dot(cudaStream_t st, const SsdP& p, float* buf, uint16_t* pair_hi, uint16_t* pair_lo, float* dsend) {
   const int64_t quads = (int64_t)p.N * p.P / 4;
-  if ((p.P & 3) || !pair_hi || !pair_lo || !p.hprev || p.nc > SCAN_DOT_MAX_NC || quads > 4 * 1024) return false;
+  if ((p.P & 3) || !pair_hi || !p.hprev || p.nc > SCAN_DOT_MAX_NC || quads > 4 * 1024) return false;
   const int items = quads <= 1024 ? 1 : (quads <= 2048 ? 2 : 4);
   const unsigned threads = (unsigned)(((quads + items - 1) / items + 31) / 32 * 32);
   const unsigned grid = (unsigned)(p.B * p.H);
@@ -762,10 +763,13 @@ struct WSums { const float* rpart; const float* csum; const float* esum; const f
 // CTAs fit on an SM, so that the 192 CTAs of a 2048-token launch at 24 heads are resident at once (one CTA per SM
 // meant a second wave of 44 CTAs).
 constexpr int ROWS_THREADS = 256;
+// LEAN16 (the bf16-input scan: no dt, no skip term, dx = dx~ already written by the fused kernel): only <dY, y_off>
+// is formed per row, dY read as bf16 from dy16 (rows of H*P).
+template <bool LEAN16>
 __global__ void __launch_bounds__(ROWS_THREADS, 2) chunk_rows_finish_w_kernel(SsdP p, WSums ws, float* __restrict__ dx, int64_t lddx,
                                                                            const float* __restrict__ dd, float* __restrict__ da_out,
                                                                            float* __restrict__ ddt_out, float* __restrict__ part,
-                                                                           SsdGrads::RawDt raw) {
+                                                                           SsdGrads::RawDt raw, const uint16_t* __restrict__ dy16) {
   __shared__ float s_ddtx[PREP_MAX_Q], s_dS[PREP_MAX_Q], s_dD[PREP_MAX_Q], s_dt[PREP_MAX_Q], s_e[PREP_MAX_Q], wsum[ROWS_THREADS / 32], red[32];
   constexpr int NHW = ROWS_THREADS / 16;
   const int w = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
@@ -793,6 +797,21 @@ __global__ void __launch_bounds__(ROWS_THREADS, 2) chunk_rows_finish_w_kernel(Ss
     }
     for (int j = l16; j < P4; j += 16) {
       float4 xv[2], dxt[2], dyv[2], yo[2];
+      if (LEAN16) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (t[u] < p.Q) {
+            const int64_t tk = tok0 + t[u];
+            const uint2 d = reinterpret_cast<const uint2*>(dy16 + tk * hp + h * p.P)[j];
+            yo[u] = reinterpret_cast<const float4*>(ws.yoff + tk * hp + h * p.P)[j];
+            dyv[u] = make_float4(__uint_as_float(d.x << 16), __uint_as_float(d.x & 0xffff0000u), __uint_as_float(d.y << 16), __uint_as_float(d.y & 0xffff0000u));
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+          if (t[u] < p.Q) s2[u] = fmaf(dyv[u].x, yo[u].x, fmaf(dyv[u].y, yo[u].y, fmaf(dyv[u].z, yo[u].z, fmaf(dyv[u].w, yo[u].w, s2[u]))));
+        continue;
+      }
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         if (t[u] < p.Q) {
@@ -917,7 +936,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, int nsplit,
   if (mode == 0 && pair_hi) {       // dG as a bf16 pair: it is only ever an operand of the dC / dB contractions
     uint32_t h, l;
     split_bf16_pair(s, h, l);
-    pair_hi[batch * mn + r] = (uint16_t)h; pair_lo[batch * mn + r] = (uint16_t)l;
+    pair_hi[batch * mn + r] = (uint16_t)h;
+    if (pair_lo) pair_lo[batch * mn + r] = (uint16_t)l;
   } else if (mode == 0) {
     out[batch * mn + r] = accumulate ? out[batch * mn + r] + s : s;
   } else {
@@ -1099,7 +1119,7 @@ static FusedArgs fused_args(const SsdIn& in, const SsdWs& ws) {
   fa.S = ws.S;
   const int64_t pitch = 2 * (int64_t)in.G * in.N;
   fa.b = Op16{ws.bc_hi, ws.bc_lo, pitch};
-  fa.c = Op16{ws.bc_hi + in.G * in.N, ws.bc_lo + in.G * in.N, pitch};
+  fa.c = Op16{ws.bc_hi + in.G * in.N, ws.bc_lo ? ws.bc_lo + in.G * in.N : nullptr, pitch};
   return fa;
 }
 
@@ -1257,7 +1277,7 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
                           reinterpret_cast<uintptr_t>(g.dx) | reinterpret_cast<uintptr_t>(p.dxt)) % 16 == 0);
     if (fz) {
       WSums wsm{ws.rpart, ws.csum, ws.esum, ws.yoff, p.Q / 128};
-      chunk_rows_finish_w_kernel<<<(unsigned)nbch, ROWS_THREADS, 0, st>>>(p, wsm, g.dx, g.lddx, dsend, g.da, g.ddt, ws.part, in.dt ? g.raw : SsdGrads::RawDt{});
+      chunk_rows_finish_w_kernel<false><<<(unsigned)nbch, ROWS_THREADS, 0, st>>>(p, wsm, g.dx, g.lddx, dsend, g.da, g.ddt, ws.part, in.dt ? g.raw : SsdGrads::RawDt{}, nullptr);
       PMB_LAUNCHED();
     } else if (vec_ok && nbch <= 4 * 148 && p.Q <= PREP_MAX_Q) {
       chunk_rows_finish_kernel<<<(unsigned)nbch, PREP_THREADS, 0, st>>>(p, g.dx, g.lddx, dsend, g.da, g.ddt, ws.part);
@@ -1380,6 +1400,193 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
     PMB_TRY(reduce(op.nsplit, p.N, 2, g.db, g.lddbc));
   }
   return PMB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The scan on bf16 inputs as they are (the bf16-storage mode of the block, mamba2/block.rs:203-208: x, B, C in
+// bf16, the recurrence in fp32).  x, B, C and dY go to the tensor cores as plain bf16 operands (one MMA per
+// product instead of the three of an fp32 pair), a, S, the chunk states and every accumulator stay fp32, y and dx
+// leave the fused kernels as bf16.  No fp32 copy of any (B,T,H,P) tensor is made.
+// ---------------------------------------------------------------------------------------------
+
+// dst[tk,h,:] = bf16(src[tk,h,:] * f):  mode 0: f = exp(S_end - S_t) (operand of the chunk states and of dB),
+// mode 1: f = exp(S_t) (operand of d(states) and of dC).  Eight elements per thread.
+__global__ void __launch_bounds__(256) scale_rows16_kernel(const uint16_t* __restrict__ src, const float* __restrict__ S,
+                                                           uint16_t* __restrict__ dst, int64_t rows, int T, int H, int P, int Q, int mode) {
+  const int P8 = P >> 3;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * H * P8) return;
+  const int j = (int)(i % P8); const int64_t w = i / P8; const int h = (int)(w % H); const int64_t tk = w / H;
+  const int t = (int)(tk % T);
+  const float* sp = S + ((tk / T) * H + h) * T;
+  const float f = mode == 0 ? __expf(sp[(t / Q) * Q + Q - 1] - sp[t]) : __expf(sp[t]);
+  const int64_t o = (tk * H + h) * (int64_t)P + 8 * j;
+  const uint4 v = *reinterpret_cast<const uint4*>(src + o);
+  const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+  uint32_t out[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const __nv_bfloat162 r = __floats2bfloat162_rn(__uint_as_float(in[e] << 16) * f, __uint_as_float(in[e] & 0xffff0000u) * f);
+    out[e] = *reinterpret_cast<const uint32_t*>(&r);
+  }
+  *reinterpret_cast<uint4*>(dst + o) = make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+bool ssd16_supported(int B, int T, int H, int P, int N, int G, int Q) {
+  if (!fused_enabled() || !ssd_fused_supported(P, N, Q, false) || P != 64) return false;
+  if (Q <= 0 || T % Q != 0 || Q > PREP_MAX_Q || !(G == 1 || G == H)) return false;
+  if (T / Q > SCAN_DOT_MAX_NC || (int64_t)N * P / 4 > 4 * 1024) return false;        // the one-launch reverse scan
+  return (int64_t)B * T < (1LL << 31) && (int64_t)B * (T / Q) * H * N < (1LL << 31);
+}
+
+// Workspace of the bf16-input scan: the fields of SsdWs that its kernels touch (every *_lo stays NULL, which is how the
+// contractions know that the operands are plain bf16), plus fp32 landing buffers for dB and dC.
+size_t ssd16_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* base, size_t bytes, SsdWs* out, float** db32, float** dc32) {
+  Arena ar(base, bytes);
+  SsdWs w{};
+  const int nc = T / Q;
+  const size_t hp = (size_t)B * T * H * P, gn = (size_t)B * T * G * N, stn = (size_t)B * nc * H * N * P, qq = (size_t)B * nc * G * Q * Q;
+  const size_t bth = (size_t)B * T * H;
+  w.S = ar.take<float>(bth);
+  w.hprev = ar.take<float>(stn);
+  w.hlast = ar.take<float>((size_t)B * H * N * P);
+  w.xs_hi = ar.take<uint16_t>(hp);
+  w.xt_hi = ar.take<uint16_t>(hp);
+  w.bc_hi = ar.take<uint16_t>(2 * gn);
+  w.hp_hi = ar.take<uint16_t>(stn);
+  w.yoff = ar.take<float>(hp);
+  w.dh = ar.take<float>(stn);
+  w.rows = ar.take<float>(bth);
+  w.part = ar.take<float>((size_t)B * nc * 3 * H);
+  {
+    const size_t nbcg = (size_t)B * nc * G;
+    const size_t dbc = (size_t)ssd_pairs_dbc_nsplit(B, T, H, N, G, Q) * nbcg * Q * N;
+    const size_t dgp = (size_t)ssd_pairs_dg_nsplit(B, T, H, G, Q) * nbcg * Q * Q;
+    w.splitk = ar.take<float>(dbc > dgp ? dbc : dgp);
+  }
+  w.dys_hi = ar.take<uint16_t>(hp);
+  w.dg_hi = ar.take<uint16_t>(qq);
+  w.dh_hi = ar.take<uint16_t>(stn);
+  w.csum = ar.take<float>(bth);
+  w.esum = ar.take<float>(bth);
+  w.rpart = ar.take<float>(bth * (Q / 128));
+  float* b32 = ar.take<float>(gn);
+  float* c32 = ar.take<float>(gn);
+  if (out) *out = w;
+  if (db32) *db32 = b32;
+  if (dc32) *dc32 = c32;
+  return ar.ok ? ar.used() : 0;
+}
+
+static SsdIn ssd16_in(int B, int T, int H, int P, int N, int G, int Q, const float* a) {
+  SsdIn in{};
+  in.B = B; in.T = T; in.H = H; in.P = P; in.N = N; in.G = G; in.Q = Q;
+  in.ldx = (int64_t)H * P; in.a = a; in.ldbc = (int64_t)G * N;
+  return in;
+}
+
+pmb_status ssd16_fwd(cudaStream_t st, int B, int T, int H, int P, int N, int G, int Q, const uint16_t* x, const float* a,
+                     const uint16_t* b, const uint16_t* c, const float* init_state, uint16_t* y, float* final_state, const SsdWs& ws) {
+  const SsdIn in = ssd16_in(B, T, H, P, N, G, Q, a);
+  SsdP p;
+  PMB_TRY(fill_params(in, ws, &p));
+  const int nbch = p.B * p.nc * p.H;
+  const int64_t tok = (int64_t)B * T, hp = (int64_t)H * P, gn = (int64_t)G * N;
+  {
+    ProfScope prof(st, "ssd_chunk_cumsum", 0.0, 8.0 * tok * p.H);
+    chunk_cumsum_kernel<<<(unsigned)cdiv((int64_t)nbch * 32, 256), 256, 0, st>>>(p, CumsumRaw{});
+    PMB_LAUNCHED();
+  }
+  {
+    // B | C side by side (the layout every contraction's tensor maps describe) and x, which the backward reads again
+    ProfScope prof(st, "ssd16_keep_inputs", 0.0, 4.0 * tok * (hp + 2 * gn));
+    PMB_CUDA(cudaMemcpy2DAsync(ws.bc_hi, (size_t)(4 * gn), b, (size_t)(2 * gn), (size_t)(2 * gn), (size_t)tok, cudaMemcpyDeviceToDevice, st));
+    PMB_CUDA(cudaMemcpy2DAsync(ws.bc_hi + gn, (size_t)(4 * gn), c, (size_t)(2 * gn), (size_t)(2 * gn), (size_t)tok, cudaMemcpyDeviceToDevice, st));
+    PMB_CUDA(cudaMemcpyAsync(ws.xt_hi, x, (size_t)(tok * hp) * 2, cudaMemcpyDeviceToDevice, st));
+  }
+  {
+    ProfScope prof(st, "ssd16_prescale_x", 0.0, 4.0 * tok * hp);
+    scale_rows16_kernel<<<(unsigned)cdiv(tok * H * (P / 8), 256), 256, 0, st>>>(x, ws.S, ws.xs_hi, tok, T, H, P, Q, 0);
+    PMB_LAUNCHED();
+  }
+  PMB_TRY(ssd_pairs_state(st, in, ws, 0));
+  {
+    ProfScope prof(st, "ssd_state_pass", 0.0, 8.0 * (double)p.B * p.H * p.N * p.P * p.nc);
+    PMB_TRY(launch_state_scan(st, p, p.hprev, init_state, p.hlast, 0, ws.hp_hi, nullptr));
+  }
+  FusedArgs fa = fused_args(in, ws);
+  fa.v = Op16{ws.xt_hi, nullptr, hp};
+  fa.state = Op16{ws.hp_hi, nullptr, p.P};
+  fa.out16 = y; fa.ldo = hp;
+  fa.off_out = ws.yoff;
+  PMB_TRY(ssd_fused(st, 0, fa));
+  if (final_state) PMB_CUDA(cudaMemcpyAsync(final_state, ws.hlast, (size_t)p.B * p.H * p.N * p.P * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  return PMB_OK;
+}
+
+pmb_status ssd16_bwd(cudaStream_t st, int B, int T, int H, int P, int N, int G, int Q, const float* a, const uint16_t* dy,
+                     uint16_t* dx, float* da, uint16_t* db, uint16_t* dc, const SsdWs& ws_in, float* db32, float* dc32) {
+  const SsdIn in = ssd16_in(B, T, H, P, N, G, Q, a);
+  SsdWs ws = ws_in;
+  ws.dy_hi = const_cast<uint16_t*>(dy); ws.dy_lo = nullptr;
+  SsdP p;
+  PMB_TRY(fill_params(in, ws, &p));
+  const int nbch = p.B * p.nc * p.H, nbcg = p.B * p.nc * p.G;
+  const int64_t tok = (int64_t)B * T, hp = (int64_t)H * P, gn = (int64_t)G * N;
+  float* dsend = ws.rows;
+  {
+    ProfScope prof(st, "ssd16_prescale_dy", 0.0, 4.0 * tok * hp);
+    scale_rows16_kernel<<<(unsigned)cdiv(tok * H * (P / 8), 256), 256, 0, st>>>(dy, ws.S, ws.dys_hi, tok, T, H, P, Q, 1);
+    PMB_LAUNCHED();
+  }
+  PMB_TRY(ssd_pairs_state(st, in, ws, 1));
+  {
+    ProfScope prof(st, "ssd_bwd_state_pass", 0.0, 12.0 * p.B * p.H * p.N * p.P * p.nc);
+    if (!launch_state_scan_rev_dot(st, p, p.dh, ws.dh_hi, nullptr, dsend)) return fail(PMB_ERR_UNSUPPORTED, "ssd16: reverse scan shape");
+    PMB_LAUNCHED();
+  }
+  {
+    FusedArgs fa = fused_args(in, ws);
+    fa.v = Op16{dy, nullptr, hp};
+    fa.state = Op16{ws.dh_hi, nullptr, p.P};
+    fa.out16 = dx; fa.ldo = hp;
+    fa.xt = Op16{ws.xt_hi, nullptr, hp};
+    fa.csum = ws.csum; fa.esum = ws.esum; fa.rpart = ws.rpart;
+    PMB_TRY(ssd_fused(st, 1, fa));
+  }
+  {
+    ProfScope prof(st, "ssd_bwd_rows", 0.0, tok * p.H * (6.0 * p.P + 32.0));
+    WSums wsm{ws.rpart, ws.csum, ws.esum, ws.yoff, p.Q / 128};
+    chunk_rows_finish_w_kernel<true><<<(unsigned)nbch, ROWS_THREADS, 0, st>>>(p, wsm, nullptr, 0, dsend, da, nullptr, ws.part, SsdGrads::RawDt{}, dy);
+    PMB_LAUNCHED();
+  }
+  auto reduce = [&](int nsplit, int cols, int mode, float* out, int64_t ld, int tile) -> pmb_status {
+    if (nsplit <= 1) return PMB_OK;
+    const int64_t total = (int64_t)nbcg * p.Q * cols;
+    splitk_reduce_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(ws.splitk, nsplit, p.Q, cols, mode, p.G, p.Q, out, ld, total, tile, 0,
+                                                                     mode == 0 ? ws.dg_hi : nullptr, nullptr);
+    PMB_LAUNCHED();
+    return PMB_OK;
+  };
+  {
+    ProfScope prof(st, "ssd_bwd_dg_pair", 2.0 * tok * p.H * p.Q * p.P, 0.0);
+    const int nsg = ssd_pairs_dg_nsplit(p.B, p.T, p.H, p.G, p.Q);
+    PMB_TRY(ssd_pairs_dg(st, in, ws, nsg));
+    PMB_TRY(reduce(nsg, p.Q, 0, nullptr, 0, 128));
+  }
+  const int ns = ssd_pairs_dbc_nsplit(p.B, p.T, p.H, p.N, p.G, p.Q);
+  {
+    ProfScope prof(st, "ssd_bwd_dc_pair", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
+    PMB_TRY(ssd_pairs_dbc(st, in, ws, 0, dc32, gn, ns, ws.splitk));
+    PMB_TRY(reduce(ns, p.N, 1, dc32, gn, BM));
+  }
+  PMB_TRY(cast_f32_bf16(st, dc32, dc, tok * gn));
+  {
+    ProfScope prof(st, "ssd_bwd_db_pair", 2.0 * tok * p.N * (p.G * p.Q + (double)p.H * p.P), 0.0);
+    PMB_TRY(ssd_pairs_dbc(st, in, ws, 1, db32, gn, ns, ws.splitk));
+    PMB_TRY(reduce(ns, p.N, 2, db32, gn, BM));
+  }
+  return cast_f32_bf16(st, db32, db, tok * gn);
 }
 
 }  // namespace pmb

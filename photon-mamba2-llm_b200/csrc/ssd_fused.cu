@@ -94,6 +94,7 @@ struct Params {
   int H, hpg, Q, nc, nb, T, N;
   const float* S;
   float* out; int64_t ldo;
+  uint16_t* out16;          // when set: the result goes here as bf16 (same row pitch, in elements) instead of to `out`
   const float* x; int64_t ldx; const float* D;
   float* off_out;           // mode 0, optional: (B,T,H,P) the carried-state part of y, exp(S_t) C_t h_prev
   float* csum; float* esum; // mode 1: (B,T,H)  c_s = sum_{t>s} W[t,s];  e_s = exp(S_end - S_s) <x~_s, B_s dh>
@@ -487,6 +488,7 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
           }
         }
         float4* dst = reinterpret_cast<float4*>(p.out + trow * p.ldo + h * P + c0);
+        uint2* dst16 = reinterpret_cast<uint2*>(p.out16 + trow * p.ldo + h * P + c0);
         const float4* xs = (MODE == 0 && p.D) ? reinterpret_cast<const float4*>(p.x + trow * p.ldx + h * P + c0) : nullptr;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -499,7 +501,12 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
             const float4 q = (c0 == 32 * grp) ? xpre[j] : xs[j];
             o.x = fmaf(dv, q.x, o.x); o.y = fmaf(dv, q.y, o.y); o.z = fmaf(dv, q.z, o.z); o.w = fmaf(dv, q.w, o.w);
           }
-          dst[j] = o;
+          if (p.out16) {
+            const __nv_bfloat162 b0 = __floats2bfloat162_rn(o.x, o.y), b1 = __floats2bfloat162_rn(o.z, o.w);
+            dst16[j] = make_uint2(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1));
+          } else {
+            dst[j] = o;
+          }
         }
       }
     }
@@ -597,7 +604,7 @@ static pmb_status launch(cudaStream_t st, const FusedArgs& a) {
   if (NS == 1) { ms.rop[1] = ms.rop[0]; ms.cop[1] = ms.cop[0]; ms.v[1] = ms.v[0]; ms.st[1] = ms.st[0]; ms.xr[1] = ms.xr[0]; }
   Params p{};
   p.H = a.H; p.hpg = a.H / a.G; p.Q = a.Q; p.nc = nc; p.nb = a.Q / RB; p.T = a.T; p.N = a.N;
-  p.S = a.S; p.out = a.out; p.ldo = a.ldo; p.x = a.x; p.ldx = a.ldx; p.D = a.D;
+  p.S = a.S; p.out = a.out; p.out16 = a.out16; p.ldo = a.ldo; p.x = a.x; p.ldx = a.ldx; p.D = a.D;
   p.off_out = a.off_out; p.csum = a.csum; p.esum = a.esum; p.rpart = a.rpart;
   p.status = status_ptr();
   PMB_SMEM_OPT_IN(GE::SMEM, ssd_fused_kernel<MODE, NS, NK, PB>);
@@ -646,7 +653,8 @@ pmb_status ssd_fused(cudaStream_t st, int mode, const FusedArgs& a) {
   if (mode == 1 && (!a.xt.hi || !a.csum || !a.esum || !a.rpart)) return fail(PMB_ERR_ARG, "ssd_fused: mode 1 needs x~ and the three sum outputs");
   if ((int64_t)a.B * a.T >= (1LL << 31) || (int64_t)a.B * (a.T / a.Q) * a.H * a.N >= (1LL << 31))
     return fail(PMB_ERR_SHAPE, "ssd_fused: too many rows for 32-bit tile coordinates");
-  if ((a.ldo & 3) || (reinterpret_cast<uintptr_t>(a.out) & 15) || (a.D && ((a.ldx & 3) || (reinterpret_cast<uintptr_t>(a.x) & 15))))
+  if (!a.out && !a.out16) return fail(PMB_ERR_ARG, "ssd_fused: no output");
+  if ((a.ldo & 3) || ((reinterpret_cast<uintptr_t>(a.out) | reinterpret_cast<uintptr_t>(a.out16)) & 15) || (a.D && ((a.ldx & 3) || (reinterpret_cast<uintptr_t>(a.x) & 15))))
     return fail(PMB_ERR_SHAPE, "ssd_fused: output and x rows must be 16-byte aligned");
   const double tok = (double)a.B * a.T;
   // algorithmic work: G per head (2 Q N), masked product (2 Q P) over the causal half (counted in full), state term (2 N P)

@@ -16,6 +16,7 @@ struct FusedArgs {
   Op16 v;                  // mode 0: x~ = x*dt (B*T, H*P);  mode 1: dY (B*T, H*P)
   Op16 state;              // mode 0: h_prev (B*nc*H*N, P);  mode 1: dh (B*nc*H*N, P)   (rows of P, contiguous)
   float* out; int64_t ldo; // mode 0: y;  mode 1: dx~   (token rows, head h at column h*P)
+  uint16_t* out16;         // when set, the result is written here as bf16 (row pitch ldo elements) and `out` is not used
   const float* x; int64_t ldx; const float* D;   // mode 0: skip term D[h] * x (D == NULL: none)
   float* off_out;          // mode 0, optional: (B,T,H,P) the carried-state part of y, exp(S_t) C_t h_prev
   // mode 1 only: x~ (the rows of the CTA, for dM = dY x~^T) and the sums of W[t,s] = dM[t,s] G[t,s] exp(S_t - S_s), s < t
@@ -27,6 +28,7 @@ struct FusedArgs {
 
 // Shapes the fused kernels take: block_len a multiple of 128 (at most 1024); d_state and d_head in {64, 128} with
 // plain bf16 operands, d_state = d_head = 64 with (hi, lo) pairs (what fits the shared-memory plan of both modes).
+// The other contractions below take d_head = 64 only.
 bool ssd_fused_supported(int P, int N, int Q, bool pairs);
 
 // mode 0: Y[t,:]   = sum_{s<=t} (C_t.B_s) exp(S_t-S_s) x~_s + exp(S_t) C_t h_prev + D x_t          per (b, chunk, head)

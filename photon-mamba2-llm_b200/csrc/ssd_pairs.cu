@@ -6,8 +6,8 @@
 //   dC[t,n]      = sum_{s<=t} dG[t,s] B[s,n] + sum_h sum_p dYs_h[t,p] h_prev_h[n,p]
 //   dB[s,n]      = sum_{t>=s} dG[t,s] C[t,n] + sum_h sum_p xs_h[s,p]  dh_h[n,p]
 // (mamba2/ssd_ops.rs:201-234 and its autograd compute the same quantities op by op.)
-// Shapes: block_len % 128 == 0, d_state = d_head = 64 (where the fused kernel runs); other shapes keep the 3xTF32 /
-// FMA engines.
+// Shapes: block_len % 128 == 0, d_state = d_head = 64 with (hi, lo) pairs; with plain bf16 operands (no lo arrays in
+// the workspace: the bf16-input scan) d_state may also be 128.  Other shapes keep the 3xTF32 / FMA engines.
 #include "common.cuh"
 #include "kernels.h"
 #include "pair_bgemm.cuh"
@@ -40,8 +40,9 @@ struct PP {
 constexpr int MAX_Q = 1024;
 
 // ---- states (MODE 0) / dstates (MODE 1): maps 0 = B or C (MN-major: n contiguous, token rows), 1 = xs or dYs (MN-major)
+template <int NS_>
 struct PState {
-  static constexpr int BN = 64, NS = 2;
+  static constexpr int BN = 64, NS = NS_;
   static constexpr bool SEG_EPI = false;
   static constexpr int AUX_FLOATS = 0;
   float* aux;
@@ -69,8 +70,9 @@ struct PState {
 
 // ---- dG: one segment per head (K = d_head), folded with that head's decay mask in registers.
 // maps 0 = dY (K-major rows t), 1 = x~ (K-major rows s)
+template <int NS_>
 struct PDG {
-  static constexpr int BN = 128, NS = 2;
+  static constexpr int BN = 128, NS = NS_;
   static constexpr bool SEG_EPI = true;
   static constexpr int AUX_FLOATS = 2 * MAX_Q;   // two halves of S (Q), one per segment in flight
   float* aux;
@@ -119,16 +121,17 @@ struct PDG {
       for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
     } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) store_pair4(p.dg_hi + o + 4 * j, p.dg_lo + o + 4 * j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      for (int j = 0; j < 8; ++j)
+        store_pair4(p.dg_hi + o + 4 * j, NS == 2 ? p.dg_lo + o + 4 * j : nullptr, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
     }
   }
 };
 
 // ---- dC (MODE 0) / dB (MODE 1).  maps: 0 = dG (MODE 0: K-major rows t; MODE 1: MN-major, s contiguous, t rows),
 // 1 = B or C (MN-major), 2 = dYs or xs (K-major rows), 3 = h_prev or dh (K-major rows n)
-template <int MODE>
+template <int MODE, int NS_>
 struct PDBC {
-  static constexpr int BN = 64, NS = 2;
+  static constexpr int BN = 64, NS = NS_;
   static constexpr bool SEG_EPI = false;
   static constexpr int AUX_FLOATS = 0;
   float* aux;
@@ -196,6 +199,7 @@ unsigned int* status_ptr() {
 // logical map i of the set <- the (hi, lo) arrays of one operand
 pmb_status set_map(MapSet* ms, int i, const uint16_t* hi, const uint16_t* lo, int64_t d0, int64_t d1, int64_t d2, int64_t s0, int64_t s1, int b0, int b1) {
   PMB_TRY(sf::bf16_map3(&ms->m[2 * i], hi, d0, d1, d2, s0, s1, b0, b1));
+  if (!lo) { ms->m[2 * i + 1] = ms->m[2 * i]; return PMB_OK; }      // plain bf16 operand: the lo map is never used
   return sf::bf16_map3(&ms->m[2 * i + 1], lo, d0, d1, d2, s0, s1, b0, b1);
 }
 
@@ -206,13 +210,14 @@ pmb_status ssd_pairs_state(cudaStream_t st, const SsdIn& in, const SsdWs& ws, in
   p.st_out = mode == 0 ? ws.hprev : ws.dh;
   const int64_t tok = (int64_t)p.B * p.T, bcp = 2 * (int64_t)p.G * p.N, hp = (int64_t)p.H * p.P;
   const uint16_t* a_hi = mode == 0 ? ws.bc_hi : ws.bc_hi + p.G * p.N;
-  const uint16_t* a_lo = mode == 0 ? ws.bc_lo : ws.bc_lo + p.G * p.N;
+  const uint16_t* a_lo = !ws.bc_lo ? nullptr : (mode == 0 ? ws.bc_lo : ws.bc_lo + p.G * p.N);
   MapSet ms{};
   PMB_TRY(set_map(&ms, 0, a_hi, a_lo, p.N, tok, p.G, bcp, p.N, 64, 64));
   PMB_TRY(set_map(&ms, 1, mode == 0 ? ws.xs_hi : ws.dys_hi, mode == 0 ? ws.xs_lo : ws.dys_lo, p.P, tok, p.H, hp, p.P, 64, 64));
   for (int i = 4; i < 8; ++i) ms.m[i] = ms.m[0];
   ProfScope prof(st, mode == 0 ? "ssd_chunk_state_pair" : "ssd_bwd_dstate_pair", 2.0 * tok * p.H * p.N * p.P, 0.0);
-  return pbg::launch(st, ms, mk<PState>(p, p.N, p.P), p.B * p.nc * p.H, status_ptr());
+  if (!ws.bc_lo) return pbg::launch(st, ms, mk<PState<1>>(p, p.N, p.P), p.B * p.nc * p.H, status_ptr());
+  return pbg::launch(st, ms, mk<PState<2>>(p, p.N, p.P), p.B * p.nc * p.H, status_ptr());
 }
 
 // Head-split factor of a per-group contraction with `ctas` CTAs per split: as many splits as fit the machine in ONE wave
@@ -228,7 +233,7 @@ static int pick_head_split(int64_t ctas, int hpg, int ctas_per_sm) {
 
 int ssd_pairs_dg_nsplit(int B, int T, int H, int G, int Q) {
   const int nbcg = B * (T / Q) * G, hpg = H / G, qt = Q / pbg::BM;
-  return pick_head_split((int64_t)nbcg * (qt * (qt + 1) / 2), hpg, pbg::Geometry<PDG::BN, PDG::NS>::CTAS_PER_SM);
+  return pick_head_split((int64_t)nbcg * (qt * (qt + 1) / 2), hpg, pbg::Geometry<PDG<2>::BN, 2>::CTAS_PER_SM);
 }
 
 pmb_status ssd_pairs_dg(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int nsplit) {
@@ -239,13 +244,14 @@ pmb_status ssd_pairs_dg(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int n
   PMB_TRY(set_map(&ms, 0, ws.dy_hi, ws.dy_lo, p.P, tok, p.H, hp, p.P, 64, 128));
   PMB_TRY(set_map(&ms, 1, ws.xt_hi, ws.xt_lo, p.P, tok, p.H, hp, p.P, 64, 128));
   for (int i = 4; i < 8; ++i) ms.m[i] = ms.m[0];
-  return pbg::launch(st, ms, mk<PDG>(p, p.Q, p.Q), p.B * p.nc * p.G * nsplit, status_ptr());
+  if (!ws.dy_lo) return pbg::launch(st, ms, mk<PDG<1>>(p, p.Q, p.Q), p.B * p.nc * p.G * nsplit, status_ptr());
+  return pbg::launch(st, ms, mk<PDG<2>>(p, p.Q, p.Q), p.B * p.nc * p.G * nsplit, status_ptr());
 }
 
 int ssd_pairs_dbc_nsplit(int B, int T, int H, int N, int G, int Q) {
   const int nbcg = B * (T / Q) * G, hpg = H / G;
   const int tiles = (Q / pbg::BM) * (int)cdiv(N, 64);
-  return pick_head_split((int64_t)nbcg * tiles, hpg, pbg::Geometry<PDBC<0>::BN, PDBC<0>::NS>::CTAS_PER_SM);
+  return pick_head_split((int64_t)nbcg * tiles, hpg, pbg::Geometry<PDBC<0, 2>::BN, 2>::CTAS_PER_SM);
 }
 
 pmb_status ssd_pairs_dbc(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int mode, float* out, int64_t ld, int nsplit, float* part) {
@@ -259,13 +265,15 @@ pmb_status ssd_pairs_dbc(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int 
     PMB_TRY(set_map(&ms, 1, ws.bc_hi, ws.bc_lo, p.N, tok, p.G, bcp, p.N, 64, 64));
     PMB_TRY(set_map(&ms, 2, ws.dys_hi, ws.dys_lo, p.P, tok, p.H, hp, p.P, 64, 128));
     PMB_TRY(set_map(&ms, 3, ws.hp_hi, ws.hp_lo, p.P, nbch * p.N, 1, p.P, (int64_t)p.N * p.P, 64, 64));
-    return pbg::launch(st, ms, mk<PDBC<0>>(p, p.Q, p.N), (int)nbcg * nsplit, status_ptr());
+    if (!ws.bc_lo) return pbg::launch(st, ms, mk<PDBC<0, 1>>(p, p.Q, p.N), (int)nbcg * nsplit, status_ptr());
+    return pbg::launch(st, ms, mk<PDBC<0, 2>>(p, p.Q, p.N), (int)nbcg * nsplit, status_ptr());
   }
   PMB_TRY(set_map(&ms, 0, ws.dg_hi, ws.dg_lo, p.Q, nbcg * p.Q, 1, p.Q, (int64_t)p.Q * p.Q, 64, 64));
-  PMB_TRY(set_map(&ms, 1, ws.bc_hi + p.G * p.N, ws.bc_lo + p.G * p.N, p.N, tok, p.G, bcp, p.N, 64, 64));
+  PMB_TRY(set_map(&ms, 1, ws.bc_hi + p.G * p.N, ws.bc_lo ? ws.bc_lo + p.G * p.N : nullptr, p.N, tok, p.G, bcp, p.N, 64, 64));
   PMB_TRY(set_map(&ms, 2, ws.xs_hi, ws.xs_lo, p.P, tok, p.H, hp, p.P, 64, 128));
   PMB_TRY(set_map(&ms, 3, ws.dh_hi, ws.dh_lo, p.P, nbch * p.N, 1, p.P, (int64_t)p.N * p.P, 64, 64));
-  return pbg::launch(st, ms, mk<PDBC<1>>(p, p.Q, p.N), (int)nbcg * nsplit, status_ptr());
+  if (!ws.bc_lo) return pbg::launch(st, ms, mk<PDBC<1, 1>>(p, p.Q, p.N), (int)nbcg * nsplit, status_ptr());
+  return pbg::launch(st, ms, mk<PDBC<1, 2>>(p, p.Q, p.N), (int)nbcg * nsplit, status_ptr());
 }
 
 }  // namespace pmb

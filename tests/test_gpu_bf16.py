@@ -102,7 +102,10 @@ def test_lm_step_bf16_storage(pm):
     lm.close()
 
 
-@pytest.mark.parametrize("B,T,H,P,N,G,Q", [(1, 512, 4, 64, 128, 1, 256), (2, 128, 4, 16, 8, 4, 32)])
+# the first four shapes take the native bf16 scan (plain bf16 tensor-core operands: d_head 64, d_state 64 / 128, block_len
+# a multiple of 128, grouped or per-head B / C), the last one the widen -> fp32 scan -> cast route
+@pytest.mark.parametrize("B,T,H,P,N,G,Q", [(1, 512, 4, 64, 128, 1, 256), (2, 512, 8, 64, 64, 1, 128), (1, 768, 4, 64, 128, 4, 256),
+                                           (3, 384, 2, 64, 64, 1, 384), (2, 128, 4, 16, 8, 4, 32)])
 def test_ssd_scan_bf16_inputs_fp32_state(pm, B, T, H, P, N, G, Q):
     # BASELINE configs[4] dims at reduced batch/heads: bf16 x, B, C; dt = softplus(N(-2, 0.5)); A = -exp(U[log 1, log 16])
     x = randn((B, T, H, P), 1).bfloat16(); b = randn((B, T, G, N), 2).bfloat16(); c = randn((B, T, G, N), 3).bfloat16()
@@ -124,3 +127,12 @@ def test_ssd_scan_bf16_inputs_fp32_state(pm, B, T, H, P, N, G, Q):
     assert_close(da, ar.grad, tol=BF16_TOL, what="da")
     assert_close(db.float(), br.grad, tol=BF16_TOL, what="db")
     assert_close(dc.float(), cr.grad, tol=BF16_TOL, what="dc")
+    # final state, and a second segment that starts from it: against the fp32 scan on the same (bf16-rounded) values
+    ref = pm.SsdScan(x.float().cuda(), a.cuda(), b.float().cuda(), c.float().cuda(), Q)
+    _, fs_ref = ref.forward(want_final_state=True)
+    assert_close(fs, fs_ref, tol=BF16_TOL, what="final state")
+    y2_ref, fs2_ref = ref.forward(init_state=fs_ref, want_final_state=True)
+    y2, fs2 = scan.forward(init_state=fs_ref, want_final_state=True)
+    assert_close(y2.float(), y2_ref, tol=BF16_TOL, what="y from a carried state")
+    assert_close(fs2, fs2_ref, tol=BF16_TOL, what="final state from a carried state")
+    assert pm.device_status() == 0
