@@ -44,8 +44,10 @@ struct Geometry {
   static constexpr int STAGE_BYTES = NS * PART;
   // 64-wide tiles: two stages, so that two CTAs share an SM (the per-(batch, chunk, head) problems are short chains
   // that leave the SM idle between dependent steps); wider tiles: as many stages as fit in ~190 KiB, at most four
-  static constexpr int STAGES = BN <= 64 ? 2 : ((190 * 1024) / STAGE_BYTES > 4 ? 4 : (190 * 1024) / STAGE_BYTES);
-  static constexpr int CTAS_PER_SM = (BN <= 64 && STAGES * STAGE_BYTES <= 100 * 1024) ? 2 : 1;
+  // (plain bf16 operands, NS = 1: every tile is half the size and the per-segment products are one or two k-tiles long,
+  // so the 128-wide tiles take the two-stage, two-CTA plan as well)
+  static constexpr int STAGES = (BN <= 64 || NS == 1) ? 2 : ((190 * 1024) / STAGE_BYTES > 4 ? 4 : (190 * 1024) / STAGE_BYTES);
+  static constexpr int CTAS_PER_SM = ((BN <= 64 || NS == 1) && STAGES * STAGE_BYTES <= 100 * 1024) ? 2 : 1;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int SMEM_BASE = RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };

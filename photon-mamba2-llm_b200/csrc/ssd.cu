@@ -764,9 +764,9 @@ struct WSums { const float* rpart; const float* csum; const float* esum; const f
 // meant a second wave of 44 CTAs).
 constexpr int ROWS_THREADS = 256;
 // LEAN16 (the bf16-input scan: no dt, no skip term, dx = dx~ already written by the fused kernel): only <dY, y_off>
-// is formed per row, dY read as bf16 from dy16 (rows of H*P).
+// is formed per row, dY (dy16) and y_off (ws.yoff, reinterpreted) both read as bf16 rows of H*P.
 template <bool LEAN16>
-__global__ void __launch_bounds__(ROWS_THREADS, 2) chunk_rows_finish_w_kernel(SsdP p, WSums ws, float* __restrict__ dx, int64_t lddx,
+__global__ void __launch_bounds__(ROWS_THREADS, LEAN16 ? 3 : 2) chunk_rows_finish_w_kernel(SsdP p, WSums ws, float* __restrict__ dx, int64_t lddx,
                                                                            const float* __restrict__ dd, float* __restrict__ da_out,
                                                                            float* __restrict__ ddt_out, float* __restrict__ part,
                                                                            SsdGrads::RawDt raw, const uint16_t* __restrict__ dy16) {
@@ -779,7 +779,54 @@ __global__ void __launch_bounds__(ROWS_THREADS, 2) chunk_rows_finish_w_kernel(Ss
   const int P4 = p.P >> 2;
   const int hw = tid >> 4, l16 = lane & 15;
   const int64_t hp = (int64_t)p.H * p.P;
-  for (int tb = 0; tb < p.Q; tb += 2 * NHW) {
+  if (LEAN16) {
+    // eight lanes per row (16 bytes of dY and of y_off each per pass), four rows per warp and four such groups in
+    // flight per thread; y_off was written as bf16 by the fused forward kernel
+    const uint16_t* yoff16 = reinterpret_cast<const uint16_t*>(ws.yoff);
+    const int P8 = p.P >> 3, l8 = lane & 7, sub = lane >> 3;
+    constexpr int NW = ROWS_THREADS / 32, U = 4;
+    for (int tb = 0; tb < p.Q; tb += NW * 4 * U) {
+      int t[U]; float s2[U], rr[U], cs[U], es[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        t[u] = tb + (u * NW + wid) * 4 + sub; s2[u] = 0.0f; rr[u] = 0.0f; cs[u] = 0.0f; es[u] = 0.0f;
+        if (t[u] < p.Q && l8 == 0) {
+          const int64_t idx = (tok0 + t[u]) * p.H + h;
+          for (int rb = 0; rb <= t[u] / 128; ++rb) rr[u] += ws.rpart[((int64_t)w * ws.nb + rb) * p.Q + t[u]];
+          cs[u] = ws.csum[idx]; es[u] = ws.esum[idx];
+        }
+      }
+      for (int j = l8; j < P8; j += 8) {
+        uint4 d[U], y[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (t[u] < p.Q) {
+            const int64_t o = (tok0 + t[u]) * hp + h * p.P + 8 * j;
+            d[u] = *reinterpret_cast<const uint4*>(dy16 + o);
+            y[u] = *reinterpret_cast<const uint4*>(yoff16 + o);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (t[u] < p.Q) {
+            const uint32_t dw[4] = {d[u].x, d[u].y, d[u].z, d[u].w}, yw[4] = {y[u].x, y[u].y, y[u].z, y[u].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              s2[u] = fmaf(__uint_as_float(dw[e] << 16), __uint_as_float(yw[e] << 16), s2[u]);
+              s2[u] = fmaf(__uint_as_float(dw[e] & 0xffff0000u), __uint_as_float(yw[e] & 0xffff0000u), s2[u]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) s2[u] += __shfl_xor_sync(0xffffffffu, s2[u], o);
+        if (t[u] < p.Q && l8 == 0) { s_e[t[u]] = es[u]; s_dS[t[u]] = ((rr[u] - cs[u]) + s2[u]) - es[u]; }
+      }
+    }
+  }
+  for (int tb = 0; !LEAN16 && tb < p.Q; tb += 2 * NHW) {
     const int t[2] = {tb + hw, tb + NHW + hw};
     float s1[2] = {0.0f, 0.0f}, s2[2] = {0.0f, 0.0f}, s3[2] = {0.0f, 0.0f}, dtv[2] = {1.0f, 1.0f};
     float rr[2] = {0.0f, 0.0f}, cs[2] = {0.0f, 0.0f}, es[2] = {0.0f, 0.0f};
@@ -797,21 +844,6 @@ __global__ void __launch_bounds__(ROWS_THREADS, 2) chunk_rows_finish_w_kernel(Ss
     }
     for (int j = l16; j < P4; j += 16) {
       float4 xv[2], dxt[2], dyv[2], yo[2];
-      if (LEAN16) {
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          if (t[u] < p.Q) {
-            const int64_t tk = tok0 + t[u];
-            const uint2 d = reinterpret_cast<const uint2*>(dy16 + tk * hp + h * p.P)[j];
-            yo[u] = reinterpret_cast<const float4*>(ws.yoff + tk * hp + h * p.P)[j];
-            dyv[u] = make_float4(__uint_as_float(d.x << 16), __uint_as_float(d.x & 0xffff0000u), __uint_as_float(d.y << 16), __uint_as_float(d.y & 0xffff0000u));
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 2; ++u)
-          if (t[u] < p.Q) s2[u] = fmaf(dyv[u].x, yo[u].x, fmaf(dyv[u].y, yo[u].y, fmaf(dyv[u].z, yo[u].z, fmaf(dyv[u].w, yo[u].w, s2[u]))));
-        continue;
-      }
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         if (t[u] < p.Q) {
@@ -1410,9 +1442,10 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
 // ---------------------------------------------------------------------------------------------
 
 // dst[tk,h,:] = bf16(src[tk,h,:] * f):  mode 0: f = exp(S_end - S_t) (operand of the chunk states and of dB),
-// mode 1: f = exp(S_t) (operand of d(states) and of dC).  Eight elements per thread.
+// mode 1: f = exp(S_t) (operand of d(states) and of dC).  Eight elements per thread.  `keep` (optional) receives a copy of src.
 __global__ void __launch_bounds__(256) scale_rows16_kernel(const uint16_t* __restrict__ src, const float* __restrict__ S,
-                                                           uint16_t* __restrict__ dst, int64_t rows, int T, int H, int P, int Q, int mode) {
+                                                           uint16_t* __restrict__ dst, uint16_t* __restrict__ keep, int64_t rows, int T, int H,
+                                                           int P, int Q, int mode) {
   const int P8 = P >> 3;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows * H * P8) return;
@@ -1422,6 +1455,7 @@ __global__ void __launch_bounds__(256) scale_rows16_kernel(const uint16_t* __res
   const float f = mode == 0 ? __expf(sp[(t / Q) * Q + Q - 1] - sp[t]) : __expf(sp[t]);
   const int64_t o = (tk * H + h) * (int64_t)P + 8 * j;
   const uint4 v = *reinterpret_cast<const uint4*>(src + o);
+  if (keep) *reinterpret_cast<uint4*>(keep + o) = v;      // the unscaled values, for the backward
   const uint32_t in[4] = {v.x, v.y, v.z, v.w};
   uint32_t out[4];
 #pragma unroll
@@ -1454,7 +1488,7 @@ size_t ssd16_ws_layout(int B, int T, int H, int P, int N, int G, int Q, void* ba
   w.xt_hi = ar.take<uint16_t>(hp);
   w.bc_hi = ar.take<uint16_t>(2 * gn);
   w.hp_hi = ar.take<uint16_t>(stn);
-  w.yoff = ar.take<float>(hp);
+  w.yoff = reinterpret_cast<float*>(ar.take<uint16_t>(hp));      // holds bf16 here
   w.dh = ar.take<float>(stn);
   w.rows = ar.take<float>(bth);
   w.part = ar.take<float>((size_t)B * nc * 3 * H);
@@ -1498,15 +1532,14 @@ pmb_status ssd16_fwd(cudaStream_t st, int B, int T, int H, int P, int N, int G, 
     PMB_LAUNCHED();
   }
   {
-    // B | C side by side (the layout every contraction's tensor maps describe) and x, which the backward reads again
-    ProfScope prof(st, "ssd16_keep_inputs", 0.0, 4.0 * tok * (hp + 2 * gn));
+    // B | C side by side (the layout every contraction's tensor maps describe)
+    ProfScope prof(st, "ssd16_keep_bc", 0.0, 8.0 * tok * gn);
     PMB_CUDA(cudaMemcpy2DAsync(ws.bc_hi, (size_t)(4 * gn), b, (size_t)(2 * gn), (size_t)(2 * gn), (size_t)tok, cudaMemcpyDeviceToDevice, st));
     PMB_CUDA(cudaMemcpy2DAsync(ws.bc_hi + gn, (size_t)(4 * gn), c, (size_t)(2 * gn), (size_t)(2 * gn), (size_t)tok, cudaMemcpyDeviceToDevice, st));
-    PMB_CUDA(cudaMemcpyAsync(ws.xt_hi, x, (size_t)(tok * hp) * 2, cudaMemcpyDeviceToDevice, st));
   }
   {
-    ProfScope prof(st, "ssd16_prescale_x", 0.0, 4.0 * tok * hp);
-    scale_rows16_kernel<<<(unsigned)cdiv(tok * H * (P / 8), 256), 256, 0, st>>>(x, ws.S, ws.xs_hi, tok, T, H, P, Q, 0);
+    ProfScope prof(st, "ssd16_prescale_x", 0.0, 6.0 * tok * hp);      // (also keeps x for the backward, which is not handed x again)
+    scale_rows16_kernel<<<(unsigned)cdiv(tok * H * (P / 8), 256), 256, 0, st>>>(x, ws.S, ws.xs_hi, ws.xt_hi, tok, T, H, P, Q, 0);
     PMB_LAUNCHED();
   }
   PMB_TRY(ssd_pairs_state(st, in, ws, 0));
@@ -1518,7 +1551,7 @@ pmb_status ssd16_fwd(cudaStream_t st, int B, int T, int H, int P, int N, int G, 
   fa.v = Op16{ws.xt_hi, nullptr, hp};
   fa.state = Op16{ws.hp_hi, nullptr, p.P};
   fa.out16 = y; fa.ldo = hp;
-  fa.off_out = ws.yoff;
+  fa.off_out16 = reinterpret_cast<uint16_t*>(ws.yoff);
   PMB_TRY(ssd_fused(st, 0, fa));
   if (final_state) PMB_CUDA(cudaMemcpyAsync(final_state, ws.hlast, (size_t)p.B * p.H * p.N * p.P * sizeof(float), cudaMemcpyDeviceToDevice, st));
   return PMB_OK;
@@ -1536,7 +1569,7 @@ pmb_status ssd16_bwd(cudaStream_t st, int B, int T, int H, int P, int N, int G, 
   float* dsend = ws.rows;
   {
     ProfScope prof(st, "ssd16_prescale_dy", 0.0, 4.0 * tok * hp);
-    scale_rows16_kernel<<<(unsigned)cdiv(tok * H * (P / 8), 256), 256, 0, st>>>(dy, ws.S, ws.dys_hi, tok, T, H, P, Q, 1);
+    scale_rows16_kernel<<<(unsigned)cdiv(tok * H * (P / 8), 256), 256, 0, st>>>(dy, ws.S, ws.dys_hi, nullptr, tok, T, H, P, Q, 1);
     PMB_LAUNCHED();
   }
   PMB_TRY(ssd_pairs_state(st, in, ws, 1));

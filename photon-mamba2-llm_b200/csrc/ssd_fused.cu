@@ -97,6 +97,7 @@ struct Params {
   uint16_t* out16;          // when set: the result goes here as bf16 (same row pitch, in elements) instead of to `out`
   const float* x; int64_t ldx; const float* D;
   float* off_out;           // mode 0, optional: (B,T,H,P) the carried-state part of y, exp(S_t) C_t h_prev
+  uint16_t* off_out16;      // the same as bf16 (one of the two at most)
   float* csum; float* esum; // mode 1: (B,T,H)  c_s = sum_{t>s} W[t,s];  e_s = exp(S_end - S_s) <x~_s, B_s dh>
   float* rpart;             // mode 1: (B*nc*H, nb, Q)  partial row sums r_t = sum_{s<t} W[t,s] over the s of one row block
   unsigned int* status;
@@ -468,6 +469,15 @@ ssd_fused_kernel(const __grid_constant__ Maps maps, const Params p) {
             od[j] = make_float4(fac * __uint_as_float(a2[4 * j]), fac * __uint_as_float(a2[4 * j + 1]), fac * __uint_as_float(a2[4 * j + 2]),
                                 fac * __uint_as_float(a2[4 * j + 3]));
         }
+        if (MODE == 0 && p.off_out16) {
+          uint2* od = reinterpret_cast<uint2*>(p.off_out16 + (trow * p.H + h) * (int64_t)P + c0);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const __nv_bfloat162 b0 = __floats2bfloat162_rn(fac * __uint_as_float(a2[4 * j]), fac * __uint_as_float(a2[4 * j + 1]));
+            const __nv_bfloat162 b1 = __floats2bfloat162_rn(fac * __uint_as_float(a2[4 * j + 2]), fac * __uint_as_float(a2[4 * j + 3]));
+            od[j] = make_uint2(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1));
+          }
+        }
         if (MODE == 1) {
           // this row of the x~ tile: 64-element block c0 / 64, 16-byte chunks (c0 % 64) / 8 .. + 3, swizzled
           const uint8_t* xrow = base_ptr + (rop_s - base) + GE::XR_OFF + (c0 >> 6) * T128 + (r_local >> 3) * 1024 + (r_local & 7) * 128;
@@ -605,7 +615,7 @@ static pmb_status launch(cudaStream_t st, const FusedArgs& a) {
   Params p{};
   p.H = a.H; p.hpg = a.H / a.G; p.Q = a.Q; p.nc = nc; p.nb = a.Q / RB; p.T = a.T; p.N = a.N;
   p.S = a.S; p.out = a.out; p.out16 = a.out16; p.ldo = a.ldo; p.x = a.x; p.ldx = a.ldx; p.D = a.D;
-  p.off_out = a.off_out; p.csum = a.csum; p.esum = a.esum; p.rpart = a.rpart;
+  p.off_out = a.off_out; p.off_out16 = a.off_out16; p.csum = a.csum; p.esum = a.esum; p.rpart = a.rpart;
   p.status = status_ptr();
   PMB_SMEM_OPT_IN(GE::SMEM, ssd_fused_kernel<MODE, NS, NK, PB>);
   if (GE::CTAS > 1) {      // two CTAs per SM need the largest shared-memory carve-out

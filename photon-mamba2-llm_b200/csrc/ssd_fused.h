@@ -19,6 +19,7 @@ struct FusedArgs {
   uint16_t* out16;         // when set, the result is written here as bf16 (row pitch ldo elements) and `out` is not used
   const float* x; int64_t ldx; const float* D;   // mode 0: skip term D[h] * x (D == NULL: none)
   float* off_out;          // mode 0, optional: (B,T,H,P) the carried-state part of y, exp(S_t) C_t h_prev
+  uint16_t* off_out16;     // the same as bf16 (set one of the two at most)
   // mode 1 only: x~ (the rows of the CTA, for dM = dY x~^T) and the sums of W[t,s] = dM[t,s] G[t,s] exp(S_t - S_s), s < t
   Op16 xt;                 // (B*T, H*P)
   float* csum;             // (B,T,H)  c_s = sum_{t>s} W[t,s]
