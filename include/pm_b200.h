@@ -174,7 +174,11 @@ pmb_status pmb_ssd_scan_bwd(void* stream, int32_t batch, int32_t seqlen, int32_t
 
 /* Scan with bf16 inputs and fp32 state (the reference upcasts to F32 around Ops::ssd_scan, block.rs:203-208):
  * x, b, c, y and dy, dx, db, dc are contiguous bf16 (B,T,H,P) / (B,T,G,N); a, da and the states are fp32.
- * The backward reads x, b, c, y from the workspace the forward left behind (keep it untouched in between). */
+ * The backward reads x, b, c from the workspace the forward left behind (keep it untouched in between).
+ * With d_head 64, d_state 64 or 128, block_len a multiple of 128 and at most 64 chunks per sequence the bf16 tensors
+ * are the tensor-core operands as they are (one kind::f16 MMA per product; cumulative sums, decay factors, chunk
+ * states and accumulators in fp32; y and dx written as bf16 by the kernels that form them) and the eight bf16
+ * pointers must be 16-byte aligned.  Other shapes widen to fp32, run the fp32 scan and round the results. */
 size_t pmb_ssd_workspace_bytes_bf16(int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
                                     int32_t d_state, int32_t n_groups, int32_t block_len);
 pmb_status pmb_ssd_scan_fwd_bf16(void* stream, int32_t batch, int32_t seqlen, int32_t n_heads, int32_t d_head,
