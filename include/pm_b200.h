@@ -372,7 +372,9 @@ pmb_status pmb_cumsum_f32(void* stream, const float* d_x, int64_t outer, int64_t
  * (the whole table, complete right after the head's backward) is all-reduced while the stack backward runs, and the
  * token-lookup share, which exists only when the backward ends and touches at most batch * seqlen rows per rank,
  * travels as an all-gather of those rows and their token ids and is scatter-added by every rank.  Every rank must make the same calls in the
- * same order.  These calls may be captured into a CUDA graph (after one eager step, which lets NCCL set up its
+ * same order.  With two ranks the communicator is created with at most 8 NCCL CTAs (ncclConfig_t::maxCTAs: the
+ * all-reduces run beside compute kernels that want whole SMs); larger worlds keep NCCL's choice; the environment
+ * variable PMB_DP_MAX_CTAS overrides both (0 = NCCL's default).  These calls may be captured into a CUDA graph (after one eager step, which lets NCCL set up its
  * connections); NCCL then keeps the communicator alive for that graph, so destroy such graphs before pmb_dp_destroy,
  * which otherwise waits for them. */
 typedef struct pmb_dp pmb_dp;

@@ -19,6 +19,7 @@ struct NcclApi {
   void* handle = nullptr;
   ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;   // optional
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
@@ -39,6 +40,7 @@ static pmb_status load_nccl() {
   a.handle = h;
   a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
   a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
+  a.CommInitRankConfig = reinterpret_cast<decltype(a.CommInitRankConfig)>(dlsym(h, "ncclCommInitRankConfig"));
   a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(h, "ncclAllReduce"));
   a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(h, "ncclAllGather"));
   a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
@@ -87,7 +89,20 @@ extern "C" pmb_status pmb_dp_init(int32_t nranks, int32_t rank, const void* h_id
   if (cudaGetDevice(&dp->device) != cudaSuccess) return cleanup(fail(PMB_ERR_CUDA, "dp_init: no current CUDA device"));
   ncclUniqueId id;
   memcpy(&id, h_id128, sizeof(id));
-  ncclResult_t r = g_nccl.CommInitRank(&dp->comm, nranks, id, rank);
+  // The all-reduces run beside compute kernels that want whole SMs (persistent GEMMs, one-CTA-per-SM scan kernels), so
+  // the CTAs NCCL may take are capped where that was measured to pay: with two ranks a bucket needs few channels to fill
+  // the links (8: 0.2 ms of a 13.6 ms step); with four the cap cost time, so larger worlds keep NCCL's own choice.
+  // PMB_DP_MAX_CTAS overrides (0 = NCCL's default).
+  int max_ctas = nranks == 2 ? 8 : 0;
+  if (const char* e = getenv("PMB_DP_MAX_CTAS")) max_ctas = atoi(e);
+  ncclResult_t r;
+  if (max_ctas > 0 && g_nccl.CommInitRankConfig) {
+    ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+    cfg.maxCTAs = max_ctas;
+    r = g_nccl.CommInitRankConfig(&dp->comm, nranks, id, rank, &cfg);
+  } else {
+    r = g_nccl.CommInitRank(&dp->comm, nranks, id, rank);
+  }
   if (r != ncclSuccess) return cleanup(fail(PMB_ERR_CUDA, "ncclCommInitRank failed: %s", g_nccl.GetErrorString(r)));
   int least = 0, greatest = 0;
   cudaDeviceGetStreamPriorityRange(&least, &greatest);
