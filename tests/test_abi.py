@@ -43,6 +43,11 @@ def test_workspace_sizes_and_shape_errors(pm):
     # T not a multiple of block_len is rejected by the raw scan entry point
     assert pm.lib.pmb_ssd_workspace_bytes(1, 100, 2, 8, 16, 2, 64) == 0
     assert b"multiple" in pm.lib.pmb_last_error()
+    # the bf16-input scan at the scan microbenchmark's dims (B=16, T=8192, H=32, P=64, N=128) holds no fp32 copy of a
+    # (B,T,H,P) tensor: its workspace is below that of the fp32 scan at the same dims; d_head 128 takes the staging route
+    nat = pm.lib.pmb_ssd_workspace_bytes_bf16(16, 8192, 32, 64, 128, 1, 256)
+    assert 0 < nat < pm.lib.pmb_ssd_workspace_bytes(16, 8192, 32, 64, 128, 1, 256)
+    assert pm.lib.pmb_ssd_workspace_bytes_bf16(16, 8192, 32, 128, 128, 1, 256) > 2 * nat
     # n_groups must be 1 or n_heads (block.rs:128-131)
     bad = pm.Mamba2Config(d_model=128, d_state=16, d_head=32, n_heads=8, n_groups=2)
     assert pm.lib.pmb_mamba2_block_workspace_bytes(C.byref(bad.c()), 2, 128) == 0
