@@ -377,7 +377,7 @@ def lm_loss(embed: torch.Tensor, layers: list, cfg: Mamba2Config, ids: torch.Ten
 
 
 def hier_lm_loss(embed, wproj, layers0, layers1, cfg, ids, targets, group=4, cdt=torch.float32):
-    """Two-level LM of BASELINE config 3 (defined by the benchmark spec, not by the reference's PHOTON glue):
+    """Two-level benchmark LM (defined by the benchmark's configuration list, not by the reference's PHOTON glue):
     level 0 = Mamba2 stack at token rate; groups of `group` hidden states are mean-pooled and linearly projected
     into level 1, a Mamba2 stack at 1/group rate; its outputs are repeated `group` times, shifted by one group
     (causal), and added to the level-0 output before the tied LM head.  Blocks and stacks are the reference's

@@ -533,7 +533,7 @@ extern "C" pmb_status pmb_lm_step_device(pmb_lm* lm, void* stream, const int64_t
   const void* wproj = nullptr;
   if (hier) {
     // level 1: mean-pool groups of tokens, project, run the second stack at 1/group rate, add its output back
-    // shifted by one group so that no token sees its own group's future (BASELINE config 3 wiring)
+    // shifted by one group so that no token sees its own group's future (the two-level benchmark model's wiring)
     const int64_t M1 = lm->d1.M;
     wproj = h16 ? (const void*)(lm->params16 + lm->off_proj) : (const void*)(lm->params + lm->off_proj);
     PMB_TRY(hier_op(lm, st, hidden, nullptr, lm->pooled, 0));

@@ -107,7 +107,7 @@ def test_lm_step_bf16_storage(pm):
 @pytest.mark.parametrize("B,T,H,P,N,G,Q", [(1, 512, 4, 64, 128, 1, 256), (2, 512, 8, 64, 64, 1, 128), (1, 768, 4, 64, 128, 4, 256),
                                            (3, 384, 2, 64, 64, 1, 384), (2, 128, 4, 16, 8, 4, 32)])
 def test_ssd_scan_bf16_inputs_fp32_state(pm, B, T, H, P, N, G, Q):
-    # BASELINE configs[4] dims at reduced batch/heads: bf16 x, B, C; dt = softplus(N(-2, 0.5)); A = -exp(U[log 1, log 16])
+    # the scan microbenchmark's dims at reduced batch/heads: bf16 x, B, C; dt = softplus(N(-2, 0.5)); A = -exp(U[log 1, log 16])
     x = randn((B, T, H, P), 1).bfloat16(); b = randn((B, T, G, N), 2).bfloat16(); c = randn((B, T, G, N), 3).bfloat16()
     dt = torch.nn.functional.softplus(randn((B, T, H), 4, 0.5) - 2.0)
     A = -torch.exp(torch.rand(H, generator=torch.Generator().manual_seed(5)) * 2.7726)

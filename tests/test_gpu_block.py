@@ -27,7 +27,7 @@ def _oracle_block_grads(cfg, p, x, cot):
 
 
 def test_block_single_config_matches_committed_golden(pm):
-    # BASELINE config 1: B=2, T=128, D=128, I=256, H=8, P=32, N=16, G=1, Q=64, K=4, fp32
+    # the reference's CPU-runnable single-block case: B=2, T=128, D=128, I=256, H=8, P=32, N=16, G=1, Q=64, K=4, fp32
     cfg = orc.Mamba2Config(d_model=128, d_state=16, d_head=32, n_heads=8, block_len=64)
     p = orc.init_block_params(cfg, seed=1)
     x, cot = randn((2, 128, 128), 11), randn((2, 128, 128), 12)
@@ -225,7 +225,7 @@ def test_lm_checkpoint_round_trip_in_reference_format(pm, tmp_path):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, None), (torch.bfloat16, 2e-2)])
 def test_two_level_lm_config3_wiring(pm, dtype, tol):
-    # BASELINE config 3 wiring at small dims: 2 + 2 layers, pool 4, one-group causal shift
+    # the two-level benchmark model's wiring at small dims: 2 + 2 layers, pool 4, one-group causal shift
     cfg = orc.Mamba2Config(d_model=64, d_state=8, d_head=8, n_heads=8, block_len=16)
     L0, L1, B, T, V, g = 2, 2, 2, 64, 301, 4
     layers = [block_params(cfg, seed=30 + i) for i in range(L0 + L1)]
