@@ -72,11 +72,13 @@ struct Geo {
   static constexpr int V = NS * PB * T64;
   static constexpr int STAGE = COP + V;
   static constexpr int ST = NS * NK * PB * T64;
-  // TM (mode 0): the masked tile goes back into TMEM over G and is the A operand of the second product from there,
-  // so there are no masked-tile buffers in shared memory and two CTAs fit on an SM
-  static constexpr bool TM = (MODE == 0);
+  // TM: the masked tile goes back into TMEM over G and is the A operand of the second product from there, so there
+  // are no masked-tile buffers in shared memory.  Mode 0: two CTAs then fit on an SM.  Mode 1 stays at one CTA per SM
+  // (384 TMEM columns, two resident row operands) and gains only the shorter hand-over (measured: 3.5 % of the
+  // kernel with pairs, nothing with plain bf16 operands, which keep the shared-memory tile).
+  static constexpr bool TM = (MODE == 0) || (NS == 2);
   static constexpr int MOP1 = TM ? 0 : NS * T128;
-  static constexpr int BUDGET = TM ? 104 * 1024 : (MODE == 1 ? 218 : 220) * 1024;
+  static constexpr int BUDGET = MODE == 0 ? 104 * 1024 : 218 * 1024;
   static constexpr int MB = (ROP + 2 * MOP1 + 2 * STAGE <= BUDGET) ? 2 : 1;
   static constexpr int REM = BUDGET - ROP - MB * MOP1;
   static constexpr int STAGES = REM / STAGE >= 4 ? 4 : REM / STAGE;
