@@ -168,6 +168,7 @@ static pmb_status block_fwd_core(cudaStream_t st, const Dims& d, const pmb_block
   if (w.ssd.bc_hi) bc = ConvPairOut{w.ssd.bc_hi, w.ssd.bc_lo, d.I, 2 * d.G * d.N};
   PMB_TRY(conv_silu_dt_fwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, p.dt_bias, w.act, nullptr, w.ssd.bc_hi ? &bc : nullptr));
   SsdIn sin = ssd_inputs(d, p, w);
+  sin.plain16 = w16 != nullptr;
   sin.bc_pair_ready = bc.hi != nullptr;
   sin.dt_raw = w.xzd + d.I + d.X; sin.ld_raw = d.J; sin.dt_bias = p.dt_bias; sin.a_log = p.a_log;
   PMB_TRY(ssd_fwd(st, sin, nullptr, w.y, d.I, nullptr, w.ssd));
@@ -263,6 +264,7 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   uint16_t* ph = pr ? w.dxzd_hi : (w16 ? w.dxzd16 : nullptr);   // bf16 storage: plain bf16 rounding, no low part
   uint16_t* pl = pr ? w.dxzd_lo : nullptr;
   SsdIn sin = ssd_inputs(d, p, w);
+  sin.plain16 = w16 != nullptr;
   NormBwdExtra ex{};
   ex.dz_hi = ph; ex.dz_lo = pl;
   if ((pr || w16) && ssd_tc_supported(sin) && (d.P % 4 == 0)) {

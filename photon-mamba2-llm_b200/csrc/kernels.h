@@ -55,6 +55,9 @@ struct SsdIn {
   bool dy_pair_ready = false;  // backward: ws.dy_hi / dy_lo (the pair of dY) were already written by the caller
   bool bc_pair_ready = false;  // forward: ws.bc_hi / bc_lo (the pairs of B | C) were already written by the caller
   bool xs_ready = false;  // forward (internal): ws.xs was already written by the fused cumsum kernel
+  // bf16-storage mode of the block: the scan's tensor-core products read the hi halves of the operand pairs alone
+  // (one MMA per product); the producers still write both halves, the recurrence and all accumulators stay fp32
+  bool plain16 = false;
   // forward only, optional: form dt and A inside the cumsum kernel.  dt = softplus(dt_raw[token*ld_raw + h] + dt_bias[h])
   // is written to `dt` and A[h] = -exp(a_log[h]) to `A` (both must then point at writable buffers).
   const float* dt_raw = nullptr; int64_t ld_raw = 0; const float* dt_bias = nullptr; const float* a_log = nullptr;

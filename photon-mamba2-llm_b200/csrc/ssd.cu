@@ -1150,8 +1150,9 @@ static FusedArgs fused_args(const SsdIn& in, const SsdWs& ws) {
   fa.B = in.B; fa.T = in.T; fa.H = in.H; fa.P = in.P; fa.N = in.N; fa.G = in.G; fa.Q = in.Q;
   fa.S = ws.S;
   const int64_t pitch = 2 * (int64_t)in.G * in.N;
-  fa.b = Op16{ws.bc_hi, ws.bc_lo, pitch};
-  fa.c = Op16{ws.bc_hi + in.G * in.N, ws.bc_lo ? ws.bc_lo + in.G * in.N : nullptr, pitch};
+  const bool pairs = ws.bc_lo && !in.plain16;
+  fa.b = Op16{ws.bc_hi, pairs ? ws.bc_lo : nullptr, pitch};
+  fa.c = Op16{ws.bc_hi + in.G * in.N, pairs ? ws.bc_lo + in.G * in.N : nullptr, pitch};
   return fa;
 }
 
@@ -1209,8 +1210,8 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
   if (lane) PMB_TRY(order_after(lane->s, lane->ev[1], st));   // C B^T (or the operand pairs) are ready
   if (fz) {
     FusedArgs fa = fused_args(in, ws);
-    fa.v = Op16{ws.xt_hi, ws.xt_lo, (int64_t)p.H * p.P};
-    fa.state = Op16{ws.hp_hi, ws.hp_lo, p.P};
+    fa.v = Op16{ws.xt_hi, in.plain16 ? nullptr : ws.xt_lo, (int64_t)p.H * p.P};
+    fa.state = Op16{ws.hp_hi, in.plain16 ? nullptr : ws.hp_lo, p.P};
     fa.out = y; fa.ldo = ldy; fa.x = in.x; fa.ldx = in.ldx; fa.D = in.D;
     fa.off_out = ws.yoff;
     PMB_TRY(ssd_fused(st, 0, fa));
@@ -1289,10 +1290,10 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   if (fz) {
     // dY as a bf16 pair (the B / C / x~ pairs were written by the forward of this scan and are still in the workspace)
     FusedArgs fa = fused_args(in, ws);
-    fa.v = Op16{ws.dy_hi, ws.dy_lo, (int64_t)p.H * p.P};
-    fa.state = Op16{ws.dh_hi, ws.dh_lo, p.P};
+    fa.v = Op16{ws.dy_hi, in.plain16 ? nullptr : ws.dy_lo, (int64_t)p.H * p.P};
+    fa.state = Op16{ws.dh_hi, in.plain16 ? nullptr : ws.dh_lo, p.P};
     fa.out = p.dxt; fa.ldo = (int64_t)p.H * p.P;
-    fa.xt = Op16{ws.xt_hi, ws.xt_lo, (int64_t)p.H * p.P};
+    fa.xt = Op16{ws.xt_hi, in.plain16 ? nullptr : ws.xt_lo, (int64_t)p.H * p.P};
     fa.csum = ws.csum; fa.esum = ws.esum; fa.rpart = ws.rpart;
     PMB_TRY(ssd_fused(st, 1, fa));
   }

@@ -205,7 +205,15 @@ pmb_status set_map(MapSet* ms, int i, const uint16_t* hi, const uint16_t* lo, in
 
 }  // namespace
 
-pmb_status ssd_pairs_state(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int mode) {
+// plain16: the same workspace seen without its lo arrays, which is how the launchers below pick one MMA per product
+static SsdWs hi_only(const SsdWs& w) {
+  SsdWs v = w;
+  v.xt_lo = v.xs_lo = v.dys_lo = v.dg_lo = v.bc_lo = v.dy_lo = v.hp_lo = v.dh_lo = nullptr;
+  return v;
+}
+
+pmb_status ssd_pairs_state(cudaStream_t st, const SsdIn& in, const SsdWs& ws_in, int mode) {
+  const SsdWs ws = in.plain16 ? hi_only(ws_in) : ws_in;
   PP p = make_pp(in, ws);
   p.st_out = mode == 0 ? ws.hprev : ws.dh;
   const int64_t tok = (int64_t)p.B * p.T, bcp = 2 * (int64_t)p.G * p.N, hp = (int64_t)p.H * p.P;
@@ -236,7 +244,8 @@ int ssd_pairs_dg_nsplit(int B, int T, int H, int G, int Q) {
   return pick_head_split((int64_t)nbcg * (qt * (qt + 1) / 2), hpg, pbg::Geometry<PDG<2>::BN, 2>::CTAS_PER_SM);
 }
 
-pmb_status ssd_pairs_dg(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int nsplit) {
+pmb_status ssd_pairs_dg(cudaStream_t st, const SsdIn& in, const SsdWs& ws_in, int nsplit) {
+  const SsdWs ws = in.plain16 ? hi_only(ws_in) : ws_in;
   PP p = make_pp(in, ws);
   p.nsplit = nsplit;
   const int64_t tok = (int64_t)p.B * p.T, hp = (int64_t)p.H * p.P;
@@ -254,7 +263,8 @@ int ssd_pairs_dbc_nsplit(int B, int T, int H, int N, int G, int Q) {
   return pick_head_split((int64_t)nbcg * tiles, hpg, pbg::Geometry<PDBC<0, 2>::BN, 2>::CTAS_PER_SM);
 }
 
-pmb_status ssd_pairs_dbc(cudaStream_t st, const SsdIn& in, const SsdWs& ws, int mode, float* out, int64_t ld, int nsplit, float* part) {
+pmb_status ssd_pairs_dbc(cudaStream_t st, const SsdIn& in, const SsdWs& ws_in, int mode, float* out, int64_t ld, int nsplit, float* part) {
+  const SsdWs ws = in.plain16 ? hi_only(ws_in) : ws_in;
   PP p = make_pp(in, ws);
   p.out = out; p.ld = ld; p.nsplit = nsplit; p.part = part;
   const int64_t tok = (int64_t)p.B * p.T, bcp = 2 * (int64_t)p.G * p.N, hp = (int64_t)p.H * p.P;
