@@ -237,8 +237,10 @@ pmb_status pmb_mamba2_block_bwd(void* stream, const pmb_mamba2_config* cfg, cons
 /* bf16-storage block ("compute dtype" bf16, block.rs:24-42): x, residual, out, dout, dx are bf16; parameters stay
  * fp32 and the caller supplies bf16 copies of the two projection weights (pmb_cast_f32_to_bf16, refreshed whenever
  * the fp32 masters change).  The projections run as bf16 GEMMs with fp32 accumulation; conv, softplus, exp, the
- * scan and the norm run in fp32 as in the reference.  Parameter gradients are fp32.  Needs d_model, d_inner and
- * in_proj_dim to be multiples of 8. */
+ * scan's recurrence (cumulative sums, decay factors, chunk states, accumulators) and the norm run in fp32 as in the
+ * reference; on the shapes the fused scan kernels take (block_len a multiple of 128, d_state = d_head = 64) the
+ * scan's tensor-core products read their operands rounded to bf16.  Parameter gradients are fp32.  Needs d_model,
+ * d_inner and in_proj_dim to be multiples of 8. */
 size_t pmb_mamba2_block_workspace_bytes_bf16(const pmb_mamba2_config* cfg, int32_t batch, int32_t seqlen);
 pmb_status pmb_mamba2_block_fwd_bf16(void* stream, const pmb_mamba2_config* cfg, const pmb_block_params* params,
                                      const uint16_t* d_in_proj_bf16, const uint16_t* d_out_proj_bf16,

@@ -1114,12 +1114,12 @@ __global__ void __launch_bounds__(256) xt_pair_kernel(const float* __restrict__ 
   const float f = dt ? dt[tk * H + h] : 1.0f;
   const float4 v = reinterpret_cast<const float4*>(x + tk * ldx + h * P)[j];
   const int64_t o = (tk * H + h) * (int64_t)P + 4 * j;
-  store_pair4(hi + o, lo + o, v.x * f, v.y * f, v.z * f, v.w * f);
+  store_pair4(hi + o, lo ? lo + o : nullptr, v.x * f, v.y * f, v.z * f, v.w * f);      // (lo == NULL: the hi halves alone are read)
   // xs = x~ exp(S_end - S_t): the operand of the chunk-state and dB contractions
   const int b = (int)(tk / T), t = (int)(tk % T);
   const float* sp = S + ((int64_t)b * H + h) * T;
   const float f2 = f * __expf(sp[(t / Q) * Q + Q - 1] - sp[t]);
-  store_pair4(xs_hi + o, xs_lo + o, v.x * f2, v.y * f2, v.z * f2, v.w * f2);
+  store_pair4(xs_hi + o, xs_lo ? xs_lo + o : nullptr, v.x * f2, v.y * f2, v.z * f2, v.w * f2);
 }
 
 // The B and C columns (adjacent in the caller's buffer when it is the block's activation buffer, else two arrays)
@@ -1137,9 +1137,9 @@ static pmb_status fused_operand_pairs(cudaStream_t st, const SsdIn& in, const Ss
     PMB_TRY(split_pair16_strided(st, in.c, rows, gn, in.ldbc, ws.bc_hi + gn, ws.bc_lo + gn, 2 * gn));
   }
   if (want_xt) {
-    ProfScope prof(st, "ssd_xt_pair", 0.0, 8.0 * rows * in.H * in.P);
-    xt_pair_kernel<<<(unsigned)cdiv(rows * in.H * (in.P / 4), 256), 256, 0, st>>>(in.x, in.ldx, in.dt, ws.xt_hi, ws.xt_lo, rows, in.H, in.P,
-                                                                                  ws.S, in.T, in.Q, ws.xs_hi, ws.xs_lo);
+    ProfScope prof(st, "ssd_xt_pair", 0.0, (in.plain16 ? 8.0 : 12.0) * rows * in.H * in.P);
+    xt_pair_kernel<<<(unsigned)cdiv(rows * in.H * (in.P / 4), 256), 256, 0, st>>>(in.x, in.ldx, in.dt, ws.xt_hi, in.plain16 ? nullptr : ws.xt_lo, rows,
+                                                                                  in.H, in.P, ws.S, in.T, in.Q, ws.xs_hi, in.plain16 ? nullptr : ws.xs_lo);
     PMB_LAUNCHED();
   }
   return PMB_OK;
