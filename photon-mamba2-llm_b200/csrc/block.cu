@@ -165,7 +165,8 @@ static pmb_status block_fwd_core(cudaStream_t st, const Dims& d, const pmb_block
   // dt = softplus(dt_raw + bias) and A = -exp(a_log) are formed by the scan's first kernel (the chunk cumsum)
   // the B | C columns leave the conv kernel as a bf16 pair too when the fused scan kernels will read them
   ConvPairOut bc{};
-  if (w.ssd.bc_hi) bc = ConvPairOut{w.ssd.bc_hi, w.ssd.bc_lo, d.I, 2 * d.G * d.N};
+  // (bf16 storage: the scan reads the hi halves alone, so the lo halves are not written)
+  if (w.ssd.bc_hi) bc = ConvPairOut{w.ssd.bc_hi, w16 ? nullptr : w.ssd.bc_lo, d.I, 2 * d.G * d.N};
   PMB_TRY(conv_silu_dt_fwd(st, d, w.xzd, p.conv1d_weight, p.conv1d_bias, p.dt_bias, w.act, nullptr, w.ssd.bc_hi ? &bc : nullptr));
   SsdIn sin = ssd_inputs(d, p, w);
   sin.plain16 = w16 != nullptr;
@@ -270,8 +271,8 @@ static pmb_status block_grads(cudaStream_t st, const Dims& d, const pmb_block_pa
   if ((pr || w16) && ssd_tc_supported(sin) && (d.P % 4 == 0)) {
     ex.S = w.ssd.S; ex.H = d.H; ex.P = d.P; ex.T = d.T; sin.dys_ready = true;
     if (w.ssd.dy_hi) {   // the scan backward runs on bf16 pairs: dY and dY exp(S) leave the norm backward as pairs
-      ex.dy_hi = w.ssd.dy_hi; ex.dy_lo = w.ssd.dy_lo; sin.dy_pair_ready = true;
-      ex.dys_hi = w.ssd.dys_hi; ex.dys_lo = w.ssd.dys_lo;
+      ex.dy_hi = w.ssd.dy_hi; ex.dy_lo = w16 ? nullptr : w.ssd.dy_lo; sin.dy_pair_ready = true;
+      ex.dys_hi = w.ssd.dys_hi; ex.dys_lo = w16 ? nullptr : w.ssd.dys_lo;
     } else {
       ex.dys = w.ssd.dys;
     }

@@ -173,7 +173,8 @@ __device__ __forceinline__ void split_bf16_pair(float v, uint32_t& h, uint32_t& 
   const uint32_t ul = __float_as_uint(v - __uint_as_float(h << 16));
   l = (ul + 0x7fffu + ((ul >> 16) & 1u)) >> 16;
 }
-// four consecutive values to the pair arrays (8-byte aligned destinations); lo == NULL: plain bf16 rounding into hi
+// four consecutive values to the pair arrays (8-byte aligned destinations); lo == NULL: plain bf16 rounding into hi.
+// Callers that index into the arrays pass `lo ? lo + offset : nullptr`, never an offset added to a null pointer.
 __device__ __forceinline__ void store_pair4(uint16_t* hi, uint16_t* lo, float a, float b, float c, float d) {
   uint32_t h[4], l[4];
   split_bf16_pair(a, h[0], l[0]); split_bf16_pair(b, h[1], l[1]); split_bf16_pair(c, h[2], l[2]); split_bf16_pair(d, h[3], l[3]);

@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(128, 8) conv_silu_fwd_kernel(const float* __re
         // the B | C columns also go out as a bf16 pair (operands of the fused scan kernels)
         if (po.hi && c >= po.col0) {
           const int64_t o16 = ((int64_t)b * T + t) * po.width + (c - po.col0);
-          store_pair4(po.hi + o16, po.lo + o16, o[0], o[1 % VEC], o[2 % VEC], o[3 % VEC]);
+          store_pair4(po.hi + o16, po.lo ? po.lo + o16 : nullptr, o[0], o[1 % VEC], o[2 % VEC], o[3 % VEC]);
         }
       }
       else dst[(int64_t)t * X] = o[0];
@@ -231,7 +231,7 @@ __device__ __forceinline__ void conv_bwd_thread(const float* __restrict__ xzd, i
     if (t < tend && tp >= t0 && tp < t1) {
       const int64_t off = ((int64_t)b * T + tp) * ldx + col0 + c;
       if (pair_hi) {       // the gradient is only a GEMM operand: write it as a (hi, lo) bf16 pair with the same pitch
-        if (VEC == 4) store_pair4(pair_hi + off, pair_lo + off, g[0], g[1 % VEC], g[2 % VEC], g[3 % VEC]);
+        if (VEC == 4) store_pair4(pair_hi + off, pair_lo ? pair_lo + off : nullptr, g[0], g[1 % VEC], g[2 % VEC], g[3 % VEC]);
         else { uint32_t h, l; split_bf16_pair(g[0], h, l); pair_hi[off] = (uint16_t)h; if (pair_lo) pair_lo[off] = (uint16_t)l; }
       } else if (VEC == 4) *reinterpret_cast<float4*>(ddst + (int64_t)tp * ldx) = make_float4(g[0], g[1 % VEC], g[2 % VEC], g[3 % VEC]);
       else ddst[(int64_t)tp * ldx] = g[0];
@@ -641,14 +641,14 @@ __global__ void __launch_bounds__(NORM_THREADS, 3) gated_rmsnorm_bwd_vec_kernel(
         PMB_NORM_LANE(x) PMB_NORM_LANE(y) PMB_NORM_LANE(z) PMB_NORM_LANE(w)
 #undef PMB_NORM_LANE
         reinterpret_cast<float4*>(dy + row * width)[i] = o_dy;
-        if (ex.dz_hi) store_pair4(ex.dz_hi + row * lddz + 4 * i, ex.dz_lo + row * lddz + 4 * i, o_dz.x, o_dz.y, o_dz.z, o_dz.w);
+        if (ex.dz_hi) store_pair4(ex.dz_hi + row * lddz + 4 * i, ex.dz_lo ? ex.dz_lo + row * lddz + 4 * i : nullptr, o_dz.x, o_dz.y, o_dz.z, o_dz.w);
         else reinterpret_cast<float4*>(dz + row * lddz)[i] = o_dz;
-        if (ex.dy_hi) store_pair4(ex.dy_hi + row * width + 4 * i, ex.dy_lo + row * width + 4 * i, o_dy.x, o_dy.y, o_dy.z, o_dy.w);
+        if (ex.dy_hi) store_pair4(ex.dy_hi + row * width + 4 * i, ex.dy_lo ? ex.dy_lo + row * width + 4 * i : nullptr, o_dy.x, o_dy.y, o_dy.z, o_dy.w);
         if (ex.dys_hi) {   // the same, as a bf16 pair (operand of the pair contractions of the scan backward)
           const int h = (4 * i) / ex.P;
           const int64_t bb = row / ex.T, tt = row % ex.T;
           const float f = __expf(ex.S[(bb * ex.H + h) * ex.T + tt]);
-          store_pair4(ex.dys_hi + row * width + 4 * i, ex.dys_lo + row * width + 4 * i, o_dy.x * f, o_dy.y * f, o_dy.z * f, o_dy.w * f);
+          store_pair4(ex.dys_hi + row * width + 4 * i, ex.dys_lo ? ex.dys_lo + row * width + 4 * i : nullptr, o_dy.x * f, o_dy.y * f, o_dy.z * f, o_dy.w * f);
         }
         if (ex.dys) {    // dys[t, h, :] = dy[t, h, :] * exp(S[b, h, t]) for the scan backward (head width ex.P is a multiple of 4)
           const int h = (4 * i) / ex.P;

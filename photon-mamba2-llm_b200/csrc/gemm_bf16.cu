@@ -1087,7 +1087,7 @@ __global__ void split_pair16_cols_kernel(const float* __restrict__ src, int64_t 
   if (i >= rows * c4) return;
   const int64_t r = i / c4, c = (i % c4) * 4;
   const float* s = src + r * ld + c;
-  store_pair4(hi + r * ld16 + c, lo + r * ld16 + c, s[0], s[1], s[2], s[3]);
+  store_pair4(hi + r * ld16 + c, lo ? lo + r * ld16 + c : nullptr, s[0], s[1], s[2], s[3]);
 }
 
 pmb_status split_pair16_strided(cudaStream_t st, const float* src, int64_t rows, int64_t cols, int64_t ld, uint16_t* hi, uint16_t* lo,

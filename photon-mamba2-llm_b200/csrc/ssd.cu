@@ -422,10 +422,10 @@ __global__ void __launch_bounds__(PREP_THREADS) chunk_prepare_kernel(SsdP p, Cum
       const int i = i0 + u * PREP_THREADS;
       if (i < total) {
         const int64_t o = (tok0 + tt[u]) * (int64_t)(p.H * p.P) + h * p.P + 4 * jj[u];
-        if (xs_hi) store_pair4(xs_hi + o, xs_lo + o, v[u].x * f[u], v[u].y * f[u], v[u].z * f[u], v[u].w * f[u]);
+        if (xs_hi) store_pair4(xs_hi + o, xs_lo ? xs_lo + o : nullptr, v[u].x * f[u], v[u].y * f[u], v[u].z * f[u], v[u].w * f[u]);
         else *reinterpret_cast<float4*>(xs + o) = make_float4(v[u].x * f[u], v[u].y * f[u], v[u].z * f[u], v[u].w * f[u]);
         // x~ = x dt as a bf16 pair: the V operand of the fused intra-chunk kernel
-        if (xt_hi) store_pair4(xt_hi + o, xt_lo + o, v[u].x * fd[u], v[u].y * fd[u], v[u].z * fd[u], v[u].w * fd[u]);
+        if (xt_hi) store_pair4(xt_hi + o, xt_lo ? xt_lo + o : nullptr, v[u].x * fd[u], v[u].y * fd[u], v[u].z * fd[u], v[u].w * fd[u]);
       }
     }
   }
@@ -1177,7 +1177,8 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
       ProfScope prof(st, "ssd_chunk_prepare", 0.0, 8.0 * tok * p.H * (1.0 + p.P));
       // at a few hundred (b,c,h) the second phase (the only one with real traffic) is short of threads: split its rows
       const unsigned ysplit = nbch <= 148 ? 4u : (nbch <= 2 * 148 ? 2u : 1u);
-      chunk_prepare_kernel<<<dim3((unsigned)nbch, ysplit), PREP_THREADS, 0, st>>>(p, raw, ws.xs, fz ? ws.xt_hi : nullptr, ws.xt_lo, fz ? ws.xs_hi : nullptr, ws.xs_lo);
+      chunk_prepare_kernel<<<dim3((unsigned)nbch, ysplit), PREP_THREADS, 0, st>>>(p, raw, ws.xs, fz ? ws.xt_hi : nullptr, in.plain16 ? nullptr : ws.xt_lo, fz ? ws.xs_hi : nullptr,
+                                                                                  in.plain16 ? nullptr : ws.xs_lo);
       PMB_LAUNCHED();
       in_tc.xs_ready = true;
       xt_ready = fz;
@@ -1205,7 +1206,7 @@ pmb_status ssd_fwd(cudaStream_t st, const SsdIn& in, const float* init_state, fl
   int64_t nel = (int64_t)p.B * p.H * p.N * p.P;
   {
     ProfScope prof(st, "ssd_state_pass", 0.0, 8.0 * nel * p.nc);
-    PMB_TRY(launch_state_scan(st, p, p.hprev, init_state, p.hlast, 0, fz ? ws.hp_hi : nullptr, ws.hp_lo));
+    PMB_TRY(launch_state_scan(st, p, p.hprev, init_state, p.hlast, 0, fz ? ws.hp_hi : nullptr, in.plain16 ? nullptr : ws.hp_lo));
   }
   if (lane) PMB_TRY(order_after(lane->s, lane->ev[1], st));   // C B^T (or the operand pairs) are ready
   if (fz) {
@@ -1232,7 +1233,7 @@ __global__ void __launch_bounds__(256) dys_pair_kernel(const float* __restrict__
   const float f = __expf(S[((tk / T) * H + h) * T + tk % T]);
   const float4 v = reinterpret_cast<const float4*>(dy + tk * lddy + h * P)[j];
   const int64_t o = (tk * H + h) * (int64_t)P + 4 * j;
-  store_pair4(hi + o, lo + o, v.x * f, v.y * f, v.z * f, v.w * f);
+  store_pair4(hi + o, lo ? lo + o : nullptr, v.x * f, v.y * f, v.z * f, v.w * f);
 }
 
 bool ssd_bwd_takes_pairs(const SsdIn& in, const float* dy, int64_t lddy, const SsdGrads& g) {
@@ -1278,10 +1279,11 @@ pmb_status ssd_bwd(cudaStream_t st, const SsdIn& in, const float* y, int64_t ldy
   if (lane) PMB_CUDA(cudaEventRecord(lane->ev[1], st));       // dY exp(S) is ready (dC reads it)
   {
     ProfScope prof(st, "ssd_bwd_state_pass", 0.0, 12.0 * p.B * p.H * p.N * p.P * p.nc);
-    if (fz && launch_state_scan_rev_dot(st, p, p.dh, ws.dh_hi, ws.dh_lo, dsend)) {
+    uint16_t* const dh_lo = in.plain16 ? nullptr : ws.dh_lo;
+    if (fz && launch_state_scan_rev_dot(st, p, p.dh, ws.dh_hi, dh_lo, dsend)) {
       PMB_LAUNCHED();
     } else {
-      PMB_TRY(launch_state_scan(st, p, p.dh, nullptr, nullptr, 1, fz ? ws.dh_hi : nullptr, ws.dh_lo));
+      PMB_TRY(launch_state_scan(st, p, p.dh, nullptr, nullptr, 1, fz ? ws.dh_hi : nullptr, dh_lo));
       state_dot_kernel<<<(unsigned)nbch, 256, 0, st>>>(p, dsend, fz ? 1 : 0);
       PMB_LAUNCHED();
     }
